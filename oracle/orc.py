@@ -1,0 +1,84 @@
+"""ctypes binding of the CPU oracle (test infrastructure; never imported by the shipped package)."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+def build():
+    subprocess.run(["make", "-C", _HERE, "liborc.so"], check=True, stdout=subprocess.DEVNULL)
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "liborc.so")
+        if not os.path.exists(path):
+            build()
+        L = ctypes.CDLL(path)
+        L.orc_world_create.restype = ctypes.c_void_p
+        L.orc_world_create.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_uint32]
+        L.orc_world_destroy.argtypes = [ctypes.c_void_p]
+        L.orc_world_reset.argtypes = [ctypes.c_void_p]
+        L.orc_world_refresh.argtypes = [ctypes.c_void_p]
+        L.orc_world_step.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_int]
+        L.orc_stage_dynamics.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        L.orc_stage_collide.argtypes = [ctypes.c_void_p]
+        L.orc_get.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_size_t]
+        L.orc_set.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p, ctypes.c_size_t]
+        L.orc_hw_threads.restype = ctypes.c_int
+        _LIB = L
+    return _LIB
+
+
+_U32 = {"pair_count", "candidate_pairs", "contact_count", "env_status", "solver_sweeps", "contact_points"}
+
+
+class World:
+    def __init__(self, blob, env_count):
+        self._blob = bytes(blob)
+        self.env_count = env_count
+        self._h = lib().orc_world_create(self._blob, len(self._blob), env_count)
+        if not self._h:
+            raise RuntimeError("oracle rejected the template")
+
+    def close(self):
+        if self._h:
+            lib().orc_world_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def step(self, n=1, threads=0):
+        lib().orc_world_step(self._h, n, threads)
+
+    def reset(self):
+        lib().orc_world_reset(self._h)
+
+    def refresh(self):
+        lib().orc_world_refresh(self._h)
+
+    def dynamics(self, integrate_velocity=False):
+        lib().orc_stage_dynamics(self._h, int(integrate_velocity))
+
+    def collide(self):
+        lib().orc_stage_collide(self._h)
+
+    def get(self, field, per_env):
+        dt = np.uint32 if field in _U32 else np.float32
+        out = np.zeros((self.env_count, per_env), dtype=dt)
+        rc = lib().orc_get(self._h, field.encode(), out.ctypes.data, out.nbytes)
+        if rc:
+            raise KeyError(f"oracle field {field} (rc={rc}, per_env={per_env})")
+        return out
+
+    def set(self, field, value):
+        dt = np.uint32 if field in _U32 else np.float32
+        a = np.ascontiguousarray(value, dtype=dt)
+        rc = lib().orc_set(self._h, field.encode(), a.ctypes.data, a.nbytes)
+        if rc:
+            raise KeyError(f"oracle field {field} (rc={rc})")
