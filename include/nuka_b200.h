@@ -1,0 +1,187 @@
+/*
+ * C ABI of the B200-native batched articulated-robot step.
+ *
+ * The entry points, handle types, result codes, descriptor layouts and state-field ids below are the ones
+ * the reference exposes for this path in src/include/nuka/nuka.h, so a caller bound to the reference's
+ * world/step interface (C, C++ via nuka.hpp, or the Python module) can bind this library instead.
+ * Each declaration cites the reference declaration it replaces.  Entry points of the reference outside the
+ * step path (rendering, sensors, checkpoints, scene export, IK, telemetry) are not provided.
+ *
+ * Additions that have no counterpart in the reference are grouped at the end and prefixed nuka_b200_ or
+ * documented as such.
+ */
+#ifndef NUKA_B200_H
+#define NUKA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* nuka.h:11-12 opaque handles (integer ids in pointer clothing, as in src/c_abi/handle_table.hpp:13-60) */
+typedef struct nuka_device_t* nuka_device_handle;
+typedef struct nuka_world_t* nuka_world_handle;
+
+/* nuka.h:20 */
+#define NUKA_MAX_CONTACT_SLOTS_PER_ENV 4u
+
+/* nuka.h:22-32 */
+typedef enum nuka_result_t {
+    NUKA_RESULT_OK = 0,
+    NUKA_RESULT_INVALID_ARG = 1,
+    NUKA_RESULT_NULL_HANDLE = 2,
+    NUKA_RESULT_CUDA_ERROR = 3,
+    NUKA_RESULT_FILE_NOT_FOUND = 4,
+    NUKA_RESULT_PARSE_ERROR = 5,
+    NUKA_RESULT_OUT_OF_MEMORY = 6,
+    NUKA_RESULT_NOT_SUPPORTED = 7,
+    NUKA_RESULT_INTERNAL = 100
+} nuka_result_t;
+
+/* nuka.h:34-41 */
+typedef struct nuka_version_t { uint16_t major, minor, patch; } nuka_version_t;
+nuka_version_t nuka_get_version(void);
+const char* nuka_result_message(nuka_result_t result);
+/* nuka.h:42-44: thread-local text of the last failure; reading clears it. */
+const char* nuka_last_error_message(void);
+
+/* nuka.h:46-55 */
+typedef struct nuka_device_desc_t {
+    uint32_t gpu_index;
+    void* cuda_stream;                 /* borrowed cudaStream_t, or NULL for an owned stream */
+    uint8_t backend_selection_layer_enabled;
+} nuka_device_desc_t;
+nuka_result_t nuka_device_create(const nuka_device_desc_t* desc, nuka_device_handle* out);
+void nuka_device_destroy(nuka_device_handle device);
+
+/* nuka.h:57-173: same member order and types.  Members this library does not act on must be zero,
+ * otherwise creation returns NUKA_RESULT_NOT_SUPPORTED (terrain/heightfield/curriculum, instancing,
+ * cloth, OGC, substeps > 1). */
+typedef struct nuka_world_desc_t {
+    const char* scene_path;            /* ".nkt" cooked template file, or "synthetic:<name>" */
+    uint32_t env_count;
+    float fixed_dt;
+    uint8_t determinism;               /* 0 or 1; larger values are INVALID_ARG */
+    uint8_t control_mode;              /* 0 = PD position (the only mode provided) */
+    uint32_t osc_task_link;
+    float terrain_step_height, terrain_step_width, terrain_platform_width, terrain_grid_width, terrain_grid_height_max;
+    uint32_t instance_count;
+    float instance_spacing;
+    uint32_t contact_family;
+    uint32_t heightfield_terrain_type, heightfield_nrow, heightfield_ncol;
+    float heightfield_cell;
+    const char* heightfield_image_path;
+    float heightfield_radius_x, heightfield_radius_y, heightfield_elevation_z, heightfield_base_z;
+    float gravity_x, gravity_y, gravity_z;   /* all zero selects (0, 0, -9.81) */
+    uint32_t curric_levels, curric_types;
+    float terrain_feature_cell;
+    uint32_t solver_vel_iters;         /* 0 keeps the template's value */
+    uint32_t solver_pos_iters;
+    float solver_contact_margin;
+    uint32_t solver_max_pairs;
+    float solver_baumgarte_max_velocity;
+    uint32_t cloth_integrator;
+    uint32_t ogc_contact_capacity;
+    float solver_overlap_recovery_velocity;
+    uint32_t solver_substeps;
+    uint32_t contact_detection_substeps;
+} nuka_world_desc_t;
+
+/* nuka.h:175 */
+nuka_result_t nuka_world_create_from_scene(nuka_device_handle device, const nuka_world_desc_t* desc, nuka_world_handle* out);
+/* nuka.h:253-255: step and step_n enqueue on the device stream and return before completion. */
+void nuka_world_destroy(nuka_world_handle world);
+nuka_result_t nuka_world_step(nuka_world_handle world);
+nuka_result_t nuka_world_step_n(nuka_world_handle world, uint32_t step_count);
+
+/* nuka.h:256-279 */
+typedef enum nuka_execution_mode_t { NUKA_EXECUTION_EAGER = 0, NUKA_EXECUTION_GRAPH = 1 } nuka_execution_mode_t;
+nuka_result_t nuka_world_set_execution_mode(nuka_world_handle world, nuka_execution_mode_t mode);
+/* nuka.h:285 */
+nuka_result_t nuka_world_set_gravity_z(nuka_world_handle world, float gravity_z);
+/* nuka.h:289-290: 1..65535 */
+nuka_result_t nuka_world_set_velocity_iterations(nuka_world_handle world, uint32_t iterations);
+nuka_result_t nuka_world_get_velocity_iterations(nuka_world_handle world, uint32_t* out_iterations);
+/* nuka.h:376 */
+nuka_result_t nuka_world_synchronize(nuka_world_handle world);
+/* nuka.h:380-385: reset keeps drive targets; an invalid id is INVALID_ARG with no env changed. */
+nuka_result_t nuka_world_reset(nuka_world_handle world);
+nuka_result_t nuka_world_reset_envs(nuka_world_handle world, const uint32_t* env_ids, uint32_t count);
+/* nuka.h:434 */
+nuka_result_t nuka_world_forward_kinematics(nuka_world_handle world);
+/* nuka.h:479-481 */
+nuka_result_t nuka_world_get_stream(nuka_world_handle world, void** out_stream);
+nuka_result_t nuka_world_record_event(nuka_world_handle world, void* cuda_event);
+
+/* nuka.h:496-964: state field ids (values as in the reference) for the fields this path serves. */
+typedef enum nuka_state_field_t {
+    NUKA_FIELD_RIGID_BODY_TRANSFORM = 0,      /* E x B x 7 f32 */
+    NUKA_FIELD_ARTICULATION_LINK_POSE = 1,    /* E x L x 7 f32 */
+    NUKA_FIELD_JOINT_POSITION = 2,            /* E x L f32, slot 0 = root */
+    NUKA_FIELD_JOINT_VELOCITY = 3,            /* E x L f32 */
+    NUKA_FIELD_CONTACT_POINTS = 5,            /* E x 4 x 3 f32: first point of the first four candidate slots */
+    NUKA_FIELD_DRIVE_TARGET = 6,              /* E x L f32, writable */
+    NUKA_FIELD_LINK_VELOCITY = 7,             /* E x L x 6 f32, angular first */
+    NUKA_FIELD_DRIVE_STIFFNESS = 8,           /* E x L f32, writable */
+    NUKA_FIELD_DRIVE_DAMPING = 9,
+    NUKA_FIELD_DRIVE_FORCE_LIMIT = 10,
+    NUKA_FIELD_BASE_POSE = 11,                /* E x 7 f32 */
+    NUKA_FIELD_VELOCITY_TARGET = 13,          /* E x L f32, writable */
+    NUKA_FIELD_CONTACT_NORMAL = 17,           /* E x 4 x 3 f32 */
+    NUKA_FIELD_JOINT_FEEDFORWARD = 22,        /* E x L f32, writable */
+    NUKA_FIELD_BODY_LINEAR_VELOCITY = 25,     /* E x B x 3 f32 */
+    NUKA_FIELD_BODY_ANGULAR_VELOCITY = 26,    /* E x B x 3 f32 */
+    NUKA_FIELD_ACTUATOR_EFFORT = 29,          /* E x L f32 */
+    NUKA_FIELD_ENV_STATUS = 39,               /* E u32 */
+    NUKA_FIELD_SOLVER_RESIDUAL = 109,         /* E x 4 f32: normal, tangent, joint, momentum */
+    /* fields without a counterpart in the reference's public enum (parity taps of this library) */
+    NUKA_B200_FIELD_JOINT_ACCELERATION = 0x10000,   /* E x L f32 */
+    NUKA_B200_FIELD_MASS_MATRIX = 0x10001,          /* E x n x n f32, filled by the dynamics stage when tapped */
+    NUKA_B200_FIELD_PAIR_COUNT = 0x10002,           /* E u32 */
+    NUKA_B200_FIELD_CANDIDATE_PAIRS = 0x10003,      /* E x S x 2 u32, ascending (a, b) */
+    NUKA_B200_FIELD_CONTACT_COUNT = 0x10004,        /* E x S u32 */
+    NUKA_B200_FIELD_CONTACT_POINT = 0x10005,        /* E x S x 4 x 3 f32 */
+    NUKA_B200_FIELD_CONTACT_NORMAL = 0x10006,       /* E x S x 4 x 3 f32 */
+    NUKA_B200_FIELD_CONTACT_DEPTH = 0x10007,        /* E x S x 4 f32 */
+    NUKA_B200_FIELD_SOLVER_SWEEPS = 0x10008,        /* E u32 */
+    NUKA_B200_FIELD_JOINT_PSEUDO_VELOCITY = 0x10009 /* E x n f32 */
+} nuka_state_field_t;
+
+/* nuka.h:1158-1166 */
+typedef struct nuka_buffer_view_t {
+    void* device_ptr;
+    size_t element_count;
+    uint32_t element_stride_bytes;
+    uint8_t dtype;                     /* 0 f32, 1 u32, 2 u64, 3 u8 */
+} nuka_buffer_view_t;
+nuka_result_t nuka_world_get_buffer_view(nuka_world_handle world, nuka_state_field_t field, nuka_buffer_view_t* out);
+/* nuka.h:1180-1187: host <-> field byte transfer; out-of-range is INVALID_ARG, unknown field NOT_SUPPORTED. */
+nuka_result_t nuka_world_upload_field(nuka_world_handle world, nuka_state_field_t field, const void* bytes, size_t nbytes, size_t byte_offset);
+nuka_result_t nuka_world_download_field(nuka_world_handle world, nuka_state_field_t field, void* bytes, size_t nbytes, size_t byte_offset);
+
+/* ---- additions (no counterpart in the reference) ---- */
+
+/* Creates a world from an in-memory cooked template (".nkt" bytes).  The reference can only obtain
+ * articulated templates by cooking scene files through importers that are outside this path. */
+nuka_result_t nuka_world_create_from_template(nuka_device_handle device, const nuka_world_desc_t* desc,
+                                              const void* template_bytes, size_t template_size, nuka_world_handle* out);
+
+typedef struct nuka_b200_world_info_t {
+    uint32_t env_count, links_per_env, bodies_per_env, dofs_per_env, contact_slots_per_env;
+    uint32_t shared_bytes_per_env, warps_per_block;
+} nuka_b200_world_info_t;
+nuka_result_t nuka_b200_world_info(nuka_world_handle world, nuka_b200_world_info_t* out);
+
+/* Runs one pipeline stage for per-stage parity checks: 1 = kinematics + drives + dynamics without the
+ * velocity update (fills JOINT_ACCELERATION and MASS_MATRIX), 2 = collision only (fills the contact taps). */
+nuka_result_t nuka_b200_world_run_stage(nuka_world_handle world, uint32_t stage);
+
+/* Kernel launches enqueued by this world since creation (for throughput reports). */
+nuka_result_t nuka_b200_world_launch_count(nuka_world_handle world, uint64_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,360 @@
+// extern "C" boundary: handle tables, result codes, thread-local error text.  No exception crosses it
+// (reference src/c_abi/error.cpp:12-60, src/c_abi/handle_table.hpp:13-60, src/c_abi/world.cpp:493-731,
+// src/c_abi/buffer.cpp:31-205).
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <mutex>
+#include <sstream>
+
+#include "../../include/nuka_b200.h"
+#include "nkb_world.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+thread_local std::string g_last_error_out;
+
+void SetError(const std::string& text) { g_last_error = text; }
+
+struct DeviceRecord {
+    int gpu = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    uint32_t worlds = 0;
+};
+
+template <typename T>
+class HandleTable {
+public:
+    uintptr_t Insert(std::unique_ptr<T> value) {
+        std::lock_guard<std::mutex> lock(mutex_);
+        for (size_t i = 0; i < slots_.size(); ++i)
+            if (!slots_[i]) { slots_[i] = std::move(value); return i + 1; }
+        slots_.push_back(std::move(value));
+        return slots_.size();
+    }
+    T* Get(uintptr_t handle) {
+        std::lock_guard<std::mutex> lock(mutex_);
+        if (handle == 0 || handle > slots_.size()) return nullptr;
+        return slots_[handle - 1].get();
+    }
+    std::unique_ptr<T> Remove(uintptr_t handle) {
+        std::lock_guard<std::mutex> lock(mutex_);
+        if (handle == 0 || handle > slots_.size()) return nullptr;
+        return std::move(slots_[handle - 1]);
+    }
+private:
+    std::mutex mutex_;
+    std::vector<std::unique_ptr<T>> slots_;
+};
+
+struct WorldRecord {
+    std::unique_ptr<nkb::World> world;
+    uintptr_t device = 0;
+};
+
+HandleTable<DeviceRecord>& Devices() { static HandleTable<DeviceRecord> t; return t; }
+HandleTable<WorldRecord>& Worlds() { static HandleTable<WorldRecord> t; return t; }
+
+template <typename Fn>
+nuka_result_t Guard(Fn&& fn) {
+    try {
+        return fn();
+    } catch (const nkb::Error& e) {
+        SetError(e.what());
+        return static_cast<nuka_result_t>(e.code);
+    } catch (const std::bad_alloc&) {
+        SetError("host allocation failed");
+        return NUKA_RESULT_OUT_OF_MEMORY;
+    } catch (const std::exception& e) {
+        SetError(e.what());
+        return NUKA_RESULT_INTERNAL;
+    } catch (...) {
+        SetError("unknown failure");
+        return NUKA_RESULT_INTERNAL;
+    }
+}
+
+nkb::World* WorldOf(nuka_world_handle h) {
+    WorldRecord* r = Worlds().Get(reinterpret_cast<uintptr_t>(h));
+    return r ? r->world.get() : nullptr;
+}
+
+nuka_result_t ValidateDesc(const nuka_world_desc_t* d) {
+    // reference src/c_abi/world.cpp:493-528
+    if (d == nullptr) { SetError("world desc is null"); return NUKA_RESULT_INVALID_ARG; }
+    if (d->env_count == 0u) { SetError("env_count must be positive"); return NUKA_RESULT_INVALID_ARG; }
+    if (d->determinism > 1u) { SetError("determinism must be 0 or 1"); return NUKA_RESULT_INVALID_ARG; }
+    if (d->fixed_dt < 0.f || d->fixed_dt != d->fixed_dt) { SetError("fixed_dt must be positive"); return NUKA_RESULT_INVALID_ARG; }
+    if (d->control_mode != 0u) { SetError("only control mode 0 (PD position) is provided"); return NUKA_RESULT_NOT_SUPPORTED; }
+    const bool unsupported = d->terrain_step_height != 0.f || d->terrain_step_width != 0.f || d->terrain_platform_width != 0.f ||
+        d->terrain_grid_width != 0.f || d->terrain_grid_height_max != 0.f || d->instance_count > 1u || d->contact_family != 0u ||
+        d->heightfield_terrain_type != 0u || (d->heightfield_image_path != nullptr && d->heightfield_image_path[0] != '\0') ||
+        d->curric_levels != 0u || d->curric_types != 0u || d->cloth_integrator != 0u || d->ogc_contact_capacity != 0u ||
+        d->solver_substeps > 1u || d->contact_detection_substeps > 1u || d->osc_task_link != 0u;
+    if (unsupported) { SetError("the world desc selects a feature outside the articulated step path"); return NUKA_RESULT_NOT_SUPPORTED; }
+    if (d->solver_vel_iters > 65535u) { SetError("solver_vel_iters exceeds 65535"); return NUKA_RESULT_INVALID_ARG; }
+    return NUKA_RESULT_OK;
+}
+
+nuka_result_t CreateWorld(nuka_device_handle device, const nuka_world_desc_t* desc, const void* blob, size_t bytes, nuka_world_handle* out) {
+    if (out == nullptr) { SetError("out handle is null"); return NUKA_RESULT_INVALID_ARG; }
+    *out = nullptr;
+    DeviceRecord* dev = Devices().Get(reinterpret_cast<uintptr_t>(device));
+    if (dev == nullptr) { SetError("device handle is null or stale"); return NUKA_RESULT_NULL_HANDLE; }
+    const nuka_result_t valid = ValidateDesc(desc);
+    if (valid != NUKA_RESULT_OK) return valid;
+    return Guard([&]() {
+        nkb::HostTemplate tpl = nkb::HostTemplate::Parse(blob, bytes);
+        if (desc->fixed_dt > 0.f) tpl.cfg.dt = desc->fixed_dt;
+        if (desc->gravity_x != 0.f || desc->gravity_y != 0.f || desc->gravity_z != 0.f) {
+            tpl.cfg.gravity[0] = desc->gravity_x; tpl.cfg.gravity[1] = desc->gravity_y; tpl.cfg.gravity[2] = desc->gravity_z;
+        }
+        if (desc->solver_vel_iters != 0u) tpl.cfg.vel_iters = desc->solver_vel_iters;
+        if (desc->solver_pos_iters != 0u) tpl.cfg.pos_iters = desc->solver_pos_iters;
+        if (desc->solver_contact_margin > 0.f) tpl.cfg.contact_margin = desc->solver_contact_margin;
+        if (desc->solver_max_pairs != 0u) tpl.cfg.max_pairs = desc->solver_max_pairs;
+        if (desc->solver_baumgarte_max_velocity > 0.f) tpl.cfg.baumgarte_max_velocity = desc->solver_baumgarte_max_velocity;
+        if (desc->solver_overlap_recovery_velocity > 0.f) tpl.cfg.overlap_recovery_velocity = desc->solver_overlap_recovery_velocity;
+        auto record = std::make_unique<WorldRecord>();
+        record->world = std::make_unique<nkb::World>(dev->gpu, dev->stream, tpl, desc->env_count);
+        record->device = reinterpret_cast<uintptr_t>(device);
+        ++dev->worlds;
+        *out = reinterpret_cast<nuka_world_handle>(Worlds().Insert(std::move(record)));
+        return NUKA_RESULT_OK;
+    });
+}
+
+}  // namespace
+
+extern "C" {
+
+nuka_version_t nuka_get_version(void) { return {0, 1, 0}; }
+
+const char* nuka_result_message(nuka_result_t result) {
+    switch (result) {
+        case NUKA_RESULT_OK: return "ok";
+        case NUKA_RESULT_INVALID_ARG: return "invalid argument";
+        case NUKA_RESULT_NULL_HANDLE: return "null or stale handle";
+        case NUKA_RESULT_CUDA_ERROR: return "CUDA error";
+        case NUKA_RESULT_FILE_NOT_FOUND: return "file not found";
+        case NUKA_RESULT_PARSE_ERROR: return "parse error";
+        case NUKA_RESULT_OUT_OF_MEMORY: return "out of memory";
+        case NUKA_RESULT_NOT_SUPPORTED: return "not supported";
+        case NUKA_RESULT_INTERNAL: return "internal error";
+    }
+    return "unknown result";
+}
+
+const char* nuka_last_error_message(void) {
+    g_last_error_out = g_last_error;
+    g_last_error.clear();
+    return g_last_error_out.c_str();
+}
+
+nuka_result_t nuka_device_create(const nuka_device_desc_t* desc, nuka_device_handle* out) {
+    if (out == nullptr || desc == nullptr) { SetError("device desc or out handle is null"); return NUKA_RESULT_INVALID_ARG; }
+    *out = nullptr;
+    return Guard([&]() {
+        int count = 0;
+        const cudaError_t err = cudaGetDeviceCount(&count);
+        if (err != cudaSuccess || count == 0) {
+            // no CPU fallback: without a CUDA device there is nothing to run on
+            SetError(std::string("no CUDA device: ") + cudaGetErrorString(err));
+            return NUKA_RESULT_CUDA_ERROR;
+        }
+        if (desc->gpu_index >= static_cast<uint32_t>(count)) { SetError("gpu_index out of range"); return NUKA_RESULT_INVALID_ARG; }
+        auto rec = std::make_unique<DeviceRecord>();
+        rec->gpu = static_cast<int>(desc->gpu_index);
+        if (cudaSetDevice(rec->gpu) != cudaSuccess) { SetError("cudaSetDevice failed"); return NUKA_RESULT_CUDA_ERROR; }
+        if (desc->cuda_stream != nullptr) rec->stream = static_cast<cudaStream_t>(desc->cuda_stream);
+        else {
+            if (cudaStreamCreateWithFlags(&rec->stream, cudaStreamNonBlocking) != cudaSuccess) { SetError("stream creation failed"); return NUKA_RESULT_CUDA_ERROR; }
+            rec->owns_stream = true;
+        }
+        *out = reinterpret_cast<nuka_device_handle>(Devices().Insert(std::move(rec)));
+        return NUKA_RESULT_OK;
+    });
+}
+
+void nuka_device_destroy(nuka_device_handle device) {
+    auto rec = Devices().Remove(reinterpret_cast<uintptr_t>(device));
+    if (!rec) return;
+    if (rec->owns_stream) { cudaSetDevice(rec->gpu); cudaStreamDestroy(rec->stream); }
+}
+
+nuka_result_t nuka_world_create_from_template(nuka_device_handle device, const nuka_world_desc_t* desc,
+                                              const void* template_bytes, size_t template_size, nuka_world_handle* out) {
+    if (template_bytes == nullptr || template_size == 0) { SetError("template bytes are null"); return NUKA_RESULT_INVALID_ARG; }
+    return CreateWorld(device, desc, template_bytes, template_size, out);
+}
+
+nuka_result_t nuka_world_create_from_scene(nuka_device_handle device, const nuka_world_desc_t* desc, nuka_world_handle* out) {
+    if (desc == nullptr || desc->scene_path == nullptr) { SetError("scene_path is null"); if (out) *out = nullptr; return NUKA_RESULT_INVALID_ARG; }
+    const std::string path = desc->scene_path;
+    const bool nkt = path.size() > 4 && path.compare(path.size() - 4, 4, ".nkt") == 0;
+    if (!nkt) {
+        SetError("only cooked template files (.nkt) are loadable; scene importers and the cooker are outside this path");
+        if (out) *out = nullptr;
+        return NUKA_RESULT_NOT_SUPPORTED;
+    }
+    std::ifstream in(path, std::ios::binary);
+    if (!in) { SetError("cannot open " + path); if (out) *out = nullptr; return NUKA_RESULT_FILE_NOT_FOUND; }
+    std::stringstream ss;
+    ss << in.rdbuf();
+    const std::string bytes = ss.str();
+    return CreateWorld(device, desc, bytes.data(), bytes.size(), out);
+}
+
+void nuka_world_destroy(nuka_world_handle world) {
+    auto rec = Worlds().Remove(reinterpret_cast<uintptr_t>(world));
+    if (!rec) return;
+    if (DeviceRecord* dev = Devices().Get(rec->device)) { if (dev->worlds) --dev->worlds; }
+    rec->world.reset();
+}
+
+#define NKB_WORLD(w)                                                          \
+    nkb::World* w = WorldOf(world);                                           \
+    if (w == nullptr) { SetError("world handle is null or stale"); return NUKA_RESULT_NULL_HANDLE; }
+
+nuka_result_t nuka_world_step(nuka_world_handle world) { return nuka_world_step_n(world, 1u); }
+
+nuka_result_t nuka_world_step_n(nuka_world_handle world, uint32_t step_count) {
+    NKB_WORLD(w)
+    return Guard([&]() { w->Step(step_count); return NUKA_RESULT_OK; });
+}
+
+nuka_result_t nuka_world_set_execution_mode(nuka_world_handle world, nuka_execution_mode_t mode) {
+    NKB_WORLD(w)
+    if (mode != NUKA_EXECUTION_EAGER && mode != NUKA_EXECUTION_GRAPH) { SetError("unknown execution mode"); return NUKA_RESULT_INVALID_ARG; }
+    return Guard([&]() { w->SetGraphMode(mode == NUKA_EXECUTION_GRAPH); return NUKA_RESULT_OK; });
+}
+
+nuka_result_t nuka_world_set_gravity_z(nuka_world_handle world, float gravity_z) {
+    NKB_WORLD(w)
+    if (gravity_z != gravity_z) { SetError("gravity_z is NaN"); return NUKA_RESULT_INVALID_ARG; }
+    w->SetGravityZ(gravity_z);
+    return NUKA_RESULT_OK;
+}
+
+nuka_result_t nuka_world_set_velocity_iterations(nuka_world_handle world, uint32_t iterations) {
+    NKB_WORLD(w)
+    if (iterations == 0u || iterations > 65535u) { SetError("velocity iterations must be in 1..65535"); return NUKA_RESULT_INVALID_ARG; }
+    w->SetVelocityIterations(iterations);
+    return NUKA_RESULT_OK;
+}
+
+nuka_result_t nuka_world_get_velocity_iterations(nuka_world_handle world, uint32_t* out_iterations) {
+    NKB_WORLD(w)
+    if (out_iterations == nullptr) { SetError("out pointer is null"); return NUKA_RESULT_INVALID_ARG; }
+    *out_iterations = w->VelocityIterations();
+    return NUKA_RESULT_OK;
+}
+
+nuka_result_t nuka_world_synchronize(nuka_world_handle world) {
+    NKB_WORLD(w)
+    return Guard([&]() { w->Synchronize(); return NUKA_RESULT_OK; });
+}
+
+nuka_result_t nuka_world_reset(nuka_world_handle world) {
+    NKB_WORLD(w)
+    return Guard([&]() { w->Reset(nullptr, 0u); return NUKA_RESULT_OK; });
+}
+
+nuka_result_t nuka_world_reset_envs(nuka_world_handle world, const uint32_t* env_ids, uint32_t count) {
+    NKB_WORLD(w)
+    if (count == 0u) return NUKA_RESULT_OK;
+    if (env_ids == nullptr) { SetError("env_ids is null"); return NUKA_RESULT_INVALID_ARG; }
+    return Guard([&]() { w->Reset(env_ids, count); return NUKA_RESULT_OK; });
+}
+
+nuka_result_t nuka_world_forward_kinematics(nuka_world_handle world) {
+    NKB_WORLD(w)
+    return Guard([&]() { w->Refresh(); return NUKA_RESULT_OK; });
+}
+
+nuka_result_t nuka_world_get_stream(nuka_world_handle world, void** out_stream) {
+    NKB_WORLD(w)
+    if (out_stream == nullptr) { SetError("out pointer is null"); return NUKA_RESULT_INVALID_ARG; }
+    *out_stream = static_cast<void*>(w->stream());
+    return NUKA_RESULT_OK;
+}
+
+nuka_result_t nuka_world_record_event(nuka_world_handle world, void* cuda_event) {
+    NKB_WORLD(w)
+    if (cuda_event == nullptr) { SetError("event is null"); return NUKA_RESULT_INVALID_ARG; }
+    if (cudaSetDevice(w->device()) != cudaSuccess || cudaEventRecord(static_cast<cudaEvent_t>(cuda_event), w->stream()) != cudaSuccess) {
+        SetError("cudaEventRecord failed");
+        return NUKA_RESULT_CUDA_ERROR;
+    }
+    return NUKA_RESULT_OK;
+}
+
+nuka_result_t nuka_world_get_buffer_view(nuka_world_handle world, nuka_state_field_t field, nuka_buffer_view_t* out) {
+    NKB_WORLD(w)
+    if (out == nullptr) { SetError("out view is null"); return NUKA_RESULT_INVALID_ARG; }
+    return Guard([&]() {
+        nkb::FieldInfo info;
+        if (!w->Field(static_cast<uint32_t>(field), &info)) { SetError("field is not served by this path"); return NUKA_RESULT_NOT_SUPPORTED; }
+        out->device_ptr = info.ptr;
+        out->element_count = info.per_env * w->env_count();
+        out->element_stride_bytes = 4u;
+        out->dtype = static_cast<uint8_t>(info.dtype);
+        return NUKA_RESULT_OK;
+    });
+}
+
+static nuka_result_t Transfer(nuka_world_handle world, nuka_state_field_t field, void* bytes, size_t nbytes, size_t offset, bool upload) {
+    NKB_WORLD(w)
+    if (nbytes == 0u) return NUKA_RESULT_OK;
+    if (bytes == nullptr) { SetError("bytes is null"); return NUKA_RESULT_INVALID_ARG; }
+    return Guard([&]() {
+        nkb::FieldInfo info;
+        if (!w->Field(static_cast<uint32_t>(field), &info)) { SetError("field is not served by this path"); return NUKA_RESULT_NOT_SUPPORTED; }
+        const size_t total = info.per_env * w->env_count() * 4u;
+        if (offset > total || nbytes > total - offset) { SetError("transfer exceeds the field"); return NUKA_RESULT_INVALID_ARG; }
+        if (cudaSetDevice(w->device()) != cudaSuccess) { SetError("cudaSetDevice failed"); return NUKA_RESULT_CUDA_ERROR; }
+        auto* dev = static_cast<uint8_t*>(info.ptr) + offset;
+        const cudaError_t err = upload ? cudaMemcpyAsync(dev, bytes, nbytes, cudaMemcpyHostToDevice, w->stream())
+                                       : cudaMemcpyAsync(bytes, dev, nbytes, cudaMemcpyDeviceToHost, w->stream());
+        // pageable host memory makes the copy synchronous with respect to the host buffer; pinned buffers stay
+        // asynchronous on upload, downloads always complete before returning
+        if (err != cudaSuccess) { SetError(std::string("field copy: ") + cudaGetErrorString(err)); return NUKA_RESULT_CUDA_ERROR; }
+        if (!upload && cudaStreamSynchronize(w->stream()) != cudaSuccess) { SetError("field download sync failed"); return NUKA_RESULT_CUDA_ERROR; }
+        return NUKA_RESULT_OK;
+    });
+}
+
+nuka_result_t nuka_world_upload_field(nuka_world_handle world, nuka_state_field_t field, const void* bytes, size_t nbytes, size_t byte_offset) {
+    return Transfer(world, field, const_cast<void*>(bytes), nbytes, byte_offset, true);
+}
+
+nuka_result_t nuka_world_download_field(nuka_world_handle world, nuka_state_field_t field, void* bytes, size_t nbytes, size_t byte_offset) {
+    return Transfer(world, field, bytes, nbytes, byte_offset, false);
+}
+
+nuka_result_t nuka_b200_world_info(nuka_world_handle world, nuka_b200_world_info_t* out) {
+    NKB_WORLD(w)
+    if (out == nullptr) { SetError("out pointer is null"); return NUKA_RESULT_INVALID_ARG; }
+    out->env_count = w->env_count();
+    out->links_per_env = w->tpl().L; out->bodies_per_env = w->tpl().B; out->dofs_per_env = w->tpl().ndof;
+    out->contact_slots_per_env = w->tpl().cfg.max_contacts;
+    out->shared_bytes_per_env = w->shared_bytes_per_env(); out->warps_per_block = w->warps_per_block();
+    return NUKA_RESULT_OK;
+}
+
+nuka_result_t nuka_b200_world_run_stage(nuka_world_handle world, uint32_t stage) {
+    NKB_WORLD(w)
+    if (stage != 1u && stage != 2u) { SetError("stage must be 1 (dynamics) or 2 (collision)"); return NUKA_RESULT_INVALID_ARG; }
+    return Guard([&]() { w->RunStage(stage); return NUKA_RESULT_OK; });
+}
+
+nuka_result_t nuka_b200_world_launch_count(nuka_world_handle world, uint64_t* out) {
+    NKB_WORLD(w)
+    if (out == nullptr) { SetError("out pointer is null"); return NUKA_RESULT_INVALID_ARG; }
+    *out = w->launches();
+    return NUKA_RESULT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,444 @@
+// Warp-per-env articulation stages: forward kinematics, implicit PD drives, joint-space dynamics
+// (bias forces + composite-inertia mass matrix + L D L^T solve), position integration and link velocities.
+// One lane owns one link in the tree sweeps and one coordinate in the mass-matrix work; per-env intermediates
+// live in the warp's shared-memory slice.  The computed quantities are those of the reference's
+// ops/articulation.cu:505-645 (ArticulationDynamicsKernel), :836-940 (ApplyAffineDriveKernel), :732-791
+// (position integration), :647-689 (link velocities), :1561-1596 (world poses) and
+// ops/articulation_mass.cuh:124-396 (mass matrix, factor, solve).
+#pragma once
+#include "nkb_math.cuh"
+#include "nkb_types.h"
+
+namespace nkb {
+
+// Per-warp view of one env: template, state, shared-memory slice and this lane's registers.
+struct Env {
+    const TemplateView* t;
+    const StateView* s;
+    const SmemLayout* lay;
+    float* sm;
+    uint32_t env, lane;
+    // lane = link
+    uint32_t parent, jtype, depth, link_dof;
+    float q, qd, qdd, tau;
+    V3 axis;                 // unit joint axis in the link frame
+    float drive_command, drive_dissipation, drive_lower, drive_upper;
+    // lane = dof
+    uint32_t dof_link, dof_comp;   // comp == kNoLink for scalar joints
+    float vel0;              // step-start coordinate velocity
+    uint32_t status;
+};
+
+NKB_DEV float* sm_pose(const Env& e, uint32_t l) { return e.sm + e.lay->pose + 7u * l; }
+NKB_DEV float* sm_xrot(const Env& e, uint32_t l) { return e.sm + e.lay->xrot + 9u * l; }
+NKB_DEV float* sm_xtr(const Env& e, uint32_t l) { return e.sm + e.lay->xtr + 3u * l; }
+NKB_DEV float* sm_vel(const Env& e, uint32_t l) { return e.sm + e.lay->vel + 6u * l; }
+NKB_DEV float* sm_vbias(const Env& e, uint32_t l) { return e.sm + e.lay->vbias + 6u * l; }
+NKB_DEV float* sm_acc(const Env& e, uint32_t l) { return e.sm + e.lay->acc + 6u * l; }
+NKB_DEV float* sm_pbias(const Env& e, uint32_t l) { return e.sm + e.lay->pbias + 6u * l; }
+NKB_DEV float* sm_ic(const Env& e, uint32_t l) { return e.sm + e.lay->ic + 10u * l; }
+NKB_DEV float* sm_mass(const Env& e) { return e.sm + e.lay->mass; }
+NKB_DEV float* sm_factor(const Env& e) { return e.sm + e.lay->factor; }
+NKB_DEV float* sm_vec(const Env& e, uint32_t k) { return e.sm + e.lay->vecs + 32u * k; }
+// vector slots
+enum { kVecBias = 0, kVecAcc = 1, kVecFree = 2, kVecU = 3, kVecD = 4, kVecPseudo = 5, kVecTmp = 6, kVecTmp2 = 7 };
+
+NKB_DEV uint32_t joint_dofs(uint32_t t) { return (t == kRevolute || t == kPrismatic) ? 1u : t == kFloating ? 6u : t == kSpherical ? 3u : 0u; }
+
+NKB_DEV void env_begin(Env& e, const StepParams& p, float* sm, uint32_t env, uint32_t lane) {
+    e.t = &p.t; e.s = &p.s; e.lay = &p.sm; e.sm = sm; e.env = env; e.lane = lane;
+    const TemplateView& t = p.t;
+    const bool link = lane < t.L;
+    e.parent = link ? __ldg(t.parent + lane) : kNoLink;
+    e.jtype = link ? __ldg(t.jtype + lane) : (uint32_t)kFixed;
+    e.depth = link ? __ldg(t.depth + lane) : 0xffffu;
+    e.link_dof = link ? __ldg(t.link_dof + lane) : 0u;
+    e.axis = mk3(0.f, 0.f, 0.f);
+    if (link) {
+        V3 a = ld3(t.axis + 3u * lane);
+        const float ls = dot(a, a);
+        e.axis = ls > 1.0e-12f ? a * rsqrtf(ls) : mk3(0.f, 0.f, 0.f);
+    }
+    const size_t at = (size_t)env * t.L + lane;
+    e.q = link ? p.s.q[at] : 0.f;
+    e.qd = link ? p.s.qdot[at] : 0.f;
+    e.qdd = 0.f; e.tau = 0.f;
+    e.drive_command = e.drive_dissipation = e.drive_lower = e.drive_upper = 0.f;
+    const bool dof = lane < t.ndof;
+    e.dof_link = dof ? __ldg(t.dof_link + lane) : 0u;
+    e.dof_comp = kNoLink;
+    if (dof && __ldg(t.jtype + e.dof_link) == kFloating) e.dof_comp = lane - __ldg(t.link_dof + e.dof_link);
+    e.vel0 = 0.f;
+    e.status = 0u;
+}
+
+// World poses of every link, ops/articulation.cu:1561-1596 with kinematics.cuh:25-42 joint frames.
+NKB_DEV void stage_fk(Env& e) {
+    const TemplateView& t = *e.t;
+    const uint32_t l = e.lane;
+    const bool link = l < t.L;
+    V3 rpos = mk3(0.f, 0.f, 0.f);
+    Q4 rrot = mkq(1.f, 0.f, 0.f, 0.f);
+    if (link) {
+        rpos = ld3(t.offset + 3u * l);
+        rrot = ldq(t.local_quat + 4u * l);
+        if (e.jtype == kRevolute) {
+            const float half = 0.5f * e.q, s = sinf(half);
+            rrot = qnorm_le(qmul(rrot, mkq(cosf(half), e.axis.x * s, e.axis.y * s, e.axis.z * s)), 1.0e-12f);
+        } else if (e.jtype == kPrismatic) {
+            rpos = rpos + qrot(rrot, e.axis * e.q);
+        }
+    }
+    for (uint32_t d = 0; d <= t.max_depth; ++d) {
+        if (link && e.depth == d) {
+            float* out = sm_pose(e, l);
+            if (e.parent == kNoLink) {
+                if (e.jtype == kFloating) {
+                    const float* bp = e.s->base_pose + (size_t)e.env * 7u;
+#pragma unroll
+                    for (int k = 0; k < 7; ++k) out[k] = bp[k];
+                } else { st3(out, rpos); stq(out + 3, rrot); }
+            } else {
+                const float* pp = sm_pose(e, e.parent);
+                const Q4 pq = ldq(pp + 3);
+                st3(out, ld3(pp) + qrot(pq, rpos));
+                stq(out + 3, qnorm_le(qmul(pq, rrot), 1.0e-12f));
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// Joint transform (E, r) of this lane's link, ops/articulation.cu:259-277.
+NKB_DEV void joint_xform(const Env& e, float* E, V3& r) {
+    const TemplateView& t = *e.t;
+    const uint32_t l = e.lane;
+    if (e.parent == kNoLink && e.jtype == kFloating) {
+        const M3 I = m3_ident();
+#pragma unroll
+        for (int k = 0; k < 9; ++k) E[k] = I.m[k];
+        r = mk3(0.f, 0.f, 0.f);
+        return;
+    }
+    M3 jr = m3_ident();
+    r = ld3(t.offset + 3u * l);
+    const Q4 lq = ldq(t.local_quat + 4u * l);
+    if (e.jtype == kRevolute) jr = m3_axis_angle(ld3(t.axis + 3u * l), e.q);
+    else if (e.jtype == kPrismatic) r = r + qrot(lq, e.axis * e.q);
+    const M3 rot = m3_mul(m3_from_quat(lq), jr);
+#pragma unroll
+    for (int a = 0; a < 3; ++a)
+#pragma unroll
+        for (int b = 0; b < 3; ++b) E[a * 3 + b] = rot.m[b * 3 + a];
+}
+
+// Implicit PD position drives, ops/articulation.cu:836-940 (control mode 0).
+NKB_DEV void stage_drives(Env& e) {
+    const TemplateView& t = *e.t;
+    const uint32_t l = e.lane;
+    e.drive_command = e.drive_dissipation = e.drive_lower = e.drive_upper = 0.f;
+    e.tau = 0.f;
+    if (l >= t.L || joint_dofs(e.jtype) != 1u) return;
+    const size_t at = (size_t)e.env * t.L + l;
+    const float target = e.s->drive_target[at], kp = e.s->kp[at], kd = e.s->kd[at], vt = e.s->vel_target[at];
+    const float limit = e.s->force_limit[at], ff = e.s->feedforward[at];
+    if (!isfinite(target) || !isfinite(kp) || kp < 0.f || !isfinite(kd) || kd < 0.f || !isfinite(vt)) { e.status |= kStatusControlFailure; return; }
+    float lower = limit > 0.f ? -limit : -FLT_MAX, upper = limit > 0.f ? limit : FLT_MAX;
+    float damping = kd + t.cfg.dt * kp;
+    float bias = kp * (target - e.q) + damping * vt;
+    const float effort = bias - damping * e.qd;
+    if (effort < lower || effort > upper) { bias = effort; damping = 0.f; }
+    else { lower += damping * e.qd; upper += damping * e.qd; }
+    if (!isfinite(bias) || !isfinite(damping) || damping < 0.f || !isfinite(limit) || !isfinite(ff) || !isfinite(e.qd) || !isfinite(e.q)) {
+        e.status |= kStatusControlFailure; return;
+    }
+    e.drive_command = bias; e.drive_dissipation = damping; e.drive_lower = lower; e.drive_upper = upper;
+    e.tau = ff;
+}
+
+// Bias forces, mass matrix, factor and unconstrained acceleration; optionally the semi-implicit velocity
+// update.  Leaves M and its L D L^T factor in shared memory for the constraint solve.
+NKB_DEV void stage_dynamics(Env& e, bool integrate_velocity) {
+    const TemplateView& t = *e.t;
+    const uint32_t l = e.lane, L = t.L, n = t.ndof, ld = e.lay->ld;
+    const bool link = l < L;
+    const bool froot = link && e.parent == kNoLink && e.jtype == kFloating;
+    const V3 g = mk3(t.cfg.gravity[0], t.cfg.gravity[1], t.cfg.gravity[2]);
+    const float dt = t.cfg.dt;
+    float E[9]; V3 r = mk3(0.f, 0.f, 0.f);
+    if (link) {
+        joint_xform(e, E, r);
+        float* xe = sm_xrot(e, l);
+#pragma unroll
+        for (int k = 0; k < 9; ++k) xe[k] = E[k];
+        st3(sm_xtr(e, l), r);
+    }
+    // joint velocity S qd in the link frame
+    V3 jw = mk3(0.f, 0.f, 0.f), jv = mk3(0.f, 0.f, 0.f);
+    if (e.jtype == kRevolute) jw = e.axis * e.qd; else if (e.jtype == kPrismatic) jv = e.axis * e.qd;
+    V3 vw = mk3(0.f, 0.f, 0.f), vv = mk3(0.f, 0.f, 0.f), cw = vw, cv = vv;
+    if (froot) {
+        const float* lv = e.s->link_vel + ((size_t)e.env * L + l) * 6u;
+        vw = ld3(lv); vv = ld3(lv + 3);
+        st3(sm_vel(e, l), vw); st3(sm_vel(e, l) + 3, vv);
+    }
+    __syncwarp();
+    for (uint32_t d = 0; d <= t.max_depth; ++d) {
+        if (link && e.depth == d && !froot) {
+            V3 pw = mk3(0.f, 0.f, 0.f), pv = pw;
+            if (e.parent != kNoLink) { pw = ld3(sm_vel(e, e.parent)); pv = ld3(sm_vel(e, e.parent) + 3); }
+            V3 tw, tv;
+            xf_motion(E, r, pw, pv, tw, tv);
+            vw = tw + jw; vv = tv + jv;
+            st3(sm_vel(e, l), vw); st3(sm_vel(e, l) + 3, vv);
+            motion_cross(vw, vv, jw, jv, cw, cv);
+        }
+        __syncwarp();
+    }
+    // p = v x* (I v)
+    const float* I10 = t.inertia10 + 10u * (link ? l : 0u);
+    V3 pn = mk3(0.f, 0.f, 0.f), pf = pn;
+    if (link) {
+        V3 in_, if_;
+        rbi_mulv(I10, vw, vv, in_, if_);
+        force_cross(vw, vv, in_, if_, pn, pf);
+    }
+    // accelerations root to leaf with gravity injected at the root
+    V3 aw = mk3(0.f, 0.f, 0.f), av = aw;
+    for (uint32_t d = 0; d <= t.max_depth; ++d) {
+        if (link && e.depth == d) {
+            if (e.parent != kNoLink) xf_motion(E, r, ld3(sm_acc(e, e.parent)), ld3(sm_acc(e, e.parent) + 3), aw, av);
+            else if (e.jtype == kFloating) {
+                const V3 gl = qrot_inv(ldq(e.s->base_pose + (size_t)e.env * 7u + 3), g);
+                aw = mk3(0.f, 0.f, 0.f); av = -gl;
+            } else xf_motion(E, r, mk3(0.f, 0.f, 0.f), -g, aw, av);
+            aw = aw + cw; av = av + cv;
+            st3(sm_acc(e, l), aw); st3(sm_acc(e, l) + 3, av);
+        }
+        __syncwarp();
+    }
+    if (link) {
+        V3 in_, if_;
+        rbi_mulv(I10, aw, av, in_, if_);
+        pn = pn + in_; pf = pf + if_;
+        st3(sm_pbias(e, l), pn); st3(sm_pbias(e, l) + 3, pf);
+        float* ic = sm_ic(e, l);
+#pragma unroll
+        for (int k = 0; k < 10; ++k) ic[k] = __ldg(I10 + k);
+    }
+    __syncwarp();
+    // leaf to root: bias forces and composite inertias, children in list order
+    for (uint32_t rem = t.max_depth + 1u; rem > 0u; --rem) {
+        if (link && e.depth == rem - 1u) {
+            const uint32_t cb = __ldg(t.child_begin + l), ce = __ldg(t.child_begin + l + 1u);
+            float* ic = sm_ic(e, l);
+            for (uint32_t c = cb; c < ce; ++c) {
+                const uint32_t child = __ldg(t.children + c);
+                V3 cn, cf;
+                xf_force_t(sm_xrot(e, child), ld3(sm_xtr(e, child)), ld3(sm_pbias(e, child)), ld3(sm_pbias(e, child) + 3), cn, cf);
+                pn = pn + cn; pf = pf + cf;
+                float add[10];
+                rbi_to_parent(sm_xrot(e, child), ld3(sm_xtr(e, child)), sm_ic(e, child), add);
+#pragma unroll
+                for (int k = 0; k < 10; ++k) ic[k] += add[k];
+            }
+            st3(sm_pbias(e, l), pn); st3(sm_pbias(e, l) + 3, pf);
+        }
+        __syncwarp();
+    }
+    // generalized bias and right-hand side, lane = coordinate
+    const float diss_of_link = __shfl_sync(NKB_FULL, e.drive_dissipation, e.dof_link);
+    const float tau_of_link = __shfl_sync(NKB_FULL, e.tau, e.dof_link);
+    const float qd_of_link = __shfl_sync(NKB_FULL, e.qd, e.dof_link);
+    const float q_of_link = __shfl_sync(NKB_FULL, e.q, e.dof_link);
+    float rhs = 0.f;
+    const bool dof = l < n;
+    if (dof) {
+        const uint32_t dl = e.dof_link;
+        const float* pb = sm_pbias(e, dl);
+        float bias;
+        if (e.dof_comp == kNoLink) {
+            V3 a = ld3(t.axis + 3u * dl);
+            const float ls = dot(a, a);
+            if (ls > 1.0e-12f) a = a * rsqrtf(ls);
+            const uint32_t jt = __ldg(t.jtype + dl);
+            bias = jt == kRevolute ? dot(a, ld3(pb)) : dot(a, ld3(pb + 3));
+            e.vel0 = qd_of_link;
+            const float damping = __ldg(t.damping + dl) + diss_of_link;
+            const float spring = __ldg(t.stiffness + dl) * (q_of_link - __ldg(t.spring_ref + dl));
+            rhs = tau_of_link - bias - damping * e.vel0 - spring;
+        } else {
+            bias = pb[e.dof_comp];
+            e.vel0 = sm_vel(e, dl)[e.dof_comp];
+            rhs = -bias;
+        }
+        sm_vec(e, kVecBias)[l] = bias;
+    }
+    // mass matrix, ops/articulation_mass.cuh:124-253
+    float* M = sm_mass(e);
+    for (uint32_t k = l; k < n * ld; k += 32u) M[k] = 0.f;
+    __syncwarp();
+    if (t.floating_root && l < 6u) {
+        const float* ic = sm_ic(e, 0u);
+        const float m = ic[0]; const V3 h = ld3(ic + 1);
+        const float Ib[9] = {ic[4], ic[7], ic[8], ic[7], ic[5], ic[9], ic[8], ic[9], ic[6]};
+        const float hx[9] = {0.f, -h.z, h.y, h.z, 0.f, -h.x, -h.y, h.x, 0.f};
+        float* row = M + l * ld;
+        if (l < 3u) {
+#pragma unroll
+            for (int c = 0; c < 3; ++c) { row[c] = Ib[l * 3 + c]; row[3 + c] = hx[l * 3 + c]; }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 3; ++c) { row[c] = -hx[(l - 3) * 3 + c]; row[3 + c] = (int)(l - 3) == c ? m : 0.f; }
+        }
+    }
+    if (link && !froot && joint_dofs(e.jtype) == 1u) {
+        const uint32_t di = e.link_dof;
+        const float* ic = sm_ic(e, l);
+        V3 fn, ff;
+        if (e.jtype == kRevolute) rbi_mulv(ic, e.axis, mk3(0.f, 0.f, 0.f), fn, ff); else rbi_mulv(ic, mk3(0.f, 0.f, 0.f), e.axis, fn, ff);
+        float diag = e.jtype == kRevolute ? dot(e.axis, fn) : dot(e.axis, ff);
+        diag += __ldg(t.armature + l);
+        diag += dt * e.drive_dissipation;
+        M[di * ld + di] = diag;
+        uint32_t walk = l;
+        for (;;) {
+            const uint32_t p = __ldg(t.parent + walk);
+            if (p == kNoLink) break;
+            V3 pn2, pf2;
+            xf_force_t(sm_xrot(e, walk), ld3(sm_xtr(e, walk)), fn, ff, pn2, pf2);
+            fn = pn2; ff = pf2;
+            walk = p;
+            const uint32_t wt = __ldg(t.jtype + walk);
+            if (joint_dofs(wt) == 0u) continue;
+            const uint32_t dj = __ldg(t.link_dof + walk);
+            if (wt == kFloating) {
+                const float f6[6] = {fn.x, fn.y, fn.z, ff.x, ff.y, ff.z};
+#pragma unroll
+                for (int b = 0; b < 6; ++b) { M[di * ld + b] = f6[b]; M[b * ld + di] = f6[b]; }
+                continue;
+            }
+            V3 a = ld3(t.axis + 3u * walk);
+            const float ls = dot(a, a);
+            if (ls > 1.0e-12f) a = a * rsqrtf(ls);
+            const float entry = wt == kRevolute ? dot(a, fn) : dot(a, ff);
+            M[di * ld + dj] = entry; M[dj * ld + di] = entry;
+        }
+    }
+    __syncwarp();
+    if (e.s->dbg_mass != nullptr) {
+        float* out = e.s->dbg_mass + (size_t)e.env * n * n;
+        for (uint32_t k = l; k < n * n; k += 32u) out[k] = M[(k / n) * ld + k % n];
+    }
+    // L D L^T, unit lower triangle with D on the diagonal and pivot floor 1e-6 (articulation_mass.cuh:269-335)
+    float* F = sm_factor(e);
+    for (uint32_t k = l; k < n * ld; k += 32u) F[k] = M[k];
+    __syncwarp();
+    for (uint32_t k = 0; k < n; ++k) {
+        const float dk = fmaxf(F[k * ld + k], 1.0e-6f);
+        __syncwarp();
+        if (l == k) F[k * ld + k] = dk;
+        float lik = 0.f;
+        if (l > k && l < n) { lik = F[l * ld + k] / dk; F[l * ld + k] = lik; }
+        __syncwarp();
+        if (l > k && l < n)
+            for (uint32_t j = k + 1u; j <= l; ++j) F[l * ld + j] -= lik * F[j * ld + k] * dk;
+        __syncwarp();
+    }
+    // solve L D L^T x = rhs, lane = coordinate (articulation_mass.cuh:357-396)
+    float x = dof ? rhs : 0.f;
+    for (uint32_t j = 0; j < n; ++j) {
+        const float xj = __shfl_sync(NKB_FULL, x, j);
+        if (l > j && l < n) x -= F[l * ld + j] * xj;
+    }
+    if (dof) x /= F[l * ld + l];
+    for (uint32_t jj = n; jj > 0u; --jj) {
+        const uint32_t j = jj - 1u;
+        const float xj = __shfl_sync(NKB_FULL, x, j);
+        if (l < j) x -= F[j * ld + l] * xj;
+    }
+    if (dof) sm_vec(e, kVecAcc)[l] = x;
+    __syncwarp();
+    // accelerations back to links, velocity update (articulation.cu:597-615)
+    const float acc_of_mine = link && joint_dofs(e.jtype) == 1u ? sm_vec(e, kVecAcc)[e.link_dof] : 0.f;
+    e.qdd = acc_of_mine;
+    if (integrate_velocity) {
+        if (link && joint_dofs(e.jtype) == 1u) e.qd = e.qd + dt * acc_of_mine;
+        const bool base_coord = dof && e.dof_comp != kNoLink;
+        float nv = 0.f;
+        if (base_coord) {
+            const uint32_t c = e.dof_comp, i = c % 3u, j = (i + 1u) % 3u, k = (i + 2u) % 3u;
+            const float* rv = sm_vel(e, e.dof_link);
+            const float transport = c < 3u ? 0.f : rv[j] * rv[3u + k] - rv[k] * rv[3u + j];
+            nv = e.vel0 + dt * (x + transport);
+        }
+        __syncwarp();
+        if (base_coord) sm_vel(e, e.dof_link)[e.dof_comp] = nv;
+        __syncwarp();
+    }
+}
+
+// q += dt (qdot + pseudo); floating base pose; ops/articulation.cu:732-791.
+NKB_DEV void stage_integrate_links(Env& e, bool use_pseudo) {
+    const TemplateView& t = *e.t;
+    const uint32_t l = e.lane;
+    if (l >= t.L) return;
+    const float dt = t.cfg.dt;
+    const float* ps = sm_vec(e, kVecPseudo);
+    if (joint_dofs(e.jtype) == 1u) e.q += (e.qd + (use_pseudo ? ps[e.link_dof] : 0.f)) * dt;
+    else e.q += e.qd * dt;
+    if (e.parent == kNoLink && e.jtype == kFloating) {
+        float* rv = sm_vel(e, l);
+        float v[6];
+#pragma unroll
+        for (int i = 0; i < 6; ++i) v[i] = rv[i] + (use_pseudo ? ps[i] : 0.f);
+        float* bp = e.s->base_pose + (size_t)e.env * 7u;
+        const Q4 rot = ldq(bp + 3);
+        const V3 vw = qrot(rot, mk3(v[3], v[4], v[5]));
+        st3(bp, ld3(bp) + vw * dt);
+        const Q4 dq = mkq(1.0f, 0.5f * v[0] * dt, 0.5f * v[1] * dt, 0.5f * v[2] * dt);
+        stq(bp + 3, qnorm_lt(qmul(rot, dq), 1.0e-24f));
+        const V3 turned = qrot_inv(qnorm_lt(dq, 1.0e-24f), mk3(rv[3], rv[4], rv[5]));
+        rv[3] = turned.x; rv[4] = turned.y; rv[5] = turned.z;
+    }
+}
+
+// Link spatial velocities after the solve, ops/articulation.cu:647-689.
+NKB_DEV void stage_link_velocities(Env& e) {
+    const TemplateView& t = *e.t;
+    const uint32_t l = e.lane;
+    const bool link = l < t.L;
+    const bool froot = link && e.parent == kNoLink && e.jtype == kFloating;
+    float E[9]; V3 r = mk3(0.f, 0.f, 0.f);
+    if (link) joint_xform(e, E, r);
+    V3 jw = mk3(0.f, 0.f, 0.f), jv = jw;
+    if (e.jtype == kRevolute) jw = e.axis * e.qd; else if (e.jtype == kPrismatic) jv = e.axis * e.qd;
+    for (uint32_t d = 0; d <= t.max_depth; ++d) {
+        if (link && e.depth == d && !froot) {
+            V3 pw = mk3(0.f, 0.f, 0.f), pv = pw;
+            if (e.parent != kNoLink) { pw = ld3(sm_vel(e, e.parent)); pv = ld3(sm_vel(e, e.parent) + 3); }
+            V3 tw, tv;
+            xf_motion(E, r, pw, pv, tw, tv);
+            st3(sm_vel(e, l), tw + jw); st3(sm_vel(e, l) + 3, tv + jv);
+        }
+        __syncwarp();
+    }
+}
+
+// Writes the articulation's public state back to global memory.
+NKB_DEV void stage_store_links(Env& e) {
+    const TemplateView& t = *e.t;
+    const uint32_t l = e.lane, L = t.L;
+    if (l < L) {
+        const size_t at = (size_t)e.env * L + l;
+        e.s->q[at] = e.q; e.s->qdot[at] = e.qd; e.s->qddot[at] = e.qdd; e.s->tau[at] = e.tau;
+    }
+    float* gp = e.s->link_pose + (size_t)e.env * L * 7u;
+    const float* sp = e.sm + e.lay->pose;
+    for (uint32_t k = l; k < L * 7u; k += 32u) gp[k] = sp[k];
+    float* gv = e.s->link_vel + (size_t)e.env * L * 6u;
+    const float* sv = e.sm + e.lay->vel;
+    for (uint32_t k = l; k < L * 6u; k += 32u) gv[k] = sv[k];
+}
+
+}  // namespace nkb

@@ -1,0 +1,30 @@
+// Launch entry points of the CUDA side, callable from plain C++ translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include "nkb_types.h"
+
+namespace nkb {
+
+constexpr uint32_t kWarpsPerBlockMax = 8u;
+
+struct ResetField {
+    void* dst;            // E x words
+    const void* src;      // template words, per-env snapshot, or null for a constant fill
+    uint32_t words;
+    uint32_t per_env_src; // 1: src is E x words
+    uint32_t fill;
+};
+constexpr uint32_t kMaxResetFields = 24u;
+struct ResetParams {
+    uint32_t env_count;
+    const uint32_t* env_ids;   // device list of envs to reset, or null for all
+    uint32_t field_count;
+    ResetField fields[kMaxResetFields];
+};
+
+// Enqueues `p.steps` fused steps (or one parity-tap stage, see StepMode) for every env.
+cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream);
+// Restores `count` envs (all when r.env_ids is null) from their snapshots.
+cudaError_t launch_reset(const ResetParams& r, uint32_t count, cudaStream_t stream);
+
+}  // namespace nkb

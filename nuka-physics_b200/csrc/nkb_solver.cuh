@@ -1,0 +1,788 @@
+// Warp-per-env block-descent velocity solve with split-impulse position pass.
+// Blocks are the env's free bodies (6 coordinates: linear, angular) followed by its articulation (one
+// coordinate per DoF).  Blocks descend colour by colour; each block takes safeguarded Newton steps with an
+// exact line search on its local augmented Lagrangian, then the multipliers update with momentum.
+// One lane owns one block coordinate in the Newton system and one head in the row evaluations.
+// The algorithm is that of the reference's tile route: ops/block_descent_tile.cuh:743-797 (head setup),
+// :1103-1144 (colouring), :1508-1666 (assemble/factor/solve), :2089-2301 (line search, block descent),
+// :2493-2595 (dual update), :2379-2489 (momentum balance), :2608-2744 (finish, position marks),
+// :2942-3087 (sweep loop) and ops/block_descent.cu:1734-1753 (position bias).
+#pragma once
+#include "nkb_laws.cuh"
+#include "nkb_rows.cuh"
+
+namespace nkb {
+
+static_assert(HF_COUNT == kHeadWords, "head field count must match the host layout");
+
+constexpr uint32_t kNewtonSteps = 16u, kLineSteps = 32u;
+constexpr float kLineTol = 1.0e-6f, kRoundings = 8.0f;
+
+struct Tile {
+    uint32_t nheads, nblocks, iteration;
+    float momentum, residual, tol;
+};
+
+NKB_DEV uint32_t* sm_binfo(const Env& e) { return reinterpret_cast<uint32_t*>(e.sm + e.lay->binfo); }
+// binfo words: dim[nb], color[nb], inc_begin[nb + 1], inc[2 * head_cap]
+NKB_DEV uint32_t& blk_dim(const Env& e, uint32_t b) { return sm_binfo(e)[b]; }
+NKB_DEV uint32_t& blk_color(const Env& e, uint32_t nb, uint32_t b) { return sm_binfo(e)[nb + b]; }
+NKB_DEV uint32_t& blk_inc_begin(const Env& e, uint32_t nb, uint32_t b) { return sm_binfo(e)[2u * nb + b]; }
+NKB_DEV uint32_t* blk_inc(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u * nb + 1u; }
+NKB_DEV float* sm_bmass(const Env& e, uint32_t b) { return e.sm + e.lay->bmass + 7u * b; }
+NKB_DEV float* sm_bfree(const Env& e, uint32_t b) { return e.sm + e.lay->bfree + 6u * b; }
+NKB_DEV float* sm_bpseudo(const Env& e, uint32_t b) { return e.sm + e.lay->bpseudo + 6u * b; }
+NKB_DEV float* sm_chol(const Env& e) { return e.sm + e.lay->chol; }
+
+NKB_DEV uint32_t head_axes(const Env& e, uint32_t h) { return (hu(e, HF_FLAGS, h) & (kHeadContact | kHeadScalar)) == kHeadContact ? 3u : 1u; }
+NKB_DEV uint32_t head_owner(const Env& e, uint32_t h, uint32_t side) { const uint32_t o = hu(e, HF_OWNER, h); return side == 0u ? (o & 0xffffu) : (o >> 16); }
+
+// Jacobian entry of head h (incidence `side`) on coordinate i of its block, for contact axis ax.
+NKB_DEV float head_jac(const Env& e, uint32_t h, uint32_t side, uint32_t ax, uint32_t i, uint32_t block) {
+    const TemplateView& t = *e.t;
+    if (block == t.B) {
+        const uint32_t jo = hu(e, HF_JOFF, h);
+        if (jo & kUnitRow) return i == (jo & 0xffffu) ? hf(e, HF_UNITV, h) : 0.f;
+        return sm_jpool(e)[jo + ax * t.ndof + i];
+    }
+    const V3 dir = hf3(e, ax == 0u ? HF_N : ax == 1u ? HF_T1 : HF_T2, h);
+    const float sgn = side == 0u ? 1.f : -1.f;
+    if (i < 3u) return sgn * comp(dir, (int)i);
+    const V3 r = hf3(e, side == 0u ? HF_RA : HF_RB, h);
+    return sgn * comp(cross(r, dir), (int)i - 3);
+}
+
+// Mass entry (i, k) of a block.
+NKB_DEV float block_mass(const Env& e, uint32_t block, uint32_t i, uint32_t k) {
+    if (block == e.t->B) return sm_mass(e)[i * e.lay->ld + k];
+    const float* bm = sm_bmass(e, block);
+    if (i < 3u || k < 3u) return (i == k) ? bm[0] : 0.f;
+    const uint32_t a = i - 3u, b = k - 3u;
+    const uint32_t idx = a == b ? a : (a + b == 1u ? 3u : a + b == 2u ? 4u : 5u);
+    return bm[1u + idx];
+}
+NKB_DEV float* block_vel(const Env& e, uint32_t block, bool position) {
+    if (block == e.t->B) return sm_vec(e, position ? kVecPseudo : kVecU);
+    return position ? sm_bpseudo(e, block) : sm_bvel(e, block);
+}
+NKB_DEV const float* block_free(const Env& e, uint32_t block) { return block == e.t->B ? sm_vec(e, kVecFree) : sm_bfree(e, block); }
+
+// M^-1 g for a block, lane = coordinate.
+NKB_DEV float solve_block_mass(const Env& e, uint32_t block, float g) {
+    const TemplateView& t = *e.t;
+    const uint32_t l = e.lane;
+    if (block == t.B) {
+        const uint32_t n = t.ndof, ld = e.lay->ld;
+        const float* F = sm_factor(e);
+        float x = l < n ? g : 0.f;
+        for (uint32_t j = 0; j < n; ++j) { const float xj = __shfl_sync(NKB_FULL, x, j); if (l > j && l < n) x -= F[l * ld + j] * xj; }
+        if (l < n) x /= F[l * ld + l];
+        for (uint32_t jj = n; jj > 0u; --jj) { const uint32_t j = jj - 1u; const float xj = __shfl_sync(NKB_FULL, x, j); if (l < j) x -= F[j * ld + l] * xj; }
+        return x;
+    }
+    const float g3 = __shfl_sync(NKB_FULL, g, 3), g4 = __shfl_sync(NKB_FULL, g, 4), g5 = __shfl_sync(NKB_FULL, g, 5);
+    if (l < 3u) return g * __ldg(t.inv_mass + block);
+    if (l < 6u) { const V3 w = sym_mulv(sm_bwinv(e, block), mk3(g3, g4, g5)); return comp(w, (int)l - 3); }
+    return 0.f;
+}
+
+// J M^-1 J^T of an articulated row from one forward solve with the unit-lower factor (articulation_mass.cuh:413-441)
+NKB_DEV float mass_coupling(const Env& e, const float* row) {
+    const uint32_t n = e.t->ndof, ld = e.lay->ld;
+    const float* F = sm_factor(e);
+    float y[kMaxDof];
+    float r = 0.f;
+    for (uint32_t i = 0; i < n; ++i) {
+        float a = row[i];
+        for (uint32_t j = 0; j < i; ++j) a -= F[i * ld + j] * y[j];
+        y[i] = a;
+        r += a * a / F[i * ld + i];
+    }
+    return r;
+}
+
+NKB_DEV void head_response(const Env& e, uint32_t h, V3 move, V3& f, float& cxx, float& cyy, float& czz, float& cyz) {
+    const Resp rs = {hf(e, HF_RSD, h), hf(e, HF_RSR, h)};
+    const V3 dual = hf3(e, HF_DUAL, h), res = hf3(e, HF_RES, h);
+    const float rho = hf(e, HF_RHO, h);
+    const STerm n = scalar_impulse(dual.x, rho, res.x - move.x, hf(e, HF_LOWER, h), hf(e, HF_UPPER, h), rs);
+    f = mk3(n.impulse, 0.f, 0.f);
+    cxx = n.curvature; cyy = czz = cyz = 0.f;
+    if (head_axes(e, h) != 3u) return;
+    const float mu = hf(e, HF_MU, h);
+    tangent_impulse(dual, rho, res.y - move.y, res.z - move.z, hf(e, HF_NB, h), mu, mu, f.y, f.z, cyy, czz, cyz);
+}
+
+// Head setup: penalty, response scales (block_descent_tile.cuh:743-797).
+NKB_DEV void init_heads(Env& e, const Tile& tile) {
+    const TemplateView& t = *e.t;
+    for (uint32_t h = e.lane; h < tile.nheads; h += 32u) {
+        float shares[2] = {0.f, 0.f};
+        const uint32_t fl = hu(e, HF_FLAGS, h);
+        const uint32_t jo = hu(e, HF_JOFF, h);
+        bool valid = true;
+        for (uint32_t side = 0u; side < 2u; ++side) {
+            const uint32_t ob = head_owner(e, h, side);
+            float c = 0.f;
+            if (ob == kNoBlock16) { /* static or kinematic side: no response */ }
+            else if (ob == t.B) {
+                if (jo & kUnitRow) {
+                    float row[kMaxDof];
+                    for (uint32_t i = 0; i < t.ndof; ++i) row[i] = i == (jo & 0xffffu) ? hf(e, HF_UNITV, h) : 0.f;
+                    c = mass_coupling(e, row);
+                } else c = mass_coupling(e, sm_jpool(e) + jo);
+            } else {
+                const V3 dir = hf3(e, HF_N, h) * (side == 0u ? 1.f : -1.f);
+                const V3 ang = cross(hf3(e, side == 0u ? HF_RA : HF_RB, h), dir);
+                c = __ldg(t.inv_mass + ob) * dot(dir, dir) + dot(ang, sym_mulv(sm_bwinv(e, ob), ang));
+            }
+            valid &= c >= 0.f && isfinite(c);
+            shares[side] = c;
+        }
+        const float response = (valid && isfinite(shares[0] + shares[1])) ? shares[0] + shares[1] : nanf("");
+        const float coupling = shares[0] * shares[1], largest = fmaxf(shares[0], shares[1]);
+        const float coupled = coupling > 0.f ? (response + sqrtf(response * response + 12.0f * coupling)) / (6.0f * coupling) : FLT_MAX;
+        const float cap = 100.0f / largest;
+        float rho = response > 0.f ? fminf(cap, coupled) : 0.f;
+        if (!(response == 0.f || (response > 0.f && rho > 0.f && rho <= FLT_MAX))) { e.status |= kStatusSolverFailure; rho = nanf(""); }
+        const Resp rs = scalar_response(rho, 0.0f);
+        hf(e, HF_RHO, h) = rho; hf(e, HF_RSD, h) = rs.dual_scale; hf(e, HF_RSR, h) = rs.residual_scale;
+        hf(e, HF_NB, h) = 0.f;
+        hst3(e, HF_BASE, h, hf3(e, HF_DUAL, h));
+        hst3(e, HF_RES, h, mk3(0.f, 0.f, 0.f)); hst3(e, HF_MOVE, h, mk3(0.f, 0.f, 0.f)); hst3(e, HF_STEP, h, mk3(0.f, 0.f, 0.f));
+        hst3(e, HF_RXS, h, mk3(0.f, 0.f, 0.f)); hf(e, HF_RXW, h) = 0.f; hst3(e, HF_RXP, h, mk3(0.f, 0.f, 0.f));
+        (void)fl;
+    }
+    __syncwarp();
+}
+
+// Incidence lists (heads of each block in head order) and greedy colours.
+NKB_DEV void index_blocks(Env& e, const Tile& tile, bool color) {
+    const uint32_t nb = tile.nblocks;
+    uint32_t* inc = blk_inc(e, nb);
+    uint32_t at = 0u;
+    for (uint32_t b = 0u; b < nb; ++b) {
+        if (e.lane == 0u) blk_inc_begin(e, nb, b) = at;
+        for (uint32_t base = 0u; base < tile.nheads; base += 32u) {
+            const uint32_t h = base + e.lane;
+            bool hit = false;
+            if (h < tile.nheads) { const uint32_t o = hu(e, HF_OWNER, h); hit = (o & 0xffffu) == b || (o >> 16) == b; }
+            const uint32_t m = __ballot_sync(NKB_FULL, hit);
+            if (hit) inc[at + __popc(m & ((1u << e.lane) - 1u))] = h;
+            at += __popc(m);
+        }
+    }
+    if (e.lane == 0u) blk_inc_begin(e, nb, nb) = at;
+    __syncwarp();
+    if (!color) return;
+    for (uint32_t b = 0u; b < nb; ++b) {
+        uint32_t taken = 0u;
+        const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
+        for (uint32_t k = ib + e.lane; k < ie; k += 32u) {
+            const uint32_t o = hu(e, HF_OWNER, inc[k]);
+            const uint32_t first = o & 0xffffu, second = o >> 16;
+            const uint32_t other = first == b ? second : first;
+            if (other < b) taken |= 1u << blk_color(e, nb, other);
+        }
+        taken = __reduce_or_sync(NKB_FULL, taken);
+        if (e.lane == 0u) blk_color(e, nb, b) = blk_dim(e, b) != 0u ? min((uint32_t)__ffs(~taken) - 1u, 31u) : 0xffffffffu;
+        __syncwarp();
+    }
+}
+
+// residual = rhs dt - J u at the blocks' current velocities (block_descent_tile.cuh:891-930)
+NKB_DEV void init_residuals(Env& e, const Tile& tile) {
+    const TemplateView& t = *e.t;
+    const float dt = t.cfg.dt;
+    for (uint32_t h = e.lane; h < tile.nheads; h += 32u) {
+        const uint32_t axes = head_axes(e, h);
+        V3 res = mk3(0.f, 0.f, 0.f);
+        for (uint32_t ax = 0u; ax < axes; ++ax) {
+            float along = 0.f;
+            for (uint32_t side = 0u; side < 2u; ++side) {
+                const uint32_t b = head_owner(e, h, side);
+                if (b == kNoBlock16) continue;
+                const uint32_t dim = blk_dim(e, b);
+                const float* u = block_vel(e, b, false);
+                float part = 0.f;
+                for (uint32_t i = 0u; i < dim; ++i) part += head_jac(e, h, side, ax, i, b) * u[i];
+                along += part;
+            }
+            setc(res, (int)ax, (ax == 0u ? hf(e, HF_RHS, h) * dt : 0.f) - along);
+        }
+        hst3(e, HF_RES, h, res);
+    }
+    __syncwarp();
+}
+
+// Row steps J d of a block's incident heads; d is staged in shared memory.
+NKB_DEV void row_steps(Env& e, const Tile& tile, uint32_t b, const float* dvec) {
+    const uint32_t nb = tile.nblocks, dim = blk_dim(e, b);
+    const uint32_t* inc = blk_inc(e, nb);
+    const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
+    for (uint32_t k = ib + e.lane; k < ie; k += 32u) {
+        const uint32_t h = inc[k];
+        const uint32_t side = head_owner(e, h, 0u) == b ? 0u : 1u;
+        const uint32_t axes = head_axes(e, h);
+        V3 step = mk3(0.f, 0.f, 0.f);
+        const uint32_t jo = hu(e, HF_JOFF, h);
+        if (b == e.t->B && (jo & kUnitRow)) step.x = hf(e, HF_UNITV, h) * dvec[jo & 0xffffu];
+        else for (uint32_t ax = 0u; ax < axes; ++ax) {
+            float s = 0.f;
+            for (uint32_t i = 0u; i < dim; ++i) s += head_jac(e, h, side, ax, i, b) * dvec[i];
+            setc(step, (int)ax, s);
+        }
+        hst3(e, HF_STEP, h, step);
+    }
+    __syncwarp();
+}
+
+NKB_DEV void line_derivatives(Env& e, const Tile& tile, uint32_t b, float alpha, float islope, float icurv, float& slope, float& curvature, float& magnitude) {
+    const uint32_t nb = tile.nblocks;
+    const uint32_t* inc = blk_inc(e, nb);
+    const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
+    CSum rs = {0.f, 0.f};
+    float rc = 0.f, rm = 0.f;
+    for (uint32_t k = ib + e.lane; k < ie; k += 32u) {
+        const uint32_t h = inc[k];
+        const V3 step = hf3(e, HF_STEP, h), move = hf3(e, HF_MOVE, h);
+        const V3 trial = mk3(fmaf(alpha, step.x, move.x), fmaf(alpha, step.y, move.y), fmaf(alpha, step.z, move.z));
+        V3 f; float cxx, cyy, czz, cyz;
+        head_response(e, h, trial, f, cxx, cyy, czz, cyz);
+        csum_addp(rs, f.x, step.x); csum_addp(rs, f.y, step.y); csum_addp(rs, f.z, step.z);
+        rm += fabsf(f.x * step.x) + fabsf(f.y * step.y) + fabsf(f.z * step.z);
+        rc += cxx * step.x * step.x + cyy * step.y * step.y + czz * step.z * step.z + 2.0f * cyz * step.y * step.z;
+    }
+    CSum total = {-rs.value, -rs.error};
+    if (e.lane == 0u) { csum_addp(total, alpha, icurv); csum_add(total, islope); }
+    slope = warp_csum_total(total);
+    curvature = icurv + warp_sum(rc);
+    magnitude = fabsf(islope) + alpha * icurv + warp_sum(rm);
+}
+
+NKB_DEV float search_line(Env& e, const Tile& tile, uint32_t b, float islope, float icurv) {
+    float slope, curvature, magnitude;
+    line_derivatives(e, tile, b, 0.0f, islope, icurv, slope, curvature, magnitude);
+    const float initial = slope;
+    if (!(initial < 0.0f)) return 0.0f;
+    float low = 0.0f, high = 0.0f, alpha = 1.0f;
+    bool bounded = false;
+    for (uint32_t step = 0u; step < kLineSteps; ++step) {
+        line_derivatives(e, tile, b, alpha, islope, icurv, slope, curvature, magnitude);
+        if (!isfinite(slope) || !isfinite(curvature)) { high = alpha; bounded = true; alpha = 0.5f * (low + high); continue; }
+        if (fabsf(slope) <= fmaxf(kLineTol * -initial, kRoundings * FLT_EPSILON * magnitude)) return alpha;
+        if (slope < 0.0f) low = alpha; else { high = alpha; bounded = true; }
+        if (bounded && high - low <= FLT_EPSILON * high) break;
+        float next = alpha - slope / curvature;
+        if (!(next > low && (!bounded || next < high))) next = bounded ? 0.5f * (low + high) : 2.0f * alpha;
+        alpha = next;
+    }
+    return low;
+}
+
+NKB_DEV void apply_moves(Env& e, const Tile& tile, uint32_t b, float alpha) {
+    const uint32_t nb = tile.nblocks;
+    const uint32_t* inc = blk_inc(e, nb);
+    const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
+    for (uint32_t k = ib + e.lane; k < ie; k += 32u) {
+        const uint32_t h = inc[k];
+        const V3 step = hf3(e, HF_STEP, h), move = hf3(e, HF_MOVE, h);
+        hst3(e, HF_MOVE, h, mk3(fmaf(alpha, step.x, move.x), fmaf(alpha, step.y, move.y), fmaf(alpha, step.z, move.z)));
+    }
+    __syncwarp();
+}
+
+// Newton steps with exact line search on one block; KN >= the block's dimension.
+template <int KN>
+__device__ __noinline__ void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
+    const TemplateView& t = *e.t;
+    const uint32_t l = e.lane, nb = tile.nblocks, dim = blk_dim(e, b);
+    const bool coord = l < dim;
+    const uint32_t* inc = blk_inc(e, nb);
+    const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
+    float* velocity = block_vel(e, b, position);
+    float* dvec = sm_vec(e, kVecD);
+    bool coupled = false;
+    for (uint32_t k = ib + l; k < ie; k += 32u) {
+        const uint32_t h = inc[k];
+        const uint32_t o = hu(e, HF_OWNER, h);
+        coupled |= (o & 0xffffu) != kNoBlock16 && (o >> 16) != kNoBlock16;
+        hf(e, HF_NB, h) = hf(e, HF_DUAL, h);
+        hst3(e, HF_MOVE, h, mk3(0.f, 0.f, 0.f));
+    }
+    coupled = __any_sync(NKB_FULL, coupled);
+    __syncwarp();
+    float mrow[KN];
+#pragma unroll
+    for (int k = 0; k < KN; ++k) mrow[k] = (coord && (uint32_t)k < dim) ? block_mass(e, b, l, (uint32_t)k) : ((uint32_t)k == l ? 1.f : 0.f);
+    const float start = coord ? velocity[l] : 0.f;
+    const float fr = (coord && !position) ? block_free(e, b)[l] : 0.f;
+    float u = start;
+    if (tile.iteration == 0u && !position) {
+        const float d = coord ? fr - u : 0.f;
+        float ms = 0.f;
+#pragma unroll
+        for (int k = 0; k < KN; ++k) ms += mrow[k] * __shfl_sync(NKB_FULL, d, k);
+        CSum cs = {0.f, 0.f};
+        if (coord) csum_addp(cs, d, ms);
+        const float ic = warp_csum_total(cs);
+        if (ic > 0.f && isfinite(ic)) {
+            if (l < (uint32_t)KN) dvec[l] = d;
+            __syncwarp();
+            row_steps(e, tile, b, dvec);
+            const float alpha = search_line(e, tile, b, -ic, ic);
+            if (alpha > 0.f) { u = fmaf(alpha, d, u); apply_moves(e, tile, b, alpha); }
+        }
+    }
+    bool failure = false;
+    float primal = FLT_MAX;
+    for (uint32_t step = 0u; step < kNewtonSteps; ++step) {
+        // ---- assemble H (row l in registers) and g ----
+        float hrow[KN];
+        const float diff = u - fr;
+        const float part = diff - u;
+        const float diff_err = (u - (diff - part)) + (-fr - part);
+        CSum inertial = {0.f, 0.f};
+        float scale = 0.f, diag = 0.f;
+#pragma unroll
+        for (int k = 0; k < KN; ++k) {
+            const float hi = __shfl_sync(NKB_FULL, diff, k), lo = __shfl_sync(NKB_FULL, diff_err, k);
+            hrow[k] = mrow[k];
+            csum_addp(inertial, mrow[k], hi);
+            csum_addp(inertial, mrow[k], lo);
+            scale += fabsf(mrow[k]) * fabsf(hi);
+        }
+        CSum g = {-inertial.value, -inertial.error};
+        for (uint32_t chunk = ib; chunk < ie; chunk += 32u) {
+            const bool listed = chunk + l < ie;
+            const uint32_t own = listed ? inc[chunk + l] : 0u;
+            V3 f = mk3(0.f, 0.f, 0.f), noise = f;
+            float cxx = 0.f, cyy = 0.f, czz = 0.f, cyz = 0.f;
+            uint32_t unit = 0xffffffffu, side = 0u, axes = 1u;
+            float unitv = 0.f;
+            if (listed) {
+                const V3 move = hf3(e, HF_MOVE, own), res = hf3(e, HF_RES, own);
+                head_response(e, own, move, f, cxx, cyy, czz, cyz);
+                noise = mk3(fabsf(f.x) + cxx * (fabsf(res.x) + fabsf(move.x)), fabsf(f.y) + cyy * (fabsf(res.y) + fabsf(move.y)),
+                            fabsf(f.z) + czz * (fabsf(res.z) + fabsf(move.z)));
+                side = head_owner(e, own, 0u) == b ? 0u : 1u;
+                axes = head_axes(e, own);
+                const uint32_t jo = hu(e, HF_JOFF, own);
+                if (b == t.B && (jo & kUnitRow)) { unit = jo & 0xffffu; unitv = hf(e, HF_UNITV, own); }
+            }
+            const bool contributes = listed && (f.x != 0.f || f.y != 0.f || f.z != 0.f || cxx != 0.f || cyy != 0.f || czz != 0.f || cyz != 0.f ||
+                                                noise.x != 0.f || noise.y != 0.f || noise.z != 0.f);
+            for (uint32_t pending = __ballot_sync(NKB_FULL, contributes && unit != 0xffffffffu); pending != 0u; pending &= pending - 1u) {
+                const int src = __ffs(pending) - 1;
+                const uint32_t target = __shfl_sync(NKB_FULL, unit, src);
+                const float v = __shfl_sync(NKB_FULL, unitv, src), fx = __shfl_sync(NKB_FULL, f.x, src);
+                const float c0 = __shfl_sync(NKB_FULL, cxx, src), nx = __shfl_sync(NKB_FULL, noise.x, src);
+                if (l == target) { diag += v * c0 * v; csum_addp(g, v, fx); scale += fabsf(v) * nx; }
+            }
+            for (uint32_t pending = __ballot_sync(NKB_FULL, contributes && unit == 0xffffffffu); pending != 0u; pending &= pending - 1u) {
+                const int src = __ffs(pending) - 1;
+                const uint32_t hs = __shfl_sync(NKB_FULL, own, src), ss = __shfl_sync(NKB_FULL, side, src), as = __shfl_sync(NKB_FULL, axes, src);
+                const float fx = __shfl_sync(NKB_FULL, f.x, src), c0 = __shfl_sync(NKB_FULL, cxx, src), nx = __shfl_sync(NKB_FULL, noise.x, src);
+                const float j0 = coord ? head_jac(e, hs, ss, 0u, l, b) : 0.f;
+                csum_addp(g, j0, fx);
+                scale += fabsf(j0) * nx;
+                if (as == 1u) {
+                    const float a0 = j0 * c0;
+#pragma unroll
+                    for (int k = 0; k < KN; ++k) hrow[k] += a0 * __shfl_sync(NKB_FULL, j0, k);
+                    continue;
+                }
+                const float fy = __shfl_sync(NKB_FULL, f.y, src), fz = __shfl_sync(NKB_FULL, f.z, src);
+                const float c1 = __shfl_sync(NKB_FULL, cyy, src), c2 = __shfl_sync(NKB_FULL, czz, src), c12 = __shfl_sync(NKB_FULL, cyz, src);
+                const float ny = __shfl_sync(NKB_FULL, noise.y, src), nz = __shfl_sync(NKB_FULL, noise.z, src);
+                const float j1 = coord ? head_jac(e, hs, ss, 1u, l, b) : 0.f, j2 = coord ? head_jac(e, hs, ss, 2u, l, b) : 0.f;
+                csum_addp(g, j1, fy); csum_addp(g, j2, fz);
+                scale += fabsf(j1) * ny + fabsf(j2) * nz;
+                const float a0 = j0 * c0, a1 = j1 * c1 + j2 * c12, a2 = j2 * c2 + j1 * c12;
+#pragma unroll
+                for (int k = 0; k < KN; ++k)
+                    hrow[k] += a0 * __shfl_sync(NKB_FULL, j0, k) + a1 * __shfl_sync(NKB_FULL, j1, k) + a2 * __shfl_sync(NKB_FULL, j2, k);
+            }
+        }
+        float force = 0.f, inertia = 0.f;
+        bool finite = true;
+#pragma unroll
+        for (int k = 0; k < KN; ++k) {
+            if ((uint32_t)k == l) hrow[k] += diag;
+            finite &= isfinite(hrow[k]);
+            scale += fabsf(hrow[k]) * fabsf(__shfl_sync(NKB_FULL, u, k));
+        }
+        if (coord) { force = g.value + g.error; inertia = inertial.value + inertial.error; }
+        finite &= isfinite(force);
+        if (!__all_sync(NKB_FULL, finite)) { failure = true; break; }
+        bool converged = __all_sync(NKB_FULL, !coord || fabsf(force) <= kRoundings * FLT_EPSILON * scale);
+        float d = 0.f;
+        if (converged && tile.tol > 0.f) {
+            d = solve_block_mass(e, b, force);
+            converged = __all_sync(NKB_FULL, !coord || fabsf(d) < tile.tol);
+        }
+        if (converged) { primal = 0.f; break; }
+        // ---- Cholesky in registers: lane l keeps row l of L (block_descent_tile.cuh:1623-1641) ----
+        bool valid = true;
+        float inverse = 0.f;
+#pragma unroll
+        for (int k = 0; k < KN; ++k) {
+            if ((uint32_t)k >= dim) break;
+            float value = hrow[k];
+#pragma unroll
+            for (int j = 0; j < k; ++j) value -= hrow[j] * __shfl_sync(NKB_FULL, hrow[j], k);
+            const float pivot = __shfl_sync(NKB_FULL, value, k);
+            valid &= pivot > 0.f && pivot <= FLT_MAX;
+            const float root = sqrtf(valid ? pivot : 1.0f), sc = 1.0f / root;
+            hrow[k] = l == (uint32_t)k ? root : value * sc;
+            inverse = l == (uint32_t)k ? sc : inverse;
+        }
+        if (!valid) { failure = true; break; }
+        // ---- d = H^-1 g ----
+        {
+            float* Lt = sm_chol(e);
+            constexpr int kS = KN + 1;
+            float r = force;
+#pragma unroll
+            for (int j = 0; j < KN; ++j) {
+                if ((uint32_t)j >= dim) break;
+                const float y = __shfl_sync(NKB_FULL, r * inverse, j);
+                r = l == (uint32_t)j ? y : (l > (uint32_t)j ? fmaf(-hrow[j], y, r) : r);
+                if (l > (uint32_t)j && l < (uint32_t)KN) Lt[j * kS + l] = hrow[j];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int k = KN; k > 0; --k) {
+                if ((uint32_t)k > dim) continue;
+                const int j = k - 1;
+                const float x = __shfl_sync(NKB_FULL, r * inverse, j);
+                const float lv = l < (uint32_t)j ? Lt[l * kS + j] : 0.f;
+                r = l == (uint32_t)j ? x : fmaf(-lv, x, r);
+            }
+            __syncwarp();
+            d = coord ? r : 0.f;
+        }
+        float ms = 0.f;
+#pragma unroll
+        for (int k = 0; k < KN; ++k) ms += mrow[k] * __shfl_sync(NKB_FULL, d, k);
+        CSum dec = {0.f, 0.f}, slo = {0.f, 0.f}, cur = {0.f, 0.f};
+        if (coord) { csum_addp(dec, force, d); csum_addp(slo, inertia, d); csum_addp(cur, d, ms); }
+        const float total_dec = warp_csum_total(dec), islope = warp_csum_total(slo), icurv = warp_csum_total(cur);
+        if (!isfinite(total_dec) || !isfinite(islope) || !isfinite(icurv)) { failure = true; break; }
+        if (!(total_dec > 0.f)) break;
+        if (l < (uint32_t)KN) dvec[l] = d;
+        __syncwarp();
+        row_steps(e, tile, b, dvec);
+        const float alpha = search_line(e, tile, b, islope, icurv);
+        const float after = fmaf(alpha, d, u);
+        const bool fin = __all_sync(NKB_FULL, !coord || isfinite(after));
+        const bool rounded = __all_sync(NKB_FULL, !coord || after == u);
+        if (!fin) { failure = true; break; }
+        primal = warp_max((coord && !rounded) ? fabsf(alpha * d) : 0.f);
+        if (!(alpha > 0.f)) break;
+        u = after;
+        apply_moves(e, tile, b, alpha);
+        if (rounded) break;
+    }
+    for (uint32_t k = ib + l; k < ie; k += 32u) {
+        const uint32_t h = inc[k];
+        const V3 res = hf3(e, HF_RES, h), move = hf3(e, HF_MOVE, h);
+        hst3(e, HF_RES, h, mk3(__fsub_rn(res.x, move.x), __fsub_rn(res.y, move.y), __fsub_rn(res.z, move.z)));
+    }
+    if (failure) e.status |= kStatusSolverFailure;
+    float moved = failure ? FLT_MAX : 0.f;
+    if (coord) moved = fmaxf(moved, residual_abs(u - start));
+    moved = warp_max(moved);
+    tile.momentum = fmaxf(tile.momentum, moved);
+    if (failure) primal = FLT_MAX;
+    tile.residual = fmaxf(tile.residual, fmaxf(primal, coupled ? moved : 0.f));
+    if (coord) velocity[l] = u;
+    __syncwarp();
+}
+
+template <int KN>
+NKB_DEV void descend_blocks(Env& e, Tile& tile, bool position) {
+    const uint32_t nb = tile.nblocks, B = e.t->B;
+    for (uint32_t color = 0u; color < 32u; ++color) {
+        bool any = false;
+        for (uint32_t b = 0u; b < nb; ++b) {
+            if (blk_color(e, nb, b) != color) continue;
+            any = true;
+            if (b < B) descend_block<8>(e, tile, b, position);
+            else descend_block<KN>(e, tile, b, position);
+        }
+        if (!any && color > 0u) { bool later = false; for (uint32_t b = 0u; b < nb; ++b) later |= blk_color(e, nb, b) != 0xffffffffu && blk_color(e, nb, b) > color; if (!later) break; }
+    }
+}
+
+struct DualMomentum { float t, beta; };
+
+// Dual update over every head (block_descent_tile.cuh:2493-2595); returns the residual classes.
+NKB_DEV void update_duals(Env& e, const Tile& tile, DualMomentum* mom, bool velocity, bool commit, float out[3]) {
+    float cn = 0.f, ct = 0.f, cj = 0.f;
+    double restart = 0.0;
+    for (uint32_t h = e.lane; h < tile.nheads; h += 32u) {
+        const uint32_t fl = hu(e, HF_FLAGS, h);
+        const bool contact = (fl & (kHeadContact | kHeadScalar)) == kHeadContact;
+        const V3 tdual = commit ? hf3(e, HF_DUAL, h) : hf3(e, HF_BASE, h);
+        const V3 res = hf3(e, HF_RES, h);
+        const float rho = hf(e, HF_RHO, h), lower = hf(e, HF_LOWER, h), upper = hf(e, HF_UPPER, h), mu = hf(e, HF_MU, h);
+        const Resp rs = {hf(e, HF_RSD, h), hf(e, HF_RSR, h)};
+        const float normal = scalar_impulse(tdual.x, rho, res.x, lower, upper, rs).impulse;
+        Relax rx;
+        rx.step = hf3(e, HF_RXS, h); rx.weight = hf(e, HF_RXW, h); rx.point = hf3(e, HF_RXP, h);
+        if (!commit) { rx.step = mk3(0.f, 0.f, 0.f); rx.weight = 0.f; rx.point = rx.step; }
+        V3 dual;
+        if (!contact) dual = mk3(normal, 0.f, 0.f);
+        else {
+            float iy, iz, c1, c2, c3;
+            tangent_impulse(tdual, rho, res.y, res.z, normal, mu, mu, iy, iz, c1, c2, c3);
+            dual = relax_contact_impulse(tdual, mk3(normal, iy, iz), rx);
+        }
+        float sn, st;
+        multiplier_steps(tdual, dual, rs.residual_scale, rs.dual_scale, rho, contact ? mu : 0.f, contact ? mu : 0.f, sn, st);
+        if (!commit && rs.residual_scale > 0.f) sn = fabsf(dual.x - tdual.x) / rs.residual_scale;
+        const V3 physical = commit ? dual : tdual;
+        if (!contact) {
+            const bool normal_row = (fl & kHeadContactNormal) != 0u;
+            const float rate = -res.x;
+            const float violation = physical.x > 0.f ? fabsf(rate) : fmaxf(-rate, 0.f);
+            const float r = normal_row ? fmaxf(sn, violation) : sn;
+            if (normal_row) cn = fmaxf(cn, residual_abs(r)); else cj = fmaxf(cj, residual_abs(r));
+        } else {
+            if (commit) { hst3(e, HF_RXS, h, rx.step); hf(e, HF_RXW, h) = rx.weight; hst3(e, HF_RXP, h, rx.point); }
+            const V3 v = mk3(-res.x, -res.y, -res.z);
+            cn = fmaxf(cn, residual_abs(physical.x > 0.f ? fabsf(v.x) : fmaxf(-v.x, 0.f)));
+            ct = fmaxf(ct, residual_abs(fmaxf(st, fmaxf(along_axis(physical.y, v.y), along_axis(physical.z, v.z)))));
+        }
+        if (!commit) continue;
+        if (velocity) hst3(e, HF_LAM, h, dual);
+        const bool extrapolate = contact || rs.dual_scale != 0.f;
+        const V3 base = hf3(e, HF_BASE, h);
+        if (extrapolate) restart += momentum_restart(tdual, dual, base, multiplier_metric(rs.residual_scale, rho, contact, mu, mu));
+        if (mom != nullptr) hst3(e, HF_MOVE, h, base);
+        hst3(e, HF_DUAL, h, dual);
+        hst3(e, HF_BASE, h, dual);
+    }
+    __syncwarp();
+    out[0] = warp_max(cn); out[1] = warp_max(ct); out[2] = warp_max(cj);
+    if (mom != nullptr) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) restart += __shfl_xor_sync(NKB_FULL, restart, o);
+        if (restart > 0.0) mom->t = 1.0f;
+        const float tn = 0.5f * (1.0f + sqrtf(fmaf(4.0f * mom->t, mom->t, 1.0f)));
+        mom->beta = (mom->t - 1.0f) / tn;
+        mom->t = tn;
+        for (uint32_t h = e.lane; h < tile.nheads; h += 32u) {
+            const bool contact = head_axes(e, h) == 3u;
+            const bool extrapolate = contact || hf(e, HF_RSD, h) != 0.f;
+            const float mu = hf(e, HF_MU, h);
+            hst3(e, HF_DUAL, h, extrapolate_dual(hf3(e, HF_MOVE, h), hf3(e, HF_BASE, h), extrapolate ? mom->beta : 0.f,
+                                                 hf(e, HF_LOWER, h), hf(e, HF_UPPER, h), contact, mu, mu));
+        }
+        __syncwarp();
+    }
+}
+
+// Momentum balance of every moving block against the physical multipliers (block_descent_tile.cuh:2379-2489).
+NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
+    const uint32_t nb = tile.nblocks, l = e.lane;
+    const uint32_t* inc = blk_inc(e, nb);
+    for (uint32_t color = 0u; color < 32u; ++color) for (uint32_t b = 0u; b < nb; ++b) {
+        if (blk_color(e, nb, b) != color) continue;
+        const uint32_t dim = blk_dim(e, b);
+        const bool coord = l < dim;
+        float* vel = block_vel(e, b, false);
+        const float* fr = block_free(e, b);
+        double balance = 0.0;
+        if (coord) for (uint32_t j = 0u; j < dim; ++j) balance -= (double)block_mass(e, b, l, j) * ((double)vel[j] - fr[j]);
+        const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
+        for (uint32_t k = ib; k < ie; ++k) {
+            const uint32_t h = inc[k];
+            const uint32_t side = head_owner(e, h, 0u) == b ? 0u : 1u, axes = head_axes(e, h);
+            const V3 lam = hf3(e, HF_LAM, h);
+            for (uint32_t ax = 0u; ax < axes; ++ax) {
+                const float imp = comp(lam, (int)ax);
+                if (imp == 0.f) continue;
+                if (coord) balance += (double)head_jac(e, h, side, ax, l, b) * imp;
+            }
+        }
+        const float force = coord ? (float)balance : 0.f;
+        const bool finite = __all_sync(NKB_FULL, !coord || fabs(balance) <= FLT_MAX);
+        float residual = FLT_MAX, dir = 0.f;
+        if (finite) {
+            dir = solve_block_mass(e, b, force);
+            residual = warp_max(coord ? (isfinite(dir) ? fabsf(dir) : FLT_MAX) : 0.f);
+        }
+        tile.residual = fmaxf(tile.residual, residual);
+        if (reconstruct && finite) {
+            if (coord) vel[l] += dir;
+            tile.momentum = fmaxf(tile.momentum, residual);
+            __syncwarp();
+        }
+    }
+}
+
+// The whole constraint solve of one env.  On entry the heads are built, the articulation's post-dynamics
+// velocity is in (e.qd, sm_vel(root)) and free-body velocities are in sm_bvel.
+template <int KN>
+NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
+    const TemplateView& t = *e.t;
+    const uint32_t l = e.lane, B = t.B, n = t.ndof;
+    Tile tile;
+    tile.nheads = nheads; tile.nblocks = B + (n != 0u ? 1u : 0u); tile.iteration = 0u;
+    tile.momentum = tile.residual = 0.f; tile.tol = t.cfg.velocity_tolerance;
+    const uint32_t nb = tile.nblocks;
+    // rigid blocks: free velocity, mass, carried constraint velocity (block_descent_rigid.cuh:4-48)
+    for (uint32_t b = l; b < B; b += 32u) {
+        float* bv = sm_bvel(e, b);
+        float* bf = sm_bfree(e, b);
+        const float im = __ldg(t.inv_mass + b);
+        uint32_t dim = 0u;
+        if (im > 0.f && __ldg(t.body_to_link + b) == kNoLink) {
+            const float* w = sm_bwinv(e, b);
+            const double xx = w[0], yy = w[1], zz = w[2], xy = w[3], xz = w[4], yz = w[5];
+            const double cxx = yy * zz - yz * yz, cyy = xx * zz - xz * xz, czz = xx * yy - xy * xy;
+            const double cxy = xz * yz - xy * zz, cxz = xy * yz - xz * yy, cyz = xy * xz - xx * yz;
+            const double det = xx * cxx + xy * cxy + xz * cxz;
+            if (det > 0.0) {
+                const double inv = 1.0 / det;
+                float* bm = sm_bmass(e, b);
+                bm[0] = (float)(1.0 / (double)im);
+                bm[1] = (float)(cxx * inv); bm[2] = (float)(cyy * inv); bm[3] = (float)(czz * inv);
+                bm[4] = (float)(cxy * inv); bm[5] = (float)(cxz * inv); bm[6] = (float)(cyz * inv);
+                dim = 6u;
+            } else e.status |= kStatusSolverFailure;
+        }
+        blk_dim(e, b) = dim;
+        const float* carry = e.s->carry_rigid + ((size_t)e.env * B + b) * 6u;
+#pragma unroll
+        for (int k = 0; k < 6; ++k) {
+            bf[k] = bv[k];
+            const float c = dim != 0u ? carry[k] : 0.f;
+            bv[k] = bf[k] + (isfinite(c) ? c : 0.f);
+        }
+        float* ps = sm_bpseudo(e, b);
+#pragma unroll
+        for (int k = 0; k < 6; ++k) ps[k] = 0.f;
+    }
+    if (n != 0u && l == 0u) blk_dim(e, B) = n;
+    // articulation coordinates: free = post-dynamics velocity
+    {
+        const float qd_of_link = __shfl_sync(NKB_FULL, e.qd, e.dof_link);
+        if (l < n) {
+            const float value = e.dof_comp == kNoLink ? qd_of_link : sm_vel(e, e.dof_link)[e.dof_comp];
+            const float c = e.s->carry_artic[(size_t)e.env * n + l];
+            sm_vec(e, kVecFree)[l] = value;
+            sm_vec(e, kVecU)[l] = value + (isfinite(c) ? c : 0.f);
+            sm_vec(e, kVecPseudo)[l] = 0.f;
+        }
+    }
+    __syncwarp();
+    init_heads(e, tile);
+    index_blocks(e, tile, true);
+    init_residuals(e, tile);
+    float rows[3] = {0.f, 0.f, 0.f};
+    float cls[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t sweeps = 0u;
+    DualMomentum mom = {1.0f, 0.0f};
+    const uint32_t iterations = t.cfg.vel_iters;
+    while (sweeps < iterations) {
+        tile.iteration = sweeps++;
+        tile.momentum = 0.f; tile.residual = 0.f;
+        descend_blocks<KN>(e, tile, false);
+        update_duals(e, tile, &mom, true, true, rows);
+        if (sweeps == iterations || fmaxf(fmaxf(rows[0], rows[1]), fmaxf(rows[2], tile.residual)) < tile.tol) measure_primals(e, tile, false);
+        if (fmaxf(fmaxf(rows[0], rows[1]), rows[2]) < tile.tol && tile.residual >= tile.tol && tile.residual < FLT_MAX) {
+            measure_primals(e, tile, true);
+            if (tile.residual < FLT_MAX) {
+                init_residuals(e, tile);
+                update_duals(e, tile, nullptr, true, false, rows);
+                tile.residual = 0.f;
+                measure_primals(e, tile, false);
+            }
+        }
+        cls[0] = rows[0]; cls[1] = rows[1]; cls[2] = rows[2]; cls[3] = tile.residual;
+        const float largest = fmaxf(fmaxf(rows[0], rows[1]), fmaxf(rows[2], tile.residual));
+        if (largest < tile.tol || largest == FLT_MAX) break;
+    }
+    if (l < 4u) e.s->solver_residual[(size_t)e.env * 4u + l] = cls[l];
+    if (l == 0u) e.s->solver_sweeps[e.env] = sweeps;
+    // finish: velocities back to the links, carried velocities to global memory
+    if (n != 0u) {
+        const float* U = sm_vec(e, kVecU);
+        if (l < n) {
+            e.s->carry_artic[(size_t)e.env * n + l] = U[l] - sm_vec(e, kVecFree)[l];
+            if (e.dof_comp != kNoLink) sm_vel(e, e.dof_link)[e.dof_comp] = U[l];
+        }
+        if (l < t.L && joint_dofs(e.jtype) == 1u) e.qd = U[e.link_dof];
+    }
+    for (uint32_t b = l; b < B; b += 32u) {
+        float* carry = e.s->carry_rigid + ((size_t)e.env * B + b) * 6u;
+        const float* bv = sm_bvel(e, b);
+        const float* bf = sm_bfree(e, b);
+#pragma unroll
+        for (int k = 0; k < 6; ++k) carry[k] = blk_dim(e, b) != 0u ? bv[k] - bf[k] : 0.f;
+    }
+    __syncwarp();
+    // split-impulse position pass
+    if (t.cfg.pos_iters != 0u && nheads != 0u) {
+        bool push = false, coupled = false;
+        for (uint32_t h = l; h < nheads; h += 32u) {
+            const uint32_t fl = hu(e, HF_FLAGS, h);
+            const bool spec = (fl & kHeadSpeculative) != 0u;
+            const float slop = spec ? 0.f : t.cfg.pos_slop;
+            const float pen_row = hf(e, HF_PEN, h);
+            const bool position = (fl & kHeadVelocityOnly) == 0u && (spec || pen_row > slop || hf(e, HF_DUAL, h) != 0.f);
+            float bias = 0.f, rounding = 0.f;
+            if (position) {
+                const float penetration = fmaxf(pen_row - slop, 0.f);
+                if (spec) {
+                    const float cd = sm_cdepth(e)[hu(e, HF_REF, h) & 0xffffu];
+                    const double depth = (double)cd - slop, reserve = (double)pen_row - cd;
+                    const double correction = t.cfg.pos_beta * fmax(depth, 0.0) + reserve;
+                    const double target = fmin(depth, 0.0) + correction;
+                    double velocity = 0.0;
+                    for (uint32_t side = 0u; side < 2u; ++side) {
+                        const uint32_t b = head_owner(e, h, side);
+                        if (b == kNoBlock16) continue;
+                        const uint32_t dim = blk_dim(e, b);
+                        const float* u = block_vel(e, b, false);
+                        double v = 0.0;
+                        for (uint32_t i = 0u; i < dim; ++i) v += (double)head_jac(e, h, side, 0u, i, b) * u[i];
+                        velocity += v;
+                    }
+                    const double limit = fmin(correction / t.cfg.dt, (double)t.cfg.baumgarte_max_velocity);
+                    bias = (float)fmin(target / t.cfg.dt - velocity, limit);
+                    rounding = (float)(target > 0.0 ? 0.0 : fmax(reserve, 0.0) / t.cfg.dt);
+                } else {
+                    bias = fminf(t.cfg.pos_beta * penetration / t.cfg.dt, t.cfg.baumgarte_max_velocity);
+                }
+            } else hu(e, HF_OWNER, h) = kNoBlock16 | (kNoBlock16 << 16);
+            const uint32_t o = hu(e, HF_OWNER, h);
+            coupled |= (o & 0xffffu) != kNoBlock16 && (o >> 16) != kNoBlock16;
+            hu(e, HF_FLAGS, h) = fl | kHeadScalar;
+            hf(e, HF_LOWER, h) = 0.f; hf(e, HF_UPPER, h) = FLT_MAX;
+            const Resp rs = scalar_response(hf(e, HF_RHO, h), 0.f);
+            hf(e, HF_RSD, h) = rs.dual_scale; hf(e, HF_RSR, h) = rs.residual_scale;
+            hst3(e, HF_RES, h, mk3(bias, 0.f, 0.f));
+            hst3(e, HF_DUAL, h, mk3(0.f, 0.f, 0.f));
+            push |= bias > rounding;
+        }
+        push = __any_sync(NKB_FULL, push); coupled = __any_sync(NKB_FULL, coupled);
+        __syncwarp();
+        if (push) {
+            index_blocks(e, tile, false);
+            const uint32_t positions = coupled ? t.cfg.pos_iters : 1u;
+            for (uint32_t it = 0u; it < positions; ++it) {
+                tile.iteration = sweeps + it;
+                descend_blocks<KN>(e, tile, true);
+                if (it + 1u < positions) update_duals(e, tile, nullptr, false, true, rows);
+            }
+        }
+    }
+    if (e.s->dbg_qdot_pseudo != nullptr && l < n) e.s->dbg_qdot_pseudo[(size_t)e.env * n + l] = sm_vec(e, kVecPseudo)[l];
+    (void)nb;
+}
+
+}  // namespace nkb

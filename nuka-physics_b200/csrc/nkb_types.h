@@ -1,0 +1,112 @@
+// Plain-data views shared by the host runtime and the CUDA kernels of the batched articulated step.
+// One "template" describes a single environment (the role of the reference's cooked nk::Model,
+// src/nk/model/model.hpp:175-244); per-env state lives in env-major arrays whose public members keep the
+// layouts of the reference's state fields (src/nk/model/fields.yaml): q/qdot per link, poses as
+// xyz + wxyz (7 floats), spatial velocities angular-first (6 floats).
+#pragma once
+#include <cstdint>
+
+namespace nkb {
+
+constexpr uint32_t kNoLink = 0xffffffffu;
+constexpr uint32_t kMaxLinks = 32u;     // one warp lane per link
+constexpr uint32_t kMaxDof = 32u;       // one warp lane per articulation coordinate
+constexpr uint32_t kMaxBodies = 64u;
+constexpr uint32_t kPtsPerSlot = 4u;
+
+enum JointType : uint32_t { kRevolute = 0, kPrismatic = 1, kFixed = 2, kFloating = 3, kSpherical = 4 };
+enum ShapeKind : uint32_t { kSphere = 0, kCapsule = 1, kBox = 2, kPlane = 3 };
+// env status bits, reference src/phi/op_schema.hpp:36-52
+enum : uint32_t { kStatusPairOverflow = 1u << 0, kStatusDofOverflow = 1u << 2, kStatusGyroFailure = 1u << 5,
+                  kStatusControlFailure = 1u << 10, kStatusSolverFailure = 1u << 13,
+                  kStatusHeadOverflow = 1u << 20 };
+// head flags
+enum : uint32_t { kHeadContact = 1u << 0, kHeadContactNormal = 1u << 1, kHeadSpeculative = 1u << 2,
+                  kHeadVelocityOnly = 1u << 3, kHeadDrive = 1u << 4, kHeadLimit = 1u << 5, kHeadFriction = 1u << 6,
+                  kHeadScalar = 1u << 7 /* position pass: only the normal axis */ };
+constexpr uint32_t kHeadWords = 54u;    // words of shared memory per solver head
+
+struct Config {
+    float dt;
+    float gravity[3];
+    float pos_beta, pos_slop, contact_margin, baumgarte_max_velocity, overlap_recovery_velocity, velocity_tolerance;
+    uint32_t vel_iters, pos_iters, max_contacts, max_pairs;
+};
+
+// Device pointers to the template tables (read-only during a step).
+struct TemplateView {
+    uint32_t L, B, ndof, max_depth, n_excluded, floating_root;
+    uint32_t head_cap;          // solver heads per env held in shared memory
+    uint32_t point_cap;         // contact points per env that get rows
+    const uint32_t *parent, *jtype, *depth, *child_begin, *children, *link_dof, *link_body, *geom_kind, *limit_flags;
+    const uint32_t *dof_link, *anc_mask;
+    const float *axis, *offset, *local_quat, *inertia10, *damping, *armature, *frictionloss, *stiffness, *spring_ref;
+    const float *limit_lower, *limit_upper, *geom_pos, *geom_quat;
+    const uint32_t *shape_kind, *contype, *conaffinity, *group, *body_to_link;
+    const int32_t *body_id;
+    const float *shape_params, *mu, *inv_mass, *inv_inertia, *inertial_pos, *inertial_quat;
+    const unsigned long long *excluded;
+    // body-row pairs (a << 16 | b, a < b, ascending) that pass the template-constant filters: not both
+    // static, bitmask/group admitted, not excluded.  Only these need an AABB test each step.
+    const uint32_t *adm_pairs;
+    uint32_t n_adm;
+    Config cfg;
+};
+
+struct CacheEntry {             // one cached contact point (warm start)
+    unsigned long long feature;
+    uint32_t pair;              // (a << 16) | b, 0xffffffff when empty
+    uint32_t age;
+    float lambda[3];
+    float normal[3];
+};
+
+// Device pointers to the per-env state, env-major.
+struct StateView {
+    uint32_t env_count;
+    float *q, *qdot, *qddot, *tau, *actuator;                   // E x L
+    float *base_pose;                                           // E x 7
+    float *link_pose;                                           // E x L x 7
+    float *link_vel;                                            // E x L x 6
+    float *drive_target, *vel_target, *kp, *kd, *force_limit, *feedforward;   // E x L
+    float *body_pose;                                           // E x B x 7
+    float *body_linvel, *body_angvel;                           // E x B x 3
+    float *carry_artic;                                         // E x ndof  (solved - free velocity of the last step)
+    float *carry_rigid;                                         // E x B x 6
+    CacheEntry *cache;                                          // E x S x 4
+    uint32_t *status;                                           // E
+    float *solver_residual;                                     // E x 4
+    uint32_t *solver_sweeps;                                    // E
+    // contact read-out (public CONTACT_* style fields and parity taps)
+    uint32_t *pair_count;                                       // E
+    uint32_t *pairs;                                            // E x S x 2
+    uint32_t *contact_count;                                    // E x S
+    float *contact_point, *contact_normal;                      // E x S x 4 x 3
+    float *contact_depth;                                       // E x S x 4
+    // optional parity taps (null unless requested)
+    float *dbg_mass;                                            // E x ndof x ndof
+    float *dbg_qdot_pseudo;                                     // E x ndof
+};
+
+// Shared-memory layout of one env (offsets in 4-byte words), filled by the host.
+struct SmemLayout {
+    uint32_t pose, xrot, xtr, vel, vbias, acc, pbias, ic;       // per link
+    uint32_t mass, factor, vecs;                                // articulation
+    uint32_t bpose, bvel, bwinv, aabb, bmass, bfree, bpseudo;   // bodies
+    uint32_t pairs, ccount, cpoint, cnormal, cdepth, cfeat;     // contacts (cfeat also stages the cache rebuild)
+    uint32_t heads, jpool, binfo, chol;                         // solver
+    uint32_t words;                                             // total per env
+    uint32_t ld;                                                // leading dimension of mass/factor (ndof | 1)
+};
+
+enum StepMode : uint32_t { kModeStep = 0, kModeDynamicsOnly = 1, kModeCollideOnly = 2, kModeRefresh = 3 };
+
+struct StepParams {
+    TemplateView t;
+    StateView s;
+    SmemLayout sm;
+    uint32_t mode;
+    uint32_t steps;
+};
+
+}  // namespace nkb

@@ -1,0 +1,452 @@
+#include "nkb_world.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+namespace nkb {
+
+namespace {
+
+constexpr int kOk = 0, kInvalidArg = 1, kCudaError = 3, kParseError = 5, kOutOfMemory = 6, kNotSupported = 7;
+
+struct BlobEntry { uint32_t dtype; uint64_t n; const uint8_t* data; };
+
+bool BlobFind(const uint8_t* blob, size_t bytes, const char* name, BlobEntry* out) {
+    if (bytes < 8 || std::memcmp(blob, "NKT1", 4) != 0) return false;
+    uint32_t count;
+    std::memcpy(&count, blob + 4, 4);
+    size_t at = 8;
+    for (uint32_t i = 0; i < count; ++i) {
+        if (at + 48 > bytes) return false;
+        uint32_t dtype; uint64_t n;
+        std::memcpy(&dtype, blob + at + 32, 4);
+        std::memcpy(&n, blob + at + 40, 8);
+        const size_t esz = dtype == 3u ? 8u : 4u;
+        const size_t payload = static_cast<size_t>((n * esz + 7u) & ~uint64_t{7});
+        if (at + 48 + payload > bytes) return false;
+        if (std::strncmp(reinterpret_cast<const char*>(blob + at), name, 32) == 0) { *out = {dtype, n, blob + at + 48}; return true; }
+        at += 48 + payload;
+    }
+    return false;
+}
+
+template <typename T>
+std::vector<T> BlobVec(const uint8_t* blob, size_t bytes, const char* name, uint64_t expect) {
+    BlobEntry e;
+    if (!BlobFind(blob, bytes, name, &e)) throw Error(kParseError, std::string("template field missing: ") + name);
+    if (e.n != expect) throw Error(kParseError, std::string("template field has the wrong size: ") + name);
+    std::vector<T> v(static_cast<size_t>(e.n));
+    if (e.n) std::memcpy(v.data(), e.data, static_cast<size_t>(e.n) * sizeof(T));
+    return v;
+}
+
+uint32_t JointDofs(uint32_t t) { return (t == kRevolute || t == kPrismatic) ? 1u : t == kFloating ? 6u : t == kSpherical ? 3u : 0u; }
+
+// ShapeFilterAdmits, reference src/collision/shape_kind.hpp:26-33
+bool FilterAdmits(uint32_t ta, uint32_t aa, uint32_t ga_, uint32_t tb, uint32_t ab, uint32_t gb_) {
+    if (((ta & ab) | (tb & aa)) == 0u) return false;
+    const int32_t ga = static_cast<int32_t>(ga_), gb = static_cast<int32_t>(gb_);
+    return !(ga != 0 && gb != 0 && (ga > 0 ? (ga != gb && gb > 0) : ga == gb));
+}
+
+}  // namespace
+
+HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
+    const auto* blob = static_cast<const uint8_t*>(blob_in);
+    if (blob == nullptr || bytes < 8 || std::memcmp(blob, "NKT1", 4) != 0) throw Error(kParseError, "not a cooked template (NKT1) blob");
+    HostTemplate t;
+    const auto cf = BlobVec<float>(blob, bytes, "cfg_f", 10);
+    const auto cu = BlobVec<uint32_t>(blob, bytes, "cfg_u", 6);
+    t.cfg.dt = cf[0]; t.cfg.gravity[0] = cf[1]; t.cfg.gravity[1] = cf[2]; t.cfg.gravity[2] = cf[3];
+    t.cfg.pos_beta = cf[4]; t.cfg.pos_slop = cf[5]; t.cfg.contact_margin = cf[6];
+    t.cfg.baumgarte_max_velocity = cf[7]; t.cfg.overlap_recovery_velocity = cf[8]; t.cfg.velocity_tolerance = cf[9];
+    t.cfg.vel_iters = cu[0]; t.cfg.pos_iters = cu[1]; t.cfg.max_contacts = cu[2]; t.cfg.max_pairs = cu[3];
+    t.L = cu[4]; t.B = cu[5];
+    const uint32_t L = t.L, B = t.B;
+    if (L > kMaxLinks) throw Error(kNotSupported, "more than 32 links per env");
+    if (B > kMaxBodies) throw Error(kNotSupported, "more than 64 collidable rows per env");
+    if (t.cfg.max_contacts > 1024u) throw Error(kNotSupported, "more than 1024 contact slots per env");
+    t.parent = BlobVec<uint32_t>(blob, bytes, "parent", L);
+    t.jtype = BlobVec<uint32_t>(blob, bytes, "jtype", L);
+    t.link_body = BlobVec<uint32_t>(blob, bytes, "link_body", L);
+    t.geom_kind = BlobVec<uint32_t>(blob, bytes, "geom_kind", L);
+    t.limit_flags = BlobVec<uint32_t>(blob, bytes, "limit_flags", L);
+    t.axis = BlobVec<float>(blob, bytes, "axis", 3 * L);
+    const auto local_pos = BlobVec<float>(blob, bytes, "local_pos", 3 * L);
+    t.local_quat = BlobVec<float>(blob, bytes, "local_quat", 4 * L);
+    const auto parent_offset = BlobVec<float>(blob, bytes, "parent_offset", 3 * L);
+    const auto inertia = BlobVec<float>(blob, bytes, "inertia", 36 * L);
+    t.damping = BlobVec<float>(blob, bytes, "damping", L);
+    t.armature = BlobVec<float>(blob, bytes, "armature", L);
+    t.frictionloss = BlobVec<float>(blob, bytes, "frictionloss", L);
+    t.stiffness = BlobVec<float>(blob, bytes, "stiffness", L);
+    t.spring_ref = BlobVec<float>(blob, bytes, "spring_ref", L);
+    t.limit_lower = BlobVec<float>(blob, bytes, "limit_lower", L);
+    t.limit_upper = BlobVec<float>(blob, bytes, "limit_upper", L);
+    t.geom_pos = BlobVec<float>(blob, bytes, "geom_pos", 3 * L);
+    t.geom_quat = BlobVec<float>(blob, bytes, "geom_quat", 4 * L);
+    t.q0 = BlobVec<float>(blob, bytes, "q0", L);
+    t.base_pose0 = BlobVec<float>(blob, bytes, "base_pose0", 7);
+    t.kp0 = BlobVec<float>(blob, bytes, "kp0", L);
+    t.kd0 = BlobVec<float>(blob, bytes, "kd0", L);
+    t.force_limit0 = BlobVec<float>(blob, bytes, "force_limit0", L);
+    t.shape_kind = BlobVec<uint32_t>(blob, bytes, "shape_kind", B);
+    t.contype = BlobVec<uint32_t>(blob, bytes, "contype", B);
+    t.conaffinity = BlobVec<uint32_t>(blob, bytes, "conaffinity", B);
+    t.group = BlobVec<uint32_t>(blob, bytes, "group", B);
+    t.body_to_link = BlobVec<uint32_t>(blob, bytes, "body_to_link", B);
+    t.body_id = BlobVec<int32_t>(blob, bytes, "body_id", B);
+    t.shape_params = BlobVec<float>(blob, bytes, "shape_params", 4 * B);
+    t.mu = BlobVec<float>(blob, bytes, "mu", B);
+    t.inv_mass = BlobVec<float>(blob, bytes, "inv_mass", B);
+    t.inv_inertia = BlobVec<float>(blob, bytes, "inv_inertia", 3 * B);
+    t.inertial_pos = BlobVec<float>(blob, bytes, "inertial_pos", 3 * B);
+    t.inertial_quat = BlobVec<float>(blob, bytes, "inertial_quat", 4 * B);
+    t.body_pose0 = BlobVec<float>(blob, bytes, "body_pose0", 7 * B);
+    BlobEntry ex;
+    if (BlobFind(blob, bytes, "excluded", &ex) && ex.n) {
+        t.excluded.resize(static_cast<size_t>(ex.n));
+        std::memcpy(t.excluded.data(), ex.data, static_cast<size_t>(ex.n) * 8u);
+        if (!std::is_sorted(t.excluded.begin(), t.excluded.end())) throw Error(kParseError, "excluded pair keys must ascend");
+    }
+    // derived tree tables
+    t.depth.assign(L, 0); t.link_dof.assign(L, 0); t.anc_mask.assign(L, 0); t.offset.assign(3 * L, 0.f);
+    for (uint32_t l = 0; l < L; ++l) {
+        const uint32_t p = t.parent[l];
+        if (p != kNoLink && p >= l) throw Error(kParseError, "links must follow their parents");
+        if (p == kNoLink && l != 0u) throw Error(kNotSupported, "one articulation (a single root link) per env");
+        if (t.jtype[l] == kSpherical) throw Error(kNotSupported, "spherical joints");
+        if (t.jtype[l] > kSpherical) throw Error(kParseError, "unknown joint type");
+        if (t.jtype[l] == kFloating && p != kNoLink) throw Error(kParseError, "a floating joint must be the root");
+        t.depth[l] = p == kNoLink ? 0u : t.depth[p] + 1u;
+        t.max_depth = std::max(t.max_depth, t.depth[l]);
+        t.link_dof[l] = t.ndof;
+        for (uint32_t c = 0; c < JointDofs(t.jtype[l]); ++c) t.dof_link.push_back(l);
+        t.ndof += JointDofs(t.jtype[l]);
+        t.anc_mask[l] = (p == kNoLink ? 0u : t.anc_mask[p]) | (1u << l);
+        for (int k = 0; k < 3; ++k) t.offset[3 * l + k] = local_pos[3 * l + k] + parent_offset[3 * l + k];
+        if (t.link_body[l] >= B && B != 0u) throw Error(kParseError, "link_body out of range");
+    }
+    if (t.ndof > kMaxDof) throw Error(kNotSupported, "more than 32 articulation coordinates per env");
+    t.floating_root = (L > 0 && t.jtype[0] == kFloating) ? 1u : 0u;
+    t.child_begin.assign(L + 1, 0);
+    for (uint32_t l = 0; l < L; ++l) {
+        t.child_begin[l] = static_cast<uint32_t>(t.children.size());
+        for (uint32_t c = 0; c < L; ++c) if (t.parent[c] == l) t.children.push_back(c);
+    }
+    t.child_begin[L] = static_cast<uint32_t>(t.children.size());
+    if (t.children.empty()) t.children.push_back(0);
+    // rigid-body form of the 6x6 link inertias: [[I, h^x], [-h^x, m 1]]
+    t.inertia10.assign(10 * L, 0.f);
+    for (uint32_t l = 0; l < L; ++l) {
+        const float* I = inertia.data() + 36 * l;
+        const float m = I[3 * 6 + 3];
+        const float hx = I[2 * 6 + 4], hy = I[0 * 6 + 5], hz = I[1 * 6 + 3];
+        float* o = t.inertia10.data() + 10 * l;
+        o[0] = m; o[1] = hx; o[2] = hy; o[3] = hz;
+        o[4] = I[0]; o[5] = I[7]; o[6] = I[14]; o[7] = I[1]; o[8] = I[2]; o[9] = I[8];
+        // verify the structure so a non-rigid-body matrix is rejected rather than silently reshaped
+        const float ref[36] = {o[4], o[7], o[8], 0.f, -hz, hy,   o[7], o[5], o[9], hz, 0.f, -hx,   o[8], o[9], o[6], -hy, hx, 0.f,
+                               0.f, hz, -hy, m, 0.f, 0.f,   -hz, 0.f, hx, 0.f, m, 0.f,   hy, -hx, 0.f, 0.f, 0.f, m};
+        float scale = 1e-6f;
+        for (int k = 0; k < 36; ++k) scale = std::max(scale, std::fabs(I[k]));
+        for (int k = 0; k < 36; ++k)
+            if (std::fabs(I[k] - ref[k]) > 1e-5f * scale) throw Error(kNotSupported, "link spatial inertia is not of rigid-body form");
+    }
+    // admissible body-row pairs
+    for (uint32_t b = 0; b < B; ++b) {
+        if (t.body_to_link[b] != kNoLink && t.body_to_link[b] >= L) throw Error(kParseError, "body_to_link out of range");
+        if (t.shape_kind[b] > kPlane) throw Error(kNotSupported, "shape kind without an analytic manifold");
+    }
+    for (uint32_t a = 0; a < B; ++a) for (uint32_t b = a + 1; b < B; ++b) {
+        if (t.body_id[a] < 0 && t.body_id[b] < 0) continue;
+        if (!FilterAdmits(t.contype[a], t.conaffinity[a], t.group[a], t.contype[b], t.conaffinity[b], t.group[b])) continue;
+        const unsigned long long key = (static_cast<unsigned long long>(a) << 32) | b;
+        if (std::binary_search(t.excluded.begin(), t.excluded.end(), key)) continue;
+        const uint32_t ka = t.shape_kind[a], kb = t.shape_kind[b];
+        const bool analytic = !((ka == kCapsule && kb == kBox) || (ka == kBox && kb == kCapsule) || (ka == kPlane && kb == kPlane));
+        if (!analytic) throw Error(kNotSupported, "capsule-box pairs need the convex narrowphase, which this path does not provide");
+        t.adm_pairs.push_back((a << 16) | b);
+    }
+    if (t.adm_pairs.empty()) t.adm_pairs.push_back(0);
+    t.joint_rows = 0;
+    for (uint32_t l = 0; l < L; ++l) {
+        if (JointDofs(t.jtype[l]) != 1u) continue;
+        t.joint_rows += ((t.limit_flags[l] & 1u) ? 1u : 0u) + ((t.limit_flags[l] & 2u) ? 1u : 0u) + (t.frictionloss[l] > 0.f ? 1u : 0u) + 1u;
+    }
+    if (!(t.cfg.dt > 0.f) || !std::isfinite(t.cfg.dt)) throw Error(kInvalidArg, "template dt must be positive");
+    return t;
+}
+
+void World::Check(cudaError_t err, const char* what) {
+    if (err == cudaSuccess) return;
+    const int code = err == cudaErrorMemoryAllocation ? kOutOfMemory : kCudaError;
+    throw Error(code, std::string(what) + ": " + cudaGetErrorString(err));
+}
+
+template <typename T>
+T* World::Alloc(size_t count, bool zero) {
+    void* p = nullptr;
+    const size_t bytes = std::max<size_t>(count, 1) * sizeof(T);
+    Check(cudaMalloc(&p, bytes), "cudaMalloc");
+    allocations_.push_back(p);
+    if (zero) Check(cudaMemsetAsync(p, 0, bytes, stream_), "cudaMemset");
+    return static_cast<T*>(p);
+}
+
+template <typename T>
+const T* World::Upload(const std::vector<T>& v) {
+    T* p = Alloc<T>(v.size(), v.empty());
+    if (!v.empty()) Check(cudaMemcpyAsync(p, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice, stream_), "template upload");
+    return p;
+}
+
+void World::BuildLayout() {
+    const HostTemplate& t = tpl_;
+    SmemLayout& s = params_.sm;
+    const uint32_t L = t.L, B = t.B, n = t.ndof, S = t.cfg.max_contacts;
+    TemplateView& tv = params_.t;
+    tv.point_cap = std::min(4u * S, 32u);
+    tv.head_cap = (tv.point_cap + t.joint_rows + 3u) & ~3u;
+    if (tv.head_cap == 0u) tv.head_cap = 4u;
+    uint32_t at = 0;
+    auto take = [&](uint32_t words) { const uint32_t o = at; at += (words + 1u) & ~1u; return o; };
+    s.ld = n | 1u;
+    s.pose = take(7 * L); s.xrot = take(9 * L); s.xtr = take(3 * L);
+    s.vel = take(6 * L); s.vbias = take(6 * L); s.acc = take(6 * L); s.pbias = take(6 * L); s.ic = take(10 * L);
+    s.mass = take(n * s.ld); s.factor = take(n * s.ld); s.vecs = take(8 * 32);
+    s.bpose = take(7 * B); s.bvel = take(6 * B); s.bwinv = take(6 * B); s.aabb = take(6 * B);
+    s.bmass = take(7 * B); s.bfree = take(6 * B); s.bpseudo = take(6 * B);
+    s.pairs = take(S); s.ccount = take(S); s.cpoint = take(12 * S); s.cnormal = take(12 * S); s.cdepth = take(4 * S);
+    s.cfeat = take(8 * S + 4 * S * 10 + 4 * S);   // feature words, cache staging entries, owner marks
+    s.heads = take(kHeadWords * tv.head_cap);
+    s.jpool = take(tv.point_cap * 3u * n);
+    const uint32_t nb = B + (n ? 1u : 0u);
+    s.binfo = take(3 * nb + 1 + 2 * tv.head_cap);
+    const uint32_t kn = n <= 8 ? 8 : n <= 16 ? 16 : n <= 20 ? 20 : n <= 24 ? 24 : 32;
+    s.chol = take(kn * (kn + 1));
+    s.words = at;
+    const size_t bytes = static_cast<size_t>(s.words) * 4u;
+    if (bytes > 220u * 1024u) throw Error(kNotSupported, "template needs more shared memory per env than one SM provides");
+    warps_per_block_ = static_cast<uint32_t>(std::max<size_t>(1, std::min<size_t>(kWarpsPerBlockMax, (110u * 1024u) / bytes)));
+}
+
+World::World(int device, cudaStream_t stream, const HostTemplate& tpl, uint32_t env_count)
+    : device_(device), stream_(stream), tpl_(tpl), env_count_(env_count) {
+    Check(cudaSetDevice(device_), "cudaSetDevice");
+    try {
+        const HostTemplate& t = tpl_;
+        TemplateView& v = params_.t;
+        v.L = t.L; v.B = t.B; v.ndof = t.ndof; v.max_depth = t.max_depth; v.floating_root = t.floating_root;
+        v.n_excluded = static_cast<uint32_t>(t.excluded.size());
+        v.cfg = t.cfg;
+        BuildLayout();
+        v.parent = Upload(t.parent); v.jtype = Upload(t.jtype); v.depth = Upload(t.depth); v.child_begin = Upload(t.child_begin);
+        v.children = Upload(t.children); v.link_dof = Upload(t.link_dof); v.link_body = Upload(t.link_body);
+        v.geom_kind = Upload(t.geom_kind); v.limit_flags = Upload(t.limit_flags); v.dof_link = Upload(t.dof_link); v.anc_mask = Upload(t.anc_mask);
+        v.axis = Upload(t.axis); v.offset = Upload(t.offset); v.local_quat = Upload(t.local_quat); v.inertia10 = Upload(t.inertia10);
+        v.damping = Upload(t.damping); v.armature = Upload(t.armature); v.frictionloss = Upload(t.frictionloss);
+        v.stiffness = Upload(t.stiffness); v.spring_ref = Upload(t.spring_ref); v.limit_lower = Upload(t.limit_lower);
+        v.limit_upper = Upload(t.limit_upper); v.geom_pos = Upload(t.geom_pos); v.geom_quat = Upload(t.geom_quat);
+        v.shape_kind = Upload(t.shape_kind); v.contype = Upload(t.contype); v.conaffinity = Upload(t.conaffinity); v.group = Upload(t.group);
+        v.body_to_link = Upload(t.body_to_link); v.body_id = Upload(t.body_id); v.shape_params = Upload(t.shape_params); v.mu = Upload(t.mu);
+        v.inv_mass = Upload(t.inv_mass); v.inv_inertia = Upload(t.inv_inertia); v.inertial_pos = Upload(t.inertial_pos);
+        v.inertial_quat = Upload(t.inertial_quat); v.excluded = Upload(t.excluded);
+        v.adm_pairs = Upload(t.adm_pairs);
+        v.n_adm = (t.adm_pairs.size() == 1 && t.adm_pairs[0] == 0u) ? 0u : static_cast<uint32_t>(t.adm_pairs.size());
+        const size_t E = env_count_, L = t.L, B = t.B, n = t.ndof, S = t.cfg.max_contacts;
+        StateView& s = params_.s;
+        s.env_count = env_count_;
+        s.q = Alloc<float>(E * L); s.qdot = Alloc<float>(E * L); s.qddot = Alloc<float>(E * L); s.tau = Alloc<float>(E * L);
+        s.actuator = Alloc<float>(E * L);
+        s.base_pose = Alloc<float>(E * 7); s.link_pose = Alloc<float>(E * L * 7); s.link_vel = Alloc<float>(E * L * 6);
+        s.drive_target = Alloc<float>(E * L); s.vel_target = Alloc<float>(E * L); s.kp = Alloc<float>(E * L); s.kd = Alloc<float>(E * L);
+        s.force_limit = Alloc<float>(E * L); s.feedforward = Alloc<float>(E * L);
+        s.body_pose = Alloc<float>(E * B * 7); s.body_linvel = Alloc<float>(E * B * 3); s.body_angvel = Alloc<float>(E * B * 3);
+        s.carry_artic = Alloc<float>(E * n); s.carry_rigid = Alloc<float>(E * B * 6);
+        s.cache = Alloc<CacheEntry>(E * S * 4);
+        s.status = Alloc<uint32_t>(E); s.solver_residual = Alloc<float>(E * 4); s.solver_sweeps = Alloc<uint32_t>(E);
+        s.pair_count = Alloc<uint32_t>(E); s.pairs = Alloc<uint32_t>(E * S * 2); s.contact_count = Alloc<uint32_t>(E * S);
+        s.contact_point = Alloc<float>(E * S * 12); s.contact_normal = Alloc<float>(E * S * 12); s.contact_depth = Alloc<float>(E * S * 4);
+        s.dbg_mass = nullptr; s.dbg_qdot_pseudo = nullptr;
+        Seed();
+    } catch (...) {
+        for (void* p : allocations_) cudaFree(p);
+        allocations_.clear();
+        throw;
+    }
+}
+
+World::~World() {
+    cudaSetDevice(device_);
+    cudaStreamSynchronize(stream_);
+    if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+    if (graph_) cudaGraphDestroy(graph_);
+    for (void* p : allocations_) cudaFree(p);
+}
+
+// Every env starts from the template (reference src/nk/pipeline/world.cpp:289-654); the same table drives
+// per-env resets.
+void World::Seed() {
+    const HostTemplate& t = tpl_;
+    StateView& s = params_.s;
+    const uint32_t L = t.L, B = t.B, n = t.ndof, S = t.cfg.max_contacts;
+    std::vector<CacheEntry> empty(1);
+    std::memset(empty.data(), 0, sizeof(CacheEntry));
+    empty[0].pair = 0xffffffffu;
+    std::vector<CacheEntry> empties(static_cast<size_t>(std::max(1u, 4u * S)), empty[0]);
+    cache_empty_ = const_cast<CacheEntry*>(Upload(empties));
+    const float* q0 = Upload(t.q0);
+    const float* base0 = Upload(t.base_pose0);
+    const float* body0 = Upload(t.body_pose0);
+    const float* kp0 = Upload(t.kp0);
+    const float* kd0 = Upload(t.kd0);
+    const float* fl0 = Upload(t.force_limit0);
+    reset_.env_count = env_count_;
+    reset_.env_ids = nullptr;
+    uint32_t f = 0;
+    auto add = [&](void* dst, const void* src, uint32_t words) { if (words) reset_.fields[f++] = {dst, src, words, 0u, 0u}; };
+    add(s.q, q0, L); add(s.qdot, nullptr, L); add(s.qddot, nullptr, L); add(s.tau, nullptr, L); add(s.actuator, nullptr, L);
+    add(s.base_pose, base0, L ? 7u : 0u); add(s.link_vel, nullptr, 6 * L);
+    add(s.body_pose, body0, 7 * B); add(s.body_linvel, nullptr, 3 * B); add(s.body_angvel, nullptr, 3 * B);
+    add(s.carry_artic, nullptr, n); add(s.carry_rigid, nullptr, 6 * B);
+    add(s.cache, cache_empty_, 4 * S * static_cast<uint32_t>(sizeof(CacheEntry) / 4));
+    add(s.status, nullptr, 1); add(s.solver_residual, nullptr, 4); add(s.solver_sweeps, nullptr, 1);
+    reset_.field_count = f;
+    // drive inputs are seeded once; resets keep them (reference nuka.h:378-379)
+    ResetParams seed = reset_;
+    auto add_seed = [&](void* dst, const void* src, uint32_t words) { if (words) seed.fields[seed.field_count++] = {dst, src, words, 0u, 0u}; };
+    add_seed(s.drive_target, q0, L); add_seed(s.kp, kp0, L); add_seed(s.kd, kd0, L); add_seed(s.force_limit, fl0, L);
+    add_seed(s.vel_target, nullptr, L); add_seed(s.feedforward, nullptr, L);
+    Check(launch_reset(seed, env_count_, stream_), "seed launch");
+    ++launches_;
+    Refresh();
+}
+
+void World::Refresh() {
+    StepParams p = params_;
+    p.mode = kModeRefresh; p.steps = 1;
+    Check(cudaSetDevice(device_), "cudaSetDevice");
+    Check(launch_step(p, warps_per_block_, stream_), "refresh launch");
+    ++launches_;
+}
+
+void World::RunStage(uint32_t mode) {
+    StateView& s = params_.s;
+    const size_t E = env_count_, n = tpl_.ndof;
+    if (mode == kModeDynamicsOnly && s.dbg_mass == nullptr) s.dbg_mass = Alloc<float>(E * n * n);
+    StepParams p = params_;
+    p.mode = mode; p.steps = 1;
+    Check(cudaSetDevice(device_), "cudaSetDevice");
+    Check(launch_step(p, warps_per_block_, stream_), "stage launch");
+    ++launches_;
+}
+
+void World::SetGraphMode(bool on) {
+    graph_mode_ = on;
+    graph_valid_ = false;
+}
+
+void World::Step(uint32_t n) {
+    if (n == 0u) return;
+    Check(cudaSetDevice(device_), "cudaSetDevice");
+    StepParams p = params_;
+    p.mode = kModeStep;
+    if (!graph_mode_) {
+        p.steps = n;      // the kernel advances n steps per launch; inputs are constant across them
+        Check(launch_step(p, warps_per_block_, stream_), "step launch");
+        ++launches_;
+        return;
+    }
+    if (!graph_valid_) {
+        if (graph_exec_) { cudaGraphExecDestroy(graph_exec_); graph_exec_ = nullptr; }
+        if (graph_) { cudaGraphDestroy(graph_); graph_ = nullptr; }
+        p.steps = 1;
+        // configure the kernel's shared-memory attribute outside the capture
+        StepParams warm = params_;
+        warm.mode = kModeRefresh; warm.steps = 1;
+        Check(launch_step(warm, warps_per_block_, stream_), "graph warm-up launch");
+        ++launches_;
+        Check(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal), "begin capture");
+        const cudaError_t launched = launch_step(p, warps_per_block_, stream_);
+        const cudaError_t ended = cudaStreamEndCapture(stream_, &graph_);
+        Check(launched, "captured step launch");
+        Check(ended, "end capture");
+        Check(cudaGraphInstantiate(&graph_exec_, graph_, 0), "graph instantiate");
+        graph_valid_ = true;
+    }
+    for (uint32_t k = 0; k < n; ++k) { Check(cudaGraphLaunch(graph_exec_, stream_), "graph launch"); ++launches_; }
+}
+
+void World::Reset(const uint32_t* env_ids, uint32_t count) {
+    Check(cudaSetDevice(device_), "cudaSetDevice");
+    ResetParams r = reset_;
+    if (env_ids == nullptr) {
+        Check(launch_reset(r, env_count_, stream_), "reset launch");
+    } else {
+        if (count == 0u) return;
+        for (uint32_t k = 0; k < count; ++k) if (env_ids[k] >= env_count_) throw Error(kInvalidArg, "reset_envs: env id out of range");
+        std::vector<uint32_t> ids(env_ids, env_ids + count);
+        std::sort(ids.begin(), ids.end());
+        ids.erase(std::unique(ids.begin(), ids.end()), ids.end());
+        if (ids.size() > reset_ids_cap_) {
+            reset_ids_ = Alloc<uint32_t>(env_count_, false);
+            reset_ids_cap_ = env_count_;
+        }
+        // the id list must outlive the async copy: synchronise the (rare) partial reset path
+        Check(cudaMemcpyAsync(reset_ids_, ids.data(), ids.size() * 4u, cudaMemcpyHostToDevice, stream_), "reset ids upload");
+        Check(cudaStreamSynchronize(stream_), "reset ids sync");
+        r.env_ids = reset_ids_;
+        Check(launch_reset(r, static_cast<uint32_t>(ids.size()), stream_), "reset launch");
+    }
+    ++launches_;
+    Refresh();
+}
+
+void World::Synchronize() {
+    Check(cudaSetDevice(device_), "cudaSetDevice");
+    Check(cudaStreamSynchronize(stream_), "stream synchronize");
+}
+
+bool World::Field(uint32_t id, FieldInfo* out) {
+    StateView& s = params_.s;
+    const size_t L = tpl_.L, B = tpl_.B, n = tpl_.ndof, S = tpl_.cfg.max_contacts;
+    auto set = [&](void* p, size_t per_env, uint32_t dtype, bool w) { *out = {p, per_env, dtype, w}; return true; };
+    switch (id) {
+        case 0: return set(s.body_pose, B * 7, 0, true);
+        case 1: return set(s.link_pose, L * 7, 0, false);
+        case 2: return set(s.q, L, 0, true);
+        case 3: return set(s.qdot, L, 0, true);
+        case 6: return set(s.drive_target, L, 0, true);
+        case 7: return set(s.link_vel, L * 6, 0, true);
+        case 8: return set(s.kp, L, 0, true);
+        case 9: return set(s.kd, L, 0, true);
+        case 10: return set(s.force_limit, L, 0, true);
+        case 11: return set(s.base_pose, L ? 7 : 0, 0, true);
+        case 13: return set(s.vel_target, L, 0, true);
+        case 22: return set(s.feedforward, L, 0, true);
+        case 25: return set(s.body_linvel, B * 3, 0, true);
+        case 26: return set(s.body_angvel, B * 3, 0, true);
+        case 29: return set(s.actuator, L, 0, false);
+        case 39: return set(s.status, 1, 1, true);
+        case 109: return set(s.solver_residual, 4, 0, false);
+        case 0x10000: return set(s.qddot, L, 0, false);
+        case 0x10001:
+            if (s.dbg_mass == nullptr) s.dbg_mass = Alloc<float>(static_cast<size_t>(env_count_) * n * n);
+            return set(s.dbg_mass, n * n, 0, false);
+        case 0x10002: return set(s.pair_count, 1, 1, false);
+        case 0x10003: return set(s.pairs, S * 2, 1, false);
+        case 0x10004: return set(s.contact_count, S, 1, false);
+        case 0x10005: return set(s.contact_point, S * 12, 0, false);
+        case 0x10006: return set(s.contact_normal, S * 12, 0, false);
+        case 0x10007: return set(s.contact_depth, S * 4, 0, false);
+        case 0x10008: return set(s.solver_sweeps, 1, 1, false);
+        case 0x10009:
+            if (s.dbg_qdot_pseudo == nullptr) s.dbg_qdot_pseudo = Alloc<float>(static_cast<size_t>(env_count_) * n);
+            return set(s.dbg_qdot_pseudo, n, 0, false);
+        default: return false;
+    }
+}
+
+}  // namespace nkb

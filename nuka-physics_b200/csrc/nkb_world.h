@@ -1,0 +1,93 @@
+// Host runtime of the batched articulated step: cooked-template parsing, device storage, the field table,
+// step/reset/refresh launches.  Mirrors the role of the reference's nk::World (src/nk/pipeline/world.cpp)
+// for this path; there is no op list to dispatch because the step is one fused kernel.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+#include "nkb_launch.h"
+#include "nkb_types.h"
+
+namespace nkb {
+
+struct Error : std::runtime_error {
+    int code;   // nuka_result_t value
+    Error(int c, const std::string& what) : std::runtime_error(what), code(c) {}
+};
+
+// One env's cooked template on the host.
+struct HostTemplate {
+    uint32_t L = 0, B = 0, ndof = 0, max_depth = 0, floating_root = 0;
+    Config cfg{};
+    std::vector<uint32_t> parent, jtype, depth, child_begin, children, link_dof, link_body, geom_kind, limit_flags, dof_link, anc_mask;
+    std::vector<float> axis, offset, local_quat, inertia10, damping, armature, frictionloss, stiffness, spring_ref;
+    std::vector<float> limit_lower, limit_upper, geom_pos, geom_quat, q0, base_pose0, kp0, kd0, force_limit0;
+    std::vector<uint32_t> shape_kind, contype, conaffinity, group, body_to_link;
+    std::vector<int32_t> body_id;
+    std::vector<float> shape_params, mu, inv_mass, inv_inertia, inertial_pos, inertial_quat, body_pose0;
+    std::vector<unsigned long long> excluded;
+    std::vector<uint32_t> adm_pairs;
+    uint32_t joint_rows = 0;     // limit + friction + drive rows one env can emit
+    static HostTemplate Parse(const void* blob, size_t bytes);
+};
+
+struct FieldInfo {
+    void* ptr = nullptr;
+    size_t per_env = 0;          // elements per env
+    uint32_t dtype = 0;          // 0 f32, 1 u32
+    bool writable = false;
+};
+
+class World {
+public:
+    World(int device, cudaStream_t stream, const HostTemplate& tpl, uint32_t env_count);
+    ~World();
+    World(const World&) = delete;
+    World& operator=(const World&) = delete;
+
+    void Step(uint32_t n);
+    void RunStage(uint32_t mode);
+    void Refresh();
+    void Reset(const uint32_t* env_ids, uint32_t count);   // null ids: all envs
+    void Synchronize();
+    bool Field(uint32_t id, FieldInfo* out);
+    void SetVelocityIterations(uint32_t n) { params_.t.cfg.vel_iters = n; graph_valid_ = false; }
+    uint32_t VelocityIterations() const { return params_.t.cfg.vel_iters; }
+    void SetGravityZ(float g) { params_.t.cfg.gravity[2] = g; graph_valid_ = false; }
+    void SetGraphMode(bool on);
+    cudaStream_t stream() const { return stream_; }
+    int device() const { return device_; }
+    uint32_t env_count() const { return env_count_; }
+    const HostTemplate& tpl() const { return tpl_; }
+    uint32_t shared_bytes_per_env() const { return params_.sm.words * 4u; }
+    uint32_t warps_per_block() const { return warps_per_block_; }
+    uint64_t launches() const { return launches_; }
+
+private:
+    template <typename T> T* Alloc(size_t count, bool zero = true);
+    template <typename T> const T* Upload(const std::vector<T>& v);
+    void Check(cudaError_t err, const char* what);
+    void BuildLayout();
+    void Seed();
+
+    int device_;
+    cudaStream_t stream_;
+    HostTemplate tpl_;
+    uint32_t env_count_;
+    StepParams params_{};
+    uint32_t warps_per_block_ = 1;
+    std::vector<void*> allocations_;
+    ResetParams reset_{};
+    uint32_t* reset_ids_ = nullptr;
+    uint32_t reset_ids_cap_ = 0;
+    CacheEntry* cache_empty_ = nullptr;
+    bool graph_mode_ = false, graph_valid_ = false;
+    cudaGraph_t graph_ = nullptr;
+    cudaGraphExec_t graph_exec_ = nullptr;
+    uint64_t launches_ = 0;
+};
+
+}  // namespace nkb

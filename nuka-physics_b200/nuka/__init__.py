@@ -1,0 +1,196 @@
+"""B200-native batched articulated-robot step behind the reference's world/step interface.
+
+The surface mirrors the reference's Python module for this path (python/nuka/__init__.py:27-101,
+python/src/nuka_ext.cpp:2546-2600): ``Device.create``, ``World.create_from_scene`` / ``step`` / ``step_n`` /
+``synchronize`` / ``reset`` / ``reset_envs`` / ``view`` / ``set_velocity_iterations``; ``FieldView`` exposes
+world-owned device memory without a copy (``__cuda_array_interface__`` and ``__dlpack__``).
+Every call goes through the C ABI of ``libnuka_b200.so``; nothing here computes physics.
+"""
+import ctypes
+import enum
+
+import numpy as np
+
+from . import _abi, nkt, templates  # noqa: F401
+
+
+class NukaError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"{_abi.lib().nuka_result_message(code).decode()} ({code}): {message}")
+        self.code = code
+
+
+def _check(code):
+    if code != _abi.OK:
+        raise NukaError(code, _abi.lib().nuka_last_error_message().decode())
+
+
+class Field(enum.IntEnum):
+    """State field ids (reference nuka.h:496-964) plus this library's parity taps."""
+    RIGID_BODY_TRANSFORM = 0
+    ARTICULATION_LINK_POSE = 1
+    JOINT_POSITION = 2
+    JOINT_VELOCITY = 3
+    DRIVE_TARGET = 6
+    LINK_VELOCITY = 7
+    DRIVE_STIFFNESS = 8
+    DRIVE_DAMPING = 9
+    DRIVE_FORCE_LIMIT = 10
+    BASE_POSE = 11
+    VELOCITY_TARGET = 13
+    JOINT_FEEDFORWARD = 22
+    BODY_LINEAR_VELOCITY = 25
+    BODY_ANGULAR_VELOCITY = 26
+    ACTUATOR_EFFORT = 29
+    ENV_STATUS = 39
+    SOLVER_RESIDUAL = 109
+    JOINT_ACCELERATION = 0x10000
+    MASS_MATRIX = 0x10001
+    PAIR_COUNT = 0x10002
+    CANDIDATE_PAIRS = 0x10003
+    CONTACT_COUNT = 0x10004
+    CONTACT_POINT = 0x10005
+    CONTACT_NORMAL = 0x10006
+    CONTACT_DEPTH = 0x10007
+    SOLVER_SWEEPS = 0x10008
+    JOINT_PSEUDO_VELOCITY = 0x10009
+
+
+class Device:
+    def __init__(self, handle, gpu_index):
+        self._h = handle
+        self.gpu_index = gpu_index
+
+    @classmethod
+    def create(cls, gpu_index=0, cuda_stream=None):
+        desc = _abi.DeviceDesc(gpu_index, cuda_stream, 0)
+        out = ctypes.c_void_p()
+        _check(_abi.lib().nuka_device_create(ctypes.byref(desc), ctypes.byref(out)))
+        return cls(out, gpu_index)
+
+    def destroy(self):
+        if self._h:
+            _abi.lib().nuka_device_destroy(self._h)
+            self._h = None
+
+
+class FieldView:
+    """Borrowed view of a world-owned device buffer; valid until the world is destroyed."""
+
+    def __init__(self, world, field, view):
+        self._world = world
+        self.field = Field(field)
+        self.device_ptr = view.device_ptr
+        self.element_count = view.element_count
+        self.dtype = np.dtype(np.float32 if view.dtype == 0 else np.uint32)
+        self.shape = (world.env_count, view.element_count // world.env_count)
+
+    @property
+    def __cuda_array_interface__(self):
+        return {"shape": self.shape, "typestr": self.dtype.str, "data": (self.device_ptr, False), "version": 3, "strides": None}
+
+    def torch(self):
+        import torch
+        return torch.as_tensor(self, device=f"cuda:{self._world.device.gpu_index}")
+
+    def __dlpack__(self, stream=None):
+        return self.torch().__dlpack__(stream=stream)
+
+    def __dlpack_device__(self):
+        return (2, self._world.device.gpu_index)   # kDLCUDA
+
+
+class World:
+    def __init__(self, device, handle, env_count):
+        self.device = device
+        self._h = handle
+        self.env_count = env_count
+        info = _abi.WorldInfo()
+        _check(_abi.lib().nuka_b200_world_info(self._h, ctypes.byref(info)))
+        self.info = info
+
+    @staticmethod
+    def _desc(scene_path, env_count, dt, determinism, control_mode, **solver):
+        d = _abi.WorldDesc()
+        d.scene_path = scene_path.encode() if scene_path else None
+        d.env_count, d.fixed_dt, d.determinism, d.control_mode = env_count, dt, determinism, control_mode
+        for k, v in solver.items():
+            setattr(d, k, v)
+        return d
+
+    @classmethod
+    def create_from_scene(cls, device, scene_path, env_count, dt=0.0, determinism=0, control_mode=0, **solver):
+        d = cls._desc(scene_path, env_count, dt, determinism, control_mode, **solver)
+        out = ctypes.c_void_p()
+        _check(_abi.lib().nuka_world_create_from_scene(device._h, ctypes.byref(d), ctypes.byref(out)))
+        return cls(device, out, env_count)
+
+    @classmethod
+    def create_from_template(cls, device, blob, env_count, dt=0.0, determinism=0, control_mode=0, **solver):
+        d = cls._desc(None, env_count, dt, determinism, control_mode, **solver)
+        out = ctypes.c_void_p()
+        blob = bytes(blob)
+        _check(_abi.lib().nuka_world_create_from_template(device._h, ctypes.byref(d), blob, len(blob), ctypes.byref(out)))
+        return cls(device, out, env_count)
+
+    def destroy(self):
+        if self._h:
+            _abi.lib().nuka_world_destroy(self._h)
+            self._h = None
+
+    def step(self):
+        _check(_abi.lib().nuka_world_step(self._h))
+
+    def step_n(self, n):
+        _check(_abi.lib().nuka_world_step_n(self._h, n))
+
+    def synchronize(self):
+        _check(_abi.lib().nuka_world_synchronize(self._h))
+
+    def reset(self):
+        _check(_abi.lib().nuka_world_reset(self._h))
+
+    def reset_envs(self, env_ids):
+        ids = np.ascontiguousarray(env_ids, dtype=np.uint32)
+        _check(_abi.lib().nuka_world_reset_envs(self._h, ids.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), ids.size))
+
+    def forward_kinematics(self):
+        _check(_abi.lib().nuka_world_forward_kinematics(self._h))
+
+    def set_velocity_iterations(self, n):
+        _check(_abi.lib().nuka_world_set_velocity_iterations(self._h, n))
+
+    def get_velocity_iterations(self):
+        out = ctypes.c_uint32()
+        _check(_abi.lib().nuka_world_get_velocity_iterations(self._h, ctypes.byref(out)))
+        return out.value
+
+    def set_execution_mode(self, graph):
+        _check(_abi.lib().nuka_world_set_execution_mode(self._h, 1 if graph else 0))
+
+    def run_stage(self, stage):
+        _check(_abi.lib().nuka_b200_world_run_stage(self._h, stage))
+
+    def launch_count(self):
+        out = ctypes.c_uint64()
+        _check(_abi.lib().nuka_b200_world_launch_count(self._h, ctypes.byref(out)))
+        return out.value
+
+    def view(self, field):
+        v = _abi.BufferView()
+        _check(_abi.lib().nuka_world_get_buffer_view(self._h, int(field), ctypes.byref(v)))
+        return FieldView(self, field, v)
+
+    def upload(self, field, array, byte_offset=0):
+        a = np.ascontiguousarray(array)
+        _check(_abi.lib().nuka_world_upload_field(self._h, int(field), a.ctypes.data, a.nbytes, byte_offset))
+
+    def download(self, field):
+        v = self.view(field)
+        out = np.zeros(v.shape, dtype=v.dtype)
+        _check(_abi.lib().nuka_world_download_field(self._h, int(field), out.ctypes.data, out.nbytes, 0))
+        return out
+
+
+def sync(world):
+    world.synchronize()
