@@ -500,3 +500,23 @@ void orc_narrowphase(const orc_model *m, orc_env *e) {
         e->contact_points += mf.count;
     }
 }
+
+/* Known-answer access for tests: one analytic pair. pose = xyz + wxyz, params = shape_params (4).
+ * out: count, then per point position(3) normal(3) penetration(1) (raw manifold, no separation shell). */
+int orc_manifold(uint32_t kind_a, const float *pose_a, const float *params_a, uint32_t kind_b, const float *pose_b,
+                 const float *params_b, float query, float *out) {
+    prim p[2];
+    const float *poses[2] = {pose_a, pose_b}, *pars[2] = {params_a, params_b};
+    for (int k = 0; k < 2; ++k) {
+        quat q = qld(poses[k] + 3);
+        p[k].f.cx = qrot_raw(q, V3(1, 0, 0)); p[k].f.cy = qrot_raw(q, V3(0, 1, 0)); p[k].f.cz = qrot_raw(q, V3(0, 0, 1));
+        p[k].f.t = v3ld(poses[k]);
+        p[k].radius = pars[k][0]; p[k].hh = pars[k][1]; p[k].he = V3(pars[k][0], pars[k][1], pars[k][2]);
+    }
+    manifold mf;
+    primitive_pair(kind_a, &p[0], kind_b, &p[1], query, &mf);
+    for (uint32_t i = 0; i < mf.count; ++i) {
+        v3st(out + 7 * i, mf.p[i].pos); v3st(out + 7 * i + 3, mf.p[i].n); out[7 * i + 6] = mf.p[i].pen;
+    }
+    return (int)mf.count;
+}

@@ -1,0 +1,145 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle on the same seeded inputs and
+against the committed golden fixtures.
+
+Tolerances (fp32): mass matrices, accelerations and single-step post-solve velocities within 1e-5 of the
+field's largest magnitude; 100-step contact-free trajectories within 1e-4; candidate pair lists bit-exact.
+"""
+import os
+
+import numpy as np
+import pytest
+
+import nuka
+from nuka import Field as F, templates as T
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def rel(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-12))
+
+
+def quad_inputs(E, seed=0):
+    st = T.quadruped_state(E, seed)
+    rng = np.random.Generator(np.random.PCG64(7 + seed))
+    qdot = np.zeros((E, 13), np.float32)
+    qdot[:, 1:] = rng.normal(0, 0.5, size=(E, 12))
+    lv = np.zeros((E, 13, 6), np.float32)
+    lv[:, 0, :] = rng.normal(0, 0.3, size=(E, 6))
+    return st["q"], qdot, st["base_pose"], lv.reshape(E, -1)
+
+
+def make_pair(device, oracle, tb, E, state):
+    blob = tb.blob()
+    w = nuka.World.create_from_template(device, blob, E)
+    o = oracle.World(blob, E)
+    names = {"q": F.JOINT_POSITION, "qdot": F.JOINT_VELOCITY, "base_pose": F.BASE_POSE, "link_velocity": F.LINK_VELOCITY,
+             "body_pose": F.RIGID_BODY_TRANSFORM, "body_linear_velocity": F.BODY_LINEAR_VELOCITY}
+    for k, v in state.items():
+        w.upload(names[k], v)
+        o.set(k, v.reshape(E, -1))
+    w.forward_kinematics()
+    o.refresh()
+    return w, o
+
+
+def test_arm7_dynamics_and_trajectory(device, oracle):
+    E = 64
+    st = T.arm7_state(E, 0)
+    w, o = make_pair(device, oracle, T.arm7(0), E, st)
+    assert rel(w.download(F.ARTICULATION_LINK_POSE), o.get("link_pose", 56)) < 1e-6
+    w.run_stage(1); o.dynamics(False)
+    assert rel(w.download(F.MASS_MATRIX), o.get("mass_matrix", 49)) < 1e-5
+    assert rel(w.download(F.JOINT_ACCELERATION), o.get("qddot", 8)) < 2e-5
+    w.step_n(100); o.step(100)
+    assert rel(w.download(F.JOINT_POSITION), o.get("q", 8)) < 1e-4
+    assert rel(w.download(F.JOINT_VELOCITY), o.get("qdot", 8)) < 1e-4
+    assert w.download(F.ENV_STATUS).max() == 0
+    w.destroy()
+
+
+def test_arm7_golden(device):
+    g = np.load(os.path.join(GOLDEN, "arm7_seed0.npz"))
+    w = nuka.World.create_from_template(device, T.arm7(0).blob(), 4)
+    w.upload(F.JOINT_POSITION, g["q_in"]); w.upload(F.JOINT_VELOCITY, g["qdot_in"]); w.forward_kinematics()
+    w.run_stage(1)
+    assert rel(w.download(F.MASS_MATRIX), g["mass"]) < 1e-5 and rel(w.download(F.JOINT_ACCELERATION), g["qdd"]) < 2e-5
+    w.step_n(100)
+    assert rel(w.download(F.JOINT_POSITION), g["q_100"]) < 1e-4
+    w.destroy()
+
+
+def test_quadruped_stages(device, oracle):
+    E = 256
+    q, qdot, base, lv = quad_inputs(E)
+    state = {"q": q, "qdot": qdot, "base_pose": base, "link_velocity": lv}
+    w, o = make_pair(device, oracle, T.quadruped(0), E, state)
+    assert rel(w.download(F.RIGID_BODY_TRANSFORM), o.get("body_pose", 98)) < 1e-6
+    w.run_stage(1); o.dynamics(False)
+    assert rel(w.download(F.MASS_MATRIX), o.get("mass_matrix", 324)) < 1e-5
+    assert rel(w.download(F.JOINT_ACCELERATION), o.get("qddot", 13)) < 2e-5
+    w.run_stage(2); o.collide()
+    assert np.array_equal(w.download(F.PAIR_COUNT), o.get("pair_count", 1))
+    assert np.array_equal(w.download(F.CANDIDATE_PAIRS), o.get("candidate_pairs", 16))      # bit-exact, canonical order
+    assert np.array_equal(w.download(F.CONTACT_COUNT), o.get("contact_count", 8))
+    assert rel(w.download(F.CONTACT_POINT), o.get("contact_point", 96)) < 1e-5
+    assert rel(w.download(F.CONTACT_DEPTH), o.get("contact_depth", 32)) < 1e-4
+    w.destroy()
+
+
+def test_quadruped_single_step_post_solve(device, oracle):
+    E = 256
+    q, qdot, base, lv = quad_inputs(E)
+    state = {"q": q, "qdot": qdot, "base_pose": base, "link_velocity": lv}
+    w, o = make_pair(device, oracle, T.quadruped(0), E, state)
+    w.step(); o.step(1)
+    assert o.get("contact_points", 1).sum() > E          # the case really has contacts
+    assert rel(w.download(F.JOINT_VELOCITY), o.get("qdot", 13)) < 1e-5
+    assert rel(w.download(F.LINK_VELOCITY), o.get("link_velocity", 78)) < 1e-5
+    assert rel(w.download(F.BASE_POSE), o.get("base_pose", 7)) < 1e-6
+    assert rel(w.download(F.JOINT_POSITION), o.get("q", 13)) < 1e-6
+    assert np.array_equal(w.download(F.SOLVER_SWEEPS)[:, 0], o.get("solver_sweeps", 1)[:, 0])
+    assert w.download(F.ENV_STATUS).max() == 0
+    w.destroy()
+
+
+def test_quadruped_golden(device):
+    g = np.load(os.path.join(GOLDEN, "quadruped_seed0.npz"))
+    w = nuka.World.create_from_template(device, T.quadruped(0).blob(), 4)
+    for f, k in ((F.JOINT_POSITION, "q_in"), (F.JOINT_VELOCITY, "qdot_in"), (F.BASE_POSE, "base_in"), (F.LINK_VELOCITY, "link_vel_in")):
+        w.upload(f, g[k])
+    w.forward_kinematics()
+    w.run_stage(2)
+    assert np.array_equal(w.download(F.CANDIDATE_PAIRS), g["pairs"]) and np.array_equal(w.download(F.CONTACT_COUNT), g["contact_count"])
+    w.step()
+    assert rel(w.download(F.JOINT_VELOCITY), g["qdot_1"]) < 1e-5 and rel(w.download(F.LINK_VELOCITY), g["link_vel_1"]) < 1e-5
+    w.destroy()
+
+
+def test_quadruped_no_contact_trajectory(device, oracle):
+    """100 steps without contacts (no ground plane): 1e-4."""
+    E = 64
+    tb = T.quadruped(0)
+    tb.bodies = [b for b in tb.bodies if b["kind"] != T.PLANE]
+    q, qdot, base, lv = quad_inputs(E, 1)
+    w, o = make_pair(device, oracle, tb, E, {"q": q, "qdot": qdot * 0.2, "base_pose": base, "link_velocity": lv})
+    w.step_n(100); o.step(100)
+    assert rel(w.download(F.JOINT_POSITION), o.get("q", 13)) < 1e-4
+    assert rel(w.download(F.BASE_POSE), o.get("base_pose", 7)) < 1e-4
+    w.destroy()
+
+
+def test_quadruped_stands_for_a_second(device):
+    """Size-independent property at the benchmark size: all 4096 robots keep standing on their feet."""
+    E = 4096
+    w = nuka.World.create_from_template(device, T.quadruped(0).blob(), E)
+    st = T.quadruped_state(E, 0)
+    w.upload(F.JOINT_POSITION, st["q"]); w.upload(F.BASE_POSE, st["base_pose"]); w.forward_kinematics()
+    w.step_n(200)
+    base = w.download(F.BASE_POSE)
+    assert np.isfinite(base).all() and base[:, 2].min() > 0.2 and base[:, 2].max() < 0.4
+    assert np.allclose(np.linalg.norm(base[:, 3:], axis=1), 1.0, atol=1e-4)
+    assert w.download(F.ENV_STATUS).max() == 0
+    w.destroy()
