@@ -155,7 +155,7 @@ NKB_DEV void add_pt(Manifold& o, V3 pos, V3 n, float pen, uint32_t key) {
     if (o.count < 4u) { o.pos[o.count] = pos; o.n[o.count] = n; o.pen[o.count] = pen; o.key[o.count] = key; ++o.count; }
 }
 
-__device__ __noinline__ void reduce_emit(Cand* c, int n, V3 normal, Manifold& o) {
+static __device__ __noinline__ void reduce_emit(Cand* c, int n, V3 normal, Manifold& o) {
     if (n <= 0) return;
     const int keep = n < 4 ? n : 4;
     for (int s = 0; s < keep; ++s) {
@@ -173,7 +173,7 @@ __device__ __noinline__ void reduce_emit(Cand* c, int n, V3 normal, Manifold& o)
     for (int i = 0; i < keep; ++i) add_pt(o, c[i].pos, normal, c[i].pen, c[i].feat);
 }
 
-__device__ __noinline__ void reduce_emit_spread(Cand* c, int n, V3 normal, Manifold& o) {
+static __device__ __noinline__ void reduce_emit_spread(Cand* c, int n, V3 normal, Manifold& o) {
     o.count = 0;
     if (n <= 0) return;
     if (n <= 4) {
@@ -320,7 +320,7 @@ NKB_DEV void capsule_capsule(const Prim& a, const Prim& b, Manifold& o, float qu
 
 struct ClipPoly { V3 v[8]; int count; };
 NKB_DEV void poly_add(ClipPoly& p, V3 v) { if (p.count < 8) { p.v[p.count] = v; ++p.count; } }
-__device__ __noinline__ void clip_plane(const ClipPoly& in, V3 pp, V3 pn, ClipPoly& out) {
+static __device__ __noinline__ void clip_plane(const ClipPoly& in, V3 pp, V3 pn, ClipPoly& out) {
     out.count = 0;
     for (int i = 0; i < in.count; ++i) {
         const int j = (i + 1) % in.count;
@@ -336,7 +336,7 @@ __device__ __noinline__ void clip_plane(const ClipPoly& in, V3 pp, V3 pn, ClipPo
 }
 NKB_DEV float fabs_dot(V3 a, V3 b) { const float d = dot(a, b); return d < 0.f ? -d : d; }
 
-__device__ __noinline__ void box_box(const Prim& A, const Prim& B, Manifold& o, float query) {
+static __device__ __noinline__ void box_box(const Prim& A, const Prim& B, Manifold& o, float query) {
     const V3 ha = A.he, hb = B.he, dpos = B.f.t - A.f.t;
     const V3 ax[3] = {A.f.cx, A.f.cy, A.f.cz}, bx[3] = {B.f.cx, B.f.cy, B.f.cz};
     float AbsR[3][3];

@@ -27,7 +27,17 @@ struct Env {
     uint32_t dof_link, dof_comp;   // comp == kNoLink for scalar joints
     float vel0;              // step-start coordinate velocity
     uint32_t status;
+    uint32_t* cyc;           // stage cycle counters of this env, or null
+    long long t0;
 };
+
+// Adds the cycles since the last tick to stage counter k (profiling tap, off unless requested).
+NKB_DEV void tick(Env& e, int k) {
+    if (e.cyc == nullptr) return;
+    const long long now = clock64();
+    if (e.lane == 0u) e.cyc[k] += (uint32_t)(now - e.t0);
+    e.t0 = now;
+}
 
 NKB_DEV float* sm_pose(const Env& e, uint32_t l) { return e.sm + e.lay->pose + 7u * l; }
 NKB_DEV float* sm_xrot(const Env& e, uint32_t l) { return e.sm + e.lay->xrot + 9u * l; }
@@ -70,6 +80,8 @@ NKB_DEV void env_begin(Env& e, const StepParams& p, float* sm, uint32_t env, uin
     if (dof && __ldg(t.jtype + e.dof_link) == kFloating) e.dof_comp = lane - __ldg(t.link_dof + e.dof_link);
     e.vel0 = 0.f;
     e.status = 0u;
+    e.cyc = p.s.dbg_cycles != nullptr ? p.s.dbg_cycles + (size_t)env * 24u : nullptr;
+    e.t0 = clock64();
 }
 
 // World poses of every link, ops/articulation.cu:1561-1596 with kinematics.cuh:25-42 joint frames.

@@ -123,7 +123,7 @@ NKB_DEV void stage_store_bodies(Env& e, bool velocities) {
 }
 
 template <int KN>
-__global__ void __launch_bounds__(kWarpsPerBlockMax * 32) step_kernel(const StepParams p) {
+__global__ void __maxnreg__(168) step_kernel(const __grid_constant__ StepParams p) {
     extern __shared__ float smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t env = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -145,7 +145,8 @@ __global__ void __launch_bounds__(kWarpsPerBlockMax * 32) step_kernel(const Step
             }
             return;
         }
-        if (has_artic) { stage_fk(e); stage_drives(e); stage_dynamics(e, p.mode != kModeDynamicsOnly); }
+        tick(e, 0);
+        if (has_artic) { stage_fk(e); tick(e, 1); stage_drives(e); stage_dynamics(e, p.mode != kModeDynamicsOnly); tick(e, 2); }
         if (p.mode == kModeDynamicsOnly) {
             if (lane < t.L) p.s.qddot[(size_t)env * t.L + lane] = e.qdd;
             return;
@@ -155,8 +156,11 @@ __global__ void __launch_bounds__(kWarpsPerBlockMax * 32) step_kernel(const Step
         if (has_collidables) {
             stage_aabbs(e);
             pair_count = stage_pairs(e);
+            tick(e, 3);
             stage_narrowphase(e, pair_count);
+            tick(e, 4);
             stage_store_contacts(e, pair_count);
+            tick(e, 5);
         }
         if (p.mode == kModeCollideOnly) {
             if (has_bodies) stage_store_bodies(e, false);
@@ -167,10 +171,13 @@ __global__ void __launch_bounds__(kWarpsPerBlockMax * 32) step_kernel(const Step
             return;
         }
         nheads = stage_rows(e, pair_count);
+        tick(e, 6);
         stage_warm_start(e, nheads);
+        tick(e, 7);
         stage_solve<KN>(e, nheads);
         if (has_collidables) stage_cache_commit(e, nheads, sm + p.sm.heads + HF_LAM * t.head_cap);
         if (has_artic) stage_readout_drives(e, nheads);
+        tick(e, 12);
         if (has_artic) { stage_integrate_links(e, use_pseudo); }
         if (has_bodies) stage_integrate_bodies(e, use_pseudo);
         __syncwarp();
@@ -199,9 +206,27 @@ __global__ void __launch_bounds__(kWarpsPerBlockMax * 32) step_kernel(const Step
         for (int o = 16; o > 0; o >>= 1) st |= __shfl_xor_sync(NKB_FULL, st, o);
         if (lane == 0u && st != 0u) p.s.status[env] |= st;
         __syncwarp();
+        tick(e, 13);
     }
 }
 
+template <int KN>
+cudaError_t launch_kn(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
+    const size_t bytes = (size_t)warps_per_block * p.sm.words * sizeof(float);
+    if (bytes > 48u * 1024u) {
+        const cudaError_t err = cudaFuncSetAttribute(step_kernel<KN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (err != cudaSuccess) return err;
+    }
+    const uint32_t blocks = (p.s.env_count + warps_per_block - 1u) / warps_per_block;
+    step_kernel<KN><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+// This file is compiled once per coordinate-count bucket (-DNKB_KN=8|16|20|24|32) and once without the macro
+// for the dispatcher and the reset kernel, so the buckets build in parallel.
+#ifdef NKB_KN
+template cudaError_t launch_kn<NKB_KN>(const StepParams&, uint32_t, cudaStream_t);
+#else
 // Per-env reset from the creation snapshot (reference ops/readout.cu:771-776 RestoreState semantics).
 __global__ void reset_kernel(ResetParams r) {
     const uint32_t slot = blockIdx.x;
@@ -215,19 +240,11 @@ __global__ void reset_kernel(ResetParams r) {
     }
 }
 
-template <int KN>
-static cudaError_t launch_kn(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
-    const size_t bytes = (size_t)warps_per_block * p.sm.words * sizeof(float);
-    static thread_local size_t configured = 0;
-    if (bytes > configured) {
-        const cudaError_t err = cudaFuncSetAttribute(step_kernel<KN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-        if (err != cudaSuccess) return err;
-        configured = bytes;
-    }
-    const uint32_t blocks = (p.s.env_count + warps_per_block - 1u) / warps_per_block;
-    step_kernel<KN><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
-    return cudaGetLastError();
-}
+extern template cudaError_t launch_kn<8>(const StepParams&, uint32_t, cudaStream_t);
+extern template cudaError_t launch_kn<16>(const StepParams&, uint32_t, cudaStream_t);
+extern template cudaError_t launch_kn<20>(const StepParams&, uint32_t, cudaStream_t);
+extern template cudaError_t launch_kn<24>(const StepParams&, uint32_t, cudaStream_t);
+extern template cudaError_t launch_kn<32>(const StepParams&, uint32_t, cudaStream_t);
 
 cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
     const uint32_t n = p.t.ndof;
@@ -243,5 +260,6 @@ cudaError_t launch_reset(const ResetParams& r, uint32_t count, cudaStream_t stre
     reset_kernel<<<count, 128, 0, stream>>>(r);
     return cudaGetLastError();
 }
+#endif
 
 }  // namespace nkb

@@ -294,7 +294,7 @@ NKB_DEV void apply_moves(Env& e, const Tile& tile, uint32_t b, float alpha) {
 
 // Newton steps with exact line search on one block; KN >= the block's dimension.
 template <int KN>
-__device__ __noinline__ void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
+NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     const TemplateView& t = *e.t;
     const uint32_t l = e.lane, nb = tile.nblocks, dim = blk_dim(e, b);
     const bool coord = l < dim;
@@ -404,6 +404,7 @@ __device__ __noinline__ void descend_block(Env& e, Tile& tile, uint32_t b, bool 
                     hrow[k] += a0 * __shfl_sync(NKB_FULL, j0, k) + a1 * __shfl_sync(NKB_FULL, j1, k) + a2 * __shfl_sync(NKB_FULL, j2, k);
             }
         }
+        if (e.cyc != nullptr && l == 0u) { const long long now = clock64(); e.cyc[16] += (uint32_t)(now - e.t0); }
         float force = 0.f, inertia = 0.f;
         bool finite = true;
 #pragma unroll
@@ -680,8 +681,10 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
     }
     __syncwarp();
     init_heads(e, tile);
+    tick(e, 8);
     index_blocks(e, tile, true);
     init_residuals(e, tile);
+    tick(e, 9);
     float rows[3] = {0.f, 0.f, 0.f};
     float cls[4] = {0.f, 0.f, 0.f, 0.f};
     uint32_t sweeps = 0u;
@@ -691,6 +694,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
         tile.iteration = sweeps++;
         tile.momentum = 0.f; tile.residual = 0.f;
         descend_blocks<KN>(e, tile, false);
+        tick(e, 10);
         update_duals(e, tile, &mom, true, true, rows);
         if (sweeps == iterations || fmaxf(fmaxf(rows[0], rows[1]), fmaxf(rows[2], tile.residual)) < tile.tol) measure_primals(e, tile, false);
         if (fmaxf(fmaxf(rows[0], rows[1]), rows[2]) < tile.tol && tile.residual >= tile.tol && tile.residual < FLT_MAX) {
@@ -704,6 +708,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
         }
         cls[0] = rows[0]; cls[1] = rows[1]; cls[2] = rows[2]; cls[3] = tile.residual;
         const float largest = fmaxf(fmaxf(rows[0], rows[1]), fmaxf(rows[2], tile.residual));
+        tick(e, 11);
         if (largest < tile.tol || largest == FLT_MAX) break;
     }
     if (l < 4u) e.s->solver_residual[(size_t)e.env * 4u + l] = cls[l];
@@ -781,6 +786,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
             }
         }
     }
+    tick(e, 14);
     if (e.s->dbg_qdot_pseudo != nullptr && l < n) e.s->dbg_qdot_pseudo[(size_t)e.env * n + l] = sm_vec(e, kVecPseudo)[l];
     (void)nb;
 }

@@ -207,7 +207,20 @@ void World::BuildLayout() {
     SmemLayout& s = params_.sm;
     const uint32_t L = t.L, B = t.B, n = t.ndof, S = t.cfg.max_contacts;
     TemplateView& tv = params_.t;
-    tv.point_cap = std::min(4u * S, 32u);
+    // contact points the admissible pairs can produce in the S slots: sphere pairs give 1 point, capsule pairs 2,
+    // box/plane pairs up to 4; the S largest capacities bound what one step can hold
+    {
+        std::vector<uint32_t> caps;
+        if (!(t.adm_pairs.size() == 1 && t.adm_pairs[0] == 0u))
+            for (uint32_t key : t.adm_pairs) {
+                const uint32_t ka = t.shape_kind[key >> 16], kb = t.shape_kind[key & 0xffffu];
+                caps.push_back((ka == kSphere || kb == kSphere) ? 1u : (ka == kCapsule || kb == kCapsule) ? 2u : 4u);
+            }
+        std::sort(caps.begin(), caps.end(), [](uint32_t a, uint32_t b) { return a > b; });
+        uint32_t total = 0;
+        for (size_t k = 0; k < caps.size() && k < S; ++k) total += caps[k];
+        tv.point_cap = std::min(total, 32u);
+    }
     tv.head_cap = (tv.point_cap + t.joint_rows + 3u) & ~3u;
     if (tv.head_cap == 0u) tv.head_cap = 4u;
     uint32_t at = 0;
@@ -229,7 +242,16 @@ void World::BuildLayout() {
     s.words = at;
     const size_t bytes = static_cast<size_t>(s.words) * 4u;
     if (bytes > 220u * 1024u) throw Error(kNotSupported, "template needs more shared memory per env than one SM provides");
-    warps_per_block_ = static_cast<uint32_t>(std::max<size_t>(1, std::min<size_t>(kWarpsPerBlockMax, (110u * 1024u) / bytes)));
+    // block shape that keeps the most warps resident on one SM (228 KB shared memory, 1 KB reserved per block)
+    size_t best = 0;
+    warps_per_block_ = 1;
+    for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) {
+        const size_t block = w * bytes + 1024u;
+        if (w * bytes > 227u * 1024u) break;
+        const size_t blocks = std::min<size_t>(32, (228u * 1024u) / block);
+        const size_t resident = std::min<size_t>(64, blocks * w);
+        if (resident >= best) { best = resident; warps_per_block_ = w; }
+    }
 }
 
 World::World(int device, cudaStream_t stream, const HostTemplate& tpl, uint32_t env_count)
@@ -269,7 +291,7 @@ World::World(int device, cudaStream_t stream, const HostTemplate& tpl, uint32_t 
         s.status = Alloc<uint32_t>(E); s.solver_residual = Alloc<float>(E * 4); s.solver_sweeps = Alloc<uint32_t>(E);
         s.pair_count = Alloc<uint32_t>(E); s.pairs = Alloc<uint32_t>(E * S * 2); s.contact_count = Alloc<uint32_t>(E * S);
         s.contact_point = Alloc<float>(E * S * 12); s.contact_normal = Alloc<float>(E * S * 12); s.contact_depth = Alloc<float>(E * S * 4);
-        s.dbg_mass = nullptr; s.dbg_qdot_pseudo = nullptr;
+        s.dbg_mass = nullptr; s.dbg_qdot_pseudo = nullptr; s.dbg_cycles = nullptr;
         Seed();
     } catch (...) {
         for (void* p : allocations_) cudaFree(p);
@@ -445,6 +467,9 @@ bool World::Field(uint32_t id, FieldInfo* out) {
         case 0x10009:
             if (s.dbg_qdot_pseudo == nullptr) s.dbg_qdot_pseudo = Alloc<float>(static_cast<size_t>(env_count_) * n);
             return set(s.dbg_qdot_pseudo, n, 0, false);
+        case 0x1000A:      // stage cycle counters accumulate from the first request on; writable so callers can clear them
+            if (s.dbg_cycles == nullptr) s.dbg_cycles = Alloc<uint32_t>(static_cast<size_t>(env_count_) * 24u);
+            return set(s.dbg_cycles, 24, 1, true);
         default: return false;
     }
 }

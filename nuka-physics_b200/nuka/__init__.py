@@ -54,6 +54,7 @@ class Field(enum.IntEnum):
     CONTACT_DEPTH = 0x10007
     SOLVER_SWEEPS = 0x10008
     JOINT_PSEUDO_VELOCITY = 0x10009
+    STAGE_CYCLES = 0x1000A
 
 
 class Device:

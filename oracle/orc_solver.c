@@ -331,11 +331,15 @@ static void row_steps(tile_t *t, uint32_t bi, const float *d) {
     }
 }
 
+/* Work counters for diagnostics (single-threaded runs only): block descents, Newton steps, line evaluations. */
+unsigned long long orc_work_counters[4];
+
 /* block_descent_tile.cuh:2048-2086 TileLineDerivatives */
 static void line_derivatives(tile_t *t, uint32_t bi, float alpha, float islope, float icurv, float *slope, float *curvature, float *magnitude) {
     const block_t *b = &t->blocks[bi];
     tsum rs = {0, 0};
     float rc = 0.0f, rm = 0.0f;
+    ++orc_work_counters[2];
     for (uint32_t k = 0; k < b->ninc; ++k) {
         const head_t *h = &t->heads[b->inc[k]];
         const v3 trial = V3(fmaf(alpha, h->step.x, h->move.x), fmaf(alpha, h->step.y, h->move.y), fmaf(alpha, h->step.z, h->move.z));
@@ -414,10 +418,12 @@ static void descend_block(tile_t *t, uint32_t bi, int position) {
     }
     int failure = 0;
     float primal = FLT_MAX;
+    ++orc_work_counters[0];
     float *H = (float *)malloc(sizeof(float) * n * n);
     for (uint32_t step = 0; step < NEWTON_STEPS; ++step) {
         float force[ORC_MAX_DOF], inertia[ORC_MAX_DOF];
         int converged = 0;
+        ++orc_work_counters[1];
         /* TileNewtonDirection :1936-1992 */
         if (!assemble_block(t, bi, u, fr, H, force, inertia, &converged)) { failure = 1; break; }
         if (converged && t->tol > 0.0f) {
