@@ -122,9 +122,8 @@ NKB_DEV void stage_store_bodies(Env& e, bool velocities) {
     }
 }
 
-template <int KN>
 __global__ void __maxnreg__(168) step_kernel(const __grid_constant__ StepParams p) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t env = blockIdx.x * (blockDim.x >> 5) + warp;
     if (env >= p.s.env_count) return;
@@ -174,7 +173,7 @@ __global__ void __maxnreg__(168) step_kernel(const __grid_constant__ StepParams 
         tick(e, 6);
         stage_warm_start(e, nheads);
         tick(e, 7);
-        stage_solve<KN>(e, nheads);
+        stage_solve(e, nheads);
         if (has_collidables) stage_cache_commit(e, nheads, sm + p.sm.heads + HF_LAM * t.head_cap);
         if (has_artic) stage_readout_drives(e, nheads);
         tick(e, 12);
@@ -210,23 +209,6 @@ __global__ void __maxnreg__(168) step_kernel(const __grid_constant__ StepParams 
     }
 }
 
-template <int KN>
-cudaError_t launch_kn(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
-    const size_t bytes = (size_t)warps_per_block * p.sm.words * sizeof(float);
-    if (bytes > 48u * 1024u) {
-        const cudaError_t err = cudaFuncSetAttribute(step_kernel<KN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-        if (err != cudaSuccess) return err;
-    }
-    const uint32_t blocks = (p.s.env_count + warps_per_block - 1u) / warps_per_block;
-    step_kernel<KN><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
-    return cudaGetLastError();
-}
-
-// This file is compiled once per coordinate-count bucket (-DNKB_KN=8|16|20|24|32) and once without the macro
-// for the dispatcher and the reset kernel, so the buckets build in parallel.
-#ifdef NKB_KN
-template cudaError_t launch_kn<NKB_KN>(const StepParams&, uint32_t, cudaStream_t);
-#else
 // Per-env reset from the creation snapshot (reference ops/readout.cu:771-776 RestoreState semantics).
 __global__ void reset_kernel(ResetParams r) {
     const uint32_t slot = blockIdx.x;
@@ -240,19 +222,15 @@ __global__ void reset_kernel(ResetParams r) {
     }
 }
 
-extern template cudaError_t launch_kn<8>(const StepParams&, uint32_t, cudaStream_t);
-extern template cudaError_t launch_kn<16>(const StepParams&, uint32_t, cudaStream_t);
-extern template cudaError_t launch_kn<20>(const StepParams&, uint32_t, cudaStream_t);
-extern template cudaError_t launch_kn<24>(const StepParams&, uint32_t, cudaStream_t);
-extern template cudaError_t launch_kn<32>(const StepParams&, uint32_t, cudaStream_t);
-
 cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
-    const uint32_t n = p.t.ndof;
-    if (n <= 8u) return launch_kn<8>(p, warps_per_block, stream);
-    if (n <= 16u) return launch_kn<16>(p, warps_per_block, stream);
-    if (n <= 20u) return launch_kn<20>(p, warps_per_block, stream);
-    if (n <= 24u) return launch_kn<24>(p, warps_per_block, stream);
-    return launch_kn<32>(p, warps_per_block, stream);
+    const size_t bytes = (size_t)warps_per_block * p.sm.words * sizeof(float);
+    if (bytes > 48u * 1024u) {
+        const cudaError_t err = cudaFuncSetAttribute(step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (err != cudaSuccess) return err;
+    }
+    const uint32_t blocks = (p.s.env_count + warps_per_block - 1u) / warps_per_block;
+    step_kernel<<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_reset(const ResetParams& r, uint32_t count, cudaStream_t stream) {
@@ -260,6 +238,5 @@ cudaError_t launch_reset(const ResetParams& r, uint32_t count, cudaStream_t stre
     reset_kernel<<<count, 128, 0, stream>>>(r);
     return cudaGetLastError();
 }
-#endif
 
 }  // namespace nkb

@@ -33,13 +33,16 @@ NKB_DEV STerm scalar_impulse(float dual, float rho, float residual, float lower,
 }
 
 NKB_DEV float cone_argument(float dual, float rho, float mu, float residual) {
-    const bool dual_zero = dual == 0.0f;
-    const float dual_quotient = __fdiv_rn(dual + (dual_zero ? 1.0f : 0.0f), mu);
-    const float d = dual_zero ? dual : dual_quotient;
-    const float low = fmaf(-d, mu, dual);
-    const bool low_zero = low == 0.0f;
-    const float low_quotient = __fdiv_rn(low + (low_zero ? 1.0f : 0.0f), mu);
-    const float d_low = low_zero ? low : low_quotient;
+    float d = dual, d_low = 0.0f;      // exact for mu == 1 (isotropic friction), the common case
+    if (mu != 1.0f) {
+        const bool dual_zero = dual == 0.0f;
+        const float dual_quotient = __fdiv_rn(dual + (dual_zero ? 1.0f : 0.0f), mu);
+        d = dual_zero ? dual : dual_quotient;
+        const float low = fmaf(-d, mu, dual);
+        const bool low_zero = low == 0.0f;
+        const float low_quotient = __fdiv_rn(low + (low_zero ? 1.0f : 0.0f), mu);
+        d_low = low_zero ? low : low_quotient;
+    }
     const float p = __fmul_rn(rho, mu);
     const float t = __fmul_rn(p, residual);
     const float t_low = __fadd_rn(fmaf(p, residual, -t), __fmul_rn(fmaf(rho, mu, -p), residual));
@@ -55,8 +58,9 @@ NKB_DEV void tangent_impulse(V3 dual, float rho, float res_y, float res_z, float
     iy = iz = cyy = czz = cyz = 0.f;
     if (rho <= 0.0f) return;
     const float scale = fmaxf(mu_first, mu_second);
-    const float mu_y = mu_first <= 0.0f ? 0.0f : mu_first / scale;
-    const float mu_z = mu_second <= 0.0f ? 0.0f : mu_second / scale;
+    const bool isotropic = mu_first == mu_second;
+    const float mu_y = mu_first <= 0.0f ? 0.0f : (isotropic ? 1.0f : mu_first / scale);
+    const float mu_z = mu_second <= 0.0f ? 0.0f : (isotropic ? 1.0f : mu_second / scale);
     const float q_y = mu_y == 0.0f ? 0.0f : cone_argument(dual.y, rho, mu_y, res_y);
     const float q_z = mu_z == 0.0f ? 0.0f : cone_argument(dual.z, rho, mu_z, res_z);
     const float radius = (normal_impulse < 0.0f ? 0.0f : normal_impulse) * fmaxf(scale, 0.0f);
@@ -66,13 +70,14 @@ NKB_DEV void tangent_impulse(V3 dual, float rho, float res_y, float res_z, float
         return;
     }
     if (radius == 0.0f) return;
-    const float norm = hypotf(q_y, q_z);
+    const float norm = sqrtf(fmaf(q_y, q_y, q_z * q_z));
     if (norm <= radius) {
         iy = mu_y * q_y; iz = mu_z * q_z;
         cyy = rho * mu_y * mu_y; czz = rho * mu_z * mu_z;
         return;
     }
-    const float dy = q_y / norm, dz = q_z / norm, cs = rho * radius / norm;
+    const float inv_norm = __frcp_rn(norm);
+    const float dy = q_y * inv_norm, dz = q_z * inv_norm, cs = rho * radius * inv_norm;
     iy = mu_y * radius * dy; iz = mu_z * radius * dz;
     cyy = cs * mu_y * mu_y * dz * dz;
     czz = cs * mu_z * mu_z * dy * dy;

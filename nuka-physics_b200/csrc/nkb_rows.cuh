@@ -17,7 +17,9 @@ enum HeadField : uint32_t {
     HF_RXS = HF_STEP + 3, HF_RXW = HF_RXS + 3, HF_RXP,
     HF_N = HF_RXP + 3, HF_T1 = HF_N + 3, HF_T2 = HF_T1 + 3, HF_RA = HF_T2 + 3, HF_RB = HF_RA + 3,
     HF_LAM = HF_RB + 3,          // physical multipliers after the velocity solve
-    HF_COUNT = HF_LAM + 3
+    HF_F = HF_LAM + 3,           // response impulse, curvature (xx, yy, zz, yz) and noise scale at the current move
+    HF_C = HF_F + 3, HF_NZ = HF_C + 4,
+    HF_COUNT = HF_NZ + 3
 };
 constexpr uint32_t kNoBlock16 = 0xffffu;
 constexpr uint32_t kUnitRow = 0x80000000u;   // HF_JOFF: unit row on coordinate (value & 0xffff)
@@ -133,7 +135,7 @@ NKB_DEV uint32_t stage_rows(Env& e, uint32_t pair_count) {
         float* pool = sm_jpool(e);
         for (uint32_t h = 0u; h < ncontact; ++h) {
             const uint32_t ref = hu(e, HF_REF, h), la = ref >> 16, lb = hu(e, HF_JOFF, h) & 0xffffu;
-            const uint32_t joff = h * 3u * n;
+            const uint32_t n4 = (n + 3u) & ~3u, joff = h * 3u * n4;
             const V3 point = ld3(sm_cpoint(e, ref & 0xffffu));
             const V3 dirs[3] = {hf3(e, HF_N, h), hf3(e, HF_T1, h), hf3(e, HF_T2, h)};
             if (dof) {
@@ -154,8 +156,8 @@ NKB_DEV uint32_t stage_rows(Env& e, uint32_t pair_count) {
                         ent[ax] += v;
                     }
                 }
-                pool[joff + lane] = ent[0]; pool[joff + n + lane] = ent[1]; pool[joff + 2u * n + lane] = ent[2];
-            }
+                pool[joff + lane] = ent[0]; pool[joff + n4 + lane] = ent[1]; pool[joff + 2u * n4 + lane] = ent[2];
+            } else if (lane < n4) { pool[joff + lane] = 0.f; pool[joff + n4 + lane] = 0.f; pool[joff + 2u * n4 + lane] = 0.f; }
             if (lane == 0u) hu(e, HF_JOFF, h) = joff;
         }
     }

@@ -24,11 +24,14 @@ struct Tile {
 };
 
 NKB_DEV uint32_t* sm_binfo(const Env& e) { return reinterpret_cast<uint32_t*>(e.sm + e.lay->binfo); }
-// binfo words: dim[nb], color[nb], inc_begin[nb + 1], inc[2 * head_cap]
+// binfo words: dim[nb], color[nb], inc_begin[nb + 1], inc[2 * head_cap], utab[4 * 32]
 NKB_DEV uint32_t& blk_dim(const Env& e, uint32_t b) { return sm_binfo(e)[b]; }
 NKB_DEV uint32_t& blk_color(const Env& e, uint32_t nb, uint32_t b) { return sm_binfo(e)[nb + b]; }
 NKB_DEV uint32_t& blk_inc_begin(const Env& e, uint32_t nb, uint32_t b) { return sm_binfo(e)[2u * nb + b]; }
 NKB_DEV uint32_t* blk_inc(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u * nb + 1u; }
+// unit rows of the articulation by coordinate: utab[slot * 32 + coordinate] = head or ~0 (slots: lower limit, upper limit,
+// dry friction, drive)
+NKB_DEV uint32_t* unit_table(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u * nb + 1u + 2u * e.t->head_cap; }
 NKB_DEV float* sm_bmass(const Env& e, uint32_t b) { return e.sm + e.lay->bmass + 7u * b; }
 NKB_DEV float* sm_bfree(const Env& e, uint32_t b) { return e.sm + e.lay->bfree + 6u * b; }
 NKB_DEV float* sm_bpseudo(const Env& e, uint32_t b) { return e.sm + e.lay->bpseudo + 6u * b; }
@@ -43,7 +46,7 @@ NKB_DEV float head_jac(const Env& e, uint32_t h, uint32_t side, uint32_t ax, uin
     if (block == t.B) {
         const uint32_t jo = hu(e, HF_JOFF, h);
         if (jo & kUnitRow) return i == (jo & 0xffffu) ? hf(e, HF_UNITV, h) : 0.f;
-        return sm_jpool(e)[jo + ax * t.ndof + i];
+        return sm_jpool(e)[jo + ax * ((t.ndof + 3u) & ~3u) + i];
     }
     const V3 dir = hf3(e, ax == 0u ? HF_N : ax == 1u ? HF_T1 : HF_T2, h);
     const float sgn = side == 0u ? 1.f : -1.f;
@@ -173,6 +176,16 @@ NKB_DEV void index_blocks(Env& e, const Tile& tile, bool color) {
         }
     }
     if (e.lane == 0u) blk_inc_begin(e, nb, nb) = at;
+    uint32_t* utab = unit_table(e, nb);
+#pragma unroll
+    for (uint32_t slot = 0u; slot < 4u; ++slot) utab[slot * 32u + e.lane] = 0xffffffffu;
+    __syncwarp();
+    for (uint32_t h = e.lane; h < tile.nheads; h += 32u) {
+        const uint32_t jo = hu(e, HF_JOFF, h), o = hu(e, HF_OWNER, h), fl = hu(e, HF_FLAGS, h);
+        if (!(jo & kUnitRow) || ((o & 0xffffu) != e.t->B && (o >> 16) != e.t->B)) continue;
+        const uint32_t slot = (fl & kHeadDrive) ? 3u : (fl & kHeadFriction) ? 2u : hf(e, HF_UNITV, h) < 0.f ? 1u : 0u;
+        utab[slot * 32u + (jo & 0xffffu)] = h;
+    }
     __syncwarp();
     if (!color) return;
     for (uint32_t b = 0u; b < nb; ++b) {
@@ -215,69 +228,124 @@ NKB_DEV void init_residuals(Env& e, const Tile& tile) {
     __syncwarp();
 }
 
-// Row steps J d of a block's incident heads; d is staged in shared memory.
+// Leading dimension of a shared-memory matrix whose rows are read as float4 by one lane per row:
+// a multiple of 4 words that is 4 mod 8, so the eight lanes of a quarter warp hit distinct bank groups.
+NKB_DEV uint32_t pad_ld(uint32_t n) { const uint32_t ld = (n + 3u) & ~3u; return (ld & 7u) == 0u ? ld + 4u : ld; }
+
+// Register copy of one head for the row evaluations.
+struct HeadRegs {
+    V3 dual, res, move, step;
+    float rho, lower, upper, rsd, rsr, mu, nb;
+    bool cone;      // three-axis contact head
+};
+NKB_DEV HeadRegs load_head(const Env& e, uint32_t h) {
+    HeadRegs r;
+    r.dual = hf3(e, HF_DUAL, h); r.res = hf3(e, HF_RES, h); r.move = hf3(e, HF_MOVE, h); r.step = hf3(e, HF_STEP, h);
+    r.rho = hf(e, HF_RHO, h); r.lower = hf(e, HF_LOWER, h); r.upper = hf(e, HF_UPPER, h);
+    r.rsd = hf(e, HF_RSD, h); r.rsr = hf(e, HF_RSR, h); r.mu = hf(e, HF_MU, h); r.nb = hf(e, HF_NB, h);
+    r.cone = head_axes(e, h) == 3u;
+    return r;
+}
+NKB_DEV void respond(const HeadRegs& r, V3 move, V3& f, float& cxx, float& cyy, float& czz, float& cyz) {
+    const Resp rs = {r.rsd, r.rsr};
+    const STerm n = scalar_impulse(r.dual.x, r.rho, r.res.x - move.x, r.lower, r.upper, rs);
+    f = mk3(n.impulse, 0.f, 0.f);
+    cxx = n.curvature; cyy = czz = cyz = 0.f;
+    if (r.cone) tangent_impulse(r.dual, r.rho, r.res.y - move.y, r.res.z - move.z, r.nb, r.mu, r.mu, f.y, f.z, cyy, czz, cyz);
+}
+
+// Row steps J d of a block's incident heads (block_descent_tile.cuh:2019-2044); lane = head, d staged in shared
+// memory with zeros past the block's dimension.
 NKB_DEV void row_steps(Env& e, const Tile& tile, uint32_t b, const float* dvec) {
     const uint32_t nb = tile.nblocks, dim = blk_dim(e, b);
+    const bool artic = b == e.t->B;
     const uint32_t* inc = blk_inc(e, nb);
     const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
+    const uint32_t chunks = (dim + 3u) >> 2, n4 = chunks << 2;
+    const float4* d4 = reinterpret_cast<const float4*>(dvec);
     for (uint32_t k = ib + e.lane; k < ie; k += 32u) {
         const uint32_t h = inc[k];
-        const uint32_t side = head_owner(e, h, 0u) == b ? 0u : 1u;
-        const uint32_t axes = head_axes(e, h);
+        const bool cone = head_axes(e, h) == 3u;
         V3 step = mk3(0.f, 0.f, 0.f);
         const uint32_t jo = hu(e, HF_JOFF, h);
-        if (b == e.t->B && (jo & kUnitRow)) step.x = hf(e, HF_UNITV, h) * dvec[jo & 0xffffu];
-        else for (uint32_t ax = 0u; ax < axes; ++ax) {
-            float s = 0.f;
-            for (uint32_t i = 0u; i < dim; ++i) s += head_jac(e, h, side, ax, i, b) * dvec[i];
-            setc(step, (int)ax, s);
+        if (artic) {
+            if (jo & kUnitRow) step.x = hf(e, HF_UNITV, h) * dvec[jo & 0xffffu];
+            else {
+                const float4* j4 = reinterpret_cast<const float4*>(sm_jpool(e) + jo);
+                float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+                for (uint32_t c = 0u; c < chunks; ++c) {
+                    const float4 d = d4[c], r0 = j4[c];
+                    s0 = fmaf(r0.x, d.x, s0); s0 = fmaf(r0.y, d.y, s0); s0 = fmaf(r0.z, d.z, s0); s0 = fmaf(r0.w, d.w, s0);
+                    if (cone) {
+                        const float4 r1 = j4[chunks + c], r2 = j4[2u * chunks + c];
+                        s1 = fmaf(r1.x, d.x, s1); s1 = fmaf(r1.y, d.y, s1); s1 = fmaf(r1.z, d.z, s1); s1 = fmaf(r1.w, d.w, s1);
+                        s2 = fmaf(r2.x, d.x, s2); s2 = fmaf(r2.y, d.y, s2); s2 = fmaf(r2.z, d.z, s2); s2 = fmaf(r2.w, d.w, s2);
+                    }
+                }
+                step = mk3(s0, s1, s2);
+            }
+        } else {
+            const uint32_t side = head_owner(e, h, 0u) == b ? 0u : 1u;
+            const uint32_t axes = cone ? 3u : 1u;
+            for (uint32_t ax = 0u; ax < axes; ++ax) {
+                float s = 0.f;
+                for (uint32_t i = 0u; i < dim; ++i) s += head_jac(e, h, side, ax, i, b) * dvec[i];
+                setc(step, (int)ax, s);
+            }
         }
         hst3(e, HF_STEP, h, step);
     }
+    (void)n4;
     __syncwarp();
 }
 
-NKB_DEV void line_derivatives(Env& e, const Tile& tile, uint32_t b, float alpha, float islope, float icurv, float& slope, float& curvature, float& magnitude) {
+// One head's share of the line derivatives at step length alpha.
+NKB_DEV void line_terms(const HeadRegs& r, float alpha, CSum& rs, float& rc, float& rm) {
+    const V3 trial = mk3(fmaf(alpha, r.step.x, r.move.x), fmaf(alpha, r.step.y, r.move.y), fmaf(alpha, r.step.z, r.move.z));
+    V3 f; float cxx, cyy, czz, cyz;
+    respond(r, trial, f, cxx, cyy, czz, cyz);
+    csum_addp(rs, f.x, r.step.x); csum_addp(rs, f.y, r.step.y); csum_addp(rs, f.z, r.step.z);
+    rm += fabsf(f.x * r.step.x) + fabsf(f.y * r.step.y) + fabsf(f.z * r.step.z);
+    rc += cxx * r.step.x * r.step.x + cyy * r.step.y * r.step.y + czz * r.step.z * r.step.z + 2.0f * cyz * r.step.y * r.step.z;
+}
+
+// Exact line search on the block's one-dimensional model (block_descent_tile.cuh:2048-2125): the first
+// evaluation (alpha = 0) gives the initial slope, the following ones bracket and polish the root.  With at most
+// 32 incident heads each lane keeps its head in registers for the whole search.
+NKB_DEV float search_line(Env& e, const Tile& tile, uint32_t b, float islope, float icurv) {
     const uint32_t nb = tile.nblocks;
     const uint32_t* inc = blk_inc(e, nb);
     const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
-    CSum rs = {0.f, 0.f};
-    float rc = 0.f, rm = 0.f;
-    for (uint32_t k = ib + e.lane; k < ie; k += 32u) {
-        const uint32_t h = inc[k];
-        const V3 step = hf3(e, HF_STEP, h), move = hf3(e, HF_MOVE, h);
-        const V3 trial = mk3(fmaf(alpha, step.x, move.x), fmaf(alpha, step.y, move.y), fmaf(alpha, step.z, move.z));
-        V3 f; float cxx, cyy, czz, cyz;
-        head_response(e, h, trial, f, cxx, cyy, czz, cyz);
-        csum_addp(rs, f.x, step.x); csum_addp(rs, f.y, step.y); csum_addp(rs, f.z, step.z);
-        rm += fabsf(f.x * step.x) + fabsf(f.y * step.y) + fabsf(f.z * step.z);
-        rc += cxx * step.x * step.x + cyy * step.y * step.y + czz * step.z * step.z + 2.0f * cyz * step.y * step.z;
-    }
-    CSum total = {-rs.value, -rs.error};
-    if (e.lane == 0u) { csum_addp(total, alpha, icurv); csum_add(total, islope); }
-    slope = warp_csum_total(total);
-    curvature = icurv + warp_sum(rc);
-    magnitude = fabsf(islope) + alpha * icurv + warp_sum(rm);
-}
-
-NKB_DEV float search_line(Env& e, const Tile& tile, uint32_t b, float islope, float icurv) {
-    float slope, curvature, magnitude;
-    line_derivatives(e, tile, b, 0.0f, islope, icurv, slope, curvature, magnitude);
-    const float initial = slope;
-    if (!(initial < 0.0f)) return 0.0f;
-    float low = 0.0f, high = 0.0f, alpha = 1.0f;
-    bool bounded = false;
-    for (uint32_t step = 0u; step < kLineSteps; ++step) {
-        line_derivatives(e, tile, b, alpha, islope, icurv, slope, curvature, magnitude);
+    const bool single = ie - ib <= 32u, mine = ib + e.lane < ie;
+    HeadRegs cached;
+    if (single && mine) cached = load_head(e, inc[ib + e.lane]);
+    float low = 0.0f, high = 0.0f, alpha = 0.0f, initial = 0.0f, result = 0.0f;
+    bool bounded = false, have = false;
+    for (int step = -1; step < (int)kLineSteps; ++step) {
+        CSum rs = {0.f, 0.f};
+        float rc = 0.f, rm = 0.f;
+        if (single) { if (mine) line_terms(cached, alpha, rs, rc, rm); }
+        else for (uint32_t k = ib + e.lane; k < ie; k += 32u) { const HeadRegs r = load_head(e, inc[k]); line_terms(r, alpha, rs, rc, rm); }
+        CSum total = {-rs.value, -rs.error};
+        if (e.lane == 0u) { csum_addp(total, alpha, icurv); csum_add(total, islope); }
+        const float slope = warp_csum_total(total);
+        const float curvature = icurv + warp_sum(rc);
+        const float magnitude = fabsf(islope) + alpha * icurv + warp_sum(rm);
+        if (step < 0) {
+            initial = slope;
+            if (!(initial < 0.0f)) { have = true; result = 0.0f; break; }
+            alpha = 1.0f;
+            continue;
+        }
         if (!isfinite(slope) || !isfinite(curvature)) { high = alpha; bounded = true; alpha = 0.5f * (low + high); continue; }
-        if (fabsf(slope) <= fmaxf(kLineTol * -initial, kRoundings * FLT_EPSILON * magnitude)) return alpha;
+        if (fabsf(slope) <= fmaxf(kLineTol * -initial, kRoundings * FLT_EPSILON * magnitude)) { have = true; result = alpha; break; }
         if (slope < 0.0f) low = alpha; else { high = alpha; bounded = true; }
         if (bounded && high - low <= FLT_EPSILON * high) break;
         float next = alpha - slope / curvature;
         if (!(next > low && (!bounded || next < high))) next = bounded ? 0.5f * (low + high) : 2.0f * alpha;
         alpha = next;
     }
-    return low;
+    return have ? result : low;
 }
 
 NKB_DEV void apply_moves(Env& e, const Tile& tile, uint32_t b, float alpha) {
@@ -292,16 +360,34 @@ NKB_DEV void apply_moves(Env& e, const Tile& tile, uint32_t b, float alpha) {
     __syncwarp();
 }
 
-// Newton steps with exact line search on one block; KN >= the block's dimension.
-template <int KN>
+// Newton steps with exact line search on one block.  Lane i owns coordinate i and row i of the Newton matrix,
+// which lives in the env's shared-memory slice in float4-readable rows; lane k also owns the k-th incident
+// head in the row evaluations and publishes its response through the head's shared-memory fields.
 NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     const TemplateView& t = *e.t;
     const uint32_t l = e.lane, nb = tile.nblocks, dim = blk_dim(e, b);
-    const bool coord = l < dim;
+    const bool coord = l < dim, artic = b == t.B;
     const uint32_t* inc = blk_inc(e, nb);
     const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
+    const uint32_t chunks = (dim + 3u) >> 2, ldh = pad_ld(dim);
     float* velocity = block_vel(e, b, position);
     float* dvec = sm_vec(e, kVecD);
+    float* hi_v = sm_vec(e, kVecS0);
+    float* lo_v = sm_vec(e, kVecS1);
+    float* u_v = sm_vec(e, kVecS2);
+    float* H = e.sm + e.lay->chol;
+    float* Hr = H + (coord ? l : 0u) * ldh;
+    float4* Hr4 = reinterpret_cast<float4*>(Hr);
+    float* m6 = e.sm + e.lay->bm6;      // 6 x 12 dense mass of a rigid block, then 3 x 8 Jacobian rows of one head
+    float* jscr = m6 + 72u;
+    const float* Mr;                    // this lane's row of the block mass, zero past the block's dimension
+    if (artic) Mr = sm_mass(e) + (coord ? l : 0u) * e.lay->ld;
+    else {
+        if (l < 6u) for (uint32_t k = 0u; k < 8u; ++k) m6[l * 12u + k] = k < 6u ? block_mass(e, b, l, k) : 0.f;
+        if (l < 24u) jscr[l] = 0.f;
+        Mr = m6 + (coord ? l : 0u) * 12u;
+    }
+    const float4* Mr4 = reinterpret_cast<const float4*>(Mr);
     bool coupled = false;
     for (uint32_t k = ib + l; k < ie; k += 32u) {
         const uint32_t h = inc[k];
@@ -312,169 +398,196 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     }
     coupled = __any_sync(NKB_FULL, coupled);
     __syncwarp();
-    float mrow[KN];
-#pragma unroll
-    for (int k = 0; k < KN; ++k) mrow[k] = (coord && (uint32_t)k < dim) ? block_mass(e, b, l, (uint32_t)k) : ((uint32_t)k == l ? 1.f : 0.f);
     const float start = coord ? velocity[l] : 0.f;
     const float fr = (coord && !position) ? block_free(e, b)[l] : 0.f;
     float u = start;
-    if (tile.iteration == 0u && !position) {
-        const float d = coord ? fr - u : 0.f;
-        float ms = 0.f;
-#pragma unroll
-        for (int k = 0; k < KN; ++k) ms += mrow[k] * __shfl_sync(NKB_FULL, d, k);
-        CSum cs = {0.f, 0.f};
-        if (coord) csum_addp(cs, d, ms);
-        const float ic = warp_csum_total(cs);
-        if (ic > 0.f && isfinite(ic)) {
-            if (l < (uint32_t)KN) dvec[l] = d;
-            __syncwarp();
-            row_steps(e, tile, b, dvec);
-            const float alpha = search_line(e, tile, b, -ic, ic);
-            if (alpha > 0.f) { u = fmaf(alpha, d, u); apply_moves(e, tile, b, alpha); }
-        }
-    }
     bool failure = false;
     float primal = FLT_MAX;
-    for (uint32_t step = 0u; step < kNewtonSteps; ++step) {
-        // ---- assemble H (row l in registers) and g ----
-        float hrow[KN];
-        const float diff = u - fr;
-        const float part = diff - u;
-        const float diff_err = (u - (diff - part)) + (-fr - part);
-        CSum inertial = {0.f, 0.f};
-        float scale = 0.f, diag = 0.f;
-#pragma unroll
-        for (int k = 0; k < KN; ++k) {
-            const float hi = __shfl_sync(NKB_FULL, diff, k), lo = __shfl_sync(NKB_FULL, diff_err, k);
-            hrow[k] = mrow[k];
-            csum_addp(inertial, mrow[k], hi);
-            csum_addp(inertial, mrow[k], lo);
-            scale += fabsf(mrow[k]) * fabsf(hi);
-        }
-        CSum g = {-inertial.value, -inertial.error};
-        for (uint32_t chunk = ib; chunk < ie; chunk += 32u) {
-            const bool listed = chunk + l < ie;
-            const uint32_t own = listed ? inc[chunk + l] : 0u;
-            V3 f = mk3(0.f, 0.f, 0.f), noise = f;
-            float cxx = 0.f, cyy = 0.f, czz = 0.f, cyz = 0.f;
-            uint32_t unit = 0xffffffffu, side = 0u, axes = 1u;
-            float unitv = 0.f;
-            if (listed) {
-                const V3 move = hf3(e, HF_MOVE, own), res = hf3(e, HF_RES, own);
-                head_response(e, own, move, f, cxx, cyy, czz, cyz);
-                noise = mk3(fabsf(f.x) + cxx * (fabsf(res.x) + fabsf(move.x)), fabsf(f.y) + cyy * (fabsf(res.y) + fabsf(move.y)),
-                            fabsf(f.z) + czz * (fabsf(res.z) + fabsf(move.z)));
-                side = head_owner(e, own, 0u) == b ? 0u : 1u;
-                axes = head_axes(e, own);
-                const uint32_t jo = hu(e, HF_JOFF, own);
-                if (b == t.B && (jo & kUnitRow)) { unit = jo & 0xffffu; unitv = hf(e, HF_UNITV, own); }
+    tick(e, 15);
+    // step -1 (first velocity sweep only) is the line search toward the free velocity; steps >= 0 are Newton steps
+    for (int step = (tile.iteration == 0u && !position) ? -1 : 0; step < (int)kNewtonSteps; ++step) {
+        float d = 0.f, force = 0.f, inertia = 0.f;
+        if (step < 0) {
+            d = coord ? fr - u : 0.f;
+        } else {
+            // ---- lane = head: responses at the current moves, published to shared memory ----
+            uint32_t dense_any = 0u;
+            for (uint32_t k = ib + l; k < ie; k += 32u) {
+                const uint32_t h = inc[k];
+                const HeadRegs r = load_head(e, h);
+                V3 f; float cxx, cyy, czz, cyz;
+                respond(r, r.move, f, cxx, cyy, czz, cyz);
+                const V3 noise = mk3(fabsf(f.x) + cxx * (fabsf(r.res.x) + fabsf(r.move.x)), fabsf(f.y) + cyy * (fabsf(r.res.y) + fabsf(r.move.y)),
+                                     fabsf(f.z) + czz * (fabsf(r.res.z) + fabsf(r.move.z)));
+                hst3(e, HF_F, h, f); hst3(e, HF_NZ, h, noise);
+                hf(e, HF_C, h) = cxx; hf(e, HF_C + 1u, h) = cyy; hf(e, HF_C + 2u, h) = czz; hf(e, HF_C + 3u, h) = cyz;
+                const bool contributes = f.x != 0.f || f.y != 0.f || f.z != 0.f || cxx != 0.f || cyy != 0.f || czz != 0.f || cyz != 0.f ||
+                                         noise.x != 0.f || noise.y != 0.f || noise.z != 0.f;
+                const bool unit = artic && (hu(e, HF_JOFF, h) & kUnitRow) != 0u;
+                dense_any |= (contributes && !unit) ? 1u : 0u;
             }
-            const bool contributes = listed && (f.x != 0.f || f.y != 0.f || f.z != 0.f || cxx != 0.f || cyy != 0.f || czz != 0.f || cyz != 0.f ||
-                                                noise.x != 0.f || noise.y != 0.f || noise.z != 0.f);
-            for (uint32_t pending = __ballot_sync(NKB_FULL, contributes && unit != 0xffffffffu); pending != 0u; pending &= pending - 1u) {
-                const int src = __ffs(pending) - 1;
-                const uint32_t target = __shfl_sync(NKB_FULL, unit, src);
-                const float v = __shfl_sync(NKB_FULL, unitv, src), fx = __shfl_sync(NKB_FULL, f.x, src);
-                const float c0 = __shfl_sync(NKB_FULL, cxx, src), nx = __shfl_sync(NKB_FULL, noise.x, src);
-                if (l == target) { diag += v * c0 * v; csum_addp(g, v, fx); scale += fabsf(v) * nx; }
+            // ---- lane = coordinate: inertial part of H (row l) and g ----
+            const float diff = u - fr;
+            const float part = diff - u;
+            const float diff_err = (u - (diff - part)) + (-fr - part);
+            hi_v[l] = diff; lo_v[l] = diff_err; u_v[l] = u;
+            __syncwarp();
+            CSum inertial = {0.f, 0.f};
+            float scale = 0.f, diag = 0.f;
+            if (coord) for (uint32_t c = 0u; c < chunks; ++c) {
+                const float4 m = Mr4[c], hi = reinterpret_cast<const float4*>(hi_v)[c], lo = reinterpret_cast<const float4*>(lo_v)[c];
+                Hr4[c] = m;
+                csum_addp(inertial, m.x, hi.x); inertial.error = fmaf(m.x, lo.x, inertial.error);
+                csum_addp(inertial, m.y, hi.y); inertial.error = fmaf(m.y, lo.y, inertial.error);
+                csum_addp(inertial, m.z, hi.z); inertial.error = fmaf(m.z, lo.z, inertial.error);
+                csum_addp(inertial, m.w, hi.w); inertial.error = fmaf(m.w, lo.w, inertial.error);
+                scale += fabsf(m.x) * fabsf(hi.x) + fabsf(m.y) * fabsf(hi.y) + fabsf(m.z) * fabsf(hi.z) + fabsf(m.w) * fabsf(hi.w);
             }
-            for (uint32_t pending = __ballot_sync(NKB_FULL, contributes && unit == 0xffffffffu); pending != 0u; pending &= pending - 1u) {
-                const int src = __ffs(pending) - 1;
-                const uint32_t hs = __shfl_sync(NKB_FULL, own, src), ss = __shfl_sync(NKB_FULL, side, src), as = __shfl_sync(NKB_FULL, axes, src);
-                const float fx = __shfl_sync(NKB_FULL, f.x, src), c0 = __shfl_sync(NKB_FULL, cxx, src), nx = __shfl_sync(NKB_FULL, noise.x, src);
-                const float j0 = coord ? head_jac(e, hs, ss, 0u, l, b) : 0.f;
-                csum_addp(g, j0, fx);
-                scale += fabsf(j0) * nx;
-                if (as == 1u) {
-                    const float a0 = j0 * c0;
-#pragma unroll
-                    for (int k = 0; k < KN; ++k) hrow[k] += a0 * __shfl_sync(NKB_FULL, j0, k);
-                    continue;
+            CSum g = {-inertial.value, -inertial.error};
+            tick(e, 16);
+            // rows on a single coordinate only touch that coordinate (block_descent_tile.cuh:1555-1568)
+            if (artic) {
+                const uint32_t* utab = unit_table(e, nb);
+                for (uint32_t slot = 0u; slot < 4u; ++slot) {
+                    const uint32_t h = utab[slot * 32u + l];
+                    if (h == 0xffffffffu) continue;
+                    const float v = hf(e, HF_UNITV, h);
+                    diag += v * hf(e, HF_C, h) * v;
+                    csum_addp(g, v, hf(e, HF_F, h));
+                    scale += fabsf(v) * hf(e, HF_NZ, h);
                 }
-                const float fy = __shfl_sync(NKB_FULL, f.y, src), fz = __shfl_sync(NKB_FULL, f.z, src);
-                const float c1 = __shfl_sync(NKB_FULL, cyy, src), c2 = __shfl_sync(NKB_FULL, czz, src), c12 = __shfl_sync(NKB_FULL, cyz, src);
-                const float ny = __shfl_sync(NKB_FULL, noise.y, src), nz = __shfl_sync(NKB_FULL, noise.z, src);
-                const float j1 = coord ? head_jac(e, hs, ss, 1u, l, b) : 0.f, j2 = coord ? head_jac(e, hs, ss, 2u, l, b) : 0.f;
-                csum_addp(g, j1, fy); csum_addp(g, j2, fz);
-                scale += fabsf(j1) * ny + fabsf(j2) * nz;
+            }
+            // dense rows: H += J^T C J, g += J^T f, one head at a time with its values broadcast from shared memory
+            if (__any_sync(NKB_FULL, dense_any != 0u)) for (uint32_t k = ib; k < ie; ++k) {
+                const uint32_t hs = inc[k];
+                const uint32_t jo = hu(e, HF_JOFF, hs);
+                if (artic && (jo & kUnitRow)) continue;
+                const V3 f = hf3(e, HF_F, hs), nz = hf3(e, HF_NZ, hs);
+                const float c0 = hf(e, HF_C, hs), c1 = hf(e, HF_C + 1u, hs), c2 = hf(e, HF_C + 2u, hs), c12 = hf(e, HF_C + 3u, hs);
+                if (!(f.x != 0.f || f.y != 0.f || f.z != 0.f || c0 != 0.f || c1 != 0.f || c2 != 0.f || c12 != 0.f || nz.x != 0.f || nz.y != 0.f || nz.z != 0.f)) continue;
+                const float* jr; uint32_t js;
+                if (artic) { jr = sm_jpool(e) + jo; js = chunks << 2; }
+                else {
+                    const uint32_t ss = head_owner(e, hs, 0u) == b ? 0u : 1u, as = head_axes(e, hs);
+                    __syncwarp();
+                    if (l < 6u) for (uint32_t ax = 0u; ax < 3u; ++ax) jscr[ax * 8u + l] = ax < as ? head_jac(e, hs, ss, ax, l, b) : 0.f;
+                    __syncwarp();
+                    jr = jscr; js = 8u;
+                }
+                const float j0 = coord ? jr[l] : 0.f, j1 = coord ? jr[js + l] : 0.f, j2 = coord ? jr[2u * js + l] : 0.f;
+                csum_addp(g, j0, f.x); csum_addp(g, j1, f.y); csum_addp(g, j2, f.z);
+                scale += fabsf(j0) * nz.x + fabsf(j1) * nz.y + fabsf(j2) * nz.z;
                 const float a0 = j0 * c0, a1 = j1 * c1 + j2 * c12, a2 = j2 * c2 + j1 * c12;
-#pragma unroll
-                for (int k = 0; k < KN; ++k)
-                    hrow[k] += a0 * __shfl_sync(NKB_FULL, j0, k) + a1 * __shfl_sync(NKB_FULL, j1, k) + a2 * __shfl_sync(NKB_FULL, j2, k);
+                if (coord) {
+                    const float4* r0 = reinterpret_cast<const float4*>(jr);
+                    const float4* r1 = reinterpret_cast<const float4*>(jr + js);
+                    const float4* r2 = reinterpret_cast<const float4*>(jr + 2u * js);
+                    for (uint32_t c = 0u; c < chunks; ++c) {
+                        float4 h4 = Hr4[c];
+                        const float4 x = r0[c], y = r1[c], z = r2[c];
+                        h4.x += a0 * x.x + a1 * y.x + a2 * z.x;
+                        h4.y += a0 * x.y + a1 * y.y + a2 * z.y;
+                        h4.z += a0 * x.z + a1 * y.z + a2 * z.z;
+                        h4.w += a0 * x.w + a1 * y.w + a2 * z.w;
+                        Hr4[c] = h4;
+                    }
+                }
             }
-        }
-        if (e.cyc != nullptr && l == 0u) { const long long now = clock64(); e.cyc[16] += (uint32_t)(now - e.t0); }
-        float force = 0.f, inertia = 0.f;
-        bool finite = true;
-#pragma unroll
-        for (int k = 0; k < KN; ++k) {
-            if ((uint32_t)k == l) hrow[k] += diag;
-            finite &= isfinite(hrow[k]);
-            scale += fabsf(hrow[k]) * fabsf(__shfl_sync(NKB_FULL, u, k));
-        }
-        if (coord) { force = g.value + g.error; inertia = inertial.value + inertial.error; }
-        finite &= isfinite(force);
-        if (!__all_sync(NKB_FULL, finite)) { failure = true; break; }
-        bool converged = __all_sync(NKB_FULL, !coord || fabsf(force) <= kRoundings * FLT_EPSILON * scale);
-        float d = 0.f;
-        if (converged && tile.tol > 0.f) {
-            d = solve_block_mass(e, b, force);
-            converged = __all_sync(NKB_FULL, !coord || fabsf(d) < tile.tol);
-        }
-        if (converged) { primal = 0.f; break; }
-        // ---- Cholesky in registers: lane l keeps row l of L (block_descent_tile.cuh:1623-1641) ----
-        bool valid = true;
-        float inverse = 0.f;
-#pragma unroll
-        for (int k = 0; k < KN; ++k) {
-            if ((uint32_t)k >= dim) break;
-            float value = hrow[k];
-#pragma unroll
-            for (int j = 0; j < k; ++j) value -= hrow[j] * __shfl_sync(NKB_FULL, hrow[j], k);
-            const float pivot = __shfl_sync(NKB_FULL, value, k);
-            valid &= pivot > 0.f && pivot <= FLT_MAX;
-            const float root = sqrtf(valid ? pivot : 1.0f), sc = 1.0f / root;
-            hrow[k] = l == (uint32_t)k ? root : value * sc;
-            inverse = l == (uint32_t)k ? sc : inverse;
-        }
-        if (!valid) { failure = true; break; }
-        // ---- d = H^-1 g ----
-        {
-            float* Lt = sm_chol(e);
-            constexpr int kS = KN + 1;
+            tick(e, 17);
+            bool finite = true;
+            if (coord) {
+                Hr[l] += diag;
+                for (uint32_t c = 0u; c < chunks; ++c) {
+                    const float4 v = Hr4[c], uu = reinterpret_cast<const float4*>(u_v)[c];
+                    finite &= isfinite(v.x) && isfinite(v.y) && isfinite(v.z) && isfinite(v.w);
+                    scale += fabsf(v.x) * fabsf(uu.x) + fabsf(v.y) * fabsf(uu.y) + fabsf(v.z) * fabsf(uu.z) + fabsf(v.w) * fabsf(uu.w);
+                }
+                force = g.value + g.error; inertia = inertial.value + inertial.error;
+            }
+            finite &= isfinite(force);
+            if (!__all_sync(NKB_FULL, finite)) { failure = true; break; }
+            bool converged = __all_sync(NKB_FULL, !coord || fabsf(force) <= kRoundings * FLT_EPSILON * scale);
+            if (converged && tile.tol > 0.f) {
+                d = solve_block_mass(e, b, force);
+                converged = __all_sync(NKB_FULL, !coord || fabsf(d) < tile.tol);
+            }
+            if (converged) { primal = 0.f; break; }
+            tick(e, 18);
+            // ---- Cholesky, row l of L over row l of H (block_descent_tile.cuh:1623-1641) ----
+            bool valid = true;
+            float inverse = 0.f;
+            __syncwarp();
+            for (uint32_t k = 0u; k < dim; ++k) {
+                float value = 0.f;
+                if (coord && l >= k) {
+                    const float4* Hk4 = reinterpret_cast<const float4*>(H + k * ldh);
+                    const uint32_t full = k >> 2;
+                    float s0 = 0.f, s1 = 0.f;
+                    for (uint32_t c = 0u; c < full; ++c) {
+                        const float4 a = Hr4[c], bb = Hk4[c];
+                        s0 = fmaf(a.x, bb.x, s0); s1 = fmaf(a.y, bb.y, s1); s0 = fmaf(a.z, bb.z, s0); s1 = fmaf(a.w, bb.w, s1);
+                    }
+                    const float4 a = Hr4[full], bb = Hk4[full];
+                    const uint32_t rem = k & 3u;
+                    if (rem > 0u) s0 = fmaf(a.x, bb.x, s0);
+                    if (rem > 1u) s1 = fmaf(a.y, bb.y, s1);
+                    if (rem > 2u) s0 = fmaf(a.z, bb.z, s0);
+                    value = Hr[k] - (s0 + s1);
+                }
+                const float pivot = __shfl_sync(NKB_FULL, value, k);
+                valid &= pivot > 0.f && pivot <= FLT_MAX;
+                const float sc = rsqrtf(valid ? pivot : 1.0f), root = pivot * sc;
+                if (coord && l >= k) Hr[k] = l == k ? root : value * sc;
+                inverse = l == k ? sc : inverse;
+                __syncwarp();
+            }
+            if (!valid) { failure = true; break; }
+            tick(e, 19);
+            // ---- d = H^-1 g ----
             float r = force;
-#pragma unroll
-            for (int j = 0; j < KN; ++j) {
-                if ((uint32_t)j >= dim) break;
+            for (uint32_t j = 0u; j < dim; ++j) {
                 const float y = __shfl_sync(NKB_FULL, r * inverse, j);
-                r = l == (uint32_t)j ? y : (l > (uint32_t)j ? fmaf(-hrow[j], y, r) : r);
-                if (l > (uint32_t)j && l < (uint32_t)KN) Lt[j * kS + l] = hrow[j];
+                r = l == j ? y : ((coord && l > j) ? fmaf(-Hr[j], y, r) : r);
             }
-            __syncwarp();
-#pragma unroll
-            for (int k = KN; k > 0; --k) {
-                if ((uint32_t)k > dim) continue;
-                const int j = k - 1;
+            for (uint32_t jj = dim; jj > 0u; --jj) {
+                const uint32_t j = jj - 1u;
                 const float x = __shfl_sync(NKB_FULL, r * inverse, j);
-                const float lv = l < (uint32_t)j ? Lt[l * kS + j] : 0.f;
-                r = l == (uint32_t)j ? x : fmaf(-lv, x, r);
+                r = l == j ? x : (l < j ? fmaf(-H[j * ldh + l], x, r) : r);
             }
-            __syncwarp();
             d = coord ? r : 0.f;
         }
+        // ---- curvature and slopes along d ----
+        __syncwarp();
+        dvec[l] = d;
+        __syncwarp();
         float ms = 0.f;
-#pragma unroll
-        for (int k = 0; k < KN; ++k) ms += mrow[k] * __shfl_sync(NKB_FULL, d, k);
+        if (coord) for (uint32_t c = 0u; c < chunks; ++c) {
+            const float4 m = Mr4[c], dd = reinterpret_cast<const float4*>(dvec)[c];
+            ms = fmaf(m.x, dd.x, ms); ms = fmaf(m.y, dd.y, ms); ms = fmaf(m.z, dd.z, ms); ms = fmaf(m.w, dd.w, ms);
+        }
         CSum dec = {0.f, 0.f}, slo = {0.f, 0.f}, cur = {0.f, 0.f};
         if (coord) { csum_addp(dec, force, d); csum_addp(slo, inertia, d); csum_addp(cur, d, ms); }
-        const float total_dec = warp_csum_total(dec), islope = warp_csum_total(slo), icurv = warp_csum_total(cur);
-        if (!isfinite(total_dec) || !isfinite(islope) || !isfinite(icurv)) { failure = true; break; }
-        if (!(total_dec > 0.f)) break;
-        if (l < (uint32_t)KN) dvec[l] = d;
-        __syncwarp();
+        const float icurv = warp_csum_total(cur);
+        float islope;
+        if (step < 0) {
+            if (!(icurv > 0.f && isfinite(icurv))) continue;
+            islope = -icurv;
+        } else {
+            const float total_dec = warp_csum_total(dec);
+            islope = warp_csum_total(slo);
+            if (!isfinite(total_dec) || !isfinite(islope) || !isfinite(icurv)) { failure = true; break; }
+            if (!(total_dec > 0.f)) break;
+        }
+        tick(e, 20);
         row_steps(e, tile, b, dvec);
+        tick(e, 21);
         const float alpha = search_line(e, tile, b, islope, icurv);
+        tick(e, 22);
+        if (e.cyc != nullptr && l == 0u) e.cyc[23] += 1u;
+        if (step < 0) {
+            if (alpha > 0.f) { u = fmaf(alpha, d, u); apply_moves(e, tile, b, alpha); }
+            continue;
+        }
         const float after = fmaf(alpha, d, u);
         const bool fin = __all_sync(NKB_FULL, !coord || isfinite(after));
         const bool rounded = __all_sync(NKB_FULL, !coord || after == u);
@@ -501,19 +614,17 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     __syncwarp();
 }
 
-template <int KN>
+// Blocks descend colour by colour, blocks of one colour in index order (block_descent_tile.cuh:2749-2820).
 NKB_DEV void descend_blocks(Env& e, Tile& tile, bool position) {
-    const uint32_t nb = tile.nblocks, B = e.t->B;
-    for (uint32_t color = 0u; color < 32u; ++color) {
-        bool any = false;
+    const uint32_t nb = tile.nblocks;
+    uint32_t remaining = 0u;
+    for (uint32_t b = 0u; b < nb; ++b) remaining += blk_color(e, nb, b) != 0xffffffffu ? 1u : 0u;
+    for (uint32_t color = 0u; color < 32u && remaining != 0u; ++color)
         for (uint32_t b = 0u; b < nb; ++b) {
             if (blk_color(e, nb, b) != color) continue;
-            any = true;
-            if (b < B) descend_block<8>(e, tile, b, position);
-            else descend_block<KN>(e, tile, b, position);
+            --remaining;
+            descend_block(e, tile, b, position);
         }
-        if (!any && color > 0u) { bool later = false; for (uint32_t b = 0u; b < nb; ++b) later |= blk_color(e, nb, b) != 0xffffffffu && blk_color(e, nb, b) > color; if (!later) break; }
-    }
 }
 
 struct DualMomentum { float t, beta; };
@@ -626,14 +737,12 @@ NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
 
 // The whole constraint solve of one env.  On entry the heads are built, the articulation's post-dynamics
 // velocity is in (e.qd, sm_vel(root)) and free-body velocities are in sm_bvel.
-template <int KN>
 NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
     const TemplateView& t = *e.t;
     const uint32_t l = e.lane, B = t.B, n = t.ndof;
     Tile tile;
     tile.nheads = nheads; tile.nblocks = B + (n != 0u ? 1u : 0u); tile.iteration = 0u;
     tile.momentum = tile.residual = 0.f; tile.tol = t.cfg.velocity_tolerance;
-    const uint32_t nb = tile.nblocks;
     // rigid blocks: free velocity, mass, carried constraint velocity (block_descent_rigid.cuh:4-48)
     for (uint32_t b = l; b < B; b += 32u) {
         float* bv = sm_bvel(e, b);
@@ -682,113 +791,123 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
     __syncwarp();
     init_heads(e, tile);
     tick(e, 8);
-    index_blocks(e, tile, true);
-    init_residuals(e, tile);
-    tick(e, 9);
     float rows[3] = {0.f, 0.f, 0.f};
     float cls[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t sweeps = 0u;
+    uint32_t sweeps = 0u, positions = 0u, pushes = 0u;
     DualMomentum mom = {1.0f, 0.0f};
     const uint32_t iterations = t.cfg.vel_iters;
-    while (sweeps < iterations) {
-        tile.iteration = sweeps++;
-        tile.momentum = 0.f; tile.residual = 0.f;
-        descend_blocks<KN>(e, tile, false);
-        tick(e, 10);
-        update_duals(e, tile, &mom, true, true, rows);
-        if (sweeps == iterations || fmaxf(fmaxf(rows[0], rows[1]), fmaxf(rows[2], tile.residual)) < tile.tol) measure_primals(e, tile, false);
-        if (fmaxf(fmaxf(rows[0], rows[1]), rows[2]) < tile.tol && tile.residual >= tile.tol && tile.residual < FLT_MAX) {
-            measure_primals(e, tile, true);
-            if (tile.residual < FLT_MAX) {
+    // One loop drives the velocity sweeps, the hand-over and the split-impulse position sweeps so that each of
+    // the large pieces (block indexing, block descent, dual update, momentum balance) is instantiated once.
+    enum { kPhaseVelocity, kPhaseHandOver, kPhasePosition, kPhaseDone };
+    int phase = kPhaseVelocity;
+    bool reindex = true;
+    while (phase != kPhaseDone) {
+        if (reindex) {
+            index_blocks(e, tile, phase == kPhaseVelocity);
+            reindex = false;
+            if (phase == kPhaseVelocity) { init_residuals(e, tile); tick(e, 9); if (iterations == 0u) phase = kPhaseHandOver; }
+        }
+        if (phase == kPhaseHandOver) {
+            if (l < 4u) e.s->solver_residual[(size_t)e.env * 4u + l] = cls[l];
+            if (l == 0u) e.s->solver_sweeps[e.env] = sweeps;
+            // velocities back to the links, carried velocities to global memory
+            if (n != 0u) {
+                const float* U = sm_vec(e, kVecU);
+                if (l < n) {
+                    e.s->carry_artic[(size_t)e.env * n + l] = U[l] - sm_vec(e, kVecFree)[l];
+                    if (e.dof_comp != kNoLink) sm_vel(e, e.dof_link)[e.dof_comp] = U[l];
+                }
+                if (l < t.L && joint_dofs(e.jtype) == 1u) e.qd = U[e.link_dof];
+            }
+            for (uint32_t b = l; b < B; b += 32u) {
+                float* carry = e.s->carry_rigid + ((size_t)e.env * B + b) * 6u;
+                const float* bv = sm_bvel(e, b);
+                const float* bf = sm_bfree(e, b);
+#pragma unroll
+                for (int k = 0; k < 6; ++k) carry[k] = blk_dim(e, b) != 0u ? bv[k] - bf[k] : 0.f;
+            }
+            __syncwarp();
+            phase = kPhaseDone;
+            // split-impulse position pass: every head becomes a scalar push-out row (ops/block_descent.cu:1734-1753)
+            if (t.cfg.pos_iters != 0u && nheads != 0u) {
+                bool push = false, coupled = false;
+                for (uint32_t h = l; h < nheads; h += 32u) {
+                    const uint32_t fl = hu(e, HF_FLAGS, h);
+                    const bool spec = (fl & kHeadSpeculative) != 0u;
+                    const float slop = spec ? 0.f : t.cfg.pos_slop;
+                    const float pen_row = hf(e, HF_PEN, h);
+                    const bool active = (fl & kHeadVelocityOnly) == 0u && (spec || pen_row > slop || hf(e, HF_DUAL, h) != 0.f);
+                    float bias = 0.f, rounding = 0.f;
+                    if (active) {
+                        const float penetration = fmaxf(pen_row - slop, 0.f);
+                        if (spec) {
+                            const float cd = sm_cdepth(e)[hu(e, HF_REF, h) & 0xffffu];
+                            const double depth = (double)cd - slop, reserve = (double)pen_row - cd;
+                            const double correction = t.cfg.pos_beta * fmax(depth, 0.0) + reserve;
+                            const double target = fmin(depth, 0.0) + correction;
+                            double velocity = 0.0;
+                            for (uint32_t side = 0u; side < 2u; ++side) {
+                                const uint32_t b = head_owner(e, h, side);
+                                if (b == kNoBlock16) continue;
+                                const uint32_t dim = blk_dim(e, b);
+                                const float* u = block_vel(e, b, false);
+                                double v = 0.0;
+                                for (uint32_t i = 0u; i < dim; ++i) v += (double)head_jac(e, h, side, 0u, i, b) * u[i];
+                                velocity += v;
+                            }
+                            const double limit = fmin(correction / t.cfg.dt, (double)t.cfg.baumgarte_max_velocity);
+                            bias = (float)fmin(target / t.cfg.dt - velocity, limit);
+                            rounding = (float)(target > 0.0 ? 0.0 : fmax(reserve, 0.0) / t.cfg.dt);
+                        } else {
+                            bias = fminf(t.cfg.pos_beta * penetration / t.cfg.dt, t.cfg.baumgarte_max_velocity);
+                        }
+                    } else hu(e, HF_OWNER, h) = kNoBlock16 | (kNoBlock16 << 16);
+                    const uint32_t o = hu(e, HF_OWNER, h);
+                    coupled |= (o & 0xffffu) != kNoBlock16 && (o >> 16) != kNoBlock16;
+                    hu(e, HF_FLAGS, h) = fl | kHeadScalar;
+                    hf(e, HF_LOWER, h) = 0.f; hf(e, HF_UPPER, h) = FLT_MAX;
+                    const Resp rs = scalar_response(hf(e, HF_RHO, h), 0.f);
+                    hf(e, HF_RSD, h) = rs.dual_scale; hf(e, HF_RSR, h) = rs.residual_scale;
+                    hst3(e, HF_RES, h, mk3(bias, 0.f, 0.f));
+                    hst3(e, HF_DUAL, h, mk3(0.f, 0.f, 0.f));
+                    push |= bias > rounding;
+                }
+                push = __any_sync(NKB_FULL, push); coupled = __any_sync(NKB_FULL, coupled);
+                __syncwarp();
+                if (push) { phase = kPhasePosition; reindex = true; positions = coupled ? t.cfg.pos_iters : 1u; pushes = 0u; }
+            }
+            continue;
+        }
+        if (phase == kPhaseVelocity) { tile.iteration = sweeps++; tile.momentum = 0.f; tile.residual = 0.f; }
+        else tile.iteration = sweeps + pushes;
+        descend_blocks(e, tile, phase == kPhasePosition);
+        if (phase == kPhasePosition) {
+            if (++pushes >= positions) { phase = kPhaseDone; continue; }
+        } else tick(e, 10);
+        update_duals(e, tile, phase == kPhaseVelocity ? &mom : nullptr, phase == kPhaseVelocity, true, rows);
+        if (phase == kPhasePosition) continue;
+        // momentum balance: plain measure, reconstruction when only the primal lags, re-measure after it
+        for (int stage = 0; stage < 3; ++stage) {
+            const float worst_row = fmaxf(fmaxf(rows[0], rows[1]), rows[2]);
+            bool run = true;
+            if (stage == 0) run = sweeps == iterations || fmaxf(worst_row, tile.residual) < tile.tol;
+            else if (stage == 1) run = worst_row < tile.tol && tile.residual >= tile.tol && tile.residual < FLT_MAX;
+            if (stage == 1 && !run) break;
+            if (run) measure_primals(e, tile, stage == 1);
+            if (stage == 1) {
+                if (!(tile.residual < FLT_MAX)) break;
                 init_residuals(e, tile);
                 update_duals(e, tile, nullptr, true, false, rows);
                 tile.residual = 0.f;
-                measure_primals(e, tile, false);
             }
         }
         cls[0] = rows[0]; cls[1] = rows[1]; cls[2] = rows[2]; cls[3] = tile.residual;
         const float largest = fmaxf(fmaxf(rows[0], rows[1]), fmaxf(rows[2], tile.residual));
         tick(e, 11);
-        if (largest < tile.tol || largest == FLT_MAX) break;
-    }
-    if (l < 4u) e.s->solver_residual[(size_t)e.env * 4u + l] = cls[l];
-    if (l == 0u) e.s->solver_sweeps[e.env] = sweeps;
-    // finish: velocities back to the links, carried velocities to global memory
-    if (n != 0u) {
-        const float* U = sm_vec(e, kVecU);
-        if (l < n) {
-            e.s->carry_artic[(size_t)e.env * n + l] = U[l] - sm_vec(e, kVecFree)[l];
-            if (e.dof_comp != kNoLink) sm_vel(e, e.dof_link)[e.dof_comp] = U[l];
-        }
-        if (l < t.L && joint_dofs(e.jtype) == 1u) e.qd = U[e.link_dof];
-    }
-    for (uint32_t b = l; b < B; b += 32u) {
-        float* carry = e.s->carry_rigid + ((size_t)e.env * B + b) * 6u;
-        const float* bv = sm_bvel(e, b);
-        const float* bf = sm_bfree(e, b);
-#pragma unroll
-        for (int k = 0; k < 6; ++k) carry[k] = blk_dim(e, b) != 0u ? bv[k] - bf[k] : 0.f;
-    }
-    __syncwarp();
-    // split-impulse position pass
-    if (t.cfg.pos_iters != 0u && nheads != 0u) {
-        bool push = false, coupled = false;
-        for (uint32_t h = l; h < nheads; h += 32u) {
-            const uint32_t fl = hu(e, HF_FLAGS, h);
-            const bool spec = (fl & kHeadSpeculative) != 0u;
-            const float slop = spec ? 0.f : t.cfg.pos_slop;
-            const float pen_row = hf(e, HF_PEN, h);
-            const bool position = (fl & kHeadVelocityOnly) == 0u && (spec || pen_row > slop || hf(e, HF_DUAL, h) != 0.f);
-            float bias = 0.f, rounding = 0.f;
-            if (position) {
-                const float penetration = fmaxf(pen_row - slop, 0.f);
-                if (spec) {
-                    const float cd = sm_cdepth(e)[hu(e, HF_REF, h) & 0xffffu];
-                    const double depth = (double)cd - slop, reserve = (double)pen_row - cd;
-                    const double correction = t.cfg.pos_beta * fmax(depth, 0.0) + reserve;
-                    const double target = fmin(depth, 0.0) + correction;
-                    double velocity = 0.0;
-                    for (uint32_t side = 0u; side < 2u; ++side) {
-                        const uint32_t b = head_owner(e, h, side);
-                        if (b == kNoBlock16) continue;
-                        const uint32_t dim = blk_dim(e, b);
-                        const float* u = block_vel(e, b, false);
-                        double v = 0.0;
-                        for (uint32_t i = 0u; i < dim; ++i) v += (double)head_jac(e, h, side, 0u, i, b) * u[i];
-                        velocity += v;
-                    }
-                    const double limit = fmin(correction / t.cfg.dt, (double)t.cfg.baumgarte_max_velocity);
-                    bias = (float)fmin(target / t.cfg.dt - velocity, limit);
-                    rounding = (float)(target > 0.0 ? 0.0 : fmax(reserve, 0.0) / t.cfg.dt);
-                } else {
-                    bias = fminf(t.cfg.pos_beta * penetration / t.cfg.dt, t.cfg.baumgarte_max_velocity);
-                }
-            } else hu(e, HF_OWNER, h) = kNoBlock16 | (kNoBlock16 << 16);
-            const uint32_t o = hu(e, HF_OWNER, h);
-            coupled |= (o & 0xffffu) != kNoBlock16 && (o >> 16) != kNoBlock16;
-            hu(e, HF_FLAGS, h) = fl | kHeadScalar;
-            hf(e, HF_LOWER, h) = 0.f; hf(e, HF_UPPER, h) = FLT_MAX;
-            const Resp rs = scalar_response(hf(e, HF_RHO, h), 0.f);
-            hf(e, HF_RSD, h) = rs.dual_scale; hf(e, HF_RSR, h) = rs.residual_scale;
-            hst3(e, HF_RES, h, mk3(bias, 0.f, 0.f));
-            hst3(e, HF_DUAL, h, mk3(0.f, 0.f, 0.f));
-            push |= bias > rounding;
-        }
-        push = __any_sync(NKB_FULL, push); coupled = __any_sync(NKB_FULL, coupled);
-        __syncwarp();
-        if (push) {
-            index_blocks(e, tile, false);
-            const uint32_t positions = coupled ? t.cfg.pos_iters : 1u;
-            for (uint32_t it = 0u; it < positions; ++it) {
-                tile.iteration = sweeps + it;
-                descend_blocks<KN>(e, tile, true);
-                if (it + 1u < positions) update_duals(e, tile, nullptr, false, true, rows);
-            }
-        }
+        if (sweeps >= iterations || largest < tile.tol || largest == FLT_MAX) phase = kPhaseHandOver;
     }
     tick(e, 14);
     if (e.s->dbg_qdot_pseudo != nullptr && l < n) e.s->dbg_qdot_pseudo[(size_t)e.env * n + l] = sm_vec(e, kVecPseudo)[l];
-    (void)nb;
 }
 
 }  // namespace nkb

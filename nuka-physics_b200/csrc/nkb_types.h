@@ -24,7 +24,7 @@ enum : uint32_t { kStatusPairOverflow = 1u << 0, kStatusDofOverflow = 1u << 2, k
 enum : uint32_t { kHeadContact = 1u << 0, kHeadContactNormal = 1u << 1, kHeadSpeculative = 1u << 2,
                   kHeadVelocityOnly = 1u << 3, kHeadDrive = 1u << 4, kHeadLimit = 1u << 5, kHeadFriction = 1u << 6,
                   kHeadScalar = 1u << 7 /* position pass: only the normal axis */ };
-constexpr uint32_t kHeadWords = 54u;    // words of shared memory per solver head
+constexpr uint32_t kHeadWords = 64u;    // words of shared memory per solver head
 
 struct Config {
     float dt;
@@ -95,7 +95,7 @@ struct SmemLayout {
     uint32_t mass, factor, vecs;                                // articulation
     uint32_t bpose, bvel, bwinv, aabb, bmass, bfree, bpseudo;   // bodies
     uint32_t pairs, ccount, cpoint, cnormal, cdepth, cfeat;     // contacts (cfeat also stages the cache rebuild)
-    uint32_t heads, jpool, binfo, chol;                         // solver
+    uint32_t heads, jpool, binfo, chol, bm6;                    // solver (chol: Newton matrix; bm6: rigid block mass + head rows)
     uint32_t words;                                             // total per env
     uint32_t ld;                                                // leading dimension of mass/factor (ndof | 1)
 };

@@ -224,21 +224,24 @@ void World::BuildLayout() {
     tv.head_cap = (tv.point_cap + t.joint_rows + 3u) & ~3u;
     if (tv.head_cap == 0u) tv.head_cap = 4u;
     uint32_t at = 0;
-    auto take = [&](uint32_t words) { const uint32_t o = at; at += (words + 1u) & ~1u; return o; };
-    s.ld = n | 1u;
+    auto take = [&](uint32_t words) { const uint32_t o = at; at += (words + 3u) & ~3u; return o; };     // 16-byte aligned regions
+    // float4-readable matrix rows: a multiple of 4 words that is 4 mod 8 (conflict-free for one lane per row)
+    auto pad_ld = [](uint32_t k) { const uint32_t ld = (k + 3u) & ~3u; return (ld & 7u) == 0u ? ld + 4u : ld; };
+    s.ld = pad_ld(n);
     s.pose = take(7 * L); s.xrot = take(9 * L); s.xtr = take(3 * L);
     s.vel = take(6 * L); s.vbias = take(6 * L); s.acc = take(6 * L); s.pbias = take(6 * L); s.ic = take(10 * L);
-    s.mass = take(n * s.ld); s.factor = take(n * s.ld); s.vecs = take(8 * 32);
+    s.mass = take(n * s.ld); s.factor = take(n * s.ld); s.vecs = take(12 * 32);
     s.bpose = take(7 * B); s.bvel = take(6 * B); s.bwinv = take(6 * B); s.aabb = take(6 * B);
     s.bmass = take(7 * B); s.bfree = take(6 * B); s.bpseudo = take(6 * B);
     s.pairs = take(S); s.ccount = take(S); s.cpoint = take(12 * S); s.cnormal = take(12 * S); s.cdepth = take(4 * S);
     s.cfeat = take(8 * S + 4 * S * 10 + 4 * S);   // feature words, cache staging entries, owner marks
     s.heads = take(kHeadWords * tv.head_cap);
-    s.jpool = take(tv.point_cap * 3u * n);
+    s.jpool = take(tv.point_cap * 3u * ((n + 3u) & ~3u));
     const uint32_t nb = B + (n ? 1u : 0u);
-    s.binfo = take(3 * nb + 1 + 2 * tv.head_cap);
-    const uint32_t kn = n <= 8 ? 8 : n <= 16 ? 16 : n <= 20 ? 20 : n <= 24 ? 24 : 32;
-    s.chol = take(kn * (kn + 1));
+    s.binfo = take(3 * nb + 1 + 2 * tv.head_cap + 4 * 32);
+    const uint32_t hn = std::max(n, 6u);
+    s.chol = take(hn * pad_ld(hn));
+    s.bm6 = take(72 + 24);
     s.words = at;
     const size_t bytes = static_cast<size_t>(s.words) * 4u;
     if (bytes > 220u * 1024u) throw Error(kNotSupported, "template needs more shared memory per env than one SM provides");

@@ -6,7 +6,6 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "libnuka_b200.so")
 SOURCES = ["nkb_kernels.cu", "nkb_world.cpp", "nkb_abi.cpp"]
-KN_BUCKETS = [8, 16, 20, 24, 32]      # nkb_kernels.cu is also compiled once per bucket with -DNKB_KN=<n>
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 
 
@@ -25,10 +24,9 @@ def build_native(force=False, verbose=False):
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     objects = []
     procs = []
-    units = [(src, None) for src in SOURCES] + [("nkb_kernels.cu", kn) for kn in KN_BUCKETS]
-    for src, kn in units:
-        obj = os.path.join(CSRC, src.rsplit(".", 1)[0] + (f"_kn{kn}.o" if kn else ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj] + ([f"-DNKB_KN={kn}"] if kn else [])
+    for src in SOURCES:
+        obj = os.path.join(CSRC, src.rsplit(".", 1)[0] + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
