@@ -84,6 +84,34 @@ NKB_DEV void tangent_impulse(V3 dual, float rho, float res_y, float res_z, float
     cyz = -cs * mu_y * mu_z * dy * dz;
 }
 
+// cone_argument at mu == 1: compensated dual + rho * residual, no divisions
+NKB_DEV float cone_argument_unit(float dual, float rho, float residual) {
+    const float t = __fmul_rn(rho, residual);
+    const float t_low = fmaf(rho, residual, -t);
+    const float sum = __fadd_rn(dual, t);
+    const float t_part = __fsub_rn(sum, dual);
+    const float sum_low = __fadd_rn(__fsub_rn(dual, __fsub_rn(sum, t_part)), __fsub_rn(t, t_part));
+    return __fadd_rn(sum, __fadd_rn(sum_low, t_low));
+}
+
+// tangent_impulse for one isotropic friction coefficient, as the row evaluations of the Newton loop use it:
+// the same cone projection without the per-axis scaling, with the direction normalised by a reciprocal square
+// root.  Invalid inputs propagate as NaN through the arithmetic.
+NKB_DEV void cone_impulse(V3 dual, float rho, float res_y, float res_z, float normal_impulse, float mu,
+                          float& iy, float& iz, float& cyy, float& czz, float& cyz) {
+    iy = iz = cyy = czz = cyz = 0.f;
+    if (rho <= 0.0f || mu <= 0.0f) return;
+    const float q_y = cone_argument_unit(dual.y, rho, res_y), q_z = cone_argument_unit(dual.z, rho, res_z);
+    const float radius = (normal_impulse < 0.0f ? 0.0f : normal_impulse) * mu;
+    if (radius == 0.0f) return;
+    const float n2 = fmaf(q_y, q_y, q_z * q_z);
+    if (n2 <= radius * radius) { iy = q_y; iz = q_z; cyy = czz = rho; return; }
+    const float inv = rsqrtf(n2);
+    const float dy = q_y * inv, dz = q_z * inv, cs = rho * radius * inv;
+    iy = radius * dy; iz = radius * dz;
+    cyy = cs * dz * dz; czz = cs * dy * dy; cyz = -cs * dy * dz;
+}
+
 struct Relax { V3 step; float weight; V3 point; };
 NKB_DEV V3 relax_contact_impulse(V3 dual, V3 next, Relax& last) {
     const V3 step = next - dual;

@@ -104,18 +104,6 @@ NKB_DEV float mass_coupling(const Env& e, const float* row) {
     return r;
 }
 
-NKB_DEV void head_response(const Env& e, uint32_t h, V3 move, V3& f, float& cxx, float& cyy, float& czz, float& cyz) {
-    const Resp rs = {hf(e, HF_RSD, h), hf(e, HF_RSR, h)};
-    const V3 dual = hf3(e, HF_DUAL, h), res = hf3(e, HF_RES, h);
-    const float rho = hf(e, HF_RHO, h);
-    const STerm n = scalar_impulse(dual.x, rho, res.x - move.x, hf(e, HF_LOWER, h), hf(e, HF_UPPER, h), rs);
-    f = mk3(n.impulse, 0.f, 0.f);
-    cxx = n.curvature; cyy = czz = cyz = 0.f;
-    if (head_axes(e, h) != 3u) return;
-    const float mu = hf(e, HF_MU, h);
-    tangent_impulse(dual, rho, res.y - move.y, res.z - move.z, hf(e, HF_NB, h), mu, mu, f.y, f.z, cyy, czz, cyz);
-}
-
 // Head setup: penalty, response scales (block_descent_tile.cuh:743-797).
 NKB_DEV void init_heads(Env& e, const Tile& tile) {
     const TemplateView& t = *e.t;
@@ -251,7 +239,7 @@ NKB_DEV void respond(const HeadRegs& r, V3 move, V3& f, float& cxx, float& cyy, 
     const STerm n = scalar_impulse(r.dual.x, r.rho, r.res.x - move.x, r.lower, r.upper, rs);
     f = mk3(n.impulse, 0.f, 0.f);
     cxx = n.curvature; cyy = czz = cyz = 0.f;
-    if (r.cone) tangent_impulse(r.dual, r.rho, r.res.y - move.y, r.res.z - move.z, r.nb, r.mu, r.mu, f.y, f.z, cyy, czz, cyz);
+    if (r.cone) cone_impulse(r.dual, r.rho, r.res.y - move.y, r.res.z - move.z, r.nb, r.mu, f.y, f.z, cyy, czz, cyz);
 }
 
 // Row steps J d of a block's incident heads (block_descent_tile.cuh:2019-2044); lane = head, d staged in shared
@@ -263,6 +251,7 @@ NKB_DEV void row_steps(Env& e, const Tile& tile, uint32_t b, const float* dvec) 
     const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
     const uint32_t chunks = (dim + 3u) >> 2, n4 = chunks << 2;
     const float4* d4 = reinterpret_cast<const float4*>(dvec);
+#pragma unroll 1
     for (uint32_t k = ib + e.lane; k < ie; k += 32u) {
         const uint32_t h = inc[k];
         const bool cone = head_axes(e, h) == 3u;
@@ -273,6 +262,7 @@ NKB_DEV void row_steps(Env& e, const Tile& tile, uint32_t b, const float* dvec) 
             else {
                 const float4* j4 = reinterpret_cast<const float4*>(sm_jpool(e) + jo);
                 float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+#pragma unroll 1
                 for (uint32_t c = 0u; c < chunks; ++c) {
                     const float4 d = d4[c], r0 = j4[c];
                     s0 = fmaf(r0.x, d.x, s0); s0 = fmaf(r0.y, d.y, s0); s0 = fmaf(r0.z, d.z, s0); s0 = fmaf(r0.w, d.w, s0);
@@ -287,8 +277,10 @@ NKB_DEV void row_steps(Env& e, const Tile& tile, uint32_t b, const float* dvec) 
         } else {
             const uint32_t side = head_owner(e, h, 0u) == b ? 0u : 1u;
             const uint32_t axes = cone ? 3u : 1u;
+#pragma unroll 1
             for (uint32_t ax = 0u; ax < axes; ++ax) {
                 float s = 0.f;
+#pragma unroll 1
                 for (uint32_t i = 0u; i < dim; ++i) s += head_jac(e, h, side, ax, i, b) * dvec[i];
                 setc(step, (int)ax, s);
             }
@@ -321,11 +313,14 @@ NKB_DEV float search_line(Env& e, const Tile& tile, uint32_t b, float islope, fl
     if (single && mine) cached = load_head(e, inc[ib + e.lane]);
     float low = 0.0f, high = 0.0f, alpha = 0.0f, initial = 0.0f, result = 0.0f;
     bool bounded = false, have = false;
+#pragma unroll 1
     for (int step = -1; step < (int)kLineSteps; ++step) {
         CSum rs = {0.f, 0.f};
         float rc = 0.f, rm = 0.f;
         if (single) { if (mine) line_terms(cached, alpha, rs, rc, rm); }
-        else for (uint32_t k = ib + e.lane; k < ie; k += 32u) { const HeadRegs r = load_head(e, inc[k]); line_terms(r, alpha, rs, rc, rm); }
+        else
+#pragma unroll 1
+        for (uint32_t k = ib + e.lane; k < ie; k += 32u) { const HeadRegs r = load_head(e, inc[k]); line_terms(r, alpha, rs, rc, rm); }
         CSum total = {-rs.value, -rs.error};
         if (e.lane == 0u) { csum_addp(total, alpha, icurv); csum_add(total, islope); }
         const float slope = warp_csum_total(total);
@@ -341,7 +336,7 @@ NKB_DEV float search_line(Env& e, const Tile& tile, uint32_t b, float islope, fl
         if (fabsf(slope) <= fmaxf(kLineTol * -initial, kRoundings * FLT_EPSILON * magnitude)) { have = true; result = alpha; break; }
         if (slope < 0.0f) low = alpha; else { high = alpha; bounded = true; }
         if (bounded && high - low <= FLT_EPSILON * high) break;
-        float next = alpha - slope / curvature;
+        float next = alpha - __fdividef(slope, curvature);
         if (!(next > low && (!bounded || next < high))) next = bounded ? 0.5f * (low + high) : 2.0f * alpha;
         alpha = next;
     }
@@ -352,6 +347,7 @@ NKB_DEV void apply_moves(Env& e, const Tile& tile, uint32_t b, float alpha) {
     const uint32_t nb = tile.nblocks;
     const uint32_t* inc = blk_inc(e, nb);
     const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
+#pragma unroll 1
     for (uint32_t k = ib + e.lane; k < ie; k += 32u) {
         const uint32_t h = inc[k];
         const V3 step = hf3(e, HF_STEP, h), move = hf3(e, HF_MOVE, h);
@@ -383,12 +379,15 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     const float* Mr;                    // this lane's row of the block mass, zero past the block's dimension
     if (artic) Mr = sm_mass(e) + (coord ? l : 0u) * e.lay->ld;
     else {
-        if (l < 6u) for (uint32_t k = 0u; k < 8u; ++k) m6[l * 12u + k] = k < 6u ? block_mass(e, b, l, k) : 0.f;
+        if (l < 6u)
+#pragma unroll 1
+        for (uint32_t k = 0u; k < 8u; ++k) m6[l * 12u + k] = k < 6u ? block_mass(e, b, l, k) : 0.f;
         if (l < 24u) jscr[l] = 0.f;
         Mr = m6 + (coord ? l : 0u) * 12u;
     }
     const float4* Mr4 = reinterpret_cast<const float4*>(Mr);
     bool coupled = false;
+#pragma unroll 1
     for (uint32_t k = ib + l; k < ie; k += 32u) {
         const uint32_t h = inc[k];
         const uint32_t o = hu(e, HF_OWNER, h);
@@ -405,6 +404,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     float primal = FLT_MAX;
     tick(e, 15);
     // step -1 (first velocity sweep only) is the line search toward the free velocity; steps >= 0 are Newton steps
+#pragma unroll 1
     for (int step = (tile.iteration == 0u && !position) ? -1 : 0; step < (int)kNewtonSteps; ++step) {
         float d = 0.f, force = 0.f, inertia = 0.f;
         if (step < 0) {
@@ -412,6 +412,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
         } else {
             // ---- lane = head: responses at the current moves, published to shared memory ----
             uint32_t dense_any = 0u;
+#pragma unroll 1
             for (uint32_t k = ib + l; k < ie; k += 32u) {
                 const uint32_t h = inc[k];
                 const HeadRegs r = load_head(e, h);
@@ -434,7 +435,9 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             __syncwarp();
             CSum inertial = {0.f, 0.f};
             float scale = 0.f, diag = 0.f;
-            if (coord) for (uint32_t c = 0u; c < chunks; ++c) {
+            if (coord)
+#pragma unroll 1
+            for (uint32_t c = 0u; c < chunks; ++c) {
                 const float4 m = Mr4[c], hi = reinterpret_cast<const float4*>(hi_v)[c], lo = reinterpret_cast<const float4*>(lo_v)[c];
                 Hr4[c] = m;
                 csum_addp(inertial, m.x, hi.x); inertial.error = fmaf(m.x, lo.x, inertial.error);
@@ -448,6 +451,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             // rows on a single coordinate only touch that coordinate (block_descent_tile.cuh:1555-1568)
             if (artic) {
                 const uint32_t* utab = unit_table(e, nb);
+#pragma unroll 1
                 for (uint32_t slot = 0u; slot < 4u; ++slot) {
                     const uint32_t h = utab[slot * 32u + l];
                     if (h == 0xffffffffu) continue;
@@ -458,7 +462,9 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                 }
             }
             // dense rows: H += J^T C J, g += J^T f, one head at a time with its values broadcast from shared memory
-            if (__any_sync(NKB_FULL, dense_any != 0u)) for (uint32_t k = ib; k < ie; ++k) {
+            if (__any_sync(NKB_FULL, dense_any != 0u))
+#pragma unroll 1
+            for (uint32_t k = ib; k < ie; ++k) {
                 const uint32_t hs = inc[k];
                 const uint32_t jo = hu(e, HF_JOFF, hs);
                 if (artic && (jo & kUnitRow)) continue;
@@ -470,7 +476,9 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                 else {
                     const uint32_t ss = head_owner(e, hs, 0u) == b ? 0u : 1u, as = head_axes(e, hs);
                     __syncwarp();
-                    if (l < 6u) for (uint32_t ax = 0u; ax < 3u; ++ax) jscr[ax * 8u + l] = ax < as ? head_jac(e, hs, ss, ax, l, b) : 0.f;
+                    if (l < 6u)
+#pragma unroll 1
+                    for (uint32_t ax = 0u; ax < 3u; ++ax) jscr[ax * 8u + l] = ax < as ? head_jac(e, hs, ss, ax, l, b) : 0.f;
                     __syncwarp();
                     jr = jscr; js = 8u;
                 }
@@ -482,6 +490,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                     const float4* r0 = reinterpret_cast<const float4*>(jr);
                     const float4* r1 = reinterpret_cast<const float4*>(jr + js);
                     const float4* r2 = reinterpret_cast<const float4*>(jr + 2u * js);
+#pragma unroll 1
                     for (uint32_t c = 0u; c < chunks; ++c) {
                         float4 h4 = Hr4[c];
                         const float4 x = r0[c], y = r1[c], z = r2[c];
@@ -497,6 +506,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             bool finite = true;
             if (coord) {
                 Hr[l] += diag;
+#pragma unroll 1
                 for (uint32_t c = 0u; c < chunks; ++c) {
                     const float4 v = Hr4[c], uu = reinterpret_cast<const float4*>(u_v)[c];
                     finite &= isfinite(v.x) && isfinite(v.y) && isfinite(v.z) && isfinite(v.w);
@@ -517,12 +527,14 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             bool valid = true;
             float inverse = 0.f;
             __syncwarp();
+#pragma unroll 1
             for (uint32_t k = 0u; k < dim; ++k) {
                 float value = 0.f;
                 if (coord && l >= k) {
                     const float4* Hk4 = reinterpret_cast<const float4*>(H + k * ldh);
                     const uint32_t full = k >> 2;
                     float s0 = 0.f, s1 = 0.f;
+#pragma unroll 1
                     for (uint32_t c = 0u; c < full; ++c) {
                         const float4 a = Hr4[c], bb = Hk4[c];
                         s0 = fmaf(a.x, bb.x, s0); s1 = fmaf(a.y, bb.y, s1); s0 = fmaf(a.z, bb.z, s0); s1 = fmaf(a.w, bb.w, s1);
@@ -545,10 +557,12 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             tick(e, 19);
             // ---- d = H^-1 g ----
             float r = force;
+#pragma unroll 1
             for (uint32_t j = 0u; j < dim; ++j) {
                 const float y = __shfl_sync(NKB_FULL, r * inverse, j);
                 r = l == j ? y : ((coord && l > j) ? fmaf(-Hr[j], y, r) : r);
             }
+#pragma unroll 1
             for (uint32_t jj = dim; jj > 0u; --jj) {
                 const uint32_t j = jj - 1u;
                 const float x = __shfl_sync(NKB_FULL, r * inverse, j);
@@ -561,7 +575,9 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
         dvec[l] = d;
         __syncwarp();
         float ms = 0.f;
-        if (coord) for (uint32_t c = 0u; c < chunks; ++c) {
+        if (coord)
+#pragma unroll 1
+        for (uint32_t c = 0u; c < chunks; ++c) {
             const float4 m = Mr4[c], dd = reinterpret_cast<const float4*>(dvec)[c];
             ms = fmaf(m.x, dd.x, ms); ms = fmaf(m.y, dd.y, ms); ms = fmaf(m.z, dd.z, ms); ms = fmaf(m.w, dd.w, ms);
         }
@@ -598,6 +614,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
         apply_moves(e, tile, b, alpha);
         if (rounded) break;
     }
+#pragma unroll 1
     for (uint32_t k = ib + l; k < ie; k += 32u) {
         const uint32_t h = inc[k];
         const V3 res = hf3(e, HF_RES, h), move = hf3(e, HF_MOVE, h);
@@ -618,8 +635,11 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
 NKB_DEV void descend_blocks(Env& e, Tile& tile, bool position) {
     const uint32_t nb = tile.nblocks;
     uint32_t remaining = 0u;
+#pragma unroll 1
     for (uint32_t b = 0u; b < nb; ++b) remaining += blk_color(e, nb, b) != 0xffffffffu ? 1u : 0u;
+#pragma unroll 1
     for (uint32_t color = 0u; color < 32u && remaining != 0u; ++color)
+#pragma unroll 1
         for (uint32_t b = 0u; b < nb; ++b) {
             if (blk_color(e, nb, b) != color) continue;
             --remaining;

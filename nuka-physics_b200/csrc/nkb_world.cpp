@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace nkb {
@@ -242,6 +243,7 @@ void World::BuildLayout() {
     const uint32_t hn = std::max(n, 6u);
     s.chol = take(hn * pad_ld(hn));
     s.bm6 = take(72 + 24);
+    if (const char* pad = std::getenv("NUKA_B200_SMEM_PAD_WORDS")) at += (static_cast<uint32_t>(std::atoi(pad)) + 3u) & ~3u;   // occupancy experiments
     s.words = at;
     const size_t bytes = static_cast<size_t>(s.words) * 4u;
     if (bytes > 220u * 1024u) throw Error(kNotSupported, "template needs more shared memory per env than one SM provides");
