@@ -174,7 +174,7 @@ __global__ void __maxnreg__(168) step_kernel(const __grid_constant__ StepParams 
         stage_warm_start(e, nheads);
         tick(e, 7);
         stage_solve(e, nheads);
-        if (has_collidables) stage_cache_commit(e, nheads, sm + p.sm.heads + HF_LAM * t.head_cap);
+        if (has_collidables) stage_cache_commit(e, nheads);
         if (has_artic) stage_readout_drives(e, nheads);
         tick(e, 12);
         if (has_artic) { stage_integrate_links(e, use_pseudo); }

@@ -9,7 +9,7 @@
 
 namespace nkb {
 
-// head fields (each an array of head_cap words)
+// head fields (word offsets inside a head record)
 enum HeadField : uint32_t {
     HF_FLAGS = 0, HF_OWNER, HF_REF, HF_JOFF, HF_UNITV,
     HF_RHO, HF_RSD, HF_RSR, HF_LOWER, HF_UPPER, HF_MU, HF_NB, HF_PEN, HF_RHS,
@@ -24,8 +24,9 @@ enum HeadField : uint32_t {
 constexpr uint32_t kNoBlock16 = 0xffffu;
 constexpr uint32_t kUnitRow = 0x80000000u;   // HF_JOFF: unit row on coordinate (value & 0xffff)
 
-NKB_DEV float& hf(const Env& e, uint32_t field, uint32_t h) { return e.sm[e.lay->heads + field * e.t->head_cap + h]; }
-NKB_DEV uint32_t& hu(const Env& e, uint32_t field, uint32_t h) { return reinterpret_cast<uint32_t*>(e.sm)[e.lay->heads + field * e.t->head_cap + h]; }
+// heads are records of kHeadStride words (odd, so one lane per head is conflict-free and fields are immediate offsets)
+NKB_DEV float& hf(const Env& e, uint32_t field, uint32_t h) { return e.sm[e.lay->heads + h * kHeadStride + field]; }
+NKB_DEV uint32_t& hu(const Env& e, uint32_t field, uint32_t h) { return reinterpret_cast<uint32_t*>(e.sm)[e.lay->heads + h * kHeadStride + field]; }
 NKB_DEV V3 hf3(const Env& e, uint32_t field, uint32_t h) { return mk3(hf(e, field, h), hf(e, field + 1u, h), hf(e, field + 2u, h)); }
 NKB_DEV void hst3(const Env& e, uint32_t field, uint32_t h, V3 v) { hf(e, field, h) = v.x; hf(e, field + 1u, h) = v.y; hf(e, field + 2u, h) = v.z; }
 NKB_DEV float* sm_jpool(const Env& e) { return e.sm + e.lay->jpool; }
@@ -135,6 +136,7 @@ NKB_DEV uint32_t stage_rows(Env& e, uint32_t pair_count) {
         float* pool = sm_jpool(e);
         for (uint32_t h = 0u; h < ncontact; ++h) {
             const uint32_t ref = hu(e, HF_REF, h), la = ref >> 16, lb = hu(e, HF_JOFF, h) & 0xffffu;
+            __syncwarp();      // every lane has read the side-b link before lane 0 replaces it with the pool offset
             const uint32_t n4 = (n + 3u) & ~3u, joff = h * 3u * n4;
             const V3 point = ld3(sm_cpoint(e, ref & 0xffffu));
             const V3 dirs[3] = {hf3(e, HF_N, h), hf3(e, HF_T1, h), hf3(e, HF_T2, h)};
@@ -286,7 +288,7 @@ NKB_DEV void stage_warm_start(Env& e, uint32_t nheads) {
 
 // Warm start (phase 1): rebuilds the env's cache from the solved multipliers; unmatched cached points of age 0
 // survive one more step in the points no current contact owns.
-NKB_DEV void stage_cache_commit(Env& e, uint32_t nheads, const float* lambda3) {
+NKB_DEV void stage_cache_commit(Env& e, uint32_t nheads) {
     const TemplateView& t = *e.t;
     const uint32_t npts = t.cfg.max_contacts * 4u;
     if (npts == 0u) return;
@@ -346,7 +348,8 @@ NKB_DEV void stage_cache_commit(Env& e, uint32_t nheads, const float* lambda3) {
                 const uint32_t h = owner[c];
                 const uint32_t* f = sm_cfeat(e, c);
                 en.pair = head_pair(e, h); en.feature = ((unsigned long long)f[1] << 32) | f[0]; en.age = 0u;
-                en.lambda[0] = lambda3[h * 3u]; en.lambda[1] = lambda3[h * 3u + 1u]; en.lambda[2] = lambda3[h * 3u + 2u];
+                const V3 lam = hf3(e, HF_LAM, h);
+                en.lambda[0] = lam.x; en.lambda[1] = lam.y; en.lambda[2] = lam.z;
                 const V3 nn = ld3(sm_cnormal(e, c));
                 en.normal[0] = nn.x; en.normal[1] = nn.y; en.normal[2] = nn.z;
             } else {

@@ -24,7 +24,8 @@ enum : uint32_t { kStatusPairOverflow = 1u << 0, kStatusDofOverflow = 1u << 2, k
 enum : uint32_t { kHeadContact = 1u << 0, kHeadContactNormal = 1u << 1, kHeadSpeculative = 1u << 2,
                   kHeadVelocityOnly = 1u << 3, kHeadDrive = 1u << 4, kHeadLimit = 1u << 5, kHeadFriction = 1u << 6,
                   kHeadScalar = 1u << 7 /* position pass: only the normal axis */ };
-constexpr uint32_t kHeadWords = 64u;    // words of shared memory per solver head
+constexpr uint32_t kHeadWords = 64u;
+constexpr uint32_t kHeadStride = kHeadWords + 1u;   // odd record stride in shared memory    // words of shared memory per solver head
 
 struct Config {
     float dt;

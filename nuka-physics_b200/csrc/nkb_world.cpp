@@ -229,20 +229,24 @@ void World::BuildLayout() {
     // float4-readable matrix rows: a multiple of 4 words that is 4 mod 8 (conflict-free for one lane per row)
     auto pad_ld = [](uint32_t k) { const uint32_t ld = (k + 3u) & ~3u; return (ld & 7u) == 0u ? ld + 4u : ld; };
     s.ld = pad_ld(n);
-    s.pose = take(7 * L); s.xrot = take(9 * L); s.xtr = take(3 * L);
-    s.vel = take(6 * L); s.vbias = take(6 * L); s.acc = take(6 * L); s.pbias = take(6 * L); s.ic = take(10 * L);
+    s.pose = take(7 * L); s.vel = take(6 * L);
+    // the dynamics stage's link scratch and the solver's Newton scratch are live at different times and share one region
+    const uint32_t hn = std::max(n, 6u);
+    const uint32_t overlay = at;
+    s.xrot = take(9 * L); s.xtr = take(3 * L); s.vbias = take(6 * L); s.acc = take(6 * L); s.pbias = take(6 * L); s.ic = take(10 * L);
+    const uint32_t dynamics_end = at;
+    if (std::getenv("NUKA_B200_NO_OVERLAY") == nullptr) at = overlay;
+    s.chol = take(hn * pad_ld(hn)); s.bm6 = take(72 + 24);
+    at = std::max(at, dynamics_end);
     s.mass = take(n * s.ld); s.factor = take(n * s.ld); s.vecs = take(12 * 32);
     s.bpose = take(7 * B); s.bvel = take(6 * B); s.bwinv = take(6 * B); s.aabb = take(6 * B);
     s.bmass = take(7 * B); s.bfree = take(6 * B); s.bpseudo = take(6 * B);
     s.pairs = take(S); s.ccount = take(S); s.cpoint = take(12 * S); s.cnormal = take(12 * S); s.cdepth = take(4 * S);
     s.cfeat = take(8 * S + 4 * S * 10 + 4 * S);   // feature words, cache staging entries, owner marks
-    s.heads = take(kHeadWords * tv.head_cap);
+    s.heads = take(kHeadStride * tv.head_cap);
     s.jpool = take(tv.point_cap * 3u * ((n + 3u) & ~3u));
     const uint32_t nb = B + (n ? 1u : 0u);
     s.binfo = take(3 * nb + 1 + 2 * tv.head_cap + 4 * 32);
-    const uint32_t hn = std::max(n, 6u);
-    s.chol = take(hn * pad_ld(hn));
-    s.bm6 = take(72 + 24);
     if (const char* pad = std::getenv("NUKA_B200_SMEM_PAD_WORDS")) at += (static_cast<uint32_t>(std::atoi(pad)) + 3u) & ~3u;   // occupancy experiments
     s.words = at;
     const size_t bytes = static_cast<size_t>(s.words) * 4u;

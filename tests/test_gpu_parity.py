@@ -143,3 +143,32 @@ def test_quadruped_stands_for_a_second(device):
     assert np.allclose(np.linalg.norm(base[:, 3:], axis=1), 1.0, atol=1e-4)
     assert w.download(F.ENV_STATUS).max() == 0
     w.destroy()
+
+
+def test_quadruped_contact_trajectory_tracks_the_oracle(device, oracle):
+    """Standing quadrupeds in contact: warm-started multi-step trajectories stay on the oracle's (20 steps,
+    positions within 1e-4 of the largest magnitude), with the same sweep counts."""
+    E = 256
+    st = T.quadruped_state(E, 3)
+    w, o = make_pair(device, oracle, T.quadruped(0), E, {"q": st["q"], "base_pose": st["base_pose"]})
+    w.step_n(20); o.step(20)
+    assert rel(w.download(F.JOINT_POSITION), o.get("q", 13)) < 1e-4
+    assert rel(w.download(F.BASE_POSE), o.get("base_pose", 7)) < 1e-4
+    assert np.mean(w.download(F.SOLVER_SWEEPS) == o.get("solver_sweeps", 1)) > 0.98
+    assert w.download(F.ENV_STATUS).max() == 0
+    w.destroy()
+
+
+def test_benchmark_size_runs_are_reproducible(device):
+    """Two runs of the 4096-env workload from the same inputs end in byte-identical state (no data races)."""
+    E = 4096
+    blob = T.quadruped(0).blob()
+    st = T.quadruped_state(E, 0)
+    ends = []
+    for _ in range(2):
+        w = nuka.World.create_from_template(device, blob, E)
+        w.upload(F.JOINT_POSITION, st["q"]); w.upload(F.BASE_POSE, st["base_pose"]); w.forward_kinematics()
+        w.step_n(50)
+        ends.append((w.download(F.JOINT_POSITION).tobytes(), w.download(F.BASE_POSE).tobytes(), w.download(F.JOINT_VELOCITY).tobytes()))
+        w.destroy()
+    assert ends[0] == ends[1]
