@@ -183,20 +183,15 @@ def main():
     obs_local = torch.empty((E, 49), dtype=torch.float32, device="cuda")
     obs_all = torch.empty((E * world_size, 49), dtype=torch.float32, device="cuda") if distributed else None
 
-    def pack_obs():
-        # 48 observation floats + 1 reward per env (joint state, base pose, base twist, last action, height reward)
-        obs_local[:, 0:12] = views[F.JOINT_POSITION][:, 1:]
-        obs_local[:, 12:24] = views[F.JOINT_VELOCITY][:, 1:]
-        obs_local[:, 24:31] = views[F.BASE_POSE]
-        obs_local[:, 31:37] = views[F.LINK_VELOCITY][:, 0:6]
-        obs_local[:, 37:48] = views[F.DRIVE_TARGET][:, 1:12]
-        obs_local[:, 48] = views[F.BASE_POSE][:, 2]
+    from nuka import shard
 
     def one_step():
         w.step()
         if distributed:
-            pack_obs()
-            dist.all_gather_into_tensor(obs_all, obs_local)
+            # 48 observation floats + 1 reward per env, gathered as the RL caller would
+            shard.pack_observations(obs_local, views[F.JOINT_POSITION], views[F.JOINT_VELOCITY], views[F.BASE_POSE],
+                                    views[F.LINK_VELOCITY], views[F.DRIVE_TARGET])
+            shard.gather_observations(obs_local, obs_all)
 
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):

@@ -60,7 +60,7 @@ void nuka_device_destroy(nuka_device_handle device);
  * otherwise creation returns NUKA_RESULT_NOT_SUPPORTED (terrain/heightfield/curriculum, instancing,
  * cloth, OGC, substeps > 1). */
 typedef struct nuka_world_desc_t {
-    const char* scene_path;            /* ".nkt" cooked template file, or "synthetic:<name>" */
+    const char* scene_path;            /* path of a ".nkt" cooked template file */
     uint32_t env_count;
     float fixed_dt;
     uint8_t determinism;               /* 0 or 1; larger values are INVALID_ARG */
@@ -115,13 +115,13 @@ nuka_result_t nuka_world_forward_kinematics(nuka_world_handle world);
 nuka_result_t nuka_world_get_stream(nuka_world_handle world, void** out_stream);
 nuka_result_t nuka_world_record_event(nuka_world_handle world, void* cuda_event);
 
-/* nuka.h:496-964: state field ids (values as in the reference) for the fields this path serves. */
+/* nuka.h:496-964: state field ids (values as in the reference) for the fields this path serves.  The reference's
+ * CONTACT_POINTS (5) and CONTACT_NORMAL (17) views are not served; contacts are read through the tap fields below. */
 typedef enum nuka_state_field_t {
     NUKA_FIELD_RIGID_BODY_TRANSFORM = 0,      /* E x B x 7 f32 */
     NUKA_FIELD_ARTICULATION_LINK_POSE = 1,    /* E x L x 7 f32 */
     NUKA_FIELD_JOINT_POSITION = 2,            /* E x L f32, slot 0 = root */
     NUKA_FIELD_JOINT_VELOCITY = 3,            /* E x L f32 */
-    NUKA_FIELD_CONTACT_POINTS = 5,            /* E x 4 x 3 f32: first point of the first four candidate slots */
     NUKA_FIELD_DRIVE_TARGET = 6,              /* E x L f32, writable */
     NUKA_FIELD_LINK_VELOCITY = 7,             /* E x L x 6 f32, angular first */
     NUKA_FIELD_DRIVE_STIFFNESS = 8,           /* E x L f32, writable */
@@ -129,7 +129,6 @@ typedef enum nuka_state_field_t {
     NUKA_FIELD_DRIVE_FORCE_LIMIT = 10,
     NUKA_FIELD_BASE_POSE = 11,                /* E x 7 f32 */
     NUKA_FIELD_VELOCITY_TARGET = 13,          /* E x L f32, writable */
-    NUKA_FIELD_CONTACT_NORMAL = 17,           /* E x 4 x 3 f32 */
     NUKA_FIELD_JOINT_FEEDFORWARD = 22,        /* E x L f32, writable */
     NUKA_FIELD_BODY_LINEAR_VELOCITY = 25,     /* E x B x 3 f32 */
     NUKA_FIELD_BODY_ANGULAR_VELOCITY = 26,    /* E x B x 3 f32 */
