@@ -24,6 +24,7 @@ sys.path.insert(0, os.path.join(ROOT, "nuka-physics_b200"))
 
 ENVS_PER_GPU = 4096
 METRIC = "env-steps/sec (whole box) 4096-env 12-DoF quadruped"
+WORKLOAD = "quadruped (13 links, 18 DoF, 4 foot spheres + trunk box on a plane), configs[1], hold drives at the standing pose"
 # algorithmic bytes per env-step: B = 12 nj + 52 F + 8 nj + 52 F + 52 L + 8 (nj + 3 P) + 8 S + 32 P
 NJ, NF, NL = 12, 1, 13
 
@@ -121,7 +122,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "env-steps/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3 * ENVS_PER_GPU / sample_envs, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "quadruped 4096 envs (configs[1]); CPU oracle port, bounded sample", "envs_per_gpu": ENVS_PER_GPU},
+        "config": {"workload": WORKLOAD, "envs_per_gpu": ENVS_PER_GPU, "dt": 1.0 / 200.0, "velocity_iterations": 4,
+                   "note": "CPU oracle port on the host cores, bounded sample per step"},
         "cpu_baseline": {"value": value, "unit": "env-steps/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "env-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -259,7 +261,7 @@ def main():
         achieved = bytes_per * E * args.steps / (gpu_ms * 1e-3) / 1e9
         traffic = None
         try:
-            with open(os.path.join(ROOT, "profiles", "step_kernel_quadruped_traffic.json")) as f:
+            with open(os.path.join(ROOT, "profiles", "step_kernel_quadruped_traffic.txt")) as f:
                 traffic = json.load(f).get("dram_bytes_per_launch_4096_envs")
         except Exception:
             pass
@@ -267,7 +269,7 @@ def main():
             "metric": METRIC, "value": value, "unit": "env-steps/s", "n_gpus": world_size, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": gpu_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": "quadruped (13 links, 18 DoF, 4 foot spheres + trunk box on a plane), configs[1]",
+            "config": {"workload": WORKLOAD,
                        "envs_per_gpu": E, "dt": 1.0 / 200.0, "velocity_iterations": 4, "l2_flush_between_steps": flush is not None,
                        "obs_allgather": distributed, "mean_contact_slots": slots, "mean_contact_points": points},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
