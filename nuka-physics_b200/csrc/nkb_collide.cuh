@@ -9,7 +9,8 @@ namespace nkb {
 
 NKB_DEV float* sm_bpose(const Env& e, uint32_t b) { return e.sm + e.lay->bpose + 7u * b; }
 NKB_DEV float* sm_bvel(const Env& e, uint32_t b) { return e.sm + e.lay->bvel + 6u * b; }
-NKB_DEV float* sm_bwinv(const Env& e, uint32_t b) { return e.sm + e.lay->bwinv + 6u * b; }
+NKB_DEV uint32_t free_slot(const Env& e, uint32_t b) { return __ldg(e.t->free_slot + b); }
+NKB_DEV float* sm_bwinv(const Env& e, uint32_t b) { return e.sm + e.lay->bwinv + 6u * free_slot(e, b); }
 NKB_DEV float* sm_aabb(const Env& e, uint32_t b) { return e.sm + e.lay->aabb + 6u * b; }
 NKB_DEV uint32_t* sm_pairs(const Env& e) { return reinterpret_cast<uint32_t*>(e.sm + e.lay->pairs); }
 NKB_DEV uint32_t* sm_ccount(const Env& e) { return reinterpret_cast<uint32_t*>(e.sm + e.lay->ccount); }

@@ -157,6 +157,43 @@ NKB_DEV V3 extrapolate_dual(V3 base, V3 next, float beta, float lower, float upp
     const float scale = slip > radius ? radius / slip : 1.0f;
     return mk3(y.x, mu1 > 0.0f ? y.y * scale : 0.0f, mu2 > 0.0f ? y.z * scale : 0.0f);
 }
+// ---- single-coefficient (isotropic) forms used by the per-sweep dual update: the per-axis coefficients of the
+// general laws above are both mu here, so the normalised coefficients are 1 and the divisions drop out ----
+NKB_DEV V3 relax_contact_impulse_fast(V3 dual, V3 next, Relax& last) {
+    const V3 step = next - dual;
+    const V3 change = step - last.step;
+    const V3 moved = dual - last.point;
+    const float square = change.x * change.x + change.y * change.y + change.z * change.z;
+    const float along = -(moved.x * change.x + moved.y * change.y + moved.z * change.z);
+    float weight = 1.0f;
+    if (last.weight > 0.0f && along > 0.0f && square > 0.0f) weight = fminf(1.0f, __fdividef(along, square));
+    last.step = step; last.weight = weight; last.point = dual;
+    return mk3(dual.x + weight * step.x, dual.y + weight * step.y, dual.z + weight * step.z);
+}
+NKB_DEV void multiplier_steps_iso(V3 dual, V3 next, float scale, float dual_scale, float rho, float mu, float& normal, float& tangent) {
+    normal = scale > 0.0f && dual_scale != 0.0f ? __fdividef(fabsf(next.x - dual.x), scale) : 0.0f;
+    const float dy = next.y - dual.y, dz = next.z - dual.z;
+    tangent = mu > 0.0f && rho > 0.0f ? __fdividef(sqrtf(fmaf(dy, dy, dz * dz)), rho) : 0.0f;
+}
+// sum over axes of (point - next)(next - base) / metric, metric = (scale, rho, rho) for a cone head with mu > 0
+NKB_DEV double momentum_restart_iso(V3 point, V3 next, V3 base, float scale, float rho, bool cone) {
+    double r = 0.0;
+    if (scale > 0.0f) r += ((double)point.x - next.x) * ((double)next.x - base.x) * (double)__frcp_rn(scale);
+    if (cone && rho > 0.0f)
+        r += (((double)point.y - next.y) * ((double)next.y - base.y) + ((double)point.z - next.z) * ((double)next.z - base.z)) * (double)__frcp_rn(rho);
+    return r;
+}
+NKB_DEV V3 extrapolate_dual_iso(V3 base, V3 next, float beta, float lower, float upper, bool contact, float mu) {
+    if (beta == 0.0f) return next;
+    V3 y = mk3(fmaf(beta, next.x - base.x, next.x), fmaf(beta, next.y - base.y, next.y), fmaf(beta, next.z - base.z, next.z));
+    y.x = fminf(fmaxf(y.x, lower), upper);
+    if (!contact) return mk3(y.x, 0.0f, 0.0f);
+    if (!(mu > 0.0f)) return mk3(y.x, 0.0f, 0.0f);
+    const float s2 = fmaf(y.y, y.y, y.z * y.z), limit = fmaxf(y.x, 0.0f) * mu;
+    const float scale = s2 > limit * limit ? limit * rsqrtf(s2) : 1.0f;
+    return mk3(y.x, y.y * scale, y.z * scale);
+}
+
 NKB_DEV float residual_abs(float v) { return v <= FLT_MAX ? fabsf(v) : FLT_MAX; }
 
 }  // namespace nkb

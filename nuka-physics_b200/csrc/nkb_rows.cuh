@@ -293,7 +293,7 @@ NKB_DEV void stage_cache_commit(Env& e, uint32_t nheads) {
     const uint32_t npts = t.cfg.max_contacts * 4u;
     if (npts == 0u) return;
     CacheEntry* cache = e.s->cache + (size_t)e.env * npts;
-    CacheEntry* stage = reinterpret_cast<CacheEntry*>(e.sm + e.lay->cfeat + 2u * npts);   // staging after the feature words
+    CacheEntry* stage = reinterpret_cast<CacheEntry*>(e.sm + e.lay->cstage);
     uint32_t* owner = reinterpret_cast<uint32_t*>(stage + npts);
     for (uint32_t c = e.lane; c < npts; c += 32u) owner[c] = 0xffffffffu;
     __syncwarp();

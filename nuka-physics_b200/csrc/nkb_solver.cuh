@@ -32,9 +32,9 @@ NKB_DEV uint32_t* blk_inc(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u *
 // unit rows of the articulation by coordinate: utab[slot * 32 + coordinate] = head or ~0 (slots: lower limit, upper limit,
 // dry friction, drive)
 NKB_DEV uint32_t* unit_table(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u * nb + 1u + 2u * e.t->head_cap; }
-NKB_DEV float* sm_bmass(const Env& e, uint32_t b) { return e.sm + e.lay->bmass + 7u * b; }
-NKB_DEV float* sm_bfree(const Env& e, uint32_t b) { return e.sm + e.lay->bfree + 6u * b; }
-NKB_DEV float* sm_bpseudo(const Env& e, uint32_t b) { return e.sm + e.lay->bpseudo + 6u * b; }
+NKB_DEV float* sm_bmass(const Env& e, uint32_t b) { return e.sm + e.lay->bmass + 7u * free_slot(e, b); }
+NKB_DEV float* sm_bfree(const Env& e, uint32_t b) { return e.sm + e.lay->bfree + 6u * free_slot(e, b); }
+NKB_DEV float* sm_bpseudo(const Env& e, uint32_t b) { return e.sm + e.lay->bpseudo + 6u * free_slot(e, b); }
 NKB_DEV float* sm_chol(const Env& e) { return e.sm + e.lay->chol; }
 
 NKB_DEV uint32_t head_axes(const Env& e, uint32_t h) { return (hu(e, HF_FLAGS, h) & (kHeadContact | kHeadScalar)) == kHeadContact ? 3u : 1u; }
@@ -668,12 +668,12 @@ NKB_DEV void update_duals(Env& e, const Tile& tile, DualMomentum* mom, bool velo
         if (!contact) dual = mk3(normal, 0.f, 0.f);
         else {
             float iy, iz, c1, c2, c3;
-            tangent_impulse(tdual, rho, res.y, res.z, normal, mu, mu, iy, iz, c1, c2, c3);
-            dual = relax_contact_impulse(tdual, mk3(normal, iy, iz), rx);
+            cone_impulse(tdual, rho, res.y, res.z, normal, mu, iy, iz, c1, c2, c3);
+            dual = relax_contact_impulse_fast(tdual, mk3(normal, iy, iz), rx);
         }
         float sn, st;
-        multiplier_steps(tdual, dual, rs.residual_scale, rs.dual_scale, rho, contact ? mu : 0.f, contact ? mu : 0.f, sn, st);
-        if (!commit && rs.residual_scale > 0.f) sn = fabsf(dual.x - tdual.x) / rs.residual_scale;
+        multiplier_steps_iso(tdual, dual, rs.residual_scale, rs.dual_scale, rho, contact ? mu : 0.f, sn, st);
+        if (!commit && rs.residual_scale > 0.f) sn = __fdividef(fabsf(dual.x - tdual.x), rs.residual_scale);
         const V3 physical = commit ? dual : tdual;
         if (!contact) {
             const bool normal_row = (fl & kHeadContactNormal) != 0u;
@@ -691,7 +691,7 @@ NKB_DEV void update_duals(Env& e, const Tile& tile, DualMomentum* mom, bool velo
         if (velocity) hst3(e, HF_LAM, h, dual);
         const bool extrapolate = contact || rs.dual_scale != 0.f;
         const V3 base = hf3(e, HF_BASE, h);
-        if (extrapolate) restart += momentum_restart(tdual, dual, base, multiplier_metric(rs.residual_scale, rho, contact, mu, mu));
+        if (extrapolate) restart += momentum_restart_iso(tdual, dual, base, rs.residual_scale, rho, contact && mu > 0.f);
         if (mom != nullptr) hst3(e, HF_MOVE, h, base);
         hst3(e, HF_DUAL, h, dual);
         hst3(e, HF_BASE, h, dual);
@@ -709,8 +709,8 @@ NKB_DEV void update_duals(Env& e, const Tile& tile, DualMomentum* mom, bool velo
             const bool contact = head_axes(e, h) == 3u;
             const bool extrapolate = contact || hf(e, HF_RSD, h) != 0.f;
             const float mu = hf(e, HF_MU, h);
-            hst3(e, HF_DUAL, h, extrapolate_dual(hf3(e, HF_MOVE, h), hf3(e, HF_BASE, h), extrapolate ? mom->beta : 0.f,
-                                                 hf(e, HF_LOWER, h), hf(e, HF_UPPER, h), contact, mu, mu));
+            hst3(e, HF_DUAL, h, extrapolate_dual_iso(hf3(e, HF_MOVE, h), hf3(e, HF_BASE, h), extrapolate ? mom->beta : 0.f,
+                                                     hf(e, HF_LOWER, h), hf(e, HF_UPPER, h), contact, mu));
         }
         __syncwarp();
     }
@@ -720,23 +720,53 @@ NKB_DEV void update_duals(Env& e, const Tile& tile, DualMomentum* mom, bool velo
 NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
     const uint32_t nb = tile.nblocks, l = e.lane;
     const uint32_t* inc = blk_inc(e, nb);
-    for (uint32_t color = 0u; color < 32u; ++color) for (uint32_t b = 0u; b < nb; ++b) {
+#pragma unroll 1
+    for (uint32_t color = 0u; color < 32u; ++color)
+#pragma unroll 1
+    for (uint32_t b = 0u; b < nb; ++b) {
         if (blk_color(e, nb, b) != color) continue;
         const uint32_t dim = blk_dim(e, b);
-        const bool coord = l < dim;
+        const bool coord = l < dim, artic = b == e.t->B;
         float* vel = block_vel(e, b, false);
         const float* fr = block_free(e, b);
-        double balance = 0.0;
-        if (coord) for (uint32_t j = 0u; j < dim; ++j) balance -= (double)block_mass(e, b, l, j) * ((double)vel[j] - fr[j]);
         const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
-        for (uint32_t k = ib; k < ie; ++k) {
-            const uint32_t h = inc[k];
-            const uint32_t side = head_owner(e, h, 0u) == b ? 0u : 1u, axes = head_axes(e, h);
-            const V3 lam = hf3(e, HF_LAM, h);
-            for (uint32_t ax = 0u; ax < axes; ++ax) {
-                const float imp = comp(lam, (int)ax);
-                if (imp == 0.f) continue;
-                if (coord) balance += (double)head_jac(e, h, side, ax, l, b) * imp;
+        double balance = 0.0;
+        if (artic) {
+            const uint32_t n4 = (dim + 3u) & ~3u;
+            if (coord) {
+                const float* Mr = sm_mass(e) + l * e.lay->ld;
+#pragma unroll 1
+                for (uint32_t j = 0u; j < dim; ++j) balance -= (double)Mr[j] * ((double)vel[j] - fr[j]);
+                const uint32_t* utab = unit_table(e, nb);
+#pragma unroll 1
+                for (uint32_t slot = 0u; slot < 4u; ++slot) {
+                    const uint32_t h = utab[slot * 32u + l];
+                    if (h != 0xffffffffu) balance += (double)hf(e, HF_UNITV, h) * hf(e, HF_LAM, h);
+                }
+            }
+#pragma unroll 1
+            for (uint32_t k = ib; k < ie; ++k) {
+                const uint32_t h = inc[k];
+                const uint32_t jo = hu(e, HF_JOFF, h);
+                if (jo & kUnitRow) continue;
+                const V3 lam = hf3(e, HF_LAM, h);
+                if (!coord) continue;
+                const float* jr = sm_jpool(e) + jo;
+                balance += (double)jr[l] * lam.x;
+                if (head_axes(e, h) == 3u) balance += (double)jr[n4 + l] * lam.y + (double)jr[2u * n4 + l] * lam.z;
+            }
+        } else {
+            if (coord) for (uint32_t j = 0u; j < dim; ++j) balance -= (double)block_mass(e, b, l, j) * ((double)vel[j] - fr[j]);
+#pragma unroll 1
+            for (uint32_t k = ib; k < ie; ++k) {
+                const uint32_t h = inc[k];
+                const uint32_t side = head_owner(e, h, 0u) == b ? 0u : 1u, axes = head_axes(e, h);
+                const V3 lam = hf3(e, HF_LAM, h);
+                for (uint32_t ax = 0u; ax < axes; ++ax) {
+                    const float imp = comp(lam, (int)ax);
+                    if (imp == 0.f) continue;
+                    if (coord) balance += (double)head_jac(e, h, side, ax, l, b) * imp;
+                }
             }
         }
         const float force = coord ? (float)balance : 0.f;

@@ -50,6 +50,8 @@ struct TemplateView {
     // body-row pairs (a << 16 | b, a < b, ascending) that pass the template-constant filters: not both
     // static, bitmask/group admitted, not excluded.  Only these need an AABB test each step.
     const uint32_t *adm_pairs;
+    const uint32_t *free_slot;         // B: slot of a free dynamic body in the solver's rigid-block arrays; others share slot n_free
+    uint32_t n_free;
     uint32_t n_adm;
     Config cfg;
 };
@@ -95,7 +97,8 @@ struct SmemLayout {
     uint32_t pose, xrot, xtr, vel, vbias, acc, pbias, ic;       // per link
     uint32_t mass, factor, vecs;                                // articulation
     uint32_t bpose, bvel, bwinv, aabb, bmass, bfree, bpseudo;   // bodies
-    uint32_t pairs, ccount, cpoint, cnormal, cdepth, cfeat;     // contacts (cfeat also stages the cache rebuild)
+    uint32_t pairs, ccount, cpoint, cnormal, cdepth, cfeat;     // contacts
+    uint32_t cstage;                                            // cache rebuild staging (shares the Jacobian pool, dead by then)
     uint32_t heads, jpool, binfo, chol, bm6;                    // solver (chol: Newton matrix; bm6: rigid block mass + head rows)
     uint32_t words;                                             // total per env
     uint32_t ld;                                                // leading dimension of mass/factor (ndof | 1)

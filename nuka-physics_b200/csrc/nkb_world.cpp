@@ -171,6 +171,14 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
         t.adm_pairs.push_back((a << 16) | b);
     }
     if (t.adm_pairs.empty()) t.adm_pairs.push_back(0);
+    // free dynamic bodies get their own slot in the rigid-block arrays; every other row shares one scratch slot
+    t.free_slot.assign(std::max(B, 1u), 0u);
+    t.n_free = 0;
+    for (uint32_t b = 0; b < B; ++b) if (t.inv_mass[b] > 0.f && t.body_to_link[b] == kNoLink) ++t.n_free;
+    {
+        uint32_t next = 0;
+        for (uint32_t b = 0; b < B; ++b) t.free_slot[b] = (t.inv_mass[b] > 0.f && t.body_to_link[b] == kNoLink) ? next++ : t.n_free;
+    }
     t.joint_rows = 0;
     for (uint32_t l = 0; l < L; ++l) {
         if (JointDofs(t.jtype[l]) != 1u) continue;
@@ -239,12 +247,14 @@ void World::BuildLayout() {
     s.chol = take(hn * pad_ld(hn)); s.bm6 = take(72 + 24);
     at = std::max(at, dynamics_end);
     s.mass = take(n * s.ld); s.factor = take(n * s.ld); s.vecs = take(12 * 32);
-    s.bpose = take(7 * B); s.bvel = take(6 * B); s.bwinv = take(6 * B); s.aabb = take(6 * B);
-    s.bmass = take(7 * B); s.bfree = take(6 * B); s.bpseudo = take(6 * B);
+    const uint32_t slots = B ? t.n_free + 1u : 0u;
+    s.bpose = take(7 * B); s.bvel = take(6 * B); s.aabb = take(6 * B);
+    s.bwinv = take(6 * slots); s.bmass = take(7 * slots); s.bfree = take(6 * slots); s.bpseudo = take(6 * slots);
     s.pairs = take(S); s.ccount = take(S); s.cpoint = take(12 * S); s.cnormal = take(12 * S); s.cdepth = take(4 * S);
-    s.cfeat = take(8 * S + 4 * S * 10 + 4 * S);   // feature words, cache staging entries, owner marks
+    s.cfeat = take(8 * S);                        // contact identity words
     s.heads = take(kHeadStride * tv.head_cap);
-    s.jpool = take(tv.point_cap * 3u * ((n + 3u) & ~3u));
+    s.jpool = take(std::max(tv.point_cap * 3u * ((n + 3u) & ~3u), 4u * S * 10u + 4u * S));   // also the cache staging entries + owner marks
+    s.cstage = s.jpool;
     const uint32_t nb = B + (n ? 1u : 0u);
     s.binfo = take(3 * nb + 1 + 2 * tv.head_cap + 4 * 32);
     if (const char* pad = std::getenv("NUKA_B200_SMEM_PAD_WORDS")) at += (static_cast<uint32_t>(std::atoi(pad)) + 3u) & ~3u;   // occupancy experiments
@@ -285,6 +295,7 @@ World::World(int device, cudaStream_t stream, const HostTemplate& tpl, uint32_t 
         v.inv_mass = Upload(t.inv_mass); v.inv_inertia = Upload(t.inv_inertia); v.inertial_pos = Upload(t.inertial_pos);
         v.inertial_quat = Upload(t.inertial_quat); v.excluded = Upload(t.excluded);
         v.adm_pairs = Upload(t.adm_pairs);
+        v.free_slot = Upload(t.free_slot); v.n_free = t.n_free;
         v.n_adm = (t.adm_pairs.size() == 1 && t.adm_pairs[0] == 0u) ? 0u : static_cast<uint32_t>(t.adm_pairs.size());
         const size_t E = env_count_, L = t.L, B = t.B, n = t.ndof, S = t.cfg.max_contacts;
         StateView& s = params_.s;

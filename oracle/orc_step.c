@@ -179,7 +179,7 @@ void orc_step_env(const orc_model *m, orc_env *e) {
 
 int orc_hw_threads(void) {
 #ifdef _OPENMP
-    return omp_get_max_threads();
+    return omp_get_num_procs();      /* the cores this process may run on, whatever OMP_NUM_THREADS says */
 #else
     return 1;
 #endif
