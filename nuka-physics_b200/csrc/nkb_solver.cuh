@@ -55,6 +55,29 @@ NKB_DEV float head_jac(const Env& e, uint32_t h, uint32_t side, uint32_t ax, uin
     return sgn * comp(cross(r, dir), (int)i - 3);
 }
 
+// J_h[ax] . u over the coordinates of block b (u padded with zeros to a multiple of 4 for the articulation).
+NKB_DEV float head_row_dot(const Env& e, uint32_t h, uint32_t side, uint32_t ax, uint32_t block, const float* u) {
+    const TemplateView& t = *e.t;
+    if (block == t.B) {
+        const uint32_t jo = hu(e, HF_JOFF, h);
+        if (jo & kUnitRow) return hf(e, HF_UNITV, h) * u[jo & 0xffffu];
+        const uint32_t chunks = (t.ndof + 3u) >> 2;
+        const float4* j4 = reinterpret_cast<const float4*>(sm_jpool(e) + jo) + ax * chunks;
+        const float4* u4 = reinterpret_cast<const float4*>(u);
+        float s = 0.f;
+#pragma unroll 1
+        for (uint32_t c = 0u; c < chunks; ++c) {
+            const float4 a = j4[c], b4 = u4[c];
+            s = fmaf(a.x, b4.x, s); s = fmaf(a.y, b4.y, s); s = fmaf(a.z, b4.z, s); s = fmaf(a.w, b4.w, s);
+        }
+        return s;
+    }
+    float s = 0.f;
+#pragma unroll 1
+    for (uint32_t i = 0u; i < 6u; ++i) s += head_jac(e, h, side, ax, i, block) * u[i];
+    return s;
+}
+
 // Mass entry (i, k) of a block.
 NKB_DEV float block_mass(const Env& e, uint32_t block, uint32_t i, uint32_t k) {
     if (block == e.t->B) return sm_mass(e)[i * e.lay->ld + k];
@@ -203,11 +226,7 @@ NKB_DEV void init_residuals(Env& e, const Tile& tile) {
             for (uint32_t side = 0u; side < 2u; ++side) {
                 const uint32_t b = head_owner(e, h, side);
                 if (b == kNoBlock16) continue;
-                const uint32_t dim = blk_dim(e, b);
-                const float* u = block_vel(e, b, false);
-                float part = 0.f;
-                for (uint32_t i = 0u; i < dim; ++i) part += head_jac(e, h, side, ax, i, b) * u[i];
-                along += part;
+                along += head_row_dot(e, h, side, ax, b, block_vel(e, b, false));
             }
             setc(res, (int)ax, (ax == 0u ? hf(e, HF_RHS, h) * dt : 0.f) - along);
         }
@@ -836,7 +855,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
             sm_vec(e, kVecFree)[l] = value;
             sm_vec(e, kVecU)[l] = value + (isfinite(c) ? c : 0.f);
             sm_vec(e, kVecPseudo)[l] = 0.f;
-        }
+        } else { sm_vec(e, kVecFree)[l] = 0.f; sm_vec(e, kVecU)[l] = 0.f; sm_vec(e, kVecPseudo)[l] = 0.f; }   // float4 readers see zeros past n
     }
     __syncwarp();
     init_heads(e, tile);
@@ -899,11 +918,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
                             for (uint32_t side = 0u; side < 2u; ++side) {
                                 const uint32_t b = head_owner(e, h, side);
                                 if (b == kNoBlock16) continue;
-                                const uint32_t dim = blk_dim(e, b);
-                                const float* u = block_vel(e, b, false);
-                                double v = 0.0;
-                                for (uint32_t i = 0u; i < dim; ++i) v += (double)head_jac(e, h, side, 0u, i, b) * u[i];
-                                velocity += v;
+                                velocity += (double)head_row_dot(e, h, side, 0u, b, block_vel(e, b, false));
                             }
                             const double limit = fmin(correction / t.cfg.dt, (double)t.cfg.baumgarte_max_velocity);
                             bias = (float)fmin(target / t.cfg.dt - velocity, limit);
