@@ -146,7 +146,7 @@ typedef enum nuka_state_field_t {
     NUKA_B200_FIELD_CONTACT_DEPTH = 0x10007,        /* E x S x 4 f32 */
     NUKA_B200_FIELD_SOLVER_SWEEPS = 0x10008,        /* E u32 */
     NUKA_B200_FIELD_JOINT_PSEUDO_VELOCITY = 0x10009, /* E x n f32 */
-    NUKA_B200_FIELD_STAGE_CYCLES = 0x1000A /* E x 24 u32: SM cycles per pipeline stage, summed since first requested */
+    NUKA_B200_FIELD_STAGE_CYCLES = 0x1000A /* E x 32 u32: SM cycles per pipeline stage, summed since first requested */
 } nuka_state_field_t;
 
 /* nuka.h:1158-1166 */

@@ -80,7 +80,7 @@ NKB_DEV void env_begin(Env& e, const StepParams& p, float* sm, uint32_t env, uin
     if (dof && __ldg(t.jtype + e.dof_link) == kFloating) e.dof_comp = lane - __ldg(t.link_dof + e.dof_link);
     e.vel0 = 0.f;
     e.status = 0u;
-    e.cyc = p.s.dbg_cycles != nullptr ? p.s.dbg_cycles + (size_t)env * 24u : nullptr;
+    e.cyc = p.s.dbg_cycles != nullptr ? p.s.dbg_cycles + (size_t)env * 32u : nullptr;
     e.t0 = clock64();
 }
 

@@ -24,7 +24,7 @@ struct Tile {
 };
 
 NKB_DEV uint32_t* sm_binfo(const Env& e) { return reinterpret_cast<uint32_t*>(e.sm + e.lay->binfo); }
-// binfo words: dim[nb], color[nb], inc_begin[nb + 1], inc[2 * head_cap], utab[4 * 32]
+// binfo words: dim[nb], color[nb], inc_begin[nb + 1], inc[2 * head_cap], utab[4 * 32], order[nb + 1]
 NKB_DEV uint32_t& blk_dim(const Env& e, uint32_t b) { return sm_binfo(e)[b]; }
 NKB_DEV uint32_t& blk_color(const Env& e, uint32_t nb, uint32_t b) { return sm_binfo(e)[nb + b]; }
 NKB_DEV uint32_t& blk_inc_begin(const Env& e, uint32_t nb, uint32_t b) { return sm_binfo(e)[2u * nb + b]; }
@@ -32,6 +32,8 @@ NKB_DEV uint32_t* blk_inc(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u *
 // unit rows of the articulation by coordinate: utab[slot * 32 + coordinate] = head or ~0 (slots: lower limit, upper limit,
 // dry friction, drive)
 NKB_DEV uint32_t* unit_table(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u * nb + 1u + 2u * e.t->head_cap; }
+// moving blocks in descent order, order[nb] = their count
+NKB_DEV uint32_t* block_order(const Env& e, uint32_t nb) { return unit_table(e, nb) + 128u; }
 NKB_DEV float* sm_bmass(const Env& e, uint32_t b) { return e.sm + e.lay->bmass + 7u * free_slot(e, b); }
 NKB_DEV float* sm_bfree(const Env& e, uint32_t b) { return e.sm + e.lay->bfree + 6u * free_slot(e, b); }
 NKB_DEV float* sm_bpseudo(const Env& e, uint32_t b) { return e.sm + e.lay->bpseudo + 6u * free_slot(e, b); }
@@ -199,19 +201,40 @@ NKB_DEV void index_blocks(Env& e, const Tile& tile, bool color) {
     }
     __syncwarp();
     if (!color) return;
+    uint32_t colours = 0u;       // 1 + the largest colour in use
+#pragma unroll 1
     for (uint32_t b = 0u; b < nb; ++b) {
+        if (blk_dim(e, b) == 0u) { if (e.lane == 0u) blk_color(e, nb, b) = 0xffffffffu; continue; }
         uint32_t taken = 0u;
         const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
         for (uint32_t k = ib + e.lane; k < ie; k += 32u) {
             const uint32_t o = hu(e, HF_OWNER, inc[k]);
             const uint32_t first = o & 0xffffu, second = o >> 16;
             const uint32_t other = first == b ? second : first;
-            if (other < b) taken |= 1u << blk_color(e, nb, other);
+            if (other < b && blk_dim(e, other) != 0u) taken |= 1u << blk_color(e, nb, other);
         }
         taken = __reduce_or_sync(NKB_FULL, taken);
-        if (e.lane == 0u) blk_color(e, nb, b) = blk_dim(e, b) != 0u ? min((uint32_t)__ffs(~taken) - 1u, 31u) : 0xffffffffu;
+        const uint32_t c = min((uint32_t)__ffs(~taken) - 1u, 31u);
+        colours = max(colours, c + 1u);
+        if (e.lane == 0u) blk_color(e, nb, b) = c;
         __syncwarp();
     }
+    __syncwarp();
+    // descent order: colour by colour, index order inside a colour (block_descent_tile.cuh:2749-2820)
+    uint32_t* order = block_order(e, nb);
+    uint32_t count = 0u;
+#pragma unroll 1
+    for (uint32_t c = 0u; c < colours; ++c)
+#pragma unroll 1
+        for (uint32_t base = 0u; base < nb; base += 32u) {
+            const uint32_t b = base + e.lane;
+            const bool hit = b < nb && blk_color(e, nb, b) == c;
+            const uint32_t m = __ballot_sync(NKB_FULL, hit);
+            if (hit) order[count + __popc(m & ((1u << e.lane) - 1u))] = b;
+            count += __popc(m);
+        }
+    if (e.lane == 0u) order[nb] = count;
+    __syncwarp();
 }
 
 // residual = rhs dt - J u at the blocks' current velocities (block_descent_tile.cuh:891-930)
@@ -653,17 +676,10 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
 // Blocks descend colour by colour, blocks of one colour in index order (block_descent_tile.cuh:2749-2820).
 NKB_DEV void descend_blocks(Env& e, Tile& tile, bool position) {
     const uint32_t nb = tile.nblocks;
-    uint32_t remaining = 0u;
+    const uint32_t* order = block_order(e, nb);
+    const uint32_t count = order[nb];
 #pragma unroll 1
-    for (uint32_t b = 0u; b < nb; ++b) remaining += blk_color(e, nb, b) != 0xffffffffu ? 1u : 0u;
-#pragma unroll 1
-    for (uint32_t color = 0u; color < 32u && remaining != 0u; ++color)
-#pragma unroll 1
-        for (uint32_t b = 0u; b < nb; ++b) {
-            if (blk_color(e, nb, b) != color) continue;
-            --remaining;
-            descend_block(e, tile, b, position);
-        }
+    for (uint32_t k = 0u; k < count; ++k) descend_block(e, tile, order[k], position);
 }
 
 struct DualMomentum { float t, beta; };
@@ -739,11 +755,11 @@ NKB_DEV void update_duals(Env& e, const Tile& tile, DualMomentum* mom, bool velo
 NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
     const uint32_t nb = tile.nblocks, l = e.lane;
     const uint32_t* inc = blk_inc(e, nb);
+    const uint32_t* order = block_order(e, nb);
+    const uint32_t count = order[nb];
 #pragma unroll 1
-    for (uint32_t color = 0u; color < 32u; ++color)
-#pragma unroll 1
-    for (uint32_t b = 0u; b < nb; ++b) {
-        if (blk_color(e, nb, b) != color) continue;
+    for (uint32_t turn = 0u; turn < count; ++turn) {
+        const uint32_t b = order[turn];
         const uint32_t dim = blk_dim(e, b);
         const bool coord = l < dim, artic = b == e.t->B;
         float* vel = block_vel(e, b, false);
@@ -951,6 +967,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
         } else tick(e, 10);
         update_duals(e, tile, phase == kPhaseVelocity ? &mom : nullptr, phase == kPhaseVelocity, true, rows);
         if (phase == kPhasePosition) continue;
+        tick(e, 24);
         // momentum balance: plain measure, reconstruction when only the primal lags, re-measure after it
         for (int stage = 0; stage < 3; ++stage) {
             const float worst_row = fmaxf(fmaxf(rows[0], rows[1]), rows[2]);
@@ -958,12 +975,13 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
             if (stage == 0) run = sweeps == iterations || fmaxf(worst_row, tile.residual) < tile.tol;
             else if (stage == 1) run = worst_row < tile.tol && tile.residual >= tile.tol && tile.residual < FLT_MAX;
             if (stage == 1 && !run) break;
-            if (run) measure_primals(e, tile, stage == 1);
+            if (run) { measure_primals(e, tile, stage == 1); tick(e, 25); if (e.cyc != nullptr && l == 0u) e.cyc[27] += 1u; }
             if (stage == 1) {
                 if (!(tile.residual < FLT_MAX)) break;
                 init_residuals(e, tile);
                 update_duals(e, tile, nullptr, true, false, rows);
                 tile.residual = 0.f;
+                tick(e, 26);
             }
         }
         cls[0] = rows[0]; cls[1] = rows[1]; cls[2] = rows[2]; cls[3] = tile.residual;

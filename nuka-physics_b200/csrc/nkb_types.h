@@ -89,7 +89,7 @@ struct StateView {
     // optional parity taps (null unless requested)
     float *dbg_mass;                                            // E x ndof x ndof
     float *dbg_qdot_pseudo;                                     // E x ndof
-    uint32_t *dbg_cycles;                                       // E x 24 stage cycle counters
+    uint32_t *dbg_cycles;                                       // E x 32 stage cycle counters
 };
 
 // Shared-memory layout of one env (offsets in 4-byte words), filled by the host.

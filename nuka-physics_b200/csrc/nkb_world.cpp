@@ -256,7 +256,7 @@ void World::BuildLayout() {
     s.jpool = take(std::max(tv.point_cap * 3u * ((n + 3u) & ~3u), 4u * S * 10u + 4u * S));   // also the cache staging entries + owner marks
     s.cstage = s.jpool;
     const uint32_t nb = B + (n ? 1u : 0u);
-    s.binfo = take(3 * nb + 1 + 2 * tv.head_cap + 4 * 32);
+    s.binfo = take(3 * nb + 1 + 2 * tv.head_cap + 4 * 32 + nb + 1);
     if (const char* pad = std::getenv("NUKA_B200_SMEM_PAD_WORDS")) at += (static_cast<uint32_t>(std::atoi(pad)) + 3u) & ~3u;   // occupancy experiments
     s.words = at;
     const size_t bytes = static_cast<size_t>(s.words) * 4u;
@@ -488,8 +488,8 @@ bool World::Field(uint32_t id, FieldInfo* out) {
             if (s.dbg_qdot_pseudo == nullptr) s.dbg_qdot_pseudo = Alloc<float>(static_cast<size_t>(env_count_) * n);
             return set(s.dbg_qdot_pseudo, n, 0, false);
         case 0x1000A:      // stage cycle counters accumulate from the first request on; writable so callers can clear them
-            if (s.dbg_cycles == nullptr) s.dbg_cycles = Alloc<uint32_t>(static_cast<size_t>(env_count_) * 24u);
-            return set(s.dbg_cycles, 24, 1, true);
+            if (s.dbg_cycles == nullptr) s.dbg_cycles = Alloc<uint32_t>(static_cast<size_t>(env_count_) * 32u);
+            return set(s.dbg_cycles, 32, 1, true);
         default: return false;
     }
 }
