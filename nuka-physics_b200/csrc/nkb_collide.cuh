@@ -8,8 +8,10 @@
 namespace nkb {
 
 NKB_DEV float* sm_bpose(const Env& e, uint32_t b) { return e.sm + e.lay->bpose + 7u * b; }
-NKB_DEV float* sm_bvel(const Env& e, uint32_t b) { return e.sm + e.lay->bvel + 6u * b; }
+
 NKB_DEV uint32_t free_slot(const Env& e, uint32_t b) { return __ldg(e.t->free_slot + b); }
+// velocities live in the free-body slots; every link-mirror or static row shares the last slot, which holds zeros
+NKB_DEV float* sm_bvel(const Env& e, uint32_t b) { return e.sm + e.lay->bvel + 6u * free_slot(e, b); }
 NKB_DEV float* sm_bwinv(const Env& e, uint32_t b) { return e.sm + e.lay->bwinv + 6u * free_slot(e, b); }
 NKB_DEV float* sm_aabb(const Env& e, uint32_t b) { return e.sm + e.lay->aabb + 6u * b; }
 NKB_DEV uint32_t* sm_pairs(const Env& e) { return reinterpret_cast<uint32_t*>(e.sm + e.lay->pairs); }
@@ -60,8 +62,10 @@ NKB_DEV void stage_bodies(Env& e, bool kick) {
             for (int k = 0; k < 7; ++k) bp[k] = gp[k];
             V3 lv = ld3(e.s->body_linvel + gb * 3u);
             const V3 av = ld3(e.s->body_angvel + gb * 3u);
-            if (kick && __ldg(t.inv_mass + b) > 0.f) lv = lv + g * t.cfg.dt;
-            st3(bv, lv); st3(bv + 3, av);
+            const bool dynamic = __ldg(t.inv_mass + b) > 0.f;
+            if (kick && dynamic) lv = lv + g * t.cfg.dt;
+            if (dynamic) { st3(bv, lv); st3(bv + 3, av); }
+            else { st3(bv, mk3(0.f, 0.f, 0.f)); st3(bv + 3, mk3(0.f, 0.f, 0.f)); }      // static rows share the zero slot
         }
         float* w = sm_bwinv(e, b);
         if (__ldg(t.inv_mass + b) > 0.f) world_inv_inertia(ldq(bp + 3), ldq(t.inertial_quat + 4u * b), ld3(t.inv_inertia + 3u * b), w);

@@ -51,7 +51,9 @@ NKB_DEV float* sm_mass(const Env& e) { return e.sm + e.lay->mass; }
 NKB_DEV float* sm_factor(const Env& e) { return e.sm + e.lay->factor; }
 NKB_DEV float* sm_vec(const Env& e, uint32_t k) { return e.sm + e.lay->vecs + 32u * k; }
 // vector slots
-enum { kVecBias = 0, kVecAcc = 1, kVecFree = 2, kVecU = 3, kVecD = 4, kVecPseudo = 5, kVecTmp = 6, kVecTmp2 = 7, kVecS0 = 8, kVecS1 = 9, kVecS2 = 10, kVecCount = 12 };
+enum { kVecBias = 0, kVecAcc = 1, kVecFree = 2, kVecU = 3, kVecD = 4, kVecPseudo = 5, kVecTmp = 6, kVecTmp2 = 7,
+       // Newton-loop scratch shares slots whose other users run before or after the solve
+       kVecS0 = kVecTmp, kVecS1 = kVecTmp2, kVecS2 = kVecAcc, kVecCount = 8 };
 
 NKB_DEV uint32_t joint_dofs(uint32_t t) { return (t == kRevolute || t == kPrismatic) ? 1u : t == kFloating ? 6u : t == kSpherical ? 3u : 0u; }
 

@@ -115,7 +115,7 @@ NKB_DEV void stage_store_bodies(Env& e, bool velocities) {
     for (uint32_t k = e.lane; k < t.B * 7u; k += 32u) gp[k] = sp[k];
     if (!velocities) return;
     for (uint32_t b = e.lane; b < t.B; b += 32u) {
-        if (__ldg(t.body_to_link + b) != kNoLink) continue;
+        if (__ldg(t.body_to_link + b) != kNoLink || !(__ldg(t.inv_mass + b) > 0.f)) continue;     // only free dynamic bodies move
         const size_t gb = (size_t)e.env * t.B + b;
         st3(e.s->body_linvel + gb * 3u, ld3(sm_bvel(e, b)));
         st3(e.s->body_angvel + gb * 3u, ld3(sm_bvel(e, b) + 3));
