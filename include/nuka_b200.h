@@ -181,6 +181,22 @@ nuka_result_t nuka_b200_world_run_stage(nuka_world_handle world, uint32_t stage)
 /* Kernel launches enqueued by this world since creation (for throughput reports). */
 nuka_result_t nuka_b200_world_launch_count(nuka_world_handle world, uint64_t* out);
 
+/* No counterpart in the reference.  nuka_world_reset_envs without any allocation: same validation, set semantics and
+ * resulting state, but the env-id list goes through a fixed 16 KB device array built into the library instead of a
+ * buffer the world allocates on demand.  Meant for callers that cannot allocate once their episode loop runs: a
+ * training process whose framework allocator already owns the rest of the device memory (an allocation for the id
+ * list could then fail mid-run), and control loops that cannot afford the device-wide stall an allocation implies.
+ *  - at most NUKA_B200_STATIC_RESET_MAX_IDS ids per call (counted before de-duplication); more is
+ *    NUKA_ERR_INVALID_ARG and nothing changes;
+ *  - the first call on a device also looks up the array's device address; make that first call during set-up,
+ *    before any stream capture is started;
+ *  - nothing in the array needs clearing: each call overwrites the ids it is about to read;
+ *  - all worlds on one device share the array, so two calls must not be in flight at the same time on that device
+ *    (different worlds, streams or threads): they would race on the id list.  A call returns after its ids have
+ *    been consumed, so calls issued one after another from one thread are safe. */
+#define NUKA_B200_STATIC_RESET_MAX_IDS 4096u
+nuka_result_t nuka_b200_world_reset_envs_static(nuka_world_handle world, const uint32_t* env_ids, uint32_t count);
+
 #ifdef __cplusplus
 }
 #endif

@@ -269,6 +269,13 @@ nuka_result_t nuka_world_reset_envs(nuka_world_handle world, const uint32_t* env
     return Guard([&]() { w->Reset(env_ids, count); return NUKA_RESULT_OK; });
 }
 
+nuka_result_t nuka_b200_world_reset_envs_static(nuka_world_handle world, const uint32_t* env_ids, uint32_t count) {
+    NKB_WORLD(w)
+    if (count == 0u) return NUKA_RESULT_OK;
+    if (env_ids == nullptr) { SetError("env_ids is null"); return NUKA_RESULT_INVALID_ARG; }
+    return Guard([&]() { w->ResetStaticIds(env_ids, count); return NUKA_RESULT_OK; });
+}
+
 nuka_result_t nuka_world_forward_kinematics(nuka_world_handle world) {
     NKB_WORLD(w)
     return Guard([&]() { w->Refresh(); return NUKA_RESULT_OK; });

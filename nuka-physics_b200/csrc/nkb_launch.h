@@ -26,5 +26,9 @@ struct ResetParams {
 cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream);
 // Restores `count` envs (all when r.env_ids is null) from their snapshots.
 cudaError_t launch_reset(const ResetParams& r, uint32_t count, cudaStream_t stream);
+// Partial reset without a device allocation: the ids travel through a fixed device array of kStaticResetMaxIds words
+// that every world on `device` shares.  `device` must be current; r.env_ids is ignored.
+constexpr uint32_t kStaticResetMaxIds = 4096u;
+cudaError_t launch_reset_static_ids(const ResetParams& r, const uint32_t* host_ids, uint32_t count, int device, cudaStream_t stream);
 
 }  // namespace nkb

@@ -452,6 +452,24 @@ void World::Reset(const uint32_t* env_ids, uint32_t count) {
     Refresh();
 }
 
+// Same result as Reset(env_ids, count) with no allocation on the device or the host: ids are validated, sorted and
+// de-duplicated in a member array, copied into the module's fixed device array, and the stream is drained before
+// returning so the member array can be reused (Reset waits for its id copy in the same way).
+void World::ResetStaticIds(const uint32_t* env_ids, uint32_t count) {
+    Check(cudaSetDevice(device_), "cudaSetDevice");
+    if (count == 0u) return;
+    if (count > kStaticResetMaxIds) throw Error(kInvalidArg, "reset_envs_static: more than 4096 env ids in one call");
+    for (uint32_t k = 0; k < count; ++k) if (env_ids[k] >= env_count_) throw Error(kInvalidArg, "reset_envs_static: env id out of range");
+    std::copy(env_ids, env_ids + count, static_ids_host_);
+    std::sort(static_ids_host_, static_ids_host_ + count);
+    const uint32_t unique = static_cast<uint32_t>(std::unique(static_ids_host_, static_ids_host_ + count) - static_ids_host_);
+    ResetParams r = reset_;
+    Check(launch_reset_static_ids(r, static_ids_host_, unique, device_, stream_), "static-id reset launch");
+    Check(cudaStreamSynchronize(stream_), "static-id reset sync");
+    ++launches_;
+    Refresh();
+}
+
 void World::Synchronize() {
     Check(cudaSetDevice(device_), "cudaSetDevice");
     Check(cudaStreamSynchronize(stream_), "stream synchronize");

@@ -54,6 +54,7 @@ public:
     void RunStage(uint32_t mode);
     void Refresh();
     void Reset(const uint32_t* env_ids, uint32_t count);   // null ids: all envs
+    void ResetStaticIds(const uint32_t* env_ids, uint32_t count);   // partial reset that allocates nothing
     void Synchronize();
     bool Field(uint32_t id, FieldInfo* out);
     void SetVelocityIterations(uint32_t n) { params_.t.cfg.vel_iters = n; graph_valid_ = false; }
@@ -85,6 +86,7 @@ private:
     ResetParams reset_{};
     uint32_t* reset_ids_ = nullptr;
     uint32_t reset_ids_cap_ = 0;
+    uint32_t static_ids_host_[kStaticResetMaxIds];      // sorted, de-duplicated ids of the partial reset being issued
     CacheEntry* cache_empty_ = nullptr;
     bool graph_mode_ = false, graph_valid_ = false;
     cudaGraph_t graph_ = nullptr;

@@ -155,6 +155,11 @@ class World:
         ids = np.ascontiguousarray(env_ids, dtype=np.uint32)
         _check(_abi.lib().nuka_world_reset_envs(self._h, ids.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), ids.size))
 
+    def reset_envs_static(self, env_ids):
+        """reset_envs without any allocation (at most 4096 ids per call; calls on one device must not overlap)."""
+        ids = np.ascontiguousarray(env_ids, dtype=np.uint32)
+        _check(_abi.lib().nuka_b200_world_reset_envs_static(self._h, ids.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), ids.size))
+
     def forward_kinematics(self):
         _check(_abi.lib().nuka_world_forward_kinematics(self._h))
 
