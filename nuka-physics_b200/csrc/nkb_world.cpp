@@ -228,7 +228,7 @@ void World::BuildLayout() {
         std::sort(caps.begin(), caps.end(), [](uint32_t a, uint32_t b) { return a > b; });
         uint32_t total = 0;
         for (size_t k = 0; k < caps.size() && k < S; ++k) total += caps[k];
-        tv.point_cap = std::min(total, 32u);
+        tv.point_cap = std::min(total, 128u);     // bounds the head records and Jacobian pool in shared memory
     }
     tv.head_cap = (tv.point_cap + t.joint_rows + 3u) & ~3u;
     if (tv.head_cap == 0u) tv.head_cap = 4u;

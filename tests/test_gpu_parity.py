@@ -172,3 +172,39 @@ def test_benchmark_size_runs_are_reproducible(device):
         ends.append((w.download(F.JOINT_POSITION).tobytes(), w.download(F.BASE_POSE).tobytes(), w.download(F.JOINT_VELOCITY).tobytes()))
         w.destroy()
     assert ends[0] == ends[1]
+
+
+def test_free_boxes_land_like_the_oracle(device, oracle):
+    """Six free boxes falling onto a plane (the free rigid-body path: gyroscopic integration, box-plane and
+    box-box manifolds, 6-coordinate solver blocks): candidate pairs and contact counts bit-exact, poses within
+    1e-4 through the first landings."""
+    E = 64
+    st = T.box_pile_state(E, 2, count=6)
+    w, o = make_pair(device, oracle, T.box_pile(2, count=6), E, {"body_pose": st["body_pose"]})
+    B, S = 7, w.info.contact_slots_per_env
+    for k in (1, 14, 25):
+        w.step_n(k); o.step(k)
+        pc = w.download(F.PAIR_COUNT)
+        assert np.array_equal(pc, o.get("pair_count", 1))
+        live = np.arange(S)[None, :] < pc                      # slots past the pair count are unspecified
+        gp = w.download(F.CANDIDATE_PAIRS).reshape(E, S, 2)
+        op = o.get("candidate_pairs", 2 * S).reshape(E, S, 2)
+        assert np.array_equal(gp[live], op[live])
+        assert np.array_equal(w.download(F.CONTACT_COUNT)[live], o.get("contact_count", S)[live])
+        assert rel(w.download(F.RIGID_BODY_TRANSFORM), o.get("body_pose", 7 * B)) < 1e-4
+    assert w.download(F.PAIR_COUNT).max() > 0 and w.download(F.ENV_STATUS).max() == 0
+    w.destroy()
+
+
+def test_quadruped_with_free_boxes(device, oracle):
+    """configs[4]'s env: the quadruped plus four free boxes (articulated and rigid blocks in one solve)."""
+    E = 64
+    st = T.quadruped_state(E, 4)
+    w, o = make_pair(device, oracle, T.quadruped(0, boxes=4), E, {"q": st["q"], "base_pose": st["base_pose"]})
+    w.step_n(30); o.step(30)
+    assert rel(w.download(F.JOINT_POSITION), o.get("q", 13)) < 1e-4
+    assert rel(w.download(F.BASE_POSE), o.get("base_pose", 7)) < 1e-4
+    assert rel(w.download(F.RIGID_BODY_TRANSFORM), o.get("body_pose", 18 * 7)) < 1e-4
+    assert np.array_equal(w.download(F.CONTACT_COUNT), o.get("contact_count", w.info.contact_slots_per_env))
+    assert w.download(F.ENV_STATUS).max() == 0
+    w.destroy()
