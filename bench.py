@@ -154,6 +154,7 @@ def main():
     ap.add_argument("--impl", default="native")
     ap.add_argument("--envs", type=int, default=ENVS_PER_GPU)
     ap.add_argument("--no-flush", action="store_true", help="skip the L2 flush between timed steps")
+    ap.add_argument("--no-gather", action="store_true", help="N > 1: skip the per-step observation all-gather")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -189,10 +190,9 @@ def main():
 
     def one_step():
         w.step()
-        if distributed:
+        if distributed and not args.no_gather:
             # 48 observation floats + 1 reward per env, gathered as the RL caller would
-            shard.pack_observations(obs_local, views[F.JOINT_POSITION], views[F.JOINT_VELOCITY], views[F.BASE_POSE],
-                                    views[F.LINK_VELOCITY], views[F.DRIVE_TARGET])
+            w.pack_observations(obs_local)
             shard.gather_observations(obs_local, obs_all)
 
     with torch.cuda.stream(stream):
@@ -271,7 +271,7 @@ def main():
             "data": "synthetic",
             "config": {"workload": WORKLOAD,
                        "envs_per_gpu": E, "dt": 1.0 / 200.0, "velocity_iterations": 4, "l2_flush_between_steps": flush is not None,
-                       "obs_allgather": distributed, "mean_contact_slots": slots, "mean_contact_points": points},
+                       "obs_allgather": distributed and not args.no_gather, "mean_contact_slots": slots, "mean_contact_points": points},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_source": peak_kind, "algorithmic_bytes_per_env_step": bytes_per,
                          "kernel": "step_kernel", "kernel_ms": gpu_ms / args.steps},

@@ -181,6 +181,13 @@ nuka_result_t nuka_b200_world_run_stage(nuka_world_handle world, uint32_t stage)
 /* Kernel launches enqueued by this world since creation (for throughput reports). */
 nuka_result_t nuka_b200_world_launch_count(nuka_world_handle world, uint64_t* out);
 
+/* Packs one observation record per env into caller-owned device memory on the world's stream, for RL callers that
+ * exchange observations between shards: joint positions (L-1), joint velocities (L-1), base pose (7), root twist (6),
+ * drive targets of all joints but the last (L-2), base height as reward; 3 (L-1) + 13 floats per env (49 for the
+ * quadruped), the quantities python/nuka/tasks/go2_obs.py:47-48 composes.  device_out == NULL only reports the
+ * width.  NUKA_ERR_NOT_SUPPORTED for worlds without a floating-base articulation. */
+nuka_result_t nuka_b200_world_pack_observations(nuka_world_handle world, float* device_out, size_t capacity_floats, uint32_t* out_width);
+
 /* No counterpart in the reference.  nuka_world_reset_envs without any allocation: same validation, set semantics and
  * resulting state, but the env-id list goes through a fixed 16 KB device array built into the library instead of a
  * buffer the world allocates on demand.  Meant for callers that cannot allocate once their episode loop runs: a

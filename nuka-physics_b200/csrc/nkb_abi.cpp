@@ -357,6 +357,15 @@ nuka_result_t nuka_b200_world_run_stage(nuka_world_handle world, uint32_t stage)
     return Guard([&]() { w->RunStage(stage); return NUKA_RESULT_OK; });
 }
 
+nuka_result_t nuka_b200_world_pack_observations(nuka_world_handle world, float* device_out, size_t capacity_floats, uint32_t* out_width) {
+    NKB_WORLD(w)
+    const uint32_t width = w->ObservationWidth();
+    if (out_width != nullptr) *out_width = width;
+    if (device_out == nullptr) return NUKA_RESULT_OK;          // width query only
+    if (capacity_floats < static_cast<size_t>(width) * w->env_count()) { SetError("observation buffer is too small"); return NUKA_RESULT_INVALID_ARG; }
+    return Guard([&]() { w->PackObservations(device_out); return NUKA_RESULT_OK; });
+}
+
 nuka_result_t nuka_b200_world_launch_count(nuka_world_handle world, uint64_t* out) {
     NKB_WORLD(w)
     if (out == nullptr) { SetError("out pointer is null"); return NUKA_RESULT_INVALID_ARG; }

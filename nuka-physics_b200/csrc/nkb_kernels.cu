@@ -3,6 +3,7 @@
 // intermediate in the warp's shared-memory slice; global memory sees only the env's state.
 // The stage order is the reference's nk::Pipeline::BuildInterval (src/nk/pipeline/pipeline.cpp:367-986).
 #include <cuda_runtime.h>
+#include <algorithm>
 #include <cstdio>
 #include "nkb_solver.cuh"
 #include "nkb_launch.h"
@@ -230,6 +231,33 @@ cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStrea
     }
     const uint32_t blocks = (p.s.env_count + warps_per_block - 1u) / warps_per_block;
     step_kernel<<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+// One record per env for the RL caller (python/nuka/tasks/go2_obs.py:47-48 composes the same quantities):
+// joint positions and velocities (L - 1 each), base pose (7), root twist (6), drive targets of all joints but the
+// last (L - 2), and the base height as reward: 3 (L - 1) + 13 floats.
+__global__ void pack_observations_kernel(const StateView s, uint32_t L, float* out) {
+    const uint32_t width = 3u * (L - 1u) + 13u, nq = L - 1u;
+    const size_t total = (size_t)s.env_count * width;
+    for (size_t at = (size_t)blockIdx.x * blockDim.x + threadIdx.x; at < total; at += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t env = (uint32_t)(at / width), k = (uint32_t)(at % width);
+        float v;
+        if (k < nq) v = s.q[(size_t)env * L + 1u + k];
+        else if (k < 2u * nq) v = s.qdot[(size_t)env * L + 1u + (k - nq)];
+        else if (k < 2u * nq + 7u) v = s.base_pose[(size_t)env * 7u + (k - 2u * nq)];
+        else if (k < 2u * nq + 13u) v = s.link_vel[(size_t)env * L * 6u + (k - 2u * nq - 7u)];
+        else if (k < width - 1u) v = s.drive_target[(size_t)env * L + 1u + (k - 2u * nq - 13u)];
+        else v = s.base_pose[(size_t)env * 7u + 2u];
+        out[at] = v;
+    }
+}
+
+cudaError_t launch_pack_observations(const StateView& s, uint32_t L, float* out, cudaStream_t stream) {
+    if (s.env_count == 0u || L < 2u) return cudaSuccess;
+    const size_t total = (size_t)s.env_count * (3u * (L - 1u) + 13u);
+    const uint32_t blocks = (uint32_t)std::min<size_t>((total + 255u) / 256u, 148u * 8u);
+    pack_observations_kernel<<<blocks, 256, 0, stream>>>(s, L, out);
     return cudaGetLastError();
 }
 

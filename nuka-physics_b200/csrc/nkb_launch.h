@@ -26,6 +26,8 @@ struct ResetParams {
 cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream);
 // Restores `count` envs (all when r.env_ids is null) from their snapshots.
 cudaError_t launch_reset(const ResetParams& r, uint32_t count, cudaStream_t stream);
+// Packs the per-env observation record (3 (L - 1) + 13 floats) of every env into `out` (device memory).
+cudaError_t launch_pack_observations(const StateView& s, uint32_t L, float* out, cudaStream_t stream);
 // Partial reset without a device allocation: the ids travel through a fixed device array of kStaticResetMaxIds words
 // that every world on `device` shares.  `device` must be current; r.env_ids is ignored.
 constexpr uint32_t kStaticResetMaxIds = 4096u;

@@ -470,6 +470,13 @@ void World::ResetStaticIds(const uint32_t* env_ids, uint32_t count) {
     Refresh();
 }
 
+void World::PackObservations(float* device_out) {
+    if (tpl_.L < 2u || !tpl_.floating_root) throw Error(kNotSupported, "observation records need a floating-base articulation");
+    Check(cudaSetDevice(device_), "cudaSetDevice");
+    Check(launch_pack_observations(params_.s, tpl_.L, device_out, stream_), "observation pack launch");
+    ++launches_;
+}
+
 void World::Synchronize() {
     Check(cudaSetDevice(device_), "cudaSetDevice");
     Check(cudaStreamSynchronize(stream_), "stream synchronize");

@@ -56,6 +56,8 @@ public:
     void Reset(const uint32_t* env_ids, uint32_t count);   // null ids: all envs
     void ResetStaticIds(const uint32_t* env_ids, uint32_t count);   // partial reset that allocates nothing
     void Synchronize();
+    uint32_t ObservationWidth() const { return tpl_.L >= 2u ? 3u * (tpl_.L - 1u) + 13u : 0u; }
+    void PackObservations(float* device_out);
     bool Field(uint32_t id, FieldInfo* out);
     void SetVelocityIterations(uint32_t n) { params_.t.cfg.vel_iters = n; graph_valid_ = false; }
     uint32_t VelocityIterations() const { return params_.t.cfg.vel_iters; }

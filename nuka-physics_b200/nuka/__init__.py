@@ -155,6 +155,15 @@ class World:
         ids = np.ascontiguousarray(env_ids, dtype=np.uint32)
         _check(_abi.lib().nuka_world_reset_envs(self._h, ids.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), ids.size))
 
+    def observation_width(self):
+        width = ctypes.c_uint32()
+        _check(_abi.lib().nuka_b200_world_pack_observations(self._h, None, 0, ctypes.byref(width)))
+        return width.value
+
+    def pack_observations(self, out):
+        """Fills `out` (a CUDA float32 tensor or any object with data_ptr()/numel(), E x observation_width) on the world's stream."""
+        _check(_abi.lib().nuka_b200_world_pack_observations(self._h, ctypes.c_void_p(out.data_ptr()), out.numel(), None))
+
     def reset_envs_static(self, env_ids):
         """reset_envs without any allocation (at most 4096 ids per call; calls on one device must not overlap)."""
         ids = np.ascontiguousarray(env_ids, dtype=np.uint32)

@@ -48,6 +48,7 @@ EXPORTS = [
     "nuka_world_reset", "nuka_world_reset_envs", "nuka_world_forward_kinematics", "nuka_world_get_stream", "nuka_world_record_event",
     "nuka_world_get_buffer_view", "nuka_world_upload_field", "nuka_world_download_field", "nuka_world_create_from_template",
     "nuka_b200_world_info", "nuka_b200_world_run_stage", "nuka_b200_world_launch_count", "nuka_b200_world_reset_envs_static",
+    "nuka_b200_world_pack_observations",
 ]
 
 _LIB = None
@@ -83,6 +84,7 @@ def lib():
     L.nuka_world_reset.argtypes = [vp]
     L.nuka_world_reset_envs.argtypes = [vp, ctypes.POINTER(u32), u32]
     L.nuka_b200_world_reset_envs_static.argtypes = [vp, ctypes.POINTER(u32), u32]
+    L.nuka_b200_world_pack_observations.argtypes = [vp, vp, sz, ctypes.POINTER(u32)]
     L.nuka_world_forward_kinematics.argtypes = [vp]
     L.nuka_world_get_stream.argtypes = [vp, ctypes.POINTER(vp)]
     L.nuka_world_record_event.argtypes = [vp, vp]

@@ -128,3 +128,23 @@ def test_scene_path_loads_a_cooked_template_file(device, tmp_path):
     w.step_n(3)
     assert np.isfinite(w.download(F.JOINT_POSITION)).all()
     w.destroy()
+
+
+def test_pack_observations_matches_the_host_side_layout(device):
+    import torch
+    from nuka import shard
+    E = 33
+    w = nuka.World.create_from_template(device, T.quadruped(0).blob(), E)
+    st = T.quadruped_state(E, 2)
+    w.upload(F.JOINT_POSITION, st["q"]); w.upload(F.BASE_POSE, st["base_pose"]); w.forward_kinematics()
+    w.step_n(3)
+    assert w.observation_width() == shard.RECORD_FLOATS
+    out = torch.zeros((E, shard.RECORD_FLOATS), dtype=torch.float32, device="cuda")
+    w.pack_observations(out); w.synchronize()
+    views = [w.view(f).torch() for f in (F.JOINT_POSITION, F.JOINT_VELOCITY, F.BASE_POSE, F.LINK_VELOCITY, F.DRIVE_TARGET)]
+    want = shard.pack_observations(torch.zeros_like(out), *views)
+    assert torch.equal(out, want)
+    small = torch.zeros(10, dtype=torch.float32, device="cuda")
+    with pytest.raises(nuka.NukaError):
+        w.pack_observations(small)
+    w.destroy()
