@@ -97,8 +97,9 @@ NKB_DEV void stage_fk(Env& e) {
         rpos = ld3(t.offset + 3u * l);
         rrot = ldq(t.local_quat + 4u * l);
         if (e.jtype == kRevolute) {
-            const float half = 0.5f * e.q, s = sinf(half);
-            rrot = qnorm_le(qmul(rrot, mkq(cosf(half), e.axis.x * s, e.axis.y * s, e.axis.z * s)), 1.0e-12f);
+            float s, c;
+            sincos_joint(0.5f * e.q, s, c);
+            rrot = qnorm_le(qmul(rrot, mkq(c, e.axis.x * s, e.axis.y * s, e.axis.z * s)), 1.0e-12f);
         } else if (e.jtype == kPrismatic) {
             rpos = rpos + qrot(rrot, e.axis * e.q);
         }

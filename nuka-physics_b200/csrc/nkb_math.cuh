@@ -88,11 +88,33 @@ NKB_DEV M3 m3_from_quat(Q4 q) {
     o.m[6] = 2.0f * (xz - wy); o.m[7] = 2.0f * (yz + wx); o.m[8] = 1.0f - 2.0f * (xx + yy);
     return o;
 }
+// sin and cos of a joint angle: three-term Cody-Waite reduction by pi/2 and the classic single-precision minimax
+// polynomials on [-pi/4, pi/4] (1-2 ulp for |x| up to a few thousand radians).  The library sinf/cosf carry a
+// large-argument path with a local-memory table that this kernel never needs.
+NKB_DEV void sincos_joint(float x, float& s, float& c) {
+    const float q = rintf(x * 0.636619772f);
+    const int quadrant = (int)q;
+    float r = fmaf(q, -1.57079601e+00f, x);
+    r = fmaf(q, -3.13916473e-07f, r);
+    r = fmaf(q, -5.39030253e-15f, r);
+    const float r2 = r * r;
+    float sp = fmaf(-1.9515295891e-4f, r2, 8.3321608736e-3f);
+    sp = fmaf(sp, r2, -1.6666654611e-1f);
+    sp = fmaf(sp * r2, r, r);
+    float cp = fmaf(2.443315711809948e-5f, r2, -1.388731625493765e-3f);
+    cp = fmaf(cp, r2, 4.166664568298827e-2f);
+    cp = fmaf(cp * r2, r2, fmaf(-0.5f, r2, 1.0f));
+    const float sv = (quadrant & 1) ? cp : sp, cv = (quadrant & 1) ? sp : cp;
+    s = (quadrant & 2) ? -sv : sv;
+    c = ((quadrant + 1) & 2) ? -cv : cv;
+}
 NKB_DEV M3 m3_axis_angle(V3 a, float angle) {
     const float l = dot(a, a);
     if (l <= 1.0e-12f) return m3_ident();
     a = a * rsqrtf(l);
-    const float c = cosf(angle), s = sinf(angle), t = 1.0f - c;
+    float s, c;
+    sincos_joint(angle, s, c);
+    const float t = 1.0f - c;
     M3 o;
     o.m[0] = t * a.x * a.x + c; o.m[1] = t * a.x * a.y - s * a.z; o.m[2] = t * a.x * a.z + s * a.y;
     o.m[3] = t * a.x * a.y + s * a.z; o.m[4] = t * a.y * a.y + c; o.m[5] = t * a.y * a.z - s * a.x;
