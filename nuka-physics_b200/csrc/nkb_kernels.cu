@@ -123,7 +123,12 @@ NKB_DEV void stage_store_bodies(Env& e, bool velocities) {
     }
 }
 
-__global__ void __maxnreg__(168) step_kernel(const __grid_constant__ StepParams p) {
+// The cap steers the compiler's allocation (measured best between 176 and 200: 156-167 registers, 12 warps per SM
+// stay resident; at 208 it takes 171 and residency halves).
+#ifndef NKB_MAXNREG
+#define NKB_MAXNREG 192
+#endif
+__global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ StepParams p) {
     extern __shared__ __align__(16) float smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t env = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -221,6 +226,19 @@ __global__ void reset_kernel(ResetParams r) {
         const uint32_t* src = reinterpret_cast<const uint32_t*>(fd.src);
         for (uint32_t k = threadIdx.x; k < fd.words; k += blockDim.x) dst[k] = fd.per_env_src ? src[(size_t)env * fd.words + k] : (fd.src != nullptr ? src[k] : fd.fill);
     }
+}
+
+int step_kernel_resident_blocks(uint32_t warps_per_block, size_t shared_bytes) {
+    if (shared_bytes > 48u * 1024u && cudaFuncSetAttribute(step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    int blocks = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, step_kernel, (int)(warps_per_block * 32u), shared_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return blocks;
 }
 
 cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {

@@ -90,7 +90,7 @@ NKB_DEV uint32_t stage_rows(Env& e, uint32_t pair_count) {
                 const double gamma = 3.0 * (double)FLT_EPSILON / (1.0 - 3.0 * (double)FLT_EPSILON);
                 const double roundoff = gamma * (fabs((double)nn.x) * (2.0 * fabs((double)ext.x)) + fabs((double)nn.y) * (2.0 * fabs((double)ext.y)) +
                                                  fabs((double)nn.z) * (2.0 * fabs((double)ext.z)));
-                const float clearance = roundoff > 0.0 ? nextafterf((float)roundoff, FLT_MAX) : 0.0f;
+                const float clearance = roundoff > 0.0 ? __int_as_float(__float_as_int((float)roundoff) + 1) : 0.0f;     // next float up
                 const float depth = cd + clearance;
                 hu(e, HF_FLAGS, h) = kHeadContact | kHeadContactNormal | kHeadSpeculative;
                 const uint32_t own1 = ob == oa ? kNoBlock16 : ob;

@@ -269,10 +269,8 @@ void World::BuildLayout() {
     size_t resident[kWarpsPerBlockMax + 1] = {0};
     size_t best = 0;
     for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) {
-        const size_t block = w * bytes + 1024u;
         if (w * bytes > 227u * 1024u) break;
-        const size_t blocks = std::min<size_t>(32, (228u * 1024u) / block);
-        resident[w] = std::min<size_t>(64, blocks * w);
+        resident[w] = static_cast<size_t>(step_kernel_resident_blocks(w, w * bytes)) * w;      // asks the runtime
         best = std::max(best, resident[w]);
     }
     warps_per_block_ = 1;

@@ -59,7 +59,7 @@ def lib():
     global _LIB
     if _LIB is not None:
         return _LIB
-    path = _build.LIB_PATH
+    path = os.environ.get("NUKA_B200_LIBRARY") or _build.LIB_PATH       # the variable selects an alternative build of the library
     if not os.path.exists(path):
         path = _build.build_native()
     L = ctypes.CDLL(path)
