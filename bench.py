@@ -149,8 +149,10 @@ def cpu_baseline():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    # defaults follow the reference's own harness for this metric: 100 warm-up + 1000 timed steps with hold drives
+    # (tests/perf/test_go2_4096env_step_time.cpp)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=100)
     ap.add_argument("--impl", default="native")
     ap.add_argument("--envs", type=int, default=ENVS_PER_GPU)
     ap.add_argument("--no-flush", action="store_true", help="skip the L2 flush between timed steps")
