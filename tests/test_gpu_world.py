@@ -148,3 +148,40 @@ def test_pack_observations_matches_the_host_side_layout(device):
     with pytest.raises(nuka.NukaError):
         w.pack_observations(small)
     w.destroy()
+
+
+def test_device_borrows_the_callers_stream(device):
+    """A device created over a caller's stream runs its worlds there (reference python/tests/test_caller_stream.py)
+    and produces the same bytes as a device with its own stream."""
+    torch = pytest.importorskip("torch")
+    stream = torch.cuda.Stream()
+    borrowed = nuka.Device.create(0, cuda_stream=stream.cuda_stream)
+    w = quad_world(borrowed, 24, 1)
+    got = ctypes.c_void_p()
+    assert _abi.lib().nuka_world_get_stream(w._h, ctypes.byref(got)) == _abi.OK
+    assert got.value == stream.cuda_stream
+    ref = quad_world(device, 24, 1)
+    w.step_n(7); ref.step_n(7)
+    stream.synchronize()                    # the caller's own synchronisation is enough to see the results
+    assert w.download(F.JOINT_POSITION).tobytes() == ref.download(F.JOINT_POSITION).tobytes()
+    w.destroy(); ref.destroy(); borrowed.destroy()
+
+
+def test_drive_targets_written_through_a_view_steer_the_next_step(device):
+    """DRIVE_TARGET is a writable input picked up by the following step (tests/c_abi/test_drive_target_io.cpp)."""
+    torch = pytest.importorskip("torch")
+    E = 8
+    w = quad_world(device, E, 0)
+    w.step_n(50)
+    before = w.download(F.JOINT_POSITION)
+    targets = w.view(F.DRIVE_TARGET).torch()
+    targets[:, 3] += 0.3                    # one thigh joint of every env
+    torch.cuda.synchronize()
+    w.step_n(60)
+    after = w.download(F.JOINT_POSITION)
+    moved = after[:, 3] - before[:, 3]
+    assert (moved > 0.1).all() and (moved < 0.4).all()
+    others = np.delete(after - before, 3, axis=1)
+    assert np.abs(others).max() < 0.1
+    assert w.download(F.ENV_STATUS).max() == 0
+    w.destroy()
