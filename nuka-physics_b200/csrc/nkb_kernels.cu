@@ -194,10 +194,10 @@ __global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ Ste
                 if (link == kNoLink) continue;
                 float* bp = sm_bpose(e, b);
                 const float* lp = sm_pose(e, link);
-                if (__ldg(t.geom_kind + link) != 0u) {
+                if (__ldg(t.body_geom_kind + b) != 0u) {
                     const Q4 pq = ldq(lp + 3);
-                    st3(bp, ld3(lp) + qrot(pq, ld3(t.geom_pos + 3u * link)));
-                    stq(bp + 3, qmul(pq, ldq(t.geom_quat + 4u * link)));
+                    st3(bp, ld3(lp) + qrot(pq, ld3(t.body_geom_pos + 3u * b)));
+                    stq(bp + 3, qmul(pq, ldq(t.body_geom_quat + 4u * b)));
                 } else {
 #pragma unroll
                     for (int k = 0; k < 7; ++k) bp[k] = lp[k];

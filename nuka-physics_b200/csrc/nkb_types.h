@@ -43,6 +43,8 @@ struct TemplateView {
     const uint32_t *dof_link, *anc_mask;
     const float *axis, *offset, *local_quat, *inertia10, *damping, *armature, *frictionloss, *stiffness, *spring_ref;
     const float *limit_lower, *limit_upper, *geom_pos, *geom_quat;
+    const uint32_t *body_geom_kind;     // B: nonzero when the row's shape has its own frame in the link
+    const float *body_geom_pos, *body_geom_quat;   // 3B, 4B
     const uint32_t *shape_kind, *contype, *conaffinity, *group, *body_to_link;
     const int32_t *body_id;
     const float *shape_params, *mu, *inv_mass, *inv_inertia, *inertial_pos, *inertial_quat;

@@ -87,6 +87,14 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
     t.limit_upper = BlobVec<float>(blob, bytes, "limit_upper", L);
     t.geom_pos = BlobVec<float>(blob, bytes, "geom_pos", 3 * L);
     t.geom_quat = BlobVec<float>(blob, bytes, "geom_quat", 4 * L);
+    {   // shape frames per collidable row: the template's own, or each link's single shape frame (filled below)
+        BlobEntry gk;
+        if (BlobFind(blob, bytes, "body_geom_kind", &gk)) {
+            t.body_geom_kind = BlobVec<uint32_t>(blob, bytes, "body_geom_kind", B);
+            t.body_geom_pos = BlobVec<float>(blob, bytes, "body_geom_pos", 3 * B);
+            t.body_geom_quat = BlobVec<float>(blob, bytes, "body_geom_quat", 4 * B);
+        }
+    }
     t.q0 = BlobVec<float>(blob, bytes, "q0", L);
     t.base_pose0 = BlobVec<float>(blob, bytes, "base_pose0", 7);
     t.kp0 = BlobVec<float>(blob, bytes, "kp0", L);
@@ -156,8 +164,19 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
             if (std::fabs(I[k] - ref[k]) > 1e-5f * scale) throw Error(kNotSupported, "link spatial inertia is not of rigid-body form");
     }
     // admissible body-row pairs
+    const bool own_frames = !t.body_geom_kind.empty() || B == 0u;
+    if (!own_frames) { t.body_geom_kind.assign(B, 0u); t.body_geom_pos.assign(3u * B, 0.f); t.body_geom_quat.assign(4u * B, 0.f); }
     for (uint32_t b = 0; b < B; ++b) {
         if (t.body_to_link[b] != kNoLink && t.body_to_link[b] >= L) throw Error(kParseError, "body_to_link out of range");
+        if (!own_frames) {
+            const uint32_t l = t.body_to_link[b];
+            t.body_geom_quat[4u * b] = 1.f;
+            if (l != kNoLink) {
+                t.body_geom_kind[b] = t.geom_kind[l];
+                for (int k = 0; k < 3; ++k) t.body_geom_pos[3u * b + k] = t.geom_pos[3u * l + k];
+                for (int k = 0; k < 4; ++k) t.body_geom_quat[4u * b + k] = t.geom_quat[4u * l + k];
+            }
+        }
         if (t.shape_kind[b] > kPlane) throw Error(kNotSupported, "shape kind without an analytic manifold");
     }
     for (uint32_t a = 0; a < B; ++a) for (uint32_t b = a + 1; b < B; ++b) {
@@ -294,6 +313,7 @@ World::World(int device, cudaStream_t stream, const HostTemplate& tpl, uint32_t 
         v.damping = Upload(t.damping); v.armature = Upload(t.armature); v.frictionloss = Upload(t.frictionloss);
         v.stiffness = Upload(t.stiffness); v.spring_ref = Upload(t.spring_ref); v.limit_lower = Upload(t.limit_lower);
         v.limit_upper = Upload(t.limit_upper); v.geom_pos = Upload(t.geom_pos); v.geom_quat = Upload(t.geom_quat);
+        v.body_geom_kind = Upload(t.body_geom_kind); v.body_geom_pos = Upload(t.body_geom_pos); v.body_geom_quat = Upload(t.body_geom_quat);
         v.shape_kind = Upload(t.shape_kind); v.contype = Upload(t.contype); v.conaffinity = Upload(t.conaffinity); v.group = Upload(t.group);
         v.body_to_link = Upload(t.body_to_link); v.body_id = Upload(t.body_id); v.shape_params = Upload(t.shape_params); v.mu = Upload(t.mu);
         v.inv_mass = Upload(t.inv_mass); v.inv_inertia = Upload(t.inv_inertia); v.inertial_pos = Upload(t.inertial_pos);

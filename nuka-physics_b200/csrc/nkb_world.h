@@ -30,6 +30,8 @@ struct HostTemplate {
     std::vector<float> shape_params, mu, inv_mass, inv_inertia, inertial_pos, inertial_quat, body_pose0;
     std::vector<unsigned long long> excluded;
     std::vector<uint32_t> adm_pairs;
+    std::vector<uint32_t> body_geom_kind;          // per collidable row (several rows may mirror one link)
+    std::vector<float> body_geom_pos, body_geom_quat;
     std::vector<uint32_t> free_slot;
     uint32_t n_free = 0;
     uint32_t joint_rows = 0;     // limit + friction + drive rows one env can emit

@@ -1,0 +1,172 @@
+"""Cooks the articulated part of a ``.nks`` scene (the reference's JSON scene format, src/scene/format/nks.cpp) into a
+template for this library.
+
+Covered: one tree of rigid bodies joined by revolute / prismatic / fixed joints under a free or static root, the
+bodies' inertial frames, joint axes, limits, damping, armature, initial positions, and every sphere / capsule / box
+collision shape with its local frame.  The frame rules are the reference's (runtime/articulation/
+articulation_state.cpp:392-426): parent-to-child is parent_frame * local_pose * joint(q), with parent_frame.position
+kept apart as the parent offset.  Not covered: meshes, cylinders, heightfields, sensors, materials other than the
+shapes' own friction, several trees, closed loops.
+
+Self-collision is off by default: the scene's shapes mix capsules and boxes, and capsule-box pairs need the convex
+narrowphase this library does not have.  Drives hold the initial joint positions with the given gains, as the
+reference's scene-derived hold drives do in its 4096-env gate.
+"""
+import json
+
+import numpy as np
+
+from . import templates as T
+
+
+def _quat_to_matrix(q):
+    w, x, y, z = (float(v) for v in q)
+    return np.array([[1 - 2 * (y * y + z * z), 2 * (x * y - w * z), 2 * (x * z + w * y)],
+                     [2 * (x * y + w * z), 1 - 2 * (x * x + z * z), 2 * (y * z - w * x)],
+                     [2 * (x * z - w * y), 2 * (y * z + w * x), 1 - 2 * (x * x + y * y)]])
+
+
+def _quat_mul(a, b):
+    aw, ax, ay, az = a
+    bw, bx, by, bz = b
+    return (aw * bw - ax * bx - ay * by - az * bz, aw * bx + ax * bw + ay * bz - az * by,
+            aw * by - ax * bz + ay * bw + az * bx, aw * bz + ax * by - ay * bx + az * bw)
+
+
+def _pose(record, key):
+    frame = record.get(key) or {}
+    return tuple(float(v) for v in frame.get("pos", (0, 0, 0))), tuple(float(v) for v in frame.get("quat", (1, 0, 0, 0)))
+
+
+_JOINT_TYPES = {"revolute": T.REVOLUTE, "hinge": T.REVOLUTE, "prismatic": T.PRISMATIC, "slide": T.PRISMATIC, "fixed": T.FIXED}
+
+
+def _shape_of(cs):
+    kind = cs.get("type")
+    if kind == "sphere":
+        return (T.SPHERE, float(cs["radius"]))
+    if kind == "capsule":
+        return (T.CAPSULE, float(cs["radius"]), float(cs["half_height"]))
+    if kind == "box":
+        return (T.BOX, *(float(v) for v in cs["half_extents"]))
+    raise ValueError(f"collision shape type {kind!r} has no analytic manifold here")
+
+
+def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0, ground_mu=1.0, self_collision=False,
+         max_contacts=None):
+    """``scene`` is a parsed .nks document (dict) or a path.  Returns a TemplateBuilder."""
+    if not isinstance(scene, dict):
+        with open(scene) as f:
+            scene = json.load(f)
+    if scene.get("nks_version") != 1:
+        raise ValueError("unsupported nks_version")
+    roots = [n for n in scene.get("tree", []) if "rigid_body" in n]
+    if len(roots) != 1:
+        raise ValueError("exactly one articulated tree is supported")
+    tb = T.TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=0)
+    shape_rows = []
+
+    def add(node, parent_link):
+        rb = node["rigid_body"]
+        pos, quat = _pose(node, "transform")
+        joint = node.get("joint")
+        if parent_link is None:
+            jtype = T.FIXED if rb.get("is_static") else T.FLOATING
+            tb.base_pose = [*pos, *quat]
+            local_pos, local_quat, offset, axis = (0.0, 0.0, 0.0), (1.0, 0.0, 0.0, 0.0), (0.0, 0.0, 0.0), (0.0, 0.0, 1.0)
+            if jtype == T.FIXED:
+                local_pos, local_quat = pos, quat
+        else:
+            if joint is None:
+                joint = {"type": "fixed"}
+            if joint.get("type") not in _JOINT_TYPES:
+                raise ValueError(f"joint type {joint.get('type')!r} is not supported")
+            jtype = _JOINT_TYPES[joint["type"]]
+            (ppos, pquat), (cpos, cquat) = _pose(joint, "parent_frame"), _pose(joint, "child_frame")
+            if np.abs(np.array(cpos)).max() > 0 or abs(abs(cquat[0]) - 1.0) > 1e-9:
+                raise ValueError("joints with a non-identity child frame are not supported")
+            rot = _quat_to_matrix(pquat)
+            local_pos = tuple(rot @ np.array(pos))
+            local_quat = _quat_mul(pquat, quat)
+            offset = ppos
+            axis = tuple(float(v) for v in joint.get("axis", (0, 0, 1)))
+        ipos, iquat = _pose(rb, "inertial")
+        R = _quat_to_matrix(iquat)
+        inertia = R @ np.diag([float(v) for v in rb.get("inertia", (0, 0, 0))]) @ R.T
+        shapes = [c["collision_shape"] for c in node.get("children", []) if "collision_shape" in c]
+        first = shapes[0] if shapes else None
+        single = jtype in (T.REVOLUTE, T.PRISMATIC)
+        lo, hi = (float(joint.get("lower_limit", 0.0)), float(joint.get("upper_limit", 0.0))) if single else (0.0, 0.0)
+        robot_bits = dict(contype=int(first.get("contype", 1)), conaffinity=int(first.get("conaffinity", 1))) if (first and self_collision) else dict(contype=1, conaffinity=0)
+        link = tb.add_link(parent_link, jtype, axis=axis, offset=offset, mass=float(rb.get("mass", 0.0)), inertia_diag=inertia, com=ipos,
+                           q0=float(joint.get("initial_position", 0.0)) if single else 0.0, kp=kp if single else 0.0, kd=kd if single else 0.0,
+                           damping=float(joint.get("damping", 0.0)) if single else 0.0, armature=float(joint.get("armature", 0.0)) if single else 0.0,
+                           limits=(lo, hi) if single and lo < hi else None,
+                           shape=_shape_of(first) if first else None,
+                           shape_pos=_pose(first, "local")[0] if first else (0, 0, 0), shape_quat=_pose(first, "local")[1] if first else (1, 0, 0, 0),
+                           mu=float(first.get("friction_mu", 1.0)) if first else 1.0, local_pos=local_pos, local_quat=local_quat, **robot_bits)
+        if single and float(joint.get("stiffness", 0.0)) != 0.0:
+            raise ValueError("joint springs are not carried over")
+        if first:
+            shape_rows.append(link)
+        for cs in shapes[1:]:
+            bits = dict(contype=int(cs.get("contype", 1)), conaffinity=int(cs.get("conaffinity", 1))) if self_collision else dict(contype=1, conaffinity=0)
+            tb.add_link_shape(link, _shape_of(cs), *_pose(cs, "local"), mu=float(cs.get("friction_mu", 1.0)), **bits)
+            shape_rows.append(link)
+        for child in node.get("children", []):
+            if "rigid_body" in child:
+                add(child, link)
+
+    add(roots[0], None)
+    tb.add_plane(ground_height, mu=ground_mu)
+    tb.cfg["max_contacts"] = int(max_contacts) if max_contacts is not None else max(len(shape_rows), 1)
+    return tb
+
+
+def link_names(scene):
+    """Names of the tree's bodies in link order (the order ``cook`` emits them)."""
+    if not isinstance(scene, dict):
+        with open(scene) as f:
+            scene = json.load(f)
+    names = []
+
+    def walk(node):
+        names.append(node.get("name", ""))
+        for child in node.get("children", []):
+            if "rigid_body" in child:
+                walk(child)
+
+    for root in scene.get("tree", []):
+        if "rigid_body" in root:
+            walk(root)
+    return names
+
+
+def initial_state(tb, env_count):
+    """Per-env q and base pose of the template's initial configuration (what nuka_world_reset restores)."""
+    a = tb.arrays()
+    q = np.tile(a["q0"].reshape(1, -1), (env_count, 1)).astype(np.float32)
+    base = np.tile(a["base_pose0"].reshape(1, 7), (env_count, 1)).astype(np.float32)
+    return {"q": q, "base_pose": base}
+
+
+def main(argv=None):
+    """``python -m nuka.nks scene.nks out.nkt``: cooks a scene file into a template file for nuka_world_create_from_scene."""
+    import argparse
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("scene")
+    ap.add_argument("out")
+    ap.add_argument("--dt", type=float, default=1.0 / 200.0)
+    ap.add_argument("--velocity-iterations", type=int, default=4)
+    ap.add_argument("--kp", type=float, default=60.0)
+    ap.add_argument("--kd", type=float, default=2.0)
+    ap.add_argument("--ground-height", type=float, default=0.0)
+    args = ap.parse_args(argv)
+    tb = cook(args.scene, dt=args.dt, vel_iters=args.velocity_iterations, kp=args.kp, kd=args.kd, ground_height=args.ground_height)
+    with open(args.out, "wb") as f:
+        f.write(tb.blob())
+    print(f"{args.out}: {len(tb.links)} links, {len(tb.bodies)} collidable rows")
+
+
+if __name__ == "__main__":
+    main()

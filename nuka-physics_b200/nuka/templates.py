@@ -21,12 +21,15 @@ FLT_BIG = 3.0e38
 
 
 def spatial_inertia(mass, diag, com):
-    """[[Icom + m(c.c 1 - c c^T), m c^x], [-m c^x, m 1]] about the link frame, angular-first."""
+    """[[Icom + m(c.c 1 - c c^T), m c^x], [-m c^x, m 1]] about the link frame, angular-first.
+
+    ``diag`` is the rotational inertia about the centre of mass in link axes: three principal moments, or a full 3x3."""
     c = np.asarray(com, dtype=np.float64)
     I = np.zeros((6, 6))
     if mass <= 0.0:
         return I.astype(np.float32)
-    I[:3, :3] = np.diag(diag) + mass * (c.dot(c) * np.eye(3) - np.outer(c, c))
+    diag = np.asarray(diag, dtype=np.float64)
+    I[:3, :3] = (np.diag(diag) if diag.ndim == 1 else diag) + mass * (c.dot(c) * np.eye(3) - np.outer(c, c))
     cx = np.array([[0, -c[2], c[1]], [c[2], 0, -c[0]], [-c[1], c[0], 0]])
     I[:3, 3:] = mass * cx
     I[3:, :3] = -mass * cx
@@ -42,6 +45,7 @@ def box_inertia(mass, size):
 class TemplateBuilder:
     def __init__(self, dt, vel_iters, pos_iters=32, gravity=(0.0, 0.0, -9.81), max_contacts=0, contact_margin=0.0):
         self.links, self.bodies, self.excluded = [], [], set()
+        self.extra_shapes = False
         self.cfg = dict(dt=dt, gravity=gravity, vel_iters=vel_iters, pos_iters=pos_iters, pos_beta=0.3, pos_slop=0.001,
                         contact_margin=contact_margin, baumgarte_max_velocity=FLT_BIG, overlap_recovery_velocity=0.0,
                         velocity_tolerance=1.0e-5, max_contacts=max_contacts, max_pairs=0)
@@ -63,11 +67,22 @@ class TemplateBuilder:
         self.bodies.append(dict(kind=kind, params=tuple(params) + (0.0,) * (4 - len(params)),
                                 contype=0 if shape is None else contype, conaffinity=0 if shape is None else conaffinity,
                                 group=0, body_id=body, link=index, mu=mu, inv_mass=0.0, inv_inertia=(0, 0, 0),
-                                inertial_pos=(0, 0, 0), inertial_quat=(1, 0, 0, 0), pose=(0, 0, 0, 1, 0, 0, 0)))
+                                inertial_pos=(0, 0, 0), inertial_quat=(1, 0, 0, 0), pose=(0, 0, 0, 1, 0, 0, 0),
+                                geom=0 if shape is None else 1, geom_pos=tuple(shape_pos), geom_quat=tuple(shape_quat)))
         if parent is not None:
             a, b = self.links[parent]["body"], body
             self.excluded.add((min(a, b) << 32) | max(a, b))
         return index
+
+    def add_link_shape(self, link, shape, shape_pos=(0, 0, 0), shape_quat=(1, 0, 0, 0), mu=1.0, contype=1, conaffinity=0, group=0):
+        """Adds one more collidable row to ``link``.  Rows of one link, and rows of a link and its parent, never pair."""
+        body = len(self.bodies)
+        self.bodies.append(dict(kind=shape[0], params=tuple(shape[1:]) + (0.0,) * (5 - len(shape)), contype=contype,
+                                conaffinity=conaffinity, group=group, body_id=body, link=link, mu=mu, inv_mass=0.0,
+                                inv_inertia=(0, 0, 0), inertial_pos=(0, 0, 0), inertial_quat=(1, 0, 0, 0),
+                                pose=(0, 0, 0, 1, 0, 0, 0), geom=1, geom_pos=tuple(shape_pos), geom_quat=tuple(shape_quat)))
+        self.extra_shapes = True
+        return body
 
     def add_free_body(self, shape, mass, inertia_diag, pose, mu=1.0, contype=1, conaffinity=1):
         body = len(self.bodies)
@@ -123,8 +138,24 @@ class TemplateBuilder:
             "body_id": np.array([b["body_id"] for b in self.bodies], dtype=np.int32),
             "shape_params": bf("params", 4), "mu": bf("mu"), "inv_mass": bf("inv_mass"), "inv_inertia": bf("inv_inertia", 3),
             "inertial_pos": bf("inertial_pos", 3), "inertial_quat": bf("inertial_quat", 4), "body_pose0": bf("pose", 7),
-            "excluded": np.array(sorted(self.excluded), dtype=np.uint64),
         }
+        excluded = set(self.excluded)
+        if self.extra_shapes:
+            # several rows per link: per-row shape frames, and no pairs inside a link or between a link and its parent
+            out["body_geom_kind"] = np.array([b.get("geom", 0) for b in self.bodies], dtype=u32)
+            out["body_geom_pos"] = np.array([b.get("geom_pos", (0, 0, 0)) for b in self.bodies], dtype=f32).reshape(B * 3)
+            out["body_geom_quat"] = np.array([b.get("geom_quat", (1, 0, 0, 0)) for b in self.bodies], dtype=f32).reshape(B * 4)
+            for a in range(B):
+                la = self.bodies[a]["link"]
+                if la == NOLINK:
+                    continue
+                for b in range(a + 1, B):
+                    lb = self.bodies[b]["link"]
+                    if lb == NOLINK:
+                        continue
+                    if la == lb or self.links[la]["parent"] == lb or self.links[lb]["parent"] == la:
+                        excluded.add((a << 32) | b)
+        out["excluded"] = np.array(sorted(excluded), dtype=np.uint64)
         return out
 
     def blob(self):

@@ -77,6 +77,9 @@ typedef struct orc_model {
     float *damping, *armature, *frictionloss, *stiffness, *spring_ref;
     float *limit_lower, *limit_upper;
     float *geom_pos, *geom_quat;
+    /* per collidable row: frame of the shape in its link (derived from the link arrays when the template has no
+     * body_geom_* fields); lets one link carry several shapes */
+    uint32_t *body_geom_kind; float *body_geom_pos, *body_geom_quat;
     float *q0, *base_pose0;
     float *kp0, *kd0, *force_limit0;
     /* bodies */

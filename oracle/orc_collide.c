@@ -6,12 +6,12 @@
 
 /* sync_body_pose.cu:24-50 SyncLinkBodyPoseKernel */
 void orc_sync_bodies(const orc_model *m, orc_env *e) {
-    for (uint32_t l = 0; l < m->L; ++l) {
-        const uint32_t b = m->link_body[l];
-        if (b >= m->B) continue;
-        if (m->geom_kind[l] != 0u) {
+    for (uint32_t b = 0; b < m->B; ++b) {
+        const uint32_t l = m->body_to_link[b];
+        if (l == ORC_NOLINK || l >= m->L) continue;
+        if (m->body_geom_kind[b] != 0u) {
             float local[7];
-            memcpy(local, m->geom_pos + 3 * l, 12); memcpy(local + 3, m->geom_quat + 4 * l, 16);
+            memcpy(local, m->body_geom_pos + 3 * b, 12); memcpy(local + 3, m->body_geom_quat + 4 * b, 16);
             pose_compose_hd(e->link_pose + 7 * l, local, e->body_pose + 7 * b);
         } else memcpy(e->body_pose + 7 * b, e->link_pose + 7 * l, 28);
     }

@@ -128,6 +128,23 @@ orc_world *orc_world_create(const void *blob_in, size_t bytes, uint32_t env_coun
     blob_entry ex;
     if (blob_find(blob, bytes, "excluded", &ex)) { m->excluded = (uint64_t *)ex.data; m->n_excluded = (uint32_t)ex.n; }
     if (!ok || m->cfg.max_contacts > 1024u) { orc_world_destroy(w); return NULL; }
+    /* shape frames per collidable row: the template's own, or each link's single shape frame */
+    m->body_geom_kind = (uint32_t *)calloc(B + 1, 4); m->body_geom_pos = (float *)calloc(3 * B + 3, 4); m->body_geom_quat = (float *)calloc(4 * B + 4, 4);
+    {
+        blob_entry gk, gp, gq;
+        const int own = blob_find(blob, bytes, "body_geom_kind", &gk) && gk.n == B && blob_find(blob, bytes, "body_geom_pos", &gp) && gp.n == 3u * B &&
+                        blob_find(blob, bytes, "body_geom_quat", &gq) && gq.n == 4u * B;
+        for (uint32_t b = 0; b < B; ++b) {
+            const uint32_t l = m->body_to_link[b];
+            if (own) {
+                m->body_geom_kind[b] = ((const uint32_t *)gk.data)[b];
+                memcpy(m->body_geom_pos + 3 * b, (const float *)gp.data + 3 * b, 12); memcpy(m->body_geom_quat + 4 * b, (const float *)gq.data + 4 * b, 16);
+            } else if (l != ORC_NOLINK && l < L) {
+                m->body_geom_kind[b] = m->geom_kind[l];
+                memcpy(m->body_geom_pos + 3 * b, m->geom_pos + 3 * l, 12); memcpy(m->body_geom_quat + 4 * b, m->geom_quat + 4 * l, 16);
+            } else m->body_geom_quat[4 * b] = 1.0f;
+        }
+    }
     /* derived tree tables (reference model.link_tree_depth / link_child_range / link_children) */
     m->depth = (uint32_t *)calloc(L + 1, 4); m->child_begin = (uint32_t *)calloc(L + 2, 4);
     m->children = (uint32_t *)calloc(L + 1, 4); m->link_dof = (uint32_t *)calloc(L + 1, 4);
@@ -154,6 +171,7 @@ void orc_world_destroy(orc_world *w) {
     if (!w) return;
     if (w->env) { for (uint32_t i = 0; i < w->E; ++i) env_free(&w->env[i]); free(w->env); }
     free(w->m.depth); free(w->m.child_begin); free(w->m.children); free(w->m.link_dof);
+    free(w->m.body_geom_kind); free(w->m.body_geom_pos); free(w->m.body_geom_quat);
     free(w->blob_copy); free(w);
 }
 

@@ -259,3 +259,35 @@ def test_every_analytic_pair_kind_matches_the_oracle(device, oracle):
     assert {(0, 2), (1, 0), (1, 1), (1, 3), (2, 3)} <= seen        # the sphere-plane kind shows up later in time
     assert w.download(F.ENV_STATUS).max() == 0
     w.destroy()
+
+
+def test_go2_scene_template(device, oracle):
+    """The reference's Go2 scene, cooked by nuka.nks into tests/golden/go2.nkt (23 collision shapes on 13 links,
+    joint limits, rotated inertial frames): per-stage and trajectory parity with the oracle, and it keeps standing."""
+    with open(os.path.join(GOLDEN, "go2.nkt"), "rb") as f:
+        blob = f.read()
+    E = 32
+    w = nuka.World.create_from_template(device, blob, E)
+    o = oracle.World(blob, E)
+    rng = np.random.Generator(np.random.PCG64(11))
+    q = w.download(F.JOINT_POSITION)
+    q[:, 1:] += rng.uniform(-0.05, 0.05, size=(E, 12)).astype(np.float32)
+    w.upload(F.JOINT_POSITION, q); o.set("q", q)
+    w.forward_kinematics(); o.refresh()
+    B, S = w.info.bodies_per_env, w.info.contact_slots_per_env
+    assert (B, w.info.dofs_per_env) == (24, 18)
+    assert rel(w.download(F.RIGID_BODY_TRANSFORM), o.get("body_pose", 7 * B)) < 1e-6
+    w.run_stage(1); o.dynamics(False)
+    assert rel(w.download(F.MASS_MATRIX), o.get("mass_matrix", 18 * 18)) < 1e-5
+    w.step_n(20); o.step(20)
+    assert rel(w.download(F.JOINT_POSITION), o.get("q", 13)) < 1e-4
+    assert rel(w.download(F.BASE_POSE), o.get("base_pose", 7)) < 1e-4
+    pc = w.download(F.PAIR_COUNT)
+    assert np.array_equal(pc, o.get("pair_count", 1))
+    live = np.arange(S)[None, :] < pc
+    assert np.array_equal(w.download(F.CONTACT_COUNT)[live], o.get("contact_count", S)[live])
+    w.step_n(400)
+    base = w.download(F.BASE_POSE)
+    assert (base[:, 2] > 0.22).all() and (base[:, 2] < 0.33).all() and (np.abs(base[:, 4:6]) < 0.1).all()
+    assert w.download(F.ENV_STATUS).max() == 0
+    w.destroy()
