@@ -43,7 +43,6 @@ NKB_DEV float* sm_pose(const Env& e, uint32_t l) { return e.sm + e.lay->pose + 7
 NKB_DEV float* sm_xrot(const Env& e, uint32_t l) { return e.sm + e.lay->xrot + 9u * l; }
 NKB_DEV float* sm_xtr(const Env& e, uint32_t l) { return e.sm + e.lay->xtr + 3u * l; }
 NKB_DEV float* sm_vel(const Env& e, uint32_t l) { return e.sm + e.lay->vel + 6u * l; }
-NKB_DEV float* sm_vbias(const Env& e, uint32_t l) { return e.sm + e.lay->vbias + 6u * l; }
 NKB_DEV float* sm_acc(const Env& e, uint32_t l) { return e.sm + e.lay->acc + 6u * l; }
 NKB_DEV float* sm_pbias(const Env& e, uint32_t l) { return e.sm + e.lay->pbias + 6u * l; }
 NKB_DEV float* sm_ic(const Env& e, uint32_t l) { return e.sm + e.lay->ic + 10u * l; }

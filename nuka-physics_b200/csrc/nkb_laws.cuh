@@ -32,59 +32,8 @@ NKB_DEV STerm scalar_impulse(float dual, float rho, float residual, float lower,
     return t;
 }
 
-NKB_DEV float cone_argument(float dual, float rho, float mu, float residual) {
-    float d = dual, d_low = 0.0f;      // exact for mu == 1 (isotropic friction), the common case
-    if (mu != 1.0f) {
-        const bool dual_zero = dual == 0.0f;
-        const float dual_quotient = __fdiv_rn(dual + (dual_zero ? 1.0f : 0.0f), mu);
-        d = dual_zero ? dual : dual_quotient;
-        const float low = fmaf(-d, mu, dual);
-        const bool low_zero = low == 0.0f;
-        const float low_quotient = __fdiv_rn(low + (low_zero ? 1.0f : 0.0f), mu);
-        d_low = low_zero ? low : low_quotient;
-    }
-    const float p = __fmul_rn(rho, mu);
-    const float t = __fmul_rn(p, residual);
-    const float t_low = __fadd_rn(fmaf(p, residual, -t), __fmul_rn(fmaf(rho, mu, -p), residual));
-    const float sum = __fadd_rn(d, t);
-    const float t_part = __fsub_rn(sum, d);
-    const float sum_low = __fadd_rn(__fsub_rn(d, __fsub_rn(sum, t_part)), __fsub_rn(t, t_part));
-    return __fadd_rn(sum, __fadd_rn(__fadd_rn(sum_low, d_low), t_low));
-}
-
-// impulse (y, z) and curvature (yy, zz, yz) of the friction rows at a fixed cone radius
-NKB_DEV void tangent_impulse(V3 dual, float rho, float res_y, float res_z, float normal_impulse, float mu_first, float mu_second,
-                             float& iy, float& iz, float& cyy, float& czz, float& cyz) {
-    iy = iz = cyy = czz = cyz = 0.f;
-    if (rho <= 0.0f) return;
-    const float scale = fmaxf(mu_first, mu_second);
-    const bool isotropic = mu_first == mu_second;
-    const float mu_y = mu_first <= 0.0f ? 0.0f : (isotropic ? 1.0f : mu_first / scale);
-    const float mu_z = mu_second <= 0.0f ? 0.0f : (isotropic ? 1.0f : mu_second / scale);
-    const float q_y = mu_y == 0.0f ? 0.0f : cone_argument(dual.y, rho, mu_y, res_y);
-    const float q_z = mu_z == 0.0f ? 0.0f : cone_argument(dual.z, rho, mu_z, res_z);
-    const float radius = (normal_impulse < 0.0f ? 0.0f : normal_impulse) * fmaxf(scale, 0.0f);
-    if (q_y != q_y || q_z != q_z || radius != radius || rho != rho) {
-        const float invalid = q_y + q_z + radius + rho;
-        iy = iz = cyy = czz = cyz = invalid;
-        return;
-    }
-    if (radius == 0.0f) return;
-    const float norm = sqrtf(fmaf(q_y, q_y, q_z * q_z));
-    if (norm <= radius) {
-        iy = mu_y * q_y; iz = mu_z * q_z;
-        cyy = rho * mu_y * mu_y; czz = rho * mu_z * mu_z;
-        return;
-    }
-    const float inv_norm = __frcp_rn(norm);
-    const float dy = q_y * inv_norm, dz = q_z * inv_norm, cs = rho * radius * inv_norm;
-    iy = mu_y * radius * dy; iz = mu_z * radius * dz;
-    cyy = cs * mu_y * mu_y * dz * dz;
-    czz = cs * mu_z * mu_z * dy * dy;
-    cyz = -cs * mu_y * mu_z * dy * dz;
-}
-
-// cone_argument at mu == 1: compensated dual + rho * residual, no divisions
+// The reference's cone argument (augmented_row.hpp:319-340) at a normalised coefficient of 1: compensated
+// dual + rho * residual, no divisions
 NKB_DEV float cone_argument_unit(float dual, float rho, float residual) {
     const float t = __fmul_rn(rho, residual);
     const float t_low = fmaf(rho, residual, -t);
@@ -94,9 +43,9 @@ NKB_DEV float cone_argument_unit(float dual, float rho, float residual) {
     return __fadd_rn(sum, __fadd_rn(sum_low, t_low));
 }
 
-// tangent_impulse for one isotropic friction coefficient, as the row evaluations of the Newton loop use it:
-// the same cone projection without the per-axis scaling, with the direction normalised by a reciprocal square
-// root.  Invalid inputs propagate as NaN through the arithmetic.
+// Impulse (y, z) and curvature (yy, zz, yz) of the friction rows at a fixed cone radius (augmented_row.hpp:341-363)
+// for one isotropic friction coefficient: the reference's projection without the per-axis scaling, the direction
+// normalised by a reciprocal square root.  Invalid inputs propagate as NaN through the arithmetic.
 NKB_DEV void cone_impulse(V3 dual, float rho, float res_y, float res_z, float normal_impulse, float mu,
                           float& iy, float& iz, float& cyy, float& czz, float& cyz) {
     iy = iz = cyy = czz = cyz = 0.f;
@@ -112,53 +61,9 @@ NKB_DEV void cone_impulse(V3 dual, float rho, float res_y, float res_z, float no
     cyy = cs * dz * dz; czz = cs * dy * dy; cyz = -cs * dy * dz;
 }
 
+// ---- dual update helpers (ops/block_descent.cu:759-820) for one friction coefficient per contact: the reference's
+// per-axis coefficients are both mu in this library, so its normalised coefficients are 1 and the divisions drop out ----
 struct Relax { V3 step; float weight; V3 point; };
-NKB_DEV V3 relax_contact_impulse(V3 dual, V3 next, Relax& last) {
-    const V3 step = next - dual;
-    const V3 change = step - last.step;
-    const V3 moved = dual - last.point;
-    const float square = change.x * change.x + change.y * change.y + change.z * change.z;
-    const float along = -(moved.x * change.x + moved.y * change.y + moved.z * change.z);
-    float weight = 1.0f;
-    if (last.weight > 0.0f && along > 0.0f && square > 0.0f) weight = fminf(1.0f, along / square);
-    last.step = step; last.weight = weight; last.point = dual;
-    return mk3(dual.x + weight * step.x, dual.y + weight * step.y, dual.z + weight * step.z);
-}
-
-NKB_DEV double momentum_restart(V3 point, V3 next, V3 base, V3 scale) {
-    return (scale.x > 0.0f ? ((double)point.x - next.x) * ((double)next.x - base.x) / scale.x : 0.0) +
-           (scale.y > 0.0f ? ((double)point.y - next.y) * ((double)next.y - base.y) / scale.y : 0.0) +
-           (scale.z > 0.0f ? ((double)point.z - next.z) * ((double)next.z - base.z) / scale.z : 0.0);
-}
-
-NKB_DEV void multiplier_steps(V3 dual, V3 next, float scale, float dual_scale, float rho, float mu1, float mu2, float& normal, float& tangent) {
-    normal = scale > 0.0f && dual_scale != 0.0f ? fabsf(next.x - dual.x) / scale : 0.0f;
-    const float fs = fmaxf(mu1, mu2);
-    mu1 = mu1 <= 0.0f ? 0.0f : mu1 / fs;
-    mu2 = mu2 <= 0.0f ? 0.0f : mu2 / fs;
-    const float first = mu1 > 0.0f && rho > 0.0f ? (next.y - dual.y) / (rho * mu1 * mu1) : 0.0f;
-    const float second = mu2 > 0.0f && rho > 0.0f ? (next.z - dual.z) / (rho * mu2 * mu2) : 0.0f;
-    tangent = hypotf(first, second);
-}
-NKB_DEV float along_axis(float impulse, float velocity) { return impulse > 0.0f ? velocity : impulse < 0.0f ? -velocity : 0.0f; }
-NKB_DEV V3 multiplier_metric(float scale, float rho, bool contact, float mu1, float mu2) {
-    const float fr = fmaxf(mu1, mu2);
-    const float first = contact && mu1 > 0.0f ? mu1 / fr : 0.0f;
-    const float second = contact && mu2 > 0.0f ? mu2 / fr : 0.0f;
-    return mk3(scale, rho * first * first, rho * second * second);
-}
-NKB_DEV V3 extrapolate_dual(V3 base, V3 next, float beta, float lower, float upper, bool contact, float mu1, float mu2) {
-    if (beta == 0.0f) return next;
-    V3 y = mk3(fmaf(beta, next.x - base.x, next.x), fmaf(beta, next.y - base.y, next.y), fmaf(beta, next.z - base.z, next.z));
-    y.x = fminf(fmaxf(y.x, lower), upper);
-    if (!contact) return mk3(y.x, 0.0f, 0.0f);
-    const float first = mu1 > 0.0f ? y.y / mu1 : 0.0f, second = mu2 > 0.0f ? y.z / mu2 : 0.0f;
-    const float slip = hypotf(first, second), radius = fmaxf(y.x, 0.0f);
-    const float scale = slip > radius ? radius / slip : 1.0f;
-    return mk3(y.x, mu1 > 0.0f ? y.y * scale : 0.0f, mu2 > 0.0f ? y.z * scale : 0.0f);
-}
-// ---- single-coefficient (isotropic) forms used by the per-sweep dual update: the per-axis coefficients of the
-// general laws above are both mu here, so the normalised coefficients are 1 and the divisions drop out ----
 NKB_DEV V3 relax_contact_impulse_fast(V3 dual, V3 next, Relax& last) {
     const V3 step = next - dual;
     const V3 change = step - last.step;
@@ -194,6 +99,7 @@ NKB_DEV V3 extrapolate_dual_iso(V3 base, V3 next, float beta, float lower, float
     return mk3(y.x, y.y * scale, y.z * scale);
 }
 
+NKB_DEV float along_axis(float impulse, float velocity) { return impulse > 0.0f ? velocity : impulse < 0.0f ? -velocity : 0.0f; }
 NKB_DEV float residual_abs(float v) { return v <= FLT_MAX ? fabsf(v) : FLT_MAX; }
 
 }  // namespace nkb

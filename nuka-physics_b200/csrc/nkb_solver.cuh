@@ -37,7 +37,6 @@ NKB_DEV uint32_t* block_order(const Env& e, uint32_t nb) { return unit_table(e, 
 NKB_DEV float* sm_bmass(const Env& e, uint32_t b) { return e.sm + e.lay->bmass + 7u * free_slot(e, b); }
 NKB_DEV float* sm_bfree(const Env& e, uint32_t b) { return e.sm + e.lay->bfree + 6u * free_slot(e, b); }
 NKB_DEV float* sm_bpseudo(const Env& e, uint32_t b) { return e.sm + e.lay->bpseudo + 6u * free_slot(e, b); }
-NKB_DEV float* sm_chol(const Env& e) { return e.sm + e.lay->chol; }
 
 NKB_DEV uint32_t head_axes(const Env& e, uint32_t h) { return (hu(e, HF_FLAGS, h) & (kHeadContact | kHeadScalar)) == kHeadContact ? 3u : 1u; }
 NKB_DEV uint32_t head_owner(const Env& e, uint32_t h, uint32_t side) { const uint32_t o = hu(e, HF_OWNER, h); return side == 0u ? (o & 0xffffu) : (o >> 16); }
