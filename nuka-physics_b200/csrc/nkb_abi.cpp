@@ -87,7 +87,8 @@ nuka_result_t ValidateDesc(const nuka_world_desc_t* d) {
     if (d->env_count == 0u) { SetError("env_count must be positive"); return NUKA_RESULT_INVALID_ARG; }
     if (d->determinism > 1u) { SetError("determinism must be 0 or 1"); return NUKA_RESULT_INVALID_ARG; }
     if (d->fixed_dt < 0.f || d->fixed_dt != d->fixed_dt) { SetError("fixed_dt must be positive"); return NUKA_RESULT_INVALID_ARG; }
-    if (d->control_mode != 0u) { SetError("only control mode 0 (PD position) is provided"); return NUKA_RESULT_NOT_SUPPORTED; }
+    if (d->control_mode > 5u) { SetError("control_mode must be 0..5"); return NUKA_RESULT_INVALID_ARG; }
+    if (d->control_mode > 2u) { SetError("control modes 3-5 (computed torque, OSC, actuator) are not provided"); return NUKA_RESULT_NOT_SUPPORTED; }
     const bool unsupported = d->terrain_step_height != 0.f || d->terrain_step_width != 0.f || d->terrain_platform_width != 0.f ||
         d->terrain_grid_width != 0.f || d->terrain_grid_height_max != 0.f || d->instance_count > 1u || d->contact_family != 0u ||
         d->heightfield_terrain_type != 0u || (d->heightfield_image_path != nullptr && d->heightfield_image_path[0] != '\0') ||
@@ -108,6 +109,7 @@ nuka_result_t CreateWorld(nuka_device_handle device, const nuka_world_desc_t* de
     return Guard([&]() {
         nkb::HostTemplate tpl = nkb::HostTemplate::Parse(blob, bytes);
         if (desc->fixed_dt > 0.f) tpl.cfg.dt = desc->fixed_dt;
+        tpl.cfg.control_mode = desc->control_mode;
         if (desc->gravity_x != 0.f || desc->gravity_y != 0.f || desc->gravity_z != 0.f) {
             tpl.cfg.gravity[0] = desc->gravity_x; tpl.cfg.gravity[1] = desc->gravity_y; tpl.cfg.gravity[2] = desc->gravity_z;
         }

@@ -146,7 +146,7 @@ NKB_DEV void joint_xform(const Env& e, float* E, V3& r) {
         for (int b = 0; b < 3; ++b) E[a * 3 + b] = rot.m[b * 3 + a];
 }
 
-// Implicit PD position drives, ops/articulation.cu:836-940 (control mode 0).
+// Affine joint drives, ops/articulation.cu:836-940: implicit PD position (mode 0), direct torque (1), velocity (2).
 NKB_DEV void stage_drives(Env& e) {
     const TemplateView& t = *e.t;
     const uint32_t l = e.lane;
@@ -156,10 +156,16 @@ NKB_DEV void stage_drives(Env& e) {
     const size_t at = (size_t)e.env * t.L + l;
     const float target = e.s->drive_target[at], kp = e.s->kp[at], kd = e.s->kd[at], vt = e.s->vel_target[at];
     const float limit = e.s->force_limit[at], ff = e.s->feedforward[at];
-    if (!isfinite(target) || !isfinite(kp) || kp < 0.f || !isfinite(kd) || kd < 0.f || !isfinite(vt)) { e.status |= kStatusControlFailure; return; }
+    const uint32_t mode = t.cfg.control_mode;
+    const bool position_control = mode == 0u, velocity_control = mode == 2u;
+    if ((position_control && (!isfinite(target) || !isfinite(kp) || kp < 0.f || !isfinite(kd) || kd < 0.f)) ||
+        ((position_control || velocity_control) && !isfinite(vt)) || (velocity_control && (!isfinite(kp) || kp < 0.f))) {
+        e.status |= kStatusControlFailure; return;
+    }
     float lower = limit > 0.f ? -limit : -FLT_MAX, upper = limit > 0.f ? limit : FLT_MAX;
-    float damping = kd + t.cfg.dt * kp;
-    float bias = kp * (target - e.q) + damping * vt;
+    float damping = 0.f, bias = target;                       // torque mode: the target field carries the commanded effort
+    if (position_control) { damping = kd + t.cfg.dt * kp; bias = kp * (target - e.q) + damping * vt; }
+    else if (velocity_control) { damping = kp; bias = damping * vt; }
     const float effort = bias - damping * e.qd;
     if (effort < lower || effort > upper) { bias = effort; damping = 0.f; }
     else { lower += damping * e.qd; upper += damping * e.qd; }

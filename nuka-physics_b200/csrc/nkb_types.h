@@ -32,6 +32,7 @@ struct Config {
     float gravity[3];
     float pos_beta, pos_slop, contact_margin, baumgarte_max_velocity, overlap_recovery_velocity, velocity_tolerance;
     uint32_t vel_iters, pos_iters, max_contacts, max_pairs;
+    uint32_t control_mode;      // 0 PD position, 1 torque, 2 velocity (reference phi/articulation_contract.hpp:16-23)
 };
 
 // Device pointers to the template tables (read-only during a step).

@@ -63,6 +63,7 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
     t.cfg.pos_beta = cf[4]; t.cfg.pos_slop = cf[5]; t.cfg.contact_margin = cf[6];
     t.cfg.baumgarte_max_velocity = cf[7]; t.cfg.overlap_recovery_velocity = cf[8]; t.cfg.velocity_tolerance = cf[9];
     t.cfg.vel_iters = cu[0]; t.cfg.pos_iters = cu[1]; t.cfg.max_contacts = cu[2]; t.cfg.max_pairs = cu[3];
+    t.cfg.control_mode = 0u;       // the world descriptor selects another mode
     t.L = cu[4]; t.B = cu[5];
     const uint32_t L = t.L, B = t.B;
     if (L > kMaxLinks) throw Error(kNotSupported, "more than 32 links per env");

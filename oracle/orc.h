@@ -61,6 +61,7 @@ typedef struct orc_config {
     float velocity_tolerance;
     uint32_t max_contacts;      /* candidate slots per env */
     uint32_t max_pairs;         /* 0: same as max_contacts */
+    uint32_t control_mode;      /* 0 PD position, 1 torque, 2 velocity (phi/articulation_contract.hpp:16-23) */
 } orc_config;
 
 /* One env's cooked template (reference src/nk/model/model.hpp:175-244, 488-548). */

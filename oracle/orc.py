@@ -24,6 +24,7 @@ def lib():
         L.orc_world_create.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_uint32]
         L.orc_world_destroy.argtypes = [ctypes.c_void_p]
         L.orc_world_reset.argtypes = [ctypes.c_void_p]
+        L.orc_world_set_control_mode.argtypes = [ctypes.c_void_p, ctypes.c_uint32]
         L.orc_world_refresh.argtypes = [ctypes.c_void_p]
         L.orc_world_step.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_int]
         L.orc_stage_dynamics.argtypes = [ctypes.c_void_p, ctypes.c_int]
@@ -55,6 +56,9 @@ class World:
 
     def step(self, n=1, threads=0):
         lib().orc_world_step(self._h, n, threads)
+
+    def set_control_mode(self, mode):
+        lib().orc_world_set_control_mode(self._h, int(mode))
 
     def reset(self):
         lib().orc_world_reset(self._h)

@@ -54,8 +54,12 @@ void orc_apply_drives(const orc_model *m, orc_env *e) {
         e->drive_lower[l] = e->drive_upper[l] = 0.0f;
         e->tau[l] = 0.0f;
         if (joint_dofs(m->jtype[l]) != 1u) continue;
-        if (!isfinite(e->drive_target[l]) || !isfinite(e->kp[l]) || e->kp[l] < 0.0f ||
-            !isfinite(e->kd[l]) || e->kd[l] < 0.0f || !isfinite(e->vel_target[l])) {
+        const uint32_t mode = m->cfg.control_mode;
+        const int position_control = mode == 0u, velocity_control = mode == 2u;
+        if ((position_control && (!isfinite(e->drive_target[l]) || !isfinite(e->kp[l]) || e->kp[l] < 0.0f ||
+                                  !isfinite(e->kd[l]) || e->kd[l] < 0.0f)) ||
+            ((position_control || velocity_control) && !isfinite(e->vel_target[l])) ||
+            (velocity_control && (!isfinite(e->kp[l]) || e->kp[l] < 0.0f))) {
             e->status |= ORC_STATUS_CONTROL_FAILURE;
             continue;
         }
@@ -63,8 +67,14 @@ void orc_apply_drives(const orc_model *m, orc_env *e) {
         const float limit = e->force_limit[l];
         float lower = limit > 0.0f ? -limit : -FLT_MAX;
         float upper = limit > 0.0f ? limit : FLT_MAX;
-        float damping = e->kd[l] + dt * e->kp[l];
-        float bias = e->kp[l] * (e->drive_target[l] - e->q[l]) + damping * e->vel_target[l];
+        float damping = 0.0f, bias = 0.0f;
+        if (position_control) {
+            damping = e->kd[l] + dt * e->kp[l];
+            bias = e->kp[l] * (e->drive_target[l] - e->q[l]) + damping * e->vel_target[l];
+        } else if (velocity_control) {
+            damping = e->kp[l];
+            bias = damping * e->vel_target[l];
+        } else bias = e->drive_target[l];          /* torque: the target field carries the commanded effort */
         const float effort = bias - damping * velocity;
         const int saturated = effort < lower || effort > upper;
         if (saturated) {

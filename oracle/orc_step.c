@@ -175,6 +175,9 @@ void orc_world_destroy(orc_world *w) {
     free(w->blob_copy); free(w);
 }
 
+/* control mode of every env: 0 PD position, 1 torque, 2 velocity; other values are ignored */
+void orc_world_set_control_mode(orc_world *w, uint32_t mode) { if (mode <= 2u) w->m.cfg.control_mode = mode; }
+
 void orc_world_reset(orc_world *w) { for (uint32_t i = 0; i < w->E; ++i) env_seed(&w->m, &w->env[i]); }
 void orc_world_refresh(orc_world *w) { for (uint32_t i = 0; i < w->E; ++i) { orc_fk(&w->m, &w->env[i]); orc_sync_bodies(&w->m, &w->env[i]); } }
 

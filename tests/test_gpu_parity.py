@@ -291,3 +291,37 @@ def test_go2_scene_template(device, oracle):
     assert (base[:, 2] > 0.22).all() and (base[:, 2] < 0.33).all() and (np.abs(base[:, 4:6]) < 0.1).all()
     assert w.download(F.ENV_STATUS).max() == 0
     w.destroy()
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_torque_and_velocity_control_modes(device, oracle, mode):
+    """control_mode 1 (the target field is a joint torque) and 2 (velocity servo with gain kp): trajectories of the
+    standing quadruped under each mode follow the oracle's."""
+    E = 48
+    tb = T.quadruped(0)
+    blob = tb.blob()
+    w = nuka.World.create_from_template(device, blob, E, control_mode=mode)
+    o = oracle.World(blob, E)
+    o.set_control_mode(mode)
+    st = T.quadruped_state(E, 6)
+    rng = np.random.Generator(np.random.PCG64(20 + mode))
+    target = np.zeros((E, 13), np.float32)
+    vt = np.zeros((E, 13), np.float32)
+    if mode == 1:
+        target[:, 1:] = rng.uniform(-3.0, 3.0, size=(E, 12))          # joint torques, N m
+    else:
+        vt[:, 1:] = rng.uniform(-0.5, 0.5, size=(E, 12))              # joint velocity targets, rad/s
+    for world_set, oracle_name, value in ((F.JOINT_POSITION, "q", st["q"]), (F.BASE_POSE, "base_pose", st["base_pose"]),
+                                          (F.DRIVE_TARGET, "drive_target", target), (F.VELOCITY_TARGET, "velocity_target", vt)):
+        w.upload(world_set, value); o.set(oracle_name, value.reshape(E, -1))
+    w.forward_kinematics(); o.refresh()
+    w.step_n(1); o.step(1)
+    # the velocity servo (gain 40 on every joint) makes the step stiffer than the PD hold: 5e-5 there, 2e-5 for torques
+    assert rel(w.download(F.JOINT_VELOCITY), o.get("qdot", 13)) < (2e-5 if mode == 1 else 5e-5)
+    w.step_n(19); o.step(19)
+    assert rel(w.download(F.JOINT_POSITION), o.get("q", 13)) < 1e-4
+    assert rel(w.download(F.BASE_POSE), o.get("base_pose", 7)) < 1e-4
+    assert w.download(F.ENV_STATUS).max() == 0
+    moved = np.abs(w.download(F.JOINT_POSITION)[:, 1:] - st["q"][:, 1:]).max()
+    assert moved > 0.01                                               # the commands really drive the joints
+    w.destroy()
