@@ -1,6 +1,6 @@
 """Cooks the reference's Go2 scene (examples/scenes/go2.nks) into tests/golden/go2.nkt.
 
-Run in a checkout that has the reference tree; the GPU box only sees the cooked template.  The scene's joint
+Run with NUKA_REFERENCE_ROOT pointing at a checkout of the reference; tests only need the cooked template.  The scene's joint
 positions are all zero, which violates the calf limits, so the template starts from the robot's usual standing
 pose (hip 0, thigh 0.9, calf -1.8 rad, base 0.30 m above the ground) and its drives hold that pose.
 """
@@ -12,7 +12,7 @@ sys.path.insert(0, os.path.join(HERE, "..", "..", "nuka-physics_b200"))
 
 from nuka import nks  # noqa: E402
 
-SCENE = os.environ.get("NUKA_REFERENCE_ROOT", "/root/reference") + "/examples/scenes/go2.nks"
+SCENE = os.path.join(os.environ.get("NUKA_REFERENCE_ROOT", ""), "examples", "scenes", "go2.nks")
 STANCE = {"hip": 0.0, "thigh": 0.9, "calf": -1.8}
 
 
