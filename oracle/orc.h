@@ -8,9 +8,11 @@
  *
  * Pin status: the reference has no CPU implementation of this path and its MJX
  * golden trajectories are Git-LFS pointers only, so this restatement is pinned on
- * the closed-form expectations of the reference's own tests (see tests/): the
- * solref/solimp hand table, analytic manifold cases, brute-force pair sets,
- * momentum exchange, resting contact, rotated-gravity covariance, M == d(RNEA)/dqdd.
+ * the closed-form expectations of the reference's own tests (see tests/): analytic
+ * manifold cases, the friction-cone / relaxation / momentum-restart cases of
+ * tests/math/test_contact_tangent.cpp, the contact-identity rules of
+ * tests/constraint/test_contact_identity.cpp, brute-force pair sets, momentum
+ * exchange, resting contact, rotated-gravity covariance, M qdd == tau - bias.
  * Numerical agreement with MuJoCo itself is "parity unpinned".
  *
  * Conventions (reference src/math/cuda_spatial_ops.cuh:1-30, nuka.h:498):

@@ -501,6 +501,18 @@ void orc_narrowphase(const orc_model *m, orc_env *e) {
     }
 }
 
+/* Known-answer access for tests: the contact identity of one point (nk/contact/contact_identity.hpp), as the
+ * narrowphase composes it: feature 0xffffffff means "no stable feature", then the quantised local points decide. */
+uint64_t orc_contact_identity(uint32_t feature, const float *local_a, const float *local_b, uint32_t slot) {
+    uint64_t h = 1469598103934665603ull;
+    h = hash_word(h, feature_token(feature, v3ld(local_a)));
+    h = hash_word(h, feature_token(feature, v3ld(local_b)));
+    h = hash_word(h, slot);
+    h = hash_word(h, 0u);
+    h = hash_word(h, 0u);
+    return h;
+}
+
 /* Known-answer access for tests: one analytic pair. pose = xyz + wxyz, params = shape_params (4).
  * out: count, then per point position(3) normal(3) penetration(1) (raw manifold, no separation shell). */
 int orc_manifold(uint32_t kind_a, const float *pose_a, const float *params_a, uint32_t kind_b, const float *pose_b,

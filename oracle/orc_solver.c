@@ -769,3 +769,28 @@ void orc_solve(const orc_model *m, orc_env *e) {
     }
     free(jac_pool); free(t.heads); free(inc_pool); free(rigid_mass); free(t.blocks);
 }
+
+
+/* Known-answer access for tests: the row laws of nk/solve/augmented_row.hpp.
+ * which 0: momentum_restart(point, next, base, scale) -> out[0] (in: 12 floats)
+ * which 1: two relaxation steps of tests/math/test_contact_tangent.cpp:20-35 (in[0] = beta) -> root xyz, weight
+ * which 2: tangent_impulse(dual 0, rho in[0], residual in[1..3], normal in[4], mu in[5] both axes) -> iy, iz, yy, zz, yz */
+void orc_law_kat(int which, const float *in, double *out) {
+    if (which == 0) {
+        out[0] = momentum_restart(V3(in[0], in[1], in[2]), V3(in[3], in[4], in[5]), V3(in[6], in[7], in[8]), V3(in[9], in[10], in[11]));
+    } else if (which == 1) {
+        relax_t history;
+        memset(&history, 0, sizeof history);
+        const v3 start = V3(10.0f, 1.0f, 0.0f);
+        const v3 first = relax_contact_impulse(start, V3(10.0f, -2.0f, 0.0f), &history);
+        const v3 point = V3(first.x + (first.x - start.x) * in[0], first.y + (first.y - start.y) * in[0], first.z + (first.z - start.z) * in[0]);
+        const v3 root = relax_contact_impulse(point, V3(10.0f, -2.0f * point.y, 0.0f), &history);
+        out[0] = root.x; out[1] = root.y; out[2] = root.z; out[3] = history.weight;
+    } else if (which == 2) {
+        v3 impulse = V3(0, 0, 0);
+        sym3 curv;
+        memset(&curv, 0, sizeof curv);
+        tangent_impulse(V3(0, 0, 0), in[0], V3(in[1], in[2], in[3]), in[4], in[5], in[5], &impulse, &curv);
+        out[0] = impulse.y; out[1] = impulse.z; out[2] = curv.yy; out[3] = curv.zz; out[4] = curv.yz;
+    }
+}

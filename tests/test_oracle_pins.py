@@ -250,3 +250,74 @@ def test_rotated_gravity_covariance(oracle):
     (p0, q0), (p1, q1) = results
     assert np.allclose(R @ p0[:3].astype(np.float64), p1[:3], atol=2e-5)
     assert np.allclose(q0, q1, atol=2e-5)
+
+
+# ---- row laws and contact identity: the expectations of tests/math/test_contact_tangent.cpp and
+# ---- tests/constraint/test_contact_identity.cpp of the reference, evaluated on the oracle's restatements
+
+def _law(oracle, which, values):
+    import ctypes
+    lib = oracle.lib()
+    lib.orc_law_kat.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_double)]
+    lib.orc_law_kat.restype = None
+    arr = (ctypes.c_float * max(len(values), 1))(*values)
+    out = (ctypes.c_double * 8)()
+    lib.orc_law_kat(which, arr, out)
+    return list(out)
+
+
+def test_momentum_restart_signs(oracle):
+    # test_contact_tangent.cpp:8-18
+    scale = [2.0, 4.0, 0.0]
+    assert _law(oracle, 0, [1.0, 2.0, 0.0, 0.8, 1.8, 0.0, 1.1, 2.1, 0.0] + scale)[0] < 0.0
+    assert _law(oracle, 0, [0.4, 1.4, 0.0, 0.5, 1.5, 0.0, 0.8, 1.8, 0.0] + scale)[0] > 0.0
+    assert _law(oracle, 0, [1.0, 2.0, 3.0, 1.0, 2.0, 3.0, 0.0, 0.0, 0.0] + scale)[0] == 0.0
+
+
+def test_relaxation_finds_the_linear_root(oracle):
+    # test_contact_tangent.cpp:20-35
+    for beta in (0.0, 0.5):
+        x, y, z, weight = _law(oracle, 1, [beta])[:4]
+        assert x == 10.0 and abs(y) <= 5.0e-7 and z == 0.0
+        assert abs(weight - 1.0 / 3.0) <= 1.0e-7
+        assert y * y + z * z <= x * x
+
+
+def test_collapsed_friction_sets_have_zero_response(oracle):
+    # test_contact_tangent.cpp:37-63 (EvaluateTangentImpulse leg): zero normal impulse -> no tangent response
+    for mu in (1.1e-5, 0.5, 2.0):
+        for value in (0.0, 0.1):
+            assert _law(oracle, 2, [10.0, 0.0, value, -value, 0.0, mu])[:5] == [0.0] * 5
+
+
+def test_friction_magnitude_and_coulomb_limit(oracle):
+    # test_contact_tangent.cpp:65-90 (EvaluateTangentImpulse leg)
+    for mu in (1.1e-5, 0.5, 2.0):
+        normal, rho = 0.05, 10.0
+        radius = np.float32(mu) * np.float32(normal)
+        for fraction in (0.25, 2.0):
+            residual = [0.0, 0.6 * fraction * radius / rho, 0.8 * fraction * radius / rho]
+            magnitude = radius * min(fraction, 1.0)
+            iy, iz, yy, zz, yz = _law(oracle, 2, [rho] + residual + [normal, mu])[:5]
+            assert abs(iy - 0.6 * magnitude) <= radius * 2.0e-6 and abs(iz - 0.8 * magnitude) <= radius * 2.0e-6
+            if fraction < 1.0:
+                assert abs(yy - rho) <= 2.0e-5 and abs(zz - rho) <= 2.0e-5
+
+
+def test_contact_identity_rules(oracle):
+    # test_contact_identity.cpp:47-66: stable features override point motion; without features the quantised
+    # local points decide (1/4096 bins)
+    import ctypes
+    lib = oracle.lib()
+    lib.orc_contact_identity.argtypes = [ctypes.c_uint32, ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float), ctypes.c_uint32]
+    lib.orc_contact_identity.restype = ctypes.c_uint64
+
+    def ident(feature, a, b, slot=2):
+        return lib.orc_contact_identity(feature, (ctypes.c_float * 3)(*a), (ctypes.c_float * 3)(*b), slot)
+
+    a, b = (0.1, -0.2, 0.3), (-0.4, 0.5, -0.6)
+    assert ident(7, a, b) == ident(7, (2.0, 3.0, 4.0), (-2.0, -3.0, -4.0))
+    none = 0xffffffff
+    assert ident(none, a, b) == ident(none, (0.1 + 0.00001, -0.2, 0.3), b)
+    assert ident(none, a, b) != ident(none, (0.1 + 0.001, -0.2, 0.3), b)
+    assert ident(7, a, b, 2) != ident(7, a, b, 3) and ident(7, a, b) != ident(8, a, b)
