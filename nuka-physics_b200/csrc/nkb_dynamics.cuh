@@ -23,9 +23,9 @@ struct Env {
     float q, qd, qdd, tau;
     V3 axis;                 // unit joint axis in the link frame
     float drive_command, drive_dissipation, drive_lower, drive_upper;
-    // lane = dof
-    uint32_t dof_link, dof_comp;   // comp == kNoLink for scalar joints
-    float vel0;              // step-start coordinate velocity
+    // lane = dof: a lane owns coordinates lane and lane + 32 (the second only when the articulation has more than 32)
+    uint32_t dof_link[2], dof_comp[2];   // comp == kNoLink for scalar joints
+    float vel0[2];           // step-start coordinate velocity
     uint32_t status;
     uint32_t* cyc;           // stage cycle counters of this env, or null
     long long t0;
@@ -48,7 +48,13 @@ NKB_DEV float* sm_pbias(const Env& e, uint32_t l) { return e.sm + e.lay->pbias +
 NKB_DEV float* sm_ic(const Env& e, uint32_t l) { return e.sm + e.lay->ic + 10u * l; }
 NKB_DEV float* sm_mass(const Env& e) { return e.sm + e.lay->mass; }
 NKB_DEV float* sm_factor(const Env& e) { return e.sm + e.lay->factor; }
-NKB_DEV float* sm_vec(const Env& e, uint32_t k) { return e.sm + e.lay->vecs + 32u * k; }
+NKB_DEV float* sm_vec(const Env& e, uint32_t k) { return e.sm + e.lay->vecs + e.lay->vstride * k; }   // 32 or 64 words per vector
+// value of coordinate j from per-lane registers x[r] (coordinate lane + 32 r)
+template <int NR>
+NKB_DEV float coord_bcast(const float (&x)[NR], uint32_t j) {
+    if (NR == 1) return __shfl_sync(NKB_FULL, x[0], j);
+    return __shfl_sync(NKB_FULL, j < 32u ? x[0] : x[NR - 1], j & 31u);
+}
 // vector slots
 enum { kVecBias = 0, kVecAcc = 1, kVecFree = 2, kVecU = 3, kVecD = 4, kVecPseudo = 5, kVecTmp = 6, kVecTmp2 = 7,
        // Newton-loop scratch shares slots whose other users run before or after the solve
@@ -75,11 +81,15 @@ NKB_DEV void env_begin(Env& e, const StepParams& p, float* sm, uint32_t env, uin
     e.qd = link ? p.s.qdot[at] : 0.f;
     e.qdd = 0.f; e.tau = 0.f;
     e.drive_command = e.drive_dissipation = e.drive_lower = e.drive_upper = 0.f;
-    const bool dof = lane < t.ndof;
-    e.dof_link = dof ? __ldg(t.dof_link + lane) : 0u;
-    e.dof_comp = kNoLink;
-    if (dof && __ldg(t.jtype + e.dof_link) == kFloating) e.dof_comp = lane - __ldg(t.link_dof + e.dof_link);
-    e.vel0 = 0.f;
+#pragma unroll
+    for (uint32_t r = 0u; r < 2u; ++r) {
+        const uint32_t c = lane + 32u * r;
+        const bool dof = c < t.ndof;
+        e.dof_link[r] = dof ? __ldg(t.dof_link + c) : 0u;
+        e.dof_comp[r] = kNoLink;
+        if (dof && __ldg(t.jtype + e.dof_link[r]) == kFloating) e.dof_comp[r] = c - __ldg(t.link_dof + e.dof_link[r]);
+        e.vel0[r] = 0.f;
+    }
     e.status = 0u;
     e.cyc = p.s.dbg_cycles != nullptr ? p.s.dbg_cycles + (size_t)env * 32u : nullptr;
     e.t0 = clock64();
@@ -178,6 +188,7 @@ NKB_DEV void stage_drives(Env& e) {
 
 // Bias forces, mass matrix, factor and unconstrained acceleration; optionally the semi-implicit velocity
 // update.  Leaves M and its L D L^T factor in shared memory for the constraint solve.
+template <int NR>
 NKB_DEV void stage_dynamics(Env& e, bool integrate_velocity) {
     const TemplateView& t = *e.t;
     const uint32_t l = e.lane, L = t.L, n = t.ndof, ld = e.lay->ld;
@@ -267,32 +278,38 @@ NKB_DEV void stage_dynamics(Env& e, bool integrate_velocity) {
         __syncwarp();
     }
     // generalized bias and right-hand side, lane = coordinate
-    const float diss_of_link = __shfl_sync(NKB_FULL, e.drive_dissipation, e.dof_link);
-    const float tau_of_link = __shfl_sync(NKB_FULL, e.tau, e.dof_link);
-    const float qd_of_link = __shfl_sync(NKB_FULL, e.qd, e.dof_link);
-    const float q_of_link = __shfl_sync(NKB_FULL, e.q, e.dof_link);
-    float rhs = 0.f;
-    const bool dof = l < n;
-    if (dof) {
-        const uint32_t dl = e.dof_link;
-        const float* pb = sm_pbias(e, dl);
-        float bias;
-        if (e.dof_comp == kNoLink) {
-            V3 a = ld3(t.axis + 3u * dl);
-            const float ls = dot(a, a);
-            if (ls > 1.0e-12f) a = a * rsqrtf(ls);
-            const uint32_t jt = __ldg(t.jtype + dl);
-            bias = jt == kRevolute ? dot(a, ld3(pb)) : dot(a, ld3(pb + 3));
-            e.vel0 = qd_of_link;
-            const float damping = __ldg(t.damping + dl) + diss_of_link;
-            const float spring = __ldg(t.stiffness + dl) * (q_of_link - __ldg(t.spring_ref + dl));
-            rhs = tau_of_link - bias - damping * e.vel0 - spring;
-        } else {
-            bias = pb[e.dof_comp];
-            e.vel0 = sm_vel(e, dl)[e.dof_comp];
-            rhs = -bias;
+    float rhs[NR];
+    bool dof[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const uint32_t c = l + 32u * r;
+        const float diss_of_link = __shfl_sync(NKB_FULL, e.drive_dissipation, e.dof_link[r]);
+        const float tau_of_link = __shfl_sync(NKB_FULL, e.tau, e.dof_link[r]);
+        const float qd_of_link = __shfl_sync(NKB_FULL, e.qd, e.dof_link[r]);
+        const float q_of_link = __shfl_sync(NKB_FULL, e.q, e.dof_link[r]);
+        rhs[r] = 0.f;
+        dof[r] = c < n;
+        if (dof[r]) {
+            const uint32_t dl = e.dof_link[r];
+            const float* pb = sm_pbias(e, dl);
+            float bias;
+            if (e.dof_comp[r] == kNoLink) {
+                V3 a = ld3(t.axis + 3u * dl);
+                const float ls = dot(a, a);
+                if (ls > 1.0e-12f) a = a * rsqrtf(ls);
+                const uint32_t jt = __ldg(t.jtype + dl);
+                bias = jt == kRevolute ? dot(a, ld3(pb)) : dot(a, ld3(pb + 3));
+                e.vel0[r] = qd_of_link;
+                const float damping = __ldg(t.damping + dl) + diss_of_link;
+                const float spring = __ldg(t.stiffness + dl) * (q_of_link - __ldg(t.spring_ref + dl));
+                rhs[r] = tau_of_link - bias - damping * e.vel0[r] - spring;
+            } else {
+                bias = pb[e.dof_comp[r]];
+                e.vel0[r] = sm_vel(e, dl)[e.dof_comp[r]];
+                rhs[r] = -bias;
+            }
+            sm_vec(e, kVecBias)[c] = bias;
         }
-        sm_vec(e, kVecBias)[l] = bias;
     }
     // mass matrix, ops/articulation_mass.cuh:124-253
     float* M = sm_mass(e);
@@ -357,43 +374,59 @@ NKB_DEV void stage_dynamics(Env& e, bool integrate_velocity) {
     for (uint32_t k = 0; k < n; ++k) {
         const float dk = fmaxf(F[k * ld + k], 1.0e-6f);
         __syncwarp();
-        if (l == k) F[k * ld + k] = dk;
-        float lik = 0.f;
-        if (l > k && l < n) { lik = F[l * ld + k] / dk; F[l * ld + k] = lik; }
+        if (l == (k & 31u)) F[k * ld + k] = dk;
+        float lik[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const uint32_t row = l + 32u * r;
+            lik[r] = 0.f;
+            if (row > k && row < n) { lik[r] = F[row * ld + k] / dk; F[row * ld + k] = lik[r]; }
+        }
         __syncwarp();
-        if (l > k && l < n)
-            for (uint32_t j = k + 1u; j <= l; ++j) F[l * ld + j] -= lik * F[j * ld + k] * dk;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const uint32_t row = l + 32u * r;
+            if (row > k && row < n)
+                for (uint32_t j = k + 1u; j <= row; ++j) F[row * ld + j] -= lik[r] * F[j * ld + k] * dk;
+        }
         __syncwarp();
     }
     // solve L D L^T x = rhs, lane = coordinate (articulation_mass.cuh:357-396)
-    float x = dof ? rhs : 0.f;
+    float x[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) x[r] = dof[r] ? rhs[r] : 0.f;
     for (uint32_t j = 0; j < n; ++j) {
-        const float xj = __shfl_sync(NKB_FULL, x, j);
-        if (l > j && l < n) x -= F[l * ld + j] * xj;
+        const float xj = coord_bcast<NR>(x, j);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) { const uint32_t row = l + 32u * r; if (row > j && row < n) x[r] -= F[row * ld + j] * xj; }
     }
-    if (dof) x /= F[l * ld + l];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) { const uint32_t row = l + 32u * r; if (dof[r]) x[r] /= F[row * ld + row]; }
     for (uint32_t jj = n; jj > 0u; --jj) {
         const uint32_t j = jj - 1u;
-        const float xj = __shfl_sync(NKB_FULL, x, j);
-        if (l < j) x -= F[j * ld + l] * xj;
+        const float xj = coord_bcast<NR>(x, j);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) { const uint32_t row = l + 32u * r; if (row < j) x[r] -= F[j * ld + row] * xj; }
     }
-    if (dof) sm_vec(e, kVecAcc)[l] = x;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) if (dof[r]) sm_vec(e, kVecAcc)[l + 32u * r] = x[r];
     __syncwarp();
     // accelerations back to links, velocity update (articulation.cu:597-615)
     const float acc_of_mine = link && joint_dofs(e.jtype) == 1u ? sm_vec(e, kVecAcc)[e.link_dof] : 0.f;
     e.qdd = acc_of_mine;
     if (integrate_velocity) {
         if (link && joint_dofs(e.jtype) == 1u) e.qd = e.qd + dt * acc_of_mine;
-        const bool base_coord = dof && e.dof_comp != kNoLink;
+        // the floating base's six coordinates come first, so they sit in register slot 0
+        const bool base_coord = dof[0] && e.dof_comp[0] != kNoLink;
         float nv = 0.f;
         if (base_coord) {
-            const uint32_t c = e.dof_comp, i = c % 3u, j = (i + 1u) % 3u, k = (i + 2u) % 3u;
-            const float* rv = sm_vel(e, e.dof_link);
+            const uint32_t c = e.dof_comp[0], i = c % 3u, j = (i + 1u) % 3u, k = (i + 2u) % 3u;
+            const float* rv = sm_vel(e, e.dof_link[0]);
             const float transport = c < 3u ? 0.f : rv[j] * rv[3u + k] - rv[k] * rv[3u + j];
-            nv = e.vel0 + dt * (x + transport);
+            nv = e.vel0[0] + dt * (x[0] + transport);
         }
         __syncwarp();
-        if (base_coord) sm_vel(e, e.dof_link)[e.dof_comp] = nv;
+        if (base_coord) sm_vel(e, e.dof_link[0])[e.dof_comp[0]] = nv;
         __syncwarp();
     }
 }

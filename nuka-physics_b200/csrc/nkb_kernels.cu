@@ -128,6 +128,8 @@ NKB_DEV void stage_store_bodies(Env& e, bool velocities) {
 #ifndef NKB_MAXNREG
 #define NKB_MAXNREG 192
 #endif
+// NR = coordinates per lane: 1 for articulations of up to 32 coordinates, 2 for up to 64.
+template <int NR>
 __global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ StepParams p) {
     extern __shared__ __align__(16) float smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -151,7 +153,7 @@ __global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ Ste
             return;
         }
         tick(e, 0);
-        if (has_artic) { stage_fk(e); tick(e, 1); stage_drives(e); stage_dynamics(e, p.mode != kModeDynamicsOnly); tick(e, 2); }
+        if (has_artic) { stage_fk(e); tick(e, 1); stage_drives(e); stage_dynamics<NR>(e, p.mode != kModeDynamicsOnly); tick(e, 2); }
         if (p.mode == kModeDynamicsOnly) {
             if (lane < t.L) p.s.qddot[(size_t)env * t.L + lane] = e.qdd;
             return;
@@ -175,11 +177,11 @@ __global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ Ste
             if (lane == 0u) p.s.status[env] |= st;
             return;
         }
-        nheads = stage_rows(e, pair_count);
+        nheads = stage_rows<NR>(e, pair_count);
         tick(e, 6);
         stage_warm_start(e, nheads);
         tick(e, 7);
-        stage_solve(e, nheads);
+        stage_solve<NR>(e, nheads);
         if (has_collidables) stage_cache_commit(e, nheads);
         if (has_artic) stage_readout_drives(e, nheads);
         tick(e, 12);
@@ -228,27 +230,35 @@ __global__ void reset_kernel(ResetParams r) {
     }
 }
 
-int step_kernel_resident_blocks(uint32_t warps_per_block, size_t shared_bytes) {
-    if (shared_bytes > 48u * 1024u && cudaFuncSetAttribute(step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared_bytes) != cudaSuccess) {
+template <int NR>
+static int resident_blocks(uint32_t warps_per_block, size_t shared_bytes) {
+    if (shared_bytes > 48u * 1024u && cudaFuncSetAttribute(step_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared_bytes) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     int blocks = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, step_kernel, (int)(warps_per_block * 32u), shared_bytes) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, step_kernel<NR>, (int)(warps_per_block * 32u), shared_bytes) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     return blocks;
 }
 
+int step_kernel_resident_blocks(uint32_t ndof, uint32_t warps_per_block, size_t shared_bytes) {
+    return ndof > 32u ? resident_blocks<2>(warps_per_block, shared_bytes) : resident_blocks<1>(warps_per_block, shared_bytes);
+}
+
 cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
     const size_t bytes = (size_t)warps_per_block * p.sm.words * sizeof(float);
+    const bool wide = p.t.ndof > 32u;
     if (bytes > 48u * 1024u) {
-        const cudaError_t err = cudaFuncSetAttribute(step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        const cudaError_t err = wide ? cudaFuncSetAttribute(step_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes)
+                                     : cudaFuncSetAttribute(step_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
         if (err != cudaSuccess) return err;
     }
     const uint32_t blocks = (p.s.env_count + warps_per_block - 1u) / warps_per_block;
-    step_kernel<<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
+    if (wide) step_kernel<2><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
+    else step_kernel<1><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
     return cudaGetLastError();
 }
 

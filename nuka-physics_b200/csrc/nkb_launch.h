@@ -24,7 +24,7 @@ struct ResetParams {
 
 // Blocks of `warps_per_block` warps with `shared_bytes` of dynamic shared memory that one SM keeps resident (registers,
 // shared memory and block slots considered); 0 when the shape cannot launch.  The device must be current.
-int step_kernel_resident_blocks(uint32_t warps_per_block, size_t shared_bytes);
+int step_kernel_resident_blocks(uint32_t ndof, uint32_t warps_per_block, size_t shared_bytes);
 // Enqueues `p.steps` fused steps (or one parity-tap stage, see StepMode) for every env.
 cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream);
 // Restores `count` envs (all when r.env_ids is null) from their snapshots.

@@ -55,6 +55,7 @@ NKB_DEV uint32_t side_block(const Env& e, uint32_t body, uint32_t& link) {
 }
 
 // Builds every head of the env.  Returns the head count (capped at head_cap).
+template <int NR>
 NKB_DEV uint32_t stage_rows(Env& e, uint32_t pair_count) {
     const TemplateView& t = *e.t;
     const uint32_t S = t.cfg.max_contacts, n = t.ndof, L = t.L, lane = e.lane;
@@ -115,22 +116,28 @@ NKB_DEV uint32_t stage_rows(Env& e, uint32_t pair_count) {
     __syncwarp();
     // chain Jacobians of articulated sides, lane = coordinate (ops/articulation_types.cuh:193-238)
     if (n != 0u && ncontact != 0u) {
-        V3 axis_w = mk3(0.f, 0.f, 0.f), origin = axis_w;
-        uint32_t jt = kFixed;
-        const bool dof = lane < n;
-        if (dof) {
-            const uint32_t dl = e.dof_link;
-            jt = __ldg(t.jtype + dl);
-            if (jt == kFloating) {
-                const float* bp = e.s->base_pose + (size_t)e.env * 7u;
-                const Q4 br = ldq(bp + 3);
-                const uint32_t c = e.dof_comp % 3u;
-                axis_w = qrot(br, mk3(c == 0u ? 1.f : 0.f, c == 1u ? 1.f : 0.f, c == 2u ? 1.f : 0.f));
-                origin = ld3(bp);
-            } else {
-                V3 a = ld3(t.axis + 3u * dl);
-                axis_w = qrot(ldq(sm_pose(e, dl) + 3), a);
-                origin = ld3(sm_pose(e, dl));
+        V3 axis_w[NR], origin[NR];
+        uint32_t jt[NR];
+        bool dof[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            axis_w[r] = mk3(0.f, 0.f, 0.f); origin[r] = axis_w[r];
+            jt[r] = kFixed;
+            dof[r] = lane + 32u * r < n;
+            if (dof[r]) {
+                const uint32_t dl = e.dof_link[r];
+                jt[r] = __ldg(t.jtype + dl);
+                if (jt[r] == kFloating) {
+                    const float* bp = e.s->base_pose + (size_t)e.env * 7u;
+                    const Q4 br = ldq(bp + 3);
+                    const uint32_t c = e.dof_comp[r] % 3u;
+                    axis_w[r] = qrot(br, mk3(c == 0u ? 1.f : 0.f, c == 1u ? 1.f : 0.f, c == 2u ? 1.f : 0.f));
+                    origin[r] = ld3(bp);
+                } else {
+                    V3 a = ld3(t.axis + 3u * dl);
+                    axis_w[r] = qrot(ldq(sm_pose(e, dl) + 3), a);
+                    origin[r] = ld3(sm_pose(e, dl));
+                }
             }
         }
         float* pool = sm_jpool(e);
@@ -140,26 +147,30 @@ NKB_DEV uint32_t stage_rows(Env& e, uint32_t pair_count) {
             const uint32_t n4 = (n + 3u) & ~3u, joff = h * 3u * n4;
             const V3 point = ld3(sm_cpoint(e, ref & 0xffffu));
             const V3 dirs[3] = {hf3(e, HF_N, h), hf3(e, HF_T1, h), hf3(e, HF_T2, h)};
-            if (dof) {
-                float ent[3] = {0.f, 0.f, 0.f};
 #pragma unroll
-                for (int side = 0; side < 2; ++side) {
-                    const uint32_t cl = side == 0 ? la : lb;
-                    if (cl == 0xffffu) continue;
-                    if (!((__ldg(t.anc_mask + cl) >> e.dof_link) & 1u)) continue;
-                    const float sgn = side == 0 ? 1.f : -1.f;
+            for (int r = 0; r < NR; ++r) {
+                const uint32_t c = lane + 32u * r;
+                if (dof[r]) {
+                    float ent[3] = {0.f, 0.f, 0.f};
 #pragma unroll
-                    for (int ax = 0; ax < 3; ++ax) {
-                        const V3 f = dirs[ax] * sgn;
-                        float v;
-                        if (jt == kFloating) v = e.dof_comp < 3u ? dot(cross(axis_w, point - origin), f) + 0.0f : dot(axis_w, f);
-                        else if (jt == kPrismatic) v = dot(axis_w, f);
-                        else v = dot(cross(axis_w, point - origin), f) + 0.0f;
-                        ent[ax] += v;
+                    for (int side = 0; side < 2; ++side) {
+                        const uint32_t cl = side == 0 ? la : lb;
+                        if (cl == 0xffffu) continue;
+                        if (!((__ldg(t.anc_mask + cl) >> e.dof_link[r]) & 1u)) continue;
+                        const float sgn = side == 0 ? 1.f : -1.f;
+#pragma unroll
+                        for (int ax = 0; ax < 3; ++ax) {
+                            const V3 f = dirs[ax] * sgn;
+                            float v;
+                            if (jt[r] == kFloating) v = e.dof_comp[r] < 3u ? dot(cross(axis_w[r], point - origin[r]), f) + 0.0f : dot(axis_w[r], f);
+                            else if (jt[r] == kPrismatic) v = dot(axis_w[r], f);
+                            else v = dot(cross(axis_w[r], point - origin[r]), f) + 0.0f;
+                            ent[ax] += v;
+                        }
                     }
-                }
-                pool[joff + lane] = ent[0]; pool[joff + n4 + lane] = ent[1]; pool[joff + 2u * n4 + lane] = ent[2];
-            } else if (lane < n4) { pool[joff + lane] = 0.f; pool[joff + n4 + lane] = 0.f; pool[joff + 2u * n4 + lane] = 0.f; }
+                    pool[joff + c] = ent[0]; pool[joff + n4 + c] = ent[1]; pool[joff + 2u * n4 + c] = ent[2];
+                } else if (c < n4) { pool[joff + c] = 0.f; pool[joff + n4 + c] = 0.f; pool[joff + 2u * n4 + c] = 0.f; }
+            }
             if (lane == 0u) hu(e, HF_JOFF, h) = joff;
         }
     }

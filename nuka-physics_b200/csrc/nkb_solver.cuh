@@ -24,16 +24,16 @@ struct Tile {
 };
 
 NKB_DEV uint32_t* sm_binfo(const Env& e) { return reinterpret_cast<uint32_t*>(e.sm + e.lay->binfo); }
-// binfo words: dim[nb], color[nb], inc_begin[nb + 1], inc[2 * head_cap], utab[4 * 32], order[nb + 1]
+// binfo words: dim[nb], color[nb], inc_begin[nb + 1], inc[2 * head_cap], utab[4 * vstride], order[nb + 1]
 NKB_DEV uint32_t& blk_dim(const Env& e, uint32_t b) { return sm_binfo(e)[b]; }
 NKB_DEV uint32_t& blk_color(const Env& e, uint32_t nb, uint32_t b) { return sm_binfo(e)[nb + b]; }
 NKB_DEV uint32_t& blk_inc_begin(const Env& e, uint32_t nb, uint32_t b) { return sm_binfo(e)[2u * nb + b]; }
 NKB_DEV uint32_t* blk_inc(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u * nb + 1u; }
-// unit rows of the articulation by coordinate: utab[slot * 32 + coordinate] = head or ~0 (slots: lower limit, upper limit,
-// dry friction, drive)
+// unit rows of the articulation by coordinate: utab[slot * vstride + coordinate] = head or ~0 (slots: lower limit,
+// upper limit, dry friction, drive; vstride = 32 or 64 coordinates)
 NKB_DEV uint32_t* unit_table(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u * nb + 1u + 2u * e.t->head_cap; }
 // moving blocks in descent order, order[nb] = their count
-NKB_DEV uint32_t* block_order(const Env& e, uint32_t nb) { return unit_table(e, nb) + 128u; }
+NKB_DEV uint32_t* block_order(const Env& e, uint32_t nb) { return unit_table(e, nb) + 4u * e.lay->vstride; }
 NKB_DEV float* sm_bmass(const Env& e, uint32_t b) { return e.sm + e.lay->bmass + 7u * free_slot(e, b); }
 NKB_DEV float* sm_bfree(const Env& e, uint32_t b) { return e.sm + e.lay->bfree + 6u * free_slot(e, b); }
 NKB_DEV float* sm_bpseudo(const Env& e, uint32_t b) { return e.sm + e.lay->bpseudo + 6u * free_slot(e, b); }
@@ -94,23 +94,38 @@ NKB_DEV float* block_vel(const Env& e, uint32_t block, bool position) {
 }
 NKB_DEV const float* block_free(const Env& e, uint32_t block) { return block == e.t->B ? sm_vec(e, kVecFree) : sm_bfree(e, block); }
 
-// M^-1 g for a block, lane = coordinate.
-NKB_DEV float solve_block_mass(const Env& e, uint32_t block, float g) {
+// x = M^-1 g for a block; a lane holds coordinates lane + 32 r.
+template <int NR>
+NKB_DEV void solve_block_mass(const Env& e, uint32_t block, const float (&g)[NR], float (&x)[NR]) {
     const TemplateView& t = *e.t;
     const uint32_t l = e.lane;
     if (block == t.B) {
         const uint32_t n = t.ndof, ld = e.lay->ld;
         const float* F = sm_factor(e);
-        float x = l < n ? g : 0.f;
-        for (uint32_t j = 0; j < n; ++j) { const float xj = __shfl_sync(NKB_FULL, x, j); if (l > j && l < n) x -= F[l * ld + j] * xj; }
-        if (l < n) x /= F[l * ld + l];
-        for (uint32_t jj = n; jj > 0u; --jj) { const uint32_t j = jj - 1u; const float xj = __shfl_sync(NKB_FULL, x, j); if (l < j) x -= F[j * ld + l] * xj; }
-        return x;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) x[r] = l + 32u * r < n ? g[r] : 0.f;
+#pragma unroll 1
+        for (uint32_t j = 0; j < n; ++j) {
+            const float xj = coord_bcast<NR>(x, j);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) { const uint32_t row = l + 32u * r; if (row > j && row < n) x[r] -= F[row * ld + j] * xj; }
+        }
+#pragma unroll
+        for (int r = 0; r < NR; ++r) { const uint32_t row = l + 32u * r; if (row < n) x[r] /= F[row * ld + row]; }
+#pragma unroll 1
+        for (uint32_t jj = n; jj > 0u; --jj) {
+            const uint32_t j = jj - 1u;
+            const float xj = coord_bcast<NR>(x, j);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) { const uint32_t row = l + 32u * r; if (row < j) x[r] -= F[j * ld + row] * xj; }
+        }
+        return;
     }
-    const float g3 = __shfl_sync(NKB_FULL, g, 3), g4 = __shfl_sync(NKB_FULL, g, 4), g5 = __shfl_sync(NKB_FULL, g, 5);
-    if (l < 3u) return g * __ldg(t.inv_mass + block);
-    if (l < 6u) { const V3 w = sym_mulv(sm_bwinv(e, block), mk3(g3, g4, g5)); return comp(w, (int)l - 3); }
-    return 0.f;
+    const float g3 = __shfl_sync(NKB_FULL, g[0], 3), g4 = __shfl_sync(NKB_FULL, g[0], 4), g5 = __shfl_sync(NKB_FULL, g[0], 5);
+#pragma unroll
+    for (int r = 0; r < NR; ++r) x[r] = 0.f;
+    if (l < 3u) x[0] = g[0] * __ldg(t.inv_mass + block);
+    else if (l < 6u) { const V3 w = sym_mulv(sm_bwinv(e, block), mk3(g3, g4, g5)); x[0] = comp(w, (int)l - 3); }
 }
 
 // J M^-1 J^T of an articulated row from one forward solve with the unit-lower factor (articulation_mass.cuh:413-441)
@@ -189,14 +204,13 @@ NKB_DEV void index_blocks(Env& e, const Tile& tile, bool color) {
     }
     if (e.lane == 0u) blk_inc_begin(e, nb, nb) = at;
     uint32_t* utab = unit_table(e, nb);
-#pragma unroll
-    for (uint32_t slot = 0u; slot < 4u; ++slot) utab[slot * 32u + e.lane] = 0xffffffffu;
+    for (uint32_t k = e.lane; k < 4u * e.lay->vstride; k += 32u) utab[k] = 0xffffffffu;
     __syncwarp();
     for (uint32_t h = e.lane; h < tile.nheads; h += 32u) {
         const uint32_t jo = hu(e, HF_JOFF, h), o = hu(e, HF_OWNER, h), fl = hu(e, HF_FLAGS, h);
         if (!(jo & kUnitRow) || ((o & 0xffffu) != e.t->B && (o >> 16) != e.t->B)) continue;
         const uint32_t slot = (fl & kHeadDrive) ? 3u : (fl & kHeadFriction) ? 2u : hf(e, HF_UNITV, h) < 0.f ? 1u : 0u;
-        utab[slot * 32u + (jo & 0xffffu)] = h;
+        utab[slot * e.lay->vstride + (jo & 0xffffu)] = h;
     }
     __syncwarp();
     if (!color) return;
@@ -397,13 +411,14 @@ NKB_DEV void apply_moves(Env& e, const Tile& tile, uint32_t b, float alpha) {
     __syncwarp();
 }
 
-// Newton steps with exact line search on one block.  Lane i owns coordinate i and row i of the Newton matrix,
-// which lives in the env's shared-memory slice in float4-readable rows; lane k also owns the k-th incident
-// head in the row evaluations and publishes its response through the head's shared-memory fields.
+// Newton steps with exact line search on one block.  A lane owns coordinates lane + 32 r (r < NR) and the same rows of
+// the Newton matrix, which lives in the env's shared-memory slice in float4-readable rows; lane k also owns the k-th
+// incident head in the row evaluations and publishes its response through the head's shared-memory fields.
+template <int NR>
 NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     const TemplateView& t = *e.t;
     const uint32_t l = e.lane, nb = tile.nblocks, dim = blk_dim(e, b);
-    const bool coord = l < dim, artic = b == t.B;
+    const bool artic = b == t.B;
     const uint32_t* inc = blk_inc(e, nb);
     const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
     const uint32_t chunks = (dim + 3u) >> 2, ldh = pad_ld(dim);
@@ -413,22 +428,23 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     float* lo_v = sm_vec(e, kVecS1);
     float* u_v = sm_vec(e, kVecS2);
     float* H = e.sm + e.lay->chol;
-    float* Hr = H + (coord ? l : 0u) * ldh;
-    float4* Hr4 = reinterpret_cast<float4*>(Hr);
     float* m6 = e.sm + e.lay->bm6;      // 6 x 12 dense mass of a rigid block, then 3 x 8 Jacobian rows of one head
     float* jscr = m6 + 72u;
-    const float* Mr;                    // this lane's row of the block mass, zero past the block's dimension
-    if (artic) Mr = sm_mass(e) + (coord ? l : 0u) * e.lay->ld;
-    else {
-        if (l < 6u)
-#pragma unroll 1
-        for (uint32_t k = 0u; k < 8u; ++k) m6[l * 12u + k] = k < 6u ? block_mass(e, b, l, k) : 0.f;
+    if (!artic) {
+        if (l < 6u) for (uint32_t k = 0u; k < 8u; ++k) m6[l * 12u + k] = k < 6u ? block_mass(e, b, l, k) : 0.f;
         if (l < 24u) jscr[l] = 0.f;
-        Mr = m6 + (coord ? l : 0u) * 12u;
     }
-    const float4* Mr4 = reinterpret_cast<const float4*>(Mr);
+    bool coord[NR];
+    float* Hr[NR];
+    const float* Mr[NR];                // this lane's rows of the block mass, zero past the block's dimension
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const uint32_t c = l + 32u * r;
+        coord[r] = c < dim;
+        Hr[r] = H + (coord[r] ? c : 0u) * ldh;
+        Mr[r] = artic ? sm_mass(e) + (coord[r] ? c : 0u) * e.lay->ld : m6 + (coord[r] ? c : 0u) * 12u;
+    }
     bool coupled = false;
-#pragma unroll 1
     for (uint32_t k = ib + l; k < ie; k += 32u) {
         const uint32_t h = inc[k];
         const uint32_t o = hu(e, HF_OWNER, h);
@@ -438,29 +454,36 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     }
     coupled = __any_sync(NKB_FULL, coupled);
     __syncwarp();
-    const float start = coord ? velocity[l] : 0.f;
-    const float fr = (coord && !position) ? block_free(e, b)[l] : 0.f;
-    float u = start;
+    float start[NR], fr[NR], u[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        start[r] = coord[r] ? velocity[l + 32u * r] : 0.f;
+        fr[r] = (coord[r] && !position) ? block_free(e, b)[l + 32u * r] : 0.f;
+        u[r] = start[r];
+    }
     bool failure = false;
     float primal = FLT_MAX;
     tick(e, 15);
     // step -1 (first velocity sweep only) is the line search toward the free velocity; steps >= 0 are Newton steps
 #pragma unroll 1
     for (int step = (tile.iteration == 0u && !position) ? -1 : 0; step < (int)kNewtonSteps; ++step) {
-        float d = 0.f, force = 0.f, inertia = 0.f;
+        float d[NR], force[NR], inertia[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) { d[r] = 0.f; force[r] = 0.f; inertia[r] = 0.f; }
         if (step < 0) {
-            d = coord ? fr - u : 0.f;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) d[r] = coord[r] ? fr[r] - u[r] : 0.f;
         } else {
             // ---- lane = head: responses at the current moves, published to shared memory ----
             uint32_t dense_any = 0u;
 #pragma unroll 1
             for (uint32_t k = ib + l; k < ie; k += 32u) {
                 const uint32_t h = inc[k];
-                const HeadRegs r = load_head(e, h);
+                const HeadRegs hr = load_head(e, h);
                 V3 f; float cxx, cyy, czz, cyz;
-                respond(r, r.move, f, cxx, cyy, czz, cyz);
-                const V3 noise = mk3(fabsf(f.x) + cxx * (fabsf(r.res.x) + fabsf(r.move.x)), fabsf(f.y) + cyy * (fabsf(r.res.y) + fabsf(r.move.y)),
-                                     fabsf(f.z) + czz * (fabsf(r.res.z) + fabsf(r.move.z)));
+                respond(hr, hr.move, f, cxx, cyy, czz, cyz);
+                const V3 noise = mk3(fabsf(f.x) + cxx * (fabsf(hr.res.x) + fabsf(hr.move.x)), fabsf(f.y) + cyy * (fabsf(hr.res.y) + fabsf(hr.move.y)),
+                                     fabsf(f.z) + czz * (fabsf(hr.res.z) + fabsf(hr.move.z)));
                 hst3(e, HF_F, h, f); hst3(e, HF_NZ, h, noise);
                 hf(e, HF_C, h) = cxx; hf(e, HF_C + 1u, h) = cyy; hf(e, HF_C + 2u, h) = czz; hf(e, HF_C + 3u, h) = cyz;
                 const bool contributes = f.x != 0.f || f.y != 0.f || f.z != 0.f || cxx != 0.f || cyy != 0.f || czz != 0.f || cyz != 0.f ||
@@ -468,162 +491,220 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                 const bool unit = artic && (hu(e, HF_JOFF, h) & kUnitRow) != 0u;
                 dense_any |= (contributes && !unit) ? 1u : 0u;
             }
-            // ---- lane = coordinate: inertial part of H (row l) and g ----
-            const float diff = u - fr;
-            const float part = diff - u;
-            const float diff_err = (u - (diff - part)) + (-fr - part);
-            hi_v[l] = diff; lo_v[l] = diff_err; u_v[l] = u;
-            __syncwarp();
-            CSum inertial = {0.f, 0.f};
-            float scale = 0.f, diag = 0.f;
-            if (coord)
-#pragma unroll 1
-            for (uint32_t c = 0u; c < chunks; ++c) {
-                const float4 m = Mr4[c], hi = reinterpret_cast<const float4*>(hi_v)[c], lo = reinterpret_cast<const float4*>(lo_v)[c];
-                Hr4[c] = m;
-                csum_addp(inertial, m.x, hi.x); inertial.error = fmaf(m.x, lo.x, inertial.error);
-                csum_addp(inertial, m.y, hi.y); inertial.error = fmaf(m.y, lo.y, inertial.error);
-                csum_addp(inertial, m.z, hi.z); inertial.error = fmaf(m.z, lo.z, inertial.error);
-                csum_addp(inertial, m.w, hi.w); inertial.error = fmaf(m.w, lo.w, inertial.error);
-                scale += fabsf(m.x) * fabsf(hi.x) + fabsf(m.y) * fabsf(hi.y) + fabsf(m.z) * fabsf(hi.z) + fabsf(m.w) * fabsf(hi.w);
+            // ---- lane = coordinate: inertial part of H (rows of this lane) and g ----
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const float diff = u[r] - fr[r];
+                const float part = diff - u[r];
+                const float diff_err = (u[r] - (diff - part)) + (-fr[r] - part);
+                hi_v[l + 32u * r] = diff; lo_v[l + 32u * r] = diff_err; u_v[l + 32u * r] = u[r];
             }
-            CSum g = {-inertial.value, -inertial.error};
+            __syncwarp();
+            CSum inertial[NR], g[NR];
+            float scale[NR], diag[NR];
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                inertial[r].value = 0.f; inertial[r].error = 0.f;
+                scale[r] = 0.f; diag[r] = 0.f;
+                if (coord[r]) {
+                    const float4* Mr4 = reinterpret_cast<const float4*>(Mr[r]);
+                    float4* Hr4 = reinterpret_cast<float4*>(Hr[r]);
+#pragma unroll 1
+                    for (uint32_t c = 0u; c < chunks; ++c) {
+                        const float4 m = Mr4[c], hi = reinterpret_cast<const float4*>(hi_v)[c], lo = reinterpret_cast<const float4*>(lo_v)[c];
+                        Hr4[c] = m;
+                        csum_addp(inertial[r], m.x, hi.x); inertial[r].error = fmaf(m.x, lo.x, inertial[r].error);
+                        csum_addp(inertial[r], m.y, hi.y); inertial[r].error = fmaf(m.y, lo.y, inertial[r].error);
+                        csum_addp(inertial[r], m.z, hi.z); inertial[r].error = fmaf(m.z, lo.z, inertial[r].error);
+                        csum_addp(inertial[r], m.w, hi.w); inertial[r].error = fmaf(m.w, lo.w, inertial[r].error);
+                        scale[r] += fabsf(m.x) * fabsf(hi.x) + fabsf(m.y) * fabsf(hi.y) + fabsf(m.z) * fabsf(hi.z) + fabsf(m.w) * fabsf(hi.w);
+                    }
+                }
+                g[r].value = -inertial[r].value; g[r].error = -inertial[r].error;
+            }
             tick(e, 16);
             // rows on a single coordinate only touch that coordinate (block_descent_tile.cuh:1555-1568)
             if (artic) {
                 const uint32_t* utab = unit_table(e, nb);
+                const uint32_t vs = e.lay->vstride;
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
 #pragma unroll 1
-                for (uint32_t slot = 0u; slot < 4u; ++slot) {
-                    const uint32_t h = utab[slot * 32u + l];
-                    if (h == 0xffffffffu) continue;
-                    const float v = hf(e, HF_UNITV, h);
-                    diag += v * hf(e, HF_C, h) * v;
-                    csum_addp(g, v, hf(e, HF_F, h));
-                    scale += fabsf(v) * hf(e, HF_NZ, h);
+                    for (uint32_t slot = 0u; slot < 4u; ++slot) {
+                        const uint32_t h = utab[slot * vs + l + 32u * r];
+                        if (h == 0xffffffffu) continue;
+                        const float v = hf(e, HF_UNITV, h);
+                        diag[r] += v * hf(e, HF_C, h) * v;
+                        csum_addp(g[r], v, hf(e, HF_F, h));
+                        scale[r] += fabsf(v) * hf(e, HF_NZ, h);
+                    }
                 }
             }
             // dense rows: H += J^T C J, g += J^T f, one head at a time with its values broadcast from shared memory
-            if (__any_sync(NKB_FULL, dense_any != 0u))
+            if (__any_sync(NKB_FULL, dense_any != 0u)) {
 #pragma unroll 1
-            for (uint32_t k = ib; k < ie; ++k) {
-                const uint32_t hs = inc[k];
-                const uint32_t jo = hu(e, HF_JOFF, hs);
-                if (artic && (jo & kUnitRow)) continue;
-                const V3 f = hf3(e, HF_F, hs), nz = hf3(e, HF_NZ, hs);
-                const float c0 = hf(e, HF_C, hs), c1 = hf(e, HF_C + 1u, hs), c2 = hf(e, HF_C + 2u, hs), c12 = hf(e, HF_C + 3u, hs);
-                if (!(f.x != 0.f || f.y != 0.f || f.z != 0.f || c0 != 0.f || c1 != 0.f || c2 != 0.f || c12 != 0.f || nz.x != 0.f || nz.y != 0.f || nz.z != 0.f)) continue;
-                const float* jr; uint32_t js;
-                if (artic) { jr = sm_jpool(e) + jo; js = chunks << 2; }
-                else {
-                    const uint32_t ss = head_owner(e, hs, 0u) == b ? 0u : 1u, as = head_axes(e, hs);
-                    __syncwarp();
-                    if (l < 6u)
-#pragma unroll 1
-                    for (uint32_t ax = 0u; ax < 3u; ++ax) jscr[ax * 8u + l] = ax < as ? head_jac(e, hs, ss, ax, l, b) : 0.f;
-                    __syncwarp();
-                    jr = jscr; js = 8u;
-                }
-                const float j0 = coord ? jr[l] : 0.f, j1 = coord ? jr[js + l] : 0.f, j2 = coord ? jr[2u * js + l] : 0.f;
-                csum_addp(g, j0, f.x); csum_addp(g, j1, f.y); csum_addp(g, j2, f.z);
-                scale += fabsf(j0) * nz.x + fabsf(j1) * nz.y + fabsf(j2) * nz.z;
-                const float a0 = j0 * c0, a1 = j1 * c1 + j2 * c12, a2 = j2 * c2 + j1 * c12;
-                if (coord) {
+                for (uint32_t k = ib; k < ie; ++k) {
+                    const uint32_t hs = inc[k];
+                    const uint32_t jo = hu(e, HF_JOFF, hs);
+                    if (artic && (jo & kUnitRow)) continue;
+                    const V3 f = hf3(e, HF_F, hs), nz = hf3(e, HF_NZ, hs);
+                    const float c0 = hf(e, HF_C, hs), c1 = hf(e, HF_C + 1u, hs), c2 = hf(e, HF_C + 2u, hs), c12 = hf(e, HF_C + 3u, hs);
+                    if (!(f.x != 0.f || f.y != 0.f || f.z != 0.f || c0 != 0.f || c1 != 0.f || c2 != 0.f || c12 != 0.f || nz.x != 0.f || nz.y != 0.f || nz.z != 0.f)) continue;
+                    const float* jr; uint32_t js;
+                    if (artic) { jr = sm_jpool(e) + jo; js = chunks << 2; }
+                    else {
+                        const uint32_t ss = head_owner(e, hs, 0u) == b ? 0u : 1u, as = head_axes(e, hs);
+                        __syncwarp();
+                        if (l < 6u) for (uint32_t ax = 0u; ax < 3u; ++ax) jscr[ax * 8u + l] = ax < as ? head_jac(e, hs, ss, ax, l, b) : 0.f;
+                        __syncwarp();
+                        jr = jscr; js = 8u;
+                    }
                     const float4* r0 = reinterpret_cast<const float4*>(jr);
                     const float4* r1 = reinterpret_cast<const float4*>(jr + js);
                     const float4* r2 = reinterpret_cast<const float4*>(jr + 2u * js);
+#pragma unroll
+                    for (int r = 0; r < NR; ++r) {
+                        const uint32_t c = l + 32u * r;
+                        const float j0 = coord[r] ? jr[c] : 0.f, j1 = coord[r] ? jr[js + c] : 0.f, j2 = coord[r] ? jr[2u * js + c] : 0.f;
+                        csum_addp(g[r], j0, f.x); csum_addp(g[r], j1, f.y); csum_addp(g[r], j2, f.z);
+                        scale[r] += fabsf(j0) * nz.x + fabsf(j1) * nz.y + fabsf(j2) * nz.z;
+                        const float a0 = j0 * c0, a1 = j1 * c1 + j2 * c12, a2 = j2 * c2 + j1 * c12;
+                        if (coord[r]) {
+                            float4* Hr4 = reinterpret_cast<float4*>(Hr[r]);
 #pragma unroll 1
-                    for (uint32_t c = 0u; c < chunks; ++c) {
-                        float4 h4 = Hr4[c];
-                        const float4 x = r0[c], y = r1[c], z = r2[c];
-                        h4.x += a0 * x.x + a1 * y.x + a2 * z.x;
-                        h4.y += a0 * x.y + a1 * y.y + a2 * z.y;
-                        h4.z += a0 * x.z + a1 * y.z + a2 * z.z;
-                        h4.w += a0 * x.w + a1 * y.w + a2 * z.w;
-                        Hr4[c] = h4;
+                            for (uint32_t cc = 0u; cc < chunks; ++cc) {
+                                float4 h4 = Hr4[cc];
+                                const float4 x = r0[cc], y = r1[cc], z = r2[cc];
+                                h4.x += a0 * x.x + a1 * y.x + a2 * z.x;
+                                h4.y += a0 * x.y + a1 * y.y + a2 * z.y;
+                                h4.z += a0 * x.z + a1 * y.z + a2 * z.z;
+                                h4.w += a0 * x.w + a1 * y.w + a2 * z.w;
+                                Hr4[cc] = h4;
+                            }
+                        }
                     }
                 }
             }
             tick(e, 17);
-            bool finite = true;
-            if (coord) {
-                Hr[l] += diag;
+            bool finite = true, small = true;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                if (coord[r]) {
+                    float4* Hr4 = reinterpret_cast<float4*>(Hr[r]);
+                    Hr[r][l + 32u * r] += diag[r];
 #pragma unroll 1
-                for (uint32_t c = 0u; c < chunks; ++c) {
-                    const float4 v = Hr4[c], uu = reinterpret_cast<const float4*>(u_v)[c];
-                    finite &= isfinite(v.x) && isfinite(v.y) && isfinite(v.z) && isfinite(v.w);
-                    scale += fabsf(v.x) * fabsf(uu.x) + fabsf(v.y) * fabsf(uu.y) + fabsf(v.z) * fabsf(uu.z) + fabsf(v.w) * fabsf(uu.w);
+                    for (uint32_t c = 0u; c < chunks; ++c) {
+                        const float4 v = Hr4[c], uu = reinterpret_cast<const float4*>(u_v)[c];
+                        finite &= isfinite(v.x) && isfinite(v.y) && isfinite(v.z) && isfinite(v.w);
+                        scale[r] += fabsf(v.x) * fabsf(uu.x) + fabsf(v.y) * fabsf(uu.y) + fabsf(v.z) * fabsf(uu.z) + fabsf(v.w) * fabsf(uu.w);
+                    }
+                    force[r] = g[r].value + g[r].error; inertia[r] = inertial[r].value + inertial[r].error;
                 }
-                force = g.value + g.error; inertia = inertial.value + inertial.error;
+                finite &= isfinite(force[r]);
+                small &= !coord[r] || fabsf(force[r]) <= kRoundings * FLT_EPSILON * scale[r];
             }
-            finite &= isfinite(force);
             if (!__all_sync(NKB_FULL, finite)) { failure = true; break; }
-            bool converged = __all_sync(NKB_FULL, !coord || fabsf(force) <= kRoundings * FLT_EPSILON * scale);
+            bool converged = __all_sync(NKB_FULL, small);
             if (converged && tile.tol > 0.f) {
-                d = solve_block_mass(e, b, force);
-                converged = __all_sync(NKB_FULL, !coord || fabsf(d) < tile.tol);
+                solve_block_mass<NR>(e, b, force, d);
+                bool still = true;
+#pragma unroll
+                for (int r = 0; r < NR; ++r) still &= !coord[r] || fabsf(d[r]) < tile.tol;
+                converged = __all_sync(NKB_FULL, still);
             }
             if (converged) { primal = 0.f; break; }
             tick(e, 18);
-            // ---- Cholesky, row l of L over row l of H (block_descent_tile.cuh:1623-1641) ----
+            // ---- Cholesky, rows of L over the rows of H (block_descent_tile.cuh:1623-1641) ----
             bool valid = true;
-            float inverse = 0.f;
+            float inverse[NR];
+#pragma unroll
+            for (int r = 0; r < NR; ++r) inverse[r] = 0.f;
             __syncwarp();
 #pragma unroll 1
             for (uint32_t k = 0u; k < dim; ++k) {
-                float value = 0.f;
-                if (coord && l >= k) {
-                    const float4* Hk4 = reinterpret_cast<const float4*>(H + k * ldh);
-                    const uint32_t full = k >> 2;
-                    float s0 = 0.f, s1 = 0.f;
+                float value[NR];
+                const float4* Hk4 = reinterpret_cast<const float4*>(H + k * ldh);
+                const uint32_t full = k >> 2, rem = k & 3u;
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    value[r] = 0.f;
+                    if (coord[r] && l + 32u * r >= k) {
+                        const float4* Hr4 = reinterpret_cast<const float4*>(Hr[r]);
+                        float s0 = 0.f, s1 = 0.f;
 #pragma unroll 1
-                    for (uint32_t c = 0u; c < full; ++c) {
-                        const float4 a = Hr4[c], bb = Hk4[c];
-                        s0 = fmaf(a.x, bb.x, s0); s1 = fmaf(a.y, bb.y, s1); s0 = fmaf(a.z, bb.z, s0); s1 = fmaf(a.w, bb.w, s1);
+                        for (uint32_t c = 0u; c < full; ++c) {
+                            const float4 a = Hr4[c], bb = Hk4[c];
+                            s0 = fmaf(a.x, bb.x, s0); s1 = fmaf(a.y, bb.y, s1); s0 = fmaf(a.z, bb.z, s0); s1 = fmaf(a.w, bb.w, s1);
+                        }
+                        const float4 a = Hr4[full], bb = Hk4[full];
+                        if (rem > 0u) s0 = fmaf(a.x, bb.x, s0);
+                        if (rem > 1u) s1 = fmaf(a.y, bb.y, s1);
+                        if (rem > 2u) s0 = fmaf(a.z, bb.z, s0);
+                        value[r] = Hr[r][k] - (s0 + s1);
                     }
-                    const float4 a = Hr4[full], bb = Hk4[full];
-                    const uint32_t rem = k & 3u;
-                    if (rem > 0u) s0 = fmaf(a.x, bb.x, s0);
-                    if (rem > 1u) s1 = fmaf(a.y, bb.y, s1);
-                    if (rem > 2u) s0 = fmaf(a.z, bb.z, s0);
-                    value = Hr[k] - (s0 + s1);
                 }
-                const float pivot = __shfl_sync(NKB_FULL, value, k);
+                const float pivot = coord_bcast<NR>(value, k);
                 valid &= pivot > 0.f && pivot <= FLT_MAX;
                 const float sc = rsqrtf(valid ? pivot : 1.0f), root = pivot * sc;
-                if (coord && l >= k) Hr[k] = l == k ? root : value * sc;
-                inverse = l == k ? sc : inverse;
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    const uint32_t c = l + 32u * r;
+                    if (coord[r] && c >= k) Hr[r][k] = c == k ? root : value[r] * sc;
+                    inverse[r] = c == k ? sc : inverse[r];
+                }
                 __syncwarp();
             }
             if (!valid) { failure = true; break; }
             tick(e, 19);
             // ---- d = H^-1 g ----
-            float r = force;
+            float rr[NR], scaled[NR];
+#pragma unroll
+            for (int r = 0; r < NR; ++r) rr[r] = force[r];
 #pragma unroll 1
             for (uint32_t j = 0u; j < dim; ++j) {
-                const float y = __shfl_sync(NKB_FULL, r * inverse, j);
-                r = l == j ? y : ((coord && l > j) ? fmaf(-Hr[j], y, r) : r);
+#pragma unroll
+                for (int r = 0; r < NR; ++r) scaled[r] = rr[r] * inverse[r];
+                const float y = coord_bcast<NR>(scaled, j);
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    const uint32_t c = l + 32u * r;
+                    rr[r] = c == j ? y : ((coord[r] && c > j) ? fmaf(-Hr[r][j], y, rr[r]) : rr[r]);
+                }
             }
 #pragma unroll 1
             for (uint32_t jj = dim; jj > 0u; --jj) {
                 const uint32_t j = jj - 1u;
-                const float x = __shfl_sync(NKB_FULL, r * inverse, j);
-                r = l == j ? x : (l < j ? fmaf(-H[j * ldh + l], x, r) : r);
+#pragma unroll
+                for (int r = 0; r < NR; ++r) scaled[r] = rr[r] * inverse[r];
+                const float x = coord_bcast<NR>(scaled, j);
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    const uint32_t c = l + 32u * r;
+                    rr[r] = c == j ? x : (c < j ? fmaf(-H[j * ldh + c], x, rr[r]) : rr[r]);
+                }
             }
-            d = coord ? r : 0.f;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) d[r] = coord[r] ? rr[r] : 0.f;
         }
         // ---- curvature and slopes along d ----
         __syncwarp();
-        dvec[l] = d;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) dvec[l + 32u * r] = d[r];
         __syncwarp();
-        float ms = 0.f;
-        if (coord)
-#pragma unroll 1
-        for (uint32_t c = 0u; c < chunks; ++c) {
-            const float4 m = Mr4[c], dd = reinterpret_cast<const float4*>(dvec)[c];
-            ms = fmaf(m.x, dd.x, ms); ms = fmaf(m.y, dd.y, ms); ms = fmaf(m.z, dd.z, ms); ms = fmaf(m.w, dd.w, ms);
-        }
         CSum dec = {0.f, 0.f}, slo = {0.f, 0.f}, cur = {0.f, 0.f};
-        if (coord) { csum_addp(dec, force, d); csum_addp(slo, inertia, d); csum_addp(cur, d, ms); }
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            float ms = 0.f;
+            if (coord[r]) {
+                const float4* Mr4 = reinterpret_cast<const float4*>(Mr[r]);
+#pragma unroll 1
+                for (uint32_t c = 0u; c < chunks; ++c) {
+                    const float4 m = Mr4[c], dd = reinterpret_cast<const float4*>(dvec)[c];
+                    ms = fmaf(m.x, dd.x, ms); ms = fmaf(m.y, dd.y, ms); ms = fmaf(m.z, dd.z, ms); ms = fmaf(m.w, dd.w, ms);
+                }
+                csum_addp(dec, force[r], d[r]); csum_addp(slo, inertia[r], d[r]); csum_addp(cur, d[r], ms);
+            }
+        }
         const float icurv = warp_csum_total(cur);
         float islope;
         if (step < 0) {
@@ -642,20 +723,33 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
         tick(e, 22);
         if (e.cyc != nullptr && l == 0u) e.cyc[23] += 1u;
         if (step < 0) {
-            if (alpha > 0.f) { u = fmaf(alpha, d, u); apply_moves(e, tile, b, alpha); }
+            if (alpha > 0.f) {
+#pragma unroll
+                for (int r = 0; r < NR; ++r) u[r] = fmaf(alpha, d[r], u[r]);
+                apply_moves(e, tile, b, alpha);
+            }
             continue;
         }
-        const float after = fmaf(alpha, d, u);
-        const bool fin = __all_sync(NKB_FULL, !coord || isfinite(after));
-        const bool rounded = __all_sync(NKB_FULL, !coord || after == u);
+        float after[NR];
+        bool fin_l = true, rounded_l = true;
+        float step_l = 0.f;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            after[r] = fmaf(alpha, d[r], u[r]);
+            fin_l &= !coord[r] || isfinite(after[r]);
+            rounded_l &= !coord[r] || after[r] == u[r];
+            step_l = fmaxf(step_l, coord[r] ? fabsf(alpha * d[r]) : 0.f);
+        }
+        const bool fin = __all_sync(NKB_FULL, fin_l);
+        const bool rounded = __all_sync(NKB_FULL, rounded_l);
         if (!fin) { failure = true; break; }
-        primal = warp_max((coord && !rounded) ? fabsf(alpha * d) : 0.f);
+        primal = warp_max(rounded ? 0.f : step_l);
         if (!(alpha > 0.f)) break;
-        u = after;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) u[r] = after[r];
         apply_moves(e, tile, b, alpha);
         if (rounded) break;
     }
-#pragma unroll 1
     for (uint32_t k = ib + l; k < ie; k += 32u) {
         const uint32_t h = inc[k];
         const V3 res = hf3(e, HF_RES, h), move = hf3(e, HF_MOVE, h);
@@ -663,22 +757,25 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     }
     if (failure) e.status |= kStatusSolverFailure;
     float moved = failure ? FLT_MAX : 0.f;
-    if (coord) moved = fmaxf(moved, residual_abs(u - start));
+#pragma unroll
+    for (int r = 0; r < NR; ++r) if (coord[r]) moved = fmaxf(moved, residual_abs(u[r] - start[r]));
     moved = warp_max(moved);
     tile.momentum = fmaxf(tile.momentum, moved);
     if (failure) primal = FLT_MAX;
     tile.residual = fmaxf(tile.residual, fmaxf(primal, coupled ? moved : 0.f));
-    if (coord) velocity[l] = u;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) if (coord[r]) velocity[l + 32u * r] = u[r];
     __syncwarp();
 }
 
 // Blocks descend colour by colour, blocks of one colour in index order (block_descent_tile.cuh:2749-2820).
+template <int NR>
 NKB_DEV void descend_blocks(Env& e, Tile& tile, bool position) {
     const uint32_t nb = tile.nblocks;
     const uint32_t* order = block_order(e, nb);
     const uint32_t count = order[nb];
 #pragma unroll 1
-    for (uint32_t k = 0u; k < count; ++k) descend_block(e, tile, order[k], position);
+    for (uint32_t k = 0u; k < count; ++k) descend_block<NR>(e, tile, order[k], position);
 }
 
 struct DualMomentum { float t, beta; };
@@ -751,6 +848,7 @@ NKB_DEV void update_duals(Env& e, const Tile& tile, DualMomentum* mom, bool velo
 }
 
 // Momentum balance of every moving block against the physical multipliers (block_descent_tile.cuh:2379-2489).
+template <int NR>
 NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
     const uint32_t nb = tile.nblocks, l = e.lane;
     const uint32_t* inc = blk_inc(e, nb);
@@ -760,22 +858,29 @@ NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
     for (uint32_t turn = 0u; turn < count; ++turn) {
         const uint32_t b = order[turn];
         const uint32_t dim = blk_dim(e, b);
-        const bool coord = l < dim, artic = b == e.t->B;
+        const bool artic = b == e.t->B;
         float* vel = block_vel(e, b, false);
         const float* fr = block_free(e, b);
         const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
-        double balance = 0.0;
+        double balance[NR];
+        bool coord[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) { balance[r] = 0.0; coord[r] = l + 32u * r < dim; }
         if (artic) {
             const uint32_t n4 = (dim + 3u) & ~3u;
-            if (coord) {
-                const float* Mr = sm_mass(e) + l * e.lay->ld;
+            const uint32_t* utab = unit_table(e, nb);
+            const uint32_t vs = e.lay->vstride;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const uint32_t c = l + 32u * r;
+                if (!coord[r]) continue;
+                const float* Mr = sm_mass(e) + c * e.lay->ld;
 #pragma unroll 1
-                for (uint32_t j = 0u; j < dim; ++j) balance -= (double)Mr[j] * ((double)vel[j] - fr[j]);
-                const uint32_t* utab = unit_table(e, nb);
+                for (uint32_t j = 0u; j < dim; ++j) balance[r] -= (double)Mr[j] * ((double)vel[j] - fr[j]);
 #pragma unroll 1
                 for (uint32_t slot = 0u; slot < 4u; ++slot) {
-                    const uint32_t h = utab[slot * 32u + l];
-                    if (h != 0xffffffffu) balance += (double)hf(e, HF_UNITV, h) * hf(e, HF_LAM, h);
+                    const uint32_t h = utab[slot * vs + c];
+                    if (h != 0xffffffffu) balance[r] += (double)hf(e, HF_UNITV, h) * hf(e, HF_LAM, h);
                 }
             }
 #pragma unroll 1
@@ -784,13 +889,18 @@ NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
                 const uint32_t jo = hu(e, HF_JOFF, h);
                 if (jo & kUnitRow) continue;
                 const V3 lam = hf3(e, HF_LAM, h);
-                if (!coord) continue;
                 const float* jr = sm_jpool(e) + jo;
-                balance += (double)jr[l] * lam.x;
-                if (head_axes(e, h) == 3u) balance += (double)jr[n4 + l] * lam.y + (double)jr[2u * n4 + l] * lam.z;
+                const bool cone = head_axes(e, h) == 3u;
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    const uint32_t c = l + 32u * r;
+                    if (!coord[r]) continue;
+                    balance[r] += (double)jr[c] * lam.x;
+                    if (cone) balance[r] += (double)jr[n4 + c] * lam.y + (double)jr[2u * n4 + c] * lam.z;
+                }
             }
         } else {
-            if (coord) for (uint32_t j = 0u; j < dim; ++j) balance -= (double)block_mass(e, b, l, j) * ((double)vel[j] - fr[j]);
+            if (coord[0]) for (uint32_t j = 0u; j < dim; ++j) balance[0] -= (double)block_mass(e, b, l, j) * ((double)vel[j] - fr[j]);
 #pragma unroll 1
             for (uint32_t k = ib; k < ie; ++k) {
                 const uint32_t h = inc[k];
@@ -799,20 +909,27 @@ NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
                 for (uint32_t ax = 0u; ax < axes; ++ax) {
                     const float imp = comp(lam, (int)ax);
                     if (imp == 0.f) continue;
-                    if (coord) balance += (double)head_jac(e, h, side, ax, l, b) * imp;
+                    if (coord[0]) balance[0] += (double)head_jac(e, h, side, ax, l, b) * imp;
                 }
             }
         }
-        const float force = coord ? (float)balance : 0.f;
-        const bool finite = __all_sync(NKB_FULL, !coord || fabs(balance) <= FLT_MAX);
-        float residual = FLT_MAX, dir = 0.f;
+        float force[NR], dir[NR];
+        bool ok = true;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) { force[r] = coord[r] ? (float)balance[r] : 0.f; dir[r] = 0.f; ok &= !coord[r] || fabs(balance[r]) <= FLT_MAX; }
+        const bool finite = __all_sync(NKB_FULL, ok);
+        float residual = FLT_MAX;
         if (finite) {
-            dir = solve_block_mass(e, b, force);
-            residual = warp_max(coord ? (isfinite(dir) ? fabsf(dir) : FLT_MAX) : 0.f);
+            solve_block_mass<NR>(e, b, force, dir);
+            float worst = 0.f;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) if (coord[r]) worst = fmaxf(worst, isfinite(dir[r]) ? fabsf(dir[r]) : FLT_MAX);
+            residual = warp_max(worst);
         }
         tile.residual = fmaxf(tile.residual, residual);
         if (reconstruct && finite) {
-            if (coord) vel[l] += dir;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) if (coord[r]) vel[l + 32u * r] += dir[r];
             tile.momentum = fmaxf(tile.momentum, residual);
             __syncwarp();
         }
@@ -821,6 +938,7 @@ NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
 
 // The whole constraint solve of one env.  On entry the heads are built, the articulation's post-dynamics
 // velocity is in (e.qd, sm_vel(root)) and free-body velocities are in sm_bvel.
+template <int NR>
 NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
     const TemplateView& t = *e.t;
     const uint32_t l = e.lane, B = t.B, n = t.ndof;
@@ -863,14 +981,18 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
     if (n != 0u && l == 0u) blk_dim(e, B) = n;
     // articulation coordinates: free = post-dynamics velocity
     {
-        const float qd_of_link = __shfl_sync(NKB_FULL, e.qd, e.dof_link);
-        if (l < n) {
-            const float value = e.dof_comp == kNoLink ? qd_of_link : sm_vel(e, e.dof_link)[e.dof_comp];
-            const float c = e.s->carry_artic[(size_t)e.env * n + l];
-            sm_vec(e, kVecFree)[l] = value;
-            sm_vec(e, kVecU)[l] = value + (isfinite(c) ? c : 0.f);
-            sm_vec(e, kVecPseudo)[l] = 0.f;
-        } else { sm_vec(e, kVecFree)[l] = 0.f; sm_vec(e, kVecU)[l] = 0.f; sm_vec(e, kVecPseudo)[l] = 0.f; }   // float4 readers see zeros past n
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const uint32_t at = l + 32u * r;
+            const float qd_of_link = __shfl_sync(NKB_FULL, e.qd, e.dof_link[r]);
+            if (at < n) {
+                const float value = e.dof_comp[r] == kNoLink ? qd_of_link : sm_vel(e, e.dof_link[r])[e.dof_comp[r]];
+                const float c = e.s->carry_artic[(size_t)e.env * n + at];
+                sm_vec(e, kVecFree)[at] = value;
+                sm_vec(e, kVecU)[at] = value + (isfinite(c) ? c : 0.f);
+                sm_vec(e, kVecPseudo)[at] = 0.f;
+            } else { sm_vec(e, kVecFree)[at] = 0.f; sm_vec(e, kVecU)[at] = 0.f; sm_vec(e, kVecPseudo)[at] = 0.f; }   // float4 readers see zeros past n
+        }
     }
     __syncwarp();
     init_heads(e, tile);
@@ -897,9 +1019,13 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
             // velocities back to the links, carried velocities to global memory
             if (n != 0u) {
                 const float* U = sm_vec(e, kVecU);
-                if (l < n) {
-                    e.s->carry_artic[(size_t)e.env * n + l] = U[l] - sm_vec(e, kVecFree)[l];
-                    if (e.dof_comp != kNoLink) sm_vel(e, e.dof_link)[e.dof_comp] = U[l];
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    const uint32_t at = l + 32u * r;
+                    if (at < n) {
+                        e.s->carry_artic[(size_t)e.env * n + at] = U[at] - sm_vec(e, kVecFree)[at];
+                        if (e.dof_comp[r] != kNoLink) sm_vel(e, e.dof_link[r])[e.dof_comp[r]] = U[at];
+                    }
                 }
                 if (l < t.L && joint_dofs(e.jtype) == 1u) e.qd = U[e.link_dof];
             }
@@ -960,7 +1086,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
         }
         if (phase == kPhaseVelocity) { tile.iteration = sweeps++; tile.momentum = 0.f; tile.residual = 0.f; }
         else tile.iteration = sweeps + pushes;
-        descend_blocks(e, tile, phase == kPhasePosition);
+        descend_blocks<NR>(e, tile, phase == kPhasePosition);
         if (phase == kPhasePosition) {
             if (++pushes >= positions) { phase = kPhaseDone; continue; }
         } else tick(e, 10);
@@ -974,7 +1100,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
             if (stage == 0) run = sweeps == iterations || fmaxf(worst_row, tile.residual) < tile.tol;
             else if (stage == 1) run = worst_row < tile.tol && tile.residual >= tile.tol && tile.residual < FLT_MAX;
             if (stage == 1 && !run) break;
-            if (run) { measure_primals(e, tile, stage == 1); tick(e, 25); if (e.cyc != nullptr && l == 0u) e.cyc[27] += 1u; }
+            if (run) { measure_primals<NR>(e, tile, stage == 1); tick(e, 25); if (e.cyc != nullptr && l == 0u) e.cyc[27] += 1u; }
             if (stage == 1) {
                 if (!(tile.residual < FLT_MAX)) break;
                 init_residuals(e, tile);
@@ -989,7 +1115,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
         if (sweeps >= iterations || largest < tile.tol || largest == FLT_MAX) phase = kPhaseHandOver;
     }
     tick(e, 14);
-    if (e.s->dbg_qdot_pseudo != nullptr && l < n) e.s->dbg_qdot_pseudo[(size_t)e.env * n + l] = sm_vec(e, kVecPseudo)[l];
+    if (e.s->dbg_qdot_pseudo != nullptr) for (uint32_t at = l; at < n; at += 32u) e.s->dbg_qdot_pseudo[(size_t)e.env * n + at] = sm_vec(e, kVecPseudo)[at];
 }
 
 }  // namespace nkb

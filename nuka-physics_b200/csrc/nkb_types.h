@@ -10,7 +10,7 @@ namespace nkb {
 
 constexpr uint32_t kNoLink = 0xffffffffu;
 constexpr uint32_t kMaxLinks = 32u;     // one warp lane per link
-constexpr uint32_t kMaxDof = 32u;       // one warp lane per articulation coordinate
+constexpr uint32_t kMaxDof = 64u;       // a warp lane owns coordinates lane and lane + 32
 constexpr uint32_t kMaxBodies = 64u;
 constexpr uint32_t kPtsPerSlot = 4u;
 
@@ -98,7 +98,7 @@ struct StateView {
 // Shared-memory layout of one env (offsets in 4-byte words), filled by the host.
 struct SmemLayout {
     uint32_t pose, xrot, xtr, vel, vbias, acc, pbias, ic;       // per link
-    uint32_t mass, factor, vecs;                                // articulation
+    uint32_t mass, factor, vecs, vstride;                       // articulation (vstride: words per vector, 32 or 64)
     uint32_t bpose, bvel, bwinv, aabb, bmass, bfree, bpseudo;   // bodies
     uint32_t pairs, ccount, cpoint, cnormal, cdepth, cfeat;     // contacts
     uint32_t cstage;                                            // cache rebuild staging (shares the Jacobian pool, dead by then)

@@ -138,7 +138,7 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
         for (int k = 0; k < 3; ++k) t.offset[3 * l + k] = local_pos[3 * l + k] + parent_offset[3 * l + k];
         if (t.link_body[l] >= B && B != 0u) throw Error(kParseError, "link_body out of range");
     }
-    if (t.ndof > kMaxDof) throw Error(kNotSupported, "more than 32 articulation coordinates per env");
+    if (t.ndof > kMaxDof) throw Error(kNotSupported, "more than 64 articulation coordinates per env");
     t.floating_root = (L > 0 && t.jtype[0] == kFloating) ? 1u : 0u;
     t.child_begin.assign(L + 1, 0);
     for (uint32_t l = 0; l < L; ++l) {
@@ -266,7 +266,8 @@ void World::BuildLayout() {
     if (std::getenv("NUKA_B200_NO_OVERLAY") == nullptr) at = overlay;
     s.chol = take(hn * pad_ld(hn)); s.bm6 = take(72 + 24);
     at = std::max(at, dynamics_end);
-    s.mass = take(n * s.ld); s.factor = take(n * s.ld); s.vecs = take(8 * 32);
+    s.mass = take(n * s.ld); s.factor = take(n * s.ld); s.vstride = n > 32u ? 64u : 32u;
+    s.vecs = take(8 * s.vstride);
     const uint32_t slots = B ? t.n_free + 1u : 0u;
     s.bpose = take(7 * B); s.bvel = take(6 * slots);
     s.bwinv = take(6 * slots); s.bmass = take(7 * slots); s.bfree = take(6 * slots); s.bpseudo = take(6 * slots);
@@ -278,7 +279,7 @@ void World::BuildLayout() {
     s.jpool = take(std::max(std::max(tv.point_cap * 3u * ((n + 3u) & ~3u), 4u * S * 10u + 4u * S), 6u * B));
     s.cstage = s.jpool; s.aabb = s.jpool;
     const uint32_t nb = B + (n ? 1u : 0u);
-    s.binfo = take(3 * nb + 1 + 2 * tv.head_cap + 4 * 32 + nb + 1);
+    s.binfo = take(3 * nb + 1 + 2 * tv.head_cap + 4 * s.vstride + nb + 1);
     if (const char* pad = std::getenv("NUKA_B200_SMEM_PAD_WORDS")) at += (static_cast<uint32_t>(std::atoi(pad)) + 3u) & ~3u;   // occupancy experiments
     s.words = at;
     const size_t bytes = static_cast<size_t>(s.words) * 4u;
@@ -290,7 +291,7 @@ void World::BuildLayout() {
     size_t best = 0;
     for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) {
         if (w * bytes > 227u * 1024u) break;
-        resident[w] = static_cast<size_t>(step_kernel_resident_blocks(w, w * bytes)) * w;      // asks the runtime
+        resident[w] = static_cast<size_t>(step_kernel_resident_blocks(n, w, w * bytes)) * w;      // asks the runtime
         best = std::max(best, resident[w]);
     }
     warps_per_block_ = 1;

@@ -233,8 +233,12 @@ def quadruped_state(env_count, seed=0):
     return {"q": q, "base_pose": base}
 
 
-def humanoid(seed=0, dt=1.0 / 200.0, vel_iters=8):
-    """Config 3: floating pelvis, two 6-DoF legs (3-1-2), 3-DoF waist, two 7-DoF arms (3-1-3); capsule colliders."""
+def humanoid(seed=0, dt=1.0 / 200.0, vel_iters=8, self_collision=False):
+    """Config 3: floating pelvis, two 6-DoF legs (3-1-2), 3-DoF waist, two 7-DoF arms (3-1-3); capsule colliders.
+
+    Every capsule hangs from its joint down to the next joint of its chain (short stubs where joints coincide), left
+    and right limbs share their dimensions, and by default the capsules collide with the ground only: the stubs of
+    coincident joints overlap by construction, so self-collision needs a template with hand-placed geometry."""
     rng = np.random.Generator(np.random.PCG64(seed))
     tb = TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=32)
     specs = []   # (name, parent_name, axis, offset, capsule?)
@@ -256,7 +260,18 @@ def humanoid(seed=0, dt=1.0 / 200.0, vel_iters=8):
         chain(f"arm_{side}", waist, [Y, X, Z, Y, Z, X, Y],
               [(0, 0.19 * sy, 0.32), (0, 0, 0), (0, 0, 0), (0, 0, -0.28), (0, 0, -0.02), (0, 0, -0.24), (0, 0, 0)])
     radii = rng.uniform(0.03, 0.07, size=len(specs) + 1)
-    lengths = rng.uniform(0.1, 0.4, size=len(specs) + 1)
+    lengths = np.full(len(specs) + 1, 0.06)
+    lengths[0] = 0.12
+    for i, (name, parent, axis, offset) in enumerate(specs):
+        reach = float(np.linalg.norm(offset))
+        parent_row = 0 if parent == "pelvis" else [s[0] for s in specs].index(parent) + 1
+        if parent != "pelvis" and parent[:5] == name[:5] and reach > 0.1:
+            lengths[parent_row] = reach            # the parent's capsule spans to this joint
+    for i, (name, parent, axis, offset) in enumerate(specs):     # mirror the right side onto the left
+        if "_r" in name:
+            twin = [s[0] for s in specs].index(name.replace("_r", "_l")) + 1
+            radii[i + 1] = radii[twin]
+            lengths[i + 1] = lengths[twin]
     volumes = math.pi * radii ** 2 * lengths + 4.0 / 3.0 * math.pi * radii ** 3
     masses = 35.0 * volumes / volumes.sum()
     index = {}
@@ -266,12 +281,12 @@ def humanoid(seed=0, dt=1.0 / 200.0, vel_iters=8):
         diag = (m * (3 * r * r + ln * ln) / 12.0, m * (3 * r * r + ln * ln) / 12.0, 0.5 * m * r * r)
         return tb.add_link(parent, jtype, axis=axis, offset=offset, mass=m, inertia_diag=diag, com=(0, 0, -0.5 * ln),
                            kp=kp, kd=0.05 * kp, shape=(CAPSULE, r, 0.5 * ln), shape_pos=(0, 0, -0.5 * ln), mu=0.8,
-                           contype=1, conaffinity=1, armature=0.01)
+                           contype=1, conaffinity=1 if self_collision else 0, armature=0.01)
 
     index["pelvis"] = capsule_link(0, None, FLOATING, Z, (0, 0, 0), 0.0)
     for i, (name, parent, axis, offset) in enumerate(specs):
-        index[name] = capsule_link(i + 1, index[parent], REVOLUTE, axis, offset, 60.0)
-    tb.base_pose = [0, 0, 1.0, 1, 0, 0, 0]
+        index[name] = capsule_link(i + 1, index[parent], REVOLUTE, axis, offset, 300.0)
+    tb.base_pose = [0, 0, 0.05 + 0.38 + 0.38 + 0.06 + float(radii[[s[0] for s in specs].index('leg_l5') + 1]) + 0.005, 1, 0, 0, 0]
     tb.add_plane(0.0, mu=0.8, contype=2, conaffinity=1)
     return tb
 

@@ -325,3 +325,28 @@ def test_torque_and_velocity_control_modes(device, oracle, mode):
     moved = np.abs(w.download(F.JOINT_POSITION)[:, 1:] - st["q"][:, 1:]).max()
     assert moved > 0.01                                               # the commands really drive the joints
     w.destroy()
+
+
+def test_humanoid_35_coordinates(device, oracle):
+    """configs[2]'s articulation: 30 links, 35 coordinates (two per warp lane), capsules on a plane: mass matrix,
+    accelerations, a single step and a short trajectory against the oracle."""
+    E = 24
+    tb = T.humanoid(0)
+    st = T.humanoid_state(E, 1)
+    rng = np.random.Generator(np.random.PCG64(5))
+    qdot = np.zeros((E, 30), np.float32)
+    qdot[:, 1:] = rng.normal(0, 0.3, size=(E, 29))
+    w, o = make_pair(device, oracle, tb, E, {"q": st["q"], "qdot": qdot})
+    assert w.info.dofs_per_env == 35
+    assert rel(w.download(F.ARTICULATION_LINK_POSE), o.get("link_pose", 30 * 7)) < 1e-6
+    w.run_stage(1); o.dynamics(False)
+    assert rel(w.download(F.MASS_MATRIX), o.get("mass_matrix", 35 * 35)) < 1e-5
+    assert rel(w.download(F.JOINT_ACCELERATION), o.get("qddot", 30)) < 5e-5
+    w.step_n(1); o.step(1)
+    assert rel(w.download(F.JOINT_VELOCITY), o.get("qdot", 30)) < 5e-5
+    assert np.array_equal(w.download(F.PAIR_COUNT), o.get("pair_count", 1))
+    w.step_n(19); o.step(19)
+    assert rel(w.download(F.JOINT_POSITION), o.get("q", 30)) < 2e-4
+    assert rel(w.download(F.BASE_POSE), o.get("base_pose", 7)) < 2e-4
+    assert w.download(F.ENV_STATUS).max() == 0 and o.get("env_status", 1).max() == 0
+    w.destroy()
