@@ -27,6 +27,7 @@ struct Env {
     uint32_t dof_link[2], dof_comp[2];   // comp == kNoLink for scalar joints
     float vel0[2];           // step-start coordinate velocity
     uint32_t status;
+    uint32_t vstride;        // words per shared-memory vector: 32 x coordinates per lane
     uint32_t* cyc;           // stage cycle counters of this env, or null
     long long t0;
 };
@@ -48,7 +49,7 @@ NKB_DEV float* sm_pbias(const Env& e, uint32_t l) { return e.sm + e.lay->pbias +
 NKB_DEV float* sm_ic(const Env& e, uint32_t l) { return e.sm + e.lay->ic + 10u * l; }
 NKB_DEV float* sm_mass(const Env& e) { return e.sm + e.lay->mass; }
 NKB_DEV float* sm_factor(const Env& e) { return e.sm + e.lay->factor; }
-NKB_DEV float* sm_vec(const Env& e, uint32_t k) { return e.sm + e.lay->vecs + e.lay->vstride * k; }   // 32 or 64 words per vector
+NKB_DEV float* sm_vec(const Env& e, uint32_t k) { return e.sm + e.lay->vecs + e.vstride * k; }   // 32 or 64 words per vector
 // value of coordinate j from per-lane registers x[r] (coordinate lane + 32 r)
 template <int NR>
 NKB_DEV float coord_bcast(const float (&x)[NR], uint32_t j) {
@@ -62,6 +63,7 @@ enum { kVecBias = 0, kVecAcc = 1, kVecFree = 2, kVecU = 3, kVecD = 4, kVecPseudo
 
 NKB_DEV uint32_t joint_dofs(uint32_t t) { return (t == kRevolute || t == kPrismatic) ? 1u : t == kFloating ? 6u : t == kSpherical ? 3u : 0u; }
 
+template <int NR>
 NKB_DEV void env_begin(Env& e, const StepParams& p, float* sm, uint32_t env, uint32_t lane) {
     e.t = &p.t; e.s = &p.s; e.lay = &p.sm; e.sm = sm; e.env = env; e.lane = lane;
     const TemplateView& t = p.t;
@@ -81,8 +83,10 @@ NKB_DEV void env_begin(Env& e, const StepParams& p, float* sm, uint32_t env, uin
     e.qd = link ? p.s.qdot[at] : 0.f;
     e.qdd = 0.f; e.tau = 0.f;
     e.drive_command = e.drive_dissipation = e.drive_lower = e.drive_upper = 0.f;
+    e.vstride = 32u * NR;
+    e.dof_link[1] = 0u; e.dof_comp[1] = kNoLink; e.vel0[1] = 0.f;
 #pragma unroll
-    for (uint32_t r = 0u; r < 2u; ++r) {
+    for (uint32_t r = 0u; r < (uint32_t)NR; ++r) {
         const uint32_t c = lane + 32u * r;
         const bool dof = c < t.ndof;
         e.dof_link[r] = dof ? __ldg(t.dof_link + c) : 0u;

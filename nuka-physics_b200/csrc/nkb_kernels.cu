@@ -142,7 +142,7 @@ __global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ Ste
     const bool use_pseudo = t.cfg.pos_iters != 0u && (t.cfg.max_contacts != 0u || t.L != 0u);
     for (uint32_t step = 0u; step < p.steps; ++step) {
         Env e;
-        env_begin(e, p, sm, env, lane);
+        env_begin<NR>(e, p, sm, env, lane);
         if (p.mode == kModeRefresh) {
             if (has_artic) { stage_fk(e); }
             if (has_bodies) { stage_bodies(e, false); stage_store_bodies(e, false); }

@@ -33,7 +33,7 @@ NKB_DEV uint32_t* blk_inc(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u *
 // upper limit, dry friction, drive; vstride = 32 or 64 coordinates)
 NKB_DEV uint32_t* unit_table(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u * nb + 1u + 2u * e.t->head_cap; }
 // moving blocks in descent order, order[nb] = their count
-NKB_DEV uint32_t* block_order(const Env& e, uint32_t nb) { return unit_table(e, nb) + 4u * e.lay->vstride; }
+NKB_DEV uint32_t* block_order(const Env& e, uint32_t nb) { return unit_table(e, nb) + 4u * e.vstride; }
 NKB_DEV float* sm_bmass(const Env& e, uint32_t b) { return e.sm + e.lay->bmass + 7u * free_slot(e, b); }
 NKB_DEV float* sm_bfree(const Env& e, uint32_t b) { return e.sm + e.lay->bfree + 6u * free_slot(e, b); }
 NKB_DEV float* sm_bpseudo(const Env& e, uint32_t b) { return e.sm + e.lay->bpseudo + 6u * free_slot(e, b); }
@@ -129,10 +129,11 @@ NKB_DEV void solve_block_mass(const Env& e, uint32_t block, const float (&g)[NR]
 }
 
 // J M^-1 J^T of an articulated row from one forward solve with the unit-lower factor (articulation_mass.cuh:413-441)
+template <int NR>
 NKB_DEV float mass_coupling(const Env& e, const float* row) {
     const uint32_t n = e.t->ndof, ld = e.lay->ld;
     const float* F = sm_factor(e);
-    float y[kMaxDof];
+    float y[32 * NR];
     float r = 0.f;
     for (uint32_t i = 0; i < n; ++i) {
         float a = row[i];
@@ -144,6 +145,7 @@ NKB_DEV float mass_coupling(const Env& e, const float* row) {
 }
 
 // Head setup: penalty, response scales (block_descent_tile.cuh:743-797).
+template <int NR>
 NKB_DEV void init_heads(Env& e, const Tile& tile) {
     const TemplateView& t = *e.t;
     for (uint32_t h = e.lane; h < tile.nheads; h += 32u) {
@@ -157,10 +159,10 @@ NKB_DEV void init_heads(Env& e, const Tile& tile) {
             if (ob == kNoBlock16) { /* static or kinematic side: no response */ }
             else if (ob == t.B) {
                 if (jo & kUnitRow) {
-                    float row[kMaxDof];
+                    float row[32 * NR];
                     for (uint32_t i = 0; i < t.ndof; ++i) row[i] = i == (jo & 0xffffu) ? hf(e, HF_UNITV, h) : 0.f;
-                    c = mass_coupling(e, row);
-                } else c = mass_coupling(e, sm_jpool(e) + jo);
+                    c = mass_coupling<NR>(e, row);
+                } else c = mass_coupling<NR>(e, sm_jpool(e) + jo);
             } else {
                 const V3 dir = hf3(e, HF_N, h) * (side == 0u ? 1.f : -1.f);
                 const V3 ang = cross(hf3(e, side == 0u ? HF_RA : HF_RB, h), dir);
@@ -204,13 +206,13 @@ NKB_DEV void index_blocks(Env& e, const Tile& tile, bool color) {
     }
     if (e.lane == 0u) blk_inc_begin(e, nb, nb) = at;
     uint32_t* utab = unit_table(e, nb);
-    for (uint32_t k = e.lane; k < 4u * e.lay->vstride; k += 32u) utab[k] = 0xffffffffu;
+    for (uint32_t k = e.lane; k < 4u * e.vstride; k += 32u) utab[k] = 0xffffffffu;
     __syncwarp();
     for (uint32_t h = e.lane; h < tile.nheads; h += 32u) {
         const uint32_t jo = hu(e, HF_JOFF, h), o = hu(e, HF_OWNER, h), fl = hu(e, HF_FLAGS, h);
         if (!(jo & kUnitRow) || ((o & 0xffffu) != e.t->B && (o >> 16) != e.t->B)) continue;
         const uint32_t slot = (fl & kHeadDrive) ? 3u : (fl & kHeadFriction) ? 2u : hf(e, HF_UNITV, h) < 0.f ? 1u : 0u;
-        utab[slot * e.lay->vstride + (jo & 0xffffu)] = h;
+        utab[slot * e.vstride + (jo & 0xffffu)] = h;
     }
     __syncwarp();
     if (!color) return;
@@ -526,7 +528,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             // rows on a single coordinate only touch that coordinate (block_descent_tile.cuh:1555-1568)
             if (artic) {
                 const uint32_t* utab = unit_table(e, nb);
-                const uint32_t vs = e.lay->vstride;
+                const uint32_t vs = e.vstride;
 #pragma unroll
                 for (int r = 0; r < NR; ++r) {
 #pragma unroll 1
@@ -869,7 +871,7 @@ NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
         if (artic) {
             const uint32_t n4 = (dim + 3u) & ~3u;
             const uint32_t* utab = unit_table(e, nb);
-            const uint32_t vs = e.lay->vstride;
+            const uint32_t vs = e.vstride;
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
                 const uint32_t c = l + 32u * r;
@@ -995,7 +997,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
         }
     }
     __syncwarp();
-    init_heads(e, tile);
+    init_heads<NR>(e, tile);
     tick(e, 8);
     float rows[3] = {0.f, 0.f, 0.f};
     float cls[4] = {0.f, 0.f, 0.f, 0.f};
