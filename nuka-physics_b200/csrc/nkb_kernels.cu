@@ -126,7 +126,7 @@ NKB_DEV void stage_store_bodies(Env& e, bool velocities) {
 // The cap steers the compiler's allocation (measured best between 176 and 200: 156-167 registers, 12 warps per SM
 // stay resident; at 208 it takes 171 and residency halves).
 #ifndef NKB_MAXNREG
-#define NKB_MAXNREG 192
+#define NKB_MAXNREG 176
 #endif
 // NR = coordinates per lane: 1 for articulations of up to 32 coordinates, 2 for up to 64.
 template <int NR>
