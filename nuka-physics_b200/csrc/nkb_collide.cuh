@@ -485,7 +485,7 @@ NKB_DEV V3 inv_xf_point(const float* pose, V3 w) {
 NKB_DEV void stage_narrowphase(Env& e, uint32_t pair_count) {
     const TemplateView& t = *e.t;
     const float separation = fmaxf(t.cfg.contact_margin, 0.0005f), reach = query_reach(t.cfg);
-    const uint32_t S = t.cfg.max_contacts;
+    const uint32_t S = t.slot_cap;            // slots past the admissible-pair count can never fill and have no storage
     uint32_t* cc = sm_ccount(e);
     for (uint32_t s = e.lane; s < S; s += 32u) {
         uint32_t count = 0u;
@@ -526,7 +526,7 @@ NKB_DEV void stage_store_contacts(Env& e, uint32_t pair_count) {
         const size_t gs = (size_t)e.env * S + s;
         const uint32_t ab = s < pair_count ? sm_pairs(e)[s] : 0u;
         e.s->pairs[gs * 2u] = ab >> 16; e.s->pairs[gs * 2u + 1u] = ab & 0xffffu;
-        const uint32_t n = sm_ccount(e)[s];
+        const uint32_t n = s < t.slot_cap ? sm_ccount(e)[s] : 0u;
         e.s->contact_count[gs] = n;
         for (uint32_t i = 0; i < 4u; ++i) {
             const bool live = i < n;

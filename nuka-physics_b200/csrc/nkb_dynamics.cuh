@@ -57,9 +57,11 @@ NKB_DEV float coord_bcast(const float (&x)[NR], uint32_t j) {
     return __shfl_sync(NKB_FULL, j < 32u ? x[0] : x[NR - 1], j & 31u);
 }
 // vector slots
-enum { kVecBias = 0, kVecAcc = 1, kVecFree = 2, kVecU = 3, kVecD = 4, kVecPseudo = 5, kVecTmp = 6, kVecTmp2 = 7,
+enum { kVecAcc = 0, kVecFree = 1, kVecU = 2, kVecPseudo = 3, kVecTmp = 4, kVecTmp2 = 5,
        // Newton-loop scratch shares slots whose other users run before or after the solve
-       kVecS0 = kVecTmp, kVecS1 = kVecTmp2, kVecS2 = kVecAcc, kVecCount = 8 };
+       kVecS0 = kVecTmp, kVecS1 = kVecTmp2, kVecS2 = kVecAcc,
+       // the Newton direction is staged after the last read of S0 in an iteration and consumed before the next write
+       kVecD = kVecS0, kVecCount = 6 };
 
 NKB_DEV uint32_t joint_dofs(uint32_t t) { return (t == kRevolute || t == kPrismatic) ? 1u : t == kFloating ? 6u : t == kSpherical ? 3u : 0u; }
 
@@ -312,7 +314,6 @@ NKB_DEV void stage_dynamics(Env& e, bool integrate_velocity) {
                 e.vel0[r] = sm_vel(e, dl)[e.dof_comp[r]];
                 rhs[r] = -bias;
             }
-            sm_vec(e, kVecBias)[c] = bias;
         }
     }
     // mass matrix, ops/articulation_mass.cuh:124-253

@@ -1,221 +1,10 @@
-// Fused step kernel of the batched articulated step: one warp advances one env through the whole pipeline
-// (kinematics, drives, dynamics, collision, row assembly, block-descent solve, integration) with every
-// intermediate in the warp's shared-memory slice; global memory sees only the env's state.
-// The stage order is the reference's nk::Pipeline::BuildInterval (src/nk/pipeline/pipeline.cpp:367-986).
+// Host side of the kernels: picks the step-kernel variant of a world, and the small reset / observation kernels.
 #include <cuda_runtime.h>
 #include <algorithm>
 #include <cstdio>
-#include "nkb_solver.cuh"
 #include "nkb_launch.h"
 
 namespace nkb {
-
-// Free rigid bodies: gyroscopic torque-free rotation + pose update (ops/articulation.cu:1059-1116,
-// ops/rigid_types.cuh:39-122).
-NKB_DEV bool solve_free_rotation(V3 w0, V3 inv_i, float dt, V3& mid_out) {
-    mid_out = mk3(0.f, 0.f, 0.f);
-    const V3 m0 = mk3(w0.x / inv_i.x, w0.y / inv_i.y, w0.z / inv_i.z);
-    const float scale = fmaxf(fabsf(m0.x), fmaxf(fabsf(m0.y), fabsf(m0.z)));
-    if (scale == 0.0f) return true;
-    const V3 u0 = m0 * (1.0f / scale);
-    const V3 a = inv_i * scale;
-    const V3 c = mk3(dt * (a.y - a.z), dt * (a.z - a.x), dt * (a.x - a.y));
-    V3 u = u0;
-    for (uint32_t it = 0; it <= 12u; ++it) {
-        const V3 mid = (u0 + u) * 0.5f;
-        const V3 r = mk3(u.x - u0.x + c.x * mid.y * mid.z, u.y - u0.y + c.y * mid.z * mid.x, u.z - u0.z + c.z * mid.x * mid.y);
-        const float res = fmaxf(fabsf(r.x), fmaxf(fabsf(r.y), fabsf(r.z)));
-        if (!isfinite(res)) return false;
-        if (res <= 1.0e-6f) { mid_out = mk3(a.x * mid.x, a.y * mid.y, a.z * mid.z); return true; }
-        if (it == 12u) break;
-        float j[3][4] = {{1.0f, 0.5f * c.x * mid.z, 0.5f * c.x * mid.y, r.x},
-                         {0.5f * c.y * mid.z, 1.0f, 0.5f * c.y * mid.x, r.y},
-                         {0.5f * c.z * mid.y, 0.5f * c.z * mid.x, 1.0f, r.z}};
-        for (int col = 0; col < 3; ++col) {
-            int piv = col;
-            for (int row = col + 1; row < 3; ++row) if (fabsf(j[row][col]) > fabsf(j[piv][col])) piv = row;
-            if (!isfinite(j[piv][col]) || fabsf(j[piv][col]) < 1.0e-12f) return false;
-            for (int k = col; k < 4; ++k) { const float tmp = j[col][k]; j[col][k] = j[piv][k]; j[piv][k] = tmp; }
-            for (int row = col + 1; row < 3; ++row) {
-                const float f = j[row][col] / j[col][col];
-                for (int k = col + 1; k < 4; ++k) j[row][k] -= f * j[col][k];
-            }
-        }
-        V3 d;
-        d.z = j[2][3] / j[2][2];
-        d.y = (j[1][3] - j[1][2] * d.z) / j[1][1];
-        d.x = (j[0][3] - j[0][1] * d.y - j[0][2] * d.z) / j[0][0];
-        bool accepted = false; float alpha = 1.0f;
-        for (int bt = 0; bt < 8; ++bt) {
-            const V3 tt = u - d * alpha;
-            const V3 md = (u0 + tt) * 0.5f;
-            const V3 tr = mk3(tt.x - u0.x + c.x * md.y * md.z, tt.y - u0.y + c.y * md.z * md.x, tt.z - u0.z + c.z * md.x * md.y);
-            const float tres = fmaxf(fabsf(tr.x), fmaxf(fabsf(tr.y), fabsf(tr.z)));
-            if (isfinite(tres) && tres < res) { u = tt; accepted = true; break; }
-            alpha *= 0.5f;
-        }
-        if (!accepted) break;
-    }
-    return false;
-}
-
-NKB_DEV void stage_integrate_bodies(Env& e, bool use_pseudo) {
-    const TemplateView& t = *e.t;
-    const float dt = t.cfg.dt;
-    for (uint32_t b = e.lane; b < t.B; b += 32u) {
-        if (!(__ldg(t.inv_mass + b) > 0.f) || __ldg(t.body_to_link + b) != kNoLink) continue;
-        float* pose = sm_bpose(e, b);
-        float* bv = sm_bvel(e, b);
-        const V3 inv_i = ld3(t.inv_inertia + 3u * b);
-        const Q4 iq = ldq(t.inertial_quat + 4u * b);
-        const Q4 principal = qnorm_le(qmul(ldq(pose + 3), iq), 1.0e-12f);
-        const V3 w0 = qrot(mkq(principal.w, -principal.x, -principal.y, -principal.z), ld3(bv + 3));
-        V3 midpoint;
-        if (!solve_free_rotation(w0, inv_i, dt, midpoint)) { e.status |= kStatusGyroFailure; continue; }
-        const V3 momentum = qrot(principal, mk3(w0.x / inv_i.x, w0.y / inv_i.y, w0.z / inv_i.z));
-        V3 v = ld3(bv);
-        const V3 w = qrot(principal, midpoint);
-        const V3 ipos = ld3(t.inertial_pos + 3u * b);
-        const V3 center = ld3(pose) + qrot(ldq(pose + 3), ipos);
-        Q4 q = qnorm_le(qmul(mkq(1.0f, 0.5f * dt * w.x, 0.5f * dt * w.y, 0.5f * dt * w.z), ldq(pose + 3)), 1.0e-12f);
-        if (use_pseudo) {
-            const float* ps = sm_bpseudo(e, b);
-            v = v + ld3(ps);
-            q = qnorm_le(qmul(mkq(1.0f, 0.5f * dt * ps[3], 0.5f * dt * ps[4], 0.5f * dt * ps[5]), q), 1.0e-12f);
-        }
-        stq(pose + 3, q);
-        st3(pose, center + v * dt - qrot(q, ipos));
-        float winv[6];
-        world_inv_inertia(q, iq, inv_i, winv);
-        st3(bv + 3, sym_mulv(winv, momentum));
-    }
-    __syncwarp();
-}
-
-// Applied drive efforts from the solved drive multipliers (ops/articulation.cu:999-1016).
-NKB_DEV void stage_readout_drives(Env& e, uint32_t nheads) {
-    const TemplateView& t = *e.t;
-    float* tmp = sm_vec(e, kVecTmp);
-    tmp[e.lane] = 0.f;
-    uint32_t* has = reinterpret_cast<uint32_t*>(sm_vec(e, kVecTmp2));
-    has[e.lane] = 0u;
-    __syncwarp();
-    for (uint32_t h = e.lane; h < nheads; h += 32u)
-        if (hu(e, HF_FLAGS, h) & kHeadDrive) { const uint32_t link = hu(e, HF_REF, h); tmp[link] = hf(e, HF_LAM, h); has[link] = 1u; }
-    __syncwarp();
-    float applied = 0.f;
-    if (e.lane < t.L && has[e.lane]) { applied = tmp[e.lane] / t.cfg.dt - e.drive_dissipation * e.qd; e.tau += applied; }
-    if (e.lane < t.L) e.s->actuator[(size_t)e.env * t.L + e.lane] = applied;
-    __syncwarp();
-}
-
-NKB_DEV void stage_store_bodies(Env& e, bool velocities) {
-    const TemplateView& t = *e.t;
-    float* gp = e.s->body_pose + (size_t)e.env * t.B * 7u;
-    const float* sp = e.sm + e.lay->bpose;
-    for (uint32_t k = e.lane; k < t.B * 7u; k += 32u) gp[k] = sp[k];
-    if (!velocities) return;
-    for (uint32_t b = e.lane; b < t.B; b += 32u) {
-        if (__ldg(t.body_to_link + b) != kNoLink || !(__ldg(t.inv_mass + b) > 0.f)) continue;     // only free dynamic bodies move
-        const size_t gb = (size_t)e.env * t.B + b;
-        st3(e.s->body_linvel + gb * 3u, ld3(sm_bvel(e, b)));
-        st3(e.s->body_angvel + gb * 3u, ld3(sm_bvel(e, b) + 3));
-    }
-}
-
-// The cap steers the compiler's allocation (measured best between 176 and 200: 156-167 registers, 12 warps per SM
-// stay resident; at 208 it takes 171 and residency halves).
-#ifndef NKB_MAXNREG
-#define NKB_MAXNREG 176
-#endif
-// NR = coordinates per lane: 1 for articulations of up to 32 coordinates, 2 for up to 64.
-template <int NR>
-__global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ StepParams p) {
-    extern __shared__ __align__(16) float smem[];
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t env = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (env >= p.s.env_count) return;
-    float* sm = smem + (size_t)warp * p.sm.words;
-    const TemplateView& t = p.t;
-    const bool has_artic = t.L != 0u, has_bodies = t.B != 0u;
-    const bool has_collidables = has_bodies && t.cfg.max_contacts != 0u;
-    const bool use_pseudo = t.cfg.pos_iters != 0u && (t.cfg.max_contacts != 0u || t.L != 0u);
-    for (uint32_t step = 0u; step < p.steps; ++step) {
-        Env e;
-        env_begin<NR>(e, p, sm, env, lane);
-        if (p.mode == kModeRefresh) {
-            if (has_artic) { stage_fk(e); }
-            if (has_bodies) { stage_bodies(e, false); stage_store_bodies(e, false); }
-            if (has_artic) {
-                float* gp = p.s.link_pose + (size_t)env * t.L * 7u;
-                for (uint32_t k = lane; k < t.L * 7u; k += 32u) gp[k] = sm[p.sm.pose + k];
-            }
-            return;
-        }
-        tick(e, 0);
-        if (has_artic) { stage_fk(e); tick(e, 1); stage_drives(e); stage_dynamics<NR>(e, p.mode != kModeDynamicsOnly); tick(e, 2); }
-        if (p.mode == kModeDynamicsOnly) {
-            if (lane < t.L) p.s.qddot[(size_t)env * t.L + lane] = e.qdd;
-            return;
-        }
-        uint32_t pair_count = 0u, nheads = 0u;
-        if (has_bodies) stage_bodies(e, true);
-        if (has_collidables) {
-            stage_aabbs(e);
-            pair_count = stage_pairs(e);
-            tick(e, 3);
-            stage_narrowphase(e, pair_count);
-            tick(e, 4);
-            stage_store_contacts(e, pair_count);
-            tick(e, 5);
-        }
-        if (p.mode == kModeCollideOnly) {
-            if (has_bodies) stage_store_bodies(e, false);
-            uint32_t st = e.status;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) st |= __shfl_xor_sync(NKB_FULL, st, o);
-            if (lane == 0u) p.s.status[env] |= st;
-            return;
-        }
-        nheads = stage_rows<NR>(e, pair_count);
-        tick(e, 6);
-        stage_warm_start(e, nheads);
-        tick(e, 7);
-        stage_solve<NR>(e, nheads);
-        if (has_collidables) stage_cache_commit(e, nheads);
-        if (has_artic) stage_readout_drives(e, nheads);
-        tick(e, 12);
-        if (has_artic) { stage_integrate_links(e, use_pseudo); }
-        if (has_bodies) stage_integrate_bodies(e, use_pseudo);
-        __syncwarp();
-        if (has_artic) { stage_fk(e); stage_link_velocities(e); stage_store_links(e); }
-        if (has_bodies) {
-            // link mirrors follow the new link poses; free bodies keep their integrated pose
-            for (uint32_t b = lane; b < t.B; b += 32u) {
-                const uint32_t link = __ldg(t.body_to_link + b);
-                if (link == kNoLink) continue;
-                float* bp = sm_bpose(e, b);
-                const float* lp = sm_pose(e, link);
-                if (__ldg(t.body_geom_kind + b) != 0u) {
-                    const Q4 pq = ldq(lp + 3);
-                    st3(bp, ld3(lp) + qrot(pq, ld3(t.body_geom_pos + 3u * b)));
-                    stq(bp + 3, qmul(pq, ldq(t.body_geom_quat + 4u * b)));
-                } else {
-#pragma unroll
-                    for (int k = 0; k < 7; ++k) bp[k] = lp[k];
-                }
-            }
-            __syncwarp();
-            stage_store_bodies(e, true);
-        }
-        uint32_t st = e.status;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) st |= __shfl_xor_sync(NKB_FULL, st, o);
-        if (lane == 0u && st != 0u) p.s.status[env] |= st;
-        __syncwarp();
-        tick(e, 13);
-    }
-}
 
 // Per-env reset from the creation snapshot (reference ops/readout.cu:771-776 RestoreState semantics).
 __global__ void reset_kernel(ResetParams r) {
@@ -230,36 +19,22 @@ __global__ void reset_kernel(ResetParams r) {
     }
 }
 
-template <int NR>
-static int resident_blocks(uint32_t warps_per_block, size_t shared_bytes) {
-    if (shared_bytes > 48u * 1024u && cudaFuncSetAttribute(step_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared_bytes) != cudaSuccess) {
-        cudaGetLastError();
-        return 0;
-    }
-    int blocks = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, step_kernel<NR>, (int)(warps_per_block * 32u), shared_bytes) != cudaSuccess) {
-        cudaGetLastError();
-        return 0;
-    }
-    return blocks;
+extern const StepVariant kStepNarrow, kStepNarrowRigid, kStepWide, kStepWideRigid;
+
+// up to 32 or up to 64 coordinates per articulation; with or without free rigid bodies
+static const StepVariant& step_variant(uint32_t ndof, uint32_t n_free) {
+    if (ndof > 32u) return n_free != 0u ? kStepWideRigid : kStepWide;
+    return n_free != 0u ? kStepNarrowRigid : kStepNarrow;
 }
 
-int step_kernel_resident_blocks(uint32_t ndof, uint32_t warps_per_block, size_t shared_bytes) {
-    return ndof > 32u ? resident_blocks<2>(warps_per_block, shared_bytes) : resident_blocks<1>(warps_per_block, shared_bytes);
+int step_kernel_registers(uint32_t ndof, uint32_t n_free) { return step_variant(ndof, n_free).registers(); }
+
+int step_kernel_resident_blocks(uint32_t ndof, uint32_t n_free, uint32_t warps_per_block, size_t shared_bytes) {
+    return step_variant(ndof, n_free).resident_blocks(warps_per_block, shared_bytes);
 }
 
 cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
-    const size_t bytes = (size_t)warps_per_block * p.sm.words * sizeof(float);
-    const bool wide = p.t.ndof > 32u;
-    if (bytes > 48u * 1024u) {
-        const cudaError_t err = wide ? cudaFuncSetAttribute(step_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes)
-                                     : cudaFuncSetAttribute(step_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-        if (err != cudaSuccess) return err;
-    }
-    const uint32_t blocks = (p.s.env_count + warps_per_block - 1u) / warps_per_block;
-    if (wide) step_kernel<2><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
-    else step_kernel<1><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
-    return cudaGetLastError();
+    return step_variant(p.t.ndof, p.t.n_free).launch(p, warps_per_block, stream);
 }
 
 // One record per env for the RL caller (python/nuka/tasks/go2_obs.py:47-48 composes the same quantities):

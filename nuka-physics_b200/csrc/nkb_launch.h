@@ -24,7 +24,18 @@ struct ResetParams {
 
 // Blocks of `warps_per_block` warps with `shared_bytes` of dynamic shared memory that one SM keeps resident (registers,
 // shared memory and block slots considered); 0 when the shape cannot launch.  The device must be current.
-int step_kernel_resident_blocks(uint32_t ndof, uint32_t warps_per_block, size_t shared_bytes);
+// The step kernel has one variant per (coordinates per lane, free rigid bodies present) pair, chosen from `ndof`
+// (up to 32 / up to 64 coordinates) and `n_free` (free dynamic bodies per env).
+int step_kernel_resident_blocks(uint32_t ndof, uint32_t n_free, uint32_t warps_per_block, size_t shared_bytes);
+// Registers per thread of the step kernel variant that serves the world.
+int step_kernel_registers(uint32_t ndof, uint32_t n_free);
+// Host-side handle of one compiled step-kernel variant.
+struct StepParams;
+struct StepVariant {
+    int (*resident_blocks)(uint32_t warps_per_block, size_t shared_bytes);
+    int (*registers)();
+    cudaError_t (*launch)(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream);
+};
 // Enqueues `p.steps` fused steps (or one parity-tap stage, see StepMode) for every env.
 cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream);
 // Restores `count` envs (all when r.env_ids is null) from their snapshots.

@@ -305,8 +305,11 @@ NKB_DEV void stage_cache_commit(Env& e, uint32_t nheads) {
     if (npts == 0u) return;
     CacheEntry* cache = e.s->cache + (size_t)e.env * npts;
     CacheEntry* stage = reinterpret_cast<CacheEntry*>(e.sm + e.lay->cstage);
-    uint32_t* owner = reinterpret_cast<uint32_t*>(stage + npts);
-    for (uint32_t c = e.lane; c < npts; c += 32u) owner[c] = 0xffffffffu;
+    // only points of fillable slots can own an entry, and a step retains at most the previous step's owners
+    const uint32_t nown = t.slot_cap * 4u;
+    const uint32_t stage_cap = min(t.point_cap, nown);
+    uint32_t* owner = reinterpret_cast<uint32_t*>(stage + stage_cap);
+    for (uint32_t c = e.lane; c < nown; c += 32u) owner[c] = 0xffffffffu;
     __syncwarp();
     // owners: first current point of each identity
     uint32_t ncontact = 0u;
@@ -343,15 +346,16 @@ NKB_DEV void stage_cache_commit(Env& e, uint32_t nheads) {
             for (uint32_t d = 0u; d < c && keep; ++d) if (cache[d].pair == en.pair && cache[d].feature == en.feature) keep = false;
         }
         const uint32_t m = __ballot_sync(NKB_FULL, keep);
-        if (keep) { en.age += 1u; stage[nret + __popc(m & ((1u << e.lane) - 1u))] = en; }
-        nret += __popc(m);
+        const uint32_t to = nret + __popc(m & ((1u << e.lane) - 1u));
+        if (keep && to < stage_cap) { en.age += 1u; stage[to] = en; }
+        nret = min(nret + __popc(m), stage_cap);
     }
     __syncwarp();
     // write the new cache: owners at their own point, retained entries into the free points in order
     uint32_t free_seen = 0u;
     for (uint32_t base = 0u; base < npts; base += 32u) {
         const uint32_t c = base + e.lane;
-        const bool is_free = c < npts && owner[c] == 0xffffffffu;
+        const bool is_free = c < npts && (c >= nown || owner[c] == 0xffffffffu);
         const uint32_t m = __ballot_sync(NKB_FULL, is_free);
         if (c < npts) {
             CacheEntry en;

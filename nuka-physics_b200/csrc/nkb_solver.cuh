@@ -29,11 +29,12 @@ NKB_DEV uint32_t& blk_dim(const Env& e, uint32_t b) { return sm_binfo(e)[b]; }
 NKB_DEV uint32_t& blk_color(const Env& e, uint32_t nb, uint32_t b) { return sm_binfo(e)[nb + b]; }
 NKB_DEV uint32_t& blk_inc_begin(const Env& e, uint32_t nb, uint32_t b) { return sm_binfo(e)[2u * nb + b]; }
 NKB_DEV uint32_t* blk_inc(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u * nb + 1u; }
-// unit rows of the articulation by coordinate: utab[slot * vstride + coordinate] = head or ~0 (slots: lower limit,
-// upper limit, dry friction, drive; vstride = 32 or 64 coordinates)
-NKB_DEV uint32_t* unit_table(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u * nb + 1u + 2u * e.t->head_cap; }
+// unit rows of the articulation by coordinate: utab[slot * vstride + coordinate] = head or 0xffff (slots: lower limit,
+// upper limit, dry friction, drive; vstride = 32 or 64 coordinates), 16-bit entries
+constexpr uint32_t kNoUnitHead = 0xffffu;
+NKB_DEV uint16_t* unit_table(const Env& e, uint32_t nb) { return reinterpret_cast<uint16_t*>(sm_binfo(e) + 3u * nb + 1u + 2u * e.t->head_cap); }
 // moving blocks in descent order, order[nb] = their count
-NKB_DEV uint32_t* block_order(const Env& e, uint32_t nb) { return unit_table(e, nb) + 4u * e.vstride; }
+NKB_DEV uint32_t* block_order(const Env& e, uint32_t nb) { return sm_binfo(e) + 3u * nb + 1u + 2u * e.t->head_cap + 2u * e.vstride; }
 NKB_DEV float* sm_bmass(const Env& e, uint32_t b) { return e.sm + e.lay->bmass + 7u * free_slot(e, b); }
 NKB_DEV float* sm_bfree(const Env& e, uint32_t b) { return e.sm + e.lay->bfree + 6u * free_slot(e, b); }
 NKB_DEV float* sm_bpseudo(const Env& e, uint32_t b) { return e.sm + e.lay->bpseudo + 6u * free_slot(e, b); }
@@ -205,14 +206,14 @@ NKB_DEV void index_blocks(Env& e, const Tile& tile, bool color) {
         }
     }
     if (e.lane == 0u) blk_inc_begin(e, nb, nb) = at;
-    uint32_t* utab = unit_table(e, nb);
-    for (uint32_t k = e.lane; k < 4u * e.vstride; k += 32u) utab[k] = 0xffffffffu;
+    uint16_t* utab = unit_table(e, nb);
+    for (uint32_t k = e.lane; k < 4u * e.vstride; k += 32u) utab[k] = (uint16_t)kNoUnitHead;
     __syncwarp();
     for (uint32_t h = e.lane; h < tile.nheads; h += 32u) {
         const uint32_t jo = hu(e, HF_JOFF, h), o = hu(e, HF_OWNER, h), fl = hu(e, HF_FLAGS, h);
         if (!(jo & kUnitRow) || ((o & 0xffffu) != e.t->B && (o >> 16) != e.t->B)) continue;
         const uint32_t slot = (fl & kHeadDrive) ? 3u : (fl & kHeadFriction) ? 2u : hf(e, HF_UNITV, h) < 0.f ? 1u : 0u;
-        utab[slot * e.vstride + (jo & 0xffffu)] = h;
+        utab[slot * e.vstride + (jo & 0xffffu)] = (uint16_t)h;
     }
     __syncwarp();
     if (!color) return;
@@ -301,9 +302,10 @@ NKB_DEV void respond(const HeadRegs& r, V3 move, V3& f, float& cxx, float& cyy, 
 
 // Row steps J d of a block's incident heads (block_descent_tile.cuh:2019-2044); lane = head, d staged in shared
 // memory with zeros past the block's dimension.
+template <bool kRigid>
 NKB_DEV void row_steps(Env& e, const Tile& tile, uint32_t b, const float* dvec) {
     const uint32_t nb = tile.nblocks, dim = blk_dim(e, b);
-    const bool artic = b == e.t->B;
+    const bool artic = !kRigid || b == e.t->B;
     const uint32_t* inc = blk_inc(e, nb);
     const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
     const uint32_t chunks = (dim + 3u) >> 2, n4 = chunks << 2;
@@ -330,6 +332,17 @@ NKB_DEV void row_steps(Env& e, const Tile& tile, uint32_t b, const float* dvec) 
                     }
                 }
                 step = mk3(s0, s1, s2);
+            }
+        } else if (k - ib < e.lay->rjac_heads) {
+            // rigid block whose head rows were staged at the start of the descent: 3 rows of 8 floats per head
+            const float4* j4 = reinterpret_cast<const float4*>(e.sm + e.lay->rjac + (k - ib) * 24u);
+            const float4 d0 = d4[0], d1 = d4[1];
+            const float4 a0 = j4[0], a1 = j4[1];
+            step.x = a0.x * d0.x + a0.y * d0.y + a0.z * d0.z + a0.w * d0.w + a1.x * d1.x + a1.y * d1.y;
+            if (cone) {
+                const float4 b0 = j4[2], b1 = j4[3], c0 = j4[4], c1 = j4[5];
+                step.y = b0.x * d0.x + b0.y * d0.y + b0.z * d0.z + b0.w * d0.w + b1.x * d1.x + b1.y * d1.y;
+                step.z = c0.x * d0.x + c0.y * d0.y + c0.z * d0.z + c0.w * d0.w + c1.x * d1.x + c1.y * d1.y;
             }
         } else {
             const uint32_t side = head_owner(e, h, 0u) == b ? 0u : 1u;
@@ -416,11 +429,12 @@ NKB_DEV void apply_moves(Env& e, const Tile& tile, uint32_t b, float alpha) {
 // Newton steps with exact line search on one block.  A lane owns coordinates lane + 32 r (r < NR) and the same rows of
 // the Newton matrix, which lives in the env's shared-memory slice in float4-readable rows; lane k also owns the k-th
 // incident head in the row evaluations and publishes its response through the head's shared-memory fields.
-template <int NR>
+// kRigid = false compiles the descent for worlds without free bodies: the articulation is the only block and the
+// rigid-block code (dense 6 x 6 mass, staged 3 x 8 Jacobian rows) drops out.
+template <int NR, bool kRigid>
 NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
-    const TemplateView& t = *e.t;
     const uint32_t l = e.lane, nb = tile.nblocks, dim = blk_dim(e, b);
-    const bool artic = b == t.B;
+    const bool artic = !kRigid || b == e.t->B;
     const uint32_t* inc = blk_inc(e, nb);
     const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
     const uint32_t chunks = (dim + 3u) >> 2, ldh = pad_ld(dim);
@@ -432,9 +446,31 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     float* H = e.sm + e.lay->chol;
     float* m6 = e.sm + e.lay->bm6;      // 6 x 12 dense mass of a rigid block, then 3 x 8 Jacobian rows of one head
     float* jscr = m6 + 72u;
+    // rigid block: dense mass, and the Jacobian rows of its incident heads staged once for the whole descent
+    // (3 rows of 8 floats per head, as many heads as the staging area holds)
     if (!artic) {
-        if (l < 6u) for (uint32_t k = 0u; k < 8u; ++k) m6[l * 12u + k] = k < 6u ? block_mass(e, b, l, k) : 0.f;
+        if (l < 6u) {
+            const float* bm = sm_bmass(e, b);
+            float* row = m6 + l * 12u;
+#pragma unroll
+            for (uint32_t k = 0u; k < 8u; ++k) row[k] = 0.f;
+            if (l < 3u) row[l] = bm[0];
+            else {
+                const uint32_t a = l - 3u;
+                row[3u] = a == 0u ? bm[1] : a == 1u ? bm[4] : bm[5];
+                row[4u] = a == 0u ? bm[4] : a == 1u ? bm[2] : bm[6];
+                row[5u] = a == 0u ? bm[5] : a == 1u ? bm[6] : bm[3];
+            }
+        }
         if (l < 24u) jscr[l] = 0.f;
+        const uint32_t staged_count = min(ie - ib, e.lay->rjac_heads);
+        float* out = e.sm + e.lay->rjac;
+#pragma unroll 1
+        for (uint32_t j = 0u; j < staged_count; ++j) {
+            const uint32_t h = inc[ib + j];
+            const uint32_t ss = head_owner(e, h, 0u) == b ? 0u : 1u, as = head_axes(e, h);
+            if (l < 24u) { const uint32_t ax = l >> 3, i = l & 7u; out[j * 24u + l] = (i < 6u && ax < as) ? head_jac(e, h, ss, ax, i, b) : 0.f; }
+        }
     }
     bool coord[NR];
     float* Hr[NR];
@@ -527,14 +563,14 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             tick(e, 16);
             // rows on a single coordinate only touch that coordinate (block_descent_tile.cuh:1555-1568)
             if (artic) {
-                const uint32_t* utab = unit_table(e, nb);
+                const uint16_t* utab = unit_table(e, nb);
                 const uint32_t vs = e.vstride;
 #pragma unroll
                 for (int r = 0; r < NR; ++r) {
 #pragma unroll 1
                     for (uint32_t slot = 0u; slot < 4u; ++slot) {
                         const uint32_t h = utab[slot * vs + l + 32u * r];
-                        if (h == 0xffffffffu) continue;
+                        if (h == kNoUnitHead) continue;
                         const float v = hf(e, HF_UNITV, h);
                         diag[r] += v * hf(e, HF_C, h) * v;
                         csum_addp(g[r], v, hf(e, HF_F, h));
@@ -554,6 +590,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                     if (!(f.x != 0.f || f.y != 0.f || f.z != 0.f || c0 != 0.f || c1 != 0.f || c2 != 0.f || c12 != 0.f || nz.x != 0.f || nz.y != 0.f || nz.z != 0.f)) continue;
                     const float* jr; uint32_t js;
                     if (artic) { jr = sm_jpool(e) + jo; js = chunks << 2; }
+                    else if (k - ib < e.lay->rjac_heads) { jr = e.sm + e.lay->rjac + (k - ib) * 24u; js = 8u; }
                     else {
                         const uint32_t ss = head_owner(e, hs, 0u) == b ? 0u : 1u, as = head_axes(e, hs);
                         __syncwarp();
@@ -719,7 +756,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             if (!(total_dec > 0.f)) break;
         }
         tick(e, 20);
-        row_steps(e, tile, b, dvec);
+        row_steps<kRigid>(e, tile, b, dvec);
         tick(e, 21);
         const float alpha = search_line(e, tile, b, islope, icurv);
         tick(e, 22);
@@ -771,13 +808,13 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
 }
 
 // Blocks descend colour by colour, blocks of one colour in index order (block_descent_tile.cuh:2749-2820).
-template <int NR>
+template <int NR, bool kRigid>
 NKB_DEV void descend_blocks(Env& e, Tile& tile, bool position) {
     const uint32_t nb = tile.nblocks;
     const uint32_t* order = block_order(e, nb);
     const uint32_t count = order[nb];
 #pragma unroll 1
-    for (uint32_t k = 0u; k < count; ++k) descend_block<NR>(e, tile, order[k], position);
+    for (uint32_t k = 0u; k < count; ++k) descend_block<NR, kRigid>(e, tile, kRigid ? order[k] : e.t->B, position);
 }
 
 struct DualMomentum { float t, beta; };
@@ -850,7 +887,7 @@ NKB_DEV void update_duals(Env& e, const Tile& tile, DualMomentum* mom, bool velo
 }
 
 // Momentum balance of every moving block against the physical multipliers (block_descent_tile.cuh:2379-2489).
-template <int NR>
+template <int NR, bool kRigid>
 NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
     const uint32_t nb = tile.nblocks, l = e.lane;
     const uint32_t* inc = blk_inc(e, nb);
@@ -858,9 +895,9 @@ NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
     const uint32_t count = order[nb];
 #pragma unroll 1
     for (uint32_t turn = 0u; turn < count; ++turn) {
-        const uint32_t b = order[turn];
+        const uint32_t b = kRigid ? order[turn] : e.t->B;
         const uint32_t dim = blk_dim(e, b);
-        const bool artic = b == e.t->B;
+        const bool artic = !kRigid || b == e.t->B;
         float* vel = block_vel(e, b, false);
         const float* fr = block_free(e, b);
         const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
@@ -870,7 +907,7 @@ NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
         for (int r = 0; r < NR; ++r) { balance[r] = 0.0; coord[r] = l + 32u * r < dim; }
         if (artic) {
             const uint32_t n4 = (dim + 3u) & ~3u;
-            const uint32_t* utab = unit_table(e, nb);
+            const uint16_t* utab = unit_table(e, nb);
             const uint32_t vs = e.vstride;
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
@@ -882,7 +919,7 @@ NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
 #pragma unroll 1
                 for (uint32_t slot = 0u; slot < 4u; ++slot) {
                     const uint32_t h = utab[slot * vs + c];
-                    if (h != 0xffffffffu) balance[r] += (double)hf(e, HF_UNITV, h) * hf(e, HF_LAM, h);
+                    if (h != kNoUnitHead) balance[r] += (double)hf(e, HF_UNITV, h) * hf(e, HF_LAM, h);
                 }
             }
 #pragma unroll 1
@@ -940,7 +977,7 @@ NKB_DEV void measure_primals(Env& e, Tile& tile, bool reconstruct) {
 
 // The whole constraint solve of one env.  On entry the heads are built, the articulation's post-dynamics
 // velocity is in (e.qd, sm_vel(root)) and free-body velocities are in sm_bvel.
-template <int NR>
+template <int NR, bool kRigid>
 NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
     const TemplateView& t = *e.t;
     const uint32_t l = e.lane, B = t.B, n = t.ndof;
@@ -1088,7 +1125,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
         }
         if (phase == kPhaseVelocity) { tile.iteration = sweeps++; tile.momentum = 0.f; tile.residual = 0.f; }
         else tile.iteration = sweeps + pushes;
-        descend_blocks<NR>(e, tile, phase == kPhasePosition);
+        descend_blocks<NR, kRigid>(e, tile, phase == kPhasePosition);
         if (phase == kPhasePosition) {
             if (++pushes >= positions) { phase = kPhaseDone; continue; }
         } else tick(e, 10);
@@ -1102,7 +1139,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
             if (stage == 0) run = sweeps == iterations || fmaxf(worst_row, tile.residual) < tile.tol;
             else if (stage == 1) run = worst_row < tile.tol && tile.residual >= tile.tol && tile.residual < FLT_MAX;
             if (stage == 1 && !run) break;
-            if (run) { measure_primals<NR>(e, tile, stage == 1); tick(e, 25); if (e.cyc != nullptr && l == 0u) e.cyc[27] += 1u; }
+            if (run) { measure_primals<NR, kRigid>(e, tile, stage == 1); tick(e, 25); if (e.cyc != nullptr && l == 0u) e.cyc[27] += 1u; }
             if (stage == 1) {
                 if (!(tile.residual < FLT_MAX)) break;
                 init_residuals(e, tile);

@@ -40,6 +40,7 @@ struct TemplateView {
     uint32_t L, B, ndof, max_depth, n_excluded, floating_root;
     uint32_t head_cap;          // solver heads per env held in shared memory
     uint32_t point_cap;         // contact points per env that get rows
+    uint32_t slot_cap;          // candidate slots one step can fill: min(max_contacts, admissible pairs)
     const uint32_t *parent, *jtype, *depth, *child_begin, *children, *link_dof, *link_body, *geom_kind, *limit_flags;
     const uint32_t *dof_link, *anc_mask;
     const float *axis, *offset, *local_quat, *inertia10, *damping, *armature, *frictionloss, *stiffness, *spring_ref;
@@ -103,6 +104,7 @@ struct SmemLayout {
     uint32_t pairs, ccount, cpoint, cnormal, cdepth, cfeat;     // contacts
     uint32_t cstage;                                            // cache rebuild staging (shares the Jacobian pool, dead by then)
     uint32_t heads, jpool, binfo, chol, bm6;                    // solver (chol: Newton matrix; bm6: rigid block mass + head rows)
+    uint32_t rjac, rjac_heads;                                  // staged Jacobian rows of one rigid block's heads (24 words each)
     uint32_t words;                                             // total per env
     uint32_t ld;                                                // leading dimension of mass/factor (ndof | 1)
 };

@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -261,25 +262,30 @@ void World::BuildLayout() {
     // the dynamics stage's link scratch and the solver's Newton scratch are live at different times and share one region
     const uint32_t hn = std::max(n, 6u);
     const uint32_t overlay = at;
-    s.xrot = take(9 * L); s.xtr = take(3 * L); s.vbias = take(6 * L); s.acc = take(6 * L); s.pbias = take(6 * L); s.ic = take(10 * L);
+    s.xrot = take(9 * L); s.xtr = take(3 * L); s.vbias = 0; s.acc = take(6 * L); s.pbias = take(6 * L); s.ic = take(10 * L);
     const uint32_t dynamics_end = at;
     if (std::getenv("NUKA_B200_NO_OVERLAY") == nullptr) at = overlay;
     s.chol = take(hn * pad_ld(hn)); s.bm6 = take(72 + 24);
+    s.rjac_heads = t.n_free ? std::min(tv.head_cap, 32u) : 0u;
+    s.rjac = take(24 * s.rjac_heads);
     at = std::max(at, dynamics_end);
     s.mass = take(n * s.ld); s.factor = take(n * s.ld); s.vstride = n > 32u ? 64u : 32u;
-    s.vecs = take(8 * s.vstride);
+    s.vecs = take(6 * s.vstride);
     const uint32_t slots = B ? t.n_free + 1u : 0u;
     s.bpose = take(7 * B); s.bvel = take(6 * slots);
     s.bwinv = take(6 * slots); s.bmass = take(7 * slots); s.bfree = take(6 * slots); s.bpseudo = take(6 * slots);
-    s.pairs = take(S); s.ccount = take(S); s.cpoint = take(12 * S); s.cnormal = take(12 * S); s.cdepth = take(4 * S);
-    s.cfeat = take(8 * S);                        // contact identity words
+    tv.slot_cap = std::min<uint32_t>(S, (t.adm_pairs.size() == 1 && t.adm_pairs[0] == 0u) ? 0u : static_cast<uint32_t>(t.adm_pairs.size()));
+    const uint32_t SC = tv.slot_cap;
+    s.pairs = take(SC); s.ccount = take(SC); s.cpoint = take(12 * SC); s.cnormal = take(12 * SC); s.cdepth = take(4 * SC);
+    s.cfeat = take(8 * SC);                       // contact identity words
     s.heads = take(kHeadStride * tv.head_cap);
     // the Jacobian pool also holds the AABBs (dead once the narrowphase is done) and, after the solve, the cache staging
     // entries + owner marks
-    s.jpool = take(std::max(std::max(tv.point_cap * 3u * ((n + 3u) & ~3u), 4u * S * 10u + 4u * S), 6u * B));
+    const uint32_t stage_cap = std::min(tv.point_cap, 4u * SC);
+    s.jpool = take(std::max(std::max(tv.point_cap * 3u * ((n + 3u) & ~3u), stage_cap * 10u + 4u * SC), 6u * B));
     s.cstage = s.jpool; s.aabb = s.jpool;
     const uint32_t nb = B + (n ? 1u : 0u);
-    s.binfo = take(3 * nb + 1 + 2 * tv.head_cap + 4 * s.vstride + nb + 1);
+    s.binfo = take(3 * nb + 1 + 2 * tv.head_cap + 2 * s.vstride + nb + 1);      // the unit-row table holds 16-bit head indices
     if (const char* pad = std::getenv("NUKA_B200_SMEM_PAD_WORDS")) at += (static_cast<uint32_t>(std::atoi(pad)) + 3u) & ~3u;   // occupancy experiments
     s.words = at;
     const size_t bytes = static_cast<size_t>(s.words) * 4u;
@@ -291,11 +297,22 @@ void World::BuildLayout() {
     size_t best = 0;
     for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) {
         if (w * bytes > 227u * 1024u) break;
-        resident[w] = static_cast<size_t>(step_kernel_resident_blocks(n, w, w * bytes)) * w;      // asks the runtime
+        resident[w] = static_cast<size_t>(step_kernel_resident_blocks(n, t.n_free, w, w * bytes)) * w;      // asks the runtime
         best = std::max(best, resident[w]);
     }
     warps_per_block_ = 1;
     for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) if (resident[w] * 10u >= best * 9u) warps_per_block_ = w;
+    if (const char* forced = std::getenv("NUKA_B200_WARPS_PER_BLOCK")) {          // block-shape experiments
+        const uint32_t w = static_cast<uint32_t>(std::atoi(forced));
+        if (w >= 1u && w <= kWarpsPerBlockMax && resident[w] != 0u) warps_per_block_ = w;
+    }
+    if (std::getenv("NUKA_B200_DEBUG_LAYOUT") != nullptr) {
+        std::fprintf(stderr, "[nuka_b200] %zu B of shared memory per env, %d registers per thread; resident warps per SM by block size:", bytes, step_kernel_registers(n, t.n_free));
+        for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) std::fprintf(stderr, " %u:%zu", w, resident[w]);
+        std::fprintf(stderr, " -> %u warps per block\n", warps_per_block_);
+        std::fprintf(stderr, "[nuka_b200] word offsets: overlay %u mass %u vecs %u bodies %u contacts %u heads %u pool %u blocks %u end %u\n",
+                     s.xrot, s.mass, s.vecs, s.bpose, s.pairs, s.heads, s.jpool, s.binfo, s.words);
+    }
 }
 
 World::World(int device, cudaStream_t stream, const HostTemplate& tpl, uint32_t env_count)
