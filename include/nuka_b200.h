@@ -23,6 +23,7 @@ extern "C" {
 /* nuka.h:11-12 opaque handles (integer ids in pointer clothing, as in src/c_abi/handle_table.hpp:13-60) */
 typedef struct nuka_device_t* nuka_device_handle;
 typedef struct nuka_world_t* nuka_world_handle;
+typedef struct nuka_checkpoint_t* nuka_checkpoint_handle;     /* nuka.h:14 */
 
 /* nuka.h:20 */
 #define NUKA_MAX_CONTACT_SLOTS_PER_ENV 4u
@@ -109,6 +110,24 @@ nuka_result_t nuka_world_synchronize(nuka_world_handle world);
 /* nuka.h:380-385: reset keeps drive targets; an invalid id is INVALID_ARG with no env changed. */
 nuka_result_t nuka_world_reset(nuka_world_handle world);
 nuka_result_t nuka_world_reset_envs(nuka_world_handle world, const uint32_t* env_ids, uint32_t count);
+/* nuka.h:387-404, src/c_abi/checkpoint.cpp:442-635.  A checkpoint holds the world's persistent state on the host
+ * (coordinates, velocities, poses, carried constraint velocities, the contact cache, status words, drive targets and
+ * gains) plus gravity, the velocity-iteration count and the number of steps taken.  capture synchronises the
+ * world's stream.  restore accepts only a checkpoint of the same world (else INVALID_ARG), keeps every buffer-view
+ * address, and refreshes link and body poses; contact read-out fields keep their last values until the next step.
+ * A restored world repeats the steps that followed the capture bit for bit.
+ * write/read use this library's own file layout (magic, layout hash, step count, byte count, bytes, host settings);
+ * read validates the hash and byte count against the reading world (mismatch or a short file: INVALID_ARG) and
+ * returns a checkpoint owned by that world.  equal compares layout, step count and bytes.  state_hash is FNV-1a 64
+ * over the same bytes and settings in fixed order. */
+nuka_result_t nuka_world_checkpoint_capture(nuka_world_handle world, nuka_checkpoint_handle* out);
+nuka_result_t nuka_world_checkpoint_restore(nuka_world_handle world, nuka_checkpoint_handle checkpoint);
+void nuka_checkpoint_destroy(nuka_checkpoint_handle checkpoint);
+nuka_result_t nuka_checkpoint_write(nuka_checkpoint_handle checkpoint, const char* path);
+nuka_result_t nuka_world_checkpoint_read(nuka_world_handle world, const char* path, nuka_checkpoint_handle* out);
+nuka_result_t nuka_checkpoint_byte_size(nuka_checkpoint_handle checkpoint, uint64_t* out_bytes);
+nuka_result_t nuka_checkpoint_equal(nuka_checkpoint_handle a, nuka_checkpoint_handle b, uint32_t* out_equal);
+nuka_result_t nuka_world_state_hash(nuka_world_handle world, uint64_t* out_hash);
 /* nuka.h:434 */
 nuka_result_t nuka_world_forward_kinematics(nuka_world_handle world);
 /* nuka.h:479-481 */

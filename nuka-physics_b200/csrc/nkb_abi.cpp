@@ -1,6 +1,7 @@
 // extern "C" boundary: handle tables, result codes, thread-local error text.  No exception crosses it
 // (reference src/c_abi/error.cpp:12-60, src/c_abi/handle_table.hpp:13-60, src/c_abi/world.cpp:493-731,
 // src/c_abi/buffer.cpp:31-205).
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <fstream>
@@ -52,10 +53,32 @@ private:
 struct WorldRecord {
     std::unique_ptr<nkb::World> world;
     uintptr_t device = 0;
+    uint64_t serial = 0;        // distinguishes worlds that reuse a handle slot
 };
+
+// Host copy of a world's persistent state and settings (reference src/c_abi/checkpoint.cpp:442-520).
+struct CheckpointRecord {
+    uintptr_t owner = 0;
+    uint64_t owner_serial = 0;
+    uint64_t layout_hash = 0;
+    uint64_t step_count = 0;
+    uint32_t velocity_iterations = 0;
+    float gravity[3] = {0.f, 0.f, 0.f};
+    std::vector<uint8_t> persistent;
+};
+
+constexpr uint64_t kCheckpointMagic = 0x3143424b554eull;      // "NUKBC1"
+
+uint64_t Fnv1a(uint64_t h, const void* data, size_t bytes) {
+    const uint8_t* p = static_cast<const uint8_t*>(data);
+    for (size_t k = 0; k < bytes; ++k) { h ^= p[k]; h *= 1099511628211ull; }
+    return h;
+}
 
 HandleTable<DeviceRecord>& Devices() { static HandleTable<DeviceRecord> t; return t; }
 HandleTable<WorldRecord>& Worlds() { static HandleTable<WorldRecord> t; return t; }
+HandleTable<CheckpointRecord>& Checkpoints() { static HandleTable<CheckpointRecord> t; return t; }
+std::atomic<uint64_t> g_world_serial{0};
 
 template <typename Fn>
 nuka_result_t Guard(Fn&& fn) {
@@ -122,6 +145,7 @@ nuka_result_t CreateWorld(nuka_device_handle device, const nuka_world_desc_t* de
         auto record = std::make_unique<WorldRecord>();
         record->world = std::make_unique<nkb::World>(dev->gpu, dev->stream, tpl, desc->env_count);
         record->device = reinterpret_cast<uintptr_t>(device);
+        record->serial = ++g_world_serial;
         ++dev->worlds;
         *out = reinterpret_cast<nuka_world_handle>(Worlds().Insert(std::move(record)));
         return NUKA_RESULT_OK;
@@ -276,6 +300,140 @@ nuka_result_t nuka_b200_world_reset_envs_static(nuka_world_handle world, const u
     if (count == 0u) return NUKA_RESULT_OK;
     if (env_ids == nullptr) { SetError("env_ids is null"); return NUKA_RESULT_INVALID_ARG; }
     return Guard([&]() { w->ResetStaticIds(env_ids, count); return NUKA_RESULT_OK; });
+}
+
+// ---- checkpoints (reference nuka.h:387-404, src/c_abi/checkpoint.cpp:442-635) ----
+
+namespace {
+void CaptureInto(nkb::World* w, CheckpointRecord* c) {
+    c->layout_hash = w->PersistentLayoutHash();
+    c->step_count = w->step_count();
+    c->velocity_iterations = w->VelocityIterations();
+    for (int k = 0; k < 3; ++k) c->gravity[k] = w->gravity()[k];
+    c->persistent.resize(w->PersistentBytes());
+    w->DownloadPersistent(c->persistent.data());
+}
+}  // namespace
+
+nuka_result_t nuka_world_checkpoint_capture(nuka_world_handle world, nuka_checkpoint_handle* out) {
+    if (out == nullptr) { SetError("out handle is null"); return NUKA_RESULT_INVALID_ARG; }
+    *out = nullptr;
+    WorldRecord* rec = Worlds().Get(reinterpret_cast<uintptr_t>(world));
+    if (rec == nullptr || !rec->world) { SetError("world handle is null or stale"); return NUKA_RESULT_NULL_HANDLE; }
+    return Guard([&]() {
+        auto c = std::make_unique<CheckpointRecord>();
+        c->owner = reinterpret_cast<uintptr_t>(world);
+        c->owner_serial = rec->serial;
+        CaptureInto(rec->world.get(), c.get());
+        *out = reinterpret_cast<nuka_checkpoint_handle>(Checkpoints().Insert(std::move(c)));
+        return NUKA_RESULT_OK;
+    });
+}
+
+nuka_result_t nuka_world_checkpoint_restore(nuka_world_handle world, nuka_checkpoint_handle checkpoint) {
+    WorldRecord* rec = Worlds().Get(reinterpret_cast<uintptr_t>(world));
+    CheckpointRecord* c = Checkpoints().Get(reinterpret_cast<uintptr_t>(checkpoint));
+    if (rec == nullptr || !rec->world || c == nullptr) { SetError("world or checkpoint handle is null or stale"); return NUKA_RESULT_NULL_HANDLE; }
+    if (c->owner != reinterpret_cast<uintptr_t>(world) || c->owner_serial != rec->serial) {
+        SetError("checkpoint belongs to another world");
+        return NUKA_RESULT_INVALID_ARG;
+    }
+    nkb::World* w = rec->world.get();
+    if (c->layout_hash != w->PersistentLayoutHash() || c->persistent.size() != w->PersistentBytes()) {
+        SetError("checkpoint layout does not match the world");
+        return NUKA_RESULT_INVALID_ARG;
+    }
+    return Guard([&]() {
+        w->SetGravity(c->gravity);
+        w->SetVelocityIterations(c->velocity_iterations);
+        w->UploadPersistent(c->persistent.data());
+        w->set_step_count(c->step_count);
+        return NUKA_RESULT_OK;
+    });
+}
+
+void nuka_checkpoint_destroy(nuka_checkpoint_handle checkpoint) {
+    Checkpoints().Remove(reinterpret_cast<uintptr_t>(checkpoint));
+}
+
+nuka_result_t nuka_checkpoint_write(nuka_checkpoint_handle checkpoint, const char* path) {
+    CheckpointRecord* c = Checkpoints().Get(reinterpret_cast<uintptr_t>(checkpoint));
+    if (c == nullptr) { SetError("checkpoint handle is null or stale"); return NUKA_RESULT_NULL_HANDLE; }
+    if (path == nullptr) { SetError("path is null"); return NUKA_RESULT_INVALID_ARG; }
+    return Guard([&]() {
+        std::ofstream file(path, std::ios::binary | std::ios::trunc);
+        const uint64_t header[4] = {kCheckpointMagic, c->layout_hash, c->step_count, c->persistent.size()};
+        file.write(reinterpret_cast<const char*>(header), sizeof(header));
+        file.write(reinterpret_cast<const char*>(c->persistent.data()), static_cast<std::streamsize>(c->persistent.size()));
+        file.write(reinterpret_cast<const char*>(&c->velocity_iterations), sizeof(uint32_t));
+        file.write(reinterpret_cast<const char*>(c->gravity), sizeof(c->gravity));
+        file.flush();
+        if (!file.good()) { SetError(std::string("cannot write ") + path); return NUKA_RESULT_INTERNAL; }
+        return NUKA_RESULT_OK;
+    });
+}
+
+nuka_result_t nuka_world_checkpoint_read(nuka_world_handle world, const char* path, nuka_checkpoint_handle* out) {
+    if (out == nullptr || path == nullptr) { SetError("out handle or path is null"); return NUKA_RESULT_INVALID_ARG; }
+    *out = nullptr;
+    WorldRecord* rec = Worlds().Get(reinterpret_cast<uintptr_t>(world));
+    if (rec == nullptr || !rec->world) { SetError("world handle is null or stale"); return NUKA_RESULT_NULL_HANDLE; }
+    return Guard([&]() {
+        nkb::World* w = rec->world.get();
+        std::ifstream file(path, std::ios::binary);
+        uint64_t header[4] = {};
+        file.read(reinterpret_cast<char*>(header), sizeof(header));
+        if (!file.good() || header[0] != kCheckpointMagic || header[1] != w->PersistentLayoutHash() || header[3] != w->PersistentBytes()) {
+            SetError(std::string("not a checkpoint of this world's layout: ") + path);
+            return NUKA_RESULT_INVALID_ARG;
+        }
+        auto c = std::make_unique<CheckpointRecord>();
+        c->owner = reinterpret_cast<uintptr_t>(world);
+        c->owner_serial = rec->serial;
+        c->layout_hash = header[1];
+        c->step_count = header[2];
+        c->persistent.resize(header[3]);
+        file.read(reinterpret_cast<char*>(c->persistent.data()), static_cast<std::streamsize>(header[3]));
+        file.read(reinterpret_cast<char*>(&c->velocity_iterations), sizeof(uint32_t));
+        file.read(reinterpret_cast<char*>(c->gravity), sizeof(c->gravity));
+        if (!file.good()) { SetError(std::string("checkpoint file is short: ") + path); return NUKA_RESULT_INVALID_ARG; }
+        *out = reinterpret_cast<nuka_checkpoint_handle>(Checkpoints().Insert(std::move(c)));
+        return NUKA_RESULT_OK;
+    });
+}
+
+nuka_result_t nuka_checkpoint_byte_size(nuka_checkpoint_handle checkpoint, uint64_t* out_bytes) {
+    CheckpointRecord* c = Checkpoints().Get(reinterpret_cast<uintptr_t>(checkpoint));
+    if (c == nullptr) { SetError("checkpoint handle is null or stale"); return NUKA_RESULT_NULL_HANDLE; }
+    if (out_bytes == nullptr) { SetError("out_bytes is null"); return NUKA_RESULT_INVALID_ARG; }
+    *out_bytes = c->persistent.size();
+    return NUKA_RESULT_OK;
+}
+
+nuka_result_t nuka_checkpoint_equal(nuka_checkpoint_handle a, nuka_checkpoint_handle b, uint32_t* out_equal) {
+    CheckpointRecord* x = Checkpoints().Get(reinterpret_cast<uintptr_t>(a));
+    CheckpointRecord* y = Checkpoints().Get(reinterpret_cast<uintptr_t>(b));
+    if (x == nullptr || y == nullptr) { SetError("checkpoint handle is null or stale"); return NUKA_RESULT_NULL_HANDLE; }
+    if (out_equal == nullptr) { SetError("out_equal is null"); return NUKA_RESULT_INVALID_ARG; }
+    *out_equal = (x->layout_hash == y->layout_hash && x->step_count == y->step_count && x->persistent == y->persistent) ? 1u : 0u;
+    return NUKA_RESULT_OK;
+}
+
+nuka_result_t nuka_world_state_hash(nuka_world_handle world, uint64_t* out_hash) {
+    if (out_hash == nullptr) { SetError("out_hash is null"); return NUKA_RESULT_INVALID_ARG; }
+    WorldRecord* rec = Worlds().Get(reinterpret_cast<uintptr_t>(world));
+    if (rec == nullptr || !rec->world) { SetError("world handle is null or stale"); return NUKA_RESULT_NULL_HANDLE; }
+    return Guard([&]() {
+        CheckpointRecord c;
+        CaptureInto(rec->world.get(), &c);
+        uint64_t h = 1469598103934665603ull;
+        h = Fnv1a(h, c.persistent.data(), c.persistent.size());
+        h = Fnv1a(h, &c.step_count, sizeof(c.step_count));
+        h = Fnv1a(h, &c.velocity_iterations, sizeof(c.velocity_iterations));
+        h = Fnv1a(h, c.gravity, sizeof(c.gravity));
+        *out_hash = h;
+        return NUKA_RESULT_OK;
+    });
 }
 
 nuka_result_t nuka_world_forward_kinematics(nuka_world_handle world) {

@@ -97,6 +97,14 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
             t.body_geom_quat = BlobVec<float>(blob, bytes, "body_geom_quat", 4 * B);
         }
     }
+    {   // optional capacity: contact points per env that get solver rows
+        BlobEntry mp;
+        t.max_points = 0u;
+        if (BlobFind(blob, bytes, "max_points", &mp)) {
+            t.max_points = BlobVec<uint32_t>(blob, bytes, "max_points", 1)[0];
+            if (t.max_points > 1024u) throw Error(kInvalidArg, "max_points above 1024");
+        }
+    }
     t.q0 = BlobVec<float>(blob, bytes, "q0", L);
     t.base_pose0 = BlobVec<float>(blob, bytes, "base_pose0", 7);
     t.kp0 = BlobVec<float>(blob, bytes, "kp0", L);
@@ -249,7 +257,8 @@ void World::BuildLayout() {
         std::sort(caps.begin(), caps.end(), [](uint32_t a, uint32_t b) { return a > b; });
         uint32_t total = 0;
         for (size_t k = 0; k < caps.size() && k < S; ++k) total += caps[k];
-        tv.point_cap = std::min(total, 128u);     // bounds the head records and Jacobian pool in shared memory
+        // bounds the head records and Jacobian pool in shared memory; the template may ask for more than the default
+        tv.point_cap = std::min(total, t.max_points != 0u ? t.max_points : 128u);
     }
     tv.head_cap = (tv.point_cap + t.joint_rows + 3u) & ~3u;
     if (tv.head_cap == 0u) tv.head_cap = 4u;
@@ -391,7 +400,7 @@ void World::Seed() {
     reset_.env_count = env_count_;
     reset_.env_ids = nullptr;
     uint32_t f = 0;
-    auto add = [&](void* dst, const void* src, uint32_t words) { if (words) reset_.fields[f++] = {dst, src, words, 0u, 0u}; };
+    auto add = [&](void* dst, const void* src, uint32_t words) { if (words) { reset_.fields[f++] = {dst, src, words, 0u, 0u}; persistent_.push_back({dst, words}); } };
     add(s.q, q0, L); add(s.qdot, nullptr, L); add(s.qddot, nullptr, L); add(s.tau, nullptr, L); add(s.actuator, nullptr, L);
     add(s.base_pose, base0, L ? 7u : 0u); add(s.link_vel, nullptr, 6 * L);
     add(s.body_pose, body0, 7 * B); add(s.body_linvel, nullptr, 3 * B); add(s.body_angvel, nullptr, 3 * B);
@@ -401,12 +410,49 @@ void World::Seed() {
     reset_.field_count = f;
     // drive inputs are seeded once; resets keep them (reference nuka.h:378-379)
     ResetParams seed = reset_;
-    auto add_seed = [&](void* dst, const void* src, uint32_t words) { if (words) seed.fields[seed.field_count++] = {dst, src, words, 0u, 0u}; };
+    auto add_seed = [&](void* dst, const void* src, uint32_t words) { if (words) { seed.fields[seed.field_count++] = {dst, src, words, 0u, 0u}; persistent_.push_back({dst, words}); } };
     add_seed(s.drive_target, q0, L); add_seed(s.kp, kp0, L); add_seed(s.kd, kd0, L); add_seed(s.force_limit, fl0, L);
     add_seed(s.vel_target, nullptr, L); add_seed(s.feedforward, nullptr, L);
     Check(launch_reset(seed, env_count_, stream_), "seed launch");
     ++launches_;
     Refresh();
+}
+
+size_t World::PersistentBytes() const {
+    size_t words = 0;
+    for (const PersistentField& f : persistent_) words += static_cast<size_t>(f.words) * env_count_;
+    return words * 4u;
+}
+
+uint64_t World::PersistentLayoutHash() const {
+    uint64_t h = 1469598103934665603ull;      // FNV-1a over the counts that fix the byte layout
+    auto mix = [&](uint64_t v) { for (int k = 0; k < 8; ++k) { h ^= (v >> (8 * k)) & 0xffu; h *= 1099511628211ull; } };
+    mix(env_count_); mix(tpl_.L); mix(tpl_.B); mix(tpl_.ndof); mix(tpl_.cfg.max_contacts);
+    for (const PersistentField& f : persistent_) mix(f.words);
+    return h;
+}
+
+void World::DownloadPersistent(uint8_t* out) {
+    Check(cudaSetDevice(device_), "cudaSetDevice");
+    size_t at = 0;
+    for (const PersistentField& f : persistent_) {
+        const size_t bytes = static_cast<size_t>(f.words) * env_count_ * 4u;
+        Check(cudaMemcpyAsync(out + at, f.ptr, bytes, cudaMemcpyDeviceToHost, stream_), "checkpoint download");
+        at += bytes;
+    }
+    Check(cudaStreamSynchronize(stream_), "checkpoint synchronize");
+}
+
+void World::UploadPersistent(const uint8_t* in) {
+    Check(cudaSetDevice(device_), "cudaSetDevice");
+    size_t at = 0;
+    for (const PersistentField& f : persistent_) {
+        const size_t bytes = static_cast<size_t>(f.words) * env_count_ * 4u;
+        Check(cudaMemcpyAsync(f.ptr, in + at, bytes, cudaMemcpyHostToDevice, stream_), "checkpoint upload");
+        at += bytes;
+    }
+    Refresh();
+    Check(cudaStreamSynchronize(stream_), "checkpoint synchronize");     // the caller's bytes may go away after the call
 }
 
 void World::Refresh() {
@@ -435,6 +481,7 @@ void World::SetGraphMode(bool on) {
 
 void World::Step(uint32_t n) {
     if (n == 0u) return;
+    step_count_ += n;
     Check(cudaSetDevice(device_), "cudaSetDevice");
     StepParams p = params_;
     p.mode = kModeStep;

@@ -30,6 +30,7 @@ struct HostTemplate {
     std::vector<float> shape_params, mu, inv_mass, inv_inertia, inertial_pos, inertial_quat, body_pose0;
     std::vector<unsigned long long> excluded;
     std::vector<uint32_t> adm_pairs;
+    uint32_t max_points = 0;            // template's contact-point capacity, 0 = default
     std::vector<uint32_t> body_geom_kind;          // per collidable row (several rows may mirror one link)
     std::vector<float> body_geom_pos, body_geom_quat;
     std::vector<uint32_t> free_slot;
@@ -65,6 +66,17 @@ public:
     uint32_t VelocityIterations() const { return params_.t.cfg.vel_iters; }
     void SetGravityZ(float g) { params_.t.cfg.gravity[2] = g; graph_valid_ = false; }
     void SetGraphMode(bool on);
+    // Persistent state: every per-env array a step carries over (coordinates, velocities, poses, carried constraint
+    // velocities, the contact cache, status words, drive inputs), in a fixed order.  A checkpoint is these bytes
+    // plus the host settings below (reference src/c_abi/checkpoint.cpp:442-520 captures the same split).
+    size_t PersistentBytes() const;
+    uint64_t PersistentLayoutHash() const;
+    void DownloadPersistent(uint8_t* out);          // synchronises the stream
+    void UploadPersistent(const uint8_t* in);       // then refreshes the derived poses
+    uint64_t step_count() const { return step_count_; }
+    void set_step_count(uint64_t n) { step_count_ = n; }
+    const float* gravity() const { return params_.t.cfg.gravity; }
+    void SetGravity(const float g[3]) { for (int k = 0; k < 3; ++k) params_.t.cfg.gravity[k] = g[k]; graph_valid_ = false; }
     cudaStream_t stream() const { return stream_; }
     int device() const { return device_; }
     uint32_t env_count() const { return env_count_; }
@@ -96,6 +108,9 @@ private:
     cudaGraph_t graph_ = nullptr;
     cudaGraphExec_t graph_exec_ = nullptr;
     uint64_t launches_ = 0;
+    uint64_t step_count_ = 0;
+    struct PersistentField { void* ptr; uint32_t words; };
+    std::vector<PersistentField> persistent_;
 };
 
 }  // namespace nkb

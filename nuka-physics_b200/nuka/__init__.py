@@ -7,6 +7,7 @@ world-owned device memory without a copy (``__cuda_array_interface__`` and ``__d
 Every call goes through the C ABI of ``libnuka_b200.so``; nothing here computes physics.
 """
 import ctypes
+import os
 import enum
 
 import numpy as np
@@ -101,6 +102,36 @@ class FieldView:
         return (2, self._world.device.gpu_index)   # kDLCUDA
 
 
+class Checkpoint:
+    """A captured world state (reference nuka.h:387-404)."""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    def write(self, path):
+        _check(_abi.lib().nuka_checkpoint_write(self._h, os.fsencode(path)))
+
+    @property
+    def byte_size(self):
+        out = ctypes.c_uint64()
+        _check(_abi.lib().nuka_checkpoint_byte_size(self._h, ctypes.byref(out)))
+        return out.value
+
+    def __eq__(self, other):
+        if not isinstance(other, Checkpoint):
+            return NotImplemented
+        out = ctypes.c_uint32()
+        _check(_abi.lib().nuka_checkpoint_equal(self._h, other._h, ctypes.byref(out)))
+        return bool(out.value)
+
+    __hash__ = None
+
+    def destroy(self):
+        if self._h:
+            _abi.lib().nuka_checkpoint_destroy(self._h)
+            self._h = None
+
+
 class World:
     def __init__(self, device, handle, env_count):
         self.device = device
@@ -168,6 +199,25 @@ class World:
         """reset_envs without any allocation (at most 4096 ids per call; calls on one device must not overlap)."""
         ids = np.ascontiguousarray(env_ids, dtype=np.uint32)
         _check(_abi.lib().nuka_b200_world_reset_envs_static(self._h, ids.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), ids.size))
+
+    def checkpoint_capture(self):
+        """Host copy of the persistent state and settings (reference nuka.h:389); synchronises the stream."""
+        h = ctypes.c_void_p()
+        _check(_abi.lib().nuka_world_checkpoint_capture(self._h, ctypes.byref(h)))
+        return Checkpoint(h)
+
+    def checkpoint_restore(self, checkpoint):
+        _check(_abi.lib().nuka_world_checkpoint_restore(self._h, checkpoint._h))
+
+    def checkpoint_read(self, path):
+        h = ctypes.c_void_p()
+        _check(_abi.lib().nuka_world_checkpoint_read(self._h, os.fsencode(path), ctypes.byref(h)))
+        return Checkpoint(h)
+
+    def state_hash(self):
+        out = ctypes.c_uint64()
+        _check(_abi.lib().nuka_world_state_hash(self._h, ctypes.byref(out)))
+        return out.value
 
     def forward_kinematics(self):
         _check(_abi.lib().nuka_world_forward_kinematics(self._h))

@@ -48,7 +48,8 @@ EXPORTS = [
     "nuka_world_reset", "nuka_world_reset_envs", "nuka_world_forward_kinematics", "nuka_world_get_stream", "nuka_world_record_event",
     "nuka_world_get_buffer_view", "nuka_world_upload_field", "nuka_world_download_field", "nuka_world_create_from_template",
     "nuka_b200_world_info", "nuka_b200_world_run_stage", "nuka_b200_world_launch_count", "nuka_b200_world_reset_envs_static",
-    "nuka_b200_world_pack_observations",
+    "nuka_b200_world_pack_observations", "nuka_world_checkpoint_capture", "nuka_world_checkpoint_restore", "nuka_checkpoint_destroy",
+    "nuka_checkpoint_write", "nuka_world_checkpoint_read", "nuka_checkpoint_byte_size", "nuka_checkpoint_equal", "nuka_world_state_hash",
 ]
 
 _LIB = None
@@ -94,5 +95,14 @@ def lib():
     L.nuka_b200_world_info.argtypes = [vp, ctypes.POINTER(WorldInfo)]
     L.nuka_b200_world_run_stage.argtypes = [vp, u32]
     L.nuka_b200_world_launch_count.argtypes = [vp, ctypes.POINTER(ctypes.c_uint64)]
+    L.nuka_world_checkpoint_capture.argtypes = [vp, ctypes.POINTER(vp)]
+    L.nuka_world_checkpoint_restore.argtypes = [vp, vp]
+    L.nuka_checkpoint_destroy.argtypes = [vp]
+    L.nuka_checkpoint_destroy.restype = None
+    L.nuka_checkpoint_write.argtypes = [vp, ctypes.c_char_p]
+    L.nuka_world_checkpoint_read.argtypes = [vp, ctypes.c_char_p, ctypes.POINTER(vp)]
+    L.nuka_checkpoint_byte_size.argtypes = [vp, ctypes.POINTER(ctypes.c_uint64)]
+    L.nuka_checkpoint_equal.argtypes = [vp, vp, ctypes.POINTER(u32)]
+    L.nuka_world_state_hash.argtypes = [vp, ctypes.POINTER(ctypes.c_uint64)]
     _LIB = L
     return L

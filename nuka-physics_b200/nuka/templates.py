@@ -43,8 +43,10 @@ def box_inertia(mass, size):
 
 
 class TemplateBuilder:
-    def __init__(self, dt, vel_iters, pos_iters=32, gravity=(0.0, 0.0, -9.81), max_contacts=0, contact_margin=0.0):
+    def __init__(self, dt, vel_iters, pos_iters=32, gravity=(0.0, 0.0, -9.81), max_contacts=0, contact_margin=0.0,
+                 max_points=0):
         self.links, self.bodies, self.excluded = [], [], set()
+        self.max_points = max_points    # contact points per env that get solver rows; 0 = derived bound, at most 128
         self.extra_shapes = False
         self.cfg = dict(dt=dt, gravity=gravity, vel_iters=vel_iters, pos_iters=pos_iters, pos_beta=0.3, pos_slop=0.001,
                         contact_margin=contact_margin, baumgarte_max_velocity=FLT_BIG, overlap_recovery_velocity=0.0,
@@ -156,6 +158,8 @@ class TemplateBuilder:
                     if la == lb or self.links[la]["parent"] == lb or self.links[lb]["parent"] == la:
                         excluded.add((a << 32) | b)
         out["excluded"] = np.array(sorted(excluded), dtype=np.uint64)
+        if self.max_points:
+            out["max_points"] = np.array([self.max_points], dtype=u32)
         return out
 
     def blob(self):
@@ -301,7 +305,7 @@ def humanoid_state(env_count, seed=0):
 def box_pile(seed=0, dt=1.0 / 240.0, vel_iters=8, count=48):
     """Config 4: free boxes on a 4x4x3 jittered lattice above a plane (template holds the nominal lattice)."""
     rng = np.random.Generator(np.random.PCG64(seed))
-    tb = TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=4 * count)
+    tb = TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=4 * count, max_points=0 if count <= 12 else 6 * count)
     for k in range(count):
         he = rng.uniform(0.02, 0.1, size=3)
         rho = rng.uniform(500.0, 2000.0)

@@ -196,6 +196,27 @@ def test_free_boxes_land_like_the_oracle(device, oracle):
     w.destroy()
 
 
+def test_full_box_pile_of_configs_3(device, oracle):
+    """configs[3]'s env at full size: 48 free boxes over a plane, 192 candidate slots, a contact-point capacity of
+    288 carried by the template.  Pair lists and contact counts bit-exact and poses within 1e-4 through the first
+    landings (after which a tumbling pile amplifies rounding differences)."""
+    E, count = 16, 48
+    st = T.box_pile_state(E, 0, count=count)
+    w, o = make_pair(device, oracle, T.box_pile(0, count=count), E, {"body_pose": st["body_pose"]})
+    B, S = count + 1, w.info.contact_slots_per_env
+    assert S == 4 * count
+    for k in (1, 19):
+        w.step_n(k); o.step(k)
+        pc = w.download(F.PAIR_COUNT)
+        assert np.array_equal(pc, o.get("pair_count", 1))
+        live = np.arange(S)[None, :] < pc
+        assert np.array_equal(w.download(F.CANDIDATE_PAIRS).reshape(E, S, 2)[live], o.get("candidate_pairs", 2 * S).reshape(E, S, 2)[live])
+        assert np.array_equal(w.download(F.CONTACT_COUNT)[live], o.get("contact_count", S)[live])
+        assert rel(w.download(F.RIGID_BODY_TRANSFORM), o.get("body_pose", 7 * B)) < 1e-4
+    assert w.download(F.CONTACT_COUNT).sum() > 0 and w.download(F.ENV_STATUS).max() == 0
+    w.destroy()
+
+
 def test_quadruped_with_free_boxes(device, oracle):
     """configs[4]'s env: the quadruped plus four free boxes (articulated and rigid blocks in one solve)."""
     E = 64
