@@ -237,14 +237,16 @@ def quadruped_state(env_count, seed=0):
     return {"q": q, "base_pose": base}
 
 
-def humanoid(seed=0, dt=1.0 / 200.0, vel_iters=8, self_collision=False):
+def humanoid(seed=0, dt=1.0 / 200.0, vel_iters=8, self_collision=True):
     """Config 3: floating pelvis, two 6-DoF legs (3-1-2), 3-DoF waist, two 7-DoF arms (3-1-3); capsule colliders.
 
-    Every capsule hangs from its joint down to the next joint of its chain (short stubs where joints coincide), left
-    and right limbs share their dimensions, and by default the capsules collide with the ground only: the stubs of
-    coincident joints overlap by construction, so self-collision needs a template with hand-placed geometry."""
+    Every capsule hangs from its joint down to the next joint of its chain (short stubs where joints coincide) and
+    left and right limbs share their dimensions.  All capsules collide with the ground.  Self-contact is between
+    the long segments (thigh, shin, upper arm, forearm) of different limbs, selected by filter bits: the stubs of
+    coincident joints and the trunk overlap their neighbours by construction and stay out of it."""
     rng = np.random.Generator(np.random.PCG64(seed))
-    tb = TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=32)
+    # 30 capsule-plane candidates are always live (the plane's box is unbounded) + 24 limb-limb pairs
+    tb = TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=56 if self_collision else 32, max_points=48 if self_collision else 0)
     specs = []   # (name, parent_name, axis, offset, capsule?)
 
     def chain(prefix, parent, axes, offsets):
@@ -280,12 +282,19 @@ def humanoid(seed=0, dt=1.0 / 200.0, vel_iters=8, self_collision=False):
     masses = 35.0 * volumes / volumes.sum()
     index = {}
 
+    limbs = {"leg_l": 0, "leg_r": 1, "arm_l": 2, "arm_r": 3}
+
     def capsule_link(i, parent, jtype, axis, offset, kp):
         r, ln, m = float(radii[i]), float(lengths[i]), float(masses[i])
+        contype, conaffinity = 1, 0
+        name = specs[i - 1][0] if i > 0 else "pelvis"
+        if self_collision and ln > 0.1 and name[:5] in limbs:
+            bit = 4 << limbs[name[:5]]                    # a long segment answers to every other limb's bit
+            contype, conaffinity = 1 | bit, (4 | 8 | 16 | 32) & ~bit
         diag = (m * (3 * r * r + ln * ln) / 12.0, m * (3 * r * r + ln * ln) / 12.0, 0.5 * m * r * r)
         return tb.add_link(parent, jtype, axis=axis, offset=offset, mass=m, inertia_diag=diag, com=(0, 0, -0.5 * ln),
                            kp=kp, kd=0.05 * kp, shape=(CAPSULE, r, 0.5 * ln), shape_pos=(0, 0, -0.5 * ln), mu=0.8,
-                           contype=1, conaffinity=1 if self_collision else 0, armature=0.01)
+                           contype=contype, conaffinity=conaffinity, armature=0.01)
 
     index["pelvis"] = capsule_link(0, None, FLOATING, Z, (0, 0, 0), 0.0)
     for i, (name, parent, axis, offset) in enumerate(specs):

@@ -349,8 +349,11 @@ def test_torque_and_velocity_control_modes(device, oracle, mode):
 
 
 def test_humanoid_35_coordinates(device, oracle):
-    """configs[2]'s articulation: 30 links, 35 coordinates (two per warp lane), capsules on a plane: mass matrix,
-    accelerations, a single step and a short trajectory against the oracle."""
+    """configs[2]'s articulation: 30 links, 35 coordinates (two per warp lane), capsules on a plane and limb-limb
+    self-contact: mass matrix, accelerations, a single step and a short trajectory against the oracle.  Envs whose
+    solve stops at the sweep limit (crossed legs pressing into each other) carry an unconverged state forward, which
+    amplifies rounding differences, so the 2e-4 trajectory bound applies to the envs that converged in every step
+    and a 1e-2 bound to the rest."""
     E = 24
     tb = T.humanoid(0)
     st = T.humanoid_state(E, 1)
@@ -366,8 +369,22 @@ def test_humanoid_35_coordinates(device, oracle):
     w.step_n(1); o.step(1)
     assert rel(w.download(F.JOINT_VELOCITY), o.get("qdot", 30)) < 5e-5
     assert np.array_equal(w.download(F.PAIR_COUNT), o.get("pair_count", 1))
-    w.step_n(19); o.step(19)
-    assert rel(w.download(F.JOINT_POSITION), o.get("q", 30)) < 2e-4
-    assert rel(w.download(F.BASE_POSE), o.get("base_pose", 7)) < 2e-4
+    S = w.info.contact_slots_per_env
+    limit = w.get_velocity_iterations()
+    converged = np.ones(E, bool)
+    self_contacts = 0
+    for _ in range(19):
+        w.step_n(1); o.step(1)
+        sweeps = w.download(F.SOLVER_SWEEPS).reshape(E)
+        assert np.array_equal(sweeps, o.get("solver_sweeps", 1).reshape(E))
+        converged &= sweeps < limit
+        cc = w.download(F.CONTACT_COUNT)
+        assert np.array_equal(cc, o.get("contact_count", S))
+        self_contacts += int(((w.download(F.CANDIDATE_PAIRS).reshape(E, S, 2)[:, :, 1] != 30) & (cc > 0)).sum())
+    assert self_contacts > 0 and converged.sum() >= E // 2
+    gq, oq = w.download(F.JOINT_POSITION), o.get("q", 30).reshape(E, 30)
+    gb, ob = w.download(F.BASE_POSE), o.get("base_pose", 7).reshape(E, 7)
+    assert rel(gq[converged], oq[converged]) < 2e-4 and rel(gb[converged], ob[converged]) < 2e-4
+    assert rel(gq, oq) < 1e-2 and rel(gb, ob) < 1e-2
     assert w.download(F.ENV_STATUS).max() == 0 and o.get("env_status", 1).max() == 0
     w.destroy()
