@@ -372,30 +372,49 @@ NKB_DEV void stage_dynamics(Env& e, bool integrate_velocity) {
         float* out = e.s->dbg_mass + (size_t)e.env * n * n;
         for (uint32_t k = l; k < n * n; k += 32u) out[k] = M[(k / n) * ld + k % n];
     }
-    // L D L^T, unit lower triangle with D on the diagonal and pivot floor 1e-6 (articulation_mass.cuh:269-335)
+    // L D L^T, unit lower triangle with D on the diagonal and pivot floor 1e-6 (articulation_mass.cuh:269-335).
+    // Column by column, lane = row: entry (row, k) = (M[row][k] - sum_{j<k} L[row][j] L[k][j] d_j) / d_k, the terms
+    // subtracted in ascending j exactly as the reference's in-place elimination subtracts them, but with both rows
+    // and the pivots read ahead of one short dependent chain instead of a read-modify-write per term.
     float* F = sm_factor(e);
+    float* piv = sm_vec(e, kVecTmp);
     for (uint32_t k = l; k < n * ld; k += 32u) F[k] = M[k];
     __syncwarp();
+#pragma unroll 1
     for (uint32_t k = 0; k < n; ++k) {
-        const float dk = fmaxf(F[k * ld + k], 1.0e-6f);
-        __syncwarp();
-        if (l == (k & 31u)) F[k * ld + k] = dk;
-        float lik[NR];
+        const float* Fk = F + k * ld;
+        float v[NR];
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
             const uint32_t row = l + 32u * r;
-            lik[r] = 0.f;
-            if (row > k && row < n) { lik[r] = F[row * ld + k] / dk; F[row * ld + k] = lik[r]; }
+            v[r] = 0.f;
+            if (row >= k && row < n) {
+                const float* Fr = F + row * ld;
+                const float4* Fr4 = reinterpret_cast<const float4*>(Fr);
+                const float4* Fk4 = reinterpret_cast<const float4*>(Fk);
+                const float4* piv4 = reinterpret_cast<const float4*>(piv);
+                float acc = Fr[k];
+                const uint32_t full = k >> 2;
+#pragma unroll 1
+                for (uint32_t c = 0u; c < full; ++c) {
+                    const float4 a = Fr4[c], b4 = Fk4[c], p = piv4[c];
+                    acc -= a.x * b4.x * p.x; acc -= a.y * b4.y * p.y; acc -= a.z * b4.z * p.z; acc -= a.w * b4.w * p.w;
+                }
+                for (uint32_t j = full << 2; j < k; ++j) acc -= Fr[j] * Fk[j] * piv[j];
+                v[r] = acc;
+            }
         }
+        const float dk = fmaxf(coord_bcast<NR>(v, k), 1.0e-6f);
         __syncwarp();
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
             const uint32_t row = l + 32u * r;
-            if (row > k && row < n)
-                for (uint32_t j = k + 1u; j <= row; ++j) F[row * ld + j] -= lik[r] * F[j * ld + k] * dk;
+            if (row == k) { F[row * ld + k] = dk; piv[k] = dk; }
+            else if (row > k && row < n) F[row * ld + k] = v[r] / dk;
         }
         __syncwarp();
     }
+    // the strict upper triangle keeps M's entries; only the lower triangle and the diagonal are read below
     // solve L D L^T x = rhs, lane = coordinate (articulation_mass.cuh:357-396)
     float x[NR];
 #pragma unroll
