@@ -130,25 +130,80 @@ NKB_DEV void solve_block_mass(const Env& e, uint32_t block, const float (&g)[NR]
 }
 
 // J M^-1 J^T of an articulated row from one forward solve with the unit-lower factor (articulation_mass.cuh:413-441)
+// Row with a single entry `value` at coordinate `at`: the solve starts there, the leading zeros contribute nothing.
 template <int NR>
-NKB_DEV float mass_coupling(const Env& e, const float* row) {
+NKB_DEV float mass_coupling_unit(const Env& e, uint32_t at, float value) {
     const uint32_t n = e.t->ndof, ld = e.lay->ld;
     const float* F = sm_factor(e);
     float y[32 * NR];
     float r = 0.f;
-    for (uint32_t i = 0; i < n; ++i) {
-        float a = row[i];
-        for (uint32_t j = 0; j < i; ++j) a -= F[i * ld + j] * y[j];
+    for (uint32_t i = at; i < n; ++i) {
+        float a = i == at ? value : 0.f;
+        for (uint32_t j = at; j < i; ++j) a -= F[i * ld + j] * y[j];
         y[i] = a;
         r += a * a / F[i * ld + i];
     }
     return r;
 }
 
+// The same for dense rows (contact rows against the articulation), all lanes on one row at a time: lane = coordinate
+// in the forward solve, then lane = row adds its row's terms in coordinate order, so the sum is the sequential one.
+// Results land in HF_RSD of each head (a field init_heads fills afterwards).
+template <int NR>
+NKB_DEV void mass_coupling_dense(Env& e, const Tile& tile) {
+    const TemplateView& t = *e.t;
+    const uint32_t n = t.ndof, ld = e.lay->ld, l = e.lane;
+    if (n == 0u) return;
+    const float* F = sm_factor(e);
+    float* terms = e.sm + e.lay->chol;                  // Newton scratch, free until the first descent: >= n x n words
+    const uint32_t batch = n < 32u ? n : 32u;           // rows per batch
+    float diag[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) { const uint32_t c = l + 32u * r; diag[r] = c < n ? F[c * ld + c] : 1.f; }
+    for (uint32_t base = 0u; base < tile.nheads; base += 32u) {
+        const uint32_t h = base + l;
+        bool dense = false;
+        if (h < tile.nheads) {
+            const uint32_t o = hu(e, HF_OWNER, h);
+            dense = ((o & 0xffffu) == t.B || (o >> 16) == t.B) && !(hu(e, HF_JOFF, h) & kUnitRow);
+        }
+        uint32_t todo = __ballot_sync(NKB_FULL, dense);
+        while (todo != 0u) {
+            uint32_t in_batch = 0u, mine = 0xffffffffu;
+#pragma unroll 1
+            for (; todo != 0u && in_batch < batch; ++in_batch) {
+                const uint32_t src = (uint32_t)__ffs(todo) - 1u;
+                todo &= todo - 1u;
+                if (l == src) mine = in_batch;
+                const float* row = sm_jpool(e) + hu(e, HF_JOFF, base + src);
+                float x[NR];
+#pragma unroll
+                for (int r = 0; r < NR; ++r) { const uint32_t c = l + 32u * r; x[r] = c < n ? row[c] : 0.f; }
+#pragma unroll 1
+                for (uint32_t j = 0u; j < n; ++j) {
+                    const float xj = coord_bcast<NR>(x, j);
+#pragma unroll
+                    for (int r = 0; r < NR; ++r) { const uint32_t c = l + 32u * r; if (c > j && c < n) x[r] -= F[c * ld + j] * xj; }
+                }
+#pragma unroll
+                for (int r = 0; r < NR; ++r) { const uint32_t c = l + 32u * r; if (c < n) terms[in_batch * n + c] = x[r] * x[r] / diag[r]; }
+            }
+            __syncwarp();
+            if (mine != 0xffffffffu) {
+                float r = 0.f;
+                for (uint32_t i = 0u; i < n; ++i) r += terms[mine * n + i];
+                hf(e, HF_RSD, h) = r;
+            }
+            __syncwarp();
+        }
+    }
+}
+
 // Head setup: penalty, response scales (block_descent_tile.cuh:743-797).
 template <int NR>
 NKB_DEV void init_heads(Env& e, const Tile& tile) {
     const TemplateView& t = *e.t;
+    mass_coupling_dense<NR>(e, tile);
     for (uint32_t h = e.lane; h < tile.nheads; h += 32u) {
         float shares[2] = {0.f, 0.f};
         const uint32_t fl = hu(e, HF_FLAGS, h);
@@ -159,11 +214,8 @@ NKB_DEV void init_heads(Env& e, const Tile& tile) {
             float c = 0.f;
             if (ob == kNoBlock16) { /* static or kinematic side: no response */ }
             else if (ob == t.B) {
-                if (jo & kUnitRow) {
-                    float row[32 * NR];
-                    for (uint32_t i = 0; i < t.ndof; ++i) row[i] = i == (jo & 0xffffu) ? hf(e, HF_UNITV, h) : 0.f;
-                    c = mass_coupling<NR>(e, row);
-                } else c = mass_coupling<NR>(e, sm_jpool(e) + jo);
+                if (jo & kUnitRow) c = mass_coupling_unit<NR>(e, jo & 0xffffu, hf(e, HF_UNITV, h));
+                else c = hf(e, HF_RSD, h);
             } else {
                 const V3 dir = hf3(e, HF_N, h) * (side == 0u ? 1.f : -1.f);
                 const V3 ang = cross(hf3(e, side == 0u ? HF_RA : HF_RB, h), dir);
