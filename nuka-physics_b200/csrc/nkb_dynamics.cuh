@@ -162,7 +162,8 @@ NKB_DEV void joint_xform(const Env& e, float* E, V3& r) {
         for (int b = 0; b < 3; ++b) E[a * 3 + b] = rot.m[b * 3 + a];
 }
 
-// Affine joint drives, ops/articulation.cu:836-940: implicit PD position (mode 0), direct torque (1), velocity (2).
+// Affine joint drives, ops/articulation.cu:836-940: implicit PD position (mode 0), direct torque (1), velocity (2),
+// actuator (5: torque command inside a signed torque-speed envelope).
 NKB_DEV void stage_drives(Env& e) {
     const TemplateView& t = *e.t;
     const uint32_t l = e.lane;
@@ -178,10 +179,17 @@ NKB_DEV void stage_drives(Env& e) {
         ((position_control || velocity_control) && !isfinite(vt)) || (velocity_control && (!isfinite(kp) || kp < 0.f))) {
         e.status |= kStatusControlFailure; return;
     }
+    const float noload = mode == 5u ? e.s->noload_speed[at] : 0.f;
+    if (!isfinite(noload)) { e.status |= kStatusControlFailure; return; }
     float lower = limit > 0.f ? -limit : -FLT_MAX, upper = limit > 0.f ? limit : FLT_MAX;
     float damping = 0.f, bias = target;                       // torque mode: the target field carries the commanded effort
     if (position_control) { damping = kd + t.cfg.dt * kp; bias = kp * (target - e.q) + damping * vt; }
     else if (velocity_control) { damping = kp; bias = damping * vt; }
+    else if (mode == 5u && limit > 0.f && noload > 0.f) {
+        const float speed_bias = limit * e.qd / noload;
+        lower = fminf(fmaxf(-limit - speed_bias, -limit), limit);
+        upper = fminf(fmaxf(limit - speed_bias, -limit), limit);
+    }
     const float effort = bias - damping * e.qd;
     if (effort < lower || effort > upper) { bias = effort; damping = 0.f; }
     else { lower += damping * e.qd; upper += damping * e.qd; }

@@ -38,7 +38,9 @@ class Field(enum.IntEnum):
     DRIVE_DAMPING = 9
     DRIVE_FORCE_LIMIT = 10
     BASE_POSE = 11
+    TORQUE_INPUT = 12
     VELOCITY_TARGET = 13
+    ACTUATOR_NOLOAD_SPEED = 14
     JOINT_FEEDFORWARD = 22
     BODY_LINEAR_VELOCITY = 25
     BODY_ANGULAR_VELOCITY = 26

@@ -63,7 +63,7 @@ typedef struct orc_config {
     float velocity_tolerance;
     uint32_t max_contacts;      /* candidate slots per env */
     uint32_t max_pairs;         /* 0: same as max_contacts */
-    uint32_t control_mode;      /* 0 PD position, 1 torque, 2 velocity (phi/articulation_contract.hpp:16-23) */
+    uint32_t control_mode;      /* 0 PD position, 1 torque, 2 velocity, 5 actuator (phi/articulation_contract.hpp:16-23) */
 } orc_config;
 
 /* One env's cooked template (reference src/nk/model/model.hpp:175-244, 488-548). */
@@ -124,7 +124,7 @@ typedef struct orc_env {
     float *link_vel;                         /* L*6 */
     float *link_acc, *link_vbias, *link_pbias, *link_S;  /* L*6 */
     float *link_xup, *link_ic;               /* L*36 */
-    float *drive_target, *vel_target, *kp, *kd, *force_limit, *feedforward;
+    float *drive_target, *vel_target, *kp, *kd, *force_limit, *feedforward, *noload_speed;
     float *drive_command, *drive_dissipation, *drive_lower, *drive_upper;
     float *actuator_applied;                 /* L */
     float *M, *Mfactor, *bias;               /* ndof^2, ndof^2, ndof */

@@ -59,7 +59,8 @@ void orc_apply_drives(const orc_model *m, orc_env *e) {
         if ((position_control && (!isfinite(e->drive_target[l]) || !isfinite(e->kp[l]) || e->kp[l] < 0.0f ||
                                   !isfinite(e->kd[l]) || e->kd[l] < 0.0f)) ||
             ((position_control || velocity_control) && !isfinite(e->vel_target[l])) ||
-            (velocity_control && (!isfinite(e->kp[l]) || e->kp[l] < 0.0f))) {
+            (velocity_control && (!isfinite(e->kp[l]) || e->kp[l] < 0.0f)) ||
+            (mode == 5u && !isfinite(e->noload_speed[l]))) {
             e->status |= ORC_STATUS_CONTROL_FAILURE;
             continue;
         }
@@ -74,7 +75,15 @@ void orc_apply_drives(const orc_model *m, orc_env *e) {
         } else if (velocity_control) {
             damping = e->kp[l];
             bias = damping * e->vel_target[l];
-        } else bias = e->drive_target[l];          /* torque: the target field carries the commanded effort */
+        } else {
+            bias = e->drive_target[l];             /* torque, actuator: the target field carries the commanded effort */
+            if (mode == 5u && limit > 0.0f && e->noload_speed[l] > 0.0f) {
+                /* signed torque-speed envelope, articulation.cu:892-898 */
+                const float speed_bias = limit * velocity / e->noload_speed[l];
+                lower = fminf(fmaxf(-limit - speed_bias, -limit), limit);
+                upper = fminf(fmaxf(limit - speed_bias, -limit), limit);
+            }
+        }
         const float effort = bias - damping * velocity;
         const int saturated = effort < lower || effort > upper;
         if (saturated) {

@@ -314,10 +314,11 @@ def test_go2_scene_template(device, oracle):
     w.destroy()
 
 
-@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("mode", [1, 2, 5])
 def test_torque_and_velocity_control_modes(device, oracle, mode):
-    """control_mode 1 (the target field is a joint torque) and 2 (velocity servo with gain kp): trajectories of the
-    standing quadruped under each mode follow the oracle's."""
+    """control_mode 1 (the target field is a joint torque), 2 (velocity servo with gain kp) and 5 (actuator: torque
+    command inside a torque-speed envelope, written through TORQUE_INPUT): trajectories of the standing quadruped
+    under each mode follow the oracle's."""
     E = 48
     tb = T.quadruped(0)
     blob = tb.blob()
@@ -328,17 +329,26 @@ def test_torque_and_velocity_control_modes(device, oracle, mode):
     rng = np.random.Generator(np.random.PCG64(20 + mode))
     target = np.zeros((E, 13), np.float32)
     vt = np.zeros((E, 13), np.float32)
+    extra = []
     if mode == 1:
         target[:, 1:] = rng.uniform(-3.0, 3.0, size=(E, 12))          # joint torques, N m
+    elif mode == 5:
+        target[:, 1:] = rng.uniform(-6.0, 6.0, size=(E, 12))          # commands beyond the 4 N m stall torque
+        limit = np.full((E, 13), 4.0, np.float32)
+        noload = np.zeros((E, 13), np.float32)
+        noload[:, 1:] = rng.uniform(1.0, 3.0, size=(E, 12))           # rad/s
+        noload[:, 1] = 0.0                                            # one joint without a speed envelope
+        extra = [(F.DRIVE_FORCE_LIMIT, "drive_force_limit", limit), (F.ACTUATOR_NOLOAD_SPEED, "noload_speed", noload)]
     else:
         vt[:, 1:] = rng.uniform(-0.5, 0.5, size=(E, 12))              # joint velocity targets, rad/s
     for world_set, oracle_name, value in ((F.JOINT_POSITION, "q", st["q"]), (F.BASE_POSE, "base_pose", st["base_pose"]),
-                                          (F.DRIVE_TARGET, "drive_target", target), (F.VELOCITY_TARGET, "velocity_target", vt)):
+                                          (F.TORQUE_INPUT if mode == 5 else F.DRIVE_TARGET, "drive_target", target),
+                                          (F.VELOCITY_TARGET, "velocity_target", vt), *extra):
         w.upload(world_set, value); o.set(oracle_name, value.reshape(E, -1))
     w.forward_kinematics(); o.refresh()
     w.step_n(1); o.step(1)
     # the velocity servo (gain 40 on every joint) makes the step stiffer than the PD hold: 5e-5 there, 2e-5 for torques
-    assert rel(w.download(F.JOINT_VELOCITY), o.get("qdot", 13)) < (2e-5 if mode == 1 else 5e-5)
+    assert rel(w.download(F.JOINT_VELOCITY), o.get("qdot", 13)) < (5e-5 if mode == 2 else 2e-5)
     w.step_n(19); o.step(19)
     assert rel(w.download(F.JOINT_POSITION), o.get("q", 13)) < 1e-4
     assert rel(w.download(F.BASE_POSE), o.get("base_pose", 7)) < 1e-4
