@@ -174,6 +174,32 @@ def test_benchmark_size_runs_are_reproducible(device):
     assert ends[0] == ends[1]
 
 
+def test_env_shards_equal_the_whole_batch(device):
+    """The property multi-GPU runs rest on, at configs[4]'s per-GPU size: 8192 quadruped + 4 boxes envs stepped as one
+    world and as two 4096-env shards (contiguous env ranges, as nuka.shard.env_range hands them out) end in
+    byte-identical state, so a sharded run equals the single-world run env for env."""
+    from nuka import shard
+    E, parts = 8192, 2
+    blob = T.quadruped(0, boxes=4).blob()
+    st = T.quadruped_state(E, 4)
+    fields = (F.JOINT_POSITION, F.JOINT_VELOCITY, F.BASE_POSE, F.RIGID_BODY_TRANSFORM, F.BODY_LINEAR_VELOCITY, F.CONTACT_COUNT)
+
+    def run(lo, hi):
+        w = nuka.World.create_from_template(device, blob, hi - lo)
+        w.upload(F.JOINT_POSITION, st["q"][lo:hi]); w.upload(F.BASE_POSE, st["base_pose"][lo:hi]); w.forward_kinematics()
+        w.step_n(30)
+        out = [w.download(f).copy() for f in fields]
+        w.destroy()
+        return out
+
+    whole = run(0, E)
+    for rank in range(parts):
+        lo, hi = shard.env_range(rank, parts, E)
+        part = run(lo, hi)
+        for f, a, b in zip(fields, whole, part):
+            assert np.array_equal(a[lo:hi], b), (rank, f)
+
+
 def test_free_boxes_land_like_the_oracle(device, oracle):
     """Six free boxes falling onto a plane (the free rigid-body path: gyroscopic integration, box-plane and
     box-box manifolds, 6-coordinate solver blocks): candidate pairs and contact counts bit-exact, poses within
