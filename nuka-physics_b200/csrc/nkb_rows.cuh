@@ -256,12 +256,6 @@ NKB_DEV void stage_warm_start(Env& e, uint32_t nheads) {
     const TemplateView& t = *e.t;
     const uint32_t npts = t.cfg.max_contacts * 4u;
     const CacheEntry* cache = e.s->cache + (size_t)e.env * npts;
-    // a cache of up to 32 points is read once, one entry per lane, and searched in registers
-    const bool resident = npts <= 32u;
-    CacheEntry mine;
-    mine.pair = 0xffffffffu; mine.feature = 0ull; mine.age = 0xffffffffu;
-    mine.lambda[0] = mine.lambda[1] = mine.lambda[2] = 0.f; mine.normal[0] = mine.normal[1] = mine.normal[2] = 0.f;
-    if (resident && e.lane < npts && nheads != 0u && (hu(e, HF_FLAGS, 0u) & kHeadContact)) mine = cache[e.lane];
     for (uint32_t h = 0u; h < nheads; ++h) {
         if (!(hu(e, HF_FLAGS, h) & kHeadContact)) break;     // contact heads come first
         const uint32_t at = hu(e, HF_REF, h) & 0xffffu;
@@ -281,24 +275,15 @@ NKB_DEV void stage_warm_start(Env& e, uint32_t nheads) {
         }
         if (dup) continue;
         uint32_t found = 0xffffffffu;
-        CacheEntry en;
-        if (resident) {
-            const uint32_t m = __ballot_sync(NKB_FULL, mine.pair == pair && mine.feature == feat && mine.age < 2u);
-            if (m == 0u) continue;
-            found = (uint32_t)__ffs(m) - 1u;
-#pragma unroll
-            for (int k = 0; k < 3; ++k) { en.lambda[k] = __shfl_sync(NKB_FULL, mine.lambda[k], found); en.normal[k] = __shfl_sync(NKB_FULL, mine.normal[k], found); }
-        } else {
-            for (uint32_t base = 0u; base < npts && found == 0xffffffffu; base += 32u) {
-                const uint32_t c = base + e.lane;
-                const bool hit = c < npts && cache[c].pair == pair && cache[c].feature == feat && cache[c].age < 2u;
-                const uint32_t m = __ballot_sync(NKB_FULL, hit);
-                if (m != 0u) found = base + (uint32_t)__ffs(m) - 1u;
-            }
-            if (found == 0xffffffffu) continue;
-            if (e.lane == 0u) en = cache[found];
+        for (uint32_t base = 0u; base < npts && found == 0xffffffffu; base += 32u) {
+            const uint32_t c = base + e.lane;
+            const bool hit = c < npts && cache[c].pair == pair && cache[c].feature == feat && cache[c].age < 2u;
+            const uint32_t m = __ballot_sync(NKB_FULL, hit);
+            if (m != 0u) found = base + (uint32_t)__ffs(m) - 1u;
         }
+        if (found == 0xffffffffu) continue;
         if (e.lane == 0u) {
+            const CacheEntry en = cache[found];
             const V3 nrm = ld3(sm_cnormal(e, at)), cn = mk3(en.normal[0], en.normal[1], en.normal[2]);
             if (dot(nrm, cn) > 0.25f) {
                 V3 ot1, ot2, t1, t2;

@@ -354,10 +354,10 @@ NKB_DEV void respond(const HeadRegs& r, V3 move, V3& f, float& cxx, float& cyy, 
 
 // Row steps J d of a block's incident heads (block_descent_tile.cuh:2019-2044); lane = head, d staged in shared
 // memory with zeros past the block's dimension.
-template <bool kRigid>
+template <bool kArtic>
 NKB_DEV void row_steps(Env& e, const Tile& tile, uint32_t b, const float* dvec) {
-    const uint32_t nb = tile.nblocks, dim = blk_dim(e, b);
-    const bool artic = !kRigid || b == e.t->B;
+    const uint32_t nb = tile.nblocks, dim = kArtic ? blk_dim(e, b) : 6u;
+    constexpr bool artic = kArtic;
     const uint32_t* inc = blk_inc(e, nb);
     const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
     const uint32_t chunks = (dim + 3u) >> 2, n4 = chunks << 2;
@@ -483,10 +483,12 @@ NKB_DEV void apply_moves(Env& e, const Tile& tile, uint32_t b, float alpha) {
 // incident head in the row evaluations and publishes its response through the head's shared-memory fields.
 // kRigid = false compiles the descent for worlds without free bodies: the articulation is the only block and the
 // rigid-block code (dense 6 x 6 mass, staged 3 x 8 Jacobian rows) drops out.
-template <int NR, bool kRigid>
+// kDim = 0: the articulation's block, dimension read at run time.  kDim = 6: a free rigid body; the loops over its
+// coordinates have constant bounds and unroll.  Each instance carries only its own kind's code.
+template <int NR, bool kRigid, int kDim>
 NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
-    const uint32_t l = e.lane, nb = tile.nblocks, dim = blk_dim(e, b);
-    const bool artic = !kRigid || b == e.t->B;
+    const uint32_t l = e.lane, nb = tile.nblocks, dim = kDim != 0 ? (uint32_t)kDim : blk_dim(e, b);
+    constexpr bool artic = kDim == 0;
     const uint32_t* inc = blk_inc(e, nb);
     const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
     const uint32_t chunks = (dim + 3u) >> 2, ldh = pad_ld(dim);
@@ -599,7 +601,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                 if (coord[r]) {
                     const float4* Mr4 = reinterpret_cast<const float4*>(Mr[r]);
                     float4* Hr4 = reinterpret_cast<float4*>(Hr[r]);
-#pragma unroll 1
+#pragma unroll (kDim != 0 ? 8 : 1)
                     for (uint32_t c = 0u; c < chunks; ++c) {
                         const float4 m = Mr4[c], hi = reinterpret_cast<const float4*>(hi_v)[c], lo = reinterpret_cast<const float4*>(lo_v)[c];
                         Hr4[c] = m;
@@ -662,7 +664,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                         const float a0 = j0 * c0, a1 = j1 * c1 + j2 * c12, a2 = j2 * c2 + j1 * c12;
                         if (coord[r]) {
                             float4* Hr4 = reinterpret_cast<float4*>(Hr[r]);
-#pragma unroll 1
+#pragma unroll (kDim != 0 ? 8 : 1)
                             for (uint32_t cc = 0u; cc < chunks; ++cc) {
                                 float4 h4 = Hr4[cc];
                                 const float4 x = r0[cc], y = r1[cc], z = r2[cc];
@@ -683,7 +685,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                 if (coord[r]) {
                     float4* Hr4 = reinterpret_cast<float4*>(Hr[r]);
                     Hr[r][l + 32u * r] += diag[r];
-#pragma unroll 1
+#pragma unroll (kDim != 0 ? 8 : 1)
                     for (uint32_t c = 0u; c < chunks; ++c) {
                         const float4 v = Hr4[c], uu = reinterpret_cast<const float4*>(u_v)[c];
                         finite &= isfinite(v.x) && isfinite(v.y) && isfinite(v.z) && isfinite(v.w);
@@ -711,7 +713,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
 #pragma unroll
             for (int r = 0; r < NR; ++r) inverse[r] = 0.f;
             __syncwarp();
-#pragma unroll 1
+#pragma unroll (kDim != 0 ? 8 : 1)
             for (uint32_t k = 0u; k < dim; ++k) {
                 float value[NR];
                 const float4* Hk4 = reinterpret_cast<const float4*>(H + k * ldh);
@@ -722,7 +724,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                     if (coord[r] && l + 32u * r >= k) {
                         const float4* Hr4 = reinterpret_cast<const float4*>(Hr[r]);
                         float s0 = 0.f, s1 = 0.f;
-#pragma unroll 1
+#pragma unroll (kDim != 0 ? 8 : 1)
                         for (uint32_t c = 0u; c < full; ++c) {
                             const float4 a = Hr4[c], bb = Hk4[c];
                             s0 = fmaf(a.x, bb.x, s0); s1 = fmaf(a.y, bb.y, s1); s0 = fmaf(a.z, bb.z, s0); s1 = fmaf(a.w, bb.w, s1);
@@ -751,7 +753,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             float rr[NR], scaled[NR];
 #pragma unroll
             for (int r = 0; r < NR; ++r) rr[r] = force[r];
-#pragma unroll 1
+#pragma unroll (kDim != 0 ? 8 : 1)
             for (uint32_t j = 0u; j < dim; ++j) {
 #pragma unroll
                 for (int r = 0; r < NR; ++r) scaled[r] = rr[r] * inverse[r];
@@ -762,7 +764,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                     rr[r] = c == j ? y : ((coord[r] && c > j) ? fmaf(-Hr[r][j], y, rr[r]) : rr[r]);
                 }
             }
-#pragma unroll 1
+#pragma unroll (kDim != 0 ? 8 : 1)
             for (uint32_t jj = dim; jj > 0u; --jj) {
                 const uint32_t j = jj - 1u;
 #pragma unroll
@@ -788,7 +790,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             float ms = 0.f;
             if (coord[r]) {
                 const float4* Mr4 = reinterpret_cast<const float4*>(Mr[r]);
-#pragma unroll 1
+#pragma unroll (kDim != 0 ? 8 : 1)
                 for (uint32_t c = 0u; c < chunks; ++c) {
                     const float4 m = Mr4[c], dd = reinterpret_cast<const float4*>(dvec)[c];
                     ms = fmaf(m.x, dd.x, ms); ms = fmaf(m.y, dd.y, ms); ms = fmaf(m.z, dd.z, ms); ms = fmaf(m.w, dd.w, ms);
@@ -808,7 +810,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             if (!(total_dec > 0.f)) break;
         }
         tick(e, 20);
-        row_steps<kRigid>(e, tile, b, dvec);
+        row_steps<artic>(e, tile, b, dvec);
         tick(e, 21);
         const float alpha = search_line(e, tile, b, islope, icurv);
         tick(e, 22);
@@ -866,7 +868,12 @@ NKB_DEV void descend_blocks(Env& e, Tile& tile, bool position) {
     const uint32_t* order = block_order(e, nb);
     const uint32_t count = order[nb];
 #pragma unroll 1
-    for (uint32_t k = 0u; k < count; ++k) descend_block<NR, kRigid>(e, tile, kRigid ? order[k] : e.t->B, position);
+    for (uint32_t k = 0u; k < count; ++k) {
+        if (!kRigid) { descend_block<NR, false, 0>(e, tile, e.t->B, position); continue; }
+        const uint32_t b = order[k];
+        if (b == e.t->B) descend_block<NR, kRigid, 0>(e, tile, b, position);
+        else descend_block<1, kRigid, 6>(e, tile, b, position);     // a rigid block's 6 coordinates: one per lane
+    }
 }
 
 struct DualMomentum { float t, beta; };
