@@ -517,13 +517,25 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             }
         }
         if (l < 24u) jscr[l] = 0.f;
-        const uint32_t staged_count = min(ie - ib, e.lay->rjac_heads);
-        float* out = e.sm + e.lay->rjac;
-#pragma unroll 1
-        for (uint32_t j = 0u; j < staged_count; ++j) {
-            const uint32_t h = inc[ib + j];
-            const uint32_t ss = head_owner(e, h, 0u) == b ? 0u : 1u, as = head_axes(e, h);
-            if (l < 24u) { const uint32_t ax = l >> 3, i = l & 7u; out[j * 24u + l] = (i < 6u && ax < as) ? head_jac(e, h, ss, ax, i, b) : 0.f; }
+        // lane = incident head: its three rows [direction, arm x direction, 0, 0], signed by the side it sits on
+        const uint32_t staged_count = min(ie - ib, e.lay->rjac_heads);      // at most 32: one pass
+        if (l < staged_count) {
+            const uint32_t h = inc[ib + l];
+            const float sgn = head_owner(e, h, 0u) == b ? 1.f : -1.f;
+            const uint32_t as = head_axes(e, h);
+            const V3 arm = hf3(e, sgn > 0.f ? HF_RA : HF_RB, h);
+            float4* out = reinterpret_cast<float4*>(e.sm + e.lay->rjac + l * 24u);
+#pragma unroll
+            for (uint32_t ax = 0u; ax < 3u; ++ax) {
+                float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
+                if (ax < as) {
+                    const V3 dir = hf3(e, ax == 0u ? HF_N : ax == 1u ? HF_T1 : HF_T2, h);
+                    const V3 ang = cross(arm, dir);
+                    lo4 = make_float4(sgn * dir.x, sgn * dir.y, sgn * dir.z, sgn * ang.x);
+                    hi4 = make_float4(sgn * ang.y, sgn * ang.z, 0.f, 0.f);
+                }
+                out[2u * ax] = lo4; out[2u * ax + 1u] = hi4;
+            }
         }
     }
     bool coord[NR];
