@@ -261,10 +261,19 @@ def main():
         peak, peak_kind = hbm_peak()
         bytes_per = algorithmic_bytes(slots, points)
         achieved = bytes_per * E * args.steps / (gpu_ms * 1e-3) / 1e9
-        traffic = None
+        traffic, issue = None, None
         try:
             with open(os.path.join(ROOT, "profiles", "step_kernel_quadruped_traffic.txt")) as f:
-                traffic = json.load(f).get("dram_bytes_per_launch_4096_envs")
+                captured = json.load(f)
+            traffic = captured.get("dram_bytes_per_launch_4096_envs")
+            # the bound that explains this kernel: warp instructions issued per second (instruction count of one
+            # captured 4096-env launch, scaled by envs) against one instruction per scheduler per cycle
+            instructions = captured.get("warp_instructions_per_launch_4096_envs")
+            if instructions and clocks.get("sm_mhz"):
+                issued = instructions / 4096.0 * E * args.steps / (gpu_ms * 1e-3)
+                issue_peak = 148 * 4 * clocks["sm_mhz"] * 1e6
+                issue = {"achieved": issued / 1e9, "peak": issue_peak / 1e9, "unit": "G warp-instructions/s",
+                         "frac": issued / issue_peak, "note": "148 SMs x 4 schedulers x SM clock; instruction count from the ncu capture"}
         except Exception:
             pass
         line = {
@@ -276,7 +285,7 @@ def main():
                        "obs_allgather": distributed and not args.no_gather, "mean_contact_slots": slots, "mean_contact_points": points},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_source": peak_kind, "algorithmic_bytes_per_env_step": bytes_per,
-                         "kernel": "step_kernel", "kernel_ms": gpu_ms / args.steps},
+                         "kernel": "step_kernel", "kernel_ms": gpu_ms / args.steps, "issue": issue},
             "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": int(targets.numel() * 4),
                     "d2h_bytes_per_step": int(out_q.numel() * 4 + out_b.numel() * 4)},
             "gpu_launches": int(launches),
