@@ -53,8 +53,12 @@ def _shape_of(cs):
 
 
 def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0, ground_mu=1.0, self_collision=False,
-         max_contacts=None):
-    """``scene`` is a parsed .nks document (dict) or a path.  Returns a TemplateBuilder."""
+         max_contacts=None, max_points=None):
+    """``scene`` is a parsed .nks document (dict) or a path.  Returns a TemplateBuilder.
+
+    ``max_points`` caps the contact points per env that get solver rows (default: the bound derived from the shape
+    pairs, at most 128); a smaller cap shrinks the env's shared-memory slice, and a step that exceeds it sets the
+    env's head-overflow status bit and drops the excess."""
     if not isinstance(scene, dict):
         with open(scene) as f:
             scene = json.load(f)
@@ -120,6 +124,7 @@ def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0,
     add(roots[0], None)
     tb.add_plane(ground_height, mu=ground_mu)
     tb.cfg["max_contacts"] = int(max_contacts) if max_contacts is not None else max(len(shape_rows), 1)
+    tb.max_points = int(max_points) if max_points is not None else 0
     return tb
 
 
@@ -161,8 +166,10 @@ def main(argv=None):
     ap.add_argument("--kp", type=float, default=60.0)
     ap.add_argument("--kd", type=float, default=2.0)
     ap.add_argument("--ground-height", type=float, default=0.0)
+    ap.add_argument("--max-points", type=int, default=None, help="contact points per env that get solver rows")
     args = ap.parse_args(argv)
-    tb = cook(args.scene, dt=args.dt, vel_iters=args.velocity_iterations, kp=args.kp, kd=args.kd, ground_height=args.ground_height)
+    tb = cook(args.scene, dt=args.dt, vel_iters=args.velocity_iterations, kp=args.kp, kd=args.kd, ground_height=args.ground_height,
+              max_points=args.max_points)
     with open(args.out, "wb") as f:
         f.write(tb.blob())
     print(f"{args.out}: {len(tb.links)} links, {len(tb.bodies)} collidable rows")

@@ -17,7 +17,8 @@ STANCE = {"hip": 0.0, "thigh": 0.9, "calf": -1.8}
 
 
 def main():
-    tb = nks.cook(SCENE, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0)
+    # 32 contact points per env: four feet plus every other segment lying on the ground needs 24
+    tb = nks.cook(SCENE, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, max_points=32)
     names = nks.link_names(SCENE)
     for link, name in zip(tb.links, names):
         for key, angle in STANCE.items():
