@@ -213,7 +213,9 @@ def _add_quadruped(tb, kp=40.0, kd=1.0, mu=0.8):
 
 def quadruped(seed=0, dt=1.0 / 200.0, vel_iters=4, boxes=0):
     """Config 2 (and, with ``boxes``, config 5): floating-base quadruped on a ground plane."""
-    tb = TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=8 if boxes == 0 else 24)
+    # with boxes: 4 foot points + 4 per resting box + box-box manifolds; 40 points with solver rows cover the scenes seen
+    # (mean 20), more sets the env's head-overflow status bit
+    tb = TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=8 if boxes == 0 else 24, max_points=0 if boxes == 0 else 40)
     _add_quadruped(tb)
     tb.base_pose = [0, 0, 0.31, 1, 0, 0, 0]
     rng = np.random.Generator(np.random.PCG64(seed))
@@ -314,7 +316,7 @@ def humanoid_state(env_count, seed=0):
 def box_pile(seed=0, dt=1.0 / 240.0, vel_iters=8, count=48):
     """Config 4: free boxes on a 4x4x3 jittered lattice above a plane (template holds the nominal lattice)."""
     rng = np.random.Generator(np.random.PCG64(seed))
-    tb = TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=4 * count, max_points=0 if count <= 12 else 6 * count)
+    tb = TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=4 * count, max_points=6 * count)
     for k in range(count):
         he = rng.uniform(0.02, 0.1, size=3)
         rho = rng.uniform(500.0, 2000.0)
