@@ -121,6 +121,28 @@ def test_nan_input_sets_the_status_bit_without_faulting(device):
     w.destroy()
 
 
+def test_contact_point_capacity_overflow_sets_the_status_bit_and_drops_the_excess(device):
+    """Six boxes landing produce more contact points than a template capacity of 8: the envs that exceed it raise the
+    head-overflow status bit (1 << 20), the extra points get no solver rows, and stepping goes on with finite state."""
+    E = 32
+    tb = T.box_pile(2, count=6)
+    tb.max_points = 8
+    st = T.box_pile_state(E, 2, count=6)
+    w = nuka.World.create_from_template(device, tb.blob(), E)
+    w.upload(F.RIGID_BODY_TRANSFORM, st["body_pose"])
+    w.forward_kinematics()
+    w.step_n(60)
+    status = w.download(F.ENV_STATUS)[:, 0]
+    points = w.download(F.CONTACT_COUNT).sum(axis=1)
+    assert (points > 8).any()
+    assert ((status & (1 << 20)) != 0).any()
+    assert (((status & (1 << 20)) != 0) | (points <= 8)).all()          # every env over the capacity in the last step is flagged
+    assert np.isfinite(w.download(F.RIGID_BODY_TRANSFORM)).all() and np.isfinite(w.download(F.BODY_LINEAR_VELOCITY)).all()
+    w.step_n(5)                                                          # and the world keeps stepping
+    w.synchronize()
+    w.destroy()
+
+
 def test_scene_path_loads_a_cooked_template_file(device, tmp_path):
     path = tmp_path / "arm.nkt"
     path.write_bytes(T.arm7(0).blob())
