@@ -54,3 +54,21 @@ def test_cooked_scene_runs_in_the_oracle(oracle, tmp_path):
     o.step(200)
     assert o.get("env_status", 1).max() == 0
     assert np.isfinite(o.get("base_pose", 7)).all() and o.get("pair_count", 1).max() >= 1
+
+
+def test_contact_point_capacity_travels_in_the_template(tmp_path):
+    """The cooker's max_points option becomes the template's optional max_points record (absent by default); the Go2
+    fixture carries 32."""
+    import os
+    from nuka import nkt
+    assert "max_points" not in nks.cook(_scene()).arrays()
+    arrays = nkt.unpack(nks.cook(_scene(), max_points=12).blob())
+    assert arrays["max_points"].tolist() == [12]
+    out = tmp_path / "robot.nkt"
+    path = tmp_path / "robot.nks"
+    path.write_text(json.dumps(_scene()))
+    nks.main([str(path), str(out), "--max-points", "20"])
+    assert nkt.unpack(out.read_bytes())["max_points"].tolist() == [20]
+    fixture = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "go2.nkt")
+    with open(fixture, "rb") as f:
+        assert nkt.unpack(f.read())["max_points"].tolist() == [32]
