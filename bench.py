@@ -29,8 +29,8 @@ WORKLOAD = "quadruped (13 links, 18 DoF, 4 foot spheres + trunk box on a plane),
 NJ, NF, NL = 12, 1, 13
 
 
-def algorithmic_bytes(slots, points):
-    return 12 * NJ + 52 * NF + 8 * NJ + 52 * NF + 52 * NL + 8 * (NJ + 3 * points) + 8 * slots + 32 * points
+def algorithmic_bytes(slots, points, free_bodies=0):
+    return 12 * NJ + 52 * NF + 8 * NJ + 52 * NF + 52 * NL + 104 * free_bodies + 8 * (NJ + 3 * points) + 8 * slots + 32 * points
 
 
 def hbm_peak():
@@ -157,6 +157,8 @@ def main():
     ap.add_argument("--envs", type=int, default=ENVS_PER_GPU)
     ap.add_argument("--no-flush", action="store_true", help="skip the L2 flush between timed steps")
     ap.add_argument("--no-gather", action="store_true", help="N > 1: skip the per-step observation all-gather")
+    ap.add_argument("--boxes", type=int, default=0,
+                    help="free 0.1 m boxes beside each quadruped: 4 with --envs 8192 per GPU is configs[4]'s shard (not the headline workload)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -176,7 +178,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     E = args.envs
     dev = nuka.Device.create(local_rank)
-    w = nuka.World.create_from_template(dev, T.quadruped(0).blob(), E)
+    w = nuka.World.create_from_template(dev, T.quadruped(0, boxes=args.boxes).blob(), E)
     st = T.quadruped_state(E, seed=rank)
     w.upload(F.JOINT_POSITION, st["q"]); w.upload(F.BASE_POSE, st["base_pose"]); w.forward_kinematics()
     w.synchronize()
@@ -259,12 +261,14 @@ def main():
         value = total_envs * args.steps / (gpu_ms * 1e-3)
         e2e_value = total_envs * args.steps / (e2e_ms * 1e-3)
         peak, peak_kind = hbm_peak()
-        bytes_per = algorithmic_bytes(slots, points)
+        bytes_per = algorithmic_bytes(slots, points, args.boxes)
         achieved = bytes_per * E * args.steps / (gpu_ms * 1e-3) / 1e9
         traffic, issue = None, None
         try:
             with open(os.path.join(ROOT, "profiles", "step_kernel_quadruped_traffic.txt")) as f:
                 captured = json.load(f)
+            if args.boxes:
+                raise ValueError("the capture is of the headline workload")
             traffic = captured.get("dram_bytes_per_launch_4096_envs")
             # the bound that explains this kernel: warp instructions issued per second (instruction count of one
             # captured 4096-env launch, scaled by envs) against one instruction per scheduler per cycle
@@ -280,7 +284,7 @@ def main():
             "metric": METRIC, "value": value, "unit": "env-steps/s", "n_gpus": world_size, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": gpu_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD,
+            "config": {"workload": WORKLOAD if not args.boxes else WORKLOAD.replace("configs[1]", f"configs[4]'s env: + {args.boxes} free 0.1 m boxes"),
                        "envs_per_gpu": E, "dt": 1.0 / 200.0, "velocity_iterations": 4, "l2_flush_between_steps": flush is not None,
                        "obs_allgather": distributed and not args.no_gather, "mean_contact_slots": slots, "mean_contact_points": points},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
