@@ -9,16 +9,61 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
 
 
+REFERENCE_CHECKOUT = os.environ.get("NUKA_REFERENCE_CHECKOUT", "/root/reference")
+
+
 def build():
-    subprocess.run(["make", "-C", _HERE, "liborc.so"], check=True, stdout=subprocess.DEVNULL)
+    """Builds the restatement (portable and contraction-free variants) and, where the reference checkout is present,
+    the binding of the reference's own headers (oracle/_ref)."""
+    subprocess.run(["make", "-C", _HERE, "liborc.so", "liborc_strict.so"], check=True, stdout=subprocess.DEVNULL)
+    if os.path.isdir(os.path.join(REFERENCE_CHECKOUT, "src")):
+        subprocess.run(["make", "-C", _HERE, "_ref/libref_headers.so", f"REF={REFERENCE_CHECKOUT}"], check=True, stdout=subprocess.DEVNULL)
 
 
-def lib():
+def build_native():
+    """-O3 -march=native build for the machine that times the CPU baseline; returns its path or None."""
+    done = subprocess.run(["make", "-C", _HERE, "liborc_native.so"], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    path = os.path.join(_HERE, "liborc_native.so")
+    return path if done.returncode == 0 and os.path.exists(path) else None
+
+
+def _declare_kat(L, prefix):
+    f = getattr(L, prefix + "_manifold_frames")
+    f.restype = ctypes.c_int
+    f.argtypes = [ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p,
+                  ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p]
+    g = getattr(L, prefix + "_law_batch")
+    g.restype = None
+    g.argtypes = [ctypes.c_int, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32]
+    return L
+
+
+def strict_lib():
+    """The restatement compiled without floating-point contraction (differential tests)."""
+    path = os.path.join(_HERE, "liborc_strict.so")
+    if not os.path.exists(path):
+        build()
+    return _declare_kat(ctypes.CDLL(path), "orc")
+
+
+def ref_lib():
+    """The reference's own headers behind a C binding, or None where neither the built file nor the checkout exists."""
+    path = os.path.join(_HERE, "_ref", "libref_headers.so")
+    if not os.path.exists(path):
+        if not os.path.isdir(os.path.join(REFERENCE_CHECKOUT, "src")):
+            return None
+        build()
+    return _declare_kat(ctypes.CDLL(path), "ref")
+
+
+def lib(path=None):
+    """The restatement; `path` selects another build of it (liborc_native.so) for the caller's own use."""
     global _LIB
-    if _LIB is None:
-        path = os.path.join(_HERE, "liborc.so")
-        if not os.path.exists(path):
-            build()
+    if _LIB is None or path is not None:
+        if path is None:
+            path = os.path.join(_HERE, "liborc.so")
+            if not os.path.exists(path):
+                build()
         L = ctypes.CDLL(path)
         L.orc_world_create.restype = ctypes.c_void_p
         L.orc_world_create.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_uint32]

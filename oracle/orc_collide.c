@@ -532,3 +532,23 @@ int orc_manifold(uint32_t kind_a, const float *pose_a, const float *params_a, ui
     }
     return (int)mf.count;
 }
+
+/* Differential-test access: one analytic pair given world frames (cx, cy, cz, t: 12 floats) instead of poses, so that
+ * this restatement and the reference's own header evaluate the same inputs bit for bit.  out as orc_manifold;
+ * keys: the stable feature key of each point.  Returns the point count, -1 for a pair kind without a handler. */
+int orc_manifold_frames(uint32_t kind_a, const float *frame_a, const float *params_a, uint32_t kind_b, const float *frame_b,
+                        const float *params_b, float query, float *out, uint64_t *keys) {
+    prim p[2];
+    const float *frames[2] = {frame_a, frame_b}, *pars[2] = {params_a, params_b};
+    for (int k = 0; k < 2; ++k) {
+        p[k].f.cx = v3ld(frames[k]); p[k].f.cy = v3ld(frames[k] + 3); p[k].f.cz = v3ld(frames[k] + 6); p[k].f.t = v3ld(frames[k] + 9);
+        p[k].radius = pars[k][0]; p[k].hh = pars[k][1]; p[k].he = V3(pars[k][0], pars[k][1], pars[k][2]);
+    }
+    manifold mf;
+    if (!primitive_pair(kind_a, &p[0], kind_b, &p[1], query, &mf)) return -1;
+    for (uint32_t i = 0; i < mf.count; ++i) {
+        v3st(out + 7 * i, mf.p[i].pos); v3st(out + 7 * i + 3, mf.p[i].n); out[7 * i + 6] = mf.p[i].pen;
+        keys[i] = mf.p[i].key;
+    }
+    return (int)mf.count;
+}

@@ -794,3 +794,28 @@ void orc_law_kat(int which, const float *in, double *out) {
         out[0] = impulse.y; out[1] = impulse.z; out[2] = curv.yy; out[3] = curv.zz; out[4] = curv.yz;
     }
 }
+
+/* Differential-test access: the row laws over n records, same record layouts as the reference-header binding
+ * (oracle/ref_headers.cpp: ref_law_batch), which 0..4. */
+void orc_law_batch(int which, uint32_t n, const float *in, uint32_t in_stride, float *out, uint32_t out_stride) {
+    for (uint32_t i = 0; i < n; ++i) {
+        const float *x = in + (size_t)i * in_stride;
+        float *o = out + (size_t)i * out_stride;
+        if (which == 0) {
+            const sterm_t t = scalar_impulse(x[0], x[1], x[2], x[3], x[4], x[5], float_scalar_response(x[1], x[3]));
+            o[0] = t.impulse; o[1] = t.curvature;
+        } else if (which == 1) {
+            o[0] = cone_argument(x[0], x[1], x[2], x[3]);
+        } else if (which == 2) {
+            v3 impulse; sym3 curv;
+            tangent_impulse(V3(0.0f, x[0], x[1]), x[2], V3(0.0f, x[3], x[4]), x[5], x[6], x[7], &impulse, &curv);
+            o[0] = impulse.y; o[1] = impulse.z; o[2] = curv.yy; o[3] = curv.zz; o[4] = curv.yz;
+        } else if (which == 3) {
+            o[0] = (float)momentum_restart(V3(x[0], x[1], x[2]), V3(x[3], x[4], x[5]), V3(x[6], x[7], x[8]), V3(x[9], x[10], x[11]));
+        } else if (which == 4) {
+            relax_t last = {V3(x[6], x[7], x[8]), x[9], V3(x[10], x[11], x[12])};
+            const v3 r = relax_contact_impulse(V3(x[0], x[1], x[2]), V3(x[3], x[4], x[5]), &last);
+            o[0] = r.x; o[1] = r.y; o[2] = r.z; o[3] = last.weight;
+        }
+    }
+}

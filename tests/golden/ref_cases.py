@@ -1,0 +1,133 @@
+"""Seeded random inputs of the differential tests between the reference's own headers (oracle/_ref) and the C
+restatement: analytic contact pairs and augmented-Lagrangian row laws.  Shared by tests/test_ref_differential.py and
+tests/golden/make_ref_vectors.py so that the live comparison and the committed vectors see the same cases."""
+import numpy as np
+
+SPHERE, CAPSULE, BOX, PLANE = 0, 1, 2, 3
+PAIR_KINDS = [(SPHERE, SPHERE), (SPHERE, BOX), (BOX, SPHERE), (SPHERE, PLANE), (PLANE, SPHERE), (BOX, PLANE), (PLANE, BOX),
+              (BOX, BOX), (CAPSULE, PLANE), (PLANE, CAPSULE), (CAPSULE, SPHERE), (SPHERE, CAPSULE), (CAPSULE, CAPSULE)]
+
+
+def _frames(quat, pos):
+    """World axes of unit quaternions (wxyz), float32 arithmetic as one fixed expression, then the origin: n x 12."""
+    q = quat.astype(np.float32)
+    w, x, y, z = q[:, 0], q[:, 1], q[:, 2], q[:, 3]
+    one, two = np.float32(1), np.float32(2)
+    cx = np.stack([one - two * (y * y + z * z), two * (x * y + w * z), two * (x * z - w * y)], 1)
+    cy = np.stack([two * (x * y - w * z), one - two * (x * x + z * z), two * (y * z + w * x)], 1)
+    cz = np.stack([two * (x * z + w * y), two * (y * z - w * x), one - two * (x * x + y * y)], 1)
+    return np.concatenate([cx, cy, cz, pos.astype(np.float32)], 1).astype(np.float32)
+
+
+def _unit_quats(rng, n, snap):
+    """Random orientations; a `snap` fraction is an exact multiple of 90 degrees about a coordinate axis (face ties)."""
+    q = rng.normal(size=(n, 4))
+    q /= np.linalg.norm(q, axis=1, keepdims=True)
+    exact = np.array([[1, 0, 0, 0], [0, 1, 0, 0], [0, 0, 1, 0], [0, 0, 0, 1],
+                      [np.sqrt(0.5), np.sqrt(0.5), 0, 0], [np.sqrt(0.5), 0, np.sqrt(0.5), 0], [np.sqrt(0.5), 0, 0, np.sqrt(0.5)]])
+    pick = rng.random(n) < snap
+    q[pick] = exact[rng.integers(0, len(exact), pick.sum())]
+    return q
+
+
+def _params(rng, kind, n):
+    p = np.zeros((n, 4), np.float32)
+    if kind == SPHERE:
+        p[:, 0] = rng.uniform(0.02, 0.4, n)
+    elif kind == CAPSULE:
+        p[:, 0] = rng.uniform(0.02, 0.2, n); p[:, 1] = rng.uniform(0.05, 0.5, n); p[:, 2] = p[:, 0]
+    elif kind == BOX:
+        p[:, :3] = rng.uniform(0.02, 0.4, (n, 3))
+        cube = rng.random(n) < 0.2
+        p[cube, 1] = p[cube, 0]; p[cube, 2] = p[cube, 0]
+    return p
+
+
+def manifold_cases(ka, kb, n, seed):
+    """n cases of one pair kind: frames (n x 12 each), params (n x 4 each), query radius (n).  The second shape sits
+    within touching range of the first, so about half the cases are in contact; a share has axis-aligned orientations
+    (box face ties, parallel capsule axes), coincident centres or equal poses on one axis."""
+    rng = np.random.default_rng([seed, ka, kb])
+    pa, pb = _params(rng, ka, n), _params(rng, kb, n)
+    qa, qb = _unit_quats(rng, n, 0.25), _unit_quats(rng, n, 0.25)
+    same = rng.random(n) < 0.15
+    qb[same] = qa[same]                                   # parallel axes / aligned faces
+    near = rng.random(n) < 0.1
+    qb[near] = qa[near] + rng.normal(scale=1e-4, size=(near.sum(), 4))
+    qb /= np.linalg.norm(qb, axis=1, keepdims=True)
+    reach = np.maximum(pa[:, :3].max(1) + pa[:, 1], 0.05) + np.maximum(pb[:, :3].max(1) + pb[:, 1], 0.05)
+    ta = rng.uniform(-1, 1, (n, 3))
+    direction = rng.normal(size=(n, 3))
+    direction /= np.linalg.norm(direction, axis=1, keepdims=True)
+    axis_dir = rng.random(n) < 0.2
+    direction[axis_dir] = np.eye(3)[rng.integers(0, 3, axis_dir.sum())]
+    spread = 4.0 if PLANE in (ka, kb) else 1.3          # a plane is a half-space: everything below it touches
+    tb = ta + direction * (reach * rng.uniform(0.0, spread, n))[:, None]
+    coincide = rng.random(n) < 0.03
+    tb[coincide] = ta[coincide]
+    if kb == PLANE:
+        qb[rng.random(n) < 0.5] = (1, 0, 0, 0)
+    if ka == PLANE:
+        qa[rng.random(n) < 0.5] = (1, 0, 0, 0)
+    query = np.where(rng.random(n) < 0.3, 0.0, rng.uniform(0.0, 0.05, n)).astype(np.float32)
+    return _frames(qa, ta), pa, _frames(qb, tb), pb, query
+
+
+def run_manifolds(fn, ka, kb, cases):
+    """Evaluates one binding (`orc_manifold_frames` or `ref_manifold_frames`) on the cases: counts, points, keys."""
+    fa, pa, fb, pb, query = cases
+    n = len(query)
+    counts = np.zeros(n, np.int32)
+    points = np.zeros((n, 4, 7), np.float32)
+    keys = np.zeros((n, 4), np.uint64)
+    for i in range(n):
+        counts[i] = fn(ka, fa[i].ctypes.data, pa[i].ctypes.data, kb, fb[i].ctypes.data, pb[i].ctypes.data, float(query[i]),
+                       points[i].ctypes.data, keys[i].ctypes.data)
+    return counts, points, keys
+
+
+LAWS = {0: (6, 2), 1: (4, 1), 2: (8, 5), 3: (12, 1), 4: (13, 4)}      # which -> (floats in, floats out)
+
+
+def law_cases(which, n, seed):
+    rng = np.random.default_rng([seed, 100 + which])
+    sign = lambda k: rng.choice([-1.0, 1.0], k)
+    mag = lambda k, lo, hi: 10.0 ** rng.uniform(lo, hi, k)
+    if which == 0:      # dual rho residual compliance lower upper
+        x = np.stack([sign(n) * mag(n, -4, 1), mag(n, -1, 4), sign(n) * mag(n, -6, 0), np.where(rng.random(n) < 0.5, 0.0, mag(n, -8, 0)),
+                      np.zeros(n), np.zeros(n)], 1)
+        kind = rng.integers(0, 4, n)
+        x[:, 4] = np.select([kind == 0, kind == 1, kind == 2], [0.0, -np.inf, -mag(n, -3, 1)], -3.4028234663852886e38)
+        x[:, 5] = np.select([kind == 0, kind == 1, kind == 2], [3.4028234663852886e38, 0.0, 0.0], 3.4028234663852886e38)
+        x[kind == 2, 5] = -x[kind == 2, 4]
+        x[rng.random(n) < 0.05, 0] = 0.0
+    elif which == 1:    # dual rho mu residual
+        x = np.stack([sign(n) * mag(n, -5, 1), mag(n, -1, 4), mag(n, -5, 0), sign(n) * mag(n, -7, 0)], 1)
+        x[rng.random(n) < 0.1, 0] = 0.0
+        x[rng.random(n) < 0.1, 2] = 1.0
+    elif which == 2:    # dual_y dual_z rho res_y res_z normal mu1 mu2
+        mu = mag(n, -5, 0.3)
+        x = np.stack([sign(n) * mag(n, -5, 0), sign(n) * mag(n, -5, 0), mag(n, -1, 4), sign(n) * mag(n, -7, -1), sign(n) * mag(n, -7, -1),
+                      mag(n, -4, 1), mu, mu], 1)
+        other = rng.random(n) < 0.3
+        x[other, 7] = mag(other.sum(), -5, 0.3)
+        x[rng.random(n) < 0.1, 5] = 0.0                  # zero normal impulse: the cone collapses
+        x[rng.random(n) < 0.05, 5] *= -1.0
+        zero = rng.random(n) < 0.1
+        x[zero, 0] = 0.0; x[zero, 1] = 0.0
+    elif which == 3:    # point next base scale
+        x = rng.normal(size=(n, 12))
+        x[:, 9:] = np.where(rng.random((n, 3)) < 0.2, 0.0, mag(3 * n, -3, 2).reshape(n, 3))
+    else:               # dual next last.step last.weight last.point
+        x = rng.normal(size=(n, 13))
+        x[:, 9] = np.where(rng.random(n) < 0.3, 0.0, rng.uniform(0.05, 1.0, n))
+        again = rng.random(n) < 0.1
+        x[again, 6:9] = x[again, 3:6] - x[again, 0:3]     # unchanged step: zero secant denominator
+    return np.ascontiguousarray(x, dtype=np.float32)
+
+
+def run_laws(fn, which, x):
+    n_in, n_out = LAWS[which]
+    out = np.zeros((len(x), n_out), np.float32)
+    fn(which, len(x), x.ctypes.data, n_in, out.ctypes.data, n_out)
+    return out
