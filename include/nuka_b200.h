@@ -166,8 +166,7 @@ typedef enum nuka_state_field_t {
     NUKA_B200_FIELD_CONTACT_NORMAL = 0x10006,       /* E x S x 4 x 3 f32 */
     NUKA_B200_FIELD_CONTACT_DEPTH = 0x10007,        /* E x S x 4 f32 */
     NUKA_B200_FIELD_SOLVER_SWEEPS = 0x10008,        /* E u32 */
-    NUKA_B200_FIELD_JOINT_PSEUDO_VELOCITY = 0x10009, /* E x n f32 */
-    NUKA_B200_FIELD_STAGE_CYCLES = 0x1000A /* E x 32 u32: SM cycles per pipeline stage, summed since first requested */
+    NUKA_B200_FIELD_JOINT_PSEUDO_VELOCITY = 0x10009 /* E x n f32 */
 } nuka_state_field_t;
 
 /* nuka.h:1158-1166 */
@@ -189,9 +188,14 @@ nuka_result_t nuka_world_download_field(nuka_world_handle world, nuka_state_fiel
 nuka_result_t nuka_world_create_from_template(nuka_device_handle device, const nuka_world_desc_t* desc,
                                               const void* template_bytes, size_t template_size, nuka_world_handle* out);
 
+/* Parses a cooked template as world creation would and reports the same result code (OK, PARSE_ERROR for a malformed
+ * or truncated container, NOT_SUPPORTED / INVALID_ARG for a model outside this path's limits), without a device. */
+nuka_result_t nuka_b200_template_check(const void* template_bytes, size_t template_size);
+
 typedef struct nuka_b200_world_info_t {
     uint32_t env_count, links_per_env, bodies_per_env, dofs_per_env, contact_slots_per_env;
     uint32_t shared_bytes_per_env, warps_per_block;
+    float fixed_dt;                 /* the step the world integrates with (desc->fixed_dt, else the template's) */
 } nuka_b200_world_info_t;
 nuka_result_t nuka_b200_world_info(nuka_world_handle world, nuka_b200_world_info_t* out);
 
@@ -202,12 +206,50 @@ nuka_result_t nuka_b200_world_run_stage(nuka_world_handle world, uint32_t stage)
 /* Kernel launches enqueued by this world since creation (for throughput reports). */
 nuka_result_t nuka_b200_world_launch_count(nuka_world_handle world, uint64_t* out);
 
-/* Packs one observation record per env into caller-owned device memory on the world's stream, for RL callers that
- * exchange observations between shards: joint positions (L-1), joint velocities (L-1), base pose (7), root twist (6),
- * drive targets of all joints but the last (L-2), base height as reward; 3 (L-1) + 13 floats per env (49 for the
- * quadruped), the quantities python/nuka/tasks/go2_obs.py:47-48 composes.  device_out == NULL only reports the
- * width.  NUKA_ERR_NOT_SUPPORTED for worlds without a floating-base articulation. */
-nuka_result_t nuka_b200_world_pack_observations(nuka_world_handle world, float* device_out, size_t capacity_floats, uint32_t* out_width);
+/* The observation record of the reference's gym layer, python/nuka/tasks/go2_obs.py:11-20 and :282-305
+ * (Go2ObsBuilder.compute_obs), composed by one kernel on the world's stream instead of a chain of tensor ops.  For a
+ * floating-base robot with nj = L - 1 actuated joints a record holds, in order:
+ *     base linear velocity (base frame) x lin_vel_scale      3      (reference scale 2.0)
+ *     base angular velocity (base frame) x ang_vel_scale     3      (0.25)
+ *     world (0, 0, -1) rotated into the base frame           3
+ *     command x command_scale                                3      ((2.0, 2.0, 0.25))
+ *     (q - default_position) x dof_pos_scale                 nj     (1.0), joints in the caller's order
+ *     qdot x dof_vel_scale                                   nj     (0.05), joints in the caller's order
+ *     last_action                                            nj
+ * every value clipped to [-clip, clip] (100), i.e. 12 + 3 nj floats: 48 for a 12-joint quadruped.  With `reward`
+ * non-null its value follows the record unclipped, for callers that exchange observation + reward in one buffer.
+ * All pointers are device memory read on the world's stream.  Zero-initialise the struct and call
+ * nuka_b200_observation_desc_defaults for the reference's scales. */
+typedef struct nuka_b200_observation_desc_t {
+    const float* command;            /* E x 3, or 3 floats for every env when command_stride is 0 */
+    uint32_t command_stride;         /* floats between consecutive envs' commands: 0 or >= 3 */
+    const float* last_action;        /* E x nj, NULL = zeros */
+    const float* default_position;   /* nj in the caller's joint order, NULL = zeros */
+    const uint32_t* joint_order;     /* nj: library joint slot (0-based; slot j is link j + 1) read for the caller's joint i; NULL = identity.
+                                        The reference's table of the same meaning is urdf_from_nuka_slot, go2_obs.py:252-262 */
+    const float* reward;             /* E, NULL = no reward column */
+    float lin_vel_scale, ang_vel_scale, dof_pos_scale, dof_vel_scale;
+    float command_scale[3];
+    float clip;
+    uint32_t row_stride;             /* floats between consecutive records in device_out; 0 = the record width */
+} nuka_b200_observation_desc_t;
+void nuka_b200_observation_desc_defaults(nuka_b200_observation_desc_t* desc);
+/* Writes E records into device_out (caller-owned device memory, e.g. this rank's slice of a gather buffer).
+ * device_out == NULL only reports the record width (without the reward column) in *out_width.
+ * NUKA_ERR_NOT_SUPPORTED for worlds without a floating-base articulation, INVALID_ARG for a null command, a stride
+ * below the record width or a buffer that is too small. */
+nuka_result_t nuka_b200_world_pack_observations(nuka_world_handle world, const nuka_b200_observation_desc_t* desc,
+                                                float* device_out, size_t capacity_floats, uint32_t* out_width);
+
+/* nuka_world_reset_envs (nuka.h:380-385) with the env set chosen on the device: resets every env whose word in
+ * device_mask (E x u32 device memory, read on the world's stream) is non-zero and recomputes their derived poses.
+ * Nothing crosses to the host and nothing synchronises, so an episode loop can chain step, termination test and
+ * reset on one stream (the reference's gym layer downloads the done ids first, python/nuka/gym/env.py autoreset). */
+nuka_result_t nuka_b200_world_reset_envs_masked(nuka_world_handle world, const uint32_t* device_mask);
+
+/* Switches the per-step contact read-out arrays (PAIR_COUNT ... CONTACT_DEPTH below) on (non-zero, the default) or
+ * off.  While off the step skips those stores and the arrays keep their last contents. */
+nuka_result_t nuka_b200_world_set_contact_readout(nuka_world_handle world, uint32_t enabled);
 
 /* No counterpart in the reference.  nuka_world_reset_envs without any allocation: same validation, set semantics and
  * resulting state, but the env-id list goes through a fixed 16 KB device array built into the library instead of a

@@ -7,6 +7,7 @@
 #include <fstream>
 #include <mutex>
 #include <sstream>
+#include <unordered_map>
 
 #include "../../include/nuka_b200.h"
 #include "nkb_world.h"
@@ -25,35 +26,40 @@ struct DeviceRecord {
     uint32_t worlds = 0;
 };
 
+// Handles are ids that count up and are never handed out twice: a handle kept after its object was destroyed stays
+// unknown for good, whatever is created later (reference src/c_abi/handle_table.hpp:18-26).
 template <typename T>
 class HandleTable {
 public:
     uintptr_t Insert(std::unique_ptr<T> value) {
         std::lock_guard<std::mutex> lock(mutex_);
-        for (size_t i = 0; i < slots_.size(); ++i)
-            if (!slots_[i]) { slots_[i] = std::move(value); return i + 1; }
-        slots_.push_back(std::move(value));
-        return slots_.size();
+        const uintptr_t id = next_id_++;
+        values_.emplace(id, std::move(value));
+        return id;
     }
     T* Get(uintptr_t handle) {
         std::lock_guard<std::mutex> lock(mutex_);
-        if (handle == 0 || handle > slots_.size()) return nullptr;
-        return slots_[handle - 1].get();
+        const auto it = values_.find(handle);
+        return it == values_.end() ? nullptr : it->second.get();
     }
     std::unique_ptr<T> Remove(uintptr_t handle) {
         std::lock_guard<std::mutex> lock(mutex_);
-        if (handle == 0 || handle > slots_.size()) return nullptr;
-        return std::move(slots_[handle - 1]);
+        const auto it = values_.find(handle);
+        if (it == values_.end()) return nullptr;
+        std::unique_ptr<T> value = std::move(it->second);
+        values_.erase(it);
+        return value;
     }
 private:
     std::mutex mutex_;
-    std::vector<std::unique_ptr<T>> slots_;
+    uintptr_t next_id_ = 1;
+    std::unordered_map<uintptr_t, std::unique_ptr<T>> values_;
 };
 
 struct WorldRecord {
     std::unique_ptr<nkb::World> world;
     uintptr_t device = 0;
-    uint64_t serial = 0;        // distinguishes worlds that reuse a handle slot
+    uint64_t serial = 0;        // creation order; a checkpoint remembers its owner's
 };
 
 // Host copy of a world's persistent state and settings (reference src/c_abi/checkpoint.cpp:442-520).
@@ -119,6 +125,7 @@ nuka_result_t ValidateDesc(const nuka_world_desc_t* d) {
         d->solver_substeps > 1u || d->contact_detection_substeps > 1u || d->osc_task_link != 0u;
     if (unsupported) { SetError("the world desc selects a feature outside the articulated step path"); return NUKA_RESULT_NOT_SUPPORTED; }
     if (d->solver_vel_iters > 65535u) { SetError("solver_vel_iters exceeds 65535"); return NUKA_RESULT_INVALID_ARG; }
+    if (d->solver_pos_iters > 65535u) { SetError("solver_pos_iters exceeds 65535"); return NUKA_RESULT_INVALID_ARG; }
     return NUKA_RESULT_OK;
 }
 
@@ -214,6 +221,11 @@ nuka_result_t nuka_world_create_from_template(nuka_device_handle device, const n
                                               const void* template_bytes, size_t template_size, nuka_world_handle* out) {
     if (template_bytes == nullptr || template_size == 0) { SetError("template bytes are null"); return NUKA_RESULT_INVALID_ARG; }
     return CreateWorld(device, desc, template_bytes, template_size, out);
+}
+
+nuka_result_t nuka_b200_template_check(const void* template_bytes, size_t template_size) {
+    if (template_bytes == nullptr || template_size == 0) { SetError("template bytes are null"); return NUKA_RESULT_INVALID_ARG; }
+    return Guard([&]() { (void)nkb::HostTemplate::Parse(template_bytes, template_size); return NUKA_RESULT_OK; });
 }
 
 nuka_result_t nuka_world_create_from_scene(nuka_device_handle device, const nuka_world_desc_t* desc, nuka_world_handle* out) {
@@ -472,13 +484,16 @@ nuka_result_t nuka_world_get_buffer_view(nuka_world_handle world, nuka_state_fie
     });
 }
 
+// Argument checks in the reference's order (src/c_abi/buffer.cpp:98-110): a null buffer with a size first, then the
+// handle, then the empty transfer.
 static nuka_result_t Transfer(nuka_world_handle world, nuka_state_field_t field, void* bytes, size_t nbytes, size_t offset, bool upload) {
+    if (bytes == nullptr && nbytes > 0u) { SetError("bytes is null"); return NUKA_RESULT_INVALID_ARG; }
     NKB_WORLD(w)
     if (nbytes == 0u) return NUKA_RESULT_OK;
-    if (bytes == nullptr) { SetError("bytes is null"); return NUKA_RESULT_INVALID_ARG; }
     return Guard([&]() {
         nkb::FieldInfo info;
         if (!w->Field(static_cast<uint32_t>(field), &info)) { SetError("field is not served by this path"); return NUKA_RESULT_NOT_SUPPORTED; }
+        if (upload && !info.writable) { SetError("field is an output of the step and cannot be uploaded"); return NUKA_RESULT_NOT_SUPPORTED; }
         const size_t total = info.per_env * w->env_count() * 4u;
         if (offset > total || nbytes > total - offset) { SetError("transfer exceeds the field"); return NUKA_RESULT_INVALID_ARG; }
         if (cudaSetDevice(w->device()) != cudaSuccess) { SetError("cudaSetDevice failed"); return NUKA_RESULT_CUDA_ERROR; }
@@ -508,6 +523,7 @@ nuka_result_t nuka_b200_world_info(nuka_world_handle world, nuka_b200_world_info
     out->links_per_env = w->tpl().L; out->bodies_per_env = w->tpl().B; out->dofs_per_env = w->tpl().ndof;
     out->contact_slots_per_env = w->tpl().cfg.max_contacts;
     out->shared_bytes_per_env = w->shared_bytes_per_env(); out->warps_per_block = w->warps_per_block();
+    out->fixed_dt = w->tpl().cfg.dt;
     return NUKA_RESULT_OK;
 }
 
@@ -517,13 +533,48 @@ nuka_result_t nuka_b200_world_run_stage(nuka_world_handle world, uint32_t stage)
     return Guard([&]() { w->RunStage(stage); return NUKA_RESULT_OK; });
 }
 
-nuka_result_t nuka_b200_world_pack_observations(nuka_world_handle world, float* device_out, size_t capacity_floats, uint32_t* out_width) {
+void nuka_b200_observation_desc_defaults(nuka_b200_observation_desc_t* d) {
+    if (d == nullptr) return;
+    // python/nuka/tasks/go2_obs.py:56-66
+    d->lin_vel_scale = 2.0f; d->ang_vel_scale = 0.25f; d->dof_pos_scale = 1.0f; d->dof_vel_scale = 0.05f;
+    d->command_scale[0] = 2.0f; d->command_scale[1] = 2.0f; d->command_scale[2] = 0.25f;
+    d->clip = 100.0f;
+}
+
+nuka_result_t nuka_b200_world_pack_observations(nuka_world_handle world, const nuka_b200_observation_desc_t* desc,
+                                                float* device_out, size_t capacity_floats, uint32_t* out_width) {
     NKB_WORLD(w)
     const uint32_t width = w->ObservationWidth();
     if (out_width != nullptr) *out_width = width;
     if (device_out == nullptr) return NUKA_RESULT_OK;          // width query only
-    if (capacity_floats < static_cast<size_t>(width) * w->env_count()) { SetError("observation buffer is too small"); return NUKA_RESULT_INVALID_ARG; }
-    return Guard([&]() { w->PackObservations(device_out); return NUKA_RESULT_OK; });
+    if (width == 0u) { SetError("the world has no actuated joints to observe"); return NUKA_RESULT_NOT_SUPPORTED; }
+    if (desc == nullptr || desc->command == nullptr) { SetError("observation desc or its command pointer is null"); return NUKA_RESULT_INVALID_ARG; }
+    if (desc->command_stride != 0u && desc->command_stride < 3u) { SetError("command_stride must be 0 or at least 3"); return NUKA_RESULT_INVALID_ARG; }
+    const uint32_t record = width + (desc->reward != nullptr ? 1u : 0u);
+    const uint32_t stride = desc->row_stride != 0u ? desc->row_stride : record;
+    if (stride < record) { SetError("row_stride is below the record width"); return NUKA_RESULT_INVALID_ARG; }
+    const size_t need = static_cast<size_t>(stride) * (w->env_count() - 1u) + record;
+    if (capacity_floats < need) { SetError("observation buffer is too small"); return NUKA_RESULT_INVALID_ARG; }
+    if (!(desc->clip >= 0.f)) { SetError("clip must not be negative"); return NUKA_RESULT_INVALID_ARG; }
+    nkb::ObservationParams o{};
+    o.command = desc->command; o.command_stride = desc->command_stride; o.last_action = desc->last_action;
+    o.default_position = desc->default_position; o.joint_order = desc->joint_order; o.reward = desc->reward;
+    o.lin_vel_scale = desc->lin_vel_scale; o.ang_vel_scale = desc->ang_vel_scale; o.dof_pos_scale = desc->dof_pos_scale;
+    o.dof_vel_scale = desc->dof_vel_scale;
+    for (int k = 0; k < 3; ++k) o.command_scale[k] = desc->command_scale[k];
+    o.clip = desc->clip; o.row_stride = stride;
+    return Guard([&]() { w->PackObservations(o, device_out); return NUKA_RESULT_OK; });
+}
+
+nuka_result_t nuka_b200_world_reset_envs_masked(nuka_world_handle world, const uint32_t* device_mask) {
+    NKB_WORLD(w)
+    if (device_mask == nullptr) { SetError("device_mask is null"); return NUKA_RESULT_INVALID_ARG; }
+    return Guard([&]() { w->ResetMasked(device_mask); return NUKA_RESULT_OK; });
+}
+
+nuka_result_t nuka_b200_world_set_contact_readout(nuka_world_handle world, uint32_t enabled) {
+    NKB_WORLD(w)
+    return Guard([&]() { w->SetContactReadout(enabled != 0u); return NUKA_RESULT_OK; });
 }
 
 nuka_result_t nuka_b200_world_launch_count(nuka_world_handle world, uint64_t* out) {

@@ -28,17 +28,26 @@ struct Env {
     float vel0[2];           // step-start coordinate velocity
     uint32_t status;
     uint32_t vstride;        // words per shared-memory vector: 32 x coordinates per lane
+#ifdef NKB_STAGE_TAPS
     uint32_t* cyc;           // stage cycle counters of this env, or null
     long long t0;
+#endif
 };
 
-// Adds the cycles since the last tick to stage counter k (profiling tap, off unless requested).
+// Stage cycle counters are a build-time instrument (-DNKB_STAGE_TAPS); the shipped kernel carries none of it.
+#ifdef NKB_STAGE_TAPS
+// Adds the cycles since the last tick to stage counter k.
 NKB_DEV void tick(Env& e, int k) {
     if (e.cyc == nullptr) return;
     const long long now = clock64();
     if (e.lane == 0u) e.cyc[k] += (uint32_t)(now - e.t0);
     e.t0 = now;
 }
+NKB_DEV void tick_count(Env& e, int k) { if (e.cyc != nullptr && e.lane == 0u) e.cyc[k] += 1u; }
+#else
+NKB_DEV void tick(Env&, int) {}
+NKB_DEV void tick_count(Env&, int) {}
+#endif
 
 NKB_DEV float* sm_pose(const Env& e, uint32_t l) { return e.sm + e.lay->pose + 7u * l; }
 NKB_DEV float* sm_xrot(const Env& e, uint32_t l) { return e.sm + e.lay->xrot + 9u * l; }
@@ -97,8 +106,10 @@ NKB_DEV void env_begin(Env& e, const StepParams& p, float* sm, uint32_t env, uin
         e.vel0[r] = 0.f;
     }
     e.status = 0u;
+#ifdef NKB_STAGE_TAPS
     e.cyc = p.s.dbg_cycles != nullptr ? p.s.dbg_cycles + (size_t)env * 32u : nullptr;
     e.t0 = clock64();
+#endif
 }
 
 // World poses of every link, ops/articulation.cu:1561-1596 with kinematics.cuh:25-42 joint frames.

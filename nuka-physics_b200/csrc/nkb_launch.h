@@ -18,6 +18,7 @@ constexpr uint32_t kMaxResetFields = 24u;
 struct ResetParams {
     uint32_t env_count;
     const uint32_t* env_ids;   // device list of envs to reset, or null for all
+    const uint32_t* env_mask;  // device array of env_count words; with env_ids null, only envs with a non-zero word reset
     uint32_t field_count;
     ResetField fields[kMaxResetFields];
 };
@@ -40,11 +41,29 @@ struct StepVariant {
 cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream);
 // Restores `count` envs (all when r.env_ids is null) from their snapshots.
 cudaError_t launch_reset(const ResetParams& r, uint32_t count, cudaStream_t stream);
-// Packs the per-env observation record (3 (L - 1) + 13 floats) of every env into `out` (device memory).
-cudaError_t launch_pack_observations(const StateView& s, uint32_t L, float* out, cudaStream_t stream);
+// Observation record of the reference's gym layer (python/nuka/tasks/go2_obs.py:11-20) for a floating-base robot with
+// nj = L - 1 actuated joints: base linear velocity x lin_scale (3), base angular velocity x ang_scale (3), gravity
+// direction in the base frame (3), command x command_scale (3), (q - default) x pos_scale in caller joint order (nj),
+// qdot x vel_scale in caller joint order (nj), last action (nj); every value clipped to [-clip, clip].  An optional
+// reward column follows.  All pointers are device memory.
+struct ObservationParams {
+    const float* command;           // E x 3, or 3 floats shared by every env when command_stride == 0
+    uint32_t command_stride;        // floats between the commands of consecutive envs (0 or >= 3)
+    const float* last_action;       // E x nj, or null for zeros
+    const float* default_position;  // nj, caller joint order; null for zeros
+    const uint32_t* joint_order;    // nj: library joint slot (0-based, slot j is link j + 1) read for caller joint i; null = identity
+    const float* reward;            // E, copied into column 9 + 3 + 3 nj when non-null
+    float lin_vel_scale, ang_vel_scale, dof_pos_scale, dof_vel_scale;
+    float command_scale[3];
+    float clip;
+    uint32_t row_stride;            // floats between consecutive records in the output (>= the record width)
+};
+cudaError_t launch_pack_observations(const StateView& s, uint32_t L, const ObservationParams& o, float* out, cudaStream_t stream);
 // Partial reset without a device allocation: the ids travel through a fixed device array of kStaticResetMaxIds words
 // that every world on `device` shares.  `device` must be current; r.env_ids is ignored.
 constexpr uint32_t kStaticResetMaxIds = 4096u;
-cudaError_t launch_reset_static_ids(const ResetParams& r, const uint32_t* host_ids, uint32_t count, int device, cudaStream_t stream);
+// On success *device_ids is the array's address on `device` (the ids stay there until the next call).
+cudaError_t launch_reset_static_ids(const ResetParams& r, const uint32_t* host_ids, uint32_t count, int device, cudaStream_t stream,
+                                    const uint32_t** device_ids);
 
 }  // namespace nkb

@@ -826,7 +826,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
         tick(e, 21);
         const float alpha = search_line(e, tile, b, islope, icurv);
         tick(e, 22);
-        if (e.cyc != nullptr && l == 0u) e.cyc[23] += 1u;
+        tick_count(e, 23);
         if (step < 0) {
             if (alpha > 0.f) {
 #pragma unroll
@@ -1210,7 +1210,7 @@ NKB_DEV void stage_solve(Env& e, uint32_t nheads) {
             if (stage == 0) run = sweeps == iterations || fmaxf(worst_row, tile.residual) < tile.tol;
             else if (stage == 1) run = worst_row < tile.tol && tile.residual >= tile.tol && tile.residual < FLT_MAX;
             if (stage == 1 && !run) break;
-            if (run) { measure_primals<NR, kRigid>(e, tile, stage == 1); tick(e, 25); if (e.cyc != nullptr && l == 0u) e.cyc[27] += 1u; }
+            if (run) { measure_primals<NR, kRigid>(e, tile, stage == 1); tick(e, 25); tick_count(e, 27); }
             if (stage == 1) {
                 if (!(tile.residual < FLT_MAX)) break;
                 init_residuals(e, tile);

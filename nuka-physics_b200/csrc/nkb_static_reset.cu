@@ -43,7 +43,9 @@ static cudaError_t static_reset_ids(int device, uint32_t** out) {
     return cudaSuccess;
 }
 
-cudaError_t launch_reset_static_ids(const ResetParams& r, const uint32_t* host_ids, uint32_t count, int device, cudaStream_t stream) {
+cudaError_t launch_reset_static_ids(const ResetParams& r, const uint32_t* host_ids, uint32_t count, int device, cudaStream_t stream,
+                                    const uint32_t** device_ids) {
+    *device_ids = nullptr;
     if (count == 0u) return cudaSuccess;
     if (count > kStaticResetMaxIds) return cudaErrorInvalidValue;
     uint32_t* ids = nullptr;
@@ -52,6 +54,7 @@ cudaError_t launch_reset_static_ids(const ResetParams& r, const uint32_t* host_i
     err = cudaMemcpyAsync(ids, host_ids, (size_t)count * sizeof(uint32_t), cudaMemcpyHostToDevice, stream);
     if (err != cudaSuccess) return err;
     reset_kernel_static_ids<<<count, 128, 0, stream>>>(r, ids);
+    *device_ids = ids;
     return cudaGetLastError();
 }
 

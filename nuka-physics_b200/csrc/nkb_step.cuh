@@ -6,6 +6,7 @@
 // variants build in parallel; NKB_STEP_VARIANT defines the host-side handle of one.
 #pragma once
 #include <cuda_runtime.h>
+#include <mutex>
 #include "nkb_solver.cuh"
 #include "nkb_launch.h"
 
@@ -132,8 +133,10 @@ template <int NR, bool kRigid>
 __global__ void __maxnreg__(176) step_kernel(const __grid_constant__ StepParams p) {
     extern __shared__ __align__(16) float smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t env = blockIdx.x * (blockDim.x >> 5) + warp;
+    uint32_t env = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (p.sel_ids != nullptr) env = env < p.sel_count ? p.sel_ids[env] : 0xffffffffu;
     if (env >= p.s.env_count) return;
+    if (p.sel_mask != nullptr && p.sel_mask[env] == 0u) return;
     float* sm = smem + (size_t)warp * p.sm.words;
     const TemplateView& t = p.t;
     const bool has_artic = t.L != 0u, has_bodies = t.B != 0u;
@@ -216,9 +219,28 @@ __global__ void __maxnreg__(176) step_kernel(const __grid_constant__ StepParams 
     }
 }
 
+// Raises the kernel's dynamic shared-memory limit to `bytes` if it is not there yet.  The limit is per function and
+// per device and only ever grows, so worlds of different sizes stepped from different threads cannot undo each other's
+// setting between the attribute call and the launch.
+template <int NR, bool kRigid>
+static cudaError_t variant_reserve_shared(size_t bytes) {
+    static std::mutex lock;
+    static size_t reserved[64] = {0};
+    if (bytes <= 48u * 1024u) return cudaSuccess;
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) return err;
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> hold(lock);
+    if (bytes <= reserved[device]) return cudaSuccess;
+    err = cudaFuncSetAttribute(step_kernel<NR, kRigid>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (err == cudaSuccess) reserved[device] = bytes;
+    return err;
+}
+
 template <int NR, bool kRigid>
 static int variant_resident_blocks(uint32_t warps_per_block, size_t shared_bytes) {
-    if (shared_bytes > 48u * 1024u && cudaFuncSetAttribute(step_kernel<NR, kRigid>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared_bytes) != cudaSuccess) {
+    if (variant_reserve_shared<NR, kRigid>(shared_bytes) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
@@ -240,11 +262,11 @@ static int variant_registers() {
 template <int NR, bool kRigid>
 static cudaError_t variant_launch(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
     const size_t bytes = (size_t)warps_per_block * p.sm.words * sizeof(float);
-    if (bytes > 48u * 1024u) {
-        const cudaError_t err = cudaFuncSetAttribute(step_kernel<NR, kRigid>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-        if (err != cudaSuccess) return err;
-    }
-    const uint32_t blocks = (p.s.env_count + warps_per_block - 1u) / warps_per_block;
+    const cudaError_t err = variant_reserve_shared<NR, kRigid>(bytes);
+    if (err != cudaSuccess) return err;
+    const uint32_t warps = p.sel_ids != nullptr ? p.sel_count : p.s.env_count;
+    if (warps == 0u) return cudaSuccess;
+    const uint32_t blocks = (warps + warps_per_block - 1u) / warps_per_block;
     step_kernel<NR, kRigid><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
     return cudaGetLastError();
 }

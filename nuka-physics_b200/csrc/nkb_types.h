@@ -117,6 +117,11 @@ struct StepParams {
     SmemLayout sm;
     uint32_t mode;
     uint32_t steps;
+    // Env selection of a refresh launch (null: every env).  sel_ids lists sel_count envs, one warp each; sel_mask is
+    // an E-word device array whose non-zero entries pick the envs of a full-size launch.
+    const uint32_t* sel_ids;
+    uint32_t sel_count;
+    const uint32_t* sel_mask;
 };
 
 }  // namespace nkb

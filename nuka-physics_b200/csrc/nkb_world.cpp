@@ -10,6 +10,7 @@ namespace nkb {
 
 namespace {
 
+constexpr uint32_t kMaxStepsPerLaunch = 64u;
 constexpr int kOk = 0, kInvalidArg = 1, kCudaError = 3, kParseError = 5, kOutOfMemory = 6, kNotSupported = 7;
 
 struct BlobEntry { uint32_t dtype; uint64_t n; const uint8_t* data; };
@@ -24,19 +25,49 @@ bool BlobFind(const uint8_t* blob, size_t bytes, const char* name, BlobEntry* ou
         uint32_t dtype; uint64_t n;
         std::memcpy(&dtype, blob + at + 32, 4);
         std::memcpy(&n, blob + at + 40, 8);
+        if (dtype > 3u || n > (uint64_t{1} << 40)) return false;
         const size_t esz = dtype == 3u ? 8u : 4u;
         const size_t payload = static_cast<size_t>((n * esz + 7u) & ~uint64_t{7});
-        if (at + 48 + payload > bytes) return false;
+        if (payload > bytes - at - 48) return false;
         if (std::strncmp(reinterpret_cast<const char*>(blob + at), name, 32) == 0) { *out = {dtype, n, blob + at + 48}; return true; }
         at += 48 + payload;
     }
     return false;
 }
 
+// dtype code of a record (0 f32, 1 u32, 2 i32, 3 u64) that a vector of T may be filled from
+// Walks every record header once: a container whose directory does not fit its byte count is rejected as a whole, so
+// a cut-off optional record cannot pass for an absent one.
+void BlobValidate(const uint8_t* blob, size_t bytes) {
+    uint32_t count;
+    std::memcpy(&count, blob + 4, 4);
+    size_t at = 8;
+    for (uint32_t i = 0; i < count; ++i) {
+        if (bytes < 48 || at > bytes - 48) throw Error(kParseError, "template container is truncated");
+        uint32_t dtype; uint64_t n;
+        std::memcpy(&dtype, blob + at + 32, 4);
+        std::memcpy(&n, blob + at + 40, 8);
+        if (dtype > 3u) throw Error(kParseError, "template record has an unknown dtype");
+        if (n > (uint64_t{1} << 40)) throw Error(kParseError, "template record count exceeds the container");
+        const size_t payload = static_cast<size_t>((n * (dtype == 3u ? 8u : 4u) + 7u) & ~uint64_t{7});
+        if (payload > bytes - at - 48) throw Error(kParseError, "template record exceeds the container");
+        at += 48 + payload;
+    }
+}
+
+template <typename T> constexpr uint32_t DtypeOf();
+template <> constexpr uint32_t DtypeOf<float>() { return 0u; }
+template <> constexpr uint32_t DtypeOf<uint32_t>() { return 1u; }
+template <> constexpr uint32_t DtypeOf<int32_t>() { return 2u; }
+template <> constexpr uint32_t DtypeOf<unsigned long long>() { return 3u; }
+
+// The blob is untrusted: a record is only copied when its dtype is the one the field is read as, so the byte count
+// BlobFind bounds-checked (n x the dtype's element size) is the byte count copied.
 template <typename T>
 std::vector<T> BlobVec(const uint8_t* blob, size_t bytes, const char* name, uint64_t expect) {
     BlobEntry e;
-    if (!BlobFind(blob, bytes, name, &e)) throw Error(kParseError, std::string("template field missing: ") + name);
+    if (!BlobFind(blob, bytes, name, &e)) throw Error(kParseError, std::string("template field missing or truncated: ") + name);
+    if (e.dtype != DtypeOf<T>()) throw Error(kParseError, std::string("template field has the wrong dtype: ") + name);
     if (e.n != expect) throw Error(kParseError, std::string("template field has the wrong size: ") + name);
     std::vector<T> v(static_cast<size_t>(e.n));
     if (e.n) std::memcpy(v.data(), e.data, static_cast<size_t>(e.n) * sizeof(T));
@@ -57,6 +88,7 @@ bool FilterAdmits(uint32_t ta, uint32_t aa, uint32_t ga_, uint32_t tb, uint32_t 
 HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
     const auto* blob = static_cast<const uint8_t*>(blob_in);
     if (blob == nullptr || bytes < 8 || std::memcmp(blob, "NKT1", 4) != 0) throw Error(kParseError, "not a cooked template (NKT1) blob");
+    BlobValidate(blob, bytes);
     HostTemplate t;
     const auto cf = BlobVec<float>(blob, bytes, "cfg_f", 10);
     const auto cu = BlobVec<uint32_t>(blob, bytes, "cfg_u", 6);
@@ -65,6 +97,8 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
     t.cfg.baumgarte_max_velocity = cf[7]; t.cfg.overlap_recovery_velocity = cf[8]; t.cfg.velocity_tolerance = cf[9];
     t.cfg.vel_iters = cu[0]; t.cfg.pos_iters = cu[1]; t.cfg.max_contacts = cu[2]; t.cfg.max_pairs = cu[3];
     t.cfg.control_mode = 0u;       // the world descriptor selects another mode
+    // sweep counts bound the length of one kernel launch, which cannot be cancelled once it runs
+    if (t.cfg.vel_iters > 65535u || t.cfg.pos_iters > 65535u) throw Error(kInvalidArg, "template iteration counts must not exceed 65535");
     t.L = cu[4]; t.B = cu[5];
     const uint32_t L = t.L, B = t.B;
     if (L > kMaxLinks) throw Error(kNotSupported, "more than 32 links per env");
@@ -125,8 +159,7 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
     t.body_pose0 = BlobVec<float>(blob, bytes, "body_pose0", 7 * B);
     BlobEntry ex;
     if (BlobFind(blob, bytes, "excluded", &ex) && ex.n) {
-        t.excluded.resize(static_cast<size_t>(ex.n));
-        std::memcpy(t.excluded.data(), ex.data, static_cast<size_t>(ex.n) * 8u);
+        t.excluded = BlobVec<unsigned long long>(blob, bytes, "excluded", ex.n);
         if (!std::is_sorted(t.excluded.begin(), t.excluded.end())) throw Error(kParseError, "excluded pair keys must ascend");
     }
     // derived tree tables
@@ -146,6 +179,8 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
         t.anc_mask[l] = (p == kNoLink ? 0u : t.anc_mask[p]) | (1u << l);
         for (int k = 0; k < 3; ++k) t.offset[3 * l + k] = local_pos[3 * l + k] + parent_offset[3 * l + k];
         if (t.link_body[l] >= B && B != 0u) throw Error(kParseError, "link_body out of range");
+        if (t.limit_flags[l] > 3u) throw Error(kParseError, "limit_flags holds bits beyond lower | upper");
+        if (t.geom_kind[l] > 1u) throw Error(kParseError, "geom_kind must be 0 (shape frame = link frame) or 1 (own frame)");
     }
     if (t.ndof > kMaxDof) throw Error(kNotSupported, "more than 64 articulation coordinates per env");
     t.floating_root = (L > 0 && t.jtype[0] == kFloating) ? 1u : 0u;
@@ -188,6 +223,7 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
             }
         }
         if (t.shape_kind[b] > kPlane) throw Error(kNotSupported, "shape kind without an analytic manifold");
+        if (t.body_geom_kind[b] > 1u) throw Error(kParseError, "body_geom_kind must be 0 or 1");
     }
     for (uint32_t a = 0; a < B; ++a) for (uint32_t b = a + 1; b < B; ++b) {
         if (t.body_id[a] < 0 && t.body_id[b] < 0) continue;
@@ -458,9 +494,12 @@ void World::UploadPersistent(const uint8_t* in) {
     Check(cudaStreamSynchronize(stream_), "checkpoint synchronize");     // the caller's bytes may go away after the call
 }
 
-void World::Refresh() {
+// Recomputes the derived poses (link poses, body mirrors) from the coordinates: of every env, of the `count` envs
+// listed in the device array `ids`, or of the envs whose word in the device array `mask` is non-zero.
+void World::Refresh(const uint32_t* ids, uint32_t count, const uint32_t* mask) {
     StepParams p = params_;
     p.mode = kModeRefresh; p.steps = 1;
+    p.sel_ids = ids; p.sel_count = ids != nullptr ? count : 0u; p.sel_mask = mask;
     Check(cudaSetDevice(device_), "cudaSetDevice");
     Check(launch_step(p, warps_per_block_, stream_), "refresh launch");
     ++launches_;
@@ -469,7 +508,7 @@ void World::Refresh() {
 void World::RunStage(uint32_t mode) {
     StateView& s = params_.s;
     const size_t E = env_count_, n = tpl_.ndof;
-    if (mode == kModeDynamicsOnly && s.dbg_mass == nullptr) s.dbg_mass = Alloc<float>(E * n * n);
+    if (mode == kModeDynamicsOnly && s.dbg_mass == nullptr) { s.dbg_mass = Alloc<float>(E * n * n); graph_valid_ = false; }
     StepParams p = params_;
     p.mode = mode; p.steps = 1;
     Check(cudaSetDevice(device_), "cudaSetDevice");
@@ -489,9 +528,13 @@ void World::Step(uint32_t n) {
     StepParams p = params_;
     p.mode = kModeStep;
     if (!graph_mode_) {
-        p.steps = n;      // the kernel advances n steps per launch; inputs are constant across them
-        Check(launch_step(p, warps_per_block_, stream_), "step launch");
-        ++launches_;
+        // the kernel advances several steps per launch (inputs are constant across them; state goes back to global
+        // memory after every step, so the split changes no result); the cap keeps any one launch short
+        for (uint32_t done = 0u; done < n; done += kMaxStepsPerLaunch) {
+            p.steps = std::min(n - done, kMaxStepsPerLaunch);
+            Check(launch_step(p, warps_per_block_, stream_), "step launch");
+            ++launches_;
+        }
         return;
     }
     if (!graph_valid_) {
@@ -534,9 +577,24 @@ void World::Reset(const uint32_t* env_ids, uint32_t count) {
         Check(cudaStreamSynchronize(stream_), "reset ids sync");
         r.env_ids = reset_ids_;
         Check(launch_reset(r, static_cast<uint32_t>(ids.size()), stream_), "reset launch");
+        launches_ += 2;
+        Refresh(reset_ids_, static_cast<uint32_t>(ids.size()), nullptr);
+        return;
     }
     ++launches_;
     Refresh();
+}
+
+// Resets the envs whose word in the device array `mask` (env_count words, read on the world's stream) is non-zero.
+// Everything stays on the stream: no id list crosses to the host and nothing synchronises, so an episode loop can
+// chain step -> termination test -> reset without draining the GPU.
+void World::ResetMasked(const uint32_t* mask) {
+    Check(cudaSetDevice(device_), "cudaSetDevice");
+    ResetParams r = reset_;
+    r.env_ids = nullptr; r.env_mask = mask;
+    Check(launch_reset(r, env_count_, stream_), "masked reset launch");
+    ++launches_;
+    Refresh(nullptr, 0u, mask);
 }
 
 // Same result as Reset(env_ids, count) with no allocation on the device or the host: ids are validated, sorted and
@@ -551,17 +609,29 @@ void World::ResetStaticIds(const uint32_t* env_ids, uint32_t count) {
     std::sort(static_ids_host_, static_ids_host_ + count);
     const uint32_t unique = static_cast<uint32_t>(std::unique(static_ids_host_, static_ids_host_ + count) - static_ids_host_);
     ResetParams r = reset_;
-    Check(launch_reset_static_ids(r, static_ids_host_, unique, device_, stream_), "static-id reset launch");
-    Check(cudaStreamSynchronize(stream_), "static-id reset sync");
+    const uint32_t* device_ids = nullptr;
+    Check(launch_reset_static_ids(r, static_ids_host_, unique, device_, stream_, &device_ids), "static-id reset launch");
     ++launches_;
-    Refresh();
+    Refresh(device_ids, unique, nullptr);       // derived poses of the reset envs only; reads the ids still in the array
+    Check(cudaStreamSynchronize(stream_), "static-id reset sync");
 }
 
-void World::PackObservations(float* device_out) {
+void World::PackObservations(const ObservationParams& o, float* device_out) {
     if (tpl_.L < 2u || !tpl_.floating_root) throw Error(kNotSupported, "observation records need a floating-base articulation");
     Check(cudaSetDevice(device_), "cudaSetDevice");
-    Check(launch_pack_observations(params_.s, tpl_.L, device_out, stream_), "observation pack launch");
+    Check(launch_pack_observations(params_.s, tpl_.L, o, device_out, stream_), "observation pack launch");
     ++launches_;
+}
+
+// Contact read-out arrays (pair list, counts, points, normals, depths) are written every step while enabled; a
+// caller that only reads robot state switches them off and saves the stores.
+void World::SetContactReadout(bool on) {
+    StateView& s = params_.s;
+    if (on == (s.pair_count != nullptr)) return;
+    if (on) { s.pair_count = readout_.pair_count; s.pairs = readout_.pairs; s.contact_count = readout_.contact_count;
+              s.contact_point = readout_.contact_point; s.contact_normal = readout_.contact_normal; s.contact_depth = readout_.contact_depth; }
+    else { readout_ = s; s.pair_count = nullptr; }
+    graph_valid_ = false;
 }
 
 void World::Synchronize() {
@@ -595,9 +665,12 @@ bool World::Field(uint32_t id, FieldInfo* out) {
         case 109: return set(s.solver_residual, 4, 0, false);
         case 0x10000: return set(s.qddot, L, 0, false);
         case 0x10001:
-            if (s.dbg_mass == nullptr) s.dbg_mass = Alloc<float>(static_cast<size_t>(env_count_) * n * n);
+            // a captured graph holds its own copy of the kernel parameters: a tap allocated after the capture forces
+            // a new capture, or the graph would keep stepping with a null tap pointer
+            if (s.dbg_mass == nullptr) { s.dbg_mass = Alloc<float>(static_cast<size_t>(env_count_) * n * n); graph_valid_ = false; }
             return set(s.dbg_mass, n * n, 0, false);
-        case 0x10002: return set(s.pair_count, 1, 1, false);
+        // contact read-outs: while switched off (SetContactReadout) the arrays keep the last values written
+        case 0x10002: return set(s.pair_count != nullptr ? s.pair_count : readout_.pair_count, 1, 1, false);
         case 0x10003: return set(s.pairs, S * 2, 1, false);
         case 0x10004: return set(s.contact_count, S, 1, false);
         case 0x10005: return set(s.contact_point, S * 12, 0, false);
@@ -605,11 +678,13 @@ bool World::Field(uint32_t id, FieldInfo* out) {
         case 0x10007: return set(s.contact_depth, S * 4, 0, false);
         case 0x10008: return set(s.solver_sweeps, 1, 1, false);
         case 0x10009:
-            if (s.dbg_qdot_pseudo == nullptr) s.dbg_qdot_pseudo = Alloc<float>(static_cast<size_t>(env_count_) * n);
+            if (s.dbg_qdot_pseudo == nullptr) { s.dbg_qdot_pseudo = Alloc<float>(static_cast<size_t>(env_count_) * n); graph_valid_ = false; }
             return set(s.dbg_qdot_pseudo, n, 0, false);
+#ifdef NKB_STAGE_TAPS
         case 0x1000A:      // stage cycle counters accumulate from the first request on; writable so callers can clear them
-            if (s.dbg_cycles == nullptr) s.dbg_cycles = Alloc<uint32_t>(static_cast<size_t>(env_count_) * 32u);
+            if (s.dbg_cycles == nullptr) { s.dbg_cycles = Alloc<uint32_t>(static_cast<size_t>(env_count_) * 32u); graph_valid_ = false; }
             return set(s.dbg_cycles, 32, 1, true);
+#endif
         default: return false;
     }
 }

@@ -55,12 +55,14 @@ public:
 
     void Step(uint32_t n);
     void RunStage(uint32_t mode);
-    void Refresh();
+    void Refresh(const uint32_t* ids = nullptr, uint32_t count = 0u, const uint32_t* mask = nullptr);
     void Reset(const uint32_t* env_ids, uint32_t count);   // null ids: all envs
     void ResetStaticIds(const uint32_t* env_ids, uint32_t count);   // partial reset that allocates nothing
+    void ResetMasked(const uint32_t* device_mask);                  // partial reset chosen on the device, no host sync
+    void SetContactReadout(bool on);
     void Synchronize();
-    uint32_t ObservationWidth() const { return tpl_.L >= 2u ? 3u * (tpl_.L - 1u) + 13u : 0u; }
-    void PackObservations(float* device_out);
+    uint32_t ObservationWidth() const { return tpl_.L >= 2u ? 3u * (tpl_.L - 1u) + 12u : 0u; }      // without the reward column
+    void PackObservations(const ObservationParams& o, float* device_out);
     bool Field(uint32_t id, FieldInfo* out);
     void SetVelocityIterations(uint32_t n) { params_.t.cfg.vel_iters = n; graph_valid_ = false; }
     uint32_t VelocityIterations() const { return params_.t.cfg.vel_iters; }
@@ -97,6 +99,7 @@ private:
     HostTemplate tpl_;
     uint32_t env_count_;
     StepParams params_{};
+    StateView readout_{};               // contact read-out pointers while the read-out is switched off
     uint32_t warps_per_block_ = 1;
     std::vector<void*> allocations_;
     ResetParams reset_{};

@@ -57,7 +57,7 @@ class Field(enum.IntEnum):
     CONTACT_DEPTH = 0x10007
     SOLVER_SWEEPS = 0x10008
     JOINT_PSEUDO_VELOCITY = 0x10009
-    STAGE_CYCLES = 0x1000A
+    STAGE_CYCLES = 0x1000A      # served only by a library built with NUKA_B200_STAGE_TAPS=1 (profiling builds)
 
 
 class Device:
@@ -189,13 +189,34 @@ class World:
         _check(_abi.lib().nuka_world_reset_envs(self._h, ids.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)), ids.size))
 
     def observation_width(self):
+        """Floats per observation record (12 + 3 x actuated joints; 48 for a 12-joint quadruped), reward column excluded."""
         width = ctypes.c_uint32()
-        _check(_abi.lib().nuka_b200_world_pack_observations(self._h, None, 0, ctypes.byref(width)))
+        _check(_abi.lib().nuka_b200_world_pack_observations(self._h, None, None, 0, ctypes.byref(width)))
         return width.value
 
-    def pack_observations(self, out):
-        """Fills `out` (a CUDA float32 tensor or any object with data_ptr()/numel(), E x observation_width) on the world's stream."""
-        _check(_abi.lib().nuka_b200_world_pack_observations(self._h, ctypes.c_void_p(out.data_ptr()), out.numel(), None))
+    def observation_desc(self, command, last_action=None, default_position=None, joint_order=None, reward=None, row_stride=0):
+        """Descriptor of the reference's observation record (python/nuka/tasks/go2_obs.py:11-20) with its scales; the
+        arguments are CUDA tensors (command: 3 floats for every env, or E x 3) that must outlive the pack calls."""
+        d = _abi.ObservationDesc()
+        _abi.lib().nuka_b200_observation_desc_defaults(ctypes.byref(d))
+        d.command = command.data_ptr()
+        d.command_stride = 0 if command.numel() == 3 else int(command.stride(0))
+        for name, value in (("last_action", last_action), ("default_position", default_position), ("joint_order", joint_order), ("reward", reward)):
+            setattr(d, name, value.data_ptr() if value is not None else None)
+        d.row_stride = int(row_stride)
+        d._keep = (command, last_action, default_position, joint_order, reward)
+        return d
+
+    def pack_observations(self, desc, out):
+        """Writes one record per env into `out` (CUDA float32 tensor, row stride desc.row_stride or the record width) on the world's stream."""
+        _check(_abi.lib().nuka_b200_world_pack_observations(self._h, ctypes.byref(desc), ctypes.c_void_p(out.data_ptr()), out.numel(), None))
+
+    def reset_envs_masked(self, mask):
+        """Resets the envs whose word in `mask` (CUDA tensor of E 32-bit words) is non-zero; stays on the world's stream, no host sync."""
+        _check(_abi.lib().nuka_b200_world_reset_envs_masked(self._h, ctypes.c_void_p(mask.data_ptr())))
+
+    def set_contact_readout(self, enabled):
+        _check(_abi.lib().nuka_b200_world_set_contact_readout(self._h, 1 if enabled else 0))
 
     def reset_envs_static(self, env_ids):
         """reset_envs without any allocation (at most 4096 ids per call; calls on one device must not overlap)."""

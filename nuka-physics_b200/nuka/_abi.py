@@ -38,7 +38,15 @@ class BufferView(ctypes.Structure):
 
 class WorldInfo(ctypes.Structure):
     _fields_ = [(n, ctypes.c_uint32) for n in ("env_count", "links_per_env", "bodies_per_env", "dofs_per_env", "contact_slots_per_env",
-                                                "shared_bytes_per_env", "warps_per_block")]
+                                                "shared_bytes_per_env", "warps_per_block")] + [("fixed_dt", ctypes.c_float)]
+
+
+class ObservationDesc(ctypes.Structure):
+    _fields_ = [("command", ctypes.c_void_p), ("command_stride", ctypes.c_uint32), ("last_action", ctypes.c_void_p),
+                ("default_position", ctypes.c_void_p), ("joint_order", ctypes.c_void_p), ("reward", ctypes.c_void_p),
+                ("lin_vel_scale", ctypes.c_float), ("ang_vel_scale", ctypes.c_float), ("dof_pos_scale", ctypes.c_float),
+                ("dof_vel_scale", ctypes.c_float), ("command_scale", ctypes.c_float * 3), ("clip", ctypes.c_float),
+                ("row_stride", ctypes.c_uint32)]
 
 
 EXPORTS = [
@@ -48,7 +56,8 @@ EXPORTS = [
     "nuka_world_reset", "nuka_world_reset_envs", "nuka_world_forward_kinematics", "nuka_world_get_stream", "nuka_world_record_event",
     "nuka_world_get_buffer_view", "nuka_world_upload_field", "nuka_world_download_field", "nuka_world_create_from_template",
     "nuka_b200_world_info", "nuka_b200_world_run_stage", "nuka_b200_world_launch_count", "nuka_b200_world_reset_envs_static",
-    "nuka_b200_world_pack_observations", "nuka_world_checkpoint_capture", "nuka_world_checkpoint_restore", "nuka_checkpoint_destroy",
+    "nuka_b200_world_pack_observations", "nuka_b200_observation_desc_defaults", "nuka_b200_world_reset_envs_masked",
+    "nuka_b200_world_set_contact_readout", "nuka_b200_template_check", "nuka_world_checkpoint_capture", "nuka_world_checkpoint_restore", "nuka_checkpoint_destroy",
     "nuka_checkpoint_write", "nuka_world_checkpoint_read", "nuka_checkpoint_byte_size", "nuka_checkpoint_equal", "nuka_world_state_hash",
 ]
 
@@ -85,7 +94,11 @@ def lib():
     L.nuka_world_reset.argtypes = [vp]
     L.nuka_world_reset_envs.argtypes = [vp, ctypes.POINTER(u32), u32]
     L.nuka_b200_world_reset_envs_static.argtypes = [vp, ctypes.POINTER(u32), u32]
-    L.nuka_b200_world_pack_observations.argtypes = [vp, vp, sz, ctypes.POINTER(u32)]
+    L.nuka_b200_world_pack_observations.argtypes = [vp, ctypes.POINTER(ObservationDesc), vp, sz, ctypes.POINTER(u32)]
+    L.nuka_b200_observation_desc_defaults.argtypes = [ctypes.POINTER(ObservationDesc)]
+    L.nuka_b200_observation_desc_defaults.restype = None
+    L.nuka_b200_world_reset_envs_masked.argtypes = [vp, vp]
+    L.nuka_b200_world_set_contact_readout.argtypes = [vp, u32]
     L.nuka_world_forward_kinematics.argtypes = [vp]
     L.nuka_world_get_stream.argtypes = [vp, ctypes.POINTER(vp)]
     L.nuka_world_record_event.argtypes = [vp, vp]

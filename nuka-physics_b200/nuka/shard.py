@@ -2,12 +2,12 @@
 
 Envs never interact (the reference drops cross-env pairs, src/phi/op_schema.hpp:236-252, and builds trees, slots,
 rows and solver tiles per env), so rank g of G owns a contiguous env range and steps it alone.  The only exchange
-is the caller's: packed observations + reward per env, gathered after a step (python/nuka/gym/env.py composes the
-same 48 floats on the GPU, python/nuka/tasks/go2_obs.py:47-48).
+is the caller's: the observation record + reward per env, gathered after a step.  The pack kernel writes each rank's
+records straight into that rank's slice of the gather buffer, so the all-gather runs in place without a staging copy.
 """
-import torch
+import numpy as np
 
-OBS_FLOATS = 48       # joint positions 12, joint velocities 12, base pose 7, base twist 6, last targets 11
+OBS_FLOATS = 48                     # python/nuka/tasks/go2_obs.py:11-20, 12 actuated joints
 RECORD_FLOATS = OBS_FLOATS + 1      # + reward
 
 
@@ -26,26 +26,49 @@ def shard_sizes(world_size, total_envs):
     return [env_range(r, world_size, total_envs)[1] - env_range(r, world_size, total_envs)[0] for r in range(world_size)]
 
 
-def pack_observations(out, q, qdot, base_pose, link_velocity, drive_target):
-    """Writes one record per env into `out` (E x 49): quadruped observation + height reward.
-
-    q, qdot, drive_target are E x 13 (slot 0 = root), base_pose E x 7, link_velocity E x 78 (root twist first)."""
-    out[:, 0:12] = q[:, 1:]
-    out[:, 12:24] = qdot[:, 1:]
-    out[:, 24:31] = base_pose
-    out[:, 31:37] = link_velocity[:, 0:6]
-    out[:, 37:48] = drive_target[:, 1:12]
-    out[:, 48] = base_pose[:, 2]
+def observation_record(q, qdot, link_pose, link_velocity, command, last_action, default_position=None, joint_order=None,
+                       reward=None, scales=(2.0, 0.25, 1.0, 0.05), command_scale=(2.0, 2.0, 0.25), clip=100.0):
+    """numpy statement of the observation record (python/nuka/tasks/go2_obs.py:282-305): the checker of the pack kernel
+    and the host-side form for CPU tests.  q, qdot: E x L (slot 0 = root); link_pose E x L x 7; link_velocity E x L x 6
+    (angular first); command E x 3 or 3; last_action E x nj.  Returns E x (12 + 3 nj [+ 1])."""
+    q, qdot = np.asarray(q, np.float32), np.asarray(qdot, np.float32)
+    E, L = q.shape
+    nj = L - 1
+    pose = np.asarray(link_pose, np.float32).reshape(E, L, 7)
+    twist = np.asarray(link_velocity, np.float32).reshape(E, L, 6)[:, 0]
+    order = np.arange(nj) if joint_order is None else np.asarray(joint_order, np.int64)
+    default = np.zeros(nj, np.float32) if default_position is None else np.asarray(default_position, np.float32)
+    w, u = pose[:, 0, 3:4], pose[:, 0, 4:7]
+    g = np.broadcast_to(np.array([0.0, 0.0, -1.0], np.float32), (E, 3))
+    gravity = (w * w - (u * u).sum(-1, keepdims=True)) * g - 2.0 * w * np.cross(u, g) + 2.0 * u * (u * g).sum(-1, keepdims=True)
+    cmd = np.broadcast_to(np.asarray(command, np.float32).reshape(-1, 3), (E, 3)) * np.asarray(command_scale, np.float32)
+    parts = [twist[:, 3:6] * np.float32(scales[0]), twist[:, 0:3] * np.float32(scales[1]), gravity.astype(np.float32), cmd,
+             (q[:, 1:][:, order] - default) * np.float32(scales[2]), qdot[:, 1:][:, order] * np.float32(scales[3]),
+             np.asarray(last_action, np.float32).reshape(E, nj)]
+    out = np.clip(np.concatenate(parts, axis=1), -clip, clip).astype(np.float32)
+    if reward is not None:
+        out = np.concatenate([out, np.asarray(reward, np.float32).reshape(E, 1)], axis=1)
     return out
 
 
-def gather_observations(local, gathered=None, group=None):
-    """All-gathers equally sized per-rank records (E_local x 49) into (world_size * E_local) x 49, rank-major."""
+def gather_buffer(local_envs, world_size, width=RECORD_FLOATS, device=None):
+    """Rank-major gather buffer (world_size * local_envs) x width; rank r's records live in rows [r E, (r + 1) E)."""
+    import torch
+    return torch.empty((world_size * local_envs, width), dtype=torch.float32, device=device)
+
+
+def local_slice(gathered, rank, world_size):
+    """This rank's rows of the gather buffer: the pack kernel's output and the in-place all-gather's input."""
+    rows = gathered.shape[0] // world_size
+    return gathered[rank * rows:(rank + 1) * rows]
+
+
+def gather_observations(gathered, rank=None, group=None):
+    """In-place all-gather: every rank has filled its own slice (local_slice) of `gathered`; afterwards all slices are valid."""
     import torch.distributed as dist
     world = dist.get_world_size(group)
-    if gathered is None:
-        gathered = torch.empty((world * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
-    if gathered.shape[0] != world * local.shape[0]:
-        raise ValueError("gather buffer does not hold world_size shards")
-    dist.all_gather_into_tensor(gathered, local.contiguous(), group=group)
+    rank = dist.get_rank(group) if rank is None else rank
+    if gathered.shape[0] % world:
+        raise ValueError("gather buffer does not hold world_size equal shards")
+    dist.all_gather_into_tensor(gathered, local_slice(gathered, rank, world), group=group)
     return gathered

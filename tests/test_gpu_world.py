@@ -152,23 +152,106 @@ def test_scene_path_loads_a_cooked_template_file(device, tmp_path):
     w.destroy()
 
 
-def test_pack_observations_matches_the_host_side_layout(device):
+def test_observation_record_matches_the_reference_contract(device):
+    """The pack kernel against the numpy statement of python/nuka/tasks/go2_obs.py:282-305 (the reference checks its
+    own composer the same way, python/tests/test_gym_env.py:87), with a joint permutation, a reward column and a row
+    stride as used for a gather-buffer slice."""
     import torch
     from nuka import shard
     E = 33
     w = nuka.World.create_from_template(device, T.quadruped(0).blob(), E)
     st = T.quadruped_state(E, 2)
+    st["base_pose"][:, 3:] += 0.3 * np.random.default_rng(1).normal(size=(E, 4)).astype(np.float32)     # tilted bases
+    st["base_pose"][:, 3:] /= np.linalg.norm(st["base_pose"][:, 3:], axis=1, keepdims=True)
     w.upload(F.JOINT_POSITION, st["q"]); w.upload(F.BASE_POSE, st["base_pose"]); w.forward_kinematics()
     w.step_n(3)
-    assert w.observation_width() == shard.RECORD_FLOATS
-    out = torch.zeros((E, shard.RECORD_FLOATS), dtype=torch.float32, device="cuda")
-    w.pack_observations(out); w.synchronize()
-    views = [w.view(f).torch() for f in (F.JOINT_POSITION, F.JOINT_VELOCITY, F.BASE_POSE, F.LINK_VELOCITY, F.DRIVE_TARGET)]
-    want = shard.pack_observations(torch.zeros_like(out), *views)
-    assert torch.equal(out, want)
+    assert w.observation_width() == shard.OBS_FLOATS
+    rng = np.random.default_rng(3)
+    command = torch.tensor(rng.normal(size=(E, 3)).astype(np.float32), device="cuda")
+    action = torch.tensor(rng.normal(size=(E, 12)).astype(np.float32), device="cuda")
+    default = torch.tensor(rng.normal(size=12).astype(np.float32), device="cuda")
+    order = torch.tensor(rng.permutation(12).astype(np.int32), device="cuda")
+    reward = torch.tensor(rng.normal(size=E).astype(np.float32), device="cuda")
+    stride = 56
+    out = torch.full((E, stride), -7.0, dtype=torch.float32, device="cuda")
+    desc = w.observation_desc(command, last_action=action, default_position=default, joint_order=order, reward=reward, row_stride=stride)
+    w.pack_observations(desc, out); w.synchronize()
+    get = lambda f: w.download(f)
+    want = shard.observation_record(get(F.JOINT_POSITION), get(F.JOINT_VELOCITY), get(F.ARTICULATION_LINK_POSE), get(F.LINK_VELOCITY),
+                                    command.cpu().numpy(), action.cpu().numpy(), default.cpu().numpy(), order.cpu().numpy(),
+                                    reward=reward.cpu().numpy())
+    got = out.cpu().numpy()
+    assert np.allclose(got[:, :49], want, rtol=1e-6, atol=1e-6)
+    assert np.array_equal(got[:, 12:24], want[:, 12:24]) and np.array_equal(got[:, 36:49], want[:, 36:49])
+    assert (got[:, 49:] == -7.0).all()                      # the padding of each row is untouched
+    # shared command, identity order, no reward, packed rows
+    shared = torch.tensor([0.5, 0.0, -0.1], device="cuda")
+    tight = torch.zeros((E, 48), dtype=torch.float32, device="cuda")
+    w.pack_observations(w.observation_desc(shared), tight); w.synchronize()
+    want = shard.observation_record(get(F.JOINT_POSITION), get(F.JOINT_VELOCITY), get(F.ARTICULATION_LINK_POSE), get(F.LINK_VELOCITY),
+                                    (0.5, 0.0, -0.1), np.zeros((E, 12), np.float32))
+    assert np.allclose(tight.cpu().numpy(), want, rtol=1e-6, atol=1e-6)
     small = torch.zeros(10, dtype=torch.float32, device="cuda")
     with pytest.raises(nuka.NukaError):
-        w.pack_observations(small)
+        w.pack_observations(w.observation_desc(shared), small)
+    w.destroy()
+
+
+def test_masked_reset_matches_reset_envs(device):
+    """The device-mask reset gives the bytes of nuka_world_reset_envs for the same env set, without a host round trip."""
+    import torch
+    E = 40
+    a, b = quad_world(device, E, 4), quad_world(device, E, 4)
+    a.step_n(5); b.step_n(5)
+    ids = np.array([0, 7, 8, 31, 39], np.uint32)
+    mask = torch.zeros(E, dtype=torch.int32, device="cuda")
+    mask[torch.tensor(ids.astype(np.int64), device="cuda")] = 1
+    torch.cuda.synchronize()
+    a.reset_envs(ids); b.reset_envs_masked(mask)
+    fields = (F.JOINT_POSITION, F.JOINT_VELOCITY, F.BASE_POSE, F.ARTICULATION_LINK_POSE, F.RIGID_BODY_TRANSFORM, F.LINK_VELOCITY, F.ENV_STATUS)
+    for f in fields:
+        assert a.download(f).tobytes() == b.download(f).tobytes(), f
+    a.step_n(3); b.step_n(3)
+    for f in fields:
+        assert a.download(f).tobytes() == b.download(f).tobytes(), f
+    a.destroy(); b.destroy()
+
+
+def test_contact_readout_can_be_switched_off(device):
+    E = 16
+    a, b = quad_world(device, E, 2), quad_world(device, E, 2)
+    b.set_contact_readout(False)
+    a.step_n(40); b.step_n(40)
+    assert a.download(F.JOINT_POSITION).tobytes() == b.download(F.JOINT_POSITION).tobytes()
+    assert a.download(F.CONTACT_COUNT).sum() > 0 and b.download(F.CONTACT_COUNT).sum() == 0      # never written while off
+    b.set_contact_readout(True)
+    a.step(); b.step()
+    assert np.array_equal(a.download(F.CONTACT_COUNT), b.download(F.CONTACT_COUNT))
+    assert np.array_equal(a.download(F.PAIR_COUNT), b.download(F.PAIR_COUNT))
+    a.destroy(); b.destroy()
+
+
+def test_destroyed_handles_stay_dead(device):
+    """Handle ids are never reused (reference src/c_abi/handle_table.hpp:18-26): a handle kept past destroy does not
+    address a world created later."""
+    lib = _abi.lib()
+    w = quad_world(device, 4, 0)
+    stale = ctypes.c_void_p(w._h.value)
+    w.destroy()
+    fresh = quad_world(device, 4, 0)
+    assert fresh._h.value != stale.value
+    assert lib.nuka_world_step(stale) == _abi.NULL_HANDLE
+    fresh.step()
+    fresh.destroy()
+
+
+def test_outputs_reject_uploads(device):
+    w = quad_world(device, 4, 0)
+    lib = _abi.lib()
+    buf = np.zeros((4, 13 * 7), np.float32)
+    assert lib.nuka_world_upload_field(w._h, int(F.ARTICULATION_LINK_POSE), buf.ctypes.data, buf.nbytes, 0) == _abi.NOT_SUPPORTED
+    assert lib.nuka_world_upload_field(w._h, int(F.SOLVER_RESIDUAL), buf.ctypes.data, 16, 0) == _abi.NOT_SUPPORTED
+    assert lib.nuka_world_download_field(w._h, int(F.ARTICULATION_LINK_POSE), buf.ctypes.data, buf.nbytes, 0) == _abi.OK
     w.destroy()
 
 

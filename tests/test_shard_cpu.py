@@ -22,15 +22,32 @@ def test_env_ranges_tile_the_env_set():
         shard.env_range(2, 2, 10)
 
 
-def test_pack_observations_layout():
-    E = 5
+def test_observation_record_follows_the_reference_contract():
+    """python/nuka/tasks/go2_obs.py:11-20: scales 2.0 / 0.25 / 1.0 / 0.05, command scale (2, 2, 0.25), gravity in the base
+    frame, caller joint order through the permutation table, clip to +-100."""
+    E, L = 5, 13
     rng = np.random.default_rng(0)
-    q, qd, tg = (torch.from_numpy(rng.normal(size=(E, 13)).astype(np.float32)) for _ in range(3))
-    base = torch.from_numpy(rng.normal(size=(E, 7)).astype(np.float32))
-    lv = torch.from_numpy(rng.normal(size=(E, 78)).astype(np.float32))
-    out = shard.pack_observations(torch.zeros(E, shard.RECORD_FLOATS), q, qd, base, lv, tg)
-    assert torch.equal(out[:, :12], q[:, 1:]) and torch.equal(out[:, 24:31], base)
-    assert torch.equal(out[:, 31:37], lv[:, :6]) and torch.equal(out[:, 48], base[:, 2])
+    q, qd = rng.normal(size=(E, L)).astype(np.float32), rng.normal(size=(E, L)).astype(np.float32)
+    pose = rng.normal(size=(E, L, 7)).astype(np.float32)
+    pose[:, :, 3:] /= np.linalg.norm(pose[:, :, 3:], axis=-1, keepdims=True)
+    pose[0, 0, 3:] = (1, 0, 0, 0)                                   # upright base: gravity is (0, 0, -1)
+    c, s_ = np.cos(0.25), np.sin(0.25)
+    pose[1, 0, 3:] = (c, s_, 0, 0)                                  # rolled by 0.5 rad about x
+    twist = rng.normal(size=(E, L, 6)).astype(np.float32)
+    twist[2, 0, 3] = 80.0                                           # 80 x 2.0 is clipped to 100
+    action = rng.normal(size=(E, 12)).astype(np.float32)
+    default = rng.normal(size=12).astype(np.float32)
+    order = rng.permutation(12)
+    out = shard.observation_record(q, qd, pose, twist, (0.5, -0.2, 1.0), action, default, order)
+    assert out.shape == (E, shard.OBS_FLOATS)
+    assert np.allclose(out[0, 0:3], twist[0, 0, 3:6] * 2.0) and np.allclose(out[0, 3:6], twist[0, 0, 0:3] * 0.25)
+    assert np.allclose(out[0, 6:9], (0, 0, -1), atol=1e-6)
+    assert np.allclose(out[1, 6:9], (0, -np.sin(0.5), -np.cos(0.5)), atol=1e-6)
+    assert np.allclose(out[:, 9:12], (1.0, -0.4, 0.25))
+    assert np.allclose(out[:, 12:24], q[:, 1:][:, order] - default) and np.allclose(out[:, 24:36], qd[:, 1:][:, order] * 0.05)
+    assert np.array_equal(out[:, 36:48], action) and out[2, 0] == 100.0
+    with_reward = shard.observation_record(q, qd, pose, twist, (0.5, -0.2, 1.0), action, default, order, reward=np.arange(E))
+    assert with_reward.shape == (E, shard.RECORD_FLOATS) and np.array_equal(with_reward[:, 48], np.arange(E, dtype=np.float32))
 
 
 def _free_port():
@@ -46,10 +63,12 @@ def _rank_main(rank, world, port, total_envs, result_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     begin, end = shard.env_range(rank, world, total_envs)
     # each rank's record carries its global env id, so the gathered order can be checked
-    local = torch.zeros((end - begin, shard.RECORD_FLOATS))
+    gathered = shard.gather_buffer(end - begin, world)
+    gathered.fill_(-1.0)
+    local = shard.local_slice(gathered, rank, world)         # what the pack kernel writes into
     local[:, 0] = torch.arange(begin, end, dtype=torch.float32)
     local[:, 48] = float(rank)
-    gathered = shard.gather_observations(local)
+    shard.gather_observations(gathered)
     dist.barrier()
     torch.save(gathered, os.path.join(result_dir, f"rank{rank}.pt"))
     dist.destroy_process_group()

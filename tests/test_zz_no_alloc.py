@@ -52,6 +52,40 @@ def test_static_reset_matches_reset_envs_on_consecutive_calls(device):
         w.destroy()
 
 
+def _free_device_bytes():
+    import torch
+    torch.cuda.synchronize()
+    return torch.cuda.mem_get_info()[0]
+
+
+def test_static_reset_allocates_nothing_and_two_worlds_share_the_array(device):
+    """After the set-up call the free device memory does not move across further static resets (the property the entry
+    point exists for), and two worlds on the device that call in turn each get exactly their own ids reset: the
+    shared id array is rewritten by every call."""
+    pytest.importorskip("torch")
+    E = 64
+    a, b = _pair(device, E)
+    fresh = nuka.World.create_from_template(device, T.quadruped(0).blob(), E)
+    q0 = fresh.download(F.JOINT_POSITION)
+    a.reset_envs_static(np.array([1], np.uint32))             # set-up call: resolves the array's address once
+    before = _free_device_bytes()
+    ids_a, ids_b = np.array([5, 6, 7, 50], np.uint32), np.array([9, 60], np.uint32)
+    for _ in range(4):
+        a.reset_envs_static(ids_a)
+        b.reset_envs_static(ids_b)
+        assert _free_device_bytes() == before
+        a.step_n(2); b.step_n(2)
+    assert _free_device_bytes() == before
+    a.reset_envs_static(ids_a); b.reset_envs_static(ids_b)
+    qa, qb = a.download(F.JOINT_POSITION), b.download(F.JOINT_POSITION)
+    reset_a, reset_b = np.zeros(E, bool), np.zeros(E, bool)
+    reset_a[ids_a] = True; reset_b[ids_b] = True
+    assert np.array_equal(qa[reset_a], q0[reset_a]) and not np.array_equal(qa[~reset_a & (np.arange(E) != 1)], q0[~reset_a & (np.arange(E) != 1)])
+    assert np.array_equal(qb[reset_b], q0[reset_b]) and (qb[~reset_b] != q0[~reset_b]).any(axis=1).all()
+    for w in (a, b, fresh):
+        w.destroy()
+
+
 def test_static_reset_rejects_bad_requests_without_mutation(device):
     E = 32
     w = nuka.World.create_from_template(device, T.quadruped(0).blob(), E)
