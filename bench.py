@@ -2,16 +2,27 @@
 """Throughput bench of the batched articulated step.
 
     python bench.py --gpus N --steps K --warmup W          (torchrun launches it for N > 1)
-    python bench.py --impl reference ...                   (the CPU arm: the oracle on the host cores)
+    python bench.py --impl reference ...                   (the CPU arm: the oracle port on all host cores)
 
-A "step" is one physics step of every env of the workload.  N = 1 runs the 4096-env quadruped
-(BASELINE.json configs[1]); N > 1 gives every rank its own 4096-env shard (weak scaling, no data-path
-collective) and all-gathers the packed observations after every step (configs[4]'s exchange).
+A "step" is one physics step of every env of the workload: 4096 quadrupeds per GPU (BASELINE.json configs[1]).
+N > 1 gives every rank its own 4096-env shard (weak scaling, no collective in the step); after every step each rank
+packs observation + reward records straight into its slice of a gather buffer and the ranks all-gather it in place
+(configs[4]'s exchange).
+
+State preparation.  The cost of a step depends on what the robots are doing: while they drop onto their feet the solver
+runs all its sweeps, once they stand it stops early.  So both arms first run `config.settle_steps` untimed steps from
+the seeded start, and every figure below is measured on that prepared state:
+    value    drives hold the standing pose (the reference gate's protocol, tests/perf/test_go2_4096env_step_time.cpp)
+    active   every step gets fresh drive targets (standing pose + noise), as an RL caller's policy would write them
+    e2e      value's workload through the C ABI with host buffers: pinned-host targets uploaded, step, observations
+             (q and base pose) downloaded, wall clock per step with the same L2 flush between steps
 Prints one JSON line on rank 0.
 """
 import argparse
+import ctypes
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -23,13 +34,17 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "nuka-physics_b200"))
 
 ENVS_PER_GPU = 4096
+SETTLE_STEPS = 1000
 METRIC = "env-steps/sec (whole box) 4096-env 12-DoF quadruped"
-WORKLOAD = "quadruped (13 links, 18 DoF, 4 foot spheres + trunk box on a plane), configs[1], hold drives at the standing pose"
-# algorithmic bytes per env-step: B = 12 nj + 52 F + 8 nj + 52 F + 52 L + 8 (nj + 3 P) + 8 S + 32 P
+WORKLOAD = "quadruped (13 links, 18 DoF, 4 foot spheres + trunk box on a plane), configs[1]"
 NJ, NF, NL = 12, 1, 13
+ACTIVE_NOISE = 0.15          # rad, standard deviation of the per-step target noise of the `active` figure
+ACTIVE_POOL = 16             # distinct target sets cycled through
 
 
 def algorithmic_bytes(slots, points, free_bodies=0):
+    """Compulsory bytes per env-step: q, qdot, target, base pose + twist in; q, qdot, base out; link pose + velocity out;
+    free bodies in + out; warm-start multipliers in + out; contact ids and points out."""
     return 12 * NJ + 52 * NF + 8 * NJ + 52 * NF + 52 * NL + 104 * free_bodies + 8 * (NJ + 3 * points) + 8 * slots + 32 * points
 
 
@@ -42,7 +57,7 @@ def hbm_peak():
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clocks and throttle reasons of one GPU while the timed region runs."""
+    """Samples SM clocks and throttle reasons of one GPU while the timed region runs (read-only queries)."""
 
     def __init__(self, index):
         super().__init__(daemon=True)
@@ -55,7 +70,7 @@ class ClockSampler(threading.Thread):
             self._run_smi()
 
     def _run_nvml(self):
-        # read-only NVML queries; the device is addressed by its UUID so CUDA_VISIBLE_DEVICES remapping cannot mislead it
+        # the device is addressed by its UUID so CUDA_VISIBLE_DEVICES remapping cannot mislead it
         import pynvml as nv
         import torch
         nv.nvmlInit()
@@ -96,67 +111,113 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons)}
 
 
-def run_reference(args):
-    """CPU arm: the reference has no CPU implementation of this path, so the oracle port is timed."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
+# ---- CPU legs: the oracle port (the reference has no CPU implementation of this path) ------------------------------------
+
+def _oracle(native=True):
+    """The oracle module bound to a build made for this machine (-O3 -march=native) when that compiles here."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import orc
+    path = orc.build_native() if native else None
+    orc.lib(path)
+    return orc, ("-O3 -march=native" if path else "-O2 -march=x86-64-v3")
+
+
+def _time_oracle(world, threads, repeats, steps):
+    """Median over `repeats` of the time of `steps` steps."""
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        world.step(steps, threads)
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times), times
+
+
+def run_reference(args):
+    """`--impl reference`: the whole workload (all 4096 envs, same settle) on the host cores, rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
     from nuka import templates as T
-    sample_envs = 512
-    tb = T.quadruped(0)
-    w = orc.World(tb.blob(), sample_envs)
-    st = T.quadruped_state(sample_envs, 0)
+    orc, flags = _oracle()
+    E = ENVS_PER_GPU
+    w = orc.World(T.quadruped(0).blob(), E)
+    st = T.quadruped_state(E, 0)
     w.set("q", st["q"]); w.set("base_pose", st["base_pose"]); w.refresh()
     threads = orc.lib().orc_hw_threads()
-    for _ in range(args.warmup):
-        w.step(1, threads)
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        w.step(1, threads)
-    dt = time.perf_counter() - t0
-    value = sample_envs * args.steps / dt
-    sample = f"{sample_envs} of {ENVS_PER_GPU} envs per step, {args.steps} steps, OpenMP over envs"
+    w.step(args.settle, threads)
+    settle_s = time.perf_counter() - t0
+    w.step(args.warmup, threads)
+    repeats = 5
+    per_repeat = max(1, args.steps // repeats)
+    median, times = _time_oracle(w, threads, repeats, per_repeat)
+    value = E * per_repeat / median
+    sample = f"all {E} envs x {per_repeat} steps, median of {repeats} repeats, after {args.settle} settle + {args.warmup} warm-up steps, OpenMP over envs, {flags}"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "env-steps/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3 * ENVS_PER_GPU / sample_envs, "higher_is_better": True,
+        "warmup": args.warmup, "ms_per_step": median / per_repeat * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "envs_per_gpu": ENVS_PER_GPU, "dt": 1.0 / 200.0, "velocity_iterations": 4,
-                   "note": "CPU oracle port on the host cores, bounded sample per step"},
-        "cpu_baseline": {"value": value, "unit": "env-steps/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": {"workload": WORKLOAD, "envs_per_gpu": E, "dt": 1.0 / 200.0, "velocity_iterations": 4, "settle_steps": args.settle,
+                   "drives": "hold the standing pose", "settle_seconds": settle_s,
+                   "note": "CPU oracle port on the host cores; the reference has no CPU implementation of this path"},
+        "cpu_baseline": {"value": value, "unit": "env-steps/s", "cores": threads, "kind": "port", "sample": sample,
+                         "spread": [E * per_repeat / t for t in times]},
         "e2e": {"value": value, "unit": "env-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
-def cpu_baseline():
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import orc
+def cpu_baseline(state):
+    """The oracle on all host cores, seeded with the GPU run's prepared state (a bounded sample of the same workload)."""
     from nuka import templates as T
-    envs, steps = 512, 40
-    w = orc.World(T.quadruped(0).blob(), envs)
-    st = T.quadruped_state(envs, 0)
-    w.set("q", st["q"]); w.set("base_pose", st["base_pose"]); w.refresh()
+    orc, flags = _oracle()
+    E = ENVS_PER_GPU
+    w = orc.World(T.quadruped(0).blob(), E)
+    for name, value in state.items():
+        w.set(name, value)
+    w.refresh()
+    w.set("link_velocity", state["link_velocity"])
     threads = orc.lib().orc_hw_threads()
-    w.step(5, threads)
-    t0 = time.perf_counter()
-    w.step(steps, threads)
-    dt = time.perf_counter() - t0
-    return {"value": envs * steps / dt, "unit": "env-steps/s", "cores": threads, "kind": "port",
-            "sample": f"{envs} of {ENVS_PER_GPU} envs x {steps} steps of the same workload, OpenMP over envs"}
+    w.step(10, threads)                      # rebuilds the contact cache the state transfer does not carry
+    median, times = _time_oracle(w, threads, 5, 6)
+    return {"value": E * 6 / median, "unit": "env-steps/s", "cores": threads, "kind": "port",
+            "sample": f"all {E} envs x 6 steps, median of 5 repeats, started from this run's prepared state (+10 untimed steps), "
+                      f"OpenMP over envs, {flags}",
+            "spread": [E * 6 / t for t in times]}
+
+
+def fp32_peak(device_index):
+    """Register-resident FMA rate of this GPU in TFLOP/s (csrc/probe/fp32_peak.cu), or None."""
+    try:
+        from nuka import _build
+        lib = ctypes.CDLL(_build.build_probe())
+        tflops, ms = ctypes.c_float(), ctypes.c_float()
+        if lib.nkb_probe_fp32_peak(int(device_index), 5, ctypes.byref(tflops), ctypes.byref(ms)) != 0:
+            return None
+        return float(tflops.value)
+    except Exception:
+        return None
+
+
+def captured_counters():
+    """Per-launch counters of one ncu capture of the step kernel on the prepared state (profiles/), or {}."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "step_kernel_quadruped_counters.json")) as f:
+            return json.load(f)
+    except Exception:
+        return {}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    # defaults follow the reference's own harness for this metric: 100 warm-up + 1000 timed steps with hold drives
-    # (tests/perf/test_go2_4096env_step_time.cpp)
-    ap.add_argument("--steps", type=int, default=1000)
-    ap.add_argument("--warmup", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native")
     ap.add_argument("--envs", type=int, default=ENVS_PER_GPU)
+    ap.add_argument("--settle", type=int, default=SETTLE_STEPS, help="untimed steps from the seeded start that prepare the measured state")
     ap.add_argument("--no-flush", action="store_true", help="skip the L2 flush between timed steps")
     ap.add_argument("--no-gather", action="store_true", help="N > 1: skip the per-step observation all-gather")
+    ap.add_argument("--no-extra", action="store_true", help="skip the configs[4] figure (65536 quadruped + 4-box envs split over the ranks)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--boxes", type=int, default=0,
                     help="free 0.1 m boxes beside each quadruped: 4 with --envs 8192 per GPU is configs[4]'s shard (not the headline workload)")
     args = ap.parse_args()
@@ -166,139 +227,239 @@ def main():
         return
     import torch
     import nuka
-    from nuka import Field as F, templates as T
+    from nuka import Field as F, shard, templates as T
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world_size = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local_rank)
+    cuda = torch.device("cuda", local_rank)
     distributed = world_size > 1
+    gather = distributed and not args.no_gather
     if distributed:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    E = args.envs
+        dist.init_process_group("nccl", device_id=cuda)
     dev = nuka.Device.create(local_rank)
-    w = nuka.World.create_from_template(dev, T.quadruped(0, boxes=args.boxes).blob(), E)
-    st = T.quadruped_state(E, seed=rank)
-    w.upload(F.JOINT_POSITION, st["q"]); w.upload(F.BASE_POSE, st["base_pose"]); w.forward_kinematics()
-    w.synchronize()
-    stream_ptr = __import__("ctypes").c_void_p()
-    nuka._check(nuka._abi.lib().nuka_world_get_stream(w._h, __import__("ctypes").byref(stream_ptr)))
-    stream = torch.cuda.ExternalStream(stream_ptr.value, device=torch.device("cuda", local_rank))
-    views = {f: w.view(f).torch() for f in (F.JOINT_POSITION, F.JOINT_VELOCITY, F.BASE_POSE, F.LINK_VELOCITY, F.DRIVE_TARGET)}
-    flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device="cuda") if not args.no_flush else None
-    obs_local = torch.empty((E, 49), dtype=torch.float32, device="cuda")
-    obs_all = torch.empty((E * world_size, 49), dtype=torch.float32, device="cuda") if distributed else None
+    flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device=cuda) if not args.no_flush else None
 
-    from nuka import shard
-
-    def one_step():
-        w.step()
-        if distributed and not args.no_gather:
-            # 48 observation floats + 1 reward per env, gathered as the RL caller would
-            w.pack_observations(obs_local)
-            shard.gather_observations(obs_local, obs_all)
-
-    with torch.cuda.stream(stream):
-        for _ in range(args.warmup):
-            one_step()
-        stream.synchronize()
-        if distributed:
-            dist.barrier()
-        torch.cuda.synchronize()
-        launches0 = w.launch_count()
-        sampler = ClockSampler(local_rank)
-        sampler.start()
-        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        for k in range(args.steps):
-            if flush is not None:
-                flush.add_(1.0)                       # evicts the 126 MB L2 between timed steps (outside the timed spans)
-            starts[k].record(stream)
-            one_step()
-            ends[k].record(stream)
-        stream.synchronize()
-        torch.cuda.synchronize()
-        if distributed:
-            dist.barrier()
-        clocks = sampler.stop()
-        gpu_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
-        launches = w.launch_count() - launches0
-        # contact statistics of the timed window's last step
+    def make_world(E, boxes, seed):
+        w = nuka.World.create_from_template(dev, T.quadruped(0, boxes=boxes).blob(), E)
+        st = T.quadruped_state(E, seed=seed)
+        w.upload(F.JOINT_POSITION, st["q"]); w.upload(F.BASE_POSE, st["base_pose"]); w.forward_kinematics()
+        w.set_contact_readout(False)            # the bench reads robot state only; contact statistics are taken once at the end
         w.synchronize()
-        counts = w.download(F.CONTACT_COUNT)
-        slots = float((counts > 0).sum(axis=1).mean())
-        points = float(counts.sum(axis=1).mean())
-        # ---- end to end: host targets in, host observations out, through the public API ----
-        targets = torch.from_numpy(w.download(F.DRIVE_TARGET)).pin_memory()
-        out_q = torch.empty((E, 13), dtype=torch.float32).pin_memory()
-        out_b = torch.empty((E, 7), dtype=torch.float32).pin_memory()
-        lib = nuka._abi.lib()
+        return w
 
-        def e2e_step():
-            nuka._check(lib.nuka_world_upload_field(w._h, int(F.DRIVE_TARGET), targets.data_ptr(), targets.numel() * 4, 0))
-            one_step()
-            nuka._check(lib.nuka_world_download_field(w._h, int(F.JOINT_POSITION), out_q.data_ptr(), out_q.numel() * 4, 0))
-            nuka._check(lib.nuka_world_download_field(w._h, int(F.BASE_POSE), out_b.data_ptr(), out_b.numel() * 4, 0))
+    def stream_of(w):
+        ptr = ctypes.c_void_p()
+        nuka._check(nuka._abi.lib().nuka_world_get_stream(w._h, ctypes.byref(ptr)))
+        return torch.cuda.ExternalStream(ptr.value, device=cuda)
 
-        for _ in range(3):
-            e2e_step()
+    class Exchange:
+        """Per-step observation + reward exchange of one world: the pack kernel writes this rank's records into its slice of
+        the gather buffer, the all-gather runs in place."""
+
+        def __init__(self, w, E):
+            self.w = w
+            self.buffer = shard.gather_buffer(E, world_size, shard.RECORD_FLOATS, device=cuda)
+            self.local = shard.local_slice(self.buffer, rank, world_size)
+            self.base = w.view(F.BASE_POSE).torch()
+            self.reward = torch.zeros(E, dtype=torch.float32, device=cuda)
+            self.command = torch.tensor([0.5, 0.0, 0.0], dtype=torch.float32, device=cuda)
+            self.last_action = torch.zeros((E, NJ), dtype=torch.float32, device=cuda)
+            self.desc = w.observation_desc(self.command, last_action=self.last_action, reward=self.reward, row_stride=shard.RECORD_FLOATS)
+
+        def run(self):
+            self.reward.copy_(self.base[:, 2])           # the caller's reward: base height
+            self.w.pack_observations(self.desc, self.local)
+            shard.gather_observations(self.buffer, rank)
+
+    def timed(w, stream, steps, warmup, before_step=None, exchange=None):
+        """`warmup` untimed then `steps` timed steps; per-step CUDA events on the world's stream, L2 flushed between steps
+        outside the timed spans.  Returns the per-step times in ms and the kernel launches inside the timed steps."""
+        def one(k):
+            if before_step is not None:
+                before_step(k)
+            w.step()
+            if exchange is not None:
+                exchange.run()
+        with torch.cuda.stream(stream):
+            for k in range(warmup):
+                one(k)
+            stream.synchronize()
+            if distributed:
+                dist.barrier()
+            torch.cuda.synchronize()
+            launches0 = w.launch_count()
+            starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+            ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+            for k in range(steps):
+                if flush is not None:
+                    flush.add_(1.0)                       # evicts the 126 MB L2 (outside the timed spans)
+                starts[k].record(stream)
+                one(warmup + k)
+                ends[k].record(stream)
+            stream.synchronize()
+            torch.cuda.synchronize()
+            if distributed:
+                dist.barrier()
+        return [s.elapsed_time(e) for s, e in zip(starts, ends)], w.launch_count() - launches0
+
+    def max_over_ranks(values):
+        t = torch.tensor(values, dtype=torch.float64, device=cuda)
+        if distributed:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t]
+
+    # ---- the headline workload ----------------------------------------------------------------------------------------
+    E = args.envs
+    w = make_world(E, args.boxes, seed=rank)
+    stream = stream_of(w)
+    exchange = Exchange(w, E) if gather else None
+    if gather:
+        with torch.cuda.stream(stream):          # NCCL's first-use cost (channel set-up, registration) lands here, not in the timed steps
+            for _ in range(20):
+                exchange.run()
+        stream.synchronize()
+    with torch.cuda.stream(stream):
+        w.step_n(args.settle)
+    stream.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    hold_ms, launches = timed(w, stream, args.steps, args.warmup, exchange=exchange)
+    clocks = sampler.stop()
+    # active drives: each step copies one of a pool of target sets (standing pose + noise) into DRIVE_TARGET on the stream
+    targets_view = w.view(F.DRIVE_TARGET).torch()
+    hold_targets = targets_view.clone()
+    gen = torch.Generator(device=cuda).manual_seed(1234 + rank)
+    pool = [hold_targets + ACTIVE_NOISE * torch.randn(hold_targets.shape, generator=gen, device=cuda) for _ in range(ACTIVE_POOL)]
+    for p in pool:
+        p[:, 0] = hold_targets[:, 0]
+    active_steps = max(10, args.steps // 2)
+    active_ms, _ = timed(w, stream, active_steps, max(args.warmup, 10), before_step=lambda k: targets_view.copy_(pool[k % ACTIVE_POOL]), exchange=exchange)
+    with torch.cuda.stream(stream):
+        targets_view.copy_(hold_targets)
+        w.step_n(50)                              # back to the hold state for the end-to-end leg
+        w.set_contact_readout(True)
+        w.step()
+    w.synchronize()
+    counts = w.download(F.CONTACT_COUNT)
+    slots = float((counts > 0).sum(axis=1).mean())
+    points = float(counts.sum(axis=1).mean())
+    sweeps = float(w.download(F.SOLVER_SWEEPS).mean())
+    w.set_contact_readout(False)
+
+    # ---- end to end through the C ABI with host buffers ---------------------------------------------------------------
+    lib = nuka._abi.lib()
+    targets = torch.from_numpy(w.download(F.DRIVE_TARGET)).pin_memory()
+    out_q = torch.empty((E, NL), dtype=torch.float32).pin_memory()
+    out_b = torch.empty((E, 7), dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        nuka._check(lib.nuka_world_upload_field(w._h, int(F.DRIVE_TARGET), targets.data_ptr(), targets.numel() * 4, 0))
+        w.step()
+        if exchange is not None:
+            with torch.cuda.stream(stream):
+                exchange.run()
+        nuka._check(lib.nuka_world_download_field(w._h, int(F.JOINT_POSITION), out_q.data_ptr(), out_q.numel() * 4, 0))
+        nuka._check(lib.nuka_world_download_field(w._h, int(F.BASE_POSE), out_b.data_ptr(), out_b.numel() * 4, 0))
+
+    for _ in range(3):
+        e2e_step()
+    e2e_steps = max(10, args.steps // 4)
+    e2e_s = 0.0
+    for _ in range(e2e_steps):
+        if flush is not None:
+            flush.add_(1.0)
         torch.cuda.synchronize()
         if distributed:
             dist.barrier()
-        e2e_steps = max(10, args.steps // 4)
         t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            e2e_step()
-        torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
-    times = torch.tensor([gpu_ms, e2e_s * 1e3 / e2e_steps * args.steps], dtype=torch.float64, device="cuda")
+        e2e_step()                               # the downloads synchronise: the step's results are on the host when it returns
+        e2e_s += time.perf_counter() - t0
+    hold_total, active_total, e2e_total = max_over_ranks([sum(hold_ms), sum(active_ms), e2e_s * 1e3])
+    per_rank = None
     if distributed:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    gpu_ms, e2e_ms = float(times[0]), float(times[1])
+        mine = torch.tensor([min(hold_ms), statistics.median(hold_ms), max(hold_ms)], dtype=torch.float64, device=cuda)
+        every = [torch.zeros_like(mine) for _ in range(world_size)]
+        dist.all_gather(every, mine)
+        per_rank = [[round(float(v), 4) for v in t] for t in every]
+
+    # the prepared state, for the CPU baseline leg (rank 0, N = 1 only)
+    prepared = None
+    if rank == 0 and world_size == 1 and not args.no_cpu and not args.boxes and E == ENVS_PER_GPU:
+        prepared = {"q": w.download(F.JOINT_POSITION), "qdot": w.download(F.JOINT_VELOCITY), "base_pose": w.download(F.BASE_POSE),
+                    "link_velocity": w.download(F.LINK_VELOCITY), "drive_target": w.download(F.DRIVE_TARGET)}
+    w.destroy()
+
+    # ---- configs[4]: 65536 envs of quadruped + 4 free boxes split evenly over the ranks, same exchange ---------------------
+    extra = None
+    if not args.no_extra and not args.boxes:
+        total = 65536
+        Ex = total // world_size
+        wx = make_world(Ex, 4, seed=100 + rank)
+        sx = stream_of(wx)
+        ex = Exchange(wx, Ex) if gather else None
+        with torch.cuda.stream(sx):
+            wx.step_n(200)                        # boxes and robots land
+        sx.synchronize()
+        x_steps = 10
+        x_ms, _ = timed(wx, sx, x_steps, 3, exchange=ex)
+        (x_total,) = max_over_ranks([sum(x_ms)])
+        wx.destroy()
+        extra = {"workload": "configs[4]: 65536 envs of quadruped + 4 free 0.1 m boxes split evenly over the ranks, observation all-gather every step",
+                 "scaling": "strong", "total_envs": total, "envs_per_gpu": Ex, "steps": x_steps, "settle_steps": 200,
+                 "ms_per_step": x_total / x_steps, "value": total * x_steps / (x_total * 1e-3), "unit": "env-steps/s"}
+
     if rank == 0:
         total_envs = E * world_size
-        value = total_envs * args.steps / (gpu_ms * 1e-3)
-        e2e_value = total_envs * args.steps / (e2e_ms * 1e-3)
+        value = total_envs * args.steps / (hold_total * 1e-3)
+        active_value = total_envs * active_steps / (active_total * 1e-3)
+        e2e_value = total_envs * e2e_steps / (e2e_total * 1e-3)
         peak, peak_kind = hbm_peak()
         bytes_per = algorithmic_bytes(slots, points, args.boxes)
-        achieved = bytes_per * E * args.steps / (gpu_ms * 1e-3) / 1e9
-        traffic, issue = None, None
-        try:
-            with open(os.path.join(ROOT, "profiles", "step_kernel_quadruped_traffic.txt")) as f:
-                captured = json.load(f)
-            if args.boxes:
-                raise ValueError("the capture is of the headline workload")
-            traffic = captured.get("dram_bytes_per_launch_4096_envs")
-            # the bound that explains this kernel: warp instructions issued per second (instruction count of one
-            # captured 4096-env launch, scaled by envs) against one instruction per scheduler per cycle
-            instructions = captured.get("warp_instructions_per_launch_4096_envs")
-            if instructions and clocks.get("sm_mhz"):
-                issued = instructions / 4096.0 * E * args.steps / (gpu_ms * 1e-3)
-                issue_peak = 148 * 4 * clocks["sm_mhz"] * 1e6
-                issue = {"achieved": issued / 1e9, "peak": issue_peak / 1e9, "unit": "G warp-instructions/s",
-                         "frac": issued / issue_peak, "note": "148 SMs x 4 schedulers x SM clock; instruction count from the ncu capture"}
-        except Exception:
-            pass
+        kernel_ms = hold_total / args.steps
+        achieved = bytes_per * E * args.steps / (hold_total * 1e-3) / 1e9
+        counters = captured_counters() if not args.boxes else {}
+        issue = fp32 = None
+        if counters.get("warp_instructions_per_env_step") and clocks.get("sm_mhz"):
+            issued = counters["warp_instructions_per_env_step"] * value / world_size
+            issue_peak = 148 * 4 * clocks["sm_mhz"] * 1e6
+            issue = {"achieved": issued / 1e9, "peak": issue_peak / 1e9, "unit": "G warp-instructions/s", "frac": issued / issue_peak,
+                     "note": "148 SMs x 4 schedulers x sampled SM clock; instruction count from the ncu capture named in `counters`"}
+        peak_tflops = fp32_peak(local_rank)
+        if counters.get("fp32_flop_per_env_step") and peak_tflops:
+            flops = counters["fp32_flop_per_env_step"] * value / world_size
+            fp32 = {"achieved": flops / 1e12, "peak": peak_tflops, "unit": "TFLOP/s", "frac": flops / 1e12 / peak_tflops,
+                    "flop_per_env_step": counters["fp32_flop_per_env_step"],
+                    "note": "executed FADD + FMUL + 2 FFMA of the captured launch (ncu thread-instruction counters) against the FMA rate "
+                            "measured by csrc/probe/fp32_peak.cu in this run"}
         line = {
             "metric": METRIC, "value": value, "unit": "env-steps/s", "n_gpus": world_size, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": gpu_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "ms_per_step": kernel_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": WORKLOAD if not args.boxes else WORKLOAD.replace("configs[1]", f"configs[4]'s env: + {args.boxes} free 0.1 m boxes"),
-                       "envs_per_gpu": E, "dt": 1.0 / 200.0, "velocity_iterations": 4, "l2_flush_between_steps": flush is not None,
-                       "obs_allgather": distributed and not args.no_gather, "mean_contact_slots": slots, "mean_contact_points": points},
+                       "envs_per_gpu": E, "dt": 1.0 / 200.0, "velocity_iterations": 4, "settle_steps": args.settle,
+                       "drives": "hold the standing pose", "l2_flush_between_steps": flush is not None,
+                       "obs_allgather": gather, "mean_contact_slots": slots, "mean_contact_points": points, "mean_solver_sweeps": sweeps},
+            "active": {"value": active_value, "unit": "env-steps/s", "ms_per_step": active_total / active_steps, "steps": active_steps,
+                       "drives": f"targets redrawn every step: standing pose + N(0, {ACTIVE_NOISE}) rad"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "peak_source": peak_kind, "algorithmic_bytes_per_env_step": bytes_per,
-                         "kernel": "step_kernel", "kernel_ms": gpu_ms / args.steps, "issue": issue},
-            "e2e": {"value": e2e_value, "unit": "env-steps/s", "h2d_bytes_per_step": int(targets.numel() * 4),
-                    "d2h_bytes_per_step": int(out_q.numel() * 4 + out_b.numel() * 4)},
+                         "traffic": counters.get("dram_bytes_per_launch"), "peak_source": peak_kind, "algorithmic_bytes_per_env_step": bytes_per,
+                         "kernel": "step_kernel", "kernel_ms": kernel_ms, "issue": issue, "fp32": fp32,
+                         "counters": counters.get("source")},
+            "e2e": {"value": e2e_value, "unit": "env-steps/s", "ms_per_step": e2e_total / e2e_steps, "steps": e2e_steps,
+                    "h2d_bytes_per_step": int(targets.numel() * 4), "d2h_bytes_per_step": int(out_q.numel() * 4 + out_b.numel() * 4)},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
-        if world_size == 1:
-            line["cpu_baseline"] = cpu_baseline()
+        if per_rank is not None:
+            line["per_rank_step_ms_min_median_max"] = per_rank
+        if extra is not None:
+            line["extra"] = extra
+        if prepared is not None:
+            line["cpu_baseline"] = cpu_baseline(prepared)
         print(json.dumps(line))
-    w.destroy()
     dev.destroy()
     if distributed:
         dist.destroy_process_group()

@@ -247,6 +247,11 @@ nuka_result_t nuka_b200_world_pack_observations(nuka_world_handle world, const n
  * reset on one stream (the reference's gym layer downloads the done ids first, python/nuka/gym/env.py autoreset). */
 nuka_result_t nuka_b200_world_reset_envs_masked(nuka_world_handle world, const uint32_t* device_mask);
 
+/* Route of the candidate-pair stage (the reference has the same two: a per-env LBVH, src/collision/lbvh_batched.cuh, and an
+ * all-pairs pass for small scenes, ops/broadphase.cu:404-474).  0: chosen by the size of the template's admissible-pair
+ * table (the default), 1: the table, 2: the per-env tree.  The pair list is the same either way. */
+nuka_result_t nuka_b200_world_set_broadphase(nuka_world_handle world, uint32_t mode);
+
 /* Switches the per-step contact read-out arrays (PAIR_COUNT ... CONTACT_DEPTH below) on (non-zero, the default) or
  * off.  While off the step skips those stores and the arrays keep their last contents. */
 nuka_result_t nuka_b200_world_set_contact_readout(nuka_world_handle world, uint32_t enabled);

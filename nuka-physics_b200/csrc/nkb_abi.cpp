@@ -572,6 +572,11 @@ nuka_result_t nuka_b200_world_reset_envs_masked(nuka_world_handle world, const u
     return Guard([&]() { w->ResetMasked(device_mask); return NUKA_RESULT_OK; });
 }
 
+nuka_result_t nuka_b200_world_set_broadphase(nuka_world_handle world, uint32_t mode) {
+    NKB_WORLD(w)
+    return Guard([&]() { w->SetBroadphase(mode); return NUKA_RESULT_OK; });
+}
+
 nuka_result_t nuka_b200_world_set_contact_readout(nuka_world_handle world, uint32_t enabled) {
     NKB_WORLD(w)
     return Guard([&]() { w->SetContactReadout(enabled != 0u); return NUKA_RESULT_OK; });

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <mutex>
 #include "nkb_solver.cuh"
+#include "nkb_lbvh.cuh"
 #include "nkb_launch.h"
 
 namespace nkb {
@@ -164,7 +165,7 @@ __global__ void __maxnreg__(176) step_kernel(const __grid_constant__ StepParams 
         if (has_bodies) stage_bodies(e, true);
         if (has_collidables) {
             stage_aabbs(e);
-            pair_count = stage_pairs(e);
+            pair_count = t.broadphase_tree != 0u ? stage_pairs_lbvh(e) : stage_pairs(e);
             tick(e, 3);
             stage_narrowphase(e, pair_count);
             tick(e, 4);

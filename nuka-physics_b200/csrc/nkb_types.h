@@ -11,7 +11,7 @@ namespace nkb {
 constexpr uint32_t kNoLink = 0xffffffffu;
 constexpr uint32_t kMaxLinks = 32u;     // one warp lane per link
 constexpr uint32_t kMaxDof = 64u;       // a warp lane owns coordinates lane and lane + 32
-constexpr uint32_t kMaxBodies = 64u;
+constexpr uint32_t kMaxBodies = 256u;   // collidable rows per env (the env's shared-memory slice is the practical limit)
 constexpr uint32_t kPtsPerSlot = 4u;
 
 enum JointType : uint32_t { kRevolute = 0, kPrismatic = 1, kFixed = 2, kFloating = 3, kSpherical = 4 };
@@ -26,6 +26,19 @@ enum : uint32_t { kHeadContact = 1u << 0, kHeadContactNormal = 1u << 1, kHeadSpe
                   kHeadScalar = 1u << 7 /* position pass: only the normal axis */ };
 constexpr uint32_t kHeadWords = 64u;
 constexpr uint32_t kHeadStride = kHeadWords + 1u;   // odd record stride in shared memory    // words of shared memory per solver head
+
+// Scratch words of the tree broadphase for B collidable rows (nkb_lbvh.cuh): sorted keys, internal nodes (children, range,
+// box), split table, ready flags and one partner bit row per body.
+#ifdef __CUDACC__
+#define NKB_HOST_DEVICE __host__ __device__
+#else
+#define NKB_HOST_DEVICE
+#endif
+NKB_HOST_DEVICE inline uint32_t lbvh_pow2(uint32_t b) { uint32_t p = 2u; while (p < b) p <<= 1u; return p; }
+NKB_HOST_DEVICE inline uint32_t lbvh_scratch_words(uint32_t B) {
+    if (B < 2u) return 0u;
+    return 2u * lbvh_pow2(B) + (B - 1u) * 10u + 4u * B + B * ((B + 31u) / 32u);
+}
 
 struct Config {
     float dt;
@@ -54,6 +67,9 @@ struct TemplateView {
     // body-row pairs (a << 16 | b, a < b, ascending) that pass the template-constant filters: not both
     // static, bitmask/group admitted, not excluded.  Only these need an AABB test each step.
     const uint32_t *adm_pairs;
+    // the same admissibility as one bit row per body: bit b of row a (ceil(B / 32) words per row) for a < b
+    const uint32_t *adm_mask;
+    uint32_t broadphase_tree;           // 1: candidate pairs come from the per-env tree, 0: from the admissible-pair table
     const uint32_t *free_slot;         // B: slot of a free dynamic body in the solver's rigid-block arrays; others share slot n_free
     uint32_t n_free;
     uint32_t n_adm;

@@ -11,6 +11,7 @@ namespace nkb {
 namespace {
 
 constexpr uint32_t kMaxStepsPerLaunch = 64u;
+constexpr uint32_t kTreeCrossoverPairs = 4096u;   // admissible pairs above which the tree broadphase is the default
 constexpr int kOk = 0, kInvalidArg = 1, kCudaError = 3, kParseError = 5, kOutOfMemory = 6, kNotSupported = 7;
 
 struct BlobEntry { uint32_t dtype; uint64_t n; const uint8_t* data; };
@@ -102,7 +103,7 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
     t.L = cu[4]; t.B = cu[5];
     const uint32_t L = t.L, B = t.B;
     if (L > kMaxLinks) throw Error(kNotSupported, "more than 32 links per env");
-    if (B > kMaxBodies) throw Error(kNotSupported, "more than 64 collidable rows per env");
+    if (B > kMaxBodies) throw Error(kNotSupported, "more than 256 collidable rows per env");
     if (t.cfg.max_contacts > 1024u) throw Error(kNotSupported, "more than 1024 contact slots per env");
     t.parent = BlobVec<uint32_t>(blob, bytes, "parent", L);
     t.jtype = BlobVec<uint32_t>(blob, bytes, "jtype", L);
@@ -225,6 +226,7 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
         if (t.shape_kind[b] > kPlane) throw Error(kNotSupported, "shape kind without an analytic manifold");
         if (t.body_geom_kind[b] > 1u) throw Error(kParseError, "body_geom_kind must be 0 or 1");
     }
+    t.adm_mask.assign(std::max<size_t>(1, static_cast<size_t>(B) * ((B + 31u) / 32u)), 0u);
     for (uint32_t a = 0; a < B; ++a) for (uint32_t b = a + 1; b < B; ++b) {
         if (t.body_id[a] < 0 && t.body_id[b] < 0) continue;
         if (!FilterAdmits(t.contype[a], t.conaffinity[a], t.group[a], t.contype[b], t.conaffinity[b], t.group[b])) continue;
@@ -234,6 +236,7 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
         const bool analytic = !((ka == kCapsule && kb == kBox) || (ka == kBox && kb == kCapsule) || (ka == kPlane && kb == kPlane));
         if (!analytic) throw Error(kNotSupported, "capsule-box pairs need the convex narrowphase, which this path does not provide");
         t.adm_pairs.push_back((a << 16) | b);
+        t.adm_mask[a * ((B + 31u) / 32u) + (b >> 5)] |= 1u << (b & 31u);
     }
     if (t.adm_pairs.empty()) t.adm_pairs.push_back(0);
     // free dynamic bodies get their own slot in the rigid-block arrays; every other row shares one scratch slot
@@ -323,7 +326,8 @@ void World::BuildLayout() {
     const uint32_t SC = tv.slot_cap;
     s.pairs = take(SC); s.ccount = take(SC); s.cpoint = take(12 * SC); s.cnormal = take(12 * SC); s.cdepth = take(4 * SC);
     s.cfeat = take(8 * SC);                       // contact identity words
-    s.heads = take(kHeadStride * tv.head_cap);
+    // before the heads exist the region serves the tree broadphase as scratch
+    s.heads = take(std::max(kHeadStride * tv.head_cap, SC != 0u ? lbvh_scratch_words(B) : 0u));
     // the Jacobian pool also holds the AABBs (dead once the narrowphase is done) and, after the solve, the cache staging
     // entries + owner marks
     const uint32_t stage_cap = std::min(tv.point_cap, 4u * SC);
@@ -386,8 +390,10 @@ World::World(int device, cudaStream_t stream, const HostTemplate& tpl, uint32_t 
         v.inv_mass = Upload(t.inv_mass); v.inv_inertia = Upload(t.inv_inertia); v.inertial_pos = Upload(t.inertial_pos);
         v.inertial_quat = Upload(t.inertial_quat); v.excluded = Upload(t.excluded);
         v.adm_pairs = Upload(t.adm_pairs);
+        v.adm_mask = Upload(t.adm_mask);
         v.free_slot = Upload(t.free_slot); v.n_free = t.n_free;
         v.n_adm = (t.adm_pairs.size() == 1 && t.adm_pairs[0] == 0u) ? 0u : static_cast<uint32_t>(t.adm_pairs.size());
+        SetBroadphase(0u);
         const size_t E = env_count_, L = t.L, B = t.B, n = t.ndof, S = t.cfg.max_contacts;
         StateView& s = params_.s;
         s.env_count = env_count_;
@@ -621,6 +627,15 @@ void World::PackObservations(const ObservationParams& o, float* device_out) {
     Check(cudaSetDevice(device_), "cudaSetDevice");
     Check(launch_pack_observations(params_.s, tpl_.L, o, device_out, stream_), "observation pack launch");
     ++launches_;
+}
+
+// Route of the candidate-pair stage.  The table route tests every admissible pair's boxes each step (B^2 / 2 tests at
+// worst); the tree route sorts, builds and walks a tree of the env's boxes.  Both give the same list, so the choice is
+// a matter of cost: by default the tree takes over once the table is longer than kTreeCrossoverPairs.
+void World::SetBroadphase(uint32_t mode) {
+    if (mode > 2u) throw Error(kInvalidArg, "broadphase mode must be 0 (by size), 1 (table) or 2 (tree)");
+    const uint32_t tree = mode == 2u || (mode == 0u && params_.t.n_adm > kTreeCrossoverPairs) ? 1u : 0u;
+    if (tree != params_.t.broadphase_tree) { params_.t.broadphase_tree = tree; graph_valid_ = false; }
 }
 
 // Contact read-out arrays (pair list, counts, points, normals, depths) are written every step while enabled; a

@@ -30,6 +30,7 @@ struct HostTemplate {
     std::vector<float> shape_params, mu, inv_mass, inv_inertia, inertial_pos, inertial_quat, body_pose0;
     std::vector<unsigned long long> excluded;
     std::vector<uint32_t> adm_pairs;
+    std::vector<uint32_t> adm_mask;      // B x ceil(B / 32) words, bit b of row a for admissible a < b
     uint32_t max_points = 0;            // template's contact-point capacity, 0 = default
     std::vector<uint32_t> body_geom_kind;          // per collidable row (several rows may mirror one link)
     std::vector<float> body_geom_pos, body_geom_quat;
@@ -60,6 +61,7 @@ public:
     void ResetStaticIds(const uint32_t* env_ids, uint32_t count);   // partial reset that allocates nothing
     void ResetMasked(const uint32_t* device_mask);                  // partial reset chosen on the device, no host sync
     void SetContactReadout(bool on);
+    void SetBroadphase(uint32_t mode);                              // 0: by table size, 1: admissible-pair table, 2: per-env tree
     void Synchronize();
     uint32_t ObservationWidth() const { return tpl_.L >= 2u ? 3u * (tpl_.L - 1u) + 12u : 0u; }      // without the reward column
     void PackObservations(const ObservationParams& o, float* device_out);

@@ -215,6 +215,10 @@ class World:
         """Resets the envs whose word in `mask` (CUDA tensor of E 32-bit words) is non-zero; stays on the world's stream, no host sync."""
         _check(_abi.lib().nuka_b200_world_reset_envs_masked(self._h, ctypes.c_void_p(mask.data_ptr())))
 
+    def set_broadphase(self, mode):
+        """0: by the size of the admissible-pair table, 1: the table, 2: the per-env tree (same pair list either way)."""
+        _check(_abi.lib().nuka_b200_world_set_broadphase(self._h, int(mode)))
+
     def set_contact_readout(self, enabled):
         _check(_abi.lib().nuka_b200_world_set_contact_readout(self._h, 1 if enabled else 0))
 

@@ -57,7 +57,7 @@ EXPORTS = [
     "nuka_world_get_buffer_view", "nuka_world_upload_field", "nuka_world_download_field", "nuka_world_create_from_template",
     "nuka_b200_world_info", "nuka_b200_world_run_stage", "nuka_b200_world_launch_count", "nuka_b200_world_reset_envs_static",
     "nuka_b200_world_pack_observations", "nuka_b200_observation_desc_defaults", "nuka_b200_world_reset_envs_masked",
-    "nuka_b200_world_set_contact_readout", "nuka_b200_template_check", "nuka_world_checkpoint_capture", "nuka_world_checkpoint_restore", "nuka_checkpoint_destroy",
+    "nuka_b200_world_set_contact_readout", "nuka_b200_world_set_broadphase", "nuka_b200_template_check", "nuka_world_checkpoint_capture", "nuka_world_checkpoint_restore", "nuka_checkpoint_destroy",
     "nuka_checkpoint_write", "nuka_world_checkpoint_read", "nuka_checkpoint_byte_size", "nuka_checkpoint_equal", "nuka_world_state_hash",
 ]
 
@@ -99,6 +99,7 @@ def lib():
     L.nuka_b200_observation_desc_defaults.restype = None
     L.nuka_b200_world_reset_envs_masked.argtypes = [vp, vp]
     L.nuka_b200_world_set_contact_readout.argtypes = [vp, u32]
+    L.nuka_b200_world_set_broadphase.argtypes = [vp, u32]
     L.nuka_world_forward_kinematics.argtypes = [vp]
     L.nuka_world_get_stream.argtypes = [vp, ctypes.POINTER(vp)]
     L.nuka_world_record_event.argtypes = [vp, vp]

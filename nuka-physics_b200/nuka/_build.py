@@ -13,7 +13,7 @@ def _stale():
     if not os.path.exists(LIB_PATH):
         return True
     built = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(os.path.dirname(os.path.dirname(_HERE)), "include", "nuka_b200.h")]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if os.path.isfile(os.path.join(CSRC, f))] + [os.path.join(os.path.dirname(os.path.dirname(_HERE)), "include", "nuka_b200.h")]
     return any(os.path.getmtime(d) > built for d in deps if os.path.exists(d))
 
 
@@ -42,6 +42,20 @@ def build_native(force=False, verbose=False):
             print(out)
     subprocess.run([nvcc, "-shared", "-o", LIB_PATH, *objects, "-Xcompiler", "-fPIC"], check=True)
     return LIB_PATH
+
+
+PROBE_PATH = os.path.join(os.path.dirname(_HERE), "libnkb_probe.so")
+
+
+def build_probe(force=False):
+    """Compiles the measurement aid used by the bench report (csrc/probe/fp32_peak.cu) into libnkb_probe.so."""
+    src = os.path.join(CSRC, "probe", "fp32_peak.cu")
+    if not force and os.path.exists(PROBE_PATH) and os.path.getmtime(PROBE_PATH) >= os.path.getmtime(src):
+        return PROBE_PATH
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared",
+                    src, "-o", PROBE_PATH], check=True, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    return PROBE_PATH
 
 
 if __name__ == "__main__":

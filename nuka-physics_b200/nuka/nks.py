@@ -53,20 +53,32 @@ def _shape_of(cs):
 
 
 def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0, ground_mu=1.0, self_collision=False,
-         max_contacts=None, max_points=None):
+         max_contacts=None, max_points=None, scene_filters=False):
     """``scene`` is a parsed .nks document (dict) or a path.  Returns a TemplateBuilder.
 
     ``max_points`` caps the contact points per env that get solver rows (default: the bound derived from the shape
     pairs, at most 128); a smaller cap shrinks the env's shared-memory slice, and a step that exceeds it sets the
-    env's head-overflow status bit and drops the excess."""
+    env's head-overflow status bit and drops the excess.
+
+    A scene may carry its own ground (a static top-level body with a plane shape) and its own position actuators
+    (an ``actuator`` component beside a joint: gain, damping, force_limit); both replace the ``ground_height`` plane and
+    the ``kp`` / ``kd`` defaults.  ``scene_filters`` keeps every shape's own contype / conaffinity bits instead of the
+    robot-versus-ground assignment."""
     if not isinstance(scene, dict):
         with open(scene) as f:
             scene = json.load(f)
     if scene.get("nks_version") != 1:
         raise ValueError("unsupported nks_version")
-    roots = [n for n in scene.get("tree", []) if "rigid_body" in n]
+    def is_ground(node):
+        return node["rigid_body"].get("is_static") and not any("rigid_body" in c for c in node.get("children", [])) and \
+            any(c.get("collision_shape", {}).get("type") == "plane" for c in node.get("children", []))
+
+    tops = [n for n in scene.get("tree", []) if "rigid_body" in n]
+    grounds = [n for n in tops if is_ground(n)]
+    roots = [n for n in tops if not is_ground(n)]
     if len(roots) != 1:
         raise ValueError("exactly one articulated tree is supported")
+    self_collision = self_collision or scene_filters
     tb = T.TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=0)
     shape_rows = []
 
@@ -102,8 +114,17 @@ def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0,
         single = jtype in (T.REVOLUTE, T.PRISMATIC)
         lo, hi = (float(joint.get("lower_limit", 0.0)), float(joint.get("upper_limit", 0.0))) if single else (0.0, 0.0)
         robot_bits = dict(contype=int(first.get("contype", 1)), conaffinity=int(first.get("conaffinity", 1))) if (first and self_collision) else dict(contype=1, conaffinity=0)
+        act = node.get("actuator") if single else None
+        if act is not None and act.get("type") != "position":
+            raise ValueError("only position actuators are carried over")
+        # a position actuator's gain is the drive stiffness; without an authored damping the reference uses the
+        # critically damped 2 sqrt(gain) (scene_ir.hpp:335-336)
+        link_kp = float(act["gain"]) if act else (kp if single else 0.0)
+        link_kd = (float(act["damping"]) if "damping" in act else 2.0 * float(act["gain"]) ** 0.5) if act else (kd if single else 0.0)
         link = tb.add_link(parent_link, jtype, axis=axis, offset=offset, mass=float(rb.get("mass", 0.0)), inertia_diag=inertia, com=ipos,
-                           q0=float(joint.get("initial_position", 0.0)) if single else 0.0, kp=kp if single else 0.0, kd=kd if single else 0.0,
+                           q0=float(joint.get("initial_position", 0.0)) if single else 0.0, kp=link_kp, kd=link_kd,
+                           force_limit=float(act.get("force_limit", 0.0)) if act else 0.0,
+                           frictionloss=float(joint.get("frictionloss", 0.0)) if single else 0.0,
                            damping=float(joint.get("damping", 0.0)) if single else 0.0, armature=float(joint.get("armature", 0.0)) if single else 0.0,
                            limits=(lo, hi) if single and lo < hi else None,
                            shape=_shape_of(first) if first else None,
@@ -122,10 +143,96 @@ def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0,
                 add(child, link)
 
     add(roots[0], None)
-    tb.add_plane(ground_height, mu=ground_mu)
+    for g in grounds:
+        plane = next(c["collision_shape"] for c in g["children"] if c.get("collision_shape", {}).get("type") == "plane")
+        (gpos, gquat) = _pose(g, "transform")
+        if abs(abs(gquat[0]) - 1.0) > 1e-9 or np.abs(np.array(_pose(plane, "local")[0])).max() > 0:
+            raise ValueError("only horizontal ground planes at the body origin are carried over")
+        bits = dict(contype=int(plane.get("contype", 1)), conaffinity=int(plane.get("conaffinity", 1))) if scene_filters else {}
+        tb.add_plane(gpos[2], mu=float(plane.get("friction_mu", 1.0)), **bits)
+    if not grounds and ground_height is not None:
+        tb.add_plane(ground_height, mu=ground_mu)
     tb.cfg["max_contacts"] = int(max_contacts) if max_contacts is not None else max(len(shape_rows), 1)
     tb.max_points = int(max_points) if max_points is not None else 0
     return tb
+
+
+def _frame(pos=(0.0, 0.0, 0.0), quat=(1.0, 0.0, 0.0, 0.0)):
+    return {"pos": [float(v) for v in pos], "quat": [float(v) for v in quat]}
+
+
+def scene_from_builder(tb):
+    """The ``.nks`` document of a procedural template: one articulated tree (revolute / prismatic / fixed joints under a
+    free or static root), its shapes, position actuators for the driven joints, and the ground planes.  It is the input
+    both cookers read: the reference's own loader and cooker (src/scene/format/nks.cpp, src/scene/cook/
+    cook_to_model.cpp) and ``cook`` above, so that the two sides are compared on one scene file."""
+    names = {T.REVOLUTE: "revolute", T.PRISMATIC: "prismatic", T.FIXED: "fixed"}
+    children = {i: [] for i in range(len(tb.links))}
+    for i, l in enumerate(tb.links):
+        if l["parent"] != T.NOLINK:
+            children[l["parent"]].append(i)
+    order, body_id = [], {}
+
+    def number(i):          # body ids follow the pre-order walk of the tree, as the loader assigns them
+        body_id[i] = len(order)
+        order.append(i)
+        for c in children[i]:
+            number(c)
+
+    number(0)
+    joint_id = {}
+    for i in order:
+        if i != 0:
+            joint_id[i] = len(joint_id)
+
+    def shape_node(b, name):
+        kind = b["kind"]
+        p = b["params"]
+        cs = {"type": {T.SPHERE: "sphere", T.CAPSULE: "capsule", T.BOX: "box", T.PLANE: "plane"}[kind],
+              "local": _frame(b.get("geom_pos", (0, 0, 0)), b.get("geom_quat", (1, 0, 0, 0))),
+              "half_extents": [float(p[0]), float(p[1]), float(p[2])] if kind == T.BOX else [0.5, 0.5, 0.5],
+              "radius": float(p[0]) if kind in (T.SPHERE, T.CAPSULE) else 0.5, "half_height": float(p[1]) if kind == T.CAPSULE else 0.5,
+              "contype": int(b["contype"]), "conaffinity": int(b["conaffinity"]), "collision_group": int(b["group"]),
+              "friction_mu": float(b["mu"]), "condim": 3, "margin": 0.0, "gap": 0.0}
+        return {"name": name, "collision_shape": cs}
+
+    def node(i):
+        l = tb.links[i]
+        root = l["parent"] == T.NOLINK
+        if l["inertia_diag"] is None:
+            raise ValueError("links with a rotated inertial frame are not written")
+        out = {"name": f"link{i}",
+               "transform": _frame(tb.base_pose[:3], tb.base_pose[3:]) if root and l["jtype"] == T.FLOATING else _frame(l["local_pos"], l["local_quat"]),
+               "rigid_body": {"parent_id": 4294967295 if root else body_id[l["parent"]], "inertial": _frame(l["com"]),
+                              "mass": float(l["mass"]), "inertia": [float(v) for v in l["inertia_diag"]],
+                              "is_static": bool(root and l["jtype"] == T.FIXED)}}
+        if not root:
+            if l["jtype"] not in names:
+                raise ValueError("only revolute, prismatic and fixed joints can be written")
+            lim = l["limits"]
+            out["joint"] = {"name": f"joint{i}", "type": names[l["jtype"]], "parent_body": body_id[l["parent"]], "child_body": body_id[i],
+                            "axis": [float(v) for v in l["axis"]], "parent_frame": _frame(l["offset"]), "child_frame": _frame(),
+                            "lower_limit": float(lim[0]) if lim else 0.0, "upper_limit": float(lim[1]) if lim else 0.0,
+                            "has_lower_limit": lim is not None, "has_upper_limit": lim is not None,
+                            "damping": float(l["damping"]), "armature": float(l["armature"]), "stiffness": 0.0,
+                            "initial_position": float(l["q0"]), "frictionloss": float(l["frictionloss"])}
+            if l["kp"] != 0.0 or l["kd"] != 0.0:
+                out["actuator"] = {"name": f"servo{i}", "type": "position", "joint_id": joint_id[i], "gain": float(l["kp"]),
+                                   "force_limit": float(l["force_limit"]), "damping": float(l["kd"])}
+        kids = [shape_node(b, f"shape{k}") for k, b in enumerate(tb.bodies) if b["link"] == i and (b["contype"] or b["conaffinity"])]
+        out["children"] = kids + [node(c) for c in children[i]]
+        return out
+
+    tree = [node(0)]
+    for k, b in enumerate(tb.bodies):
+        if b["link"] != T.NOLINK:
+            continue
+        if b["kind"] != T.PLANE or b["inv_mass"] != 0.0:
+            raise ValueError("free bodies are not written; only ground planes")
+        tree.append({"name": f"ground{k}", "transform": _frame(b["pose"][:3], b["pose"][3:]),
+                     "rigid_body": {"parent_id": 4294967295, "inertial": _frame(), "mass": 0.0, "inertia": [0.0, 0.0, 0.0], "is_static": True},
+                     "children": [shape_node(b, "plane")]})
+    return {"nks_version": 1, "physics_materials": {}, "render_materials": {}, "tree": tree, "sensors": [], "exclude_pairs": [], "contact_pairs": []}
 
 
 def link_names(scene):

@@ -61,7 +61,7 @@ class TemplateBuilder:
         index = len(self.links)
         body = len(self.bodies)
         self.links.append(dict(parent=NOLINK if parent is None else parent, jtype=jtype, axis=axis, offset=offset, mass=mass,
-                               inertia=spatial_inertia(mass, inertia_diag, com), com=com, q0=q0, kp=kp, kd=kd,
+                               inertia=spatial_inertia(mass, inertia_diag, com), com=com, inertia_diag=tuple(float(v) for v in inertia_diag) if np.ndim(inertia_diag) == 1 else None, q0=q0, kp=kp, kd=kd,
                                force_limit=force_limit, damping=damping, armature=armature, frictionloss=frictionloss,
                                limits=limits, body=body, geom=0 if shape is None else 1, geom_pos=shape_pos,
                                geom_quat=shape_quat, local_pos=local_pos, local_quat=local_quat))

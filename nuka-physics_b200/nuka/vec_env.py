@@ -95,13 +95,16 @@ class NukaVecEnv:
             self.last_action.zero_()
             obs = self._compose().clone()
         self.world.synchronize()
+        obs.record_stream(torch.cuda.current_stream())
         return obs
 
     def step(self, actions):
         """``actions``: E x num_joints CUDA float tensor in the caller's joint order.  Returns (obs, reward, terminated,
-        truncated, info); the tensors are produced on the world's stream, which the caller's stream must wait on (or
-        call ``world.synchronize()``) before reading them."""
+        truncated, info).  The work runs on the world's stream; the caller's current stream is ordered behind it on the
+        device (stream waits, no host synchronisation), so the returned tensors can be used there directly."""
         torch = self._torch
+        caller = torch.cuda.current_stream()
+        self._stream_obj.wait_stream(caller)           # the actions were produced on the caller's stream
         with torch.cuda.stream(self._stream_obj):
             action = actions.clamp(-ACTION_CLIP, ACTION_CLIP)
             target = self.default_position + self.action_scale * action            # caller joint order
@@ -121,7 +124,11 @@ class NukaVecEnv:
             self.last_action.mul_(keep)
             self.episode_steps.mul_(~done)
             obs = self._compose().clone()              # finished envs report their fresh-episode observation
-        return obs, reward, fallen, truncated & ~fallen, {"done": done}
+            terminated, truncated = fallen, truncated & ~fallen
+        caller.wait_stream(self._stream_obj)
+        for tensor in (obs, reward, terminated, truncated, done):
+            tensor.record_stream(caller)
+        return obs, reward, terminated, truncated, {"done": done}
 
     def close(self):
         self.world.destroy()

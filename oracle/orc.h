@@ -93,6 +93,8 @@ typedef struct orc_model {
     uint64_t *excluded;
     uint32_t n_excluded;
     orc_config cfg;
+    uint32_t env_count;         /* envs of the world this model serves (the reference's route choice depends on it) */
+    uint32_t broadphase;        /* 0: the reference's rule (all-pairs while B^2 E <= 2^20, else the tree), 1: all-pairs, 2: tree */
 } orc_model;
 
 /* one solver row; reference src/nk/solve/nk_row.hpp:73-101 */
@@ -185,6 +187,9 @@ void orc_body_integrate_velocity(const orc_model *m, orc_env *e);
 void orc_sync_bodies(const orc_model *m, orc_env *e);
 void orc_build_aabbs(const orc_model *m, orc_env *e);
 void orc_find_pairs(const orc_model *m, orc_env *e);
+void orc_find_pairs_lbvh(const orc_model *m, orc_env *e);
+uint32_t orc_lbvh_pair_set(uint32_t n, const float *lo, const float *hi, uint64_t *out, uint32_t capacity);
+void orc_world_set_broadphase(orc_world *w, uint32_t mode);
 void orc_narrowphase(const orc_model *m, orc_env *e);
 void orc_assemble_rows(const orc_model *m, orc_env *e);
 void orc_warm_start_prepare(const orc_model *m, orc_env *e);

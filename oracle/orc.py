@@ -70,6 +70,9 @@ def lib(path=None):
         L.orc_world_destroy.argtypes = [ctypes.c_void_p]
         L.orc_world_reset.argtypes = [ctypes.c_void_p]
         L.orc_world_set_control_mode.argtypes = [ctypes.c_void_p, ctypes.c_uint32]
+        L.orc_world_set_broadphase.argtypes = [ctypes.c_void_p, ctypes.c_uint32]
+        L.orc_lbvh_pair_set.restype = ctypes.c_uint32
+        L.orc_lbvh_pair_set.argtypes = [ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32]
         L.orc_world_refresh.argtypes = [ctypes.c_void_p]
         L.orc_world_step.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_int]
         L.orc_stage_dynamics.argtypes = [ctypes.c_void_p, ctypes.c_int]
@@ -104,6 +107,10 @@ class World:
 
     def set_control_mode(self, mode):
         lib().orc_world_set_control_mode(self._h, int(mode))
+
+    def set_broadphase(self, mode):
+        """0: the reference's route rule, 1: all-pairs, 2: LBVH tree walk."""
+        lib().orc_world_set_broadphase(self._h, int(mode))
 
     def reset(self):
         lib().orc_world_reset(self._h)

@@ -82,7 +82,7 @@ static int is_excluded(const uint64_t *keys, uint32_t n, uint64_t key) {
 /* broadphase.cu:276-282, 314-474, 476-678: the candidate set is every i<j whose AABBs overlap, not both
  * static, admitted by the bitmask filter and not excluded; after the canonical sort the per-env list is
  * ascending in (i<<32|j). Tree walk and all-pairs routes produce the same set. */
-void orc_find_pairs(const orc_model *m, orc_env *e) {
+static void find_pairs_all(const orc_model *m, orc_env *e) {
     const uint32_t cap = m->cfg.max_pairs && m->cfg.max_pairs < m->cfg.max_contacts ? m->cfg.max_pairs : m->cfg.max_contacts;
     uint32_t count = 0;
     for (uint32_t i = 0; i < m->B; ++i) for (uint32_t j = i + 1; j < m->B; ++j) {
@@ -95,6 +95,14 @@ void orc_find_pairs(const orc_model *m, orc_env *e) {
         else e->status |= ORC_STATUS_PAIR_OVERFLOW;
     }
     e->pair_count = count;
+}
+
+/* broadphase.cu:581, 608: the all-pairs kernel replaces tree build + walk while B^2 E <= 2^20 (kAllPairsItems); the
+ * world can also pin either route, for the tests that show the two agree. */
+void orc_find_pairs(const orc_model *m, orc_env *e) {
+    const uint64_t items = (uint64_t)m->B * m->B * (m->env_count ? m->env_count : 1u);
+    const int tree = m->broadphase == 2u || (m->broadphase == 0u && items > (1u << 20));
+    if (tree) orc_find_pairs_lbvh(m, e); else find_pairs_all(m, e);
 }
 
 /* ---- analytic manifolds ---- */

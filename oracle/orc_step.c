@@ -162,6 +162,8 @@ orc_world *orc_world_create(const void *blob_in, size_t bytes, uint32_t env_coun
     m->child_begin[L] = at;
     if (m->ndof > ORC_MAX_DOF) { orc_world_destroy(w); return NULL; }
     w->E = env_count;
+    w->m.env_count = env_count;
+    w->m.broadphase = 0u;
     w->env = (orc_env *)calloc(env_count ? env_count : 1u, sizeof(orc_env));
     for (uint32_t i = 0; i < env_count; ++i) { env_alloc(m, &w->env[i]); env_seed(m, &w->env[i]); }
     return w;
@@ -177,6 +179,8 @@ void orc_world_destroy(orc_world *w) {
 
 /* control mode of every env: 0 PD position, 1 torque, 2 velocity; other values are ignored */
 void orc_world_set_control_mode(orc_world *w, uint32_t mode) { if (mode <= 2u || mode == 5u) w->m.cfg.control_mode = mode; }
+
+void orc_world_set_broadphase(orc_world *w, uint32_t mode) { if (mode <= 2u) w->m.broadphase = mode; }
 
 void orc_world_reset(orc_world *w) { for (uint32_t i = 0; i < w->E; ++i) env_seed(&w->m, &w->env[i]); }
 void orc_world_refresh(orc_world *w) { for (uint32_t i = 0; i < w->E; ++i) { orc_fk(&w->m, &w->env[i]); orc_sync_bodies(&w->m, &w->env[i]); } }

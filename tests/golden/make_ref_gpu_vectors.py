@@ -1,0 +1,101 @@
+"""Golden vectors from the reference's OWN GPU implementation (oracle/_ref/ref_driver, built by oracle/ref_gpu/Makefile
+from the reference checkout).  Three phases, because the driver needs a GPU and the checkout does not travel:
+
+  python tests/golden/make_ref_gpu_vectors.py prepare   writes the scene files (.nks, from the procedural templates), the
+                                                        per-env start states and run.sh into oracle/_ref/run/, and the
+                                                        reference's cook of each scene (no GPU needed) into tests/golden/
+  bash oracle/_ref/run/run.sh                           on a machine with a GPU: steps the scenes with the reference and
+                                                        writes OUT/ref_*.nkt and OUT/ref_timing.jsonl (OUT defaults to
+                                                        gpurun_out)
+  python tests/golden/make_ref_gpu_vectors.py collect   copies the results into tests/golden/
+
+Both sides of the later comparison read the same .nks scene: the reference through its loader and cooker, this
+library through nuka.nks.cook."""
+import json
+import os
+import shutil
+import subprocess
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, os.path.join(ROOT, "nuka-physics_b200"))
+sys.path.insert(0, HERE)
+from nuka import nks, nkt, templates as T
+import ref_cases
+
+RUN = os.path.join(ROOT, "oracle", "_ref", "run")
+DRIVER = os.path.join(ROOT, "oracle", "_ref", "ref_driver")
+ENVS = 128          # above 64, where the reference solver's blocks never wait on one another
+CASES = {
+    # name: (template, state maker, dt, velocity iterations, steps, sampling stride)
+    "arm7": (lambda: T.arm7(0), lambda E: T.arm7_state(E, 0), 1.0 / 500.0, 4, 100, 20),
+    "quadruped": (lambda: T.quadruped(0), lambda E: T.quadruped_state(E, 0), 1.0 / 200.0, 4, 100, 20),
+    # the same robot started with joint rates and a base twist: meaningful joint accelerations, airborne then landing
+    "quadruped_moving": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_moving_state(E, 0), 1.0 / 200.0, 4, 40, 10),
+}
+
+
+def prepare():
+    os.makedirs(RUN, exist_ok=True)
+    lines = ["#!/bin/bash", "# written by tests/golden/make_ref_gpu_vectors.py", "set -e", 'cd "$(dirname "$0")"',
+             'OUT="${OUT:-../../../gpurun_out}"', 'mkdir -p "$OUT"', ': > "$OUT/ref_timing.jsonl"']
+    for name, (make, state, dt, iters, steps, every) in CASES.items():
+        tb = make()
+        with open(os.path.join(RUN, f"{name}.nks"), "w") as f:
+            json.dump(nks.scene_from_builder(tb), f)
+        scene = "quadruped" if name == "quadruped_moving" else name
+        shutil.copy(os.path.join(RUN, f"{name}.nks"), os.path.join(HERE, f"scene_{scene}.nks"))
+        st = {k: np.ascontiguousarray(v, np.float32) for k, v in state(ENVS).items() if k in ("q", "qdot", "base_pose", "link_velocity")}
+        with open(os.path.join(RUN, f"{name}_state.nkt"), "wb") as f:
+            f.write(nkt.pack(st))
+        subprocess.run([DRIVER, "--scene", os.path.join(RUN, f"{name}.nks"), "--envs", "1", "--cook-only", "--dump",
+                        os.path.join(HERE, f"ref_cook_{scene}.nkt")], check=True, stdout=subprocess.DEVNULL)
+        lines.append(f"../ref_driver --scene {name}.nks --envs {ENVS} --dt {dt!r} --vel-iters {iters} --state {name}_state.nkt "
+                     f"--steps {steps} --every {every} --dump \"$OUT/ref_{name}.nkt\"")
+    # the number to beat: the reference's own step on the bench workload, eager and graph mode, 100 warm-up + 1000 timed steps
+    with open(os.path.join(RUN, "quadruped_state4096.nkt"), "wb") as f:
+        st = T.quadruped_state(4096, 0)
+        f.write(nkt.pack({k: np.ascontiguousarray(st[k], np.float32) for k in ("q", "base_pose")}))
+    lines.append('../ref_driver --scene quadruped.nks --envs 4096 --dt 0.005 --vel-iters 4 --state quadruped_state4096.nkt '
+                 '--time 100,1000,3 >> "$OUT/ref_timing.jsonl"')
+    # the same after 1000 settle steps (the prepared state bench.py measures on): 1000 untimed, then 200 timed
+    lines.append('../ref_driver --scene quadruped.nks --envs 4096 --dt 0.005 --vel-iters 4 --state quadruped_state4096.nkt '
+                 '--time 1000,200,1 >> "$OUT/ref_timing.jsonl"')
+    with open(os.path.join(RUN, "run.sh"), "w") as f:
+        f.write("\n".join(lines) + "\n")
+    print("prepared", RUN)
+
+
+KEEP = ("run", "run_dt", "dyn_qddot", "dyn_mass", "dyn_bias", "start_link_pose", "start_kp", "start_kd", "start_force_limit",
+        "start_drive_target", "traj_steps", "traj_q", "traj_qdot", "traj_base_pose", "traj_status", "traj_pair_count",
+        "traj_candidate_pairs", "traj_contact_count")
+
+
+def collect(src):
+    """Keeps what the tests compare (the root twist of the link velocities, no body poses) as compressed .npz files."""
+    for name in CASES:
+        with open(os.path.join(src, f"ref_{name}.nkt"), "rb") as f:
+            arrays = nkt.unpack(f.read())
+        E, L = int(arrays["run"][0]), int(arrays["run"][1])
+        out = {k: arrays[k] for k in KEEP if k in arrays}
+        samples = len(arrays["traj_steps"])
+        if L:
+            out["traj_root_twist"] = arrays["traj_link_velocity"].reshape(samples, E, L, 6)[:, :, 0].copy()
+        np.savez_compressed(os.path.join(HERE, f"ref_gpu_{name}.npz"), **out)
+    with open(os.path.join(src, "ref_timing.jsonl")) as f:
+        lines = [line for line in f if line.startswith("{")]
+    with open(os.path.join(HERE, "ref_gpu_timing.jsonl"), "w") as f:
+        f.writelines(lines)
+    print("collected into", HERE)
+
+
+if __name__ == "__main__":
+    if len(sys.argv) >= 2 and sys.argv[1] == "prepare":
+        prepare()
+    elif len(sys.argv) >= 2 and sys.argv[1] == "collect":
+        collect(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "gpurun_out"))
+    else:
+        raise SystemExit(__doc__)

@@ -131,3 +131,20 @@ def run_laws(fn, which, x):
     out = np.zeros((len(x), n_out), np.float32)
     fn(which, len(x), x.ctypes.data, n_in, out.ctypes.data, n_out)
     return out
+
+
+def quadruped_moving_state(env_count, seed=0):
+    """Start state of the reference-GPU case with non-zero velocities: the seeded quadruped poses plus joint rates
+    N(0, 0.5) rad/s and a base twist N(0, 0.3) (angular then linear, base frame), so that joint accelerations and bias forces
+    are far from zero."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "nuka-physics_b200"))
+    from nuka import templates as T
+    st = T.quadruped_state(env_count, seed)
+    rng = np.random.Generator(np.random.PCG64(7 + seed))
+    qdot = np.zeros((env_count, 13), np.float32)
+    qdot[:, 1:] = rng.normal(0, 0.5, size=(env_count, 12))
+    twist = np.zeros((env_count, 13, 6), np.float32)
+    twist[:, 0, :] = rng.normal(0, 0.3, size=(env_count, 6))
+    return {"q": st["q"], "qdot": qdot, "base_pose": st["base_pose"], "link_velocity": twist.reshape(env_count, -1)}

@@ -1,0 +1,80 @@
+"""GPU parity against the reference's OWN GPU implementation: the CUDA path, through the C ABI, on the scene files and
+start states the unmodified reference was stepped on (tests/golden/ref_gpu_<case>.npz; see tests/refparity.py).
+
+Bars (fp32): link poses 1e-6, mass matrices and bias forces 1e-5, single-step post-solve velocities 1e-5, candidate pairs
+and contact counts bit-exact, 100-step trajectories 1e-4 in position (the contact-free arm and the landing quadruped
+alike).  Joint accelerations are held to the distance the reference itself keeps from the double-precision solve of its
+own M and bias (see tests/test_reference_parity_cpu.py)."""
+import numpy as np
+import pytest
+
+import nuka
+from nuka import Field as F
+
+import refparity as RP
+
+pytestmark = pytest.mark.gpu
+NAMES = {"q": F.JOINT_POSITION, "qdot": F.JOINT_VELOCITY, "base_pose": F.BASE_POSE, "link_velocity": F.LINK_VELOCITY}
+
+
+def make_world(device, case):
+    ref = RP.load(case)
+    if ref is None:
+        pytest.skip(f"no reference vectors for {case}")
+    tb, E, L, n, S = RP.template(case, ref)
+    w = nuka.World.create_from_template(device, tb.blob(), E)
+    st = RP.CASES[case][1](E)
+    for k in ("q", "qdot", "base_pose"):
+        if k in st:
+            w.upload(NAMES[k], st[k])
+    w.forward_kinematics()
+    if "link_velocity" in st:
+        w.upload(F.LINK_VELOCITY, st["link_velocity"])
+    return ref, w, E, L, n, S
+
+
+@pytest.mark.parametrize("case", sorted(RP.CASES))
+def test_dynamics_match_the_reference(device, case):
+    ref, w, E, L, n, S = make_world(device, case)
+    assert RP.err_env(w.download(F.ARTICULATION_LINK_POSE), ref["start_link_pose"].reshape(E, -1)) < 1e-6
+    assert np.array_equal(w.download(F.DRIVE_STIFFNESS), ref["start_kp"].reshape(E, L))
+    w.upload(F.DRIVE_STIFFNESS, np.zeros((E, L), np.float32)); w.upload(F.DRIVE_DAMPING, np.zeros((E, L), np.float32))
+    w.run_stage(1)
+    assert RP.err_env(w.download(F.MASS_MATRIX), ref["dyn_mass"].reshape(E, -1)) < 1e-5
+    exact = RP.exact_acceleration(ref["dyn_mass"], ref["dyn_bias"], n)
+    joints = slice(n - (L - 1), n)
+    scale = np.abs(exact[:, joints]).max(axis=1).max() + 1e-12
+    theirs = np.abs(ref["dyn_qddot"].reshape(E, L)[:, 1:] - exact[:, joints]).max() / scale
+    ours = np.abs(w.download(F.JOINT_ACCELERATION)[:, 1:] - exact[:, joints]).max() / scale
+    assert ours < max(2.0 * theirs, 1e-5), (ours, theirs)
+    if scale > 1.0:
+        assert RP.err_env(w.download(F.JOINT_ACCELERATION)[:, 1:], ref["dyn_qddot"].reshape(E, L)[:, 1:]) < 5e-5
+    w.destroy()
+
+
+@pytest.mark.parametrize("case", sorted(RP.CASES))
+def test_steps_match_the_reference(device, case):
+    ref, w, E, L, n, S = make_world(device, case)
+    steps = [int(s) for s in ref["traj_steps"]]
+    K = len(steps)
+    q, qd = ref["traj_q"].reshape(K, E, L), ref["traj_qdot"].reshape(K, E, L)
+    done = 0
+    for i, s in enumerate(steps):
+        w.step_n(s - done)
+        done = s
+        first = i == 0
+        assert RP.err_env(w.download(F.JOINT_POSITION), q[i]) < (1e-5 if first else 1e-4), (case, s)
+        RP.assert_velocity_parity(w.download(F.JOINT_VELOCITY), qd[i], first, (case, s, "joint rates"))
+        if ref["traj_base_pose"].size:
+            assert RP.err_env(w.download(F.BASE_POSE), ref["traj_base_pose"].reshape(K, E, 7)[i]) < (1e-5 if first else 1e-4)
+            twist = w.download(F.LINK_VELOCITY).reshape(E, L, 6)[:, 0]
+            RP.assert_velocity_parity(twist, ref["traj_root_twist"][i], first, (case, s, "root twist"))
+        assert not w.download(F.ENV_STATUS).any()
+        if S:
+            count = ref["traj_pair_count"].reshape(K, E)[i]
+            pairs = ref["traj_candidate_pairs"].reshape(K, E, S, 2)[i]
+            assert np.array_equal(w.download(F.PAIR_COUNT)[:, 0], count)
+            mine = w.download(F.CANDIDATE_PAIRS).reshape(E, S, 2)
+            assert all(np.array_equal(mine[e, :count[e]], pairs[e, :count[e]]) for e in range(E))
+            assert np.array_equal(w.download(F.CONTACT_COUNT), ref["traj_contact_count"].reshape(K, E, S)[i])
+    w.destroy()
