@@ -176,10 +176,10 @@ def cpu_baseline(state):
     w.refresh()
     w.set("link_velocity", state["link_velocity"])
     threads = orc.lib().orc_hw_threads()
-    w.step(10, threads)                      # rebuilds the contact cache the state transfer does not carry
+    w.step(60, threads)                      # rebuilds the contact cache and carried solver state the transfer does not hold
     median, times = _time_oracle(w, threads, 5, 6)
     return {"value": E * 6 / median, "unit": "env-steps/s", "cores": threads, "kind": "port",
-            "sample": f"all {E} envs x 6 steps, median of 5 repeats, started from this run's prepared state (+10 untimed steps), "
+            "sample": f"all {E} envs x 6 steps, median of 5 repeats, started from this run's prepared state (+60 untimed steps), "
                       f"OpenMP over envs, {flags}",
             "spread": [E * 6 / t for t in times]}
 

@@ -9,55 +9,68 @@
 #include <mutex>
 #include "nkb_solver.cuh"
 #include "nkb_lbvh.cuh"
+#include "nkb_manifold.cuh"
 #include "nkb_launch.h"
 
 namespace nkb {
 
-// Free rigid bodies: gyroscopic torque-free rotation + pose update (ops/articulation.cu:1059-1116,
-// ops/rigid_types.cuh:39-122).
+// Torque-free rotation of a free rigid body over one step, in its principal frame (the quantity of the reference's
+// SolveFreeRotation, ops/rigid_types.cuh:39-122, used by ops/articulation.cu:1059-1116): the implicit-midpoint form of
+// Euler's equations for the scaled angular momentum u,
+//     g(u) = u - u0 + c * (m_y m_z, m_z m_x, m_x m_y) = 0,   m = (u0 + u) / 2,   c = dt (a_y - a_z, a_z - a_x, a_x - a_y),
+// with a the scaled inverse principal inertias.  Newton's method: the Jacobian is the identity plus three off-diagonal
+// pairs, small enough to invert through its column triple products; a step is halved (at most 8 times) until the
+// residual's largest component drops; at most 12 steps to 1e-6.  `mid_out` is the midpoint angular velocity.
+struct FreeRotation {
+    V3 u0, c;
+    NKB_DEV V3 midpoint(V3 u) const { return (u0 + u) * 0.5f; }
+    NKB_DEV V3 residual(V3 u) const {
+        const V3 m = midpoint(u);
+        return mk3(u.x - u0.x + c.x * m.y * m.z, u.y - u0.y + c.y * m.z * m.x, u.z - u0.z + c.z * m.x * m.y);
+    }
+    NKB_DEV static float largest(V3 r) { return fmaxf(fabsf(r.x), fmaxf(fabsf(r.y), fabsf(r.z))); }
+    // Newton direction d with (dg/du) d = r at midpoint m, by Cramer's rule on the Jacobian's columns; false when singular
+    NKB_DEV bool direction(V3 m, V3 r, V3& d) const {
+        const V3 col0 = mk3(1.0f, 0.5f * c.y * m.z, 0.5f * c.z * m.y);
+        const V3 col1 = mk3(0.5f * c.x * m.z, 1.0f, 0.5f * c.z * m.x);
+        const V3 col2 = mk3(0.5f * c.x * m.y, 0.5f * c.y * m.x, 1.0f);
+        const V3 c12 = cross(col1, col2);
+        const float det = dot(col0, c12);
+        if (!isfinite(det) || fabsf(det) < 1.0e-12f) return false;
+        d = mk3(dot(r, c12), dot(col0, cross(r, col2)), dot(col0, cross(col1, r))) * (1.0f / det);
+        return true;
+    }
+};
+
 NKB_DEV bool solve_free_rotation(V3 w0, V3 inv_i, float dt, V3& mid_out) {
     mid_out = mk3(0.f, 0.f, 0.f);
-    const V3 m0 = mk3(w0.x / inv_i.x, w0.y / inv_i.y, w0.z / inv_i.z);
-    const float scale = fmaxf(fabsf(m0.x), fmaxf(fabsf(m0.y), fabsf(m0.z)));
-    if (scale == 0.0f) return true;
-    const V3 u0 = m0 * (1.0f / scale);
+    const V3 momentum = mk3(w0.x / inv_i.x, w0.y / inv_i.y, w0.z / inv_i.z);
+    const float scale = FreeRotation::largest(momentum);
+    if (scale == 0.0f) return true;                     // at rest
     const V3 a = inv_i * scale;
-    const V3 c = mk3(dt * (a.y - a.z), dt * (a.z - a.x), dt * (a.x - a.y));
-    V3 u = u0;
-    for (uint32_t it = 0; it <= 12u; ++it) {
-        const V3 mid = (u0 + u) * 0.5f;
-        const V3 r = mk3(u.x - u0.x + c.x * mid.y * mid.z, u.y - u0.y + c.y * mid.z * mid.x, u.z - u0.z + c.z * mid.x * mid.y);
-        const float res = fmaxf(fabsf(r.x), fmaxf(fabsf(r.y), fabsf(r.z)));
-        if (!isfinite(res)) return false;
-        if (res <= 1.0e-6f) { mid_out = mk3(a.x * mid.x, a.y * mid.y, a.z * mid.z); return true; }
-        if (it == 12u) break;
-        float j[3][4] = {{1.0f, 0.5f * c.x * mid.z, 0.5f * c.x * mid.y, r.x},
-                         {0.5f * c.y * mid.z, 1.0f, 0.5f * c.y * mid.x, r.y},
-                         {0.5f * c.z * mid.y, 0.5f * c.z * mid.x, 1.0f, r.z}};
-        for (int col = 0; col < 3; ++col) {
-            int piv = col;
-            for (int row = col + 1; row < 3; ++row) if (fabsf(j[row][col]) > fabsf(j[piv][col])) piv = row;
-            if (!isfinite(j[piv][col]) || fabsf(j[piv][col]) < 1.0e-12f) return false;
-            for (int k = col; k < 4; ++k) { const float tmp = j[col][k]; j[col][k] = j[piv][k]; j[piv][k] = tmp; }
-            for (int row = col + 1; row < 3; ++row) {
-                const float f = j[row][col] / j[col][col];
-                for (int k = col + 1; k < 4; ++k) j[row][k] -= f * j[col][k];
-            }
+    FreeRotation eq;
+    eq.u0 = momentum * (1.0f / scale);
+    eq.c = mk3(dt * (a.y - a.z), dt * (a.z - a.x), dt * (a.x - a.y));
+    V3 u = eq.u0;
+    for (int newton = 0; newton <= 12; ++newton) {
+        const V3 r = eq.residual(u);
+        const float size = FreeRotation::largest(r);
+        if (!isfinite(size)) return false;
+        if (size <= 1.0e-6f) {
+            const V3 m = eq.midpoint(u);
+            mid_out = mk3(a.x * m.x, a.y * m.y, a.z * m.z);
+            return true;
         }
         V3 d;
-        d.z = j[2][3] / j[2][2];
-        d.y = (j[1][3] - j[1][2] * d.z) / j[1][1];
-        d.x = (j[0][3] - j[0][1] * d.y - j[0][2] * d.z) / j[0][0];
-        bool accepted = false; float alpha = 1.0f;
-        for (int bt = 0; bt < 8; ++bt) {
-            const V3 tt = u - d * alpha;
-            const V3 md = (u0 + tt) * 0.5f;
-            const V3 tr = mk3(tt.x - u0.x + c.x * md.y * md.z, tt.y - u0.y + c.y * md.z * md.x, tt.z - u0.z + c.z * md.x * md.y);
-            const float tres = fmaxf(fabsf(tr.x), fmaxf(fabsf(tr.y), fabsf(tr.z)));
-            if (isfinite(tres) && tres < res) { u = tt; accepted = true; break; }
-            alpha *= 0.5f;
+        if (newton == 12 || !eq.direction(eq.midpoint(u), r, d)) return false;
+        float fraction = 1.0f;
+        bool improved = false;
+        for (int halving = 0; halving < 8 && !improved; ++halving, fraction *= 0.5f) {
+            const V3 trial = u - d * fraction;
+            const float trial_size = FreeRotation::largest(eq.residual(trial));
+            if (isfinite(trial_size) && trial_size < size) { u = trial; improved = true; }
         }
-        if (!accepted) break;
+        if (!improved) return false;
     }
     return false;
 }

@@ -40,6 +40,9 @@ NKB_HOST_DEVICE inline uint32_t lbvh_scratch_words(uint32_t B) {
     return 2u * lbvh_pow2(B) + (B - 1u) * 10u + 4u * B + B * ((B + 31u) / 32u);
 }
 
+// Scratch words of the narrowphase (nkb_manifold.cuh): one world frame per collidable row and two polygon staging areas.
+NKB_HOST_DEVICE inline uint32_t manifold_scratch_words(uint32_t B) { return 12u * B + 64u; }
+
 struct Config {
     float dt;
     float gravity[3];

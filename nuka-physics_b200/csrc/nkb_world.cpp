@@ -326,8 +326,8 @@ void World::BuildLayout() {
     const uint32_t SC = tv.slot_cap;
     s.pairs = take(SC); s.ccount = take(SC); s.cpoint = take(12 * SC); s.cnormal = take(12 * SC); s.cdepth = take(4 * SC);
     s.cfeat = take(8 * SC);                       // contact identity words
-    // before the heads exist the region serves the tree broadphase as scratch
-    s.heads = take(std::max(kHeadStride * tv.head_cap, SC != 0u ? lbvh_scratch_words(B) : 0u));
+    // before the heads exist the region serves the tree broadphase and then the narrowphase as scratch
+    s.heads = take(std::max(kHeadStride * tv.head_cap, SC != 0u ? std::max(lbvh_scratch_words(B), manifold_scratch_words(B)) : 0u));
     // the Jacobian pool also holds the AABBs (dead once the narrowphase is done) and, after the solve, the cache staging
     // entries + owner marks
     const uint32_t stage_cap = std::min(tv.point_cap, 4u * SC);

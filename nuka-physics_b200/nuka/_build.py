@@ -6,7 +6,11 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "libnuka_b200.so")
 SOURCES = ["nkb_step_n1.cu", "nkb_step_n1r.cu", "nkb_step_n2.cu", "nkb_step_n2r.cu", "nkb_kernels.cu", "nkb_static_reset.cu", "nkb_world.cpp", "nkb_abi.cpp"]
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--ftz=true", "--prec-div=false", "--prec-sqrt=false", "-Xcompiler", "-fPIC"]
+# nvcc defaults for floating point, as the reference builds its physics ops: IEEE division and square root, denormals
+# kept, fused multiply-add on.  (Approximate division / square root and flush-to-zero for the whole library measured 4 %
+# faster on the 4096-env quadruped step and changed no parity figure; the few places that use rsqrtf / __fdividef on
+# purpose say so where they do.)
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 
 
 def _stale():
