@@ -206,6 +206,83 @@ def captured_counters():
         return {}
 
 
+OTHER_WORKLOADS = {
+    # name: (description, default envs per GPU, settle steps, template, state, upload fields, (nj, F, L, free bodies))
+    "c1": ("configs[0]: 7-link fixed-base arm, no contacts, dt 1/500", 4096, 200, lambda T: T.arm7(0), lambda T, E, s: T.arm7_state(E, s), (7, 0, 8, 0)),
+    "c3": ("configs[2]: 35-coordinate humanoid, capsules, ground + limb self-contact, dt 1/200, 8 iterations", 8192, 300,
+           lambda T: T.humanoid(0), lambda T, E, s: T.humanoid_state(E, s), (29, 1, 30, 0)),
+    "c4": ("configs[3]: 48 free boxes on a plane, dt 1/240, 8 iterations", 16384, 240,
+           lambda T: T.box_pile(0), lambda T, E, s: T.box_pile_state(E, s), (0, 0, 0, 48)),
+    "c5": ("configs[4]'s shard: quadruped + 4 free 0.1 m boxes, dt 1/200, 4 iterations", 8192, 300,
+           lambda T: T.quadruped(0, boxes=4), lambda T, E, s: T.quadruped_state(E, s), (12, 1, 13, 4)),
+}
+
+
+def run_other_workload(args):
+    """`--workload c1|c3|c4|c5`: the other configurations of BASELINE.json on one GPU, device-timed on a prepared state.
+    They are parity-test configurations, not the headline; the line has the same keys minus the CPU and end-to-end legs."""
+    import torch
+    import nuka
+    from nuka import Field as F, templates as T
+    text, default_envs, settle, make, state, (nj, nf, nl, nb) = OTHER_WORKLOADS[args.workload]
+    E = args.envs if args.envs != ENVS_PER_GPU else default_envs
+    settle = args.settle if args.settle != SETTLE_STEPS else settle
+    dev = nuka.Device.create(0)
+    tb = make(T)
+    w = nuka.World.create_from_template(dev, tb.blob(), E)
+    names = {"q": F.JOINT_POSITION, "qdot": F.JOINT_VELOCITY, "base_pose": F.BASE_POSE, "body_pose": F.RIGID_BODY_TRANSFORM}
+    for k, v in state(T, E, 0).items():
+        w.upload(names[k], v)
+    w.forward_kinematics()
+    w.set_contact_readout(False)
+    ptr = ctypes.c_void_p()
+    nuka._check(nuka._abi.lib().nuka_world_get_stream(w._h, ctypes.byref(ptr)))
+    stream = torch.cuda.ExternalStream(ptr.value)
+    flush = torch.empty(256 * 1024 * 1024 // 4, dtype=torch.float32, device="cuda")
+    t0 = time.perf_counter()
+    with torch.cuda.stream(stream):
+        w.step_n(settle)
+        stream.synchronize()
+        settle_s = time.perf_counter() - t0
+        for _ in range(args.warmup):
+            w.step()
+        stream.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        for k in range(args.steps):
+            flush.add_(1.0)
+            starts[k].record(stream)
+            w.step()
+            ends[k].record(stream)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        w.set_contact_readout(True)
+        w.step()
+    w.synchronize()
+    ms = sum(a.elapsed_time(b) for a, b in zip(starts, ends)) / args.steps
+    counts = w.download(F.CONTACT_COUNT) if tb.cfg["max_contacts"] else np.zeros((E, 1), np.uint32)
+    slots, points = float((counts > 0).sum(axis=1).mean()), float(counts.sum(axis=1).mean())
+    status = int(np.bitwise_or.reduce(w.download(F.ENV_STATUS).reshape(-1)))
+    info = w.info
+    bytes_per = 12 * nj + 52 * nf + 8 * nj + 52 * nf + 52 * nl + 104 * nb + 8 * (nj + 3 * points) + 8 * slots + 32 * points
+    peak, peak_kind = hbm_peak()
+    value = E / (ms * 1e-3)
+    print(json.dumps({
+        "metric": f"env-steps/sec, {args.workload}", "value": value, "unit": "env-steps/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": text, "envs_per_gpu": E, "dt": float(info.fixed_dt), "velocity_iterations": int(tb.cfg["vel_iters"]),
+                   "settle_steps": settle, "settle_seconds": settle_s, "l2_flush_between_steps": True, "mean_contact_slots": slots,
+                   "mean_contact_points": points, "shared_bytes_per_env": int(info.shared_bytes_per_env), "status_or": status},
+        "roofline": {"bound": "hbm", "achieved": bytes_per * value / 1e9, "peak": peak, "unit": "GB/s", "frac": bytes_per * value / 1e9 / peak,
+                     "traffic": None, "peak_source": peak_kind, "algorithmic_bytes_per_env_step": bytes_per, "kernel": "step_kernel", "kernel_ms": ms},
+        "gpu_launches": args.steps, "clocks": clocks}))
+    w.destroy()
+    dev.destroy()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -218,12 +295,17 @@ def main():
     ap.add_argument("--no-gather", action="store_true", help="N > 1: skip the per-step observation all-gather")
     ap.add_argument("--no-extra", action="store_true", help="skip the configs[4] figure (65536 quadruped + 4-box envs split over the ranks)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload", default="c2", choices=["c2"] + sorted(OTHER_WORKLOADS),
+                    help="c2 is the headline (configs[1]); the others are single-GPU lines of the parity configurations")
     ap.add_argument("--boxes", type=int, default=0,
                     help="free 0.1 m boxes beside each quadruped: 4 with --envs 8192 per GPU is configs[4]'s shard (not the headline workload)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload != "c2":
+        run_other_workload(args)
         return
     import torch
     import nuka
@@ -328,18 +410,8 @@ def main():
     sampler.start()
     hold_ms, launches = timed(w, stream, args.steps, args.warmup, exchange=exchange)
     clocks = sampler.stop()
-    # active drives: each step copies one of a pool of target sets (standing pose + noise) into DRIVE_TARGET on the stream
-    targets_view = w.view(F.DRIVE_TARGET).torch()
-    hold_targets = targets_view.clone()
-    gen = torch.Generator(device=cuda).manual_seed(1234 + rank)
-    pool = [hold_targets + ACTIVE_NOISE * torch.randn(hold_targets.shape, generator=gen, device=cuda) for _ in range(ACTIVE_POOL)]
-    for p in pool:
-        p[:, 0] = hold_targets[:, 0]
-    active_steps = max(10, args.steps // 2)
-    active_ms, _ = timed(w, stream, active_steps, max(args.warmup, 10), before_step=lambda k: targets_view.copy_(pool[k % ACTIVE_POOL]), exchange=exchange)
+    # contact statistics of the measured (hold) state
     with torch.cuda.stream(stream):
-        targets_view.copy_(hold_targets)
-        w.step_n(50)                              # back to the hold state for the end-to-end leg
         w.set_contact_readout(True)
         w.step()
     w.synchronize()
@@ -349,7 +421,7 @@ def main():
     sweeps = float(w.download(F.SOLVER_SWEEPS).mean())
     w.set_contact_readout(False)
 
-    # ---- end to end through the C ABI with host buffers ---------------------------------------------------------------
+    # ---- end to end through the C ABI with host buffers, on the same hold state -----------------------------------------
     lib = nuka._abi.lib()
     targets = torch.from_numpy(w.download(F.DRIVE_TARGET)).pin_memory()
     out_q = torch.empty((E, NL), dtype=torch.float32).pin_memory()
@@ -377,6 +449,18 @@ def main():
         t0 = time.perf_counter()
         e2e_step()                               # the downloads synchronise: the step's results are on the host when it returns
         e2e_s += time.perf_counter() - t0
+    # active drives: each step copies one of a pool of target sets (standing pose + noise) into DRIVE_TARGET on the stream
+    targets_view = w.view(F.DRIVE_TARGET).torch()
+    hold_targets = targets_view.clone()
+    gen = torch.Generator(device=cuda).manual_seed(1234 + rank)
+    pool = [hold_targets + ACTIVE_NOISE * torch.randn(hold_targets.shape, generator=gen, device=cuda) for _ in range(ACTIVE_POOL)]
+    for p in pool:
+        p[:, 0] = hold_targets[:, 0]
+    active_steps = max(10, args.steps // 2)
+    active_ms, _ = timed(w, stream, active_steps, max(args.warmup, 10), before_step=lambda k: targets_view.copy_(pool[k % ACTIVE_POOL]), exchange=exchange)
+    with torch.cuda.stream(stream):
+        targets_view.copy_(hold_targets)
+
     hold_total, active_total, e2e_total = max_over_ranks([sum(hold_ms), sum(active_ms), e2e_s * 1e3])
     per_rank = None
     if distributed:

@@ -81,9 +81,11 @@ uint64_t Fnv1a(uint64_t h, const void* data, size_t bytes) {
     return h;
 }
 
-HandleTable<DeviceRecord>& Devices() { static HandleTable<DeviceRecord> t; return t; }
-HandleTable<WorldRecord>& Worlds() { static HandleTable<WorldRecord> t; return t; }
-HandleTable<CheckpointRecord>& Checkpoints() { static HandleTable<CheckpointRecord> t; return t; }
+// The tables live until the process ends and are never destroyed: an object a caller left alive must not run its
+// destructor (CUDA calls) during static destruction, when the CUDA runtime may already be gone.
+HandleTable<DeviceRecord>& Devices() { static auto* t = new HandleTable<DeviceRecord>; return *t; }
+HandleTable<WorldRecord>& Worlds() { static auto* t = new HandleTable<WorldRecord>; return *t; }
+HandleTable<CheckpointRecord>& Checkpoints() { static auto* t = new HandleTable<CheckpointRecord>; return *t; }
 std::atomic<uint64_t> g_world_serial{0};
 
 template <typename Fn>

@@ -143,8 +143,11 @@ NKB_DEV void stage_store_bodies(Env& e, bool velocities) {
 // SM; tighter caps (144 or 128 registers, 14 warps per SM) slow every warp by more than the extra residency returns.
 // NR = coordinates per lane: 1 for articulations of up to 32 coordinates, 2 for up to 64.
 // kRigid = the world has free rigid bodies; without them the rigid-block solver code is compiled out.
+#ifndef NKB_MAXNREG
+#define NKB_MAXNREG 176
+#endif
 template <int NR, bool kRigid>
-__global__ void __maxnreg__(176) step_kernel(const __grid_constant__ StepParams p) {
+__global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ StepParams p) {
     extern __shared__ __align__(16) float smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     uint32_t env = blockIdx.x * (blockDim.x >> 5) + warp;

@@ -75,9 +75,11 @@ def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0,
 
     tops = [n for n in scene.get("tree", []) if "rigid_body" in n]
     grounds = [n for n in tops if is_ground(n)]
-    roots = [n for n in tops if not is_ground(n)]
-    if len(roots) != 1:
-        raise ValueError("exactly one articulated tree is supported")
+    # a top-level body with child bodies roots the articulation; a lone dynamic body is a free rigid body
+    roots = [n for n in tops if not is_ground(n) and (any("rigid_body" in c for c in n.get("children", [])) or n["rigid_body"].get("is_static"))]
+    free = [n for n in tops if not is_ground(n) and n not in roots]
+    if len(roots) > 1:
+        raise ValueError("at most one articulated tree is supported")
     self_collision = self_collision or scene_filters
     tb = T.TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=0)
     shape_rows = []
@@ -142,7 +144,20 @@ def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0,
             if "rigid_body" in child:
                 add(child, link)
 
-    add(roots[0], None)
+    if roots:
+        add(roots[0], None)
+    for node in free:       # in document order, after the articulation's rows: the collidable row order both cookers use
+        rb = node["rigid_body"]
+        shapes = [c["collision_shape"] for c in node.get("children", []) if "collision_shape" in c]
+        if len(shapes) != 1:
+            raise ValueError("a free body needs exactly one collision shape")
+        cs = shapes[0]
+        (pos, quat), (ipos, iquat) = _pose(node, "transform"), _pose(rb, "inertial")
+        if np.abs(np.array(_pose(cs, "local")[0])).max() > 0 or np.abs(np.array(ipos)).max() > 0 or abs(abs(iquat[0]) - 1.0) > 1e-9:
+            raise ValueError("free bodies with an offset shape or inertial frame are not carried over")
+        bits = dict(contype=int(cs.get("contype", 1)), conaffinity=int(cs.get("conaffinity", 1)))
+        tb.add_free_body(_shape_of(cs), float(rb["mass"]), [float(v) for v in rb["inertia"]], (*pos, *quat), mu=float(cs.get("friction_mu", 1.0)), **bits)
+        shape_rows.append(None)
     for g in grounds:
         plane = next(c["collision_shape"] for c in g["children"] if c.get("collision_shape", {}).get("type") == "plane")
         (gpos, gquat) = _pose(g, "transform")
@@ -179,7 +194,8 @@ def scene_from_builder(tb):
         for c in children[i]:
             number(c)
 
-    number(0)
+    if tb.links:
+        number(0)
     joint_id = {}
     for i in order:
         if i != 0:
@@ -223,12 +239,18 @@ def scene_from_builder(tb):
         out["children"] = kids + [node(c) for c in children[i]]
         return out
 
-    tree = [node(0)]
+    tree = [node(0)] if tb.links else []
     for k, b in enumerate(tb.bodies):
         if b["link"] != T.NOLINK:
             continue
-        if b["kind"] != T.PLANE or b["inv_mass"] != 0.0:
-            raise ValueError("free bodies are not written; only ground planes")
+        if b["inv_mass"] > 0.0:
+            tree.append({"name": f"body{k}", "transform": _frame(b["pose"][:3], b["pose"][3:]),
+                         "rigid_body": {"parent_id": 4294967295, "inertial": _frame(b["inertial_pos"], b["inertial_quat"]), "mass": 1.0 / float(b["inv_mass"]),
+                                        "inertia": [1.0 / float(v) for v in b["inv_inertia"]], "is_static": False},
+                         "children": [shape_node(b, "shape")]})
+            continue
+        if b["kind"] != T.PLANE:
+            raise ValueError("static bodies other than ground planes are not written")
         tree.append({"name": f"ground{k}", "transform": _frame(b["pose"][:3], b["pose"][3:]),
                      "rigid_body": {"parent_id": 4294967295, "inertial": _frame(), "mass": 0.0, "inertia": [0.0, 0.0, 0.0], "is_static": True},
                      "children": [shape_node(b, "plane")]})

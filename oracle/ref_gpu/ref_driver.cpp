@@ -10,6 +10,8 @@
 //              [--dump out.nkt]               model tables + single-op dynamics + trajectory samples
 //              [--steps N --every k]          trajectory length and sampling stride
 //              [--time warm,timed,repeats]    wall-clock timing of StepConfigured in eager and graph mode, JSON on stdout
+//              [--active sigma]               with --time: every timed step first uploads fresh drive targets (cooked targets +
+//                                             N(0, sigma) rad, a pool of 16 sets), the regime of an RL caller; eager mode only
 //
 // Reference entry points used (paths in the reference): scene::nks::Load (src/scene/format/nks.hpp),
 // scene::cook::CookToModel (src/scene/cook/cook_to_model.hpp), nk::World (src/nk/pipeline/world.hpp),
@@ -19,6 +21,7 @@
 
 #include <algorithm>
 #include <chrono>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -163,6 +166,7 @@ struct Args {
     float dt = 1.0f / 200.0f;
     bool contacts = true, cook_only = false;
     int warm = 0, timed = 0, repeats = 1;
+    float active_sigma = 0.0f;
 };
 
 template <typename T>
@@ -191,6 +195,7 @@ int main(int argc, char** argv) {
         else if (k == "--no-contacts") a.contacts = false;
         else if (k == "--cook-only") a.cook_only = true;
         else if (k == "--time") { std::sscanf(next(), "%d,%d,%d", &a.warm, &a.timed, &a.repeats); }
+        else if (k == "--active") a.active_sigma = static_cast<float>(std::atof(next()));
         else { std::fprintf(stderr, "unknown argument %s\n", k.c_str()); return 2; }
     }
     if (a.scene.empty()) { std::fprintf(stderr, "--scene is required\n"); return 2; }
@@ -319,6 +324,34 @@ int main(int argc, char** argv) {
                 std::sort(ms.begin(), ms.end());
                 if (ok && !ms.empty()) std::printf(", \"%s\": %.5f", mode == 0 ? "eager_ms_per_step" : "graph_ms_per_step", ms[ms.size() / 2]);
                 else std::printf(", \"%s\": null", mode == 0 ? "eager_ms_per_step" : "graph_ms_per_step");
+            }
+            if (a.active_sigma > 0.0f && L != 0u) {
+                // fresh targets every step: one host-to-device copy of E x L floats, then one eager step
+                world.SetExecutionMode(nk::World::ExecutionMode::Eager);
+                const std::vector<float> hold = Download<float>(world, nk::FieldId::DriveTarget, size_t{E} * L);
+                std::vector<std::vector<float>> pool(16, hold);
+                uint64_t rng = 0x9e3779b97f4a7c15ull;
+                auto uniform = [&]() { rng ^= rng << 13; rng ^= rng >> 7; rng ^= rng << 17; return static_cast<float>((rng >> 11) * (1.0 / 9007199254740992.0)); };
+                for (auto& set : pool)
+                    for (size_t i = 0; i < set.size(); ++i) {
+                        if (i % L == 0u) continue;                                           // slot 0 is the root
+                        const float u1 = std::max(uniform(), 1.0e-7f), u2 = uniform();
+                        set[i] += a.active_sigma * std::sqrt(-2.0f * std::log(u1)) * std::cos(6.2831853f * u2);
+                    }
+                bool ok = true;
+                uint32_t submitted = 0;
+                auto one = [&](int k) {
+                    ok = ok && world.GetData().UploadField(nk::FieldId::DriveTarget, pool[k % 16].data(), pool[k % 16].size() * 4) &&
+                         world.StepConfigured(1u, &submitted) == nphi::Status::Ok;
+                };
+                for (int k = 0; k < std::max(a.warm / 10, 10); ++k) one(k);
+                world.Synchronize();
+                const auto t0 = std::chrono::steady_clock::now();
+                for (int k = 0; k < a.timed; ++k) one(k);
+                ok = ok && world.Synchronize() == nphi::Status::Ok;
+                const double wall = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+                if (ok) std::printf(", \"active_sigma\": %g, \"active_eager_ms_per_step\": %.5f", a.active_sigma, wall / a.timed);
+                else std::printf(", \"active_eager_ms_per_step\": null");
             }
             const auto status = Download<uint32_t>(world, nk::FieldId::EnvStatus, E);
             uint32_t any = 0; for (uint32_t s : status) any |= s;

@@ -35,20 +35,29 @@ CASES = {
     "quadruped": (lambda: T.quadruped(0), lambda E: T.quadruped_state(E, 0), 1.0 / 200.0, 4, 100, 20),
     # the same robot started with joint rates and a base twist: meaningful joint accelerations, airborne then landing
     "quadruped_moving": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_moving_state(E, 0), 1.0 / 200.0, 4, 40, 10),
+    # free rigid boxes dropping onto the plane and each other: box-box and box-plane manifolds, rigid blocks in the solver
+    "pile12": (lambda: T.box_pile(0, count=12), lambda E: T.box_pile_state(E, 0, count=12), 1.0 / 240.0, 8, 60, 20),
+    # configs[4]'s env: the quadruped with four free boxes around it
+    "quadbox": (lambda: T.quadruped(0, boxes=4), lambda E: T.quadruped_state(E, 0), 1.0 / 200.0, 4, 60, 20),
+    # configs[2]'s env: the 35-coordinate humanoid with ground and limb self-contact
+    "humanoid": (lambda: T.humanoid(0), lambda E: T.humanoid_state(E, 0), 1.0 / 200.0, 8, 40, 10),
 }
+SCENE_OF = {"quadruped_moving": "quadruped"}
+# throughput of the reference on the other configurations: (scene case, envs, dt, iterations, warm-up, timed steps)
+TIMINGS = [("humanoid", 8192, 1.0 / 200.0, 8, 100, 100), ("quadbox", 8192, 1.0 / 200.0, 4, 100, 100), ("pile48", 16384, 1.0 / 240.0, 8, 60, 20)]
 
 
 def prepare():
     os.makedirs(RUN, exist_ok=True)
-    lines = ["#!/bin/bash", "# written by tests/golden/make_ref_gpu_vectors.py", "set -e", 'cd "$(dirname "$0")"',
+    lines = ["#!/bin/bash", "# written by tests/golden/make_ref_gpu_vectors.py", 'cd "$(dirname "$0")"',
              'OUT="${OUT:-../../../gpurun_out}"', 'mkdir -p "$OUT"', ': > "$OUT/ref_timing.jsonl"']
     for name, (make, state, dt, iters, steps, every) in CASES.items():
         tb = make()
         with open(os.path.join(RUN, f"{name}.nks"), "w") as f:
             json.dump(nks.scene_from_builder(tb), f)
-        scene = "quadruped" if name == "quadruped_moving" else name
+        scene = SCENE_OF.get(name, name)
         shutil.copy(os.path.join(RUN, f"{name}.nks"), os.path.join(HERE, f"scene_{scene}.nks"))
-        st = {k: np.ascontiguousarray(v, np.float32) for k, v in state(ENVS).items() if k in ("q", "qdot", "base_pose", "link_velocity")}
+        st = {k: np.ascontiguousarray(v, np.float32).reshape(ENVS, -1) for k, v in state(ENVS).items() if k in ("q", "qdot", "base_pose", "link_velocity", "body_pose")}
         with open(os.path.join(RUN, f"{name}_state.nkt"), "wb") as f:
             f.write(nkt.pack(st))
         subprocess.run([DRIVER, "--scene", os.path.join(RUN, f"{name}.nks"), "--envs", "1", "--cook-only", "--dump",
@@ -63,7 +72,12 @@ def prepare():
                  '--time 100,1000,3 >> "$OUT/ref_timing.jsonl"')
     # the same after 1000 settle steps (the prepared state bench.py measures on): 1000 untimed, then 200 timed
     lines.append('../ref_driver --scene quadruped.nks --envs 4096 --dt 0.005 --vel-iters 4 --state quadruped_state4096.nkt '
-                 '--time 1000,200,1 >> "$OUT/ref_timing.jsonl"')
+                 '--time 1000,200,1 --active 0.15 >> "$OUT/ref_timing.jsonl"')
+    with open(os.path.join(RUN, "pile48.nks"), "w") as f:
+        json.dump(nks.scene_from_builder(T.box_pile(0, count=48)), f)
+    for scene, envs, dt, iters, warm, timed in TIMINGS:
+        lines.append(f'timeout 300 ../ref_driver --scene {scene}.nks --envs {envs} --dt {dt!r} --vel-iters {iters} --time {warm},{timed},1 '
+                     f'>> "$OUT/ref_timing.jsonl" || echo "{{\\"scene\\": \\"{scene}.nks\\", \\"envs\\": {envs}, \\"failed\\": $?}}" >> "$OUT/ref_timing.jsonl"')
     with open(os.path.join(RUN, "run.sh"), "w") as f:
         f.write("\n".join(lines) + "\n")
     print("prepared", RUN)

@@ -20,7 +20,12 @@ CASES = {
     "arm7": ("arm7", lambda E: T.arm7_state(E, 0)),
     "quadruped": ("quadruped", lambda E: T.quadruped_state(E, 0)),
     "quadruped_moving": ("quadruped", lambda E: ref_cases.quadruped_moving_state(E, 0)),
+    "pile12": ("pile12", lambda E: {"body_pose": T.box_pile_state(E, 0, count=12)["body_pose"].reshape(E, -1)}),
+    "quadbox": ("quadbox", lambda E: T.quadruped_state(E, 0)),
+    "humanoid": ("humanoid", lambda E: T.humanoid_state(E, 0)),
 }
+# contact points per env that get solver rows, where the procedural template sets its own capacity
+MAX_POINTS = {"pile12": 72, "quadbox": 40, "humanoid": 48}
 
 
 def load(case):
@@ -35,7 +40,7 @@ def template(case, ref):
     E, L, n, B, S, iters = (int(v) for v in ref["run"][:6])
     scene = CASES[case][0]
     tb = nks.cook(os.path.join(GOLDEN, f"scene_{scene}.nks"), dt=float(ref["run_dt"][0]), vel_iters=iters, kp=0.0, kd=0.0,
-                  scene_filters=True, ground_height=None, max_contacts=S)
+                  scene_filters=True, ground_height=None, max_contacts=S, max_points=MAX_POINTS.get(case))
     return tb, E, L, n, S
 
 
