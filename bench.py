@@ -200,7 +200,7 @@ def fp32_peak(device_index):
 def captured_counters():
     """Per-launch counters of one ncu capture of the step kernel on the prepared state (profiles/), or {}."""
     try:
-        with open(os.path.join(ROOT, "profiles", "step_kernel_quadruped_counters.json")) as f:
+        with open(os.path.join(ROOT, "profiles", "step_kernel_quadruped_counters.txt")) as f:
             return json.load(f)
     except Exception:
         return {}

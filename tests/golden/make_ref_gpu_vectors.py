@@ -86,16 +86,20 @@ def prepare():
 KEEP = ("run", "run_dt", "dyn_qddot", "dyn_mass", "dyn_bias", "start_link_pose", "start_kp", "start_kd", "start_force_limit",
         "start_drive_target", "traj_steps", "traj_q", "traj_qdot", "traj_base_pose", "traj_status", "traj_pair_count",
         "traj_candidate_pairs", "traj_contact_count")
+FREE_BODY_CASES = ("pile12", "quadbox")     # body poses are kept where free bodies carry state of their own
 
 
 def collect(src):
-    """Keeps what the tests compare (the root twist of the link velocities, no body poses) as compressed .npz files."""
+    """Keeps what the tests compare (the root twist of the link velocities; body poses only where free bodies exist) as
+    compressed .npz files."""
     for name in CASES:
         with open(os.path.join(src, f"ref_{name}.nkt"), "rb") as f:
             arrays = nkt.unpack(f.read())
         E, L = int(arrays["run"][0]), int(arrays["run"][1])
         out = {k: arrays[k] for k in KEEP if k in arrays}
         samples = len(arrays["traj_steps"])
+        if name in FREE_BODY_CASES:
+            out["traj_body_pose"] = arrays["traj_body_pose"]
         if L:
             out["traj_root_twist"] = arrays["traj_link_velocity"].reshape(samples, E, L, 6)[:, :, 0].copy()
         np.savez_compressed(os.path.join(HERE, f"ref_gpu_{name}.npz"), **out)

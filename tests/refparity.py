@@ -62,16 +62,58 @@ def err_envs(got, want, floor=0.0):
     return d / np.maximum(np.maximum(np.abs(want).reshape(E, -1).max(axis=1), floor), 1e-300)
 
 
-def assert_velocity_parity(got, want, first, tag):
+# Cases whose contact sequence is chaotic (boxes tumbling in a pile, a ragdoll folding onto itself): one different
+# last bit decides which corner touches first, and single envs leave the common trajectory within tens of steps.  A CPU
+# evaluation of the reference's own algorithm and the reference's GPU output show it between themselves: at 60 steps of
+# the pile the median env differs by 5e-6 and the worst by 6e-2, while candidate pairs and contact counts stay
+# bit-equal in all 128 envs at every sample.  For these cases the trajectory bars apply to the 90th percentile of the
+# envs, and the worst env is only held to 0.2.
+CHAOTIC = ("pile12", "humanoid")
+
+
+def assert_position_parity(got, want, first, tag, case, absolute=False):
+    """Positions.  After one step: 1e-5 in every env.  Along a trajectory: 1e-4 in every env, or, for the chaotic cases,
+    in 90 % of the envs with the median below 1e-5.  `absolute` measures against max(|x|, 1) (body poses in metres)."""
+    d = err_envs(got, want, floor=1.0 if absolute else 0.0)
+    if first:
+        assert d.max() < 1e-5, (tag, float(d.max()))
+    elif case in CHAOTIC:
+        assert np.median(d) < 1e-5 and np.percentile(d, 90) < 1e-4 and d.max() < 0.2, \
+            (tag, float(np.median(d)), float(np.percentile(d, 90)), float(d.max()))
+    else:
+        assert d.max() < 1e-4, (tag, float(d.max()))
+
+
+def assert_velocity_parity(got, want, first, tag, case=None):
     """Post-solve velocities.  After one step: within 1e-5 for at least 95 % of the envs and 1e-4 for all.  The block
     descent stops at its sweep limit in envs whose feet start inside the ground, and an iteration that has not converged
     amplifies the last-bit differences between two fp32 evaluations (the reference's own GPU result and a CPU evaluation of
-    the same algorithm differ by 2e-5 in 2 % of these envs, by 1e-7 in the rest).  Along a trajectory: 1e-3."""
+    the same algorithm differ by 2e-5 in 2 % of these envs, by 1e-7 in the rest).  Along a trajectory: 1e-3 (90 % of the
+    envs in the chaotic cases)."""
     d = err_envs(got, want, floor=1.0)
     if first:
         assert np.percentile(d, 95) < 1e-5 and d.max() < 1e-4, (tag, float(np.percentile(d, 95)), float(d.max()))
+    elif case in CHAOTIC:
+        assert np.percentile(d, 90) < 1e-3, (tag, float(np.percentile(d, 90)))
     else:
         assert d.max() < 1e-3, (tag, float(d.max()))
+
+
+def start_state(case, E):
+    """The per-env start state of a case, keyed by the names both worlds use (q, qdot, base_pose, body_pose)."""
+    return {k: v for k, v in CASES[case][1](E).items() if k in ("q", "qdot", "base_pose", "body_pose", "link_velocity")}
+
+
+def acceleration_errors(ref, mine, E, L, n):
+    """(ours, theirs): distance of this implementation's and of the reference's joint accelerations from the
+    double-precision solve of the reference's own M and bias, over the size of the largest exact acceleration of any
+    coordinate (the base's included: the joints of a robot in free fall do not accelerate at all)."""
+    exact = exact_acceleration(ref["dyn_mass"], ref["dyn_bias"], n)
+    joints = slice(n - (L - 1), n)
+    scale = np.abs(exact).max() + 1e-12
+    theirs = np.abs(ref["dyn_qddot"].reshape(E, L)[:, 1:] - exact[:, joints]).max() / scale
+    ours = np.abs(np.asarray(mine, np.float64)[:, 1:] - exact[:, joints]).max() / scale
+    return ours, theirs, float(np.abs(exact[:, joints]).max())
 
 
 def exact_acceleration(mass, bias, n):

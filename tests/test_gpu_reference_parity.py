@@ -14,7 +14,9 @@ from nuka import Field as F
 import refparity as RP
 
 pytestmark = pytest.mark.gpu
-NAMES = {"q": F.JOINT_POSITION, "qdot": F.JOINT_VELOCITY, "base_pose": F.BASE_POSE, "link_velocity": F.LINK_VELOCITY}
+NAMES = {"q": F.JOINT_POSITION, "qdot": F.JOINT_VELOCITY, "base_pose": F.BASE_POSE, "body_pose": F.RIGID_BODY_TRANSFORM,
+         "link_velocity": F.LINK_VELOCITY}
+ARTICULATED = sorted(c for c in RP.CASES if c != "pile12")
 
 
 def make_world(device, case):
@@ -23,8 +25,8 @@ def make_world(device, case):
         pytest.skip(f"no reference vectors for {case}")
     tb, E, L, n, S = RP.template(case, ref)
     w = nuka.World.create_from_template(device, tb.blob(), E)
-    st = RP.CASES[case][1](E)
-    for k in ("q", "qdot", "base_pose"):
+    st = RP.start_state(case, E)
+    for k in ("q", "qdot", "base_pose", "body_pose"):
         if k in st:
             w.upload(NAMES[k], st[k])
     w.forward_kinematics()
@@ -33,7 +35,7 @@ def make_world(device, case):
     return ref, w, E, L, n, S
 
 
-@pytest.mark.parametrize("case", sorted(RP.CASES))
+@pytest.mark.parametrize("case", ARTICULATED)
 def test_dynamics_match_the_reference(device, case):
     ref, w, E, L, n, S = make_world(device, case)
     assert RP.err_env(w.download(F.ARTICULATION_LINK_POSE), ref["start_link_pose"].reshape(E, -1)) < 1e-6
@@ -41,13 +43,9 @@ def test_dynamics_match_the_reference(device, case):
     w.upload(F.DRIVE_STIFFNESS, np.zeros((E, L), np.float32)); w.upload(F.DRIVE_DAMPING, np.zeros((E, L), np.float32))
     w.run_stage(1)
     assert RP.err_env(w.download(F.MASS_MATRIX), ref["dyn_mass"].reshape(E, -1)) < 1e-5
-    exact = RP.exact_acceleration(ref["dyn_mass"], ref["dyn_bias"], n)
-    joints = slice(n - (L - 1), n)
-    scale = np.abs(exact[:, joints]).max(axis=1).max() + 1e-12
-    theirs = np.abs(ref["dyn_qddot"].reshape(E, L)[:, 1:] - exact[:, joints]).max() / scale
-    ours = np.abs(w.download(F.JOINT_ACCELERATION)[:, 1:] - exact[:, joints]).max() / scale
+    ours, theirs, largest = RP.acceleration_errors(ref, w.download(F.JOINT_ACCELERATION), E, L, n)
     assert ours < max(3.0 * theirs, 2e-5), (ours, theirs)
-    if scale > 1.0:
+    if largest > 1.0:
         assert RP.err_env(w.download(F.JOINT_ACCELERATION)[:, 1:], ref["dyn_qddot"].reshape(E, L)[:, 1:]) < 1e-4
     w.destroy()
 
@@ -56,19 +54,24 @@ def test_dynamics_match_the_reference(device, case):
 def test_steps_match_the_reference(device, case):
     ref, w, E, L, n, S = make_world(device, case)
     steps = [int(s) for s in ref["traj_steps"]]
-    K = len(steps)
+    K, B = len(steps), int(ref["run"][3])
     q, qd = ref["traj_q"].reshape(K, E, L), ref["traj_qdot"].reshape(K, E, L)
     done = 0
     for i, s in enumerate(steps):
         w.step_n(s - done)
         done = s
         first = i == 0
-        assert RP.err_env(w.download(F.JOINT_POSITION), q[i]) < (1e-5 if first else 1e-4), (case, s)
-        RP.assert_velocity_parity(w.download(F.JOINT_VELOCITY), qd[i], first, (case, s, "joint rates"))
+        if L:
+            RP.assert_position_parity(w.download(F.JOINT_POSITION), q[i], first, (case, s, "q"), case)
+            RP.assert_velocity_parity(w.download(F.JOINT_VELOCITY), qd[i], first, (case, s, "joint rates"), case)
         if ref["traj_base_pose"].size:
-            assert RP.err_env(w.download(F.BASE_POSE), ref["traj_base_pose"].reshape(K, E, 7)[i]) < (1e-5 if first else 1e-4)
+            RP.assert_position_parity(w.download(F.BASE_POSE), ref["traj_base_pose"].reshape(K, E, 7)[i], first,
+                                      (case, s, "base"), case)
             twist = w.download(F.LINK_VELOCITY).reshape(E, L, 6)[:, 0]
-            RP.assert_velocity_parity(twist, ref["traj_root_twist"][i], first, (case, s, "root twist"))
+            RP.assert_velocity_parity(twist, ref["traj_root_twist"][i], first, (case, s, "root twist"), case)
+        if "traj_body_pose" in ref:
+            RP.assert_position_parity(w.download(F.RIGID_BODY_TRANSFORM).reshape(E, 7 * B), ref["traj_body_pose"].reshape(K, E, 7 * B)[i],
+                                      first, (case, s, "bodies"), case, absolute=True)
         assert not w.download(F.ENV_STATUS).any()
         if S:
             count = ref["traj_pair_count"].reshape(K, E)[i]
