@@ -6,8 +6,9 @@
 
 A "step" is one physics step of every env of the workload: 4096 quadrupeds per GPU (BASELINE.json configs[1]).
 N > 1 gives every rank its own 4096-env shard (weak scaling, no collective in the step); after every step each rank
-packs observation + reward records straight into its slice of a gather buffer and the ranks all-gather it in place
-(configs[4]'s exchange).
+packs observation + reward records straight into its slice of one of two gather buffers, and the in-place all-gather of
+that buffer runs on a side stream under the next step (configs[4]'s exchange, double-buffered; the last gather of a
+timed run is added as a tail).
 
 State preparation.  The cost of a step depends on what the robots are doing: while they drop onto their feet the solver
 runs all its sweeps, once they stand it stops early.  So both arms first run `config.settle_steps` untimed steps from
@@ -265,7 +266,8 @@ def run_other_workload(args):
     ms = sum(a.elapsed_time(b) for a, b in zip(starts, ends)) / args.steps
     counts = w.download(F.CONTACT_COUNT) if tb.cfg["max_contacts"] else np.zeros((E, 1), np.uint32)
     slots, points = float((counts > 0).sum(axis=1).mean()), float(counts.sum(axis=1).mean())
-    status = int(np.bitwise_or.reduce(w.download(F.ENV_STATUS).reshape(-1)))
+    flags = w.download(F.ENV_STATUS).reshape(-1)
+    status, flagged = int(np.bitwise_or.reduce(flags)), int((flags != 0).sum())
     info = w.info
     bytes_per = 12 * nj + 52 * nf + 8 * nj + 52 * nf + 52 * nl + 104 * nb + 8 * (nj + 3 * points) + 8 * slots + 32 * points
     peak, peak_kind = hbm_peak()
@@ -275,7 +277,7 @@ def run_other_workload(args):
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": text, "envs_per_gpu": E, "dt": float(info.fixed_dt), "velocity_iterations": int(tb.cfg["vel_iters"]),
                    "settle_steps": settle, "settle_seconds": settle_s, "l2_flush_between_steps": True, "mean_contact_slots": slots,
-                   "mean_contact_points": points, "shared_bytes_per_env": int(info.shared_bytes_per_env), "status_or": status},
+                   "mean_contact_points": points, "shared_bytes_per_env": int(info.shared_bytes_per_env), "status_or": status, "envs_with_status": flagged},
         "roofline": {"bound": "hbm", "achieved": bytes_per * value / 1e9, "peak": peak, "unit": "GB/s", "frac": bytes_per * value / 1e9 / peak,
                      "traffic": None, "peak_source": peak_kind, "algorithmic_bytes_per_env_step": bytes_per, "kernel": "step_kernel", "kernel_ms": ms},
         "gpu_launches": args.steps, "clocks": clocks}))
@@ -339,53 +341,74 @@ def main():
 
     class Exchange:
         """Per-step observation + reward exchange of one world: the pack kernel writes this rank's records into its slice of
-        the gather buffer, the all-gather runs in place."""
+        one of two gather buffers (on the world's stream, inside the step's timed span); the in-place all-gather of that
+        buffer runs on a side stream, released when the NEXT step starts, so it overlaps that step and not the L2 flush
+        between the spans.  The last gather of a run is timed as a tail."""
 
         def __init__(self, w, E):
             self.w = w
-            self.buffer = shard.gather_buffer(E, world_size, shard.RECORD_FLOATS, device=cuda)
-            self.local = shard.local_slice(self.buffer, rank, world_size)
+            self.link = shard.ObservationExchange(E, world_size, rank, shard.RECORD_FLOATS, device=cuda)
             self.base = w.view(F.BASE_POSE).torch()
             self.reward = torch.zeros(E, dtype=torch.float32, device=cuda)
             self.command = torch.tensor([0.5, 0.0, 0.0], dtype=torch.float32, device=cuda)
             self.last_action = torch.zeros((E, NJ), dtype=torch.float32, device=cuda)
             self.desc = w.observation_desc(self.command, last_action=self.last_action, reward=self.reward, row_stride=shard.RECORD_FLOATS)
 
-        def run(self):
+        def pack(self, stream):
             self.reward.copy_(self.base[:, 2])           # the caller's reward: base height
-            self.w.pack_observations(self.desc, self.local)
-            shard.gather_observations(self.buffer, rank)
+            self.w.pack_observations(self.desc, self.link.pack_target(stream))
+            self.link.packed_on(stream)
+
+        def release(self, after=None):
+            self.link.gather(after)
+
+        def drain(self, stream):
+            """Issues what is pending and orders `stream` behind it."""
+            self.link.gather()
+            self.link.wait(stream)
 
     def timed(w, stream, steps, warmup, before_step=None, exchange=None):
         """`warmup` untimed then `steps` timed steps; per-step CUDA events on the world's stream, L2 flushed between steps
-        outside the timed spans.  Returns the per-step times in ms and the kernel launches inside the timed steps."""
-        def one(k):
+        outside the timed spans.  Returns the per-step times in ms (the exchange's tail added to the last) and the kernel
+        launches inside the timed steps."""
+        def one(k, start=None):
+            if exchange is not None:
+                exchange.release(after=start)             # the previous step's gather runs under this step
             if before_step is not None:
                 before_step(k)
             w.step()
             if exchange is not None:
-                exchange.run()
+                exchange.pack(stream)
         with torch.cuda.stream(stream):
             for k in range(warmup):
                 one(k)
+            if exchange is not None:
+                exchange.drain(stream)
             stream.synchronize()
             if distributed:
                 dist.barrier()
             torch.cuda.synchronize()
             launches0 = w.launch_count()
-            starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
-            ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+            starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+            ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
             for k in range(steps):
                 if flush is not None:
                     flush.add_(1.0)                       # evicts the 126 MB L2 (outside the timed spans)
                 starts[k].record(stream)
-                one(warmup + k)
+                one(warmup + k, starts[k])
                 ends[k].record(stream)
+            starts[steps].record(stream)                  # tail: the last step's gather, with nothing to hide under
+            if exchange is not None:
+                exchange.drain(stream)
+            ends[steps].record(stream)
             stream.synchronize()
             torch.cuda.synchronize()
             if distributed:
                 dist.barrier()
-        return [s.elapsed_time(e) for s, e in zip(starts, ends)], w.launch_count() - launches0
+        times = [s.elapsed_time(e) for s, e in zip(starts[:steps], ends[:steps])]
+        if exchange is not None:
+            times[-1] += starts[steps].elapsed_time(ends[steps])
+        return times, w.launch_count() - launches0
 
     def max_over_ranks(values):
         t = torch.tensor(values, dtype=torch.float64, device=cuda)
@@ -401,8 +424,11 @@ def main():
     if gather:
         with torch.cuda.stream(stream):          # NCCL's first-use cost (channel set-up, registration) lands here, not in the timed steps
             for _ in range(20):
-                exchange.run()
+                exchange.pack(stream)
+                exchange.release()
+            exchange.drain(stream)
         stream.synchronize()
+        torch.cuda.synchronize()
     with torch.cuda.stream(stream):
         w.step_n(args.settle)
     stream.synchronize()
@@ -429,10 +455,12 @@ def main():
 
     def e2e_step():
         nuka._check(lib.nuka_world_upload_field(w._h, int(F.DRIVE_TARGET), targets.data_ptr(), targets.numel() * 4, 0))
+        if exchange is not None:
+            exchange.release()                   # the previous step's gather runs under this step
         w.step()
         if exchange is not None:
             with torch.cuda.stream(stream):
-                exchange.run()
+                exchange.pack(stream)
         nuka._check(lib.nuka_world_download_field(w._h, int(F.JOINT_POSITION), out_q.data_ptr(), out_q.numel() * 4, 0))
         nuka._check(lib.nuka_world_download_field(w._h, int(F.BASE_POSE), out_b.data_ptr(), out_b.numel() * 4, 0))
 
@@ -448,6 +476,12 @@ def main():
             dist.barrier()
         t0 = time.perf_counter()
         e2e_step()                               # the downloads synchronise: the step's results are on the host when it returns
+        e2e_s += time.perf_counter() - t0
+    if exchange is not None:                     # the last step's gather, timed with nothing to hide under
+        t0 = time.perf_counter()
+        with torch.cuda.stream(stream):
+            exchange.drain(stream)
+        stream.synchronize()
         e2e_s += time.perf_counter() - t0
     # active drives: each step copies one of a pool of target sets (standing pose + noise) into DRIVE_TARGET on the stream
     targets_view = w.view(F.DRIVE_TARGET).torch()
@@ -474,6 +508,10 @@ def main():
     if rank == 0 and world_size == 1 and not args.no_cpu and not args.boxes and E == ENVS_PER_GPU:
         prepared = {"q": w.download(F.JOINT_POSITION), "qdot": w.download(F.JOINT_VELOCITY), "base_pose": w.download(F.BASE_POSE),
                     "link_velocity": w.download(F.LINK_VELOCITY), "drive_target": w.download(F.DRIVE_TARGET)}
+    if exchange is not None:
+        with torch.cuda.stream(stream):
+            exchange.drain(stream)
+        torch.cuda.synchronize()
     w.destroy()
 
     # ---- configs[4]: 65536 envs of quadruped + 4 free boxes split evenly over the ranks, same exchange ---------------------
@@ -490,8 +528,9 @@ def main():
         x_steps = 10
         x_ms, _ = timed(wx, sx, x_steps, 3, exchange=ex)
         (x_total,) = max_over_ranks([sum(x_ms)])
+        torch.cuda.synchronize()
         wx.destroy()
-        extra = {"workload": "configs[4]: 65536 envs of quadruped + 4 free 0.1 m boxes split evenly over the ranks, observation all-gather every step",
+        extra = {"workload": "configs[4]: 65536 envs of quadruped + 4 free 0.1 m boxes split evenly over the ranks, observation all-gather every step (double-buffered, under the next step)",
                  "scaling": "strong", "total_envs": total, "envs_per_gpu": Ex, "steps": x_steps, "settle_steps": 200,
                  "ms_per_step": x_total / x_steps, "value": total * x_steps / (x_total * 1e-3), "unit": "env-steps/s"}
 
@@ -525,7 +564,7 @@ def main():
             "config": {"workload": WORKLOAD if not args.boxes else WORKLOAD.replace("configs[1]", f"configs[4]'s env: + {args.boxes} free 0.1 m boxes"),
                        "envs_per_gpu": E, "dt": 1.0 / 200.0, "velocity_iterations": 4, "settle_steps": args.settle,
                        "drives": "hold the standing pose", "l2_flush_between_steps": flush is not None,
-                       "obs_allgather": gather, "mean_contact_slots": slots, "mean_contact_points": points, "mean_solver_sweeps": sweeps},
+                       "obs_allgather": "double-buffered; issued on a side stream when the next step starts" if gather else False, "mean_contact_slots": slots, "mean_contact_points": points, "mean_solver_sweeps": sweeps},
             "active": {"value": active_value, "unit": "env-steps/s", "ms_per_step": active_total / active_steps, "steps": active_steps,
                        "drives": f"targets redrawn every step: standing pose + N(0, {ACTIVE_NOISE}) rad"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

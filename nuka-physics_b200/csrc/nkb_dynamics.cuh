@@ -28,6 +28,9 @@ struct Env {
     float vel0[2];           // step-start coordinate velocity
     uint32_t status;
     uint32_t vstride;        // words per shared-memory vector: 32 x coordinates per lane
+    // team mode: word offsets from the env's Newton scratch (matrix, block mass, staged rows) and solver vectors to this
+    // warp's private copies; zero for the env's lead warp
+    uint32_t newton_shift, vec_shift;
 #ifdef NKB_STAGE_TAPS
     uint32_t* cyc;           // stage cycle counters of this env, or null
     long long t0;
@@ -58,7 +61,7 @@ NKB_DEV float* sm_pbias(const Env& e, uint32_t l) { return e.sm + e.lay->pbias +
 NKB_DEV float* sm_ic(const Env& e, uint32_t l) { return e.sm + e.lay->ic + 10u * l; }
 NKB_DEV float* sm_mass(const Env& e) { return e.sm + e.lay->mass; }
 NKB_DEV float* sm_factor(const Env& e) { return e.sm + e.lay->factor; }
-NKB_DEV float* sm_vec(const Env& e, uint32_t k) { return e.sm + e.lay->vecs + e.vstride * k; }   // 32 or 64 words per vector
+NKB_DEV float* sm_vec(const Env& e, uint32_t k) { return e.sm + e.lay->vecs + e.vec_shift + e.vstride * k; }   // 32 or 64 words per vector
 // value of coordinate j from per-lane registers x[r] (coordinate lane + 32 r)
 template <int NR>
 NKB_DEV float coord_bcast(const float (&x)[NR], uint32_t j) {
@@ -94,7 +97,7 @@ NKB_DEV void env_begin(Env& e, const StepParams& p, float* sm, uint32_t env, uin
     e.qd = link ? p.s.qdot[at] : 0.f;
     e.qdd = 0.f; e.tau = 0.f;
     e.drive_command = e.drive_dissipation = e.drive_lower = e.drive_upper = 0.f;
-    e.vstride = 32u * NR;
+    e.vstride = 32u * NR; e.newton_shift = 0u; e.vec_shift = 0u;
     e.dof_link[1] = 0u; e.dof_comp[1] = kNoLink; e.vel0[1] = 0.f;
 #pragma unroll
     for (uint32_t r = 0u; r < (uint32_t)NR; ++r) {

@@ -28,14 +28,15 @@ struct PairCtx {
     const TemplateView* t;
     uint32_t lane;
     float separation;
+    uint32_t stage_shift;       // words from the first warp's polygon staging areas to this warp's (team mode)
 };
 NKB_DEV PairCtx pair_ctx(const Env& e, float separation) {
     PairCtx c;
-    c.sm = e.sm; c.lay = e.lay; c.t = e.t; c.lane = e.lane; c.separation = separation;
+    c.sm = e.sm; c.lay = e.lay; c.t = e.t; c.lane = e.lane; c.separation = separation; c.stage_shift = 0u;
     return c;
 }
 NKB_DEV float* ctx_frames(const PairCtx& c) { return c.sm + c.lay->heads; }                 // 12 B words
-NKB_DEV float* ctx_clip_stage(const PairCtx& c, uint32_t group) { return c.sm + c.lay->heads + 12u * c.t->B + 32u * group; }   // 2 x 32 words
+NKB_DEV float* ctx_clip_stage(const PairCtx& c, uint32_t group) { return c.sm + c.lay->heads + 12u * c.t->B + c.stage_shift + 32u * group; }   // 2 x 32 words
 NKB_DEV const float* ctx_pose(const PairCtx& c, uint32_t b) { return c.sm + c.lay->bpose + 7u * b; }
 NKB_DEV const float* ctx_shape(const PairCtx& c, uint32_t b) { return c.t->shape_params + 4u * b; }
 NKB_DEV uint32_t* ctx_count(const PairCtx& c) { return reinterpret_cast<uint32_t*>(c.sm + c.lay->ccount); }
@@ -440,13 +441,11 @@ static __device__ __noinline__ void box_box_group(PairCtx c, bool active, uint32
     if (active && !contact && r == 0u) ctx_count(c)[slot] = 0u;
 }
 
-// Contact manifolds of the candidate slots: points, normals, depths (+ the separation shell), identities, counts.
-NKB_DEV void stage_narrowphase(Env& e, uint32_t pair_count) {
+// One world frame per collidable row, cached in the narrowphase scratch for every pair that touches the body.
+NKB_DEV void narrowphase_frames(Env& e) {
     const TemplateView& t = *e.t;
-    const float separation = fmaxf(t.cfg.contact_margin, 0.0005f), reach = query_reach(t.cfg);
-    const uint32_t S = t.slot_cap, lane = e.lane;          // slots past the admissible-pair count can never fill and have no storage
-    const PairCtx c = pair_ctx(e, separation);
-    for (uint32_t b = lane; b < t.B; b += 32u) {
+    const PairCtx c = pair_ctx(e, 0.f);
+    for (uint32_t b = e.lane; b < t.B; b += 32u) {
         const float* bp = sm_bpose(e, b);
         const Q4 q = ldq(bp + 3);
         float* f = ctx_frames(c) + 12u * b;
@@ -454,7 +453,17 @@ NKB_DEV void stage_narrowphase(Env& e, uint32_t pair_count) {
         st3(f + 9, ld3(bp));
     }
     __syncwarp();
-    for (uint32_t base = 0u; base < S; base += 32u) {
+}
+
+// Contact manifolds of the candidate slots: points, normals, depths (+ the separation shell), identities, counts.
+// Range form: this warp takes the 32-slot batches first, first + stride, ... (the frames are cached beforehand).
+NKB_DEV void narrowphase_range(Env& e, uint32_t pair_count, uint32_t first, uint32_t stride) {
+    const TemplateView& t = *e.t;
+    const float separation = fmaxf(t.cfg.contact_margin, 0.0005f), reach = query_reach(t.cfg);
+    const uint32_t S = t.slot_cap, lane = e.lane;          // slots past the admissible-pair count can never fill and have no storage
+    PairCtx c = pair_ctx(e, separation);
+    c.stage_shift = 64u * first;
+    for (uint32_t base = 32u * first; base < S; base += 32u * stride) {
         const uint32_t s = base + lane;
         const bool live = s < pair_count;
         uint32_t a = 0u, b = 0u, ka = kSphere, kb = kSphere, cls = kClassNone;

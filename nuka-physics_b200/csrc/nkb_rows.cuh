@@ -252,11 +252,13 @@ NKB_DEV uint32_t stage_rows(Env& e, uint32_t pair_count) {
 NKB_DEV uint32_t head_pair(const Env& e, uint32_t h) { return sm_pairs(e)[(hu(e, HF_REF, h) & 0xffffu) >> 2]; }
 
 // Warm start (phase 0): a contact head takes the multipliers of the cached point with the same identity.
-NKB_DEV void stage_warm_start(Env& e, uint32_t nheads) {
+// Range form: this warp takes the heads first, first + stride, ... (a head's match reads earlier heads and the cache and
+// writes only the head's own dual).
+NKB_DEV void warm_start_range(Env& e, uint32_t nheads, uint32_t first, uint32_t stride) {
     const TemplateView& t = *e.t;
     const uint32_t npts = t.cfg.max_contacts * 4u;
     const CacheEntry* cache = e.s->cache + (size_t)e.env * npts;
-    for (uint32_t h = 0u; h < nheads; ++h) {
+    for (uint32_t h = first; h < nheads; h += stride) {
         if (!(hu(e, HF_FLAGS, h) & kHeadContact)) break;     // contact heads come first
         const uint32_t at = hu(e, HF_REF, h) & 0xffffu;
         const uint32_t pair = head_pair(e, h);
@@ -297,9 +299,32 @@ NKB_DEV void stage_warm_start(Env& e, uint32_t nheads) {
     __syncwarp();
 }
 
+// Owner marks of the cache rebuild: the first current point of each identity owns its cache entry.  Range form over the
+// contact heads first, first + stride, ... (a head's test reads earlier heads and writes its own point's mark).
+NKB_DEV void cache_owners_range(Env& e, uint32_t ncontact, uint32_t first, uint32_t stride) {
+    const TemplateView& t = *e.t;
+    const uint32_t stage_cap = min(t.point_cap, t.slot_cap * 4u);
+    uint32_t* owner = reinterpret_cast<uint32_t*>(reinterpret_cast<CacheEntry*>(e.sm + e.lay->cstage) + stage_cap);
+    for (uint32_t h = first; h < ncontact; h += stride) {
+        const uint32_t at = hu(e, HF_REF, h) & 0xffffu;
+        const uint32_t pair = head_pair(e, h);
+        const uint32_t* f = sm_cfeat(e, at);
+        bool dup = false;
+        for (uint32_t base = 0u; base < h; base += 32u) {
+            const uint32_t j = base + e.lane;
+            bool same = false;
+            if (j < h) { const uint32_t* g = sm_cfeat(e, hu(e, HF_REF, j) & 0xffffu); same = head_pair(e, j) == pair && g[0] == f[0] && g[1] == f[1]; }
+            dup |= __any_sync(NKB_FULL, same);
+        }
+        if (!dup && e.lane == 0u) owner[at] = h;
+    }
+    __syncwarp();
+}
+
 // Warm start (phase 1): rebuilds the env's cache from the solved multipliers; unmatched cached points of age 0
 // survive one more step in the points no current contact owns.
-NKB_DEV void stage_cache_commit(Env& e, uint32_t nheads) {
+template <typename Owners>
+NKB_DEV void stage_cache_commit(Env& e, uint32_t nheads, Owners&& owners) {
     const TemplateView& t = *e.t;
     const uint32_t npts = t.cfg.max_contacts * 4u;
     if (npts == 0u) return;
@@ -313,21 +338,13 @@ NKB_DEV void stage_cache_commit(Env& e, uint32_t nheads) {
     __syncwarp();
     // owners: first current point of each identity
     uint32_t ncontact = 0u;
-    for (uint32_t h = 0u; h < nheads; ++h) {
-        if (!(hu(e, HF_FLAGS, h) & kHeadContact)) break;
-        ++ncontact;
-        const uint32_t at = hu(e, HF_REF, h) & 0xffffu;
-        const uint32_t pair = head_pair(e, h);
-        const uint32_t* f = sm_cfeat(e, at);
-        bool dup = false;
-        for (uint32_t base = 0u; base < h; base += 32u) {
-            const uint32_t j = base + e.lane;
-            bool same = false;
-            if (j < h) { const uint32_t* g = sm_cfeat(e, hu(e, HF_REF, j) & 0xffffu); same = head_pair(e, j) == pair && g[0] == f[0] && g[1] == f[1]; }
-            dup |= __any_sync(NKB_FULL, same);
-        }
-        if (!dup && e.lane == 0u) owner[at] = h;
+    for (uint32_t base = 0u; base < nheads; base += 32u) {          // contact heads come first
+        const uint32_t h = base + e.lane;
+        const uint32_t m = __ballot_sync(NKB_FULL, h < nheads && (hu(e, HF_FLAGS, h) & kHeadContact) != 0u);
+        ncontact += __popc(m);
+        if (m != 0xffffffffu) break;
     }
+    owners(ncontact);
     __syncwarp();
     // retained old entries in ascending cache order
     uint32_t nret = 0u;

@@ -387,7 +387,7 @@ NKB_DEV void row_steps(Env& e, const Tile& tile, uint32_t b, const float* dvec) 
             }
         } else if (k - ib < e.lay->rjac_heads) {
             // rigid block whose head rows were staged at the start of the descent: 3 rows of 8 floats per head
-            const float4* j4 = reinterpret_cast<const float4*>(e.sm + e.lay->rjac + (k - ib) * 24u);
+            const float4* j4 = reinterpret_cast<const float4*>(e.sm + e.lay->rjac + e.newton_shift + (k - ib) * 24u);
             const float4 d0 = d4[0], d1 = d4[1];
             const float4 a0 = j4[0], a1 = j4[1];
             step.x = a0.x * d0.x + a0.y * d0.y + a0.z * d0.z + a0.w * d0.w + a1.x * d1.x + a1.y * d1.y;
@@ -497,8 +497,8 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     float* hi_v = sm_vec(e, kVecS0);
     float* lo_v = sm_vec(e, kVecS1);
     float* u_v = sm_vec(e, kVecS2);
-    float* H = e.sm + e.lay->chol;
-    float* m6 = e.sm + e.lay->bm6;      // 6 x 12 dense mass of a rigid block, then 3 x 8 Jacobian rows of one head
+    float* H = e.sm + e.lay->chol + e.newton_shift;
+    float* m6 = e.sm + e.lay->bm6 + e.newton_shift;      // 6 x 12 dense mass of a rigid block, then 3 x 8 Jacobian rows of one head
     float* jscr = m6 + 72u;
     // rigid block: dense mass, and the Jacobian rows of its incident heads staged once for the whole descent
     // (3 rows of 8 floats per head, as many heads as the staging area holds)
@@ -524,7 +524,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
             const float sgn = head_owner(e, h, 0u) == b ? 1.f : -1.f;
             const uint32_t as = head_axes(e, h);
             const V3 arm = hf3(e, sgn > 0.f ? HF_RA : HF_RB, h);
-            float4* out = reinterpret_cast<float4*>(e.sm + e.lay->rjac + l * 24u);
+            float4* out = reinterpret_cast<float4*>(e.sm + e.lay->rjac + e.newton_shift + l * 24u);
 #pragma unroll
             for (uint32_t ax = 0u; ax < 3u; ++ax) {
                 float4 lo4 = make_float4(0.f, 0.f, 0.f, 0.f), hi4 = lo4;
@@ -656,7 +656,7 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                     if (!(f.x != 0.f || f.y != 0.f || f.z != 0.f || c0 != 0.f || c1 != 0.f || c2 != 0.f || c12 != 0.f || nz.x != 0.f || nz.y != 0.f || nz.z != 0.f)) continue;
                     const float* jr; uint32_t js;
                     if (artic) { jr = sm_jpool(e) + jo; js = chunks << 2; }
-                    else if (k - ib < e.lay->rjac_heads) { jr = e.sm + e.lay->rjac + (k - ib) * 24u; js = 8u; }
+                    else if (k - ib < e.lay->rjac_heads) { jr = e.sm + e.lay->rjac + e.newton_shift + (k - ib) * 24u; js = 8u; }
                     else {
                         const uint32_t ss = head_owner(e, hs, 0u) == b ? 0u : 1u, as = head_axes(e, hs);
                         __syncwarp();
@@ -873,18 +873,208 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     __syncwarp();
 }
 
+// ---- team mode: several warps on one env ---------------------------------------------------------------------------------
+// Blocks of one colour share no constraint row (index_blocks colours the graph whose edges are the two-sided heads), so
+// their descents touch disjoint head records and disjoint body velocities and may run side by side.  The env's lead warp
+// walks the descent order; for a run of rigid blocks of one colour it publishes a command in shared memory, and every
+// warp of the team (the lead included) takes the blocks member, member + team, ... of the run, each on Newton scratch of
+// its own.  A result does not depend on which warp ran a block, so team sizes give bit-identical states.
+//
+// The warps meet through sequence numbers in shared memory, never through a hardware barrier: the lead bumps the
+// command's sequence number, a helper answers by copying it into its result record.  Every wait is bounded by a cycle
+// budget; a warp whose wait runs out records kStatusTeamTimeout and carries on alone (the lead descends the remaining
+// blocks itself, a helper leaves), so a team that falls apart costs a status bit, not a hung kernel.
+enum : uint32_t { kTeamDescend = 0x44455343u, kTeamExit = 0x45584954u,
+                  // stages whose outer loop is dealt out over the team: k_begin carries the stage's count argument
+                  kTeamNarrowphase = 0x4e415252u, kTeamWarmStart = 0x5741524du, kTeamCacheOwners = 0x4f574e52u };
+constexpr uint32_t kTeamCommandWords = 12u;                   // the team area: command, then 4 result words per member
+constexpr long long kTeamPatience = 4000000000ll;           // cycles a warp waits for another: about two seconds
+struct TeamCommand { uint32_t seq, op, k_begin, k_end, position, iteration, nblocks, nheads; float tol; uint32_t dead, pad0, pad1; };
+static_assert(sizeof(TeamCommand) == 4u * kTeamCommandWords, "the command occupies the first words of the team area");
+
+NKB_DEV TeamCommand* team_command(float* sm, const SmemLayout& lay) { return reinterpret_cast<TeamCommand*>(sm + lay.team_area); }
+// result record of a member: momentum, residual, status, sequence number of the last command it finished
+NKB_DEV float* team_result(float* sm, const SmemLayout& lay, uint32_t member) { return sm + lay.team_area + kTeamCommandWords + 4u * member; }
+NKB_DEV uint32_t team_peek(const uint32_t* word) { return *reinterpret_cast<const volatile uint32_t*>(word); }
+NKB_DEV void team_poke(uint32_t* word, uint32_t value) { *reinterpret_cast<volatile uint32_t*>(word) = value; }
+
+// Lead warp, before any helper looks: sequence numbers start at zero (called by every team's lead ahead of a block-wide
+// barrier at kernel start).
+NKB_DEV void team_open(float* sm, const SmemLayout& lay, uint32_t lane) {
+    TeamCommand* cmd = team_command(sm, lay);
+    if (lane == 0u) { cmd->seq = 0u; cmd->op = 0u; cmd->dead = 0u; }
+    if (lane < lay.team) reinterpret_cast<uint32_t*>(team_result(sm, lay, lane))[3] = 0u;
+}
+
+// Lead warp: publishes a command; returns its sequence number.
+NKB_DEV uint32_t team_post(float* sm, const SmemLayout& lay, uint32_t lane, uint32_t op, uint32_t k_begin, uint32_t k_end, bool position, const Tile& tile) {
+    TeamCommand* cmd = team_command(sm, lay);
+    __syncwarp();
+    const uint32_t seq = cmd->seq + 1u;
+    __syncwarp();
+    if (lane == 0u) {
+        cmd->op = op; cmd->k_begin = k_begin; cmd->k_end = k_end; cmd->position = position ? 1u : 0u;
+        cmd->iteration = tile.iteration; cmd->nblocks = tile.nblocks; cmd->nheads = tile.nheads; cmd->tol = tile.tol;
+        __threadfence_block();
+        team_poke(&cmd->seq, seq);
+    }
+    __syncwarp();
+    return seq;
+}
+
+// Lead warp: waits until every helper has answered command `seq`; false when the budget ran out.
+NKB_DEV bool team_collect(float* sm, const SmemLayout& lay, uint32_t lane, uint32_t seq) {
+    // every lane polls the same word, so the warp never splits over a wait
+    bool answered = true;
+    const long long begin = clock64();
+    for (uint32_t m = 1u; m < lay.team && answered; ++m) {
+        const uint32_t* done = reinterpret_cast<const uint32_t*>(team_result(sm, lay, m)) + 3;
+        while (team_peek(done) != seq) {
+            if (clock64() - begin > kTeamPatience) { answered = false; break; }
+            __nanosleep(40);
+        }
+    }
+    answered = __all_sync(NKB_FULL, answered);
+    __threadfence_block();
+    return answered;
+}
+
+// An env record for a warp that works on an env's shared-memory slice without owning its articulation lanes (a team's
+// helper): pointers and lane only, no link or coordinate state.
+NKB_DEV Env bare_env(float* sm, const SmemLayout* lay, const TemplateView* t, const StateView* s, uint32_t env, uint32_t lane, uint32_t vstride) {
+    Env e;
+    e.t = t; e.s = s; e.lay = lay; e.sm = sm; e.env = env; e.lane = lane;
+    e.parent = kNoLink; e.jtype = kFixed; e.depth = 0xffffu; e.link_dof = 0u;
+    e.q = e.qd = e.qdd = e.tau = 0.f;
+    e.axis = mk3(0.f, 0.f, 0.f);
+    e.drive_command = e.drive_dissipation = e.drive_lower = e.drive_upper = 0.f;
+    e.dof_link[0] = e.dof_link[1] = 0u; e.dof_comp[0] = e.dof_comp[1] = kNoLink; e.vel0[0] = e.vel0[1] = 0.f;
+    e.status = 0u; e.vstride = vstride; e.newton_shift = 0u; e.vec_shift = 0u;
+#ifdef NKB_STAGE_TAPS
+    e.cyc = nullptr; e.t0 = 0;
+#endif
+    return e;
+}
+
+// What a warp needs to descend rigid blocks, passed by value so that the function below can stay out of line without
+// forcing the caller's env record into local memory.
+struct RigidRun {
+    float* sm;
+    const SmemLayout* lay;
+    const TemplateView* t;
+    uint32_t lane, vstride, newton_shift, vec_shift;
+    uint32_t nheads, nblocks, iteration;
+    float tol;
+};
+struct RigidResult { float momentum, residual; uint32_t status; };
+
+// Descends the rigid blocks order[k_begin + first], order[k_begin + first + stride], ... < k_end of one colour.
+// Inlined at both call sites (the lead's and the helpers'): out of line, the layout offsets would be read through a
+// pointer instead of the kernel's constant bank, which measured 30 % slower on a 48-box pile.
+#ifndef NKB_RIGID_RUN_QUALIFIER
+#define NKB_RIGID_RUN_QUALIFIER __forceinline__
+#endif
+template <bool kRigid>
+__device__ NKB_RIGID_RUN_QUALIFIER RigidResult descend_rigid_run(RigidRun run, uint32_t k_begin, uint32_t k_end, uint32_t first, uint32_t stride, bool position) {
+    Env e = bare_env(run.sm, run.lay, run.t, nullptr, 0u, run.lane, run.vstride);
+    e.newton_shift = run.newton_shift; e.vec_shift = run.vec_shift;
+    Tile tile;
+    tile.nheads = run.nheads; tile.nblocks = run.nblocks; tile.iteration = run.iteration;
+    tile.momentum = 0.f; tile.residual = 0.f; tile.tol = run.tol;
+    const uint32_t* order = block_order(e, run.nblocks);
+#pragma unroll 1
+    for (uint32_t k = k_begin + first; k < k_end; k += stride) descend_block<1, kRigid, 6>(e, tile, order[k], position);
+    RigidResult out;
+    out.momentum = tile.momentum; out.residual = tile.residual; out.status = e.status;
+    return out;
+}
+
+// Lead warp: releases the helpers for good (they need not answer).
+NKB_DEV void team_dismiss(float* sm, const SmemLayout& lay, uint32_t lane) {
+    if (lay.team <= 1u) return;
+    Tile none;
+    none.nheads = 0u; none.nblocks = 0u; none.iteration = 0u; none.momentum = 0.f; none.residual = 0.f; none.tol = 0.f;
+    team_post(sm, lay, lane, kTeamExit, 0u, 0u, false, none);
+}
+
+// Lead warp: deals a stage's outer loop out over the team.  `work(first, stride)` is the loop body's range form; the lead
+// runs its own share between publishing the command and collecting the answers.  Alone (no team, or a team that fell
+// apart) the lead runs the whole range.  Returns the helpers' status bits.
+template <typename Work>
+NKB_DEV void team_fork(Env& e, uint32_t op, uint32_t count, Work&& work) {
+    const uint32_t team = e.lay->team;
+    if (team <= 1u || team_command(e.sm, *e.lay)->dead != 0u) { work(0u, 1u); return; }
+    Tile none;
+    none.nheads = 0u; none.nblocks = 0u; none.iteration = 0u; none.momentum = 0.f; none.residual = 0.f; none.tol = 0.f;
+    const uint32_t seq = team_post(e.sm, *e.lay, e.lane, op, count, 0u, false, none);
+    work(0u, team);
+    if (team_collect(e.sm, *e.lay, e.lane, seq)) {
+        for (uint32_t m = 1u; m < team; ++m) e.status |= reinterpret_cast<const uint32_t*>(team_result(e.sm, *e.lay, m))[2];
+    } else {
+        e.status |= kStatusTeamTimeout;
+        if (e.lane == 0u) team_command(e.sm, *e.lay)->dead = 1u;
+        __syncwarp();
+    }
+}
+
 // Blocks descend colour by colour, blocks of one colour in index order (block_descent_tile.cuh:2749-2820).
 template <int NR, bool kRigid>
 NKB_DEV void descend_blocks(Env& e, Tile& tile, bool position) {
     const uint32_t nb = tile.nblocks;
     const uint32_t* order = block_order(e, nb);
     const uint32_t count = order[nb];
+    if constexpr (!kRigid) {
 #pragma unroll 1
-    for (uint32_t k = 0u; k < count; ++k) {
-        if (!kRigid) { descend_block<NR, false, 0>(e, tile, e.t->B, position); continue; }
-        const uint32_t b = order[k];
-        if (b == e.t->B) descend_block<NR, kRigid, 0>(e, tile, b, position);
-        else descend_block<1, kRigid, 6>(e, tile, b, position);     // a rigid block's 6 coordinates: one per lane
+        for (uint32_t k = 0u; k < count; ++k) descend_block<NR, false, 0>(e, tile, e.t->B, position);
+    } else {
+        const uint32_t team = e.lay->team;
+        RigidRun run;
+        run.sm = e.sm; run.lay = e.lay; run.t = e.t; run.lane = e.lane; run.vstride = e.vstride; run.newton_shift = 0u; run.vec_shift = 0u;
+        run.nheads = tile.nheads; run.nblocks = nb; run.iteration = tile.iteration; run.tol = tile.tol;
+#pragma unroll 1
+        for (uint32_t k = 0u; k < count;) {
+            const uint32_t b = order[k];
+            if (b == e.t->B) { descend_block<NR, kRigid, 0>(e, tile, b, position); ++k; continue; }
+            // the run of rigid blocks that share b's colour (a rigid block's 6 coordinates: one per lane)
+            const uint32_t colour = blk_color(e, nb, b);
+            uint32_t k_end = k + 1u;
+            while (k_end < count && order[k_end] != e.t->B && blk_color(e, nb, order[k_end]) == colour) ++k_end;
+            RigidResult mine;
+            // colour 31 is the overflow colour (index_blocks hands it to every block past the 31st colour): not a set of
+            // independent blocks, so it stays with the lead
+            if (team > 1u && k_end - k > 1u && colour < 31u && team_command(e.sm, *e.lay)->dead == 0u) {
+                const uint32_t seq = team_post(e.sm, *e.lay, e.lane, kTeamDescend, k, k_end, position, tile);
+#ifdef NKB_STAGE_TAPS
+                const long long tap0 = clock64();
+#endif
+                mine = descend_rigid_run<kRigid>(run, k, k_end, 0u, team, position);
+#ifdef NKB_STAGE_TAPS
+                const long long tap1 = clock64();
+#endif
+                const bool collected = team_collect(e.sm, *e.lay, e.lane, seq);
+#ifdef NKB_STAGE_TAPS
+                if (e.cyc != nullptr && e.lane == 0u) { e.cyc[28] += (uint32_t)(tap1 - tap0); e.cyc[29] += (uint32_t)(clock64() - tap1); e.cyc[23] += 0u; }
+#endif
+                if (collected) {
+                    for (uint32_t m = 1u; m < team; ++m) {
+                        const float* r = team_result(e.sm, *e.lay, m);
+                        mine.momentum = fmaxf(mine.momentum, r[0]); mine.residual = fmaxf(mine.residual, r[1]);
+                        mine.status |= reinterpret_cast<const uint32_t*>(r)[2];
+                    }
+                } else {
+                    // a helper did not answer: the env's result is void (flagged); work alone from here on
+                    mine.status |= kStatusTeamTimeout;
+                    if (e.lane == 0u) team_command(e.sm, *e.lay)->dead = 1u;
+                    __syncwarp();
+                }
+            } else {
+                mine = descend_rigid_run<kRigid>(run, k, k_end, 0u, 1u, position);
+            }
+            tile.momentum = fmaxf(tile.momentum, mine.momentum);
+            tile.residual = fmaxf(tile.residual, mine.residual);
+            e.status |= mine.status;
+            k = k_end;
+        }
     }
 }
 

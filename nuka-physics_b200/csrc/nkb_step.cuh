@@ -6,6 +6,7 @@
 // variants build in parallel; NKB_STEP_VARIANT defines the host-side handle of one.
 #pragma once
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <mutex>
 #include "nkb_solver.cuh"
 #include "nkb_lbvh.cuh"
@@ -143,18 +144,16 @@ NKB_DEV void stage_store_bodies(Env& e, bool velocities) {
 // SM; tighter caps (144 or 128 registers, 14 warps per SM) slow every warp by more than the extra residency returns.
 // NR = coordinates per lane: 1 for articulations of up to 32 coordinates, 2 for up to 64.
 // kRigid = the world has free rigid bodies; without them the rigid-block solver code is compiled out.
+// Worlds with free bodies are held to fewer resident warps by shared memory than by registers (38 KB per env and more),
+// so their variants take a wider cap: no spills, and a team of 8 warps still fits the register file.
 #ifndef NKB_MAXNREG
 #define NKB_MAXNREG 176
 #endif
+#ifndef NKB_MAXNREG_RIGID
+#define NKB_MAXNREG_RIGID 224
+#endif
 template <int NR, bool kRigid>
-__global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ StepParams p) {
-    extern __shared__ __align__(16) float smem[];
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    uint32_t env = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (p.sel_ids != nullptr) env = env < p.sel_count ? p.sel_ids[env] : 0xffffffffu;
-    if (env >= p.s.env_count) return;
-    if (p.sel_mask != nullptr && p.sel_mask[env] == 0u) return;
-    float* sm = smem + (size_t)warp * p.sm.words;
+NKB_DEV void advance_env(const StepParams& p, float* sm, uint32_t env, uint32_t lane) {
     const TemplateView& t = p.t;
     const bool has_artic = t.L != 0u, has_bodies = t.B != 0u;
     const bool has_collidables = has_bodies && t.cfg.max_contacts != 0u;
@@ -183,7 +182,9 @@ __global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ Ste
             stage_aabbs(e);
             pair_count = t.broadphase_tree != 0u ? stage_pairs_lbvh(e) : stage_pairs(e);
             tick(e, 3);
-            stage_narrowphase(e, pair_count);
+            narrowphase_frames(e);
+            if constexpr (kRigid) team_fork(e, kTeamNarrowphase, pair_count, [&](uint32_t first, uint32_t stride) { narrowphase_range(e, pair_count, first, stride); });
+            else narrowphase_range(e, pair_count, 0u, 1u);
             tick(e, 4);
             stage_store_contacts(e, pair_count);
             tick(e, 5);
@@ -198,10 +199,17 @@ __global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ Ste
         }
         nheads = stage_rows<NR>(e, pair_count);
         tick(e, 6);
-        stage_warm_start(e, nheads);
+        if constexpr (kRigid) team_fork(e, kTeamWarmStart, nheads, [&](uint32_t first, uint32_t stride) { warm_start_range(e, nheads, first, stride); });
+        else warm_start_range(e, nheads, 0u, 1u);
+        __syncwarp();
         tick(e, 7);
         stage_solve<NR, kRigid>(e, nheads);
-        if (has_collidables) stage_cache_commit(e, nheads);
+        if (has_collidables) {
+            stage_cache_commit(e, nheads, [&](uint32_t ncontact) {
+                if constexpr (kRigid) team_fork(e, kTeamCacheOwners, ncontact, [&](uint32_t first, uint32_t stride) { cache_owners_range(e, ncontact, first, stride); });
+                else cache_owners_range(e, ncontact, 0u, 1u);
+            });
+        }
         if (has_artic) stage_readout_drives(e, nheads);
         tick(e, 12);
         if (has_artic) { stage_integrate_links(e, use_pseudo); }
@@ -234,6 +242,104 @@ __global__ void __maxnreg__(NKB_MAXNREG) step_kernel(const __grid_constant__ Ste
         __syncwarp();
         tick(e, 13);
     }
+}
+
+// A helper warp's life: wait for a command, do its share (rigid blocks of a colour on private Newton scratch, or a slice of
+// a stage's outer loop), answer, until told to leave (or until a wait runs out).
+template <bool kRigid>
+NKB_DEV void team_helper(float* sm, const SmemLayout& shared_layout, const TemplateView& t, const StateView& state, uint32_t env,
+                         uint32_t member, uint32_t lane, uint32_t vstride) {
+    // private copies of the regions a block descent scratches in (same arrangement as the env's own: Newton matrix, block
+    // mass, staged rows; then the solver vectors); everything else is the env's own
+    const uint32_t newton_span = shared_layout.rjac + 24u * shared_layout.rjac_heads - shared_layout.chol;
+    const uint32_t base = shared_layout.team_area + kTeamCommandWords + ((4u * shared_layout.team + 3u) & ~3u) + (member - 1u) * shared_layout.helper_words;
+    const uint32_t newton_shift = base - shared_layout.chol, vec_shift = base + newton_span - shared_layout.vecs;
+    const TeamCommand* cmd = team_command(sm, shared_layout);
+    uint32_t* answer = reinterpret_cast<uint32_t*>(team_result(sm, shared_layout, member));
+    uint32_t last = 0u;
+#pragma unroll 1
+    for (uint32_t trips = 0u; trips < (1u << 24); ++trips) {
+        // every lane polls the same word, so the warp never splits over the wait
+        uint32_t seq = last;
+        {
+            const long long begin = clock64();
+            while ((seq = team_peek(&cmd->seq)) == last) {
+                if (clock64() - begin > kTeamPatience) break;
+                __nanosleep(100);
+            }
+        }
+        seq = __shfl_sync(NKB_FULL, seq, 0);
+        __syncwarp();
+        if (seq == last) {                                   // the lead never called: leave, and say so
+            if (lane == 0u) atomicOr(state.status + env, kStatusTeamTimeout);
+            return;
+        }
+        __threadfence_block();
+        last = seq;
+        const uint32_t op = team_peek(&cmd->op);
+        if (op == kTeamExit) return;
+        RigidResult r = {0.f, 0.f, 0u};
+        const uint32_t k_begin = cmd->k_begin, k_end = cmd->k_end, nblocks = cmd->nblocks;
+        if (op == kTeamDescend && k_begin < k_end && k_end <= nblocks && nblocks <= t.B + 1u) {
+            RigidRun run;
+            run.sm = sm; run.lay = &shared_layout; run.t = &t; run.lane = lane; run.vstride = vstride;
+            run.newton_shift = newton_shift; run.vec_shift = vec_shift;
+            run.nheads = cmd->nheads; run.nblocks = nblocks; run.iteration = cmd->iteration; run.tol = cmd->tol;
+#ifdef NKB_STAGE_TAPS
+            const long long tap0 = clock64();
+#endif
+            r = descend_rigid_run<kRigid>(run, k_begin, k_end, member, shared_layout.team, cmd->position != 0u);
+#ifdef NKB_STAGE_TAPS
+            if (state.dbg_cycles != nullptr && lane == 0u && member == 1u) {
+                uint32_t* cyc = state.dbg_cycles + (size_t)env * 32u;
+                cyc[30] += (uint32_t)(clock64() - tap0); cyc[31] += 1u;
+            }
+#endif
+        }
+        else if (op == kTeamNarrowphase || op == kTeamWarmStart || op == kTeamCacheOwners) {
+            Env e = bare_env(sm, &shared_layout, &t, &state, env, lane, vstride);
+            if (op == kTeamNarrowphase) narrowphase_range(e, k_begin, member, shared_layout.team);
+            else if (op == kTeamWarmStart) warm_start_range(e, k_begin, member, shared_layout.team);
+            else cache_owners_range(e, k_begin, member, shared_layout.team);
+            r.status = e.status;
+        }
+        __syncwarp();
+        if (lane == 0u) {
+            float* out = team_result(sm, shared_layout, member);
+            out[0] = r.momentum; out[1] = r.residual; answer[2] = r.status;
+            __threadfence_block();
+            team_poke(answer + 3, seq);
+        }
+        __syncwarp();
+    }
+}
+
+// Block layout: blockDim.x / 32 warps, `team` consecutive warps per env (one unless the world runs in team mode); an
+// env's shared-memory slice is shared by its team.
+template <int NR, bool kRigid>
+__global__ void __maxnreg__(kRigid ? NKB_MAXNREG_RIGID : NKB_MAXNREG) step_kernel(const __grid_constant__ StepParams p) {
+    extern __shared__ __align__(16) float smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t team = kRigid ? p.sm.team : 1u;
+    const uint32_t slot = warp / team, member = warp - slot * team;
+    uint32_t env = blockIdx.x * ((blockDim.x >> 5) / team) + slot;
+    float* sm = smem + (size_t)slot * p.sm.words;
+    if constexpr (kRigid) {
+        // team mode: every lead zeroes its team's sequence numbers before any helper looks (the one block-wide barrier of
+        // the kernel, passed by every thread before any leaves)
+        if (team > 1u) {
+            if (member == 0u) team_open(sm, p.sm, lane);
+            __syncthreads();
+        }
+    }
+    if (p.sel_ids != nullptr) env = env < p.sel_count ? p.sel_ids[env] : 0xffffffffu;
+    if (env >= p.s.env_count) return;                       // the whole team leaves together
+    if (p.sel_mask != nullptr && p.sel_mask[env] == 0u) return;
+    if constexpr (kRigid) {
+        if (member != 0u) { team_helper<kRigid>(sm, p.sm, p.t, p.s, env, member, lane, 32u * NR); return; }
+    }
+    advance_env<NR, kRigid>(p, sm, env, lane);
+    if constexpr (kRigid) team_dismiss(sm, p.sm, lane);
 }
 
 // Raises the kernel's dynamic shared-memory limit to `bytes` if it is not there yet.  The limit is per function and
@@ -278,12 +384,15 @@ static int variant_registers() {
 
 template <int NR, bool kRigid>
 static cudaError_t variant_launch(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
-    const size_t bytes = (size_t)warps_per_block * p.sm.words * sizeof(float);
+    const uint32_t team = kRigid ? p.sm.team : 1u;
+    const uint32_t envs_per_block = warps_per_block / team;
+    if (envs_per_block == 0u || envs_per_block * team != warps_per_block || envs_per_block > 15u) return cudaErrorInvalidConfiguration;
+    const size_t bytes = (size_t)envs_per_block * p.sm.words * sizeof(float);
     const cudaError_t err = variant_reserve_shared<NR, kRigid>(bytes);
     if (err != cudaSuccess) return err;
-    const uint32_t warps = p.sel_ids != nullptr ? p.sel_count : p.s.env_count;
-    if (warps == 0u) return cudaSuccess;
-    const uint32_t blocks = (warps + warps_per_block - 1u) / warps_per_block;
+    const uint32_t envs = p.sel_ids != nullptr ? p.sel_count : p.s.env_count;
+    if (envs == 0u) return cudaSuccess;
+    const uint32_t blocks = (envs + envs_per_block - 1u) / envs_per_block;
     step_kernel<NR, kRigid><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
     return cudaGetLastError();
 }

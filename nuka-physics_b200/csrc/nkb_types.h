@@ -19,7 +19,8 @@ enum ShapeKind : uint32_t { kSphere = 0, kCapsule = 1, kBox = 2, kPlane = 3 };
 // env status bits, reference src/phi/op_schema.hpp:36-52
 enum : uint32_t { kStatusPairOverflow = 1u << 0, kStatusDofOverflow = 1u << 2, kStatusGyroFailure = 1u << 5,
                   kStatusControlFailure = 1u << 10, kStatusSolverFailure = 1u << 13,
-                  kStatusHeadOverflow = 1u << 20 };
+                  kStatusHeadOverflow = 1u << 20,
+                  kStatusTeamTimeout = 1u << 21 };     // a warp of an env's team gave up waiting for another (team mode)
 // head flags
 enum : uint32_t { kHeadContact = 1u << 0, kHeadContactNormal = 1u << 1, kHeadSpeculative = 1u << 2,
                   kHeadVelocityOnly = 1u << 3, kHeadDrive = 1u << 4, kHeadLimit = 1u << 5, kHeadFriction = 1u << 6,
@@ -40,8 +41,9 @@ NKB_HOST_DEVICE inline uint32_t lbvh_scratch_words(uint32_t B) {
     return 2u * lbvh_pow2(B) + (B - 1u) * 10u + 4u * B + B * ((B + 31u) / 32u);
 }
 
-// Scratch words of the narrowphase (nkb_manifold.cuh): one world frame per collidable row and two polygon staging areas.
-NKB_HOST_DEVICE inline uint32_t manifold_scratch_words(uint32_t B) { return 12u * B + 64u; }
+// Scratch words of the narrowphase (nkb_manifold.cuh): one world frame per collidable row and two polygon staging areas
+// per warp that works on the env.
+NKB_HOST_DEVICE inline uint32_t manifold_scratch_words(uint32_t B, uint32_t warps) { return 12u * B + 64u * warps; }
 
 struct Config {
     float dt;
@@ -124,6 +126,9 @@ struct SmemLayout {
     uint32_t cstage;                                            // cache rebuild staging (shares the Jacobian pool, dead by then)
     uint32_t heads, jpool, binfo, chol, bm6;                    // solver (chol: Newton matrix; bm6: rigid block mass + head rows)
     uint32_t rjac, rjac_heads;                                  // staged Jacobian rows of one rigid block's heads (24 words each)
+    // Team mode: `team` warps advance one env; warp 0 leads, the others wait for work (rigid blocks of one colour).
+    // team_area: 12 command words, 4 result words per member, then helper_words of private Newton scratch per helper.
+    uint32_t team, team_area, helper_words;
     uint32_t words;                                             // total per env
     uint32_t ld;                                                // leading dimension of mass/factor (ndof | 1)
 };

@@ -327,7 +327,7 @@ void World::BuildLayout() {
     s.pairs = take(SC); s.ccount = take(SC); s.cpoint = take(12 * SC); s.cnormal = take(12 * SC); s.cdepth = take(4 * SC);
     s.cfeat = take(8 * SC);                       // contact identity words
     // before the heads exist the region serves the tree broadphase and then the narrowphase as scratch
-    s.heads = take(std::max(kHeadStride * tv.head_cap, SC != 0u ? std::max(lbvh_scratch_words(B), manifold_scratch_words(B)) : 0u));
+    s.heads = take(std::max(kHeadStride * tv.head_cap, SC != 0u ? std::max(lbvh_scratch_words(B), manifold_scratch_words(B, t.n_free != 0u ? kWarpsPerBlockMax : 1u)) : 0u));
     // the Jacobian pool also holds the AABBs (dead once the narrowphase is done) and, after the solve, the cache staging
     // entries + owner marks
     const uint32_t stage_cap = std::min(tv.point_cap, 4u * SC);
@@ -336,6 +336,28 @@ void World::BuildLayout() {
     const uint32_t nb = B + (n ? 1u : 0u);
     s.binfo = take(3 * nb + 1 + 2 * tv.head_cap + 2 * s.vstride + nb + 1);      // the unit-row table holds 16-bit head indices
     if (const char* pad = std::getenv("NUKA_B200_SMEM_PAD_WORDS")) at += (static_cast<uint32_t>(std::atoi(pad)) + 3u) & ~3u;   // occupancy experiments
+    // Team mode.  An env of many free bodies fills most of an SM's shared memory by itself, so one warp per env would
+    // leave the SM with one or two resident warps; instead several warps share the env and descend the rigid blocks
+    // of one colour side by side (blocks of a colour share no constraint row).  Registers allow about 11 resident
+    // warps per SM, so teams only pay where shared memory already holds residency below that.
+    s.team = 1u; s.team_area = at; s.helper_words = 0u;
+    {
+        const uint32_t helper = (s.rjac + 24u * s.rjac_heads - s.chol) + 6u * s.vstride;     // Newton matrix, block mass, staged rows as the env lays them out; vectors
+        uint32_t team = 1u;
+        if (t.n_free >= 8u) {
+            const uint32_t envs_alone = std::max<uint32_t>(1u, (227u * 1024u) / (at * 4u + 1024u));      // resident envs, one warp each
+            while (team * 2u <= kWarpsPerBlockMax && envs_alone * team * 2u <= 11u &&
+                   (at + 12u + 4u * (team * 2u) + helper * (team * 2u - 1u)) * 4u <= 220u * 1024u) team *= 2u;
+        }
+        if (const char* forced = std::getenv("NUKA_B200_TEAM")) {                        // team-size experiments
+            const uint32_t w = static_cast<uint32_t>(std::atoi(forced));
+            if (w >= 1u && w <= kWarpsPerBlockMax && t.n_free != 0u && (at + 12u + 4u * w + helper * (w - 1u)) * 4u <= 220u * 1024u) team = w;
+        }
+        if (team > 1u) {
+            s.team = team; s.helper_words = (helper + 3u) & ~3u;
+            s.team_area = take(12u + ((4u * team + 3u) & ~3u) + s.helper_words * (team - 1u));
+        }
+    }
     s.words = at;
     const size_t bytes = static_cast<size_t>(s.words) * 4u;
     if (bytes > 220u * 1024u) throw Error(kNotSupported, "template needs more shared memory per env than one SM provides");
@@ -344,24 +366,26 @@ void World::BuildLayout() {
     // residency, so the largest block within 10 % of the best residency wins.
     size_t resident[kWarpsPerBlockMax + 1] = {0};
     size_t best = 0;
-    for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) {
-        if (w * bytes > 227u * 1024u) break;
-        resident[w] = static_cast<size_t>(step_kernel_resident_blocks(n, t.n_free, w, w * bytes)) * w;      // asks the runtime
+    const uint32_t team = s.team;                  // a block holds whole teams: w counts warps, w / team envs
+    for (uint32_t w = team; w <= kWarpsPerBlockMax; w += team) {
+        if ((w / team) * bytes > 227u * 1024u) break;
+        resident[w] = static_cast<size_t>(step_kernel_resident_blocks(n, t.n_free, w, (w / team) * bytes)) * w;      // asks the runtime
         best = std::max(best, resident[w]);
     }
     // among the shapes within 10 % of the best residency: a multiple of 4 warps (one per scheduler, measured 0.5 %
     // faster than 6-warp blocks at the same residency on the quadruped), else the largest
-    warps_per_block_ = 1;
-    for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) if (resident[w] * 10u >= best * 9u) warps_per_block_ = w;
-    for (uint32_t w = 4; w <= kWarpsPerBlockMax; w += 4) if (resident[w] * 10u >= best * 9u && resident[w] >= resident[warps_per_block_]) warps_per_block_ = w;
+    warps_per_block_ = team;
+    for (uint32_t w = team; w <= kWarpsPerBlockMax; w += team) if (resident[w] * 10u >= best * 9u) warps_per_block_ = w;
+    for (uint32_t w = 4; w <= kWarpsPerBlockMax; w += 4)
+        if (w % team == 0u && resident[w] * 10u >= best * 9u && resident[w] >= resident[warps_per_block_]) warps_per_block_ = w;
     if (const char* forced = std::getenv("NUKA_B200_WARPS_PER_BLOCK")) {          // block-shape experiments
         const uint32_t w = static_cast<uint32_t>(std::atoi(forced));
-        if (w >= 1u && w <= kWarpsPerBlockMax && resident[w] != 0u) warps_per_block_ = w;
+        if (w >= 1u && w <= kWarpsPerBlockMax && w % team == 0u && resident[w] != 0u) warps_per_block_ = w;
     }
     if (std::getenv("NUKA_B200_DEBUG_LAYOUT") != nullptr) {
         std::fprintf(stderr, "[nuka_b200] %zu B of shared memory per env, %d registers per thread; resident warps per SM by block size:", bytes, step_kernel_registers(n, t.n_free));
         for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) std::fprintf(stderr, " %u:%zu", w, resident[w]);
-        std::fprintf(stderr, " -> %u warps per block\n", warps_per_block_);
+        std::fprintf(stderr, " -> %u warps per block, %u per env\n", warps_per_block_, team);
         std::fprintf(stderr, "[nuka_b200] word offsets: overlay %u mass %u vecs %u bodies %u contacts %u heads %u pool %u blocks %u end %u\n",
                      s.xrot, s.mass, s.vecs, s.bpose, s.pairs, s.heads, s.jpool, s.binfo, s.words);
     }

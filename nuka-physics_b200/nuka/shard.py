@@ -3,7 +3,8 @@
 Envs never interact (the reference drops cross-env pairs, src/phi/op_schema.hpp:236-252, and builds trees, slots,
 rows and solver tiles per env), so rank g of G owns a contiguous env range and steps it alone.  The only exchange
 is the caller's: the observation record + reward per env, gathered after a step.  The pack kernel writes each rank's
-records straight into that rank's slice of the gather buffer, so the all-gather runs in place without a staging copy.
+records straight into that rank's slice of the gather buffer, so the all-gather runs in place without a staging copy;
+ObservationExchange double-buffers that buffer and runs the all-gather on a side stream, under the next step.
 """
 import numpy as np
 
@@ -72,3 +73,73 @@ def gather_observations(gathered, rank=None, group=None):
         raise ValueError("gather buffer does not hold world_size equal shards")
     dist.all_gather_into_tensor(gathered, local_slice(gathered, rank, world), group=group)
     return gathered
+
+
+class ObservationExchange:
+    """Double-buffered observation exchange of one rank.
+
+    Step k's records are packed (on the world's stream, a few microseconds) into this rank's slice of buffer k % 2;
+    the all-gather of that buffer is issued on a side stream and runs under step k + 1, which writes nothing the gather
+    reads.  The consumer of the gathered records (a learner, a logger) therefore sees them one step late, the usual
+    pipelined arrangement; `wait` orders a consumer stream behind the latest gather.  A buffer is packed again two steps
+    later, after its previous gather in side-stream order.  On CPU tensors (gloo, tests) everything is synchronous."""
+
+    def __init__(self, local_envs, world_size, rank, width=RECORD_FLOATS, device=None, group=None):
+        import torch
+        self.world_size, self.rank, self.group = world_size, rank, group
+        self.buffers = [gather_buffer(local_envs, world_size, width, device=device) for _ in range(2)]
+        self.cuda = self.buffers[0].is_cuda
+        self.side = torch.cuda.Stream(device=device) if self.cuda else None
+        self.packed = [torch.cuda.Event() for _ in range(2)] if self.cuda else None
+        self.gathered = [torch.cuda.Event() for _ in range(2)] if self.cuda else None
+        self.issued = [False, False]
+        self.parity = 0            # buffer the next pack goes into
+        self.pending = None        # buffer packed but not yet gathered
+        self.latest = None         # buffer of the last gather issued
+
+    def pack_target(self, stream=None):
+        """This rank's slice of the buffer the coming pack writes into.  `stream` (the packing stream) first waits for that
+        buffer's previous gather, issued two steps ago."""
+        k = self.parity
+        if self.cuda and self.issued[k] and stream is not None:
+            stream.wait_event(self.gathered[k])
+        return local_slice(self.buffers[k], self.rank, self.world_size)
+
+    def packed_on(self, stream=None):
+        """Call after the pack kernel was enqueued on `stream`: the buffer becomes the pending one."""
+        k = self.parity
+        if self.cuda:
+            self.packed[k].record(stream)
+        self.pending = k
+        self.parity ^= 1
+
+    def gather(self, after=None):
+        """Issues the all-gather of the pending buffer on the side stream, behind its pack and, if given, behind the event
+        `after` (a caller that wants the gather to start with its next step passes that step's start event)."""
+        import torch
+        import torch.distributed as dist
+        k = self.pending
+        if k is None:
+            return None
+        self.pending = None
+        buf = self.buffers[k]
+        if not self.cuda:
+            dist.all_gather_into_tensor(buf, local_slice(buf, self.rank, self.world_size), group=self.group)
+        else:
+            self.side.wait_event(self.packed[k])
+            if after is not None:
+                self.side.wait_event(after)
+            with torch.cuda.stream(self.side):
+                dist.all_gather_into_tensor(buf, local_slice(buf, self.rank, self.world_size), group=self.group)
+                self.gathered[k].record(self.side)
+            self.issued[k] = True
+        self.latest = k
+        return buf
+
+    def wait(self, stream=None):
+        """Orders `stream` behind the latest gather and returns its buffer (all slices valid once the stream gets there)."""
+        if self.latest is None:
+            return None
+        if self.cuda and stream is not None:
+            stream.wait_event(self.gathered[self.latest])
+        return self.buffers[self.latest]

@@ -316,7 +316,7 @@ def humanoid_state(env_count, seed=0):
 def box_pile(seed=0, dt=1.0 / 240.0, vel_iters=8, count=48):
     """Config 4: free boxes on a 4x4x3 jittered lattice above a plane (template holds the nominal lattice)."""
     rng = np.random.Generator(np.random.PCG64(seed))
-    tb = TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=4 * count, max_points=6 * count)
+    tb = TemplateBuilder(dt=dt, vel_iters=vel_iters, max_contacts=6 * count, max_points=6 * count)
     for k in range(count):
         he = rng.uniform(0.02, 0.1, size=3)
         rho = rng.uniform(500.0, 2000.0)

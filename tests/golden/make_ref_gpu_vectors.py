@@ -43,8 +43,12 @@ CASES = {
     "humanoid": (lambda: T.humanoid(0), lambda E: T.humanoid_state(E, 0), 1.0 / 200.0, 8, 40, 10),
 }
 SCENE_OF = {"quadruped_moving": "quadruped"}
-# throughput of the reference on the other configurations: (scene case, envs, dt, iterations, warm-up, timed steps)
-TIMINGS = [("humanoid", 8192, 1.0 / 200.0, 8, 100, 100), ("quadbox", 8192, 1.0 / 200.0, 4, 100, 100), ("pile48", 16384, 1.0 / 240.0, 8, 60, 20)]
+# throughput of the reference on the other configurations, on the protocol of bench.py --workload: the same seeded
+# per-env start states, the same untimed settle steps, then the timed steps
+# (scene case, envs, dt, iterations, settle steps, timed steps, start state)
+TIMINGS = [("humanoid", 8192, 1.0 / 200.0, 8, 300, 30, lambda E: T.humanoid_state(E, 0)),
+           ("quadbox", 8192, 1.0 / 200.0, 4, 300, 30, lambda E: T.quadruped_state(E, 0)),
+           ("pile48", 16384, 1.0 / 240.0, 8, 240, 20, lambda E: {"body_pose": T.box_pile_state(E, 0)["body_pose"]})]
 
 
 def prepare():
@@ -75,9 +79,16 @@ def prepare():
                  '--time 1000,200,1 --active 0.15 >> "$OUT/ref_timing.jsonl"')
     with open(os.path.join(RUN, "pile48.nks"), "w") as f:
         json.dump(nks.scene_from_builder(T.box_pile(0, count=48)), f)
-    for scene, envs, dt, iters, warm, timed in TIMINGS:
-        lines.append(f'timeout 300 ../ref_driver --scene {scene}.nks --envs {envs} --dt {dt!r} --vel-iters {iters} --time {warm},{timed},1 '
-                     f'>> "$OUT/ref_timing.jsonl" || echo "{{\\"scene\\": \\"{scene}.nks\\", \\"envs\\": {envs}, \\"failed\\": $?}}" >> "$OUT/ref_timing.jsonl"')
+    split = len(lines)
+    for scene, envs, dt, iters, warm, timed, state in TIMINGS:
+        st = {k: np.ascontiguousarray(v, np.float32).reshape(envs, -1) for k, v in state(envs).items() if k in ("q", "qdot", "base_pose", "body_pose")}
+        with open(os.path.join(RUN, f"{scene}_state{envs}.nkt"), "wb") as f:
+            f.write(nkt.pack(st))
+        lines.append(f'timeout 600 ../ref_driver --scene {scene}.nks --envs {envs} --dt {dt!r} --vel-iters {iters} --state {scene}_state{envs}.nkt '
+                     f'--time {warm},{timed},1 >> "$OUT/ref_timing.jsonl" || echo "{{\\"scene\\": \\"{scene}.nks\\", \\"envs\\": {envs}, \\"failed\\": $?}}" >> "$OUT/ref_timing.jsonl"')
+    # run.sh does everything; timings.sh only the throughput lines of the other configurations (appending)
+    with open(os.path.join(RUN, "timings.sh"), "w") as f:
+        f.write("\n".join(lines[:5] + lines[split:]) + "\n")
     with open(os.path.join(RUN, "run.sh"), "w") as f:
         f.write("\n".join(lines) + "\n")
     print("prepared", RUN)

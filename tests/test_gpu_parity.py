@@ -223,14 +223,14 @@ def test_free_boxes_land_like_the_oracle(device, oracle):
 
 
 def test_full_box_pile_of_configs_3(device, oracle):
-    """configs[3]'s env at full size: 48 free boxes over a plane, 192 candidate slots, a contact-point capacity of
+    """configs[3]'s env at full size: 48 free boxes over a plane, 288 candidate slots, a contact-point capacity of
     288 carried by the template.  Pair lists and contact counts bit-exact and poses within 1e-4 through the first
     landings (after which a tumbling pile amplifies rounding differences)."""
     E, count = 16, 48
     st = T.box_pile_state(E, 0, count=count)
     w, o = make_pair(device, oracle, T.box_pile(0, count=count), E, {"body_pose": st["body_pose"]})
     B, S = count + 1, w.info.contact_slots_per_env
-    assert S == 4 * count
+    assert S == 6 * count
     for k in (1, 19):
         w.step_n(k); o.step(k)
         pc = w.download(F.PAIR_COUNT)

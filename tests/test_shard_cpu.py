@@ -81,3 +81,39 @@ def test_two_rank_gather_is_rank_major(tmp_path):
     assert torch.equal(outs[0], outs[1])
     assert torch.equal(outs[0][:, 0], torch.arange(total, dtype=torch.float32))
     assert torch.equal(outs[0][:, 48], torch.repeat_interleave(torch.arange(world, dtype=torch.float32), total // world))
+
+
+def _exchange_main(rank, world, port, total_envs, result_dir):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    begin, end = shard.env_range(rank, world, total_envs)
+    ex = shard.ObservationExchange(end - begin, world, rank)
+    seen = []
+    for step in range(5):
+        local = ex.pack_target()                              # the pack kernel's output on a GPU
+        local.fill_(-1.0)
+        local[:, 0] = torch.arange(begin, end, dtype=torch.float32)
+        local[:, 48] = float(100 * step + rank)
+        ex.packed_on()
+        assert ex.pending == step % 2
+        out = ex.gather()
+        assert out is ex.buffers[step % 2] and ex.wait() is out and ex.gather() is None      # nothing pending twice
+        seen.append(out.clone())
+    dist.barrier()
+    torch.save(torch.stack(seen), os.path.join(result_dir, f"exchange{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def test_double_buffered_exchange_alternates_buffers(tmp_path):
+    """Two gloo ranks, five steps: buffers alternate, every gather holds the step's records of both ranks in rank-major
+    order, and a buffer's earlier contents never leak into a later step."""
+    world, total = 2, 48
+    mp.spawn(_exchange_main, args=(world, _free_port(), total, str(tmp_path)), nprocs=world, join=True)
+    outs = [torch.load(os.path.join(tmp_path, f"exchange{r}.pt")) for r in range(world)]
+    assert torch.equal(outs[0], outs[1])
+    for step in range(5):
+        assert torch.equal(outs[0][step][:, 0], torch.arange(total, dtype=torch.float32))
+        want = torch.repeat_interleave(torch.tensor([100.0 * step, 100.0 * step + 1.0]), total // world)
+        assert torch.equal(outs[0][step][:, 48], want)
