@@ -372,12 +372,14 @@ def main():
         outside the timed spans.  Returns the per-step times in ms (the exchange's tail added to the last) and the kernel
         launches inside the timed steps."""
         def one(k, start=None):
-            if exchange is not None:
-                exchange.release(after=start)             # the previous step's gather runs under this step
             if before_step is not None:
                 before_step(k)
             w.step()
             if exchange is not None:
+                # the previous step's gather runs under this step: enqueued after the step's launch, so that the host's
+                # time in the NCCL call passes while the step kernel runs, and held back on the device until the step's
+                # start event
+                exchange.release(after=start)
                 exchange.pack(stream)
         with torch.cuda.stream(stream):
             for k in range(warmup):
@@ -455,10 +457,9 @@ def main():
 
     def e2e_step():
         nuka._check(lib.nuka_world_upload_field(w._h, int(F.DRIVE_TARGET), targets.data_ptr(), targets.numel() * 4, 0))
-        if exchange is not None:
-            exchange.release()                   # the previous step's gather runs under this step
         w.step()
         if exchange is not None:
+            exchange.release()                   # the previous step's gather runs under this step
             with torch.cuda.stream(stream):
                 exchange.pack(stream)
         nuka._check(lib.nuka_world_download_field(w._h, int(F.JOINT_POSITION), out_q.data_ptr(), out_q.numel() * 4, 0))

@@ -61,7 +61,7 @@ void nuka_device_destroy(nuka_device_handle device);
  * otherwise creation returns NUKA_RESULT_NOT_SUPPORTED (terrain/heightfield/curriculum, instancing,
  * cloth, OGC, substeps > 1). */
 typedef struct nuka_world_desc_t {
-    const char* scene_path;            /* path of a ".nkt" cooked template file */
+    const char* scene_path;            /* path of a ".nks" scene file (cooked on load) or a ".nkt" cooked template file */
     uint32_t env_count;
     float fixed_dt;
     uint8_t determinism;               /* 0 or 1; larger values are INVALID_ARG */
@@ -191,6 +191,32 @@ nuka_result_t nuka_world_create_from_template(nuka_device_handle device, const n
 /* Parses a cooked template as world creation would and reports the same result code (OK, PARSE_ERROR for a malformed
  * or truncated container, NOT_SUPPORTED / INVALID_ARG for a model outside this path's limits), without a device. */
 nuka_result_t nuka_b200_template_check(const void* template_bytes, size_t template_size);
+
+/* Scene cooking.  nuka_world_create_from_scene (above) takes the reference's scene file: when scene_path holds a `.nks`
+ * document (JSON, src/scene/format/nks.cpp) the library cooks it as the reference's cooker does for the part this path
+ * covers (src/scene/cook/cook_to_model.cpp: one articulated tree of revolute / prismatic / fixed joints under a free or
+ * static root, sphere / capsule / box shapes, free rigid bodies, ground planes, position actuators as drives, the scene's
+ * contype / conaffinity bits, one candidate slot per admissible pair), with fixed_dt and the solver iteration counts of
+ * the descriptor; anything else in the scene gives NUKA_RESULT_NOT_SUPPORTED with a message, malformed JSON
+ * NUKA_RESULT_PARSE_ERROR.  A cooked template file (`.nkt`) loads as is.
+ * nuka_b200_scene_cook exposes the cooker itself (no device needed): scene text in, cooked template bytes out.  Call it
+ * with out = NULL to learn the size.  The options default (nuka_b200_cook_options_defaults) to what create_from_scene
+ * uses; the other settings serve callers that want a robot-versus-ground template from a scene that has no ground or
+ * actuators of its own. */
+typedef struct nuka_b200_cook_options_t {
+    float dt;
+    uint32_t velocity_iterations, position_iterations;
+    float default_kp, default_kd;       /* drive gains of scalar joints without an actuator (0 = undriven) */
+    uint32_t add_default_ground;        /* add a plane at ground_height when the scene has none */
+    float ground_height, ground_mu;
+    uint32_t self_collision;            /* robot rows keep their contype / conaffinity (else: they meet the ground only) */
+    uint32_t scene_filters;             /* every row keeps the scene's bits, the ground's included; implies self_collision */
+    uint32_t max_contacts;              /* candidate slots per env: 0 = one per shape row, 0xffffffff = every admissible pair */
+    uint32_t max_points;                /* contact points per env with solver rows: 0 = derived bound, at most 128 */
+} nuka_b200_cook_options_t;
+void nuka_b200_cook_options_defaults(nuka_b200_cook_options_t* options);
+nuka_result_t nuka_b200_scene_cook(const char* scene_json, size_t scene_size, const nuka_b200_cook_options_t* options, void* out,
+                                   size_t capacity, size_t* out_size);
 
 typedef struct nuka_b200_world_info_t {
     uint32_t env_count, links_per_env, bodies_per_env, dofs_per_env, contact_slots_per_env;

@@ -10,6 +10,7 @@
 #include <unordered_map>
 
 #include "../../include/nuka_b200.h"
+#include "nkb_scene.h"
 #include "nkb_world.h"
 
 namespace {
@@ -230,12 +231,43 @@ nuka_result_t nuka_b200_template_check(const void* template_bytes, size_t templa
     return Guard([&]() { (void)nkb::HostTemplate::Parse(template_bytes, template_size); return NUKA_RESULT_OK; });
 }
 
+void nuka_b200_cook_options_defaults(nuka_b200_cook_options_t* options) {
+    if (options == nullptr) return;
+    const nkb::CookOptions d;
+    options->dt = d.dt; options->velocity_iterations = d.vel_iters; options->position_iterations = d.pos_iters;
+    options->default_kp = d.kp; options->default_kd = d.kd;
+    options->add_default_ground = d.default_ground ? 1u : 0u; options->ground_height = d.ground_height; options->ground_mu = d.ground_mu;
+    options->self_collision = d.self_collision ? 1u : 0u; options->scene_filters = d.scene_filters ? 1u : 0u;
+    options->max_contacts = d.max_contacts; options->max_points = d.max_points;
+}
+
+nuka_result_t nuka_b200_scene_cook(const char* scene_json, size_t scene_size, const nuka_b200_cook_options_t* options, void* out,
+                                   size_t capacity, size_t* out_size) {
+    if (scene_json == nullptr || out_size == nullptr) { SetError("scene text or out_size is null"); return NUKA_RESULT_INVALID_ARG; }
+    return Guard([&]() {
+        nkb::CookOptions o;
+        if (options != nullptr) {
+            o.dt = options->dt; o.vel_iters = options->velocity_iterations; o.pos_iters = options->position_iterations;
+            o.kp = options->default_kp; o.kd = options->default_kd;
+            o.default_ground = options->add_default_ground != 0u; o.ground_height = options->ground_height; o.ground_mu = options->ground_mu;
+            o.self_collision = options->self_collision != 0u; o.scene_filters = options->scene_filters != 0u;
+            o.max_contacts = options->max_contacts; o.max_points = options->max_points;
+        }
+        const std::vector<uint8_t> blob = nkb::CookSceneForWorld(std::string(scene_json, scene_size), o);
+        *out_size = blob.size();
+        if (out == nullptr) return NUKA_RESULT_OK;                       // size query
+        if (capacity < blob.size()) { SetError("output buffer is smaller than the cooked template"); return NUKA_RESULT_INVALID_ARG; }
+        std::memcpy(out, blob.data(), blob.size());
+        return NUKA_RESULT_OK;
+    });
+}
+
 nuka_result_t nuka_world_create_from_scene(nuka_device_handle device, const nuka_world_desc_t* desc, nuka_world_handle* out) {
     if (desc == nullptr || desc->scene_path == nullptr) { SetError("scene_path is null"); if (out) *out = nullptr; return NUKA_RESULT_INVALID_ARG; }
     const std::string path = desc->scene_path;
-    const bool nkt = path.size() > 4 && path.compare(path.size() - 4, 4, ".nkt") == 0;
-    if (!nkt) {
-        SetError("only cooked template files (.nkt) are loadable; scene importers and the cooker are outside this path");
+    const auto ends_with = [&](const char* suffix) { const size_t n = std::strlen(suffix); return path.size() > n && path.compare(path.size() - n, n, suffix) == 0; };
+    if (!ends_with(".nks") && !ends_with(".nkt")) {
+        SetError("scene files (.nks) and cooked templates (.nkt) are loadable; the USD / URDF / MJCF importers are outside this path");
         if (out) *out = nullptr;
         return NUKA_RESULT_NOT_SUPPORTED;
     }
@@ -243,7 +275,22 @@ nuka_result_t nuka_world_create_from_scene(nuka_device_handle device, const nuka
     if (!in) { SetError("cannot open " + path); if (out) *out = nullptr; return NUKA_RESULT_FILE_NOT_FOUND; }
     std::stringstream ss;
     ss << in.rdbuf();
-    const std::string bytes = ss.str();
+    std::string bytes = ss.str();
+    // a scene document (.nks, JSON) is cooked here with the reference cooker's rules: drives from the scene's actuators,
+    // the scene's own ground and filter bits, one candidate slot per admissible pair; a cooked template (.nkt) loads as is
+    if (nkb::LooksLikeScene(bytes)) {
+        std::vector<uint8_t> cooked;
+        const nuka_result_t r = Guard([&]() {
+            nkb::CookOptions options;
+            if (desc->fixed_dt > 0.f) options.dt = desc->fixed_dt;
+            if (desc->solver_vel_iters != 0u) options.vel_iters = desc->solver_vel_iters;
+            if (desc->solver_pos_iters != 0u) options.pos_iters = desc->solver_pos_iters;
+            cooked = nkb::CookSceneForWorld(bytes, options);
+            return NUKA_RESULT_OK;
+        });
+        if (r != NUKA_RESULT_OK) { if (out) *out = nullptr; return r; }
+        return CreateWorld(device, desc, cooked.data(), cooked.size(), out);
+    }
     return CreateWorld(device, desc, bytes.data(), bytes.size(), out);
 }
 

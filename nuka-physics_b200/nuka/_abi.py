@@ -49,6 +49,13 @@ class ObservationDesc(ctypes.Structure):
                 ("row_stride", ctypes.c_uint32)]
 
 
+class CookOptions(ctypes.Structure):
+    _fields_ = [("dt", ctypes.c_float), ("velocity_iterations", ctypes.c_uint32), ("position_iterations", ctypes.c_uint32),
+                ("default_kp", ctypes.c_float), ("default_kd", ctypes.c_float), ("add_default_ground", ctypes.c_uint32),
+                ("ground_height", ctypes.c_float), ("ground_mu", ctypes.c_float), ("self_collision", ctypes.c_uint32),
+                ("scene_filters", ctypes.c_uint32), ("max_contacts", ctypes.c_uint32), ("max_points", ctypes.c_uint32)]
+
+
 EXPORTS = [
     "nuka_get_version", "nuka_result_message", "nuka_last_error_message", "nuka_device_create", "nuka_device_destroy",
     "nuka_world_create_from_scene", "nuka_world_destroy", "nuka_world_step", "nuka_world_step_n", "nuka_world_set_execution_mode",
@@ -57,7 +64,7 @@ EXPORTS = [
     "nuka_world_get_buffer_view", "nuka_world_upload_field", "nuka_world_download_field", "nuka_world_create_from_template",
     "nuka_b200_world_info", "nuka_b200_world_run_stage", "nuka_b200_world_launch_count", "nuka_b200_world_reset_envs_static",
     "nuka_b200_world_pack_observations", "nuka_b200_observation_desc_defaults", "nuka_b200_world_reset_envs_masked",
-    "nuka_b200_world_set_contact_readout", "nuka_b200_world_set_broadphase", "nuka_b200_template_check", "nuka_world_checkpoint_capture", "nuka_world_checkpoint_restore", "nuka_checkpoint_destroy",
+    "nuka_b200_world_set_contact_readout", "nuka_b200_world_set_broadphase", "nuka_b200_template_check", "nuka_b200_cook_options_defaults", "nuka_b200_scene_cook", "nuka_world_checkpoint_capture", "nuka_world_checkpoint_restore", "nuka_checkpoint_destroy",
     "nuka_checkpoint_write", "nuka_world_checkpoint_read", "nuka_checkpoint_byte_size", "nuka_checkpoint_equal", "nuka_world_state_hash",
 ]
 
@@ -98,6 +105,9 @@ def lib():
     L.nuka_b200_observation_desc_defaults.argtypes = [ctypes.POINTER(ObservationDesc)]
     L.nuka_b200_observation_desc_defaults.restype = None
     L.nuka_b200_world_reset_envs_masked.argtypes = [vp, vp]
+    L.nuka_b200_cook_options_defaults.argtypes = [ctypes.POINTER(CookOptions)]
+    L.nuka_b200_cook_options_defaults.restype = None
+    L.nuka_b200_scene_cook.argtypes = [ctypes.c_char_p, sz, ctypes.POINTER(CookOptions), vp, sz, ctypes.POINTER(sz)]
     L.nuka_b200_world_set_contact_readout.argtypes = [vp, u32]
     L.nuka_b200_world_set_broadphase.argtypes = [vp, u32]
     L.nuka_world_forward_kinematics.argtypes = [vp]

@@ -172,6 +172,28 @@ def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0,
     return tb
 
 
+def cook_native(scene_text, **options):
+    """The library's own cooker (csrc/nkb_scene.cpp, what nuka_world_create_from_scene runs on a ``.nks`` path): scene
+    text in, cooked template bytes out.  Keyword options are the fields of nuka_b200_cook_options_t; unset fields keep the
+    library's defaults (drives from the scene's actuators only, the scene's own ground and filter bits, one candidate slot
+    per admissible pair)."""
+    import ctypes
+    from . import _abi, _check
+    lib = _abi.lib()
+    o = _abi.CookOptions()
+    lib.nuka_b200_cook_options_defaults(ctypes.byref(o))
+    for key, value in options.items():
+        if not hasattr(o, key):
+            raise TypeError(f"unknown cook option {key!r}")
+        setattr(o, key, value)
+    text = scene_text.encode() if isinstance(scene_text, str) else bytes(scene_text)
+    size = ctypes.c_size_t(0)
+    _check(lib.nuka_b200_scene_cook(text, len(text), ctypes.byref(o), None, 0, ctypes.byref(size)))
+    out = ctypes.create_string_buffer(size.value)
+    _check(lib.nuka_b200_scene_cook(text, len(text), ctypes.byref(o), out, size.value, ctypes.byref(size)))
+    return out.raw[:size.value]
+
+
 def _frame(pos=(0.0, 0.0, 0.0), quat=(1.0, 0.0, 0.0, 0.0)):
     return {"pos": [float(v) for v in pos], "quat": [float(v) for v in quat]}
 

@@ -152,6 +152,28 @@ def test_scene_path_loads_a_cooked_template_file(device, tmp_path):
     w.destroy()
 
 
+def test_scene_path_takes_the_scene_file_the_reference_takes(device):
+    """nuka_world_create_from_scene on a `.nks` document: the library cooks it itself (reference semantics: the scene's
+    actuators, ground and filter bits, one candidate slot per admissible pair), and the world steps bit-identically to
+    one created from the Python cooker's template of the same file."""
+    import os
+    from nuka import nks
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "scene_quadbox.nks")
+    E = 16
+    a = nuka.World.create_from_scene(device, path, E, dt=1.0 / 200.0, solver_vel_iters=4)
+    tb = nks.cook(path, dt=1.0 / 200.0, vel_iters=4, kp=0.0, kd=0.0, scene_filters=True, ground_height=None, max_contacts=35)
+    b = nuka.World.create_from_template(device, tb.blob(), E)
+    assert a.info.contact_slots_per_env == 35 and a.info.links_per_env == 13 and a.info.bodies_per_env == b.info.bodies_per_env
+    st = T.quadruped_state(E, 0)
+    for w in (a, b):
+        w.upload(F.JOINT_POSITION, st["q"]); w.upload(F.BASE_POSE, st["base_pose"]); w.forward_kinematics()
+        w.step_n(40)
+    for f in (F.JOINT_POSITION, F.JOINT_VELOCITY, F.BASE_POSE, F.RIGID_BODY_TRANSFORM, F.CONTACT_COUNT):
+        assert np.array_equal(a.download(f), b.download(f)), f
+    assert a.download(F.CONTACT_COUNT).sum() > 0
+    a.destroy(); b.destroy()
+
+
 def test_observation_record_matches_the_reference_contract(device):
     """The pack kernel against the numpy statement of python/nuka/tasks/go2_obs.py:282-305 (the reference checks its
     own composer the same way, python/tests/test_gym_env.py:87), with a joint permutation, a reward column and a row
