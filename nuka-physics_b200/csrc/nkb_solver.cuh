@@ -725,7 +725,6 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
 #pragma unroll
             for (int r = 0; r < NR; ++r) inverse[r] = 0.f;
             __syncwarp();
-#ifdef NKB_CHOLESKY_LEFT_LOOKING
 #pragma unroll (kDim != 0 ? 8 : 1)
             for (uint32_t k = 0u; k < dim; ++k) {
                 float value[NR];
@@ -760,53 +759,6 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
                 }
                 __syncwarp();
             }
-#else
-            // Right-looking form: column k is scaled and published, then every lane updates the rest of its own rows with
-            // independent multiply-adds (the left-looking form's dot products are one dependent chain per column).  The
-            // column buffer is the low-part vector of the inertial sum, dead since that sum was taken.
-            {
-                float* col = lo_v;
-#pragma unroll (kDim != 0 ? 8 : 1)
-                for (uint32_t k = 0u; k < dim; ++k) {
-                    const float pivot = H[k * ldh + k];
-                    valid &= pivot > 0.f && pivot <= FLT_MAX;
-                    const float sc = rsqrtf(valid ? pivot : 1.0f), root = pivot * sc;
-                    float mine[NR];
-#pragma unroll
-                    for (int r = 0; r < NR; ++r) {
-                        const uint32_t c = l + 32u * r;
-                        mine[r] = 0.f;
-                        if (coord[r] && c >= k) {
-                            mine[r] = c == k ? root : Hr[r][k] * sc;
-                            Hr[r][k] = mine[r];
-                            if (c > k) col[c] = mine[r];
-                        }
-                        inverse[r] = c == k ? sc : inverse[r];
-                    }
-                    __syncwarp();
-                    // H[c][j] -= L[c][k] L[j][k] for k < j <= c: single entries up to the next multiple of 4, then whole
-                    // float4 chunks (entries past the diagonal and in the row padding take harmless values nobody reads)
-                    const uint32_t first = k + 1u, aligned = (first + 3u) & ~3u;
-#pragma unroll
-                    for (int r = 0; r < NR; ++r) {
-                        const uint32_t c = l + 32u * r;
-                        if (!(coord[r] && c > k)) continue;
-                        const float v = mine[r];
-                        for (uint32_t j = first; j < aligned && j <= c; ++j) Hr[r][j] = fmaf(-v, col[j], Hr[r][j]);
-                        float4* Hr4 = reinterpret_cast<float4*>(Hr[r]);
-                        const float4* col4 = reinterpret_cast<const float4*>(col);
-#pragma unroll (kDim != 0 ? 2 : 1)
-                        for (uint32_t q = aligned >> 2; q <= (c >> 2) && aligned <= c; ++q) {
-                            float4 h = Hr4[q];
-                            const float4 w = col4[q];
-                            h.x = fmaf(-v, w.x, h.x); h.y = fmaf(-v, w.y, h.y); h.z = fmaf(-v, w.z, h.z); h.w = fmaf(-v, w.w, h.w);
-                            Hr4[q] = h;
-                        }
-                    }
-                    __syncwarp();
-                }
-            }
-#endif
             if (!valid) { failure = true; break; }
             tick(e, 19);
             // ---- d = H^-1 g ----
