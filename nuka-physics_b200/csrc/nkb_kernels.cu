@@ -20,22 +20,26 @@ __global__ void reset_kernel(ResetParams r) {
     }
 }
 
-extern const StepVariant kStepNarrow, kStepNarrowRigid, kStepWide, kStepWideRigid;
+extern const StepVariant kStepNarrow, kStepNarrowSlim, kStepNarrowRigid, kStepWide, kStepWideRigid;
 
-// up to 32 or up to 64 coordinates per articulation; with or without free rigid bodies
-static const StepVariant& step_variant(uint32_t ndof, uint32_t n_free) {
+bool step_kernel_has_slim(uint32_t ndof, uint32_t n_free) { return ndof <= 32u && n_free == 0u; }
+
+// up to 32 or up to 64 coordinates per articulation; with or without free rigid bodies; the slim (128-register) build
+// exists for the first kind only
+static const StepVariant& step_variant(uint32_t ndof, uint32_t n_free, bool slim) {
     if (ndof > 32u) return n_free != 0u ? kStepWideRigid : kStepWide;
-    return n_free != 0u ? kStepNarrowRigid : kStepNarrow;
+    if (n_free != 0u) return kStepNarrowRigid;
+    return slim ? kStepNarrowSlim : kStepNarrow;
 }
 
-int step_kernel_registers(uint32_t ndof, uint32_t n_free) { return step_variant(ndof, n_free).registers(); }
+int step_kernel_registers(uint32_t ndof, uint32_t n_free, bool slim) { return step_variant(ndof, n_free, slim).registers(); }
 
-int step_kernel_resident_blocks(uint32_t ndof, uint32_t n_free, uint32_t warps_per_block, size_t shared_bytes) {
-    return step_variant(ndof, n_free).resident_blocks(warps_per_block, shared_bytes);
+int step_kernel_resident_blocks(uint32_t ndof, uint32_t n_free, bool slim, uint32_t warps_per_block, size_t shared_bytes) {
+    return step_variant(ndof, n_free, slim).resident_blocks(warps_per_block, shared_bytes);
 }
 
-cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
-    return step_variant(p.t.ndof, p.t.n_free).launch(p, warps_per_block, stream);
+cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, bool slim, cudaStream_t stream) {
+    return step_variant(p.t.ndof, p.t.n_free, slim).launch(p, warps_per_block, stream);
 }
 
 // One observation record per env, composed from the state arrays in one pass (the reference's gym layer builds the same

@@ -27,9 +27,11 @@ struct ResetParams {
 // shared memory and block slots considered); 0 when the shape cannot launch.  The device must be current.
 // The step kernel has one variant per (coordinates per lane, free rigid bodies present) pair, chosen from `ndof`
 // (up to 32 / up to 64 coordinates) and `n_free` (free dynamic bodies per env).
-int step_kernel_resident_blocks(uint32_t ndof, uint32_t n_free, uint32_t warps_per_block, size_t shared_bytes);
+int step_kernel_resident_blocks(uint32_t ndof, uint32_t n_free, bool slim, uint32_t warps_per_block, size_t shared_bytes);
+// Whether a slim (128-register) build of the world's kernel variant exists.
+bool step_kernel_has_slim(uint32_t ndof, uint32_t n_free);
 // Registers per thread of the step kernel variant that serves the world.
-int step_kernel_registers(uint32_t ndof, uint32_t n_free);
+int step_kernel_registers(uint32_t ndof, uint32_t n_free, bool slim);
 // Host-side handle of one compiled step-kernel variant.
 struct StepParams;
 struct StepVariant {
@@ -38,7 +40,7 @@ struct StepVariant {
     cudaError_t (*launch)(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream);
 };
 // Enqueues `p.steps` fused steps (or one parity-tap stage, see StepMode) for every env.
-cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream);
+cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, bool slim, cudaStream_t stream);
 // Restores `count` envs (all when r.env_ids is null) from their snapshots.
 cudaError_t launch_reset(const ResetParams& r, uint32_t count, cudaStream_t stream);
 // Observation record of the reference's gym layer (python/nuka/tasks/go2_obs.py:11-20) for a floating-base robot with

@@ -152,6 +152,12 @@ NKB_DEV void stage_store_bodies(Env& e, bool velocities) {
 #ifndef NKB_MAXNREG_RIGID
 #define NKB_MAXNREG_RIGID 224
 #endif
+// The slim build of the same kernel: at 128 registers a fourth warp fits each scheduler partition, so small envs (15 KB
+// of shared memory) reach 15 resident warps per SM instead of 12 and 4096 envs need two rounds instead of 2.3.  It
+// spills about 200 bytes; a world takes it only where the extra residency is really there (World::BuildLayout).
+#ifndef NKB_MAXNREG_SLIM
+#define NKB_MAXNREG_SLIM 128
+#endif
 template <int NR, bool kRigid>
 NKB_DEV void advance_env(const StepParams& p, float* sm, uint32_t env, uint32_t lane) {
     const TemplateView& t = p.t;
@@ -316,8 +322,8 @@ NKB_DEV void team_helper(float* sm, const SmemLayout& shared_layout, const Templ
 
 // Block layout: blockDim.x / 32 warps, `team` consecutive warps per env (one unless the world runs in team mode); an
 // env's shared-memory slice is shared by its team.
-template <int NR, bool kRigid>
-__global__ void __maxnreg__(kRigid ? NKB_MAXNREG_RIGID : NKB_MAXNREG) step_kernel(const __grid_constant__ StepParams p) {
+template <int NR, bool kRigid, bool kSlim>
+__global__ void __maxnreg__(kRigid ? NKB_MAXNREG_RIGID : (kSlim ? NKB_MAXNREG_SLIM : NKB_MAXNREG)) step_kernel(const __grid_constant__ StepParams p) {
     extern __shared__ __align__(16) float smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t team = kRigid ? p.sm.team : 1u;
@@ -345,7 +351,7 @@ __global__ void __maxnreg__(kRigid ? NKB_MAXNREG_RIGID : NKB_MAXNREG) step_kerne
 // Raises the kernel's dynamic shared-memory limit to `bytes` if it is not there yet.  The limit is per function and
 // per device and only ever grows, so worlds of different sizes stepped from different threads cannot undo each other's
 // setting between the attribute call and the launch.
-template <int NR, bool kRigid>
+template <int NR, bool kRigid, bool kSlim>
 static cudaError_t variant_reserve_shared(size_t bytes) {
     static std::mutex lock;
     static size_t reserved[64] = {0};
@@ -356,48 +362,48 @@ static cudaError_t variant_reserve_shared(size_t bytes) {
     if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> hold(lock);
     if (bytes <= reserved[device]) return cudaSuccess;
-    err = cudaFuncSetAttribute(step_kernel<NR, kRigid>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    err = cudaFuncSetAttribute(step_kernel<NR, kRigid, kSlim>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (err == cudaSuccess) reserved[device] = bytes;
     return err;
 }
 
-template <int NR, bool kRigid>
+template <int NR, bool kRigid, bool kSlim>
 static int variant_resident_blocks(uint32_t warps_per_block, size_t shared_bytes) {
-    if (variant_reserve_shared<NR, kRigid>(shared_bytes) != cudaSuccess) {
+    if (variant_reserve_shared<NR, kRigid, kSlim>(shared_bytes) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     int blocks = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, step_kernel<NR, kRigid>, (int)(warps_per_block * 32u), shared_bytes) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, step_kernel<NR, kRigid, kSlim>, (int)(warps_per_block * 32u), shared_bytes) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     return blocks;
 }
 
-template <int NR, bool kRigid>
+template <int NR, bool kRigid, bool kSlim>
 static int variant_registers() {
     cudaFuncAttributes attr{};
-    if (cudaFuncGetAttributes(&attr, step_kernel<NR, kRigid>) != cudaSuccess) { cudaGetLastError(); return 0; }
+    if (cudaFuncGetAttributes(&attr, step_kernel<NR, kRigid, kSlim>) != cudaSuccess) { cudaGetLastError(); return 0; }
     return attr.numRegs;
 }
 
-template <int NR, bool kRigid>
+template <int NR, bool kRigid, bool kSlim>
 static cudaError_t variant_launch(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
     const uint32_t team = kRigid ? p.sm.team : 1u;
     const uint32_t envs_per_block = warps_per_block / team;
     if (envs_per_block == 0u || envs_per_block * team != warps_per_block || envs_per_block > 15u) return cudaErrorInvalidConfiguration;
     const size_t bytes = (size_t)envs_per_block * p.sm.words * sizeof(float);
-    const cudaError_t err = variant_reserve_shared<NR, kRigid>(bytes);
+    const cudaError_t err = variant_reserve_shared<NR, kRigid, kSlim>(bytes);
     if (err != cudaSuccess) return err;
     const uint32_t envs = p.sel_ids != nullptr ? p.sel_count : p.s.env_count;
     if (envs == 0u) return cudaSuccess;
     const uint32_t blocks = (envs + envs_per_block - 1u) / envs_per_block;
-    step_kernel<NR, kRigid><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
+    step_kernel<NR, kRigid, kSlim><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
     return cudaGetLastError();
 }
 
-#define NKB_STEP_VARIANT(name, NR, RIGID) \
-    extern const StepVariant name = {variant_resident_blocks<NR, RIGID>, variant_registers<NR, RIGID>, variant_launch<NR, RIGID>};
+#define NKB_STEP_VARIANT(name, NR, RIGID, SLIM) \
+    extern const StepVariant name = {variant_resident_blocks<NR, RIGID, SLIM>, variant_registers<NR, RIGID, SLIM>, variant_launch<NR, RIGID, SLIM>};
 
 }  // namespace nkb

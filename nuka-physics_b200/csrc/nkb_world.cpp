@@ -361,30 +361,38 @@ void World::BuildLayout() {
     s.words = at;
     const size_t bytes = static_cast<size_t>(s.words) * 4u;
     if (bytes > 220u * 1024u) throw Error(kNotSupported, "template needs more shared memory per env than one SM provides");
-    // block shape that keeps the most warps resident on one SM (228 KB shared memory, 1 KB reserved per block)
-    // Measured on the 4096-env quadruped: blocks of one warp run markedly slower than blocks of 5-6 warps at the same
-    // residency, so the largest block within 10 % of the best residency wins.
-    size_t resident[kWarpsPerBlockMax + 1] = {0};
-    size_t best = 0;
+    // kernel build (regular or slim) and block shape: what keeps the most warps resident on one SM
     const uint32_t team = s.team;                  // a block holds whole teams: w counts warps, w / team envs
-    for (uint32_t w = team; w <= kWarpsPerBlockMax; w += team) {
-        if ((w / team) * bytes > 227u * 1024u) break;
-        resident[w] = static_cast<size_t>(step_kernel_resident_blocks(n, t.n_free, w, (w / team) * bytes)) * w;      // asks the runtime
-        best = std::max(best, resident[w]);
-    }
-    // among the shapes within 10 % of the best residency: a multiple of 4 warps (one per scheduler, measured 0.5 %
-    // faster than 6-warp blocks at the same residency on the quadruped), else the largest
+    size_t resident[2][kWarpsPerBlockMax + 1] = {{0}, {0}};
+    size_t best[2] = {0, 0};
+    const bool has_slim = step_kernel_has_slim(n, t.n_free);
+    for (int slim = 0; slim < (has_slim ? 2 : 1); ++slim)
+        for (uint32_t w = team; w <= kWarpsPerBlockMax; w += team) {
+            if ((w / team) * bytes > 227u * 1024u) break;
+            resident[slim][w] = static_cast<size_t>(step_kernel_resident_blocks(n, t.n_free, slim != 0, w, (w / team) * bytes)) * w;      // asks the runtime
+            best[slim] = std::max(best[slim], resident[slim][w]);
+        }
+    // The slim build pays about 200 bytes of spills for a fourth warp per scheduler partition: worth it where shared
+    // memory lets the extra warps in (measured on the 4096-env quadruped: 15 instead of 12 resident envs per SM, 0.445 ms
+    // per step instead of 0.508), not where shared memory caps residency first.
+    slim_ = has_slim && best[1] * 10u >= best[0] * 12u;
+    if (const char* forced = std::getenv("NUKA_B200_SLIM")) slim_ = has_slim && std::atoi(forced) != 0;     // variant experiments and tests
+    const size_t* fits = resident[slim_ ? 1 : 0];
+    const size_t most = best[slim_ ? 1 : 0];
+    // Block shape: the one that keeps the most warps resident (228 KB shared memory, 1 KB reserved per block); among
+    // equals a multiple of 4 warps (one per scheduler, measured 0.5 % faster than 6-warp blocks at the same residency on
+    // the quadruped), else the largest.
     warps_per_block_ = team;
-    for (uint32_t w = team; w <= kWarpsPerBlockMax; w += team) if (resident[w] * 10u >= best * 9u) warps_per_block_ = w;
-    for (uint32_t w = 4; w <= kWarpsPerBlockMax; w += 4)
-        if (w % team == 0u && resident[w] * 10u >= best * 9u && resident[w] >= resident[warps_per_block_]) warps_per_block_ = w;
+    for (uint32_t w = team; w <= kWarpsPerBlockMax; w += team) if (fits[w] == most) warps_per_block_ = w;
+    for (uint32_t w = 4; w <= kWarpsPerBlockMax; w += 4) if (w % team == 0u && fits[w] == most) warps_per_block_ = w;
     if (const char* forced = std::getenv("NUKA_B200_WARPS_PER_BLOCK")) {          // block-shape experiments
         const uint32_t w = static_cast<uint32_t>(std::atoi(forced));
-        if (w >= 1u && w <= kWarpsPerBlockMax && w % team == 0u && resident[w] != 0u) warps_per_block_ = w;
+        if (w >= 1u && w <= kWarpsPerBlockMax && w % team == 0u && fits[w] != 0u) warps_per_block_ = w;
     }
     if (std::getenv("NUKA_B200_DEBUG_LAYOUT") != nullptr) {
-        std::fprintf(stderr, "[nuka_b200] %zu B of shared memory per env, %d registers per thread; resident warps per SM by block size:", bytes, step_kernel_registers(n, t.n_free));
-        for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) std::fprintf(stderr, " %u:%zu", w, resident[w]);
+        std::fprintf(stderr, "[nuka_b200] %zu B of shared memory per env, %d registers per thread%s; resident warps per SM by block size:", bytes,
+                     step_kernel_registers(n, t.n_free, slim_), slim_ ? " (slim build)" : "");
+        for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) std::fprintf(stderr, " %u:%zu", w, fits[w]);
         std::fprintf(stderr, " -> %u warps per block, %u per env\n", warps_per_block_, team);
         std::fprintf(stderr, "[nuka_b200] word offsets: overlay %u mass %u vecs %u bodies %u contacts %u heads %u pool %u blocks %u end %u\n",
                      s.xrot, s.mass, s.vecs, s.bpose, s.pairs, s.heads, s.jpool, s.binfo, s.words);
@@ -531,7 +539,7 @@ void World::Refresh(const uint32_t* ids, uint32_t count, const uint32_t* mask) {
     p.mode = kModeRefresh; p.steps = 1;
     p.sel_ids = ids; p.sel_count = ids != nullptr ? count : 0u; p.sel_mask = mask;
     Check(cudaSetDevice(device_), "cudaSetDevice");
-    Check(launch_step(p, warps_per_block_, stream_), "refresh launch");
+    Check(launch_step(p, warps_per_block_, slim_, stream_), "refresh launch");
     ++launches_;
 }
 
@@ -542,7 +550,7 @@ void World::RunStage(uint32_t mode) {
     StepParams p = params_;
     p.mode = mode; p.steps = 1;
     Check(cudaSetDevice(device_), "cudaSetDevice");
-    Check(launch_step(p, warps_per_block_, stream_), "stage launch");
+    Check(launch_step(p, warps_per_block_, slim_, stream_), "stage launch");
     ++launches_;
 }
 
@@ -562,7 +570,7 @@ void World::Step(uint32_t n) {
         // memory after every step, so the split changes no result); the cap keeps any one launch short
         for (uint32_t done = 0u; done < n; done += kMaxStepsPerLaunch) {
             p.steps = std::min(n - done, kMaxStepsPerLaunch);
-            Check(launch_step(p, warps_per_block_, stream_), "step launch");
+            Check(launch_step(p, warps_per_block_, slim_, stream_), "step launch");
             ++launches_;
         }
         return;
@@ -574,10 +582,10 @@ void World::Step(uint32_t n) {
         // configure the kernel's shared-memory attribute outside the capture
         StepParams warm = params_;
         warm.mode = kModeRefresh; warm.steps = 1;
-        Check(launch_step(warm, warps_per_block_, stream_), "graph warm-up launch");
+        Check(launch_step(warm, warps_per_block_, slim_, stream_), "graph warm-up launch");
         ++launches_;
         Check(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal), "begin capture");
-        const cudaError_t launched = launch_step(p, warps_per_block_, stream_);
+        const cudaError_t launched = launch_step(p, warps_per_block_, slim_, stream_);
         const cudaError_t ended = cudaStreamEndCapture(stream_, &graph_);
         Check(launched, "captured step launch");
         Check(ended, "end capture");

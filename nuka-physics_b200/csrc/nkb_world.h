@@ -103,6 +103,7 @@ private:
     StepParams params_{};
     StateView readout_{};               // contact read-out pointers while the read-out is switched off
     uint32_t warps_per_block_ = 1;
+    bool slim_ = false;        // the world runs the 128-register build of its kernel variant
     std::vector<void*> allocations_;
     ResetParams reset_{};
     uint32_t* reset_ids_ = nullptr;

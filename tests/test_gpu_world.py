@@ -312,3 +312,24 @@ def test_drive_targets_written_through_a_view_steer_the_next_step(device):
     assert np.abs(others).mean() < 0.1              # the rest of the robot only adjusts its balance
     assert w.download(F.ENV_STATUS).max() == 0
     w.destroy()
+
+
+def test_slim_and_regular_kernel_builds_give_the_same_state(device):
+    """A world picks the 128-register build of its step kernel where that buys residency; the two builds are the same
+    arithmetic, so the states they produce are bit-identical."""
+    import os
+    E = 128
+    st = T.quadruped_state(E, 3)
+    out = []
+    for slim in ("0", "1"):
+        os.environ["NUKA_B200_SLIM"] = slim            # read when the world lays out its launch
+        try:
+            w = nuka.World.create_from_template(device, T.quadruped(0).blob(), E)
+        finally:
+            del os.environ["NUKA_B200_SLIM"]
+        w.upload(F.JOINT_POSITION, st["q"]); w.upload(F.BASE_POSE, st["base_pose"]); w.forward_kinematics()
+        w.step_n(80)
+        out.append([w.download(f) for f in (F.JOINT_POSITION, F.JOINT_VELOCITY, F.BASE_POSE, F.LINK_VELOCITY, F.CONTACT_COUNT, F.SOLVER_SWEEPS)])
+        w.destroy()
+    for a, b in zip(*out):
+        assert np.array_equal(a, b)
