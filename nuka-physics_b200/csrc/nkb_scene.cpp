@@ -535,7 +535,7 @@ class Cooker {
         const uint32_t L = static_cast<uint32_t>(tb_.links.size()), B = static_cast<uint32_t>(tb_.bodies.size());
         uint32_t max_contacts = o_.max_contacts;
         if (max_contacts == 0u) max_contacts = std::max(shape_rows_, 1u);
-        else if (max_contacts == kEveryAdmissiblePair) max_contacts = std::max(B * (B - (B ? 1u : 0u)) / 2u, 1u);      // narrowed by the caller
+        else if (max_contacts == kEveryAdmissiblePair) max_contacts = 1u;      // a placeholder: the caller counts the admissible pairs and cooks again
         Blob out;
         out.F32("cfg_f", {o_.dt, 0.0f, 0.0f, -9.81f, 0.3f, 0.001f, 0.0f, 3.0e38f, 0.0f, 1.0e-5f});
         out.U32("cfg_u", {o_.vel_iters, o_.pos_iters, max_contacts, 0u, L, B});
@@ -624,7 +624,6 @@ std::vector<uint8_t> CookSceneForWorld(const std::string& json_text, const CookO
     const bool none = parsed.adm_pairs.size() == 1 && parsed.adm_pairs[0] == 0u;
     CookOptions narrowed = options;
     narrowed.max_contacts = none ? 1u : static_cast<uint32_t>(parsed.adm_pairs.size());
-    if (none) return CookScene(json_text, narrowed);
     return CookScene(json_text, narrowed);
 }
 

@@ -55,6 +55,20 @@ def test_every_admissible_pair_gets_a_slot():
         assert int(arrays["cfg_u"][2]) == slots, scene
 
 
+def test_a_scene_with_more_pairs_than_slots_is_refused_by_the_template_check():
+    """48 boxes and a plane admit 1176 pairs; the path holds 1024 candidate slots per env, so the reference's budget of one
+    slot per admissible pair does not fit and the cooked template says so at the check (a caller can cook with its own
+    max_contacts instead)."""
+    from nuka import templates as T
+    text = json.dumps(nks.scene_from_builder(T.box_pile(0, count=48)))
+    lib = nuka._abi.lib()
+    blob = nks.cook_native(text)
+    assert int(nkt.unpack(blob)["cfg_u"][2]) == 1176
+    assert lib.nuka_b200_template_check(blob, len(blob)) == nuka._abi.NOT_SUPPORTED
+    blob = nks.cook_native(text, max_contacts=288, max_points=288)
+    assert lib.nuka_b200_template_check(blob, len(blob)) == 0
+
+
 def test_cooked_scene_passes_the_template_check():
     lib = nuka._abi.lib()
     for scene in SCENES:
