@@ -21,6 +21,7 @@ Prints one JSON line on rank 0.
 """
 import argparse
 import ctypes
+import gc
 import json
 import os
 import statistics
@@ -393,6 +394,8 @@ def main():
             launches0 = w.launch_count()
             starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
             ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+            gc.collect()
+            gc.disable()                                  # no collector pause between a start event and its step's launch
             for k in range(steps):
                 if flush is not None:
                     flush.add_(1.0)                       # evicts the 126 MB L2 (outside the timed spans)
@@ -403,6 +406,7 @@ def main():
             if exchange is not None:
                 exchange.drain(stream)
             ends[steps].record(stream)
+            gc.enable()
             stream.synchronize()
             torch.cuda.synchronize()
             if distributed:

@@ -65,7 +65,7 @@ typedef struct nuka_world_desc_t {
     uint32_t env_count;
     float fixed_dt;
     uint8_t determinism;               /* 0 or 1; larger values are INVALID_ARG */
-    uint8_t control_mode;              /* 0 PD position, 1 torque, 2 velocity, 5 actuator; 3 and 4 (computed torque, OSC) NOT_SUPPORTED */
+    uint8_t control_mode;              /* 0 PD position, 1 torque, 2 velocity, 3 computed torque, 5 actuator; 4 (OSC) NOT_SUPPORTED */
     uint32_t osc_task_link;
     float terrain_step_height, terrain_step_width, terrain_platform_width, terrain_grid_width, terrain_grid_height_max;
     uint32_t instance_count;
@@ -151,6 +151,7 @@ typedef enum nuka_state_field_t {
     NUKA_FIELD_VELOCITY_TARGET = 13,          /* E x L f32, writable */
     NUKA_FIELD_ACTUATOR_NOLOAD_SPEED = 14,    /* E x L f32, writable; actuator mode's torque-speed envelope, <= 0 disables it */
     NUKA_FIELD_JOINT_FEEDFORWARD = 22,        /* E x L f32, writable */
+    NUKA_FIELD_ACCELERATION_TARGET = 56,      /* E x L f32, writable; computed-torque control's feed-forward acceleration */
     NUKA_FIELD_BODY_LINEAR_VELOCITY = 25,     /* E x B x 3 f32 */
     NUKA_FIELD_BODY_ANGULAR_VELOCITY = 26,    /* E x B x 3 f32 */
     NUKA_FIELD_ACTUATOR_EFFORT = 29,          /* E x L f32 */

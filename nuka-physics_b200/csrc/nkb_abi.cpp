@@ -120,7 +120,7 @@ nuka_result_t ValidateDesc(const nuka_world_desc_t* d) {
     if (d->determinism > 1u) { SetError("determinism must be 0 or 1"); return NUKA_RESULT_INVALID_ARG; }
     if (d->fixed_dt < 0.f || d->fixed_dt != d->fixed_dt) { SetError("fixed_dt must be positive"); return NUKA_RESULT_INVALID_ARG; }
     if (d->control_mode > 5u) { SetError("control_mode must be 0..5"); return NUKA_RESULT_INVALID_ARG; }
-    if (d->control_mode == 3u || d->control_mode == 4u) { SetError("control modes 3 and 4 (computed torque, OSC) are not provided"); return NUKA_RESULT_NOT_SUPPORTED; }
+    if (d->control_mode == 4u) { SetError("control mode 4 (operational-space control) is not provided"); return NUKA_RESULT_NOT_SUPPORTED; }
     const bool unsupported = d->terrain_step_height != 0.f || d->terrain_step_width != 0.f || d->terrain_platform_width != 0.f ||
         d->terrain_grid_width != 0.f || d->terrain_grid_height_max != 0.f || d->instance_count > 1u || d->contact_family != 0u ||
         d->heightfield_terrain_type != 0u || (d->heightfield_image_path != nullptr && d->heightfield_image_path[0] != '\0') ||

@@ -188,16 +188,19 @@ NKB_DEV void stage_drives(Env& e) {
     const float target = e.s->drive_target[at], kp = e.s->kp[at], kd = e.s->kd[at], vt = e.s->vel_target[at];
     const float limit = e.s->force_limit[at], ff = e.s->feedforward[at];
     const uint32_t mode = t.cfg.control_mode;
-    const bool position_control = mode == 0u, velocity_control = mode == 2u;
+    const bool inverse_dynamics = mode == 3u;          // computed torque: the command comes from stage_computed_torque
+    const bool position_control = mode == 0u || inverse_dynamics, velocity_control = mode == 2u;
     if ((position_control && (!isfinite(target) || !isfinite(kp) || kp < 0.f || !isfinite(kd) || kd < 0.f)) ||
-        ((position_control || velocity_control) && !isfinite(vt)) || (velocity_control && (!isfinite(kp) || kp < 0.f))) {
+        ((position_control || velocity_control) && !isfinite(vt)) || (velocity_control && (!isfinite(kp) || kp < 0.f)) ||
+        (inverse_dynamics && !isfinite(e.s->acc_target[at]))) {
         e.status |= kStatusControlFailure; return;
     }
     const float noload = mode == 5u ? e.s->noload_speed[at] : 0.f;
     if (!isfinite(noload)) { e.status |= kStatusControlFailure; return; }
     float lower = limit > 0.f ? -limit : -FLT_MAX, upper = limit > 0.f ? limit : FLT_MAX;
     float damping = 0.f, bias = target;                       // torque mode: the target field carries the commanded effort
-    if (position_control) { damping = kd + t.cfg.dt * kp; bias = kp * (target - e.q) + damping * vt; }
+    if (inverse_dynamics) bias = 0.f;
+    else if (position_control) { damping = kd + t.cfg.dt * kp; bias = kp * (target - e.q) + damping * vt; }
     else if (velocity_control) { damping = kp; bias = damping * vt; }
     else if (mode == 5u && limit > 0.f && noload > 0.f) {
         const float speed_bias = limit * e.qd / noload;
@@ -210,8 +213,9 @@ NKB_DEV void stage_drives(Env& e) {
     if (!isfinite(bias) || !isfinite(damping) || damping < 0.f || !isfinite(limit) || !isfinite(ff) || !isfinite(e.qd) || !isfinite(e.q)) {
         e.status |= kStatusControlFailure; return;
     }
+    if (inverse_dynamics) { lower = limit > 0.f ? -limit : -FLT_MAX; upper = limit > 0.f ? limit : FLT_MAX; }
     e.drive_command = bias; e.drive_dissipation = damping; e.drive_lower = lower; e.drive_upper = upper;
-    e.tau = ff;
+    e.tau = inverse_dynamics ? 0.f : ff;
 }
 
 // Bias forces, mass matrix, factor and unconstrained acceleration; optionally the semi-implicit velocity
@@ -474,6 +478,144 @@ NKB_DEV void stage_dynamics(Env& e, bool integrate_velocity) {
         __syncwarp();
         if (base_coord) sm_vel(e, e.dof_link[0])[e.dof_comp[0]] = nv;
         __syncwarp();
+    }
+}
+
+// Computed-torque control (control mode 3), the quantities of the reference's ApplyDynamicsDriveKernel
+// (ops/articulation.cu:1315-1418).  Runs between a force-free dynamics pass (which leaves M's factor in shared memory and
+// the free accelerations in the lanes) and the step's dynamics pass.  With S the selector of the scalar joints,
+// H = (S M^-1 S^T)^-1 is the inertia the actuators see, a floating base's reaction included; the command is
+// H (a* + kp (q* - q) + kd (qd* - qd)) - H qdd_free - d qd (bias compensation without the passive joint damping).
+// Lane c owns column c of each small matrix and runs the reference's serial column loops (same operation order, double
+// accumulators where the reference has them); the matrices live in regions that are idle between the two dynamics passes:
+// the Newton matrix holds S M^-1 S^T and its factors, the head records' region holds H, the solver vectors the small
+// tables.
+// Out of line, with its inputs by value: the controller runs in one control mode only and must not weigh on the register
+// allocation of the step kernel's common path.
+struct TorqueIn {
+    float* sm; const SmemLayout* lay; const TemplateView* t; const StateView* s;
+    uint32_t env, lane, jtype, link_dof;
+    float q, qd, qdd, lower, upper;
+};
+struct TorqueOut { float tau, command; uint32_t status; uint32_t applied; };
+template <int NR>
+__device__ __noinline__ TorqueOut computed_torque(TorqueIn e) {
+    const TemplateView& t = *e.t;
+    TorqueOut out;
+    out.tau = 0.f; out.command = 0.f; out.status = 0u; out.applied = 0u;
+    const uint32_t l = e.lane, L = t.L, n = t.ndof, ld = e.lay->ld;
+    const bool scalar = l < L && joint_dofs(e.jtype) == 1u;
+    // a drive the affine stage rejected (bounds left at zero) switches the controller off for the env
+    if (__any_sync(NKB_FULL, scalar && e.lower == 0.f && e.upper == 0.f)) return out;
+    const uint32_t joints = __ballot_sync(NKB_FULL, scalar);
+    const uint32_t active = (uint32_t)__popc(joints);
+    if (active == 0u) return out;
+    const uint32_t rank = (uint32_t)__popc(joints & ((1u << l) - 1u));        // this lane's joint among the active ones
+    const size_t at = (size_t)e.env * L + l;
+    float* vecs = e.sm + e.lay->vecs;
+    constexpr uint32_t vs = 32u * NR;
+    float* diag = vecs + vs * kVecAcc;
+    float* free_acc = vecs + vs * kVecFree;
+    float* passive = vecs + vs * kVecU;
+    float* rhs = vecs + vs * kVecPseudo;
+    uint32_t* dofs = reinterpret_cast<uint32_t*>(vecs + vs * kVecTmp);
+    float* command = vecs + vs * kVecTmp2;
+    float* A = e.sm + e.lay->chol;                         // active x active, row stride `active`
+    float* H = e.sm + e.lay->heads;
+    const float* F = e.sm + e.lay->factor;
+    out.applied = 1u;
+    if (scalar) {
+        out.tau = e.s->feedforward[at];
+        dofs[rank] = e.link_dof;
+        free_acc[rank] = e.qdd;
+        passive[rank] = -__ldg(t.damping + l) * e.qd;
+        rhs[rank] = e.s->acc_target[at] + e.s->kp[at] * (e.s->drive_target[at] - e.q) + e.s->kd[at] * (e.s->vel_target[at] - e.qd);
+    }
+    __syncwarp();
+    const bool column = l < active;
+    float x[32 * NR];
+    // S M^-1 S^T, column by column: M x = e_dof(c) through the L D L^T factor (articulation_mass.cuh:357-411)
+    if (column) {
+        for (uint32_t i = 0u; i < n; ++i) x[i] = i == dofs[l] ? 1.0f : 0.0f;
+        for (uint32_t j = 0u; j < n; ++j)
+            for (uint32_t i = j + 1u; i < n; ++i) x[i] -= F[i * ld + j] * x[j];
+        for (uint32_t i = 0u; i < n; ++i) x[i] /= F[i * ld + i];
+        for (uint32_t end = n; end > 0u; --end) {
+            const uint32_t i = end - 1u;
+            float s = x[i];
+            for (uint32_t j = i + 1u; j < n; ++j) s -= F[j * ld + i] * x[j];
+            x[i] = s;
+        }
+        for (uint32_t r = 0u; r < active; ++r) A[r * active + l] = x[dofs[r]];
+    }
+    __syncwarp();
+    if (column)
+        for (uint32_t c = 0u; c < l; ++c) {
+            const float v = 0.5f * (A[l * active + c] + A[c * active + l]);
+            A[l * active + c] = v; A[c * active + l] = v;
+        }
+    __syncwarp();
+    // L D L^T of the actuated block (FactorControlMass): every lane follows the pivots, lane i owns row i
+    bool definite = true;
+    for (uint32_t j = 0u; j < active; ++j) {
+        double pivot = A[j * active + j];
+        for (uint32_t k = 0u; k < j; ++k) { const double v = A[j * active + k]; pivot -= v * v * diag[k]; }
+        if (!(pivot > 0.0) || !isfinite(pivot)) { definite = false; break; }
+        __syncwarp();
+        if (l == 0u) diag[j] = (float)pivot;
+        if (column && l > j) {
+            double v = A[l * active + j];
+            for (uint32_t k = 0u; k < j; ++k) v -= (double)A[l * active + k] * A[j * active + k] * diag[k];
+            A[l * active + j] = (float)(v / pivot);
+        }
+        __syncwarp();
+    }
+    if (!definite) { out.status = kStatusControlFailure; return out; }
+    // H = inverse, column by column (SolveControlMass on unit vectors)
+    if (column) {
+        for (uint32_t i = 0u; i < active; ++i) {
+            double v = i == l ? 1.0 : 0.0;
+            for (uint32_t j = 0u; j < i; ++j) v -= (double)A[i * active + j] * x[j];
+            x[i] = (float)v;
+        }
+        for (uint32_t i = 0u; i < active; ++i) x[i] /= diag[i];
+        for (uint32_t ii = active; ii > 0u; --ii) {
+            const uint32_t i = ii - 1u;
+            double v = x[i];
+            for (uint32_t j = i + 1u; j < active; ++j) v -= (double)A[j * active + i] * x[j];
+            x[i] = (float)v;
+        }
+        for (uint32_t r = 0u; r < active; ++r) H[r * active + l] = x[r];
+    }
+    __syncwarp();
+    // command = bias + H rhs, bias = -d qd - H qdd_free; lane r owns row r
+    float value = 0.f;
+    if (column) {
+        double b = passive[l];
+        for (uint32_t c = 0u; c < active; ++c) b -= (double)H[l * active + c] * free_acc[c];
+        double v = (double)(float)b;
+        for (uint32_t c = 0u; c < active; ++c) v += (double)H[l * active + c] * rhs[c];
+        value = (float)v;
+    }
+    const bool finite = __all_sync(NKB_FULL, !column || isfinite(value));
+    if (column) command[l] = finite ? value : 0.f;
+    __syncwarp();
+    if (scalar) out.command = command[rank];
+    if (!finite) out.status = kStatusControlFailure;
+    __syncwarp();
+    return out;
+}
+
+template <int NR>
+NKB_DEV void stage_computed_torque(Env& e) {
+    TorqueIn in;
+    in.sm = e.sm; in.lay = e.lay; in.t = e.t; in.s = e.s; in.env = e.env; in.lane = e.lane; in.jtype = e.jtype; in.link_dof = e.link_dof;
+    in.q = e.q; in.qd = e.qd; in.qdd = e.qdd; in.lower = e.drive_lower; in.upper = e.drive_upper;
+    const TorqueOut out = computed_torque<NR>(in);
+    e.status |= out.status;
+    if (out.applied != 0u && e.lane < e.t->L && joint_dofs(e.jtype) == 1u) {
+        e.tau = out.tau;
+        if (out.status == 0u) e.drive_command = out.command;
     }
 }
 

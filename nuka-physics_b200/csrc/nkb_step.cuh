@@ -177,7 +177,18 @@ NKB_DEV void advance_env(const StepParams& p, float* sm, uint32_t env, uint32_t 
             return;
         }
         tick(e, 0);
-        if (has_artic) { stage_fk(e); tick(e, 1); stage_drives(e); stage_dynamics<NR>(e, p.mode != kModeDynamicsOnly); tick(e, 2); }
+        if (has_artic) {
+            stage_fk(e); tick(e, 1); stage_drives(e);
+            // computed torque (pipeline.cpp:406-426) takes two passes: a force-free one on the current kinematics, the
+            // controller on its mass response and accelerations, then the step's own pass
+            const bool two_passes = t.cfg.control_mode == 3u && p.mode != kModeDynamicsOnly;
+#pragma unroll 1
+            for (int pass = two_passes ? 0 : 1; pass < 2; ++pass) {
+                stage_dynamics<NR>(e, pass == 1 && p.mode != kModeDynamicsOnly);
+                if (pass == 0) stage_computed_torque<NR>(e);
+            }
+            tick(e, 2);
+        }
         if (p.mode == kModeDynamicsOnly) {
             if (lane < t.L) p.s.qddot[(size_t)env * t.L + lane] = e.qdd;
             return;

@@ -96,7 +96,7 @@ struct StateView {
     float *base_pose;                                           // E x 7
     float *link_pose;                                           // E x L x 7
     float *link_vel;                                            // E x L x 6
-    float *drive_target, *vel_target, *kp, *kd, *force_limit, *feedforward, *noload_speed;   // E x L
+    float *drive_target, *vel_target, *kp, *kd, *force_limit, *feedforward, *noload_speed, *acc_target;   // E x L
     float *body_pose;                                           // E x B x 7
     float *body_linvel, *body_angvel;                           // E x B x 3
     float *carry_artic;                                         // E x ndof  (solved - free velocity of the last step)

@@ -432,7 +432,7 @@ World::World(int device, cudaStream_t stream, const HostTemplate& tpl, uint32_t 
         s.q = Alloc<float>(E * L); s.qdot = Alloc<float>(E * L); s.qddot = Alloc<float>(E * L); s.tau = Alloc<float>(E * L);
         s.actuator = Alloc<float>(E * L);
         s.base_pose = Alloc<float>(E * 7); s.link_pose = Alloc<float>(E * L * 7); s.link_vel = Alloc<float>(E * L * 6);
-        s.drive_target = Alloc<float>(E * L); s.vel_target = Alloc<float>(E * L); s.noload_speed = Alloc<float>(E * L); s.kp = Alloc<float>(E * L); s.kd = Alloc<float>(E * L);
+        s.drive_target = Alloc<float>(E * L); s.vel_target = Alloc<float>(E * L); s.noload_speed = Alloc<float>(E * L); s.acc_target = Alloc<float>(E * L); s.kp = Alloc<float>(E * L); s.kd = Alloc<float>(E * L);
         s.force_limit = Alloc<float>(E * L); s.feedforward = Alloc<float>(E * L);
         s.body_pose = Alloc<float>(E * B * 7); s.body_linvel = Alloc<float>(E * B * 3); s.body_angvel = Alloc<float>(E * B * 3);
         s.carry_artic = Alloc<float>(E * n); s.carry_rigid = Alloc<float>(E * B * 6);
@@ -490,6 +490,7 @@ void World::Seed() {
     auto add_seed = [&](void* dst, const void* src, uint32_t words) { if (words) { seed.fields[seed.field_count++] = {dst, src, words, 0u, 0u}; persistent_.push_back({dst, words}); } };
     add_seed(s.drive_target, q0, L); add_seed(s.kp, kp0, L); add_seed(s.kd, kd0, L); add_seed(s.force_limit, fl0, L);
     add_seed(s.vel_target, nullptr, L); add_seed(s.feedforward, nullptr, L); add_seed(s.noload_speed, nullptr, L);
+    add_seed(s.acc_target, nullptr, L);
     Check(launch_reset(seed, env_count_, stream_), "seed launch");
     ++launches_;
     Refresh();
@@ -705,6 +706,7 @@ bool World::Field(uint32_t id, FieldInfo* out) {
         case 13: return set(s.vel_target, L, 0, true);
         case 14: return set(s.noload_speed, L, 0, true);
         case 22: return set(s.feedforward, L, 0, true);
+        case 56: return set(s.acc_target, L, 0, true);
         case 25: return set(s.body_linvel, B * 3, 0, true);
         case 26: return set(s.body_angvel, B * 3, 0, true);
         case 29: return set(s.actuator, L, 0, false);

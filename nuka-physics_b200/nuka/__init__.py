@@ -42,6 +42,7 @@ class Field(enum.IntEnum):
     VELOCITY_TARGET = 13
     ACTUATOR_NOLOAD_SPEED = 14
     JOINT_FEEDFORWARD = 22
+    ACCELERATION_TARGET = 56
     BODY_LINEAR_VELOCITY = 25
     BODY_ANGULAR_VELOCITY = 26
     ACTUATOR_EFFORT = 29

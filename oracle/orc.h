@@ -126,7 +126,7 @@ typedef struct orc_env {
     float *link_vel;                         /* L*6 */
     float *link_acc, *link_vbias, *link_pbias, *link_S;  /* L*6 */
     float *link_xup, *link_ic;               /* L*36 */
-    float *drive_target, *vel_target, *kp, *kd, *force_limit, *feedforward, *noload_speed;
+    float *drive_target, *vel_target, *kp, *kd, *force_limit, *feedforward, *noload_speed, *acc_target;
     float *drive_command, *drive_dissipation, *drive_lower, *drive_upper;
     float *actuator_applied;                 /* L */
     float *M, *Mfactor, *bias;               /* ndof^2, ndof^2, ndof */
@@ -182,6 +182,9 @@ int orc_hw_threads(void);
 /* internal stages (per env) */
 void orc_fk(const orc_model *m, orc_env *e);
 void orc_apply_drives(const orc_model *m, orc_env *e);
+void orc_factor_mass(const float *M, float *F, uint32_t n);
+void orc_solve_mass(const float *F, float *x, uint32_t n);
+void orc_apply_dynamics_drives(const orc_model *m, orc_env *e);
 void orc_dynamics(const orc_model *m, orc_env *e, int integrate_velocity);
 void orc_body_integrate_velocity(const orc_model *m, orc_env *e);
 void orc_sync_bodies(const orc_model *m, orc_env *e);

@@ -55,11 +55,13 @@ void orc_apply_drives(const orc_model *m, orc_env *e) {
         e->tau[l] = 0.0f;
         if (joint_dofs(m->jtype[l]) != 1u) continue;
         const uint32_t mode = m->cfg.control_mode;
-        const int position_control = mode == 0u, velocity_control = mode == 2u;
+        const int inverse_dynamics = mode == 3u;
+        const int position_control = mode == 0u || inverse_dynamics, velocity_control = mode == 2u;
         if ((position_control && (!isfinite(e->drive_target[l]) || !isfinite(e->kp[l]) || e->kp[l] < 0.0f ||
                                   !isfinite(e->kd[l]) || e->kd[l] < 0.0f)) ||
             ((position_control || velocity_control) && !isfinite(e->vel_target[l])) ||
             (velocity_control && (!isfinite(e->kp[l]) || e->kp[l] < 0.0f)) ||
+            (inverse_dynamics && !isfinite(e->acc_target[l])) ||
             (mode == 5u && !isfinite(e->noload_speed[l]))) {
             e->status |= ORC_STATUS_CONTROL_FAILURE;
             continue;
@@ -69,7 +71,9 @@ void orc_apply_drives(const orc_model *m, orc_env *e) {
         float lower = limit > 0.0f ? -limit : -FLT_MAX;
         float upper = limit > 0.0f ? limit : FLT_MAX;
         float damping = 0.0f, bias = 0.0f;
-        if (position_control) {
+        if (inverse_dynamics) {
+            /* articulation.cu:899-901: no affine term here; the controller below writes the command */
+        } else if (position_control) {
             damping = e->kd[l] + dt * e->kp[l];
             bias = e->kp[l] * (e->drive_target[l] - e->q[l]) + damping * e->vel_target[l];
         } else if (velocity_control) {
@@ -99,12 +103,103 @@ void orc_apply_drives(const orc_model *m, orc_env *e) {
             e->status |= ORC_STATUS_CONTROL_FAILURE;
             continue;
         }
+        if (inverse_dynamics) {                    /* articulation.cu:932-939: the bounds are the plain force limit */
+            lower = limit > 0.0f ? -limit : -FLT_MAX;
+            upper = limit > 0.0f ? limit : FLT_MAX;
+        }
         e->drive_command[l] = bias;
         e->drive_dissipation[l] = damping;
         e->drive_lower[l] = lower;
         e->drive_upper[l] = upper;
-        e->tau[l] = ff;
+        e->tau[l] = inverse_dynamics ? 0.0f : ff;
     }
+}
+
+/* articulation.cu:1193-1230 FactorControlMass / SolveControlMass: L D L^T of the actuated block with double accumulators */
+static int factor_control_mass(float *a, uint32_t n, uint32_t stride, float *diagonal) {
+    for (uint32_t j = 0; j < n; ++j) {
+        double pivot = a[j * stride + j];
+        for (uint32_t k = 0; k < j; ++k) { const double v = a[j * stride + k]; pivot -= v * v * diagonal[k]; }
+        if (!(pivot > 0.0) || !isfinite(pivot)) return 0;
+        diagonal[j] = (float)pivot;
+        for (uint32_t i = j + 1u; i < n; ++i) {
+            double v = a[i * stride + j];
+            for (uint32_t k = 0; k < j; ++k) v -= (double)a[i * stride + k] * a[j * stride + k] * diagonal[k];
+            a[i * stride + j] = (float)(v / pivot);
+        }
+    }
+    return 1;
+}
+static void solve_control_mass(const float *f, const float *diagonal, uint32_t n, uint32_t stride, const float *rhs, float *x) {
+    for (uint32_t i = 0; i < n; ++i) {
+        double v = rhs[i];
+        for (uint32_t j = 0; j < i; ++j) v -= (double)f[i * stride + j] * x[j];
+        x[i] = (float)v;
+    }
+    for (uint32_t i = 0; i < n; ++i) x[i] /= diagonal[i];
+    for (uint32_t ii = n; ii > 0u; --ii) {
+        const uint32_t i = ii - 1u;
+        double v = x[i];
+        for (uint32_t j = i + 1u; j < n; ++j) v -= (double)f[j * stride + i] * x[j];
+        x[i] = (float)v;
+    }
+}
+
+/* Computed-torque control, articulation.cu:1315-1418 (ApplyDynamicsDriveKernel, ComputedTorque branch).  With S the
+ * selector of the scalar joints, H = (S M^-1 S^T)^-1 is the inertia the actuators see (a floating base's reaction
+ * included); the command is H (a* + kp (q* - q) + kd (qd* - qd)) plus the compensation of the force-free acceleration,
+ * passive joint damping left out of it. */
+void orc_apply_dynamics_drives(const orc_model *m, orc_env *e) {
+    const uint32_t L = m->L, n = m->ndof;
+    uint32_t links[ORC_MAX_DOF], dofs[ORC_MAX_DOF], active = 0u;
+    for (uint32_t l = 0; l < L; ++l)
+        if (joint_dofs(m->jtype[l]) == 1u && e->drive_lower[l] == 0.0f && e->drive_upper[l] == 0.0f) return;     /* a rejected drive */
+    for (uint32_t l = 0; l < L; ++l) {
+        if (joint_dofs(m->jtype[l]) != 1u) continue;
+        links[active] = l; dofs[active] = m->link_dof[l];
+        e->tau[l] = e->feedforward[l];
+        ++active;
+    }
+    if (active == 0u) return;
+    static _Thread_local float factor[ORC_MAX_DOF * ORC_MAX_DOF], mass[ORC_MAX_DOF * ORC_MAX_DOF];
+    float diagonal[ORC_MAX_DOF], rhs[ORC_MAX_DOF], solution[ORC_MAX_DOF], bias[ORC_MAX_DOF];
+    const uint32_t stride = n;
+    for (uint32_t c = 0; c < active; ++c) {
+        for (uint32_t d = 0; d < n; ++d) solution[d] = d == dofs[c] ? 1.0f : 0.0f;
+        orc_solve_mass(e->Mfactor, solution, n);
+        for (uint32_t r = 0; r < active; ++r) factor[r * stride + c] = solution[dofs[r]];
+    }
+    for (uint32_t r = 0; r < active; ++r)
+        for (uint32_t c = 0; c < r; ++c) {
+            const float v = 0.5f * (factor[r * stride + c] + factor[c * stride + r]);
+            factor[r * stride + c] = factor[c * stride + r] = v;
+        }
+    if (!factor_control_mass(factor, active, stride, diagonal)) { e->status |= ORC_STATUS_CONTROL_FAILURE; return; }
+    for (uint32_t c = 0; c < active; ++c) {
+        for (uint32_t r = 0; r < active; ++r) rhs[r] = r == c ? 1.0f : 0.0f;
+        solve_control_mass(factor, diagonal, active, stride, rhs, solution);
+        for (uint32_t r = 0; r < active; ++r) mass[r * stride + c] = solution[r];
+    }
+    for (uint32_t r = 0; r < active; ++r) {
+        double v = -m->damping[links[r]] * e->qdot[links[r]];
+        for (uint32_t c = 0; c < active; ++c) v -= (double)mass[r * stride + c] * e->qddot[links[c]];
+        bias[r] = (float)v;
+    }
+    for (uint32_t c = 0; c < active; ++c) {
+        const uint32_t l = links[c];
+        rhs[c] = e->acc_target[l] + e->kp[l] * (e->drive_target[l] - e->q[l]) + e->kd[l] * (e->vel_target[l] - e->qdot[l]);
+    }
+    for (uint32_t r = 0; r < active; ++r) {
+        double v = bias[r];
+        for (uint32_t c = 0; c < active; ++c) v += (double)mass[r * stride + c] * rhs[c];
+        e->drive_command[links[r]] = (float)v;
+    }
+    for (uint32_t a = 0; a < active; ++a)
+        if (!isfinite(e->drive_command[links[a]])) {
+            for (uint32_t c = 0; c < active; ++c) e->drive_command[links[c]] = 0.0f;
+            e->status |= ORC_STATUS_CONTROL_FAILURE;
+            return;
+        }
 }
 
 /* articulation.cu:259-277 JointTransform */

@@ -44,7 +44,7 @@ static void env_alloc(const orc_model *m, orc_env *e) {
     e->link_pose = falloc(7 * L); e->link_vel = falloc(6 * L); e->link_acc = falloc(6 * L);
     e->link_vbias = falloc(6 * L); e->link_pbias = falloc(6 * L); e->link_S = falloc(6 * L);
     e->link_xup = falloc(36 * L); e->link_ic = falloc(36 * L);
-    e->drive_target = falloc(L); e->vel_target = falloc(L); e->kp = falloc(L); e->kd = falloc(L); e->noload_speed = falloc(L);
+    e->drive_target = falloc(L); e->vel_target = falloc(L); e->kp = falloc(L); e->kd = falloc(L); e->noload_speed = falloc(L); e->acc_target = falloc(L);
     e->force_limit = falloc(L); e->feedforward = falloc(L);
     e->drive_command = falloc(L); e->drive_dissipation = falloc(L); e->drive_lower = falloc(L); e->drive_upper = falloc(L);
     e->actuator_applied = falloc(L);
@@ -64,7 +64,7 @@ static void env_alloc(const orc_model *m, orc_env *e) {
 }
 static void env_free(orc_env *e) {
     void *p[] = {e->q, e->qdot, e->qddot, e->tau, e->link_pose, e->link_vel, e->link_acc, e->link_vbias, e->link_pbias, e->link_S,
-                 e->link_xup, e->link_ic, e->drive_target, e->vel_target, e->kp, e->kd, e->force_limit, e->feedforward, e->noload_speed,
+                 e->link_xup, e->link_ic, e->drive_target, e->vel_target, e->kp, e->kd, e->force_limit, e->feedforward, e->noload_speed, e->acc_target,
                  e->drive_command, e->drive_dissipation, e->drive_lower, e->drive_upper, e->actuator_applied, e->M, e->Mfactor, e->bias,
                  e->body_pose, e->body_linvel, e->body_angvel, e->body_winv, e->aabb_lo, e->aabb_hi, e->pairs, e->ccount,
                  e->cpoint, e->cnormal, e->cdepth, e->cid_pair, e->cid_feature, e->rows, e->jac_pool, e->artic_vel, e->artic_free,
@@ -77,7 +77,7 @@ static void env_seed(const orc_model *m, orc_env *e) {
     const uint32_t L = m->L, B = m->B, n = m->ndof, S = m->cfg.max_contacts;
     for (uint32_t l = 0; l < L; ++l) {
         e->q[l] = m->q0[l]; e->qdot[l] = 0.0f; e->qddot[l] = 0.0f; e->tau[l] = 0.0f;
-        e->drive_target[l] = m->q0[l]; e->vel_target[l] = 0.0f; e->feedforward[l] = 0.0f;
+        e->drive_target[l] = m->q0[l]; e->vel_target[l] = 0.0f; e->feedforward[l] = 0.0f; e->acc_target[l] = 0.0f;
         e->kp[l] = m->kp0[l]; e->kd[l] = m->kd0[l]; e->force_limit[l] = m->force_limit0[l];
     }
     memset(e->link_vel, 0, sizeof(float) * 6 * L);
@@ -178,7 +178,7 @@ void orc_world_destroy(orc_world *w) {
 }
 
 /* control mode of every env: 0 PD position, 1 torque, 2 velocity; other values are ignored */
-void orc_world_set_control_mode(orc_world *w, uint32_t mode) { if (mode <= 2u || mode == 5u) w->m.cfg.control_mode = mode; }
+void orc_world_set_control_mode(orc_world *w, uint32_t mode) { if (mode <= 3u || mode == 5u) w->m.cfg.control_mode = mode; }
 
 void orc_world_set_broadphase(orc_world *w, uint32_t mode) { if (mode <= 2u) w->m.broadphase = mode; }
 
@@ -190,7 +190,16 @@ void orc_step_env(const orc_model *m, orc_env *e) {
     const int has_artic = m->L > 0u, has_bodies = m->B > 0u;
     const int has_contacts = e->row_cap > 0u;
     const int has_collidables = has_bodies && m->cfg.max_contacts > 0u;
-    if (has_artic) { orc_fk(m, e); orc_apply_drives(m, e); orc_dynamics(m, e, 1); }
+    if (has_artic) {
+        orc_fk(m, e); orc_apply_drives(m, e);
+        if (m->cfg.control_mode == 3u) {
+            /* pipeline.cpp:406-426: a force-free dynamics pass on the current kinematics, the inverse-dynamics controller on
+             * its mass response and acceleration, then the step's dynamics pass (the same mass matrix) */
+            orc_dynamics(m, e, 0);
+            orc_apply_dynamics_drives(m, e);
+        }
+        orc_dynamics(m, e, 1);
+    }
     orc_body_integrate_velocity(m, e);
     if (has_bodies) orc_sync_bodies(m, e);
     if (has_collidables) { orc_build_aabbs(m, e); orc_find_pairs(m, e); orc_narrowphase(m, e); }
@@ -244,7 +253,7 @@ static void *field_ptr(const orc_model *m, orc_env *e, const char *f, size_t *co
     R("q", e->q, L) R("qdot", e->qdot, L) R("qddot", e->qddot, L) R("tau", e->tau, L)
     R("base_pose", e->base_pose, 7) R("link_pose", e->link_pose, 7 * L) R("link_velocity", e->link_vel, 6 * L)
     R("link_acceleration", e->link_acc, 6 * L)
-    R("drive_target", e->drive_target, L) R("velocity_target", e->vel_target, L) R("noload_speed", e->noload_speed, L) R("drive_stiffness", e->kp, L)
+    R("drive_target", e->drive_target, L) R("velocity_target", e->vel_target, L) R("noload_speed", e->noload_speed, L) R("acceleration_target", e->acc_target, L) R("drive_stiffness", e->kp, L)
     R("drive_damping", e->kd, L) R("drive_force_limit", e->force_limit, L) R("joint_feedforward", e->feedforward, L)
     R("actuator_applied", e->actuator_applied, L)
     R("mass_matrix", e->M, (size_t)n * n) R("mass_factor", e->Mfactor, (size_t)n * n) R("bias", e->bias, n)

@@ -4,7 +4,7 @@
 // reference is copied into this repository.  The product never links or runs this program: tests compare against the
 // files it wrote (tests/golden/ref_*.nkt) and bench reports quote the timings it printed.
 //
-//   ref_driver --scene robot.nks --envs E --dt 0.005 --vel-iters 4 [--pos-iters k] [--no-contacts]
+//   ref_driver --scene robot.nks --envs E --dt 0.005 --vel-iters 4 [--pos-iters k] [--no-contacts] [--control-mode m]
 //              [--state state.nkt]            per-env q, qdot, base_pose, link_velocity, drive_target, kp, kd, force_limit (any subset)
 //              [--cook-only]                  stop after cooking (runs without a GPU) and dump the cooked model tables
 //              [--dump out.nkt]               model tables + single-op dynamics + trajectory samples
@@ -162,7 +162,7 @@ void DumpModel(const nk::Model& m, Container* c) {
 
 struct Args {
     std::string scene, state, dump;
-    uint32_t envs = 1, vel_iters = 0, pos_iters = 0xffffffffu, steps = 0, every = 1;
+    uint32_t envs = 1, vel_iters = 0, pos_iters = 0xffffffffu, steps = 0, every = 1, control_mode = 0;
     float dt = 1.0f / 200.0f;
     bool contacts = true, cook_only = false;
     int warm = 0, timed = 0, repeats = 1;
@@ -188,6 +188,7 @@ int main(int argc, char** argv) {
         else if (k == "--dt") a.dt = static_cast<float>(std::atof(next()));
         else if (k == "--vel-iters") a.vel_iters = static_cast<uint32_t>(std::atoi(next()));
         else if (k == "--pos-iters") a.pos_iters = static_cast<uint32_t>(std::atoi(next()));
+        else if (k == "--control-mode") a.control_mode = static_cast<uint32_t>(std::atoi(next()));
         else if (k == "--steps") a.steps = static_cast<uint32_t>(std::atoi(next()));
         else if (k == "--every") a.every = std::max(1, std::atoi(next()));
         else if (k == "--state") a.state = next();
@@ -205,6 +206,7 @@ int main(int argc, char** argv) {
         options.enable_contacts = a.contacts;
         auto cooked = nuka::scene::cook::CookToModel(scene, static_cast<int>(a.envs), options);
         Container out;
+        cooked.model.drive_mode = a.control_mode;          // as src/c_abi/world.cpp:160-166 routes the descriptor's control mode
         DumpModel(cooked.model, &out);
         if (a.cook_only) {
             if (!a.dump.empty() && !out.Write(a.dump)) { std::fprintf(stderr, "cannot write %s\n", a.dump.c_str()); return 1; }
@@ -230,7 +232,7 @@ int main(int argc, char** argv) {
             if (!Container::Read(a.state, &st)) { std::fprintf(stderr, "cannot read %s\n", a.state.c_str()); return 2; }
             const std::pair<const char*, nk::FieldId> fields[] = {
                 {"q", nk::FieldId::Q}, {"qdot", nk::FieldId::Qdot}, {"base_pose", nk::FieldId::BasePose}, {"link_velocity", nk::FieldId::LinkVelocity},
-                {"drive_target", nk::FieldId::DriveTarget},
+                {"drive_target", nk::FieldId::DriveTarget}, {"vel_target", nk::FieldId::VelocityTarget}, {"acc_target", nk::FieldId::AccelerationTarget},
                 {"kp", nk::FieldId::DriveStiffness}, {"kd", nk::FieldId::DriveDamping}, {"force_limit", nk::FieldId::DriveForceLimit},
                 {"body_pose", nk::FieldId::BodyPose}};
             for (const auto& f : fields) {

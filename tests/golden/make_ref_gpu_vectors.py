@@ -5,8 +5,8 @@ from the reference checkout).  Three phases, because the driver needs a GPU and 
                                                         per-env start states and run.sh into oracle/_ref/run/, and the
                                                         reference's cook of each scene (no GPU needed) into tests/golden/
   bash oracle/_ref/run/run.sh                           on a machine with a GPU: steps the scenes with the reference and
-                                                        writes OUT/ref_*.nkt and OUT/ref_timing.jsonl (OUT defaults to
-                                                        gpurun_out)
+                                                        writes OUT/ref_*.nkt and OUT/ref_timing.jsonl (OUT defaults to the
+                                                        repository's scratch output folder)
   python tests/golden/make_ref_gpu_vectors.py collect   copies the results into tests/golden/
 
 Both sides of the later comparison read the same .nks scene: the reference through its loader and cooker, this
@@ -41,8 +41,13 @@ CASES = {
     "quadbox": (lambda: T.quadruped(0, boxes=4), lambda E: T.quadruped_state(E, 0), 1.0 / 200.0, 4, 60, 20),
     # configs[2]'s env: the 35-coordinate humanoid with ground and limb self-contact
     "humanoid": (lambda: T.humanoid(0), lambda E: T.humanoid_state(E, 0), 1.0 / 200.0, 8, 40, 10),
+    # computed-torque control (control mode 3): the arm without contacts, the quadruped landing with saturating force limits
+    "arm7_ct": (lambda: T.arm7(0), lambda E: ref_cases.arm_computed_torque_state(E, 0), 1.0 / 500.0, 4, 100, 20),
+    "quadruped_ct": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_computed_torque_state(E, 0), 1.0 / 200.0, 4, 60, 20),
 }
-SCENE_OF = {"quadruped_moving": "quadruped"}
+SCENE_OF = {"quadruped_moving": "quadruped", "arm7_ct": "arm7", "quadruped_ct": "quadruped"}
+CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3}
+STATE_FIELDS = ("q", "qdot", "base_pose", "link_velocity", "body_pose", "drive_target", "vel_target", "acc_target", "kp", "kd", "force_limit")
 # throughput of the reference on the other configurations, on the protocol of bench.py --workload: the same seeded
 # per-env start states, the same untimed settle steps, then the timed steps
 # (scene case, envs, dt, iterations, settle steps, timed steps, start state)
@@ -61,12 +66,13 @@ def prepare():
             json.dump(nks.scene_from_builder(tb), f)
         scene = SCENE_OF.get(name, name)
         shutil.copy(os.path.join(RUN, f"{name}.nks"), os.path.join(HERE, f"scene_{scene}.nks"))
-        st = {k: np.ascontiguousarray(v, np.float32).reshape(ENVS, -1) for k, v in state(ENVS).items() if k in ("q", "qdot", "base_pose", "link_velocity", "body_pose")}
+        st = {k: np.ascontiguousarray(v, np.float32).reshape(ENVS, -1) for k, v in state(ENVS).items() if k in STATE_FIELDS}
         with open(os.path.join(RUN, f"{name}_state.nkt"), "wb") as f:
             f.write(nkt.pack(st))
         subprocess.run([DRIVER, "--scene", os.path.join(RUN, f"{name}.nks"), "--envs", "1", "--cook-only", "--dump",
                         os.path.join(HERE, f"ref_cook_{scene}.nkt")], check=True, stdout=subprocess.DEVNULL)
-        lines.append(f"../ref_driver --scene {name}.nks --envs {ENVS} --dt {dt!r} --vel-iters {iters} --state {name}_state.nkt "
+        mode = f" --control-mode {CONTROL_MODE[name]}" if name in CONTROL_MODE else ""
+        lines.append(f"../ref_driver --scene {name}.nks --envs {ENVS} --dt {dt!r} --vel-iters {iters}{mode} --state {name}_state.nkt "
                      f"--steps {steps} --every {every} --dump \"$OUT/ref_{name}.nkt\"")
     # the number to beat: the reference's own step on the bench workload, eager and graph mode, 100 warm-up + 1000 timed steps
     with open(os.path.join(RUN, "quadruped_state4096.nkt"), "wb") as f:
@@ -104,6 +110,8 @@ def collect(src):
     """Keeps what the tests compare (the root twist of the link velocities; body poses only where free bodies exist) as
     compressed .npz files."""
     for name in CASES:
+        if not os.path.exists(os.path.join(src, f"ref_{name}.nkt")):     # a partial run: keep the vectors already collected
+            continue
         with open(os.path.join(src, f"ref_{name}.nkt"), "rb") as f:
             arrays = nkt.unpack(f.read())
         E, L = int(arrays["run"][0]), int(arrays["run"][1])
@@ -114,6 +122,9 @@ def collect(src):
         if L:
             out["traj_root_twist"] = arrays["traj_link_velocity"].reshape(samples, E, L, 6)[:, :, 0].copy()
         np.savez_compressed(os.path.join(HERE, f"ref_gpu_{name}.npz"), **out)
+    if not os.path.exists(os.path.join(src, "ref_timing.jsonl")):
+        print("collected into", HERE, "(no timing file in", src + ")")
+        return
     with open(os.path.join(src, "ref_timing.jsonl")) as f:
         lines = [line for line in f if line.startswith("{")]
     with open(os.path.join(HERE, "ref_gpu_timing.jsonl"), "w") as f:

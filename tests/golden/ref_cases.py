@@ -148,3 +148,35 @@ def quadruped_moving_state(env_count, seed=0):
     twist = np.zeros((env_count, 13, 6), np.float32)
     twist[:, 0, :] = rng.normal(0, 0.3, size=(env_count, 6))
     return {"q": st["q"], "qdot": qdot, "base_pose": st["base_pose"], "link_velocity": twist.reshape(env_count, -1)}
+
+
+def arm_computed_torque_state(env_count, seed=0):
+    """Computed-torque case on the 7-link arm: seeded poses and joint rates, a position target near the pose, velocity and
+    acceleration targets, gains kp 25 / kd 3, no force limit."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "nuka-physics_b200"))
+    from nuka import templates as T
+    st = T.arm7_state(env_count, seed)
+    rng = np.random.Generator(np.random.PCG64(11 + seed))
+    L = 8
+    acc = np.zeros((env_count, L), np.float32); acc[:, 1:] = rng.normal(0, 2.0, size=(env_count, L - 1))
+    target = (st["q"] + rng.normal(0, 0.2, size=(env_count, L))).astype(np.float32)
+    vt = np.zeros((env_count, L), np.float32); vt[:, 1:] = rng.normal(0, 0.5, size=(env_count, L - 1))
+    return {"q": st["q"], "qdot": st["qdot"], "drive_target": target, "vel_target": vt, "acc_target": acc,
+            "kp": np.full((env_count, L), 25.0, np.float32), "kd": np.full((env_count, L), 3.0, np.float32)}
+
+
+def quadruped_computed_torque_state(env_count, seed=0):
+    """Computed-torque case on the quadruped: the seeded drop onto the feet, targets at the standing pose, gains
+    kp 400 / kd 40, 20 N m force limits (the landing saturates them)."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "nuka-physics_b200"))
+    from nuka import templates as T
+    st = T.quadruped_state(env_count, seed)
+    L = 13
+    target = np.tile(T.quadruped(0).arrays()["q0"].reshape(1, L), (env_count, 1)).astype(np.float32)
+    return {"q": st["q"], "base_pose": st["base_pose"], "drive_target": target,
+            "kp": np.full((env_count, L), 400.0, np.float32), "kd": np.full((env_count, L), 40.0, np.float32),
+            "force_limit": np.full((env_count, L), 20.0, np.float32)}

@@ -23,7 +23,15 @@ CASES = {
     "pile12": ("pile12", lambda E: {"body_pose": T.box_pile_state(E, 0, count=12)["body_pose"].reshape(E, -1)}),
     "quadbox": ("quadbox", lambda E: T.quadruped_state(E, 0)),
     "humanoid": ("humanoid", lambda E: T.humanoid_state(E, 0)),
+    # computed-torque control (control mode 3)
+    "arm7_ct": ("arm7", lambda E: ref_cases.arm_computed_torque_state(E, 0)),
+    "quadruped_ct": ("quadruped", lambda E: ref_cases.quadruped_computed_torque_state(E, 0)),
 }
+CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3}
+# drive inputs a case's start state may carry: state key -> (oracle field name, nuka.Field name)
+DRIVE_INPUTS = {"drive_target": ("drive_target", "DRIVE_TARGET"), "vel_target": ("velocity_target", "VELOCITY_TARGET"),
+                "acc_target": ("acceleration_target", "ACCELERATION_TARGET"), "kp": ("drive_stiffness", "DRIVE_STIFFNESS"),
+                "kd": ("drive_damping", "DRIVE_DAMPING"), "force_limit": ("drive_force_limit", "DRIVE_FORCE_LIMIT")}
 # contact points per env that get solver rows, where the procedural template sets its own capacity
 MAX_POINTS = {"pile12": 72, "quadbox": 40, "humanoid": 48}
 
@@ -101,7 +109,7 @@ def assert_velocity_parity(got, want, first, tag, case=None):
 
 def start_state(case, E):
     """The per-env start state of a case, keyed by the names both worlds use (q, qdot, base_pose, body_pose)."""
-    return {k: v for k, v in CASES[case][1](E).items() if k in ("q", "qdot", "base_pose", "body_pose", "link_velocity")}
+    return {k: v for k, v in CASES[case][1](E).items() if k in ("q", "qdot", "base_pose", "body_pose", "link_velocity") or k in DRIVE_INPUTS}
 
 
 def acceleration_errors(ref, mine, E, L, n):

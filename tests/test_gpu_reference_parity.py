@@ -24,11 +24,14 @@ def make_world(device, case):
     if ref is None:
         pytest.skip(f"no reference vectors for {case}")
     tb, E, L, n, S = RP.template(case, ref)
-    w = nuka.World.create_from_template(device, tb.blob(), E)
+    w = nuka.World.create_from_template(device, tb.blob(), E, control_mode=RP.CONTROL_MODE.get(case, 0))
     st = RP.start_state(case, E)
     for k in ("q", "qdot", "base_pose", "body_pose"):
         if k in st:
             w.upload(NAMES[k], st[k])
+    for k, (_, field) in RP.DRIVE_INPUTS.items():
+        if k in st:
+            w.upload(getattr(F, field), st[k])
     w.forward_kinematics()
     if "link_velocity" in st:
         w.upload(F.LINK_VELOCITY, st["link_velocity"])

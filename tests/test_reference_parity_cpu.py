@@ -27,6 +27,11 @@ def run_oracle(oracle, case):
     for k in ("q", "qdot", "base_pose", "body_pose"):
         if k in st:
             w.set(k, st[k])
+    for k, (name, _) in RP.DRIVE_INPUTS.items():
+        if k in st:
+            w.set(name, st[k])
+    if case in RP.CONTROL_MODE:
+        w.set_control_mode(RP.CONTROL_MODE[case])
     w.refresh()
     if "link_velocity" in st:
         w.set("link_velocity", st["link_velocity"])
