@@ -387,15 +387,17 @@ def main():
                 one(k)
             if exchange is not None:
                 exchange.drain(stream)
-            stream.synchronize()
-            if distributed:
-                dist.barrier()
-            torch.cuda.synchronize()
-            launches0 = w.launch_count()
+            # everything that takes host time happens before the ranks line up: events, the collector
             starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
             ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
             gc.collect()
             gc.disable()                                  # no collector pause between a start event and its step's launch
+            stream.synchronize()
+            torch.cuda.synchronize()
+            launches0 = w.launch_count()
+            if distributed:
+                dist.barrier()
+                torch.cuda.synchronize()
             for k in range(steps):
                 if flush is not None:
                     flush.add_(1.0)                       # evicts the 126 MB L2 (outside the timed spans)
@@ -503,7 +505,7 @@ def main():
     hold_total, active_total, e2e_total = max_over_ranks([sum(hold_ms), sum(active_ms), e2e_s * 1e3])
     per_rank = None
     if distributed:
-        mine = torch.tensor([min(hold_ms), statistics.median(hold_ms), max(hold_ms)], dtype=torch.float64, device=cuda)
+        mine = torch.tensor([min(hold_ms), statistics.median(hold_ms), max(hold_ms), float(hold_ms.index(max(hold_ms)))], dtype=torch.float64, device=cuda)
         every = [torch.zeros_like(mine) for _ in range(world_size)]
         dist.all_gather(every, mine)
         per_rank = [[round(float(v), 4) for v in t] for t in every]
@@ -582,7 +584,7 @@ def main():
             "clocks": clocks,
         }
         if per_rank is not None:
-            line["per_rank_step_ms_min_median_max"] = per_rank
+            line["per_rank_step_ms_min_median_max_slowest_step"] = per_rank
         if extra is not None:
             line["extra"] = extra
         if prepared is not None:

@@ -1011,9 +1011,12 @@ NKB_DEV void team_fork(Env& e, uint32_t op, uint32_t count, Work&& work) {
     if (team_collect(e.sm, *e.lay, e.lane, seq)) {
         for (uint32_t m = 1u; m < team; ++m) e.status |= reinterpret_cast<const uint32_t*>(team_result(e.sm, *e.lay, m))[2];
     } else {
+        // a helper did not answer: flag the env, stop using the team, and do the whole range here (the stages dealt out
+        // this way write each item from its inputs alone, so items done twice come out the same)
         e.status |= kStatusTeamTimeout;
         if (e.lane == 0u) team_command(e.sm, *e.lay)->dead = 1u;
         __syncwarp();
+        work(0u, 1u);
     }
 }
 
@@ -1039,37 +1042,44 @@ NKB_DEV void descend_blocks(Env& e, Tile& tile, bool position) {
             const uint32_t colour = blk_color(e, nb, b);
             uint32_t k_end = k + 1u;
             while (k_end < count && order[k_end] != e.t->B && blk_color(e, nb, order[k_end]) == colour) ++k_end;
-            RigidResult mine;
             // colour 31 is the overflow colour (index_blocks hands it to every block past the 31st colour): not a set of
             // independent blocks, so it stays with the lead
-            if (team > 1u && k_end - k > 1u && colour < 31u && team_command(e.sm, *e.lay)->dead == 0u) {
-                const uint32_t seq = team_post(e.sm, *e.lay, e.lane, kTeamDescend, k, k_end, position, tile);
+            const bool shared_out = team > 1u && k_end - k > 1u && colour < 31u && team_command(e.sm, *e.lay)->dead == 0u;
+            const uint32_t stride = shared_out ? team : 1u;
+            uint32_t seq = 0u;
+            if (shared_out) {
+                seq = team_post(e.sm, *e.lay, e.lane, kTeamDescend, k, k_end, position, tile);
 #ifdef NKB_STAGE_TAPS
-                const long long tap0 = clock64();
+                if (e.cyc != nullptr && e.lane == 0u) e.cyc[31] += 1u;
 #endif
-                mine = descend_rigid_run<kRigid>(run, k, k_end, 0u, team, position);
-#ifdef NKB_STAGE_TAPS
-                const long long tap1 = clock64();
-#endif
-                const bool collected = team_collect(e.sm, *e.lay, e.lane, seq);
-#ifdef NKB_STAGE_TAPS
-                if (e.cyc != nullptr && e.lane == 0u) { e.cyc[28] += (uint32_t)(tap1 - tap0); e.cyc[29] += (uint32_t)(clock64() - tap1); e.cyc[23] += 0u; }
-#endif
-                if (collected) {
-                    for (uint32_t m = 1u; m < team; ++m) {
-                        const float* r = team_result(e.sm, *e.lay, m);
-                        mine.momentum = fmaxf(mine.momentum, r[0]); mine.residual = fmaxf(mine.residual, r[1]);
-                        mine.status |= reinterpret_cast<const uint32_t*>(r)[2];
-                    }
-                } else {
-                    // a helper did not answer: the env's result is void (flagged); work alone from here on
-                    mine.status |= kStatusTeamTimeout;
-                    if (e.lane == 0u) team_command(e.sm, *e.lay)->dead = 1u;
-                    __syncwarp();
-                }
-            } else {
-                mine = descend_rigid_run<kRigid>(run, k, k_end, 0u, 1u, position);
             }
+            RigidResult mine = {0.f, 0.f, 0u};
+            bool collected = true;
+            uint32_t share = 0u;
+            // one pass takes the lead's share (all of the run when it is not shared out); further passes only run after a
+            // helper failed to answer, and take the helpers' shares
+#pragma unroll 1
+            do {
+                const RigidResult part = descend_rigid_run<kRigid>(run, k, k_end, share, stride, position);
+                mine.momentum = fmaxf(mine.momentum, part.momentum); mine.residual = fmaxf(mine.residual, part.residual);
+                mine.status |= part.status;
+                if (shared_out && share == 0u) {
+                    collected = team_collect(e.sm, *e.lay, e.lane, seq);
+                    if (collected) {
+                        for (uint32_t m = 1u; m < team; ++m) {
+                            const float* r = team_result(e.sm, *e.lay, m);
+                            mine.momentum = fmaxf(mine.momentum, r[0]); mine.residual = fmaxf(mine.residual, r[1]);
+                            mine.status |= reinterpret_cast<const uint32_t*>(r)[2];
+                        }
+                    } else {
+                        // a helper did not answer: flag the env, stop using the team, descend the helpers' shares here
+                        mine.status |= kStatusTeamTimeout;
+                        if (e.lane == 0u) team_command(e.sm, *e.lay)->dead = 1u;
+                        __syncwarp();
+                    }
+                }
+                ++share;
+            } while (shared_out && !collected && share < team);
             tile.momentum = fmaxf(tile.momentum, mine.momentum);
             tile.residual = fmaxf(tile.residual, mine.residual);
             e.status |= mine.status;

@@ -295,6 +295,7 @@ NKB_DEV void team_helper(float* sm, const SmemLayout& shared_layout, const Templ
         last = seq;
         const uint32_t op = team_peek(&cmd->op);
         if (op == kTeamExit) return;
+        if ((shared_layout.team_drill & 2u) != 0u) continue;          // drill: a helper that never answers
         RigidResult r = {0.f, 0.f, 0u};
         const uint32_t k_begin = cmd->k_begin, k_end = cmd->k_end, nblocks = cmd->nblocks;
         if (op == kTeamDescend && k_begin < k_end && k_end <= nblocks && nblocks <= t.B + 1u) {
@@ -356,7 +357,7 @@ __global__ void __maxnreg__(kRigid ? NKB_MAXNREG_RIGID : (kSlim ? NKB_MAXNREG_SL
         if (member != 0u) { team_helper<kRigid>(sm, p.sm, p.t, p.s, env, member, lane, 32u * NR); return; }
     }
     advance_env<NR, kRigid>(p, sm, env, lane);
-    if constexpr (kRigid) team_dismiss(sm, p.sm, lane);
+    if constexpr (kRigid) { if ((p.sm.team_drill & 1u) == 0u) team_dismiss(sm, p.sm, lane); }
 }
 
 // Raises the kernel's dynamic shared-memory limit to `bytes` if it is not there yet.  The limit is per function and

@@ -129,6 +129,9 @@ struct SmemLayout {
     // Team mode: `team` warps advance one env; warp 0 leads, the others wait for work (rigid blocks of one colour).
     // team_area: 12 command words, 4 result words per member, then helper_words of private Newton scratch per helper.
     uint32_t team, team_area, helper_words;
+    // Fault drills for the team's bounded waits (tests only): bit 0 = the lead leaves without dismissing its helpers,
+    // bit 1 = helpers never answer a command.  Either way every wait runs out, a status bit is set and the kernel ends.
+    uint32_t team_drill;
     uint32_t words;                                             // total per env
     uint32_t ld;                                                // leading dimension of mass/factor (ndof | 1)
 };

@@ -340,7 +340,8 @@ void World::BuildLayout() {
     // leave the SM with one or two resident warps; instead several warps share the env and descend the rigid blocks
     // of one colour side by side (blocks of a colour share no constraint row).  Registers allow about 11 resident
     // warps per SM, so teams only pay where shared memory already holds residency below that.
-    s.team = 1u; s.team_area = at; s.helper_words = 0u;
+    s.team = 1u; s.team_area = at; s.helper_words = 0u; s.team_drill = 0u;
+    if (const char* drill = std::getenv("NUKA_B200_TEAM_DRILL")) s.team_drill = static_cast<uint32_t>(std::atoi(drill)) & 3u;
     {
         const uint32_t helper = (s.rjac + 24u * s.rjac_heads - s.chol) + 6u * s.vstride;     // Newton matrix, block mass, staged rows as the env lays them out; vectors
         uint32_t team = 1u;

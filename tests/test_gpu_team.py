@@ -73,3 +73,30 @@ def test_articulation_with_boxes_in_a_team(device):
     assert not a["status"].any()
     for k in a:
         assert np.array_equal(a[k], b[k]), k
+
+
+@pytest.mark.parametrize("drill", [1, 2])
+def test_a_wait_that_runs_out_sets_the_status_bit_and_the_world_lives_on(device, drill):
+    """The team's warps wait for one another with a cycle budget, never without bound.  Drill 1: the lead leaves without
+    dismissing its helpers, which give up after their budget.  Drill 2: helpers never answer, the lead gives up on its
+    first command and finishes the env alone.  Either way the launch ends, the env carries the team-timeout bit
+    (1 << 21), and the device keeps working."""
+    E = 2
+    tb = T.box_pile(0, count=48)
+    st = T.box_pile_state(E, 0, count=48)
+    os.environ["NUKA_B200_TEAM_DRILL"] = str(drill)          # read when the world lays out its shared memory
+    try:
+        w = nuka.World.create_from_template(device, tb.blob(), E)
+    finally:
+        del os.environ["NUKA_B200_TEAM_DRILL"]
+    w.upload(F.RIGID_BODY_TRANSFORM, st["body_pose"])
+    w.forward_kinematics()
+    w.step_n(2)
+    status = w.download(F.ENV_STATUS)[:, 0]
+    assert ((status & (1 << 21)) != 0).all()
+    if drill == 2:                                            # the lead did all the work itself: the state is the one-warp state
+        want = run(device, tb, st, E, 2, 1)
+        assert np.array_equal(w.download(F.RIGID_BODY_TRANSFORM), want["pose"])
+    w.destroy()
+    healthy = run(device, tb, st, E, 3, 8)                   # the context is intact
+    assert not healthy["status"].any()
