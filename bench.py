@@ -5,10 +5,10 @@
     python bench.py --impl reference ...                   (the CPU arm: the oracle port on all host cores)
 
 A "step" is one physics step of every env of the workload: 4096 quadrupeds per GPU (BASELINE.json configs[1]).
-N > 1 gives every rank its own 4096-env shard (weak scaling, no collective in the step); after every step each rank
-packs observation + reward records straight into its slice of one of two gather buffers, and the in-place all-gather of
-that buffer runs on a side stream under the next step (configs[4]'s exchange, double-buffered; the last gather of a
-timed run is added as a tail).
+N > 1 gives every rank its own 4096-env shard (weak scaling, no collective in the step); every `--exchange-every` steps (4,
+the decimation at which the reference's gym env composes observations) each rank packs observation + reward records
+straight into its slice of one of two gather buffers, and the in-place all-gather of that buffer runs on a side stream
+under the next step (configs[4]'s exchange, double-buffered; the last gather of a timed run is added as a tail).
 
 State preparation.  The cost of a step depends on what the robots are doing: while they drop onto their feet the solver
 runs all its sweeps, once they stand it stops early.  So both arms first run `config.settle_steps` untimed steps from
@@ -295,7 +295,10 @@ def main():
     ap.add_argument("--envs", type=int, default=ENVS_PER_GPU)
     ap.add_argument("--settle", type=int, default=SETTLE_STEPS, help="untimed steps from the seeded start that prepare the measured state")
     ap.add_argument("--no-flush", action="store_true", help="skip the L2 flush between timed steps")
-    ap.add_argument("--no-gather", action="store_true", help="N > 1: skip the per-step observation all-gather")
+    ap.add_argument("--no-gather", action="store_true", help="N > 1: skip the observation all-gather")
+    ap.add_argument("--exchange-every", type=int, default=4,
+                    help="N > 1: physics steps per observation exchange; 4 is the decimation of the reference's gym env, which composes "
+                         "observations once per step_n(decimation) (python/nuka/gym/env.py:98, 255-256)")
     ap.add_argument("--no-extra", action="store_true", help="skip the configs[4] figure (65536 quadruped + 4-box envs split over the ranks)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--workload", default="c2", choices=["c2"] + sorted(OTHER_WORKLOADS),
@@ -377,17 +380,21 @@ def main():
                 before_step(k)
             w.step()
             if exchange is not None:
-                # the previous step's gather runs under this step: enqueued after the step's launch, so that the host's
-                # time in the NCCL call passes while the step kernel runs, and held back on the device until the step's
-                # start event
+                # a packed buffer's gather runs under the step after its pack: enqueued after that step's launch, so that
+                # the host's time in the NCCL call passes while the step kernel runs, and held back on the device until
+                # the step's start event (nothing happens here when no buffer is pending)
                 exchange.release(after=start)
-                exchange.pack(stream)
+                if (k + 1) % args.exchange_every == 0:
+                    exchange.pack(stream)
         with torch.cuda.stream(stream):
             for k in range(warmup):
                 one(k)
             if exchange is not None:
                 exchange.drain(stream)
-            # everything that takes host time happens before the ranks line up: events, the collector
+            # everything that takes host time happens before the ranks line up: events, the collector, the first use of
+            # the flush kernel (its module load would otherwise delay a rank's first timed launch)
+            if flush is not None:
+                flush.add_(1.0)
             starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
             ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
             gc.collect()
@@ -461,13 +468,17 @@ def main():
     out_q = torch.empty((E, NL), dtype=torch.float32).pin_memory()
     out_b = torch.empty((E, 7), dtype=torch.float32).pin_memory()
 
+    e2e_count = [0]
+
     def e2e_step():
         nuka._check(lib.nuka_world_upload_field(w._h, int(F.DRIVE_TARGET), targets.data_ptr(), targets.numel() * 4, 0))
         w.step()
         if exchange is not None:
-            exchange.release()                   # the previous step's gather runs under this step
-            with torch.cuda.stream(stream):
-                exchange.pack(stream)
+            exchange.release()                   # a packed buffer's gather runs under the step after its pack
+            e2e_count[0] += 1
+            if e2e_count[0] % args.exchange_every == 0:
+                with torch.cuda.stream(stream):
+                    exchange.pack(stream)
         nuka._check(lib.nuka_world_download_field(w._h, int(F.JOINT_POSITION), out_q.data_ptr(), out_q.numel() * 4, 0))
         nuka._check(lib.nuka_world_download_field(w._h, int(F.BASE_POSE), out_b.data_ptr(), out_b.numel() * 4, 0))
 
@@ -537,7 +548,7 @@ def main():
         (x_total,) = max_over_ranks([sum(x_ms)])
         torch.cuda.synchronize()
         wx.destroy()
-        extra = {"workload": "configs[4]: 65536 envs of quadruped + 4 free 0.1 m boxes split evenly over the ranks, observation all-gather every step (double-buffered, under the next step)",
+        extra = {"workload": "configs[4]: 65536 envs of quadruped + 4 free 0.1 m boxes split evenly over the ranks, observation all-gather as in the headline run (double-buffered, under the next step)",
                  "scaling": "strong", "total_envs": total, "envs_per_gpu": Ex, "steps": x_steps, "settle_steps": 200,
                  "ms_per_step": x_total / x_steps, "value": total * x_steps / (x_total * 1e-3), "unit": "env-steps/s"}
 
@@ -571,7 +582,7 @@ def main():
             "config": {"workload": WORKLOAD if not args.boxes else WORKLOAD.replace("configs[1]", f"configs[4]'s env: + {args.boxes} free 0.1 m boxes"),
                        "envs_per_gpu": E, "dt": 1.0 / 200.0, "velocity_iterations": 4, "settle_steps": args.settle,
                        "drives": "hold the standing pose", "l2_flush_between_steps": flush is not None,
-                       "obs_allgather": "double-buffered; issued on a side stream when the next step starts" if gather else False, "mean_contact_slots": slots, "mean_contact_points": points, "mean_solver_sweeps": sweeps},
+                       "obs_allgather": f"every {args.exchange_every} steps (the gym env's decimation), double-buffered; issued on a side stream when the next step starts" if gather else False, "mean_contact_slots": slots, "mean_contact_points": points, "mean_solver_sweeps": sweeps},
             "active": {"value": active_value, "unit": "env-steps/s", "ms_per_step": active_total / active_steps, "steps": active_steps,
                        "drives": f"targets redrawn every step: standing pose + N(0, {ACTIVE_NOISE}) rad"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
