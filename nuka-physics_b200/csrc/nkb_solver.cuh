@@ -491,6 +491,9 @@ NKB_DEV void descend_block(Env& e, Tile& tile, uint32_t b, bool position) {
     constexpr bool artic = kDim == 0;
     const uint32_t* inc = blk_inc(e, nb);
     const uint32_t ib = blk_inc_begin(e, nb, b), ie = blk_inc_begin(e, nb, b + 1u);
+    // A block without a push-out row keeps its zero position correction: its descent would minimise u^T M u from u = 0.
+    // (In the velocity phase an unconstrained block still has to reach its free velocity.)
+    if (position && ib == ie) return;
     const uint32_t chunks = (dim + 3u) >> 2, ldh = pad_ld(dim);
     float* velocity = block_vel(e, b, position);
     float* dvec = sm_vec(e, kVecD);
