@@ -154,10 +154,15 @@ typedef enum nuka_state_field_t {
     NUKA_FIELD_ACCELERATION_TARGET = 56,      /* E x L f32, writable; computed-torque control's feed-forward acceleration */
     NUKA_FIELD_BODY_LINEAR_VELOCITY = 25,     /* E x B x 3 f32 */
     NUKA_FIELD_BODY_ANGULAR_VELOCITY = 26,    /* E x B x 3 f32 */
+    NUKA_FIELD_JOINT_LIMIT_IMPULSE = 27,      /* E x L x 2 f32, read-only: the multipliers (lower, upper) the latest velocity solve left on
+                                                 each link's authored limit rows; the next step's limit rows start from them, as in the
+                                                 reference, whose assembly clears only the slots of links without that limit
+                                                 (src/phi/backend_cuda/ops/assemble_rows.cu:826-879); zeroed by a reset */
     NUKA_FIELD_ACTUATOR_EFFORT = 29,          /* E x L f32 */
     NUKA_FIELD_ENV_STATUS = 39,               /* E u32: sticky bits, the reference's (src/phi/op_schema.hpp:36-50): 1<<0 candidate
-                                                 pairs dropped, 1<<2 coordinate overflow, 1<<5 free-rotation solve not converged,
-                                                 1<<10 control input rejected, 1<<13 solver failure; this library's own: 1<<20 contact
+                                                 pairs dropped, 1<<2 coordinate overflow, 1<<5 free-rotation solve not converged
+                                                 (of the latest step only: cleared before every body integration, as in the
+                                                 reference), 1<<10 control input rejected, 1<<13 solver failure; this library's own: 1<<20 contact
                                                  points beyond the solver-row capacity dropped, 1<<21 a warp of an env's team gave
                                                  up waiting for another (the env's state is void) */
     NUKA_FIELD_SOLVER_RESIDUAL = 109,         /* E x 4 f32: normal, tangent, joint, momentum */

@@ -14,7 +14,7 @@ struct ResetField {
     uint32_t per_env_src; // 1: src is E x words
     uint32_t fill;
 };
-constexpr uint32_t kMaxResetFields = 24u;
+constexpr uint32_t kMaxResetFields = 28u;
 struct ResetParams {
     uint32_t env_count;
     const uint32_t* env_ids;   // device list of envs to reset, or null for all

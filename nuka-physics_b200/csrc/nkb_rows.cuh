@@ -222,7 +222,12 @@ NKB_DEV uint32_t stage_rows(Env& e, uint32_t pair_count) {
                 hf(e, HF_LOWER, h) = 0.f; hf(e, HF_UPPER, h) = FLT_MAX; hf(e, HF_MU, h) = 0.f;
                 hf(e, HF_PEN, h) = fmaxf(-dist, 0.0f);
                 hf(e, HF_RHS, h) = fminf(target, t.cfg.baumgarte_max_velocity) / dt;
-                hst3(e, HF_DUAL, h, mk3(0.f, 0.f, 0.f));
+                // an authored limit row starts from the multiplier the last step's solve left in its slot: the reference
+                // clears lambda only for links without that limit (ops/assemble_rows.cu:826-879; the per-step clear
+                // :366-383 covers the contact rows alone)
+                const float carried = e.s->limit_lambda[((size_t)e.env * L + lane) * 2u + side];
+                hst3(e, HF_DUAL, h, mk3(carried, 0.f, 0.f));
+                hst3(e, HF_LAM, h, mk3(carried, 0.f, 0.f));
             }
             nheads = min(nheads + total, t.head_cap);
             ++kind;       // kind 1 handled here

@@ -405,7 +405,7 @@ class Cooker {
                     else free_bodies.push_back(&n);
                 }
         if (roots.size() > 1) throw Error(kNotSupported, "at most one articulated tree is supported");
-        if (!roots.empty()) AddBody(*roots[0], kNoLink);
+        if (!roots.empty()) { AddBody(*roots[0], kNoLink); ExcludeWelded(); }
         for (const Json* node : free_bodies) AddFree(*node);      // in document order, after the articulation's rows
         for (const Json* g : grounds) {
             const Json* plane = nullptr;
@@ -449,7 +449,14 @@ class Cooker {
             l.offset = pf.pos;
             if (const Json* axis = joint->Find("axis")) {
                 if (axis->kind != Json::kArray || axis->items.size() != 3) throw Error(kParseError, "joint axis needs three numbers");
-                l.axis = {axis->items[0].number, axis->items[1].number, axis->items[2].number};
+                // as the reference cooks it (src/scene/cooker.cpp:680, math::Vec3::Normalized): float components over the
+                // float length, zero when shorter than 1e-12
+                const float x = (float)axis->items[0].number, y = (float)axis->items[1].number, z = (float)axis->items[2].number;
+                const volatile float xx = x * x, yy = y * y, zz = z * z;      // each product rounded on its own, no contraction
+                const volatile float sum = xx + yy;
+                const float length = std::sqrt((float)(sum + zz));
+                if (length < 1e-12f) l.axis = {0.0, 0.0, 0.0};
+                else l.axis = {(double)(x / length), (double)(y / length), (double)(z / length)};
             }
         }
         const Frame inertial = FrameOf(rb, "inertial");
@@ -467,7 +474,8 @@ class Cooker {
                 for (int k = 0; k < 3; ++k) sum += (R.m[i][k] * diag[k]) * R.m[j][k];
                 about_com.m[i][j] = sum;
             }
-        l.mass = rb.Number("mass", 0.0);
+        const bool static_root = parent_link == kNoLink && l.jtype == kFixed;     // a static body carries no inertia
+        l.mass = static_root ? 0.0 : rb.Number("mass", 0.0);
         l.com = inertial.pos;
         SpatialInertia(l.mass, about_com, l.com, l.inertia);
         const std::vector<const Json*> shapes = ShapesOf(node);
@@ -514,6 +522,34 @@ class Cooker {
             if (children->kind == Json::kArray)
                 for (const Json& c : children->items)
                     if (c.Has("rigid_body")) AddBody(c, link);
+    }
+
+    // The reference's weld rule (src/scene/cooker.cpp:505-536, MuJoCo's weldbody and filterparent): links joined by fixed
+    // joints form a cluster; no pair inside a cluster, and none between a cluster and the cluster of its parent link.
+    // Without fixed joints this is the parent-child exclusion AddLink already applies.
+    void ExcludeWelded() {
+        const uint32_t L = static_cast<uint32_t>(tb_.links.size());
+        auto weld = [&](uint32_t l) {
+            while (tb_.links[l].parent != kNoLink && tb_.links[l].jtype == kFixed) l = tb_.links[l].parent;
+            return l;
+        };
+        std::vector<std::vector<uint32_t>> clusters(L), rows(L);
+        for (uint32_t l = 0; l < L; ++l) clusters[weld(l)].push_back(l);
+        for (uint32_t row = 0; row < tb_.bodies.size(); ++row)
+            if (tb_.bodies[row].link != kNoLink) rows[tb_.bodies[row].link].push_back(row);
+        auto exclude = [&](uint32_t a, uint32_t b) {
+            if (a == b) return;
+            for (uint64_t ra : rows[a])
+                for (uint64_t rb : rows[b]) tb_.excluded.insert((std::min(ra, rb) << 32) | std::max(ra, rb));
+        };
+        for (uint32_t root = 0; root < L; ++root) {
+            const std::vector<uint32_t>& members = clusters[root];
+            for (size_t i = 0; i < members.size(); ++i)
+                for (size_t k = i + 1; k < members.size(); ++k) exclude(members[i], members[k]);
+            if (members.empty() || tb_.links[root].parent == kNoLink) continue;
+            for (uint32_t other : clusters[weld(tb_.links[root].parent)])
+                for (uint32_t member : members) exclude(member, other);
+        }
     }
 
     void AddFree(const Json& node) {

@@ -117,8 +117,12 @@ NKB_DEV void stage_readout_drives(Env& e, uint32_t nheads) {
     uint32_t* has = reinterpret_cast<uint32_t*>(sm_vec(e, kVecTmp2));
     has[e.lane] = 0u;
     __syncwarp();
-    for (uint32_t h = e.lane; h < nheads; h += 32u)
-        if (hu(e, HF_FLAGS, h) & kHeadDrive) { const uint32_t link = hu(e, HF_REF, h); tmp[link] = hf(e, HF_LAM, h); has[link] = 1u; }
+    for (uint32_t h = e.lane; h < nheads; h += 32u) {
+        const uint32_t fl = hu(e, HF_FLAGS, h);
+        if (fl & kHeadDrive) { const uint32_t link = hu(e, HF_REF, h); tmp[link] = hf(e, HF_LAM, h); has[link] = 1u; }
+        // a limit row's slot keeps the multiplier of the velocity solve for the next step (block_descent_tile.cuh:2556)
+        if (fl & kHeadLimit) e.s->limit_lambda[((size_t)e.env * t.L + hu(e, HF_REF, h)) * 2u + (hf(e, HF_UNITV, h) < 0.f ? 1u : 0u)] = hf(e, HF_LAM, h);
+    }
     __syncwarp();
     float applied = 0.f;
     if (e.lane < t.L && has[e.lane]) { applied = tmp[e.lane] / t.cfg.dt - e.drive_dissipation * e.qd; e.tau += applied; }
@@ -255,7 +259,13 @@ NKB_DEV void advance_env(const StepParams& p, float* sm, uint32_t env, uint32_t 
         uint32_t st = e.status;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) st |= __shfl_xor_sync(NKB_FULL, st, o);
-        if (lane == 0u && st != 0u) p.s.status[env] |= st;
+        // The gyro bit describes the latest step only (the reference clears it before every body integration,
+        // ops/articulation.cu:1053-1056, 1810-1812); every other bit stays until the env is reset.
+        if (lane == 0u && (st != 0u || has_bodies)) {
+            const uint32_t before = p.s.status[env];
+            const uint32_t after = (has_bodies ? before & ~kStatusGyroFailure : before) | st;
+            if (after != before) p.s.status[env] = after;
+        }
         __syncwarp();
         tick(e, 13);
     }

@@ -101,6 +101,7 @@ struct StateView {
     float *body_linvel, *body_angvel;                           // E x B x 3
     float *carry_artic;                                         // E x ndof  (solved - free velocity of the last step)
     float *carry_rigid;                                         // E x B x 6
+    float *limit_lambda;                                        // E x L x 2  (joint-limit multipliers of the last velocity solve: lower, upper)
     CacheEntry *cache;                                          // E x S x 4
     uint32_t *status;                                           // E
     float *solver_residual;                                     // E x 4

@@ -436,7 +436,7 @@ World::World(int device, cudaStream_t stream, const HostTemplate& tpl, uint32_t 
         s.drive_target = Alloc<float>(E * L); s.vel_target = Alloc<float>(E * L); s.noload_speed = Alloc<float>(E * L); s.acc_target = Alloc<float>(E * L); s.kp = Alloc<float>(E * L); s.kd = Alloc<float>(E * L);
         s.force_limit = Alloc<float>(E * L); s.feedforward = Alloc<float>(E * L);
         s.body_pose = Alloc<float>(E * B * 7); s.body_linvel = Alloc<float>(E * B * 3); s.body_angvel = Alloc<float>(E * B * 3);
-        s.carry_artic = Alloc<float>(E * n); s.carry_rigid = Alloc<float>(E * B * 6);
+        s.carry_artic = Alloc<float>(E * n); s.carry_rigid = Alloc<float>(E * B * 6); s.limit_lambda = Alloc<float>(E * L * 2);
         s.cache = Alloc<CacheEntry>(E * S * 4);
         s.status = Alloc<uint32_t>(E); s.solver_residual = Alloc<float>(E * 4); s.solver_sweeps = Alloc<uint32_t>(E);
         s.pair_count = Alloc<uint32_t>(E); s.pairs = Alloc<uint32_t>(E * S * 2); s.contact_count = Alloc<uint32_t>(E * S);
@@ -482,7 +482,7 @@ void World::Seed() {
     add(s.q, q0, L); add(s.qdot, nullptr, L); add(s.qddot, nullptr, L); add(s.tau, nullptr, L); add(s.actuator, nullptr, L);
     add(s.base_pose, base0, L ? 7u : 0u); add(s.link_vel, nullptr, 6 * L);
     add(s.body_pose, body0, 7 * B); add(s.body_linvel, nullptr, 3 * B); add(s.body_angvel, nullptr, 3 * B);
-    add(s.carry_artic, nullptr, n); add(s.carry_rigid, nullptr, 6 * B);
+    add(s.carry_artic, nullptr, n); add(s.carry_rigid, nullptr, 6 * B); add(s.limit_lambda, nullptr, 2 * L);
     add(s.cache, cache_empty_, 4 * S * static_cast<uint32_t>(sizeof(CacheEntry) / 4));
     add(s.status, nullptr, 1); add(s.solver_residual, nullptr, 4); add(s.solver_sweeps, nullptr, 1);
     reset_.field_count = f;
@@ -710,6 +710,7 @@ bool World::Field(uint32_t id, FieldInfo* out) {
         case 56: return set(s.acc_target, L, 0, true);
         case 25: return set(s.body_linvel, B * 3, 0, true);
         case 26: return set(s.body_angvel, B * 3, 0, true);
+        case 27: return set(s.limit_lambda, L * 2, 0, false);
         case 29: return set(s.actuator, L, 0, false);
         case 39: return set(s.status, 1, 1, true);
         case 109: return set(s.solver_residual, 4, 0, false);

@@ -45,6 +45,7 @@ class Field(enum.IntEnum):
     ACCELERATION_TARGET = 56
     BODY_LINEAR_VELOCITY = 25
     BODY_ANGULAR_VELOCITY = 26
+    JOINT_LIMIT_IMPULSE = 27
     ACTUATOR_EFFORT = 29
     ENV_STATUS = 39
     SOLVER_RESIDUAL = 109

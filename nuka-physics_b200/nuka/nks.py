@@ -107,10 +107,12 @@ def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0,
             local_pos = tuple(rot @ np.array(pos))
             local_quat = _quat_mul(pquat, quat)
             offset = ppos
-            axis = tuple(float(v) for v in joint.get("axis", (0, 0, 1)))
+            axis = _unit_axis(joint.get("axis", (0, 0, 1)))
         ipos, iquat = _pose(rb, "inertial")
         R = _quat_to_matrix(iquat)
         inertia = R @ np.diag([float(v) for v in rb.get("inertia", (0, 0, 0))]) @ R.T
+        if abs(abs(iquat[0]) - 1.0) <= 1e-12:              # principal axes along the link's: keep the three moments
+            inertia = [float(v) for v in rb.get("inertia", (0, 0, 0))]
         shapes = [c["collision_shape"] for c in node.get("children", []) if "collision_shape" in c]
         first = shapes[0] if shapes else None
         single = jtype in (T.REVOLUTE, T.PRISMATIC)
@@ -123,7 +125,9 @@ def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0,
         # critically damped 2 sqrt(gain) (scene_ir.hpp:335-336)
         link_kp = float(act["gain"]) if act else (kp if single else 0.0)
         link_kd = (float(act["damping"]) if "damping" in act else 2.0 * float(act["gain"]) ** 0.5) if act else (kd if single else 0.0)
-        link = tb.add_link(parent_link, jtype, axis=axis, offset=offset, mass=float(rb.get("mass", 0.0)), inertia_diag=inertia, com=ipos,
+        static_root = parent_link is None and jtype == T.FIXED          # a static body carries no inertia (the reference cooks zeros)
+        link = tb.add_link(parent_link, jtype, axis=axis, offset=offset, mass=0.0 if static_root else float(rb.get("mass", 0.0)),
+                           inertia_diag=(0.0, 0.0, 0.0) if static_root else inertia, com=ipos,
                            q0=float(joint.get("initial_position", 0.0)) if single else 0.0, kp=link_kp, kd=link_kd,
                            force_limit=float(act.get("force_limit", 0.0)) if act else 0.0,
                            frictionloss=float(joint.get("frictionloss", 0.0)) if single else 0.0,
@@ -146,6 +150,7 @@ def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0,
 
     if roots:
         add(roots[0], None)
+        _exclude_welded(tb)
     for node in free:       # in document order, after the articulation's rows: the collidable row order both cookers use
         rb = node["rigid_body"]
         shapes = [c["collision_shape"] for c in node.get("children", []) if "collision_shape" in c]
@@ -192,6 +197,52 @@ def cook_native(scene_text, **options):
     out = ctypes.create_string_buffer(size.value)
     _check(lib.nuka_b200_scene_cook(text, len(text), ctypes.byref(o), out, size.value, ctypes.byref(size)))
     return out.raw[:size.value]
+
+
+def _unit_axis(axis):
+    """The joint axis as the reference cooks it (src/scene/cooker.cpp:680, math::Vec3::Normalized): float32 components
+    over the float32 length, zero when shorter than 1e-12."""
+    x, y, z = (np.float32(v) for v in axis)
+    length = np.sqrt(x * x + y * y + z * z, dtype=np.float32)
+    if length < np.float32(1e-12):
+        return (0.0, 0.0, 0.0)
+    return (float(x / length), float(y / length), float(z / length))
+
+
+def _exclude_welded(tb):
+    """The reference's weld rule (src/scene/cooker.cpp:505-536, MuJoCo's weldbody and filterparent): links joined by fixed
+    joints form a cluster; no pair inside a cluster, and none between a cluster and the cluster of its parent link.  Without
+    fixed joints this is the parent-child exclusion add_link already applies."""
+    links = tb.links
+    parent = [l["parent"] for l in links]
+
+    def weld(l):
+        while parent[l] != T.NOLINK and links[l]["jtype"] == T.FIXED:
+            l = parent[l]
+        return l
+
+    clusters = {}
+    for l in range(len(links)):
+        clusters.setdefault(weld(l), []).append(l)
+    pairs = set()
+    for root, members in clusters.items():
+        for i, a in enumerate(members):
+            for b in members[i + 1:]:
+                pairs.add((min(a, b), max(a, b)))
+        if parent[root] == T.NOLINK:
+            continue
+        for other in clusters[weld(parent[root])]:
+            for member in members:
+                if member != other:
+                    pairs.add((min(member, other), max(member, other)))
+    rows = {}
+    for row, b in enumerate(tb.bodies):
+        if b["link"] != T.NOLINK:
+            rows.setdefault(b["link"], []).append(row)
+    for a, b in pairs:
+        for ra in rows.get(a, []):
+            for rb in rows.get(b, []):
+                tb.excluded.add((min(ra, rb) << 32) | max(ra, rb))
 
 
 def _frame(pos=(0.0, 0.0, 0.0), quat=(1.0, 0.0, 0.0, 0.0)):

@@ -127,6 +127,7 @@ typedef struct orc_env {
     float *link_acc, *link_vbias, *link_pbias, *link_S;  /* L*6 */
     float *link_xup, *link_ic;               /* L*36 */
     float *drive_target, *vel_target, *kp, *kd, *force_limit, *feedforward, *noload_speed, *acc_target;
+    float *limit_lambda;      /* 2 x L: the joint-limit multipliers the last velocity solve left (lower, upper per link) */
     float *drive_command, *drive_dissipation, *drive_lower, *drive_upper;
     float *actuator_applied;                 /* L */
     float *M, *Mfactor, *bias;               /* ndof^2, ndof^2, ndof */

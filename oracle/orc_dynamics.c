@@ -526,6 +526,8 @@ void orc_integrate_position(const orc_model *m, orc_env *e) {
             rv[3] = turned.x; rv[4] = turned.y; rv[5] = turned.z;
         }
     }
+    /* the gyro bit is cleared before every body integration: ops/articulation.cu:1053-1056, 1810-1812 */
+    if (m->B) e->status &= ~ORC_STATUS_GYRO_FAILURE;
     for (uint32_t b = 0; b < m->B; ++b) {
         if (m->inv_mass[b] <= 0.0f || m->body_to_link[b] != ORC_NOLINK) continue;
         float *pose = e->body_pose + 7 * b;

@@ -160,6 +160,9 @@ void orc_assemble_rows(const orc_model *m, orc_env *e) {
         for (uint32_t k = 0; k < m->ndof; ++k) r->ja[k] = 0.0f;
         r->ja[m->link_dof[l]] = side == 0u ? 1.0f : -1.0f;
         r->penetration = fmaxf(-dist, 0.0f);
+        /* an authored limit row starts from the multiplier the last step's solve left in its slot (assemble_rows.cu:826-879
+         * clears lambda only for links without that limit, and the per-step clear :366-383 covers the contact rows alone) */
+        r->lambda = e->limit_lambda[2u * l + side];
         r->tag = 1u; r->link = l;
     }
     /* joint dry friction rows, assemble_rows.cu:886-934 */

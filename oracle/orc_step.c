@@ -45,7 +45,7 @@ static void env_alloc(const orc_model *m, orc_env *e) {
     e->link_vbias = falloc(6 * L); e->link_pbias = falloc(6 * L); e->link_S = falloc(6 * L);
     e->link_xup = falloc(36 * L); e->link_ic = falloc(36 * L);
     e->drive_target = falloc(L); e->vel_target = falloc(L); e->kp = falloc(L); e->kd = falloc(L); e->noload_speed = falloc(L); e->acc_target = falloc(L);
-    e->force_limit = falloc(L); e->feedforward = falloc(L);
+    e->force_limit = falloc(L); e->feedforward = falloc(L); e->limit_lambda = falloc(2 * L);
     e->drive_command = falloc(L); e->drive_dissipation = falloc(L); e->drive_lower = falloc(L); e->drive_upper = falloc(L);
     e->actuator_applied = falloc(L);
     e->M = falloc((size_t)n * n); e->Mfactor = falloc((size_t)n * n); e->bias = falloc(n);
@@ -68,7 +68,7 @@ static void env_free(orc_env *e) {
                  e->drive_command, e->drive_dissipation, e->drive_lower, e->drive_upper, e->actuator_applied, e->M, e->Mfactor, e->bias,
                  e->body_pose, e->body_linvel, e->body_angvel, e->body_winv, e->aabb_lo, e->aabb_hi, e->pairs, e->ccount,
                  e->cpoint, e->cnormal, e->cdepth, e->cid_pair, e->cid_feature, e->rows, e->jac_pool, e->artic_vel, e->artic_free,
-                 e->qdot_pseudo, e->rigid_vel, e->rigid_free, e->body_pseudo, e->cache, e->cache_next};
+                 e->qdot_pseudo, e->rigid_vel, e->rigid_free, e->body_pseudo, e->cache, e->cache_next, e->limit_lambda};
     for (size_t i = 0; i < sizeof p / sizeof p[0]; ++i) free(p[i]);
 }
 
@@ -81,6 +81,7 @@ static void env_seed(const orc_model *m, orc_env *e) {
         e->kp[l] = m->kp0[l]; e->kd[l] = m->kd0[l]; e->force_limit[l] = m->force_limit0[l];
     }
     memset(e->link_vel, 0, sizeof(float) * 6 * L);
+    memset(e->limit_lambda, 0, sizeof(float) * 2 * L);
     if (L) memcpy(e->base_pose, m->base_pose0, 28);
     if (B) memcpy(e->body_pose, m->body_pose0, sizeof(float) * 7 * B);
     memset(e->body_linvel, 0, sizeof(float) * 3 * B); memset(e->body_angvel, 0, sizeof(float) * 3 * B);
@@ -205,6 +206,9 @@ void orc_step_env(const orc_model *m, orc_env *e) {
     if (has_collidables) { orc_build_aabbs(m, e); orc_find_pairs(m, e); orc_narrowphase(m, e); }
     if (has_contacts) { orc_assemble_rows(m, e); orc_warm_start_prepare(m, e); }
     orc_solve(m, e);
+    /* a limit row's slot keeps the multiplier of the velocity solve for the next step's row (block_descent_tile.cuh:2556) */
+    for (uint32_t r = 0; r < e->nrows; ++r)
+        if (e->rows[r].tag == 1u) e->limit_lambda[2u * e->rows[r].link + ((e->rows[r].flags & ORC_ROW_LIMIT_UPPER) ? 1u : 0u)] = e->rows[r].lambda;
     if (has_contacts) { orc_warm_start_commit(m, e); orc_readout_drives(m, e); }
     orc_integrate_position(m, e);
     if (has_artic) { orc_fk(m, e); orc_fk_link_velocities(m, e); }
@@ -262,7 +266,7 @@ static void *field_ptr(const orc_model *m, orc_env *e, const char *f, size_t *co
     R("pair_count", &e->pair_count, 1) R("candidate_pairs", e->pairs, 2 * S) R("contact_count", e->ccount, S)
     R("contact_point", e->cpoint, 12 * S) R("contact_normal", e->cnormal, 12 * S) R("contact_depth", e->cdepth, 4 * S)
     R("env_status", &e->status, 1) R("solver_residual", e->solver_residual, 4) R("solver_sweeps", &e->sweeps, 1)
-    R("contact_points", &e->contact_points, 1) R("qdot_pseudo", e->qdot_pseudo, n) R("dof_velocity", e->artic_vel, n)
+    R("limit_multiplier", e->limit_lambda, 2 * L) R("contact_points", &e->contact_points, 1) R("qdot_pseudo", e->qdot_pseudo, n) R("dof_velocity", e->artic_vel, n)
 #undef R
     *count = 0;
     return NULL;

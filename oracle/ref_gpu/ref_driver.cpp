@@ -164,7 +164,7 @@ struct Args {
     std::string scene, state, dump;
     uint32_t envs = 1, vel_iters = 0, pos_iters = 0xffffffffu, steps = 0, every = 1, control_mode = 0;
     float dt = 1.0f / 200.0f;
-    bool contacts = true, cook_only = false;
+    bool contacts = true, cook_only = false, taps = false;
     int warm = 0, timed = 0, repeats = 1;
     float active_sigma = 0.0f;
 };
@@ -195,6 +195,7 @@ int main(int argc, char** argv) {
         else if (k == "--dump") a.dump = next();
         else if (k == "--no-contacts") a.contacts = false;
         else if (k == "--cook-only") a.cook_only = true;
+        else if (k == "--taps") a.taps = true;
         else if (k == "--time") { std::sscanf(next(), "%d,%d,%d", &a.warm, &a.timed, &a.repeats); }
         else if (k == "--active") a.active_sigma = static_cast<float>(std::atof(next()));
         else { std::fprintf(stderr, "unknown argument %s\n", k.c_str()); return 2; }
@@ -272,11 +273,16 @@ int main(int argc, char** argv) {
             out.F32("start_kd", Download<float>(world, nk::FieldId::DriveDamping, size_t{E} * L));
             out.F32("start_force_limit", Download<float>(world, nk::FieldId::DriveForceLimit, size_t{E} * L));
             out.F32("start_drive_target", Download<float>(world, nk::FieldId::DriveTarget, size_t{E} * L));
-            std::vector<float> tq, tqd, tbase, ttwist, tbody;
-            std::vector<uint32_t> tstatus, tpairs, tpaircount, tcount;
+            std::vector<float> tq, tqd, tbase, ttwist, tbody, tresidual, tpseudo, tlinkpseudo, tbodypl, tbodypa, tlimit, tdepth;
+            std::vector<uint32_t> tstatus, tpairs, tpaircount, tcount, tsweeps, status_any, tstatusany;
             for (uint32_t s = 1; s <= a.steps; ++s) {
                 const nk::StepResult r = world.Step();
                 if (!r.AllOk()) { std::fprintf(stderr, "step %u failed\n", s); return 5; }
+                {   // the gyro bit describes one step only: keep every bit any step so far has raised
+                    const auto now = Download<uint32_t>(world, nk::FieldId::EnvStatus, E);
+                    if (status_any.size() != now.size()) status_any.assign(now.size(), 0u);
+                    for (size_t i = 0; i < now.size(); ++i) status_any[i] |= now[i];
+                }
                 if (s % a.every != 0u && s != 1u && s != a.steps) continue;
                 world.Synchronize();
                 auto append = [](auto& dst, const auto& src) { dst.insert(dst.end(), src.begin(), src.end()); };
@@ -286,6 +292,17 @@ int main(int argc, char** argv) {
                 append(ttwist, Download<float>(world, nk::FieldId::LinkVelocity, size_t{E} * L * 6));
                 append(tbody, Download<float>(world, nk::FieldId::BodyPose, size_t{E} * B * 7));
                 append(tstatus, Download<uint32_t>(world, nk::FieldId::EnvStatus, E));
+                append(tstatusany, status_any);
+                append(tresidual, Download<float>(world, nk::FieldId::SolverResidual, size_t{E} * 4));
+                append(tsweeps, Download<uint32_t>(world, nk::FieldId::VbdVelocitySweepCount, E));
+                if (a.taps) {
+                    append(tpseudo, Download<float>(world, nk::FieldId::QdotPseudo, size_t{E} * L));
+                    append(tlinkpseudo, Download<float>(world, nk::FieldId::LinkVelocityPseudo, size_t{E} * L * 6));
+                    append(tbodypl, Download<float>(world, nk::FieldId::BodyPseudoLinearVelocity, size_t{E} * B * 3));
+                    append(tbodypa, Download<float>(world, nk::FieldId::BodyPseudoAngularVelocity, size_t{E} * B * 3));
+                    append(tlimit, Download<float>(world, nk::FieldId::JointLimitImpulse, size_t{E} * L * 2));
+                    if (S != 0u) append(tdepth, Download<float>(world, nk::FieldId::UcontactDepth, size_t{E} * S * 4));
+                }
                 if (S != 0u) {
                     append(tpaircount, Download<uint32_t>(world, nk::FieldId::PairCount, E));
                     append(tpairs, Download<uint32_t>(world, nk::FieldId::CandidatePairs, size_t{E} * S * 2));
@@ -299,7 +316,12 @@ int main(int argc, char** argv) {
                 out.U32("traj_steps", marks);
             }
             out.F32("traj_q", tq); out.F32("traj_qdot", tqd); out.F32("traj_base_pose", tbase); out.F32("traj_link_velocity", ttwist);
-            out.F32("traj_body_pose", tbody); out.U32("traj_status", tstatus); out.U32("traj_pair_count", tpaircount);
+            out.F32("traj_body_pose", tbody); out.U32("traj_status", tstatus); out.U32("traj_status_any", tstatusany); out.F32("traj_solver_residual", tresidual); out.U32("traj_solver_sweeps", tsweeps);
+            if (a.taps) {
+                out.F32("traj_qdot_pseudo", tpseudo); out.F32("traj_link_velocity_pseudo", tlinkpseudo);
+                out.F32("traj_body_pseudo_linear", tbodypl); out.F32("traj_body_pseudo_angular", tbodypa);
+                out.F32("traj_joint_limit_impulse", tlimit); out.F32("traj_contact_depth", tdepth);
+            } out.U32("traj_pair_count", tpaircount);
             out.U32("traj_candidate_pairs", tpairs); out.U32("traj_contact_count", tcount);
             if (!out.Write(a.dump)) { std::fprintf(stderr, "cannot write %s\n", a.dump.c_str()); return 1; }
         }

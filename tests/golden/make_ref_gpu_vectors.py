@@ -44,6 +44,10 @@ CASES = {
     # computed-torque control (control mode 3): the arm without contacts, the quadruped landing with saturating force limits
     "arm7_ct": (lambda: T.arm7(0), lambda E: ref_cases.arm_computed_torque_state(E, 0), 1.0 / 500.0, 4, 100, 20),
     "quadruped_ct": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_computed_torque_state(E, 0), 1.0 / 200.0, 4, 60, 20),
+    # seeded random articulations (random trees, revolute / prismatic / fixed joints, limits, dry friction, armature,
+    # spheres with boxes or capsules, free bodies): parity beyond the benchmark robots
+    **{f"random{k}": (lambda k=k: ref_cases.random_robot(k), lambda E, k=k: ref_cases.random_robot_state(k, E), 1.0 / 250.0, 6, 60, 20)
+       for k in (0, 1, 3, 7)},
 }
 SCENE_OF = {"quadruped_moving": "quadruped", "arm7_ct": "arm7", "quadruped_ct": "quadruped"}
 CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3}
@@ -101,9 +105,9 @@ def prepare():
 
 
 KEEP = ("run", "run_dt", "dyn_qddot", "dyn_mass", "dyn_bias", "start_link_pose", "start_kp", "start_kd", "start_force_limit",
-        "start_drive_target", "traj_steps", "traj_q", "traj_qdot", "traj_base_pose", "traj_status", "traj_pair_count",
-        "traj_candidate_pairs", "traj_contact_count")
-FREE_BODY_CASES = ("pile12", "quadbox")     # body poses are kept where free bodies carry state of their own
+        "start_drive_target", "traj_steps", "traj_q", "traj_qdot", "traj_base_pose", "traj_status", "traj_status_any",
+        "traj_solver_sweeps", "traj_solver_residual", "traj_pair_count", "traj_candidate_pairs", "traj_contact_count")
+FREE_BODY_CASES = ("pile12", "quadbox", "random0", "random1", "random3", "random7")     # body poses are kept where free bodies carry state of their own
 
 
 def collect(src):

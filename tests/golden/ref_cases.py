@@ -180,3 +180,98 @@ def quadruped_computed_torque_state(env_count, seed=0):
     return {"q": st["q"], "base_pose": st["base_pose"], "drive_target": target,
             "kp": np.full((env_count, L), 400.0, np.float32), "kd": np.full((env_count, L), 40.0, np.float32),
             "force_limit": np.full((env_count, L), 20.0, np.float32)}
+
+
+def random_robot(seed):
+    """A seeded random articulation on a ground plane, for parity runs beyond the benchmark robots: a random tree of 6 to 14
+    links under a floating or a fixed base, revolute and prismatic joints with some fixed ones in between, random axes,
+    offsets, masses and inertial frames, joint limits, dry friction, armature and damping on some joints, position
+    actuators, spheres and boxes (or spheres and capsules: the two never mix, capsule-box pairs have no analytic manifold)
+    on most links, and up to three free bodies.  Returns the TemplateBuilder."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "nuka-physics_b200"))
+    from nuka import templates as T
+    rng = np.random.Generator(np.random.PCG64(1000 + seed))
+    floating = bool(rng.random() < 0.6)
+    count = int(rng.integers(6, 15))
+    round_only = bool(rng.random() < 0.5)                 # spheres + capsules, else spheres + boxes
+    tb = T.TemplateBuilder(dt=1.0 / 250.0, vel_iters=6, max_contacts=0)
+
+    def shape():
+        kind = rng.random()
+        if kind < 0.25:
+            return None
+        if kind < 0.6:
+            return (T.SPHERE, float(rng.uniform(0.03, 0.07)))
+        if round_only:
+            return (T.CAPSULE, float(rng.uniform(0.02, 0.04)), float(rng.uniform(0.03, 0.08)))
+        return (T.BOX, float(rng.uniform(0.03, 0.07)), float(rng.uniform(0.03, 0.07)), float(rng.uniform(0.03, 0.07)))
+
+    def inertia(mass):        # of a solid box of random size: physically realisable principal moments
+        return tuple(float(v) for v in T.box_inertia(mass, rng.uniform(0.06, 0.2, size=3)))
+
+    mass = float(rng.uniform(2.0, 5.0))
+    tb.add_link(None, T.FLOATING if floating else T.FIXED, mass=mass, inertia_diag=inertia(mass), shape=shape() if floating else None,
+                mu=float(rng.uniform(0.5, 1.0)), contype=1, conaffinity=0, local_pos=(0.0, 0.0, 0.0) if floating else (0.0, 0.0, 0.22))
+    tb.base_pose = [0.0, 0.0, 0.28, 1.0, 0.0, 0.0, 0.0]
+    for i in range(1, count):
+        parent = int(rng.integers(max(0, i - 4), i))
+        pick = rng.random()
+        jtype = T.REVOLUTE if pick < 0.65 else T.PRISMATIC if pick < 0.85 else T.FIXED
+        axis = rng.normal(size=3)
+        axis = tuple(float(v) for v in axis / np.linalg.norm(axis))
+        mass = float(rng.uniform(0.2, 1.5))
+        single = jtype != T.FIXED
+        limited = single and rng.random() < 0.5
+        span = 0.15 if jtype == T.PRISMATIC else 0.8
+        tb.add_link(parent, jtype, axis=axis, offset=tuple(float(v) for v in rng.uniform(-0.12, 0.12, size=3)), mass=mass,
+                    inertia_diag=inertia(mass), com=tuple(float(v) for v in rng.uniform(-0.04, 0.04, size=3)),
+                    q0=float(rng.uniform(-0.1, 0.1)) if single else 0.0,
+                    kp=float(rng.uniform(20.0, 80.0)) if single and rng.random() < 0.8 else 0.0, kd=float(rng.uniform(0.5, 2.0)) if single else 0.0,
+                    force_limit=float(rng.uniform(5.0, 30.0)) if single and rng.random() < 0.3 else 0.0,
+                    damping=float(rng.uniform(0.0, 0.3)) if single else 0.0, armature=float(rng.uniform(0.0, 0.02)) if single else 0.0,
+                    frictionloss=float(rng.uniform(0.05, 0.4)) if single and rng.random() < 0.4 else 0.0,
+                    limits=(-span * float(rng.uniform(0.3, 1.0)), span * float(rng.uniform(0.3, 1.0))) if limited else None,
+                    shape=shape(), shape_pos=tuple(float(v) for v in rng.uniform(-0.03, 0.03, size=3)), mu=float(rng.uniform(0.5, 1.0)),
+                    contype=1, conaffinity=0)
+    for l in tb.links:                                    # a drive needs both gains for the scene's actuator record
+        if l["kp"] == 0.0:
+            l["kd"] = 0.0
+    for k in range(int(rng.integers(0, 4))):
+        if round_only:
+            body = (T.SPHERE, float(rng.uniform(0.04, 0.08)))
+        else:
+            body = (T.BOX, float(rng.uniform(0.04, 0.08)), float(rng.uniform(0.04, 0.08)), float(rng.uniform(0.04, 0.08)))
+        m = float(rng.uniform(0.2, 1.0))
+        tb.add_free_body(body, m, inertia(m), (float(rng.uniform(-0.5, 0.5)), float(rng.uniform(-0.5, 0.5)), float(rng.uniform(0.09, 0.2)), 1.0, 0.0, 0.0, 0.0),
+                         mu=float(rng.uniform(0.5, 1.0)), contype=1, conaffinity=3)
+    tb.add_plane(0.0, mu=0.9, contype=2, conaffinity=1)
+    # through the scene writer and the cooker: links come back in the tree's pre-order, the order every consumer of the
+    # scene file sees
+    from nuka import nks
+    cooked = nks.cook(nks.scene_from_builder(tb), dt=1.0 / 250.0, vel_iters=6, kp=0.0, kd=0.0, scene_filters=True, ground_height=None,
+                      max_contacts=64)
+    return cooked
+
+
+def random_robot_state(seed, env_count):
+    """Per-env start state of random_robot(seed): joint positions near the initial ones, joint rates, a tilted base."""
+    tb = random_robot(seed)
+    L = len(tb.links)
+    rng = np.random.Generator(np.random.PCG64(2000 + seed))
+    q0 = np.array([l["q0"] for l in tb.links], np.float32)
+    q = np.tile(q0, (env_count, 1)) + rng.normal(0, 0.05, size=(env_count, L)).astype(np.float32)
+    qdot = rng.normal(0, 0.3, size=(env_count, L)).astype(np.float32)
+    for i, l in enumerate(tb.links):
+        if l["jtype"] not in (0, 1):
+            q[:, i] = 0.0; qdot[:, i] = 0.0
+    base = np.tile(np.array(tb.base_pose, np.float32), (env_count, 1))
+    tilt = rng.normal(0, 0.15, size=(env_count, 3))
+    quat = np.concatenate([np.ones((env_count, 1)), 0.5 * tilt], axis=1)
+    base[:, 3:] = (quat / np.linalg.norm(quat, axis=1, keepdims=True)).astype(np.float32)
+    base[:, 2] += rng.uniform(-0.03, 0.1, size=env_count).astype(np.float32)
+    out = {"q": q.astype(np.float32), "qdot": qdot.astype(np.float32)}
+    if tb.links[0]["jtype"] == 3:
+        out["base_pose"] = base
+    return out

@@ -27,6 +27,7 @@ CASES = {
     "arm7_ct": ("arm7", lambda E: ref_cases.arm_computed_torque_state(E, 0)),
     "quadruped_ct": ("quadruped", lambda E: ref_cases.quadruped_computed_torque_state(E, 0)),
 }
+CASES.update({f"random{k}": (f"random{k}", lambda E, k=k: ref_cases.random_robot_state(k, E)) for k in (0, 1, 3, 7)})
 CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3}
 # drive inputs a case's start state may carry: state key -> (oracle field name, nuka.Field name)
 DRIVE_INPUTS = {"drive_target": ("drive_target", "DRIVE_TARGET"), "vel_target": ("velocity_target", "VELOCITY_TARGET"),
@@ -79,29 +80,63 @@ def err_envs(got, want, floor=0.0):
 CHAOTIC = ("pile12", "humanoid")
 
 
-def assert_position_parity(got, want, first, tag, case, absolute=False):
-    """Positions.  After one step: 1e-5 in every env.  Along a trajectory: 1e-4 in every env, or, for the chaotic cases,
-    in 90 % of the envs with the median below 1e-5.  `absolute` measures against max(|x|, 1) (body poses in metres)."""
+# Random robots with free bodies lying beside them (the floating-base seeds).  Two of the reference's own decisions in
+# these scenes hang on numbers near the bottom of the float range, which no second evaluation of the algorithm
+# reproduces bit for bit:
+#  - a free body that the contact solve returns to its free velocity keeps an angular velocity of 1e-36 .. 1e-39 rad/s,
+#    the rounding left by the Newton steps.  The free-rotation solve (ops/rigid_types.cuh:38-120) divides by the largest
+#    momentum component; when that is below 1 / FLT_MAX the quotient overflows, the solve reports kEnvStatusGyroFailure
+#    and the body skips that step's pose update, push-out included (ops/articulation.cu:1088-1094).  Whether the residue
+#    is 4e-39 (solvable) or 2e-39 (not) differs between the reference's run and any other evaluation.  Envs in which
+#    either side has raised that bit so far are left out of the comparison (GYRO_BIT, `comparable` below); the rest must
+#    be at least 85 % of the envs.
+#  - a block whose force is 1e-20 with zero velocity is not "within rounding" (the rounding scale is zero too), and the
+#    decrement force * step underflows to zero: the block reports FLT_MAX and the env stops sweeping for that step
+#    (ops/block_descent_tile.cuh:2211-2258, 3068).  Here too the two sides can fall on different sides of the underflow.
+# The comparable envs are held to the bars of the chaotic cases up to step 40.
+SENSITIVE = ("random0", "random3", "random7")
+SENSITIVE_LAST_STEP = 40
+GYRO_BIT = 32
+
+
+def comparable(case, ref_status_any, own_status_any):
+    """Envs that enter the comparison: all of them, except, in the sensitive cases, those in which either side has
+    reported a failed free-rotation solve in any step so far."""
+    keep = np.ones(len(ref_status_any), bool)
+    if case in SENSITIVE:
+        keep = ((np.asarray(ref_status_any) | np.asarray(own_status_any)) & GYRO_BIT) == 0
+        assert keep.mean() >= 0.85, (case, float(keep.mean()))
+    return keep
+
+
+def assert_position_parity(got, want, first, tag, case, absolute=False, keep=None):
+    """Positions.  After one step: 1e-5 in every env.  Along a trajectory: 1e-4 in every env, or, for the chaotic and the
+    sensitive cases, in 90 % of the envs with the median below 1e-5.  `absolute` measures against max(|x|, 1) (body poses
+    in metres).  `keep` selects the envs that are compared."""
     d = err_envs(got, want, floor=1.0 if absolute else 0.0)
+    if keep is not None:
+        d = d[keep]
     if first:
         assert d.max() < 1e-5, (tag, float(d.max()))
-    elif case in CHAOTIC:
+    elif case in CHAOTIC or case in SENSITIVE:
         assert np.median(d) < 1e-5 and np.percentile(d, 90) < 1e-4 and d.max() < 0.2, \
             (tag, float(np.median(d)), float(np.percentile(d, 90)), float(d.max()))
     else:
         assert d.max() < 1e-4, (tag, float(d.max()))
 
 
-def assert_velocity_parity(got, want, first, tag, case=None):
+def assert_velocity_parity(got, want, first, tag, case=None, keep=None):
     """Post-solve velocities.  After one step: within 1e-5 for at least 95 % of the envs and 1e-4 for all.  The block
     descent stops at its sweep limit in envs whose feet start inside the ground, and an iteration that has not converged
     amplifies the last-bit differences between two fp32 evaluations (the reference's own GPU result and a CPU evaluation of
     the same algorithm differ by 2e-5 in 2 % of these envs, by 1e-7 in the rest).  Along a trajectory: 1e-3 (90 % of the
     envs in the chaotic cases)."""
     d = err_envs(got, want, floor=1.0)
+    if keep is not None:
+        d = d[keep]
     if first:
         assert np.percentile(d, 95) < 1e-5 and d.max() < 1e-4, (tag, float(np.percentile(d, 95)), float(d.max()))
-    elif case in CHAOTIC:
+    elif case in CHAOTIC or case in SENSITIVE:
         assert np.percentile(d, 90) < 1e-3, (tag, float(np.percentile(d, 90)))
     else:
         assert d.max() < 1e-3, (tag, float(d.max()))

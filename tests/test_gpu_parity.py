@@ -483,3 +483,27 @@ def test_computed_torque_control(device, oracle):
     assert w.download(F.ENV_STATUS).max() == 0
     assert w.download(F.BASE_POSE)[:, 2].min() > 0.1                   # the controller keeps the trunks off the ground
     w.destroy()
+
+
+def test_joint_limit_multipliers_carry_over(device, oracle):
+    """A random fixed-base arm that runs into its joint limits: the multipliers of the limit rows persist from step to
+    step (the next step's rows start from them), are readable as JOINT_LIMIT_IMPULSE, and a reset clears them."""
+    import sys
+    sys.path.insert(0, GOLDEN)
+    import ref_cases
+    E = 64
+    tb = ref_cases.random_robot(1)
+    L = len(tb.links)
+    st = ref_cases.random_robot_state(1, E)
+    w, o = make_pair(device, oracle, tb, E, {"q": st["q"], "qdot": st["qdot"]})
+    seen = False
+    for _ in range(6):
+        w.step_n(10); o.step(10)
+        mine, want = w.download(F.JOINT_LIMIT_IMPULSE).reshape(E, 2 * L), o.get("limit_multiplier", 2 * L)
+        seen |= bool((want != 0).any())
+        assert rel(mine, want) < 1e-2
+        assert rel(w.download(F.JOINT_POSITION), o.get("q", L)) < 1e-4
+    assert seen                                   # the case does reach its limits
+    w.reset()
+    assert not w.download(F.JOINT_LIMIT_IMPULSE).any()
+    w.destroy()

@@ -11,7 +11,7 @@ import nuka
 from nuka import nks, nkt
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-SCENES = ["arm7", "quadruped", "humanoid", "pile12", "quadbox"]
+SCENES = ["arm7", "quadruped", "humanoid", "pile12", "quadbox", "random0", "random1", "random3", "random7"]
 
 
 def compare(native_bytes, tb):
