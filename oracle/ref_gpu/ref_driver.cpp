@@ -235,6 +235,7 @@ int main(int argc, char** argv) {
                 {"q", nk::FieldId::Q}, {"qdot", nk::FieldId::Qdot}, {"base_pose", nk::FieldId::BasePose}, {"link_velocity", nk::FieldId::LinkVelocity},
                 {"drive_target", nk::FieldId::DriveTarget}, {"vel_target", nk::FieldId::VelocityTarget}, {"acc_target", nk::FieldId::AccelerationTarget},
                 {"kp", nk::FieldId::DriveStiffness}, {"kd", nk::FieldId::DriveDamping}, {"force_limit", nk::FieldId::DriveForceLimit},
+                {"noload_speed", nk::FieldId::ActuatorNoloadSpeed}, {"feedforward", nk::FieldId::JointF},
                 {"body_pose", nk::FieldId::BodyPose}};
             for (const auto& f : fields) {
                 const auto it = st.find(f.first);

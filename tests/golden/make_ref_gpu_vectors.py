@@ -44,14 +44,21 @@ CASES = {
     # computed-torque control (control mode 3): the arm without contacts, the quadruped landing with saturating force limits
     "arm7_ct": (lambda: T.arm7(0), lambda E: ref_cases.arm_computed_torque_state(E, 0), 1.0 / 500.0, 4, 100, 20),
     "quadruped_ct": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_computed_torque_state(E, 0), 1.0 / 200.0, 4, 60, 20),
+    # the other control modes on the landing quadruped: joint efforts with a feedforward term (1), rate targets (2),
+    # efforts inside a torque-speed envelope (5)
+    "quadruped_torque": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_mode_state(1, E), 1.0 / 200.0, 4, 40, 10),
+    "quadruped_velocity": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_mode_state(2, E), 1.0 / 200.0, 4, 40, 10),
+    "quadruped_actuator": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_mode_state(5, E), 1.0 / 200.0, 4, 40, 10),
     # seeded random articulations (random trees, revolute / prismatic / fixed joints, limits, dry friction, armature,
     # spheres with boxes or capsules, free bodies): parity beyond the benchmark robots
     **{f"random{k}": (lambda k=k: ref_cases.random_robot(k), lambda E, k=k: ref_cases.random_robot_state(k, E), 1.0 / 250.0, 6, 60, 20)
        for k in (0, 1, 3, 7)},
 }
-SCENE_OF = {"quadruped_moving": "quadruped", "arm7_ct": "arm7", "quadruped_ct": "quadruped"}
-CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3}
-STATE_FIELDS = ("q", "qdot", "base_pose", "link_velocity", "body_pose", "drive_target", "vel_target", "acc_target", "kp", "kd", "force_limit")
+SCENE_OF = {"quadruped_moving": "quadruped", "arm7_ct": "arm7", "quadruped_ct": "quadruped", "quadruped_torque": "quadruped",
+            "quadruped_velocity": "quadruped", "quadruped_actuator": "quadruped"}
+CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3, "quadruped_torque": 1, "quadruped_velocity": 2, "quadruped_actuator": 5}
+STATE_FIELDS = ("q", "qdot", "base_pose", "link_velocity", "body_pose", "drive_target", "vel_target", "acc_target", "kp", "kd", "force_limit",
+                "noload_speed", "feedforward")
 # throughput of the reference on the other configurations, on the protocol of bench.py --workload: the same seeded
 # per-env start states, the same untimed settle steps, then the timed steps
 # (scene case, envs, dt, iterations, settle steps, timed steps, start state)

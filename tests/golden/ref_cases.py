@@ -182,6 +182,41 @@ def quadruped_computed_torque_state(env_count, seed=0):
             "force_limit": np.full((env_count, L), 20.0, np.float32)}
 
 
+def quadruped_mode_state(mode, env_count, seed=0):
+    """The quadruped's seeded drop under the other control modes.  1 (torque): the target field carries joint efforts,
+    a feedforward effort on top.  2 (velocity): rate targets, the stiffness field is the rate gain, 15 N m force limits.
+    5 (actuator): efforts inside a torque-speed envelope of 3 N m stall effort and 6 rad/s no-load speed (three times those
+    efforts make the legs thrash and the trajectories chaotic within 30 steps)."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "nuka-physics_b200"))
+    from nuka import templates as T
+    st = T.quadruped_state(env_count, seed)
+    L = 13
+    rng = np.random.Generator(np.random.PCG64(3000 + 10 * mode + seed))
+    out = {"q": st["q"], "base_pose": st["base_pose"]}
+    joints = np.zeros((env_count, L), np.float32)
+    if mode == 1:
+        joints[:, 1:] = rng.normal(0, 2.0, size=(env_count, L - 1))
+        out["drive_target"] = joints
+        ff = np.zeros((env_count, L), np.float32)
+        ff[:, 1:] = rng.normal(0, 0.5, size=(env_count, L - 1))
+        out["feedforward"] = ff
+    elif mode == 2:
+        joints[:, 1:] = rng.normal(0, 1.0, size=(env_count, L - 1))
+        out["vel_target"] = joints
+        out["kp"] = np.full((env_count, L), 8.0, np.float32)
+        out["force_limit"] = np.full((env_count, L), 15.0, np.float32)
+    elif mode == 5:
+        joints[:, 1:] = rng.normal(0, 2.0, size=(env_count, L - 1))
+        out["drive_target"] = joints
+        out["force_limit"] = np.full((env_count, L), 3.0, np.float32)
+        out["noload_speed"] = np.full((env_count, L), 6.0, np.float32)
+    else:
+        raise ValueError(mode)
+    return out
+
+
 def random_robot(seed):
     """A seeded random articulation on a ground plane, for parity runs beyond the benchmark robots: a random tree of 6 to 14
     links under a floating or a fixed base, revolute and prismatic joints with some fixed ones in between, random axes,

@@ -27,12 +27,15 @@ CASES = {
     "arm7_ct": ("arm7", lambda E: ref_cases.arm_computed_torque_state(E, 0)),
     "quadruped_ct": ("quadruped", lambda E: ref_cases.quadruped_computed_torque_state(E, 0)),
 }
+CASES.update({f"quadruped_{name}": ("quadruped", lambda E, mode=mode: ref_cases.quadruped_mode_state(mode, E))
+              for name, mode in (("torque", 1), ("velocity", 2), ("actuator", 5))})
 CASES.update({f"random{k}": (f"random{k}", lambda E, k=k: ref_cases.random_robot_state(k, E)) for k in (0, 1, 3, 7)})
-CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3}
+CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3, "quadruped_torque": 1, "quadruped_velocity": 2, "quadruped_actuator": 5}
 # drive inputs a case's start state may carry: state key -> (oracle field name, nuka.Field name)
 DRIVE_INPUTS = {"drive_target": ("drive_target", "DRIVE_TARGET"), "vel_target": ("velocity_target", "VELOCITY_TARGET"),
                 "acc_target": ("acceleration_target", "ACCELERATION_TARGET"), "kp": ("drive_stiffness", "DRIVE_STIFFNESS"),
-                "kd": ("drive_damping", "DRIVE_DAMPING"), "force_limit": ("drive_force_limit", "DRIVE_FORCE_LIMIT")}
+                "kd": ("drive_damping", "DRIVE_DAMPING"), "force_limit": ("drive_force_limit", "DRIVE_FORCE_LIMIT"),
+                "noload_speed": ("noload_speed", "ACTUATOR_NOLOAD_SPEED"), "feedforward": ("joint_feedforward", "JOINT_FEEDFORWARD")}
 # contact points per env that get solver rows, where the procedural template sets its own capacity
 MAX_POINTS = {"pile12": 72, "quadbox": 40, "humanoid": 48}
 

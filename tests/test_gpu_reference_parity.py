@@ -43,7 +43,11 @@ def test_dynamics_match_the_reference(device, case):
     ref, w, E, L, n, S = make_world(device, case)
     assert RP.err_env(w.download(F.ARTICULATION_LINK_POSE), ref["start_link_pose"].reshape(E, -1)) < 1e-6
     assert np.array_equal(w.download(F.DRIVE_STIFFNESS), ref["start_kp"].reshape(E, L))
+    # the reference's single-op dispatch ran without the drive stage: switch every drive input off
     w.upload(F.DRIVE_STIFFNESS, np.zeros((E, L), np.float32)); w.upload(F.DRIVE_DAMPING, np.zeros((E, L), np.float32))
+    w.upload(F.JOINT_FEEDFORWARD, np.zeros((E, L), np.float32))
+    if RP.CONTROL_MODE.get(case) in (1, 5):       # the target field carries efforts in these modes
+        w.upload(F.DRIVE_TARGET, np.zeros((E, L), np.float32))
     w.run_stage(1)
     assert RP.err_env(w.download(F.MASS_MATRIX), ref["dyn_mass"].reshape(E, -1)) < 1e-5
     ours, theirs, largest = RP.acceleration_errors(ref, w.download(F.JOINT_ACCELERATION), E, L, n)

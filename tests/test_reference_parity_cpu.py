@@ -56,6 +56,7 @@ def test_dynamics_match_the_reference(oracle, case):
     assert RP.err_env(w.get("link_pose", 7 * L), ref["start_link_pose"].reshape(E, -1)) < 1e-6
     # the reference's single-op dispatch ran without the drive stage: compare with the drives switched off
     w.set("drive_stiffness", np.zeros((E, L), np.float32)); w.set("drive_damping", np.zeros((E, L), np.float32))
+    w.set("joint_feedforward", np.zeros((E, L), np.float32))     # enters with the drive stage, which that dispatch skipped
     w.dynamics(False)
     assert RP.err_env(w.get("mass_matrix", n * n), ref["dyn_mass"].reshape(E, -1)) < 1e-5
     bias = ref["dyn_bias"].reshape(E, n)
