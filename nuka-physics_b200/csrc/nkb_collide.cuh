@@ -103,6 +103,15 @@ NKB_DEV void stage_aabbs(Env& e) {
         if (kind == kSphere) he = mk3(p[0], p[0], p[0]);
         else if (kind == kCapsule) he = rot_abs(q, mk3(p[0], p[0], p[0] + p[1]));
         else if (kind == kBox) he = rot_abs(q, mk3(p[0], p[1], p[2]));
+        else if (kind == kCylinder) {
+            // exact: along each world axis hh |a_i| + r sqrt(1 - a_i^2), a the cylinder's axis (ops/broadphase.cu:199-208)
+            const V3 qv = mk3(q.x, q.y, q.z), ez = mk3(0.f, 0.f, 1.f);
+            const V3 tz = cross(qv, ez) * 2.0f;
+            const V3 a = ez + tz * q.w + cross(qv, tz);
+            he = mk3(p[1] * fabsf(a.x) + p[0] * sqrtf(fmaxf(0.0f, 1.0f - a.x * a.x)),
+                     p[1] * fabsf(a.y) + p[0] * sqrtf(fmaxf(0.0f, 1.0f - a.y * a.y)),
+                     p[1] * fabsf(a.z) + p[0] * sqrtf(fmaxf(0.0f, 1.0f - a.z * a.z)));
+        }
         else { out[0] = out[1] = out[2] = FLT_MAX; out[3] = out[4] = out[5] = -FLT_MAX; continue; }
         const float radius = sqrtf(dot(he, he)) + 0.0f;
         const float* bv = sm_bvel(e, b);

@@ -2,6 +2,7 @@
 // the warp's lanes are dealt out accordingly:
 //   round pairs (a sphere or capsule against anything but a box-box / box-plane manifold)   1 lane per pair, registers only
 //   box on plane                                                                              8 lanes per pair, lane = box corner
+//   cylinder on plane                                                                        16 lanes per pair, lane = rim point
 //   box on box                                                                               16 lanes per pair, lane = separating-axis
 //                                                                                            candidate, then lane = polygon vertex
 // Selections that a serial code does with arrays and loops (deepest four corners, farthest-point spread, polygon clipping)
@@ -150,7 +151,7 @@ NKB_DEV void round_pair(uint32_t ka, const BodyFrame& fa, const float* pa, uint3
     out.count = 0u;
     out.key[0] = out.key[1] = 0u;
     // the handlers are written for (first, second) = (sphere|capsule, other); the mirrored orders swap and flip the normal
-    const bool mirrored = (ka == kBox && kb == kSphere) || (ka == kPlane && (kb == kSphere || kb == kCapsule)) || (ka == kSphere && kb == kCapsule);
+    const bool mirrored = (ka == kBox && kb == kSphere) || (ka == kPlane && (kb == kSphere || kb == kCapsule)) || (ka == kSphere && (kb == kCapsule || kb == kCylinder));
     const BodyFrame& f1 = mirrored ? fb : fa;
     const BodyFrame& f2 = mirrored ? fa : fb;
     const float* p1 = mirrored ? pb : pa;
@@ -204,6 +205,30 @@ NKB_DEV void round_pair(uint32_t ka, const BodyFrame& fa, const float* pa, uint3
                 out.pos[0] = to_world(f1, p - n * dist) + out.normal * (0.5f * pen); out.pen[0] = pen; out.count = 1u;
             }
         }
+    } else if (k1 == kCylinder && k2 == kSphere) {
+        if (r1 >= 0.f && p1[1] >= 0.f) {
+            // the sphere centre in the cylinder frame (axis along local z): outside both the side and a cap the rim is nearest,
+            // else whichever of side and cap is closer to the surface; the feature (0 bottom cap, 1 side, 2 top cap, 3 bottom
+            // rim, 4 top rim) is the point's key (collision/primitive_surface.hpp:89-114, analytical_manifold.hpp:818-834)
+            const V3 p = to_local(f1, f2.t);
+            const float rho = sqrtf(p.x * p.x + p.y * p.y);
+            const V3 radial = rho > 0.f ? mk3(p.x / rho, p.y / rho, 0.f) : mk3(1.f, 0.f, 0.f);
+            const V3 axial = mk3(0.f, 0.f, p.z < 0.f ? -1.f : 1.f);
+            const float side = rho - r1, cap = fabsf(p.z) - p1[1];
+            float dist; V3 n; uint32_t feature;
+            if (side > 0.f && cap > 0.f) {
+                dist = sqrtf(side * side + cap * cap);
+                const V3 sum = radial * side + axial * cap;
+                n = mk3(sum.x / dist, sum.y / dist, sum.z / dist);
+                feature = p.z < 0.f ? 3u : 4u;
+            } else if (side > cap) { dist = side; n = radial; feature = 1u; }
+            else { dist = cap; n = axial; feature = p.z < 0.f ? 0u : 2u; }
+            const float pen = p2[0] - dist;
+            if (pen > -query) {
+                out.normal = dir_to_world(f1, n) * -1.0f;
+                out.pos[0] = to_world(f1, p - n * dist) + out.normal * (0.5f * pen); out.pen[0] = pen; out.key[0] = feature; out.count = 1u;
+            }
+        }
     } else if (k1 == kCapsule && k2 == kCapsule) {
         V3 c1, c2;
         const float d2 = segment_closest(f1.t + f1.cz * p1[1], f1.t - f1.cz * p1[1], f2.t + f2.cz * p2[1], f2.t - f2.cz * p2[1], c1, c2);
@@ -218,14 +243,17 @@ NKB_DEV void round_pair(uint32_t ka, const BodyFrame& fa, const float* pa, uint3
     // a capsule end key of 0 is "no stable feature" like every other single point: only end 1 carries one
 }
 
-enum PairClass : uint32_t { kClassNone = 0u, kClassRound = 1u, kClassBoxPlane = 2u, kClassBoxBox = 3u };
+enum PairClass : uint32_t { kClassNone = 0u, kClassRound = 1u, kClassBoxPlane = 2u, kClassBoxBox = 3u, kClassCylinderPlane = 4u };
 NKB_DEV uint32_t pair_class(uint32_t ka, uint32_t kb) {
     if (ka == kBox && kb == kBox) return kClassBoxBox;
+    if ((ka == kCylinder && kb == kPlane) || (ka == kPlane && kb == kCylinder)) return kClassCylinderPlane;
+    if ((ka == kCylinder && kb == kSphere) || (ka == kSphere && kb == kCylinder)) return kClassRound;
+    if (ka == kCylinder || kb == kCylinder) return kClassNone;
     if ((ka == kBox && kb == kPlane) || (ka == kPlane && kb == kBox)) return kClassBoxPlane;
     const bool round_a = ka == kSphere || ka == kCapsule, round_b = kb == kSphere || kb == kCapsule;
     if ((round_a && (round_b || kb == kPlane)) || (round_b && ka == kPlane)) return kClassRound;
     if ((ka == kSphere && kb == kBox) || (ka == kBox && kb == kSphere)) return kClassRound;
-    return kClassNone;          // capsule-box and plane-plane have no analytic manifold; the template check rejects them
+    return kClassNone;          // capsule-box, plane-plane and cylinders against boxes, capsules or cylinders have no analytic manifold; the template check rejects them
 }
 
 // The lowest `want` set bits of `mask`: lane index of the g-th (g < want), or 32.
@@ -258,6 +286,72 @@ static __device__ __noinline__ void box_plane_group(PairCtx c, bool active, uint
     const uint32_t kept_mask = (__ballot_sync(NKB_FULL, kept) >> gbase) & 0xffu;
     if (kept) write_point(c, slot, __popc(kept_mask & ((1u << corner) - 1u)), a, b, cw - n * (0.5f * sd), box_first ? n : -n, pen, corner);
     if (active && corner == 0u) ctx_count(c)[slot] = __popc(kept_mask);
+}
+
+// ---- cylinder on plane: 16 lanes, lane = candidate point in the reference's order (analytical_manifold.hpp:780-816).  A cap
+// ---- that faces the plane (|axis . n| >= 0.95) contributes its deepest rim point and the eight points of its octagon
+// ---- (lanes 0-8 of the lower cap); otherwise each cap contributes its deepest rim point (lanes 0, 1).  Up to four survive:
+// ---- all of them when at most four touch, else the deepest and then three times the one farthest from those kept (lowest
+// ---- lane on ties); they come out in feature order, which is lane order. ----
+static __device__ __noinline__ void cylinder_plane_group(PairCtx c, bool active, uint32_t slot, uint32_t a, uint32_t b, bool cylinder_first, float query) {
+    const uint32_t lane = c.lane, r = lane & 15u, gbase = lane & ~15u;
+    const uint32_t cyl = cylinder_first ? a : b, plane = cylinder_first ? b : a;
+    const BodyFrame fc = load_frame(c, cyl), fp = load_frame(c, plane);
+    const float* sp = ctx_shape(c, cyl);
+    const float radius = sp[0], half = sp[1];
+    const V3 n = unit_or(fp.cz, mk3(0.f, 0.f, 1.f));
+    const V3 axis = fc.cz;
+    const float d = dot(axis, n);
+    const bool on_cap = (d < 0.f ? -d : d) >= 0.95f;
+    const V3 down = unit_or(axis * d - n, fc.cx);
+    // lane -> (cap, rim step): the cap whose outward axis points against the plane normal carries the disk
+    const int cap = on_cap ? (d > 0.f ? 1 : 0) : (int)(r & 1u);
+    const int k = on_cap ? (int)r - 1 : -1;
+    const bool exists = on_cap ? r < 9u : r < 2u;
+    const float kS = 0.70710678f;
+    const int kc = k & 7, ks = (k + 6) & 7;          // sin(k 45 deg) = cos((k - 2) 45 deg)
+    auto octant_cos = [&](int i) { return i == 0 ? 1.0f : ((i == 1 || i == 7) ? kS : ((i == 2 || i == 6) ? 0.0f : ((i == 3 || i == 5) ? -kS : -1.0f))); };
+    const V3 rim = fc.cx * octant_cos(kc) + fc.cy * octant_cos(ks);
+    const V3 centre = fc.t + axis * (cap == 0 ? half : -half);
+    const V3 p = centre + (k < 0 ? down : rim) * radius;
+    const float sd = dot(p - fp.t, n);
+    const bool touching = active && exists && sd < query;
+    const float pen = -sd;
+    const V3 pos = p - n * (sd * 0.5f);
+    const uint32_t feature = k < 0 ? (uint32_t)cap : (uint32_t)(2 + cap * 8 + k);
+    const uint32_t cand_mask = (__ballot_sync(NKB_FULL, touching) >> gbase) & 0xffffu;
+    const uint32_t n_cand = __popc(cand_mask);
+    uint32_t kept_mask = cand_mask;
+    {
+        float seed_pen = -3.4e38f;
+        int seed = -1;
+#pragma unroll
+        for (int i = 0; i < 9; ++i) {
+            const float pi = __shfl_sync(NKB_FULL, pen, gbase + i);
+            if (((cand_mask >> i) & 1u) != 0u && (seed < 0 || pi > seed_pen)) { seed_pen = pi; seed = i; }
+        }
+        uint32_t spread = seed >= 0 ? 1u << seed : 0u;
+        float nearest = 3.4e38f;
+        int last = seed < 0 ? 0 : seed;
+#pragma unroll 1
+        for (int round = 1; round < 4; ++round) {
+            const V3 K = mk3(__shfl_sync(NKB_FULL, pos.x, gbase + last), __shfl_sync(NKB_FULL, pos.y, gbase + last), __shfl_sync(NKB_FULL, pos.z, gbase + last));
+            const V3 gap = pos - K;
+            nearest = fminf(nearest, dot(gap, gap));
+            float far = -1.0f;
+            int pick = -1;
+#pragma unroll
+            for (int i = 0; i < 9; ++i) {
+                const float mi = __shfl_sync(NKB_FULL, nearest, gbase + i);
+                if (((cand_mask >> i) & 1u) != 0u && ((spread >> i) & 1u) == 0u && mi > far) { far = mi; pick = i; }
+            }
+            if (pick >= 0) { spread |= 1u << pick; last = pick; }
+        }
+        if (n_cand > 4u) kept_mask = spread;
+    }
+    if (touching && ((kept_mask >> r) & 1u) != 0u)
+        write_point(c, slot, __popc(kept_mask & ((1u << r) - 1u)), a, b, pos, cylinder_first ? n : -n, pen, feature);
+    if (active && r == 0u) ctx_count(c)[slot] = n_cand < 4u ? n_cand : 4u;
 }
 
 // ---- box on box: 16 lanes ----
@@ -475,7 +569,7 @@ NKB_DEV void narrowphase_range(Env& e, uint32_t pair_count, uint32_t first, uint
             cls = pair_class(ka, kb);
             query = fmaxf(separation, fminf(motion_radius(2.0f * separation, t.cfg.dt, body_speed(e, a), body_speed(e, b)), reach));
         }
-        if (s < S && cls != kClassBoxPlane && cls != kClassBoxBox) {
+        if (s < S && cls != kClassBoxPlane && cls != kClassBoxBox && cls != kClassCylinderPlane) {
             uint32_t count = 0u;
             if (cls == kClassRound) {
                 RoundPoints pts;
@@ -495,6 +589,16 @@ NKB_DEV void narrowphase_range(Env& e, uint32_t pair_count, uint32_t first, uint
             const float gq = __shfl_sync(NKB_FULL, query, src);
             box_plane_group(c, active, base + src, ga, gb, gka == kBox, gq);
             for (int k = 0; k < 4 && todo != 0u; ++k) todo &= todo - 1u;
+        }
+        // cylinder on plane: two pairs per pass, sixteen lanes each
+        for (uint32_t todo = __ballot_sync(NKB_FULL, cls == kClassCylinderPlane); todo != 0u;) {
+            const uint32_t owner = nth_set_bit(todo, lane >> 4);
+            const bool active = owner < 32u;
+            const uint32_t src = active ? owner : 0u;
+            const uint32_t ga = __shfl_sync(NKB_FULL, a, src), gb = __shfl_sync(NKB_FULL, b, src), gka = __shfl_sync(NKB_FULL, ka, src);
+            const float gq = __shfl_sync(NKB_FULL, query, src);
+            cylinder_plane_group(c, active, base + src, ga, gb, gka == kCylinder, gq);
+            for (int k = 0; k < 2 && todo != 0u; ++k) todo &= todo - 1u;
         }
         // box on box: two pairs per pass, sixteen lanes each
         for (uint32_t todo = __ballot_sync(NKB_FULL, cls == kClassBoxBox); todo != 0u;) {

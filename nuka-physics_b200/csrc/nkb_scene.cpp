@@ -21,7 +21,7 @@ namespace {
 
 constexpr int kInvalidArg = 1, kParseError = 5, kNotSupported = 7;
 constexpr uint32_t kRevolute = 0, kPrismatic = 1, kFixed = 2, kFloating = 3;
-constexpr uint32_t kSphere = 0, kCapsule = 1, kBox = 2, kPlane = 3;
+constexpr uint32_t kSphere = 0, kCapsule = 1, kBox = 2, kPlane = 3, kCylinder = 7;
 constexpr uint32_t kNoLink = 0xffffffffu;
 
 // ---- a small JSON reader: objects keep their members in document order ----------------------------------------------------
@@ -221,6 +221,7 @@ Shape ShapeOf(const Json& cs) {
     Shape s;
     if (kind == "sphere") { s.kind = kSphere; s.params[0] = cs.Number("radius", 0.0); return s; }
     if (kind == "capsule") { s.kind = kCapsule; s.params[0] = cs.Number("radius", 0.0); s.params[1] = cs.Number("half_height", 0.0); return s; }
+    if (kind == "cylinder") { s.kind = kCylinder; s.params[0] = cs.Number("radius", 0.0); s.params[1] = cs.Number("half_height", 0.0); return s; }
     if (kind == "box") {
         const Json* he = cs.Find("half_extents");
         if (he == nullptr || he->kind != Json::kArray || he->items.size() != 3) throw Error(kParseError, "box shape without half_extents");

@@ -15,7 +15,7 @@ constexpr uint32_t kMaxBodies = 256u;   // collidable rows per env (the env's sh
 constexpr uint32_t kPtsPerSlot = 4u;
 
 enum JointType : uint32_t { kRevolute = 0, kPrismatic = 1, kFixed = 2, kFloating = 3, kSpherical = 4 };
-enum ShapeKind : uint32_t { kSphere = 0, kCapsule = 1, kBox = 2, kPlane = 3 };
+enum ShapeKind : uint32_t { kSphere = 0, kCapsule = 1, kBox = 2, kPlane = 3, kCylinder = 7 };      // the reference's collision/shape_kind.hpp:10-17
 // env status bits, reference src/phi/op_schema.hpp:36-52
 enum : uint32_t { kStatusPairOverflow = 1u << 0, kStatusDofOverflow = 1u << 2, kStatusGyroFailure = 1u << 5,
                   kStatusControlFailure = 1u << 10, kStatusSolverFailure = 1u << 13,

@@ -223,7 +223,7 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
                 for (int k = 0; k < 4; ++k) t.body_geom_quat[4u * b + k] = t.geom_quat[4u * l + k];
             }
         }
-        if (t.shape_kind[b] > kPlane) throw Error(kNotSupported, "shape kind without an analytic manifold");
+        if (t.shape_kind[b] > kPlane && t.shape_kind[b] != kCylinder) throw Error(kNotSupported, "shape kind without an analytic manifold");
         if (t.body_geom_kind[b] > 1u) throw Error(kParseError, "body_geom_kind must be 0 or 1");
     }
     t.adm_mask.assign(std::max<size_t>(1, static_cast<size_t>(B) * ((B + 31u) / 32u)), 0u);
@@ -233,8 +233,10 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
         const unsigned long long key = (static_cast<unsigned long long>(a) << 32) | b;
         if (std::binary_search(t.excluded.begin(), t.excluded.end(), key)) continue;
         const uint32_t ka = t.shape_kind[a], kb = t.shape_kind[b];
-        const bool analytic = !((ka == kCapsule && kb == kBox) || (ka == kBox && kb == kCapsule) || (ka == kPlane && kb == kPlane));
-        if (!analytic) throw Error(kNotSupported, "capsule-box pairs need the convex narrowphase, which this path does not provide");
+        // analytic manifolds exist for a cylinder against a plane or a sphere only (analytical_manifold.hpp:948-949)
+        const bool cylinder_other = (ka == kCylinder && kb != kPlane && kb != kSphere) || (kb == kCylinder && ka != kPlane && ka != kSphere);
+        const bool analytic = !((ka == kCapsule && kb == kBox) || (ka == kBox && kb == kCapsule) || (ka == kPlane && kb == kPlane) || cylinder_other);
+        if (!analytic) throw Error(kNotSupported, "capsule-box pairs and cylinders against anything but planes and spheres need the convex narrowphase, which this path does not provide");
         t.adm_pairs.push_back((a << 16) | b);
         t.adm_mask[a * ((B + 31u) / 32u) + (b >> 5)] |= 1u << (b & 31u);
     }
@@ -291,7 +293,7 @@ void World::BuildLayout() {
         if (!(t.adm_pairs.size() == 1 && t.adm_pairs[0] == 0u))
             for (uint32_t key : t.adm_pairs) {
                 const uint32_t ka = t.shape_kind[key >> 16], kb = t.shape_kind[key & 0xffffu];
-                caps.push_back((ka == kSphere || kb == kSphere) ? 1u : (ka == kCapsule || kb == kCapsule) ? 2u : 4u);
+                caps.push_back((ka == kSphere || kb == kSphere) ? 1u : (ka == kCapsule || kb == kCapsule) ? 2u : 4u);      // a cylinder on a plane: up to 4
             }
         std::sort(caps.begin(), caps.end(), [](uint32_t a, uint32_t b) { return a > b; });
         uint32_t total = 0;

@@ -49,6 +49,8 @@ def _shape_of(cs):
         return (T.CAPSULE, float(cs["radius"]), float(cs["half_height"]))
     if kind == "box":
         return (T.BOX, *(float(v) for v in cs["half_extents"]))
+    if kind == "cylinder":          # flat caps along local z; analytic manifolds against planes and spheres only
+        return (T.CYLINDER, float(cs["radius"]), float(cs["half_height"]))
     raise ValueError(f"collision shape type {kind!r} has no analytic manifold here")
 
 
@@ -277,10 +279,11 @@ def scene_from_builder(tb):
     def shape_node(b, name):
         kind = b["kind"]
         p = b["params"]
-        cs = {"type": {T.SPHERE: "sphere", T.CAPSULE: "capsule", T.BOX: "box", T.PLANE: "plane"}[kind],
+        cs = {"type": {T.SPHERE: "sphere", T.CAPSULE: "capsule", T.BOX: "box", T.PLANE: "plane", T.CYLINDER: "cylinder"}[kind],
               "local": _frame(b.get("geom_pos", (0, 0, 0)), b.get("geom_quat", (1, 0, 0, 0))),
               "half_extents": [float(p[0]), float(p[1]), float(p[2])] if kind == T.BOX else [0.5, 0.5, 0.5],
-              "radius": float(p[0]) if kind in (T.SPHERE, T.CAPSULE) else 0.5, "half_height": float(p[1]) if kind == T.CAPSULE else 0.5,
+              "radius": float(p[0]) if kind in (T.SPHERE, T.CAPSULE, T.CYLINDER) else 0.5,
+              "half_height": float(p[1]) if kind in (T.CAPSULE, T.CYLINDER) else 0.5,
               "contype": int(b["contype"]), "conaffinity": int(b["conaffinity"]), "collision_group": int(b["group"]),
               "friction_mu": float(b["mu"]), "condim": 3, "margin": 0.0, "gap": 0.0}
         return {"name": name, "collision_shape": cs}

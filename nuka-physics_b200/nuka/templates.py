@@ -15,7 +15,7 @@ import numpy as np
 from . import nkt
 
 REVOLUTE, PRISMATIC, FIXED, FLOATING = 0, 1, 2, 3
-SPHERE, CAPSULE, BOX, PLANE = 0, 1, 2, 3
+SPHERE, CAPSULE, BOX, PLANE, CYLINDER = 0, 1, 2, 3, 7          # the reference's collision/shape_kind.hpp:10-17
 NOLINK = 0xFFFFFFFF
 FLT_BIG = 3.0e38
 

@@ -35,7 +35,7 @@ extern "C" {
 enum { ORC_JOINT_REVOLUTE = 0, ORC_JOINT_PRISMATIC = 1, ORC_JOINT_FIXED = 2,
        ORC_JOINT_FLOATING = 3, ORC_JOINT_SPHERICAL = 4 };
 /* reference src/collision/shape_kind.hpp:10-19 */
-enum { ORC_SHAPE_SPHERE = 0, ORC_SHAPE_CAPSULE = 1, ORC_SHAPE_BOX = 2, ORC_SHAPE_PLANE = 3 };
+enum { ORC_SHAPE_SPHERE = 0, ORC_SHAPE_CAPSULE = 1, ORC_SHAPE_BOX = 2, ORC_SHAPE_PLANE = 3, ORC_SHAPE_CYLINDER = 7 };
 /* reference src/phi/op_schema.hpp:36-52 */
 enum { ORC_STATUS_PAIR_OVERFLOW = 1u << 0, ORC_STATUS_DOF_OVERFLOW = 1u << 2,
        ORC_STATUS_GYRO_FAILURE = 1u << 5, ORC_STATUS_CONTROL_FAILURE = 1u << 10,

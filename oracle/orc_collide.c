@@ -47,6 +47,15 @@ void orc_build_aabbs(const orc_model *m, orc_env *e) {
             case ORC_SHAPE_SPHERE: he = V3(p[0], p[0], p[0]); break;
             case ORC_SHAPE_CAPSULE: he = rot_abs(q, V3(p[0], p[0], p[0] + p[1])); break;
             case ORC_SHAPE_BOX: he = rot_abs(q, V3(p[0], p[1], p[2])); break;
+            case ORC_SHAPE_CYLINDER: {      /* broadphase.cu:199-208: per world axis hh |a_i| + r sqrt(1 - a_i^2), a the cylinder's axis */
+                const v3 qv = V3(q.x, q.y, q.z), ez = V3(0, 0, 1);
+                const v3 tz = vscale(vcross(qv, ez), 2.0f);
+                const v3 a = vadd(vadd(ez, vscale(tz, q.w)), vcross(qv, tz));
+                he = V3(p[1] * fabsf(a.x) + p[0] * sqrtf(fmaxf(0.0f, 1.0f - a.x * a.x)),
+                        p[1] * fabsf(a.y) + p[0] * sqrtf(fmaxf(0.0f, 1.0f - a.y * a.y)),
+                        p[1] * fabsf(a.z) + p[0] * sqrtf(fmaxf(0.0f, 1.0f - a.z * a.z)));
+                break;
+            }
             case ORC_SHAPE_PLANE:
                 v3st(e->aabb_lo + 3 * b, V3(-FLT_MAX, -FLT_MAX, -FLT_MAX));
                 v3st(e->aabb_hi + 3 * b, V3(FLT_MAX, FLT_MAX, FLT_MAX));
@@ -273,6 +282,56 @@ static void capsule_sphere(const prim *cap, const prim *s, manifold *o, float qu
     v3 nw = vscale(f_dir(&cap->f, n), -1.0f);
     add_pt(o, vadd(f_l2w(&cap->f, pt), vscale(nw, 0.5f * pen)), nw, pen, 0);
 }
+/* primitive_surface.hpp:89-114 cylinder branch: features 0 bottom cap, 1 side, 2 top cap, 3 bottom rim, 4 top rim */
+static int surface_cylinder(float r, float hh, v3 p, float *dist, v3 *normal, v3 *point, uint32_t *feature) {
+    if (!(r >= 0.0f && hh >= 0.0f)) return 0;
+    const float rho = sqrtf(p.x * p.x + p.y * p.y);
+    const v3 radial = rho > 0.0f ? V3(p.x / rho, p.y / rho, 0.0f) : V3(1.0f, 0.0f, 0.0f);
+    const v3 axial = V3(0.0f, 0.0f, p.z < 0.0f ? -1.0f : 1.0f);
+    const float side = rho - r, cap = fabsf(p.z) - hh;
+    if (side > 0.0f && cap > 0.0f) {
+        *dist = sqrtf(side * side + cap * cap);
+        const v3 sum = vadd(vscale(radial, side), vscale(axial, cap));
+        *normal = V3(sum.x / *dist, sum.y / *dist, sum.z / *dist);
+        *feature = p.z < 0.0f ? 3u : 4u;
+    } else if (side > cap) { *dist = side; *normal = radial; *feature = 1u; }
+    else { *dist = cap; *normal = axial; *feature = p.z < 0.0f ? 0u : 2u; }
+    *point = vsub(p, vscale(*normal, *dist));
+    return 1;
+}
+/* analytical_manifold.hpp:780-816: the lower cap's octagon and deepest point when a cap faces the plane, else each cap's
+ * deepest rim point */
+static void cylinder_plane(const prim *cyl, const prim *pl, manifold *o, float query) {
+    static const float kc[8] = {1.0f, 0.70710678f, 0.0f, -0.70710678f, -1.0f, -0.70710678f, 0.0f, 0.70710678f};
+    static const float ks[8] = {0.0f, 0.70710678f, 1.0f, 0.70710678f, 0.0f, -0.70710678f, -1.0f, -0.70710678f};
+    const v3 n = norm_or(pl->f.cz, V3(0, 0, 1));
+    const v3 axis = cyl->f.cz;
+    const float d = vdot(axis, n);
+    const int on_cap = (d < 0.0f ? -d : d) >= 0.95f;
+    const v3 down = norm_or(vsub(vscale(axis, d), n), cyl->f.cx);
+    cand c[10]; int nc = 0;
+    for (int cap = 0; cap < 2; ++cap) {
+        if (on_cap && (cap == 0) == (d > 0.0f)) continue;
+        const v3 center = vadd(cyl->f.t, vscale(axis, cap == 0 ? cyl->hh : -cyl->hh));
+        for (int k = -1; k < (on_cap ? 8 : 0); ++k) {
+            const v3 dir = k < 0 ? down : vadd(vscale(cyl->f.cx, kc[k]), vscale(cyl->f.cy, ks[k]));
+            const v3 p = vadd(center, vscale(dir, cyl->radius));
+            const float sd = vdot(vsub(p, pl->f.t), n);
+            if (sd >= query) continue;
+            c[nc].pos = vsub(p, vscale(n, sd * 0.5f)); c[nc].pen = -sd; c[nc].feat = (uint32_t)(k < 0 ? cap : 2 + cap * 8 + k); ++nc;
+        }
+    }
+    reduce_emit_spread(c, nc, n, o);
+}
+/* analytical_manifold.hpp:818-834 */
+static void cylinder_sphere(const prim *cyl, const prim *s, manifold *o, float query) {
+    float dist; v3 n, pt; uint32_t feature;
+    if (!surface_cylinder(cyl->radius, cyl->hh, f_w2l(&cyl->f, s->f.t), &dist, &n, &pt, &feature)) return;
+    float pen = s->radius - dist;
+    if (pen <= -query) return;
+    v3 nw = vscale(f_dir(&cyl->f, n), -1.0f);
+    add_pt(o, vadd(f_l2w(&cyl->f, pt), vscale(nw, 0.5f * pen)), nw, pen, feature);
+}
 /* analytical_manifold.hpp:841-896 */
 static float closest_seg_seg(v3 p1, v3 q1, v3 p2, v3 q2, v3 *c1, v3 *c2) {
     v3 d1 = vsub(q1, p1), d2 = vsub(q2, p2), r = vsub(p1, p2);
@@ -426,12 +485,16 @@ static int primitive_pair(uint32_t ka, const prim *a, uint32_t kb, const prim *b
     if (ka == ORC_SHAPE_CAPSULE && kb == ORC_SHAPE_PLANE) { capsule_plane(a, b, o, query); return 1; }
     if (ka == ORC_SHAPE_CAPSULE && kb == ORC_SHAPE_SPHERE) { capsule_sphere(a, b, o, query); return 1; }
     if (ka == ORC_SHAPE_CAPSULE && kb == ORC_SHAPE_CAPSULE) { capsule_capsule(a, b, o, query); return 1; }
+    if (ka == ORC_SHAPE_CYLINDER && kb == ORC_SHAPE_PLANE) { cylinder_plane(a, b, o, query); return 1; }
+    if (ka == ORC_SHAPE_CYLINDER && kb == ORC_SHAPE_SPHERE) { cylinder_sphere(a, b, o, query); return 1; }
     int done = 1;
     if (ka == ORC_SHAPE_BOX && kb == ORC_SHAPE_SPHERE) sphere_box(b, a, o, query);
     else if (ka == ORC_SHAPE_PLANE && kb == ORC_SHAPE_SPHERE) sphere_plane(b, a, o, query);
     else if (ka == ORC_SHAPE_PLANE && kb == ORC_SHAPE_BOX) box_plane(b, a, o, query);
     else if (ka == ORC_SHAPE_PLANE && kb == ORC_SHAPE_CAPSULE) capsule_plane(b, a, o, query);
     else if (ka == ORC_SHAPE_SPHERE && kb == ORC_SHAPE_CAPSULE) capsule_sphere(b, a, o, query);
+    else if (ka == ORC_SHAPE_PLANE && kb == ORC_SHAPE_CYLINDER) cylinder_plane(b, a, o, query);
+    else if (ka == ORC_SHAPE_SPHERE && kb == ORC_SHAPE_CYLINDER) cylinder_sphere(b, a, o, query);
     else done = 0;
     if (done) for (uint32_t i = 0; i < o->count; ++i) o->p[i].n = vneg(o->p[i].n);
     return done;

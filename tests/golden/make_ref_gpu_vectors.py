@@ -49,6 +49,8 @@ CASES = {
     "quadruped_torque": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_mode_state(1, E), 1.0 / 200.0, 4, 40, 10),
     "quadruped_velocity": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_mode_state(2, E), 1.0 / 200.0, 4, 40, 10),
     "quadruped_actuator": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_mode_state(5, E), 1.0 / 200.0, 4, 40, 10),
+    # free cylinders and spheres over a plane: the cylinder-plane (cap, rim, side) and cylinder-sphere manifolds
+    "cylinders": (lambda: ref_cases.cylinder_field(), lambda E: ref_cases.cylinder_field_state(E), 1.0 / 250.0, 8, 80, 20),
     # seeded random articulations (random trees, revolute / prismatic / fixed joints, limits, dry friction, armature,
     # spheres with boxes or capsules, free bodies): parity beyond the benchmark robots
     **{f"random{k}": (lambda k=k: ref_cases.random_robot(k), lambda E, k=k: ref_cases.random_robot_state(k, E), 1.0 / 250.0, 6, 60, 20)
@@ -114,7 +116,7 @@ def prepare():
 KEEP = ("run", "run_dt", "dyn_qddot", "dyn_mass", "dyn_bias", "start_link_pose", "start_kp", "start_kd", "start_force_limit",
         "start_drive_target", "traj_steps", "traj_q", "traj_qdot", "traj_base_pose", "traj_status", "traj_status_any",
         "traj_solver_sweeps", "traj_solver_residual", "traj_pair_count", "traj_candidate_pairs", "traj_contact_count")
-FREE_BODY_CASES = ("pile12", "quadbox", "random0", "random1", "random3", "random7")     # body poses are kept where free bodies carry state of their own
+FREE_BODY_CASES = ("pile12", "quadbox", "cylinders", "random0", "random1", "random3", "random7")     # body poses are kept where free bodies carry state of their own
 
 
 def collect(src):

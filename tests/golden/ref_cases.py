@@ -3,9 +3,10 @@ restatement: analytic contact pairs and augmented-Lagrangian row laws.  Shared b
 tests/golden/make_ref_vectors.py so that the live comparison and the committed vectors see the same cases."""
 import numpy as np
 
-SPHERE, CAPSULE, BOX, PLANE = 0, 1, 2, 3
+SPHERE, CAPSULE, BOX, PLANE, CYLINDER = 0, 1, 2, 3, 7
 PAIR_KINDS = [(SPHERE, SPHERE), (SPHERE, BOX), (BOX, SPHERE), (SPHERE, PLANE), (PLANE, SPHERE), (BOX, PLANE), (PLANE, BOX),
-              (BOX, BOX), (CAPSULE, PLANE), (PLANE, CAPSULE), (CAPSULE, SPHERE), (SPHERE, CAPSULE), (CAPSULE, CAPSULE)]
+              (BOX, BOX), (CAPSULE, PLANE), (PLANE, CAPSULE), (CAPSULE, SPHERE), (SPHERE, CAPSULE), (CAPSULE, CAPSULE),
+              (CYLINDER, PLANE), (PLANE, CYLINDER), (CYLINDER, SPHERE), (SPHERE, CYLINDER)]
 
 
 def _frames(quat, pos):
@@ -36,6 +37,8 @@ def _params(rng, kind, n):
         p[:, 0] = rng.uniform(0.02, 0.4, n)
     elif kind == CAPSULE:
         p[:, 0] = rng.uniform(0.02, 0.2, n); p[:, 1] = rng.uniform(0.05, 0.5, n); p[:, 2] = p[:, 0]
+    elif kind == CYLINDER:      # radius, half height; wheels (flat) and posts (long) alike
+        p[:, 0] = rng.uniform(0.02, 0.3, n); p[:, 1] = rng.uniform(0.01, 0.4, n)
     elif kind == BOX:
         p[:, :3] = rng.uniform(0.02, 0.4, (n, 3))
         cube = rng.random(n) < 0.2
@@ -215,6 +218,57 @@ def quadruped_mode_state(mode, env_count, seed=0):
     else:
         raise ValueError(mode)
     return out
+
+
+def cylinder_field():
+    """Free cylinders and spheres over a plane, for the cylinder manifolds: six cylinders (pucks, posts, wheels on their
+    side) in random orientations a few centimetres above the ground, and six spheres dropped onto and beside them.  Filters
+    keep the pairs to those with an analytic manifold: cylinders meet the plane and the spheres, never each other.
+    Returns the TemplateBuilder cooked through the scene round trip."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "nuka-physics_b200"))
+    from nuka import templates as T
+    from nuka import nks
+    rng = np.random.Generator(np.random.PCG64(5000))
+    tb = T.TemplateBuilder(dt=1.0 / 250.0, vel_iters=8, max_contacts=0)
+    for k in range(6):
+        radius, half = float(rng.uniform(0.04, 0.1)), float(rng.uniform(0.015, 0.08))
+        mass = float(1200.0 * np.pi * radius * radius * 2.0 * half)
+        side = mass * (3.0 * radius * radius + 4.0 * half * half) / 12.0
+        tb.add_free_body((T.CYLINDER, radius, half), mass, (float(side), float(side), float(0.5 * mass * radius * radius)),
+                         (0.3 * (k % 3 - 1), 0.3 * (k // 3) - 0.15, 0.14, 1.0, 0.0, 0.0, 0.0), mu=0.7, contype=4, conaffinity=2)
+    for k in range(6):
+        radius = float(rng.uniform(0.03, 0.06))
+        mass = float(1000.0 * 4.0 / 3.0 * np.pi * radius ** 3)
+        tb.add_free_body((T.SPHERE, radius), mass, (float(0.4 * mass * radius * radius),) * 3,
+                         (0.3 * (k % 3 - 1), 0.3 * (k // 3) - 0.15, 0.36, 1.0, 0.0, 0.0, 0.0), mu=0.6, contype=1, conaffinity=7)
+    tb.add_plane(0.0, mu=0.9, contype=2, conaffinity=1)
+    return nks.cook(nks.scene_from_builder(tb), dt=1.0 / 250.0, vel_iters=8, kp=0.0, kd=0.0, scene_filters=True, ground_height=None,
+                    max_contacts=48)
+
+
+def cylinder_field_state(env_count, seed=0):
+    """Per-env start of cylinder_field(): every cylinder in its own random orientation (a third of them exactly upright or
+    exactly on their side: cap and rim contacts, and the switch between them at |axis . normal| = 0.95), the spheres
+    scattered above them within a cylinder radius."""
+    tb = cylinder_field()
+    a = tb.arrays()
+    B = len(tb.bodies)
+    rng = np.random.Generator(np.random.PCG64(5001 + seed))
+    pose = np.tile(a["body_pose0"].reshape(1, B, 7), (env_count, 1, 1)).astype(np.float32)
+    cyl = a["shape_kind"] == 7
+    sph = a["shape_kind"] == 0
+    quat = rng.normal(size=(env_count, int(cyl.sum()), 4))
+    quat /= np.linalg.norm(quat, axis=-1, keepdims=True)
+    exact = np.array([[1.0, 0.0, 0.0, 0.0], [np.sqrt(0.5), np.sqrt(0.5), 0.0, 0.0], [np.sqrt(0.5), 0.0, np.sqrt(0.5), 0.0]])
+    pick = rng.random((env_count, int(cyl.sum()))) < 0.33
+    quat[pick] = exact[rng.integers(0, 3, int(pick.sum()))]
+    pose[:, cyl, 3:] = quat.astype(np.float32)
+    pose[:, cyl, 2] += rng.uniform(-0.02, 0.04, size=(env_count, int(cyl.sum()))).astype(np.float32)
+    pose[:, sph, :2] += rng.uniform(-0.07, 0.07, size=(env_count, int(sph.sum()), 2)).astype(np.float32)
+    pose[:, sph, 2] += rng.uniform(-0.05, 0.1, size=(env_count, int(sph.sum()))).astype(np.float32)
+    return {"body_pose": pose.reshape(env_count, -1)}
 
 
 def random_robot(seed):

@@ -27,6 +27,7 @@ CASES = {
     "arm7_ct": ("arm7", lambda E: ref_cases.arm_computed_torque_state(E, 0)),
     "quadruped_ct": ("quadruped", lambda E: ref_cases.quadruped_computed_torque_state(E, 0)),
 }
+CASES["cylinders"] = ("cylinders", lambda E: ref_cases.cylinder_field_state(E))
 CASES.update({f"quadruped_{name}": ("quadruped", lambda E, mode=mode: ref_cases.quadruped_mode_state(mode, E))
               for name, mode in (("torque", 1), ("velocity", 2), ("actuator", 5))})
 CASES.update({f"random{k}": (f"random{k}", lambda E, k=k: ref_cases.random_robot_state(k, E)) for k in (0, 1, 3, 7)})
@@ -97,8 +98,15 @@ CHAOTIC = ("pile12", "humanoid")
 #    decrement force * step underflows to zero: the block reports FLT_MAX and the env stops sweeping for that step
 #    (ops/block_descent_tile.cuh:2211-2258, 3068).  Here too the two sides can fall on different sides of the underflow.
 # The comparable envs are held to the bars of the chaotic cases up to step 40.
-SENSITIVE = ("random0", "random3", "random7")
-SENSITIVE_LAST_STEP = 40
+# `cylinders` (free cylinders and spheres dropping onto a plane and each other) has free bodies at rest like the random
+# robots and a discontinuity of its own: for a cylinder whose cap faces the plane the reference adds the rim point
+# "deepest along the plane normal", in the direction normalize(axis (axis . n) - n) (analytical_manifold.hpp:799).  For a
+# cylinder lying flat to within 1e-6 rad that vector is 1e-7 long and made of the quaternion's normalisation error, so
+# the direction points anywhere, sometimes centimetres below the plane, and the push-out kicks the body (seen in the
+# reference's own output: one of four cap points at +1.1 cm while the other three rest at -1e-5).  Which step and env that
+# happens in depends on the last bit of the pose.  The case is compared through the landing and toppling, up to step 40;
+# at step 60 a 1-ulp change of the start heights moves this repository's own result by 2e-3 in 10 % of the envs.
+SENSITIVE = {"random0": 40, "random3": 40, "random7": 40, "cylinders": 40}       # case -> last compared step
 GYRO_BIT = 32
 
 

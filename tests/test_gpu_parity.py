@@ -507,3 +507,76 @@ def test_joint_limit_multipliers_carry_over(device, oracle):
     w.reset()
     assert not w.download(F.JOINT_LIMIT_IMPULSE).any()
     w.destroy()
+
+
+def test_cylinder_manifolds_match_the_oracle(device, oracle):
+    """Free cylinders and spheres over a plane (cylinder-plane with cap, rim and side contacts, cylinder-sphere in both
+    slot orders, the mirrored ones in a second small scene).  One collide pass on the seeded poses, lowered so that most shapes touch: pair lists and contact counts
+    bit-exact, points, normals and depths within 1e-5.  Then 30 steps: counts equal and poses within 1e-4."""
+    import sys
+    sys.path.insert(0, GOLDEN)
+    import ref_cases
+    E = 128
+    tb = ref_cases.cylinder_field()
+    B = len(tb.bodies)
+    pose = ref_cases.cylinder_field_state(E)["body_pose"].reshape(E, B, 7).copy()
+    kinds = tb.arrays()["shape_kind"]
+    lowered = pose.copy()
+    lowered[:, kinds == 7, 2] -= 0.08          # cylinders into the ground by up to their radius
+    lowered[:, kinds == 0, 2] = 0.16           # spheres down onto them
+    w, o = make_pair(device, oracle, tb, E, {"body_pose": lowered.reshape(E, -1)})
+    S = w.info.contact_slots_per_env
+    w.run_stage(2); o.collide()
+    pc = w.download(F.PAIR_COUNT)
+    assert np.array_equal(pc, o.get("pair_count", 1))
+    live = np.arange(S)[None, :] < pc
+    gp = w.download(F.CANDIDATE_PAIRS).reshape(E, S, 2)
+    assert np.array_equal(gp[live], o.get("candidate_pairs", 2 * S).reshape(E, S, 2)[live])
+    cc = w.download(F.CONTACT_COUNT)
+    assert np.array_equal(cc[live], o.get("contact_count", S)[live])
+    points = (np.arange(4)[None, None, :] < cc[:, :, None]) & live[:, :, None]
+    seen = set()
+    for env, slot in zip(*np.nonzero((cc > 0) & live)):
+        seen.add((int(kinds[gp[env, slot, 0]]), int(kinds[gp[env, slot, 1]]), int(cc[env, slot])))
+    assert {(7, 3, 1), (7, 3, 2), (7, 3, 4), (7, 0, 1)} <= seen
+    for field, name in ((F.CONTACT_POINT, "contact_point"), (F.CONTACT_NORMAL, "contact_normal")):
+        assert np.abs(w.download(field).reshape(E, S, 4, 3)[points] - o.get(name, 12 * S).reshape(E, S, 4, 3)[points]).max() < 1e-5
+    assert np.abs(w.download(F.CONTACT_DEPTH).reshape(E, S, 4)[points] - o.get("contact_depth", 4 * S).reshape(E, S, 4)[points]).max() < 1e-5
+    w.destroy()
+    w, o = make_pair(device, oracle, tb, E, {"body_pose": pose.reshape(E, -1)})
+    w.step_n(30); o.step(30)
+    assert np.array_equal(w.download(F.CONTACT_COUNT), o.get("contact_count", S))
+    assert rel(w.download(F.RIGID_BODY_TRANSFORM), o.get("body_pose", 7 * B)) < 1e-4
+    w.destroy()
+    # the mirrored slot orders: plane first, then spheres, then cylinders
+    from nuka.templates import CYLINDER, SPHERE, TemplateBuilder
+    mb = TemplateBuilder(dt=1 / 250.0, vel_iters=8, max_contacts=12)
+    mb.add_plane(0.0, mu=0.9, contype=2, conaffinity=1)
+    for k in range(2):
+        mb.add_free_body((SPHERE, 0.05), 0.5, (0.0005,) * 3, (0.3 * k, 0.0, 0.15, 1, 0, 0, 0), mu=0.6, contype=1, conaffinity=7)
+    for k in range(2):
+        mb.add_free_body((CYLINDER, 0.08, 0.03), 0.7, (0.0013, 0.0013, 0.0022), (0.3 * k, 0.0, 0.02, 1, 0, 0, 0), mu=0.7, contype=4, conaffinity=2)
+    rng = np.random.Generator(np.random.PCG64(11))
+    mp = np.tile(mb.arrays()["body_pose0"].reshape(1, 5, 7), (E, 1, 1)).astype(np.float32)
+    quat = rng.normal(size=(E, 2, 4)); quat /= np.linalg.norm(quat, axis=-1, keepdims=True)
+    quat[: E // 4] = (1.0, 0.0, 0.0, 0.0)                       # a quarter flat on their caps
+    mp[:, 3:, 3:] = quat
+    mp[:, 1:3, :2] += rng.uniform(-0.08, 0.08, size=(E, 2, 2)).astype(np.float32)
+    mp[:, 1:3, 2] += rng.uniform(-0.08, 0.0, size=(E, 2)).astype(np.float32)
+    w, o = make_pair(device, oracle, mb, E, {"body_pose": mp.reshape(E, -1)})
+    S = w.info.contact_slots_per_env
+    w.run_stage(2); o.collide()
+    pc = w.download(F.PAIR_COUNT)
+    assert np.array_equal(pc, o.get("pair_count", 1))
+    live = np.arange(S)[None, :] < pc
+    gp = w.download(F.CANDIDATE_PAIRS).reshape(E, S, 2)
+    cc = w.download(F.CONTACT_COUNT)
+    assert np.array_equal(cc[live], o.get("contact_count", S)[live])
+    points = (np.arange(4)[None, None, :] < cc[:, :, None]) & live[:, :, None]
+    mk = mb.arrays()["shape_kind"]
+    seen = {(int(mk[gp[env, slot, 0]]), int(mk[gp[env, slot, 1]])) for env, slot in zip(*np.nonzero((cc > 0) & live))}
+    assert {(3, 7), (0, 7)} <= seen
+    for field, name in ((F.CONTACT_POINT, "contact_point"), (F.CONTACT_NORMAL, "contact_normal")):
+        assert np.abs(w.download(field).reshape(E, S, 4, 3)[points] - o.get(name, 12 * S).reshape(E, S, 4, 3)[points]).max() < 1e-5
+    assert np.abs(w.download(F.CONTACT_DEPTH).reshape(E, S, 4)[points] - o.get("contact_depth", 4 * S).reshape(E, S, 4)[points]).max() < 1e-5
+    w.destroy()

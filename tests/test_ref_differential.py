@@ -16,7 +16,7 @@ sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "gol
 import ref_cases as RC
 
 N_LIVE = 12000          # cases per pair kind / law in the live comparison
-NAMES = {0: "sphere", 1: "capsule", 2: "box", 3: "plane"}
+NAMES = {0: "sphere", 1: "capsule", 2: "box", 3: "plane", 7: "cylinder"}
 
 
 def ulps(a, b):

@@ -38,7 +38,7 @@ def run_oracle(oracle, case):
     return ref, w, E, L, n, S
 
 
-ARTICULATED = sorted(c for c in RP.CASES if c != "pile12")
+ARTICULATED = sorted(c for c in RP.CASES if c not in ("pile12", "cylinders"))
 
 
 @pytest.mark.parametrize("case", ARTICULATED)
@@ -77,7 +77,7 @@ def test_steps_match_the_reference(oracle, case):
     done = 0
     own_any = np.zeros(E, np.uint32)
     for i, s in enumerate(steps):
-        if case in RP.SENSITIVE and s > RP.SENSITIVE_LAST_STEP:
+        if case in RP.SENSITIVE and s > RP.SENSITIVE[case]:
             break
         for _ in range(s - done):       # one step at a time: the free-rotation bit describes the latest step only
             w.step(1)

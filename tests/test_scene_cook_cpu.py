@@ -11,7 +11,7 @@ import nuka
 from nuka import nks, nkt
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-SCENES = ["arm7", "quadruped", "humanoid", "pile12", "quadbox", "random0", "random1", "random3", "random7"]
+SCENES = ["arm7", "quadruped", "humanoid", "pile12", "quadbox", "cylinders", "random0", "random1", "random3", "random7"]
 
 
 def compare(native_bytes, tb):
@@ -88,10 +88,10 @@ def test_scene_errors_are_reported_not_thrown():
     assert e.value.code == 7                                   # NUKA_RESULT_NOT_SUPPORTED
     bad = json.loads(json.dumps(scene))
     shape = next(c for c in bad["tree"][0]["children"] if "collision_shape" in c)
-    shape["collision_shape"]["type"] = "cylinder"
+    shape["collision_shape"]["type"] = "convex_hull"
     with pytest.raises(nuka.NukaError) as e:
         nks.cook_native(json.dumps(bad))
-    assert e.value.code == 7 and "cylinder" in str(e.value)
+    assert e.value.code == 7 and "convex_hull" in str(e.value)
     with pytest.raises(nuka.NukaError) as e:
         nks.cook_native(json.dumps(scene), dt=0.0)
     assert e.value.code == 1                                   # NUKA_RESULT_INVALID_ARG
