@@ -63,7 +63,8 @@ typedef struct orc_config {
     float velocity_tolerance;
     uint32_t max_contacts;      /* candidate slots per env */
     uint32_t max_pairs;         /* 0: same as max_contacts */
-    uint32_t control_mode;      /* 0 PD position, 1 torque, 2 velocity, 5 actuator (phi/articulation_contract.hpp:16-23) */
+    uint32_t control_mode;      /* 0 PD position, 1 torque, 2 velocity, 3 computed torque, 4 operational space, 5 actuator (phi/articulation_contract.hpp:16-23) */
+    uint32_t task_link;         /* mode 4: the link that carries the task frame */
 } orc_config;
 
 /* One env's cooked template (reference src/nk/model/model.hpp:175-244, 488-548). */
@@ -127,6 +128,7 @@ typedef struct orc_env {
     float *link_acc, *link_vbias, *link_pbias, *link_S;  /* L*6 */
     float *link_xup, *link_ic;               /* L*36 */
     float *drive_target, *vel_target, *kp, *kd, *force_limit, *feedforward, *noload_speed, *acc_target;
+    float task_target[3], task_rotation[4], task_frame[7], null_kp, null_kd;     /* mode 4 inputs: world target, optional orientation (zero = position only), local frame on the task link, posture gains */
     float *limit_lambda;      /* 2 x L: the joint-limit multipliers the last velocity solve left (lower, upper per link) */
     float *drive_command, *drive_dissipation, *drive_lower, *drive_upper;
     float *actuator_applied;                 /* L */

@@ -71,6 +71,7 @@ def lib(path=None):
         L.orc_world_reset.argtypes = [ctypes.c_void_p]
         L.orc_world_set_control_mode.argtypes = [ctypes.c_void_p, ctypes.c_uint32]
         L.orc_world_set_broadphase.argtypes = [ctypes.c_void_p, ctypes.c_uint32]
+        L.orc_world_set_task_link.argtypes = [ctypes.c_void_p, ctypes.c_uint32]
         L.orc_lbvh_pair_set.restype = ctypes.c_uint32
         L.orc_lbvh_pair_set.argtypes = [ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32]
         L.orc_world_refresh.argtypes = [ctypes.c_void_p]
@@ -107,6 +108,10 @@ class World:
 
     def set_control_mode(self, mode):
         lib().orc_world_set_control_mode(self._h, int(mode))
+
+    def set_task_link(self, link):
+        """Mode 4: the link that carries the task frame."""
+        lib().orc_world_set_task_link(self._h, int(link))
 
     def set_broadphase(self, mode):
         """0: the reference's route rule, 1: all-pairs, 2: LBVH tree walk."""

@@ -55,7 +55,7 @@ void orc_apply_drives(const orc_model *m, orc_env *e) {
         e->tau[l] = 0.0f;
         if (joint_dofs(m->jtype[l]) != 1u) continue;
         const uint32_t mode = m->cfg.control_mode;
-        const int inverse_dynamics = mode == 3u;
+        const int inverse_dynamics = mode == 3u || mode == 4u;       /* articulation.cu:848-849 */
         const int position_control = mode == 0u || inverse_dynamics, velocity_control = mode == 2u;
         if ((position_control && (!isfinite(e->drive_target[l]) || !isfinite(e->kp[l]) || e->kp[l] < 0.0f ||
                                   !isfinite(e->kd[l]) || e->kd[l] < 0.0f)) ||
@@ -145,6 +145,164 @@ static void solve_control_mass(const float *f, const float *diagonal, uint32_t n
     }
 }
 
+/* articulation.cu:1234-1288 InvertTaskResponse: symmetric pseudoinverse by cyclic Jacobi rotations; directions whose
+ * eigenvalue is within 8 eps of the largest are dropped */
+static void invert_task_response(float *a, uint32_t n, float *inverse) {
+    float vec[36];
+    memset(vec, 0, sizeof vec);
+    for (uint32_t i = 0; i < n; ++i) vec[i * 6u + i] = 1.0f;
+    for (uint32_t sweep = 0; sweep < 24u; ++sweep) {
+        int changed = 0;
+        for (uint32_t p = 0; p < n; ++p) for (uint32_t q = p + 1u; q < n; ++q) {
+            const float app = a[p * 6u + p], aqq = a[q * 6u + q], apq = a[p * 6u + q];
+            if (fabsf(apq) <= FLT_EPSILON * (fabsf(app) + fabsf(aqq))) continue;
+            changed = 1;
+            const double theta = ((double)aqq - app) / (2.0 * apq);
+            const float tangent = (float)(copysign(1.0, theta) / (fabs(theta) + sqrt(1.0 + theta * theta)));
+            const float cosine = rsq(1.0f + tangent * tangent);
+            const float sine = tangent * cosine;
+            for (uint32_t k = 0; k < n; ++k) {
+                if (k != p && k != q) {
+                    const float kp = a[k * 6u + p], kq = a[k * 6u + q];
+                    a[k * 6u + p] = a[p * 6u + k] = cosine * kp - sine * kq;
+                    a[k * 6u + q] = a[q * 6u + k] = sine * kp + cosine * kq;
+                }
+                const float vp = vec[k * 6u + p], vq = vec[k * 6u + q];
+                vec[k * 6u + p] = cosine * vp - sine * vq;
+                vec[k * 6u + q] = sine * vp + cosine * vq;
+            }
+            a[p * 6u + p] = app - tangent * apq;
+            a[q * 6u + q] = aqq + tangent * apq;
+            a[p * 6u + q] = a[q * 6u + p] = 0.0f;
+        }
+        if (!changed) break;
+    }
+    float largest = 0.0f;
+    for (uint32_t i = 0; i < n; ++i) largest = fmaxf(largest, a[i * 6u + i]);
+    const float tolerance = largest * (8.0f * FLT_EPSILON);
+    for (uint32_t r = 0; r < n; ++r) for (uint32_t c = 0; c < n; ++c) {
+        double v = 0.0;
+        for (uint32_t k = 0; k < n; ++k) {
+            const float eigenvalue = a[k * 6u + k];
+            if (eigenvalue > tolerance) v += (double)vec[r * 6u + k] * vec[c * 6u + k] / eigenvalue;
+        }
+        inverse[r * 6u + c] = (float)v;
+    }
+}
+/* articulation.cu:1300-1313 TaskOrientationError: rotation vector from the current to the desired orientation */
+static v3 task_orientation_error(quat desired, quat current) {
+    current = qnorm_le(current, 1.0e-12f); desired = qnorm_le(desired, 1.0e-12f);
+    const quat err = qmul(desired, Q4(current.w, -current.x, -current.y, -current.z));
+    const float sign = err.w < 0.0f ? -1.0f : 1.0f;
+    const float length = sqrtf(err.x * err.x + err.y * err.y + err.z * err.z);
+    const float scale = length > 1.0e-7f ? sign * 2.0f * atan2f(length, fabsf(err.w)) / length : sign * 2.0f;
+    return V3(err.x * scale, err.y * scale, err.z * scale);
+}
+
+/* Operational-space control, articulation.cu:1419-1550 (the Osc branch of ApplyDynamicsDriveKernel).  J is the 6 x n
+ * Jacobian of the task frame (linear rows first), B = J M^-1 S^T its response to the actuators, H the actuated inertia
+ * of the computed-torque branch.  The task force F = (B H B^T)^+ (kp x_err - kd v - a_free - B (bias + damping + posture))
+ * acts through H B^T; joints on the chain from the task link to the root hold their posture through the nullspace gains,
+ * joints off the chain through their own drive gains. */
+static void osc_command(const orc_model *m, orc_env *e, uint32_t active, const uint32_t *links, const uint32_t *dofs,
+                        const float *mass, const float *bias, uint32_t stride) {
+    const uint32_t n = m->ndof, task_link = m->cfg.task_link;
+    static _Thread_local float jac[6 * ORC_MAX_DOF], response[6 * ORC_MAX_DOF], task_map[6 * ORC_MAX_DOF];
+    uint32_t chain[ORC_MAX_DOF];
+    float solution[ORC_MAX_DOF], rhs[ORC_MAX_DOF], posture[ORC_MAX_DOF];
+    float local_task[7];
+    memcpy(local_task, e->task_frame, sizeof local_task);
+    qst(local_task + 3, qnorm_le(qld(local_task + 3), 1.0e-12f));
+    float task_pose[7];
+    pose_compose(e->link_pose + 7 * task_link, local_task, task_pose);
+    memset(jac, 0, sizeof(float) * 6u * stride);
+    memset(chain, 0, sizeof chain);
+    for (uint32_t walk = task_link; walk != ORC_NOLINK; walk = m->parent[walk]) {
+        const uint32_t type = m->jtype[walk], dof = m->link_dof[walk];
+        const v3 lever = vsub(v3ld(task_pose), v3ld(e->link_pose + 7 * walk));
+        if (type == ORC_JOINT_FLOATING) {
+            const v3 basis[3] = {V3(1, 0, 0), V3(0, 1, 0), V3(0, 0, 1)};
+            for (uint32_t c = 0; c < 3u; ++c) {
+                const v3 axis = qrot(qld(e->base_pose + 3), basis[c]);
+                const v3 lin = vcross(axis, lever);
+                jac[dof + c] = lin.x; jac[stride + dof + c] = lin.y; jac[2u * stride + dof + c] = lin.z;
+                jac[3u * stride + dof + c] = axis.x; jac[4u * stride + dof + c] = axis.y; jac[5u * stride + dof + c] = axis.z;
+                jac[dof + 3u + c] = axis.x; jac[stride + dof + 3u + c] = axis.y; jac[2u * stride + dof + 3u + c] = axis.z;
+                jac[3u * stride + dof + 3u + c] = 0.0f; jac[4u * stride + dof + 3u + c] = 0.0f; jac[5u * stride + dof + 3u + c] = 0.0f;
+            }
+        } else if (joint_dofs(type) == 1u) {
+            const v3 axis = qrot(qld(e->link_pose + 7 * walk + 3), v3ld(m->axis + 3 * walk));
+            const int revolute = type == ORC_JOINT_REVOLUTE;
+            const v3 lin = revolute ? vcross(axis, lever) : axis, ang = revolute ? axis : V3(0, 0, 0);
+            jac[dof] = lin.x; jac[stride + dof] = lin.y; jac[2u * stride + dof] = lin.z;
+            jac[3u * stride + dof] = ang.x; jac[4u * stride + dof] = ang.y; jac[5u * stride + dof] = ang.z;
+            chain[dof] = 1u;
+        }
+    }
+    const quat desired = qld(e->task_rotation);
+    const float rotation_norm = desired.w * desired.w + desired.x * desired.x + desired.y * desired.y + desired.z * desired.z;
+    const uint32_t rows = rotation_norm > 1.0e-12f ? 6u : 3u;
+    for (uint32_t r = 0; r < rows; ++r) {
+        for (uint32_t d = 0; d < n; ++d) solution[d] = jac[r * stride + d];
+        orc_solve_mass(e->Mfactor, solution, n);
+        for (uint32_t c = 0; c < active; ++c) response[r * stride + c] = solution[dofs[c]];
+    }
+    for (uint32_t r = 0; r < rows; ++r) for (uint32_t c = 0; c < active; ++c) {
+        double v = 0.0;
+        for (uint32_t a = 0; a < active; ++a) v += (double)mass[c * stride + a] * response[r * stride + a];
+        task_map[r * stride + c] = (float)v;
+    }
+    float metric[36], inverse_metric[36];
+    memset(metric, 0, sizeof metric); memset(inverse_metric, 0, sizeof inverse_metric);
+    for (uint32_t r = 0; r < rows; ++r) for (uint32_t c = 0; c < rows; ++c) {
+        double v = 0.0;
+        for (uint32_t a = 0; a < active; ++a) v += (double)response[r * stride + a] * task_map[c * stride + a];
+        metric[r * 6u + c] = (float)v;
+    }
+    invert_task_response(metric, rows, inverse_metric);
+    const float *vel = e->link_vel + 6 * task_link, *acc = e->link_acc + 6 * task_link;
+    const v3 omega = V3(vel[0], vel[1], vel[2]), linear = V3(vel[3], vel[4], vel[5]);
+    const v3 alpha = V3(acc[0], acc[1], acc[2]), linear_accel = V3(acc[3], acc[4], acc[5]);
+    const quat rotation = qld(e->link_pose + 7 * task_link + 3);
+    const v3 offset = v3ld(local_task);
+    const v3 task_velocity = qrot(rotation, vadd(linear, vcross(omega, offset)));
+    const v3 task_angular = qrot(rotation, omega);
+    const v3 task_accel = vadd(qrot(rotation, vadd(vadd(linear_accel, vcross(omega, linear)),
+                                                   vadd(vcross(alpha, offset), vcross(omega, vcross(omega, offset))))),
+                               V3(m->cfg.gravity[0], m->cfg.gravity[1], m->cfg.gravity[2]));
+    const v3 task_angular_accel = qrot(rotation, alpha);
+    const v3 position_error = vsub(v3ld(e->task_target), v3ld(task_pose));
+    const v3 orientation_error = rows == 6u ? task_orientation_error(desired, qld(task_pose + 3)) : V3(0, 0, 0);
+    const float kp = e->kp[task_link], kd = e->kd[task_link];
+    float task_rhs[6] = {kp * position_error.x - kd * task_velocity.x - task_accel.x,
+                         kp * position_error.y - kd * task_velocity.y - task_accel.y,
+                         kp * position_error.z - kd * task_velocity.z - task_accel.z,
+                         kp * orientation_error.x - kd * task_angular.x - task_angular_accel.x,
+                         kp * orientation_error.y - kd * task_angular.y - task_angular_accel.y,
+                         kp * orientation_error.z - kd * task_angular.z - task_angular_accel.z};
+    for (uint32_t c = 0; c < active; ++c) {
+        const uint32_t l = links[c];
+        rhs[c] = chain[dofs[c]] ? e->null_kp * (e->drive_target[l] - e->q[l]) + e->null_kd * (e->vel_target[l] - e->qdot[l]) : 0.0f;
+    }
+    for (uint32_t r = 0; r < active; ++r) {
+        double v = 0.0;
+        for (uint32_t c = 0; c < active; ++c) v += (double)mass[r * stride + c] * rhs[c];
+        const uint32_t l = links[r];
+        if (!chain[dofs[r]]) v += e->kp[l] * (e->drive_target[l] - e->q[l]) + e->kd[l] * (e->vel_target[l] - e->qdot[l]);
+        posture[r] = (float)v;
+    }
+    for (uint32_t r = 0; r < rows; ++r)
+        for (uint32_t a = 0; a < active; ++a)
+            task_rhs[r] -= response[r * stride + a] * (bias[a] + m->damping[links[a]] * e->qdot[links[a]] + posture[a]);
+    float task_force[6] = {0, 0, 0, 0, 0, 0};
+    for (uint32_t r = 0; r < rows; ++r) for (uint32_t c = 0; c < rows; ++c) task_force[r] += inverse_metric[r * 6u + c] * task_rhs[c];
+    for (uint32_t a = 0; a < active; ++a) {
+        double v = bias[a] + posture[a];
+        for (uint32_t r = 0; r < rows; ++r) v += (double)task_map[r * stride + a] * task_force[r];
+        e->drive_command[links[a]] = (float)v;
+    }
+}
+
 /* Computed-torque control, articulation.cu:1315-1418 (ApplyDynamicsDriveKernel, ComputedTorque branch).  With S the
  * selector of the scalar joints, H = (S M^-1 S^T)^-1 is the inertia the actuators see (a floating base's reaction
  * included); the command is H (a* + kp (q* - q) + kd (qd* - qd)) plus the compensation of the force-free acceleration,
@@ -152,8 +310,18 @@ static void solve_control_mass(const float *f, const float *diagonal, uint32_t n
 void orc_apply_dynamics_drives(const orc_model *m, orc_env *e) {
     const uint32_t L = m->L, n = m->ndof;
     uint32_t links[ORC_MAX_DOF], dofs[ORC_MAX_DOF], active = 0u;
+    if (m->cfg.control_mode == 4u && m->cfg.task_link >= L) { e->status |= ORC_STATUS_CONTROL_FAILURE; return; }
     for (uint32_t l = 0; l < L; ++l)
         if (joint_dofs(m->jtype[l]) == 1u && e->drive_lower[l] == 0.0f && e->drive_upper[l] == 0.0f) return;     /* a rejected drive */
+    if (m->cfg.control_mode == 4u) {           /* articulation.cu:1341-1360 */
+        const uint32_t tl = m->cfg.task_link;
+        int ok = isfinite(e->kp[tl]) && e->kp[tl] >= 0.0f && isfinite(e->kd[tl]) && e->kd[tl] >= 0.0f &&
+                 isfinite(e->null_kp) && e->null_kp >= 0.0f && isfinite(e->null_kd) && e->null_kd >= 0.0f;
+        for (int k = 0; k < 3; ++k) ok &= isfinite(e->task_target[k]);
+        for (int k = 0; k < 4; ++k) ok &= isfinite(e->task_rotation[k]);
+        for (int k = 0; k < 7; ++k) ok &= isfinite(e->task_frame[k]);
+        if (!ok) { e->status |= ORC_STATUS_CONTROL_FAILURE; return; }
+    }
     for (uint32_t l = 0; l < L; ++l) {
         if (joint_dofs(m->jtype[l]) != 1u) continue;
         links[active] = l; dofs[active] = m->link_dof[l];
@@ -185,14 +353,17 @@ void orc_apply_dynamics_drives(const orc_model *m, orc_env *e) {
         for (uint32_t c = 0; c < active; ++c) v -= (double)mass[r * stride + c] * e->qddot[links[c]];
         bias[r] = (float)v;
     }
-    for (uint32_t c = 0; c < active; ++c) {
-        const uint32_t l = links[c];
-        rhs[c] = e->acc_target[l] + e->kp[l] * (e->drive_target[l] - e->q[l]) + e->kd[l] * (e->vel_target[l] - e->qdot[l]);
-    }
-    for (uint32_t r = 0; r < active; ++r) {
-        double v = bias[r];
-        for (uint32_t c = 0; c < active; ++c) v += (double)mass[r * stride + c] * rhs[c];
-        e->drive_command[links[r]] = (float)v;
+    if (m->cfg.control_mode == 4u) osc_command(m, e, active, links, dofs, mass, bias, stride);
+    else {
+        for (uint32_t c = 0; c < active; ++c) {
+            const uint32_t l = links[c];
+            rhs[c] = e->acc_target[l] + e->kp[l] * (e->drive_target[l] - e->q[l]) + e->kd[l] * (e->vel_target[l] - e->qdot[l]);
+        }
+        for (uint32_t r = 0; r < active; ++r) {
+            double v = bias[r];
+            for (uint32_t c = 0; c < active; ++c) v += (double)mass[r * stride + c] * rhs[c];
+            e->drive_command[links[r]] = (float)v;
+        }
     }
     for (uint32_t a = 0; a < active; ++a)
         if (!isfinite(e->drive_command[links[a]])) {

@@ -82,6 +82,8 @@ static void env_seed(const orc_model *m, orc_env *e) {
     }
     memset(e->link_vel, 0, sizeof(float) * 6 * L);
     memset(e->limit_lambda, 0, sizeof(float) * 2 * L);
+    memset(e->task_target, 0, sizeof e->task_target); memset(e->task_rotation, 0, sizeof e->task_rotation);
+    memset(e->task_frame, 0, sizeof e->task_frame); e->task_frame[3] = 1.0f; e->null_kp = e->null_kd = 0.0f;
     if (L) memcpy(e->base_pose, m->base_pose0, 28);
     if (B) memcpy(e->body_pose, m->body_pose0, sizeof(float) * 7 * B);
     memset(e->body_linvel, 0, sizeof(float) * 3 * B); memset(e->body_angvel, 0, sizeof(float) * 3 * B);
@@ -179,7 +181,8 @@ void orc_world_destroy(orc_world *w) {
 }
 
 /* control mode of every env: 0 PD position, 1 torque, 2 velocity; other values are ignored */
-void orc_world_set_control_mode(orc_world *w, uint32_t mode) { if (mode <= 3u || mode == 5u) w->m.cfg.control_mode = mode; }
+void orc_world_set_control_mode(orc_world *w, uint32_t mode) { if (mode <= 5u) w->m.cfg.control_mode = mode; }
+void orc_world_set_task_link(orc_world *w, uint32_t link) { w->m.cfg.task_link = link; }
 
 void orc_world_set_broadphase(orc_world *w, uint32_t mode) { if (mode <= 2u) w->m.broadphase = mode; }
 
@@ -193,7 +196,7 @@ void orc_step_env(const orc_model *m, orc_env *e) {
     const int has_collidables = has_bodies && m->cfg.max_contacts > 0u;
     if (has_artic) {
         orc_fk(m, e); orc_apply_drives(m, e);
-        if (m->cfg.control_mode == 3u) {
+        if (m->cfg.control_mode == 3u || m->cfg.control_mode == 4u) {
             /* pipeline.cpp:406-426: a force-free dynamics pass on the current kinematics, the inverse-dynamics controller on
              * its mass response and acceleration, then the step's dynamics pass (the same mass matrix) */
             orc_dynamics(m, e, 0);
@@ -266,7 +269,8 @@ static void *field_ptr(const orc_model *m, orc_env *e, const char *f, size_t *co
     R("pair_count", &e->pair_count, 1) R("candidate_pairs", e->pairs, 2 * S) R("contact_count", e->ccount, S)
     R("contact_point", e->cpoint, 12 * S) R("contact_normal", e->cnormal, 12 * S) R("contact_depth", e->cdepth, 4 * S)
     R("env_status", &e->status, 1) R("solver_residual", e->solver_residual, 4) R("solver_sweeps", &e->sweeps, 1)
-    R("limit_multiplier", e->limit_lambda, 2 * L) R("contact_points", &e->contact_points, 1) R("qdot_pseudo", e->qdot_pseudo, n) R("dof_velocity", e->artic_vel, n)
+    R("limit_multiplier", e->limit_lambda, 2 * L) R("task_target", e->task_target, 3) R("task_rotation_target", e->task_rotation, 4)
+    R("task_local_pose", e->task_frame, 7) R("task_nullspace_stiffness", &e->null_kp, 1) R("task_nullspace_damping", &e->null_kd, 1) R("contact_points", &e->contact_points, 1) R("qdot_pseudo", e->qdot_pseudo, n) R("dof_velocity", e->artic_vel, n)
 #undef R
     *count = 0;
     return NULL;

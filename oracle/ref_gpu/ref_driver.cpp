@@ -162,7 +162,7 @@ void DumpModel(const nk::Model& m, Container* c) {
 
 struct Args {
     std::string scene, state, dump;
-    uint32_t envs = 1, vel_iters = 0, pos_iters = 0xffffffffu, steps = 0, every = 1, control_mode = 0;
+    uint32_t envs = 1, vel_iters = 0, pos_iters = 0xffffffffu, steps = 0, every = 1, control_mode = 0, task_link = 0;
     float dt = 1.0f / 200.0f;
     bool contacts = true, cook_only = false, taps = false;
     int warm = 0, timed = 0, repeats = 1;
@@ -189,6 +189,7 @@ int main(int argc, char** argv) {
         else if (k == "--vel-iters") a.vel_iters = static_cast<uint32_t>(std::atoi(next()));
         else if (k == "--pos-iters") a.pos_iters = static_cast<uint32_t>(std::atoi(next()));
         else if (k == "--control-mode") a.control_mode = static_cast<uint32_t>(std::atoi(next()));
+        else if (k == "--task-link") a.task_link = static_cast<uint32_t>(std::atoi(next()));
         else if (k == "--steps") a.steps = static_cast<uint32_t>(std::atoi(next()));
         else if (k == "--every") a.every = std::max(1, std::atoi(next()));
         else if (k == "--state") a.state = next();
@@ -208,6 +209,7 @@ int main(int argc, char** argv) {
         auto cooked = nuka::scene::cook::CookToModel(scene, static_cast<int>(a.envs), options);
         Container out;
         cooked.model.drive_mode = a.control_mode;          // as src/c_abi/world.cpp:160-166 routes the descriptor's control mode
+        cooked.model.osc_task_link = a.task_link;          // src/c_abi/world.cpp:167
         DumpModel(cooked.model, &out);
         if (a.cook_only) {
             if (!a.dump.empty() && !out.Write(a.dump)) { std::fprintf(stderr, "cannot write %s\n", a.dump.c_str()); return 1; }
@@ -236,6 +238,8 @@ int main(int argc, char** argv) {
                 {"drive_target", nk::FieldId::DriveTarget}, {"vel_target", nk::FieldId::VelocityTarget}, {"acc_target", nk::FieldId::AccelerationTarget},
                 {"kp", nk::FieldId::DriveStiffness}, {"kd", nk::FieldId::DriveDamping}, {"force_limit", nk::FieldId::DriveForceLimit},
                 {"noload_speed", nk::FieldId::ActuatorNoloadSpeed}, {"feedforward", nk::FieldId::JointF},
+                {"task_target", nk::FieldId::TaskTarget}, {"task_rotation", nk::FieldId::TaskRotationTarget}, {"task_frame", nk::FieldId::TaskLocalPose},
+                {"null_kp", nk::FieldId::TaskNullspaceStiffness}, {"null_kd", nk::FieldId::TaskNullspaceDamping},
                 {"body_pose", nk::FieldId::BodyPose}};
             for (const auto& f : fields) {
                 const auto it = st.find(f.first);

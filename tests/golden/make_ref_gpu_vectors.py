@@ -49,6 +49,9 @@ CASES = {
     "quadruped_torque": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_mode_state(1, E), 1.0 / 200.0, 4, 40, 10),
     "quadruped_velocity": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_mode_state(2, E), 1.0 / 200.0, 4, 40, 10),
     "quadruped_actuator": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_mode_state(5, E), 1.0 / 200.0, 4, 40, 10),
+    # operational-space control (control mode 4): the arm's tip and one foot of the landing quadruped as task frames
+    "arm7_osc": (lambda: T.arm7(0), lambda E: ref_cases.arm_osc_state(E, 0), 1.0 / 500.0, 4, 40, 10),
+    "quadruped_osc": (lambda: T.quadruped(0), lambda E: ref_cases.quadruped_osc_state(E, 0), 1.0 / 200.0, 4, 20, 5),
     # free cylinders and spheres over a plane: the cylinder-plane (cap, rim, side) and cylinder-sphere manifolds
     "cylinders": (lambda: ref_cases.cylinder_field(), lambda E: ref_cases.cylinder_field_state(E), 1.0 / 250.0, 8, 80, 20),
     # seeded random articulations (random trees, revolute / prismatic / fixed joints, limits, dry friction, armature,
@@ -57,10 +60,12 @@ CASES = {
        for k in (0, 1, 3, 7)},
 }
 SCENE_OF = {"quadruped_moving": "quadruped", "arm7_ct": "arm7", "quadruped_ct": "quadruped", "quadruped_torque": "quadruped",
-            "quadruped_velocity": "quadruped", "quadruped_actuator": "quadruped"}
-CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3, "quadruped_torque": 1, "quadruped_velocity": 2, "quadruped_actuator": 5}
+            "quadruped_velocity": "quadruped", "quadruped_actuator": "quadruped", "arm7_osc": "arm7", "quadruped_osc": "quadruped"}
+CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3, "quadruped_torque": 1, "quadruped_velocity": 2, "quadruped_actuator": 5,
+                "arm7_osc": 4, "quadruped_osc": 4}
+TASK_LINK = {"arm7_osc": 7, "quadruped_osc": 3}
 STATE_FIELDS = ("q", "qdot", "base_pose", "link_velocity", "body_pose", "drive_target", "vel_target", "acc_target", "kp", "kd", "force_limit",
-                "noload_speed", "feedforward")
+                "noload_speed", "feedforward", "task_target", "task_rotation", "task_frame", "null_kp", "null_kd")
 # throughput of the reference on the other configurations, on the protocol of bench.py --workload: the same seeded
 # per-env start states, the same untimed settle steps, then the timed steps
 # (scene case, envs, dt, iterations, settle steps, timed steps, start state)
@@ -85,6 +90,8 @@ def prepare():
         subprocess.run([DRIVER, "--scene", os.path.join(RUN, f"{name}.nks"), "--envs", "1", "--cook-only", "--dump",
                         os.path.join(HERE, f"ref_cook_{scene}.nkt")], check=True, stdout=subprocess.DEVNULL)
         mode = f" --control-mode {CONTROL_MODE[name]}" if name in CONTROL_MODE else ""
+        if name in TASK_LINK:
+            mode += f" --task-link {TASK_LINK[name]}"
         lines.append(f"../ref_driver --scene {name}.nks --envs {ENVS} --dt {dt!r} --vel-iters {iters}{mode} --state {name}_state.nkt "
                      f"--steps {steps} --every {every} --dump \"$OUT/ref_{name}.nkt\"")
     # the number to beat: the reference's own step on the bench workload, eager and graph mode, 100 warm-up + 1000 timed steps

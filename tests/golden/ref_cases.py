@@ -185,6 +185,83 @@ def quadruped_computed_torque_state(env_count, seed=0):
             "force_limit": np.full((env_count, L), 20.0, np.float32)}
 
 
+def _quat_mul(a, b):
+    w1, x1, y1, z1 = a[..., 0], a[..., 1], a[..., 2], a[..., 3]
+    w2, x2, y2, z2 = b[..., 0], b[..., 1], b[..., 2], b[..., 3]
+    return np.stack([w1 * w2 - x1 * x2 - y1 * y2 - z1 * z2, w1 * x2 + x1 * w2 + y1 * z2 - z1 * y2,
+                     w1 * y2 - x1 * z2 + y1 * w2 + z1 * x2, w1 * z2 + x1 * y2 - y1 * x2 + z1 * w2], -1)
+
+
+def _quat_rot(q, v):
+    qv = q[..., 1:]
+    t = 2.0 * np.cross(qv, v)
+    return v + q[..., :1] * t + np.cross(qv, t)
+
+
+def arm_osc_state(env_count, seed=0):
+    """Operational-space control (mode 4) on the 7-link arm, task link 7 with its frame 0.3 m out at the tip: world targets
+    within 10 cm of the tip's start position, an orientation target within 0.3 rad of the start orientation in every
+    other env (the rest track position only), task gains kp 25 / kd 10 (the task link's drive gains), posture gains
+    20 / 20 towards the start pose.  (Stiffer task gains or softer posture gains and the six-row tasks of the reference's
+    controller run away within a hundred steps, in its own output too.)"""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "nuka-physics_b200"))
+    from nuka import templates as T
+    st = T.arm7_state(env_count, seed)
+    rng = np.random.Generator(np.random.PCG64(21 + seed))
+    L = 8
+    q = st["q"].astype(np.float64)
+    pos = np.tile(np.array([0.0, 0.0, 1.0]), (env_count, 1))
+    rot = np.tile(np.array([1.0, 0.0, 0.0, 0.0]), (env_count, 1))
+    for i in range(7):                                       # the serial chain of templates.arm7: 0.3 m links, axes z, y, z, ...
+        if i:
+            pos = pos + _quat_rot(rot, np.array([0.3, 0.0, 0.0]))
+        half = 0.5 * q[:, i + 1]
+        axis = np.array([0.0, 0.0, 1.0]) if i % 2 == 0 else np.array([0.0, 1.0, 0.0])
+        rot = _quat_mul(rot, np.concatenate([np.cos(half)[:, None], np.sin(half)[:, None] * axis[None, :]], 1))
+    tip = pos + _quat_rot(rot, np.array([0.3, 0.0, 0.0]))
+    target = tip + rng.uniform(-0.1, 0.1, size=(env_count, 3))
+    turn = rng.normal(0, 0.15, size=(env_count, 3))
+    dq = np.concatenate([np.ones((env_count, 1)), 0.5 * turn], 1)
+    desired = _quat_mul(rot, dq / np.linalg.norm(dq, axis=1, keepdims=True))
+    desired[1::2] = 0.0                                      # position-only tasks
+    frame = np.tile(np.array([0.3, 0.0, 0.0, 1.0, 0.0, 0.0, 0.0], np.float32), (env_count, 1))
+    kp = np.zeros((env_count, L), np.float32); kp[:, 7] = 25.0
+    kd = np.zeros((env_count, L), np.float32); kd[:, 7] = 10.0
+    return {"q": st["q"], "qdot": st["qdot"], "drive_target": st["q"].copy(), "kp": kp, "kd": kd,
+            "task_target": target.astype(np.float32), "task_rotation": desired.astype(np.float32), "task_frame": frame,
+            "null_kp": np.full((env_count, 1), 20.0, np.float32), "null_kd": np.full((env_count, 1), 20.0, np.float32)}
+
+
+def quadruped_osc_state(env_count, seed=0):
+    """Operational-space control on the landing quadruped: the first leg's foot (task link 3, frame at the foot sphere)
+    reaches for a point ahead of the trunk while the other three legs, off the task chain, hold the stance through their
+    own drive gains (kp 40 / kd 2); task gains 50 / 10 on link 3, posture gains 5 / 1, 20 N m force limits, an
+    orientation target in every fourth env (a foot's orientation is barely reachable through three leg joints and an
+    unactuated trunk: the controller saturates the limits there)."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "nuka-physics_b200"))
+    from nuka import templates as T
+    st = T.quadruped_state(env_count, seed)
+    rng = np.random.Generator(np.random.PCG64(31 + seed))
+    L = 13
+    stance = np.tile(T.quadruped(0).arrays()["q0"].reshape(1, L), (env_count, 1)).astype(np.float32)
+    kp = np.full((env_count, L), 40.0, np.float32); kp[:, 3] = 50.0
+    kd = np.full((env_count, L), 2.0, np.float32); kd[:, 3] = 10.0
+    target = st["base_pose"][:, :3].astype(np.float64) + np.array([0.24, 0.13, -0.2]) + rng.normal(0, 0.03, size=(env_count, 3))
+    turn = rng.normal(0, 0.3, size=(env_count, 3))
+    desired = np.concatenate([np.ones((env_count, 1)), 0.5 * turn], 1)
+    desired /= np.linalg.norm(desired, axis=1, keepdims=True)
+    desired[np.arange(env_count) % 4 != 0] = 0.0
+    frame = np.tile(np.array([0.0, 0.0, -0.213, 1.0, 0.0, 0.0, 0.0], np.float32), (env_count, 1))
+    return {"q": st["q"], "base_pose": st["base_pose"], "drive_target": stance, "kp": kp, "kd": kd,
+            "force_limit": np.full((env_count, L), 20.0, np.float32),
+            "task_target": target.astype(np.float32), "task_rotation": desired.astype(np.float32), "task_frame": frame,
+            "null_kp": np.full((env_count, 1), 5.0, np.float32), "null_kd": np.full((env_count, 1), 1.0, np.float32)}
+
+
 def quadruped_mode_state(mode, env_count, seed=0):
     """The quadruped's seeded drop under the other control modes.  1 (torque): the target field carries joint efforts,
     a feedforward effort on top.  2 (velocity): rate targets, the stiffness field is the rate gain, 15 N m force limits.

@@ -27,16 +27,24 @@ CASES = {
     "arm7_ct": ("arm7", lambda E: ref_cases.arm_computed_torque_state(E, 0)),
     "quadruped_ct": ("quadruped", lambda E: ref_cases.quadruped_computed_torque_state(E, 0)),
 }
+# operational-space control (control mode 4)
+CASES["arm7_osc"] = ("arm7", lambda E: ref_cases.arm_osc_state(E, 0))
+CASES["quadruped_osc"] = ("quadruped", lambda E: ref_cases.quadruped_osc_state(E, 0))
 CASES["cylinders"] = ("cylinders", lambda E: ref_cases.cylinder_field_state(E))
 CASES.update({f"quadruped_{name}": ("quadruped", lambda E, mode=mode: ref_cases.quadruped_mode_state(mode, E))
               for name, mode in (("torque", 1), ("velocity", 2), ("actuator", 5))})
 CASES.update({f"random{k}": (f"random{k}", lambda E, k=k: ref_cases.random_robot_state(k, E)) for k in (0, 1, 3, 7)})
-CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3, "quadruped_torque": 1, "quadruped_velocity": 2, "quadruped_actuator": 5}
+CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3, "quadruped_torque": 1, "quadruped_velocity": 2, "quadruped_actuator": 5,
+                "arm7_osc": 4, "quadruped_osc": 4}
+TASK_LINK = {"arm7_osc": 7, "quadruped_osc": 3}
 # drive inputs a case's start state may carry: state key -> (oracle field name, nuka.Field name)
 DRIVE_INPUTS = {"drive_target": ("drive_target", "DRIVE_TARGET"), "vel_target": ("velocity_target", "VELOCITY_TARGET"),
                 "acc_target": ("acceleration_target", "ACCELERATION_TARGET"), "kp": ("drive_stiffness", "DRIVE_STIFFNESS"),
                 "kd": ("drive_damping", "DRIVE_DAMPING"), "force_limit": ("drive_force_limit", "DRIVE_FORCE_LIMIT"),
-                "noload_speed": ("noload_speed", "ACTUATOR_NOLOAD_SPEED"), "feedforward": ("joint_feedforward", "JOINT_FEEDFORWARD")}
+                "noload_speed": ("noload_speed", "ACTUATOR_NOLOAD_SPEED"), "feedforward": ("joint_feedforward", "JOINT_FEEDFORWARD"),
+                "task_target": ("task_target", "TASK_TARGET"), "task_rotation": ("task_rotation_target", "TASK_ROTATION_TARGET"),
+                "task_frame": ("task_local_pose", "TASK_LOCAL_POSE"), "null_kp": ("task_nullspace_stiffness", "TASK_NULLSPACE_STIFFNESS"),
+                "null_kd": ("task_nullspace_damping", "TASK_NULLSPACE_DAMPING")}
 # contact points per env that get solver rows, where the procedural template sets its own capacity
 MAX_POINTS = {"pile12": 72, "quadbox": 40, "humanoid": 48}
 
@@ -106,7 +114,16 @@ CHAOTIC = ("pile12", "humanoid")
 # reference's own output: one of four cap points at +1.1 cm while the other three rest at -1e-5).  Which step and env that
 # happens in depends on the last bit of the pose.  The case is compared through the landing and toppling, up to step 40;
 # at step 60 a 1-ulp change of the start heights moves this repository's own result by 2e-3 in 10 % of the envs.
-SENSITIVE = {"random0": 40, "random3": 40, "random7": 40, "cylinders": 40}       # case -> last compared step
+# Operational-space control: the reference's controller inverts the 6 x 6 task metric B H B^T with a pseudoinverse that
+# keeps every eigenvalue above 8 eps of the largest (articulation.cu:1273), so a nearly unreachable task direction is
+# divided by almost nothing.  On the arm the six-row (position + orientation) tasks run away within tens of steps in the
+# reference's own output, and single envs leave the common trajectory first; the case is compared to step 30 on the
+# chaotic cases' bars.  On the quadruped a foot's orientation is barely reachable through three leg joints and the
+# unactuated trunk: in the six-row envs (every fourth) two evaluations of the same formulas differ by 1e-3 in the joint
+# rates after ONE step, so those envs are held to 5e-3 on the first step and left out afterwards; the three-row envs are
+# compared to step 10 (the landing with saturated force limits amplifies differences beyond that).
+SENSITIVE = {"random0": 40, "random3": 40, "random7": 40, "cylinders": 40, "arm7_osc": 30, "quadruped_osc": 10}       # case -> last compared step
+ILL_CONDITIONED = {"quadruped_osc": lambda E: np.arange(E) % 4 == 0}     # case -> envs left out of the comparison
 GYRO_BIT = 32
 
 
@@ -117,7 +134,16 @@ def comparable(case, ref_status_any, own_status_any):
     if case in SENSITIVE:
         keep = ((np.asarray(ref_status_any) | np.asarray(own_status_any)) & GYRO_BIT) == 0
         assert keep.mean() >= 0.85, (case, float(keep.mean()))
+    if case in ILL_CONDITIONED:
+        keep &= ~ILL_CONDITIONED[case](len(keep))
     return keep
+
+
+def assert_ill_conditioned_first_step(case, got_qdot, want_qdot):
+    """The envs a case leaves out still have to agree after one step, to 5e-3 of max(|v|, 1)."""
+    if case in ILL_CONDITIONED:
+        rows = ILL_CONDITIONED[case](len(want_qdot))
+        assert err_envs(got_qdot, want_qdot, floor=1.0)[rows].max() < 5e-3, case
 
 
 def assert_position_parity(got, want, first, tag, case, absolute=False, keep=None):

@@ -32,6 +32,8 @@ def run_oracle(oracle, case):
             w.set(name, st[k])
     if case in RP.CONTROL_MODE:
         w.set_control_mode(RP.CONTROL_MODE[case])
+    if case in RP.TASK_LINK:
+        w.set_task_link(RP.TASK_LINK[case])
     w.refresh()
     if "link_velocity" in st:
         w.set("link_velocity", st["link_velocity"])
@@ -90,6 +92,8 @@ def test_steps_match_the_reference(oracle, case):
         if L:
             RP.assert_position_parity(w.get("q", L), q[i], first, (case, s, "q"), case, keep=keep)
             RP.assert_velocity_parity(w.get("qdot", L), qd[i], first, (case, s, "joint rates"), case, keep=keep)
+            if first:
+                RP.assert_ill_conditioned_first_step(case, w.get("qdot", L), qd[i])
         if ref["traj_base_pose"].size:
             RP.assert_position_parity(w.get("base_pose", 7), ref["traj_base_pose"].reshape(K, E, 7)[i], first, (case, s, "base"), case, keep=keep)
             twist = w.get("link_velocity", 6 * L).reshape(E, L, 6)[:, 0]
