@@ -65,8 +65,8 @@ typedef struct nuka_world_desc_t {
     uint32_t env_count;
     float fixed_dt;
     uint8_t determinism;               /* 0 or 1; larger values are INVALID_ARG */
-    uint8_t control_mode;              /* 0 PD position, 1 torque, 2 velocity, 3 computed torque, 5 actuator; 4 (OSC) NOT_SUPPORTED */
-    uint32_t osc_task_link;
+    uint8_t control_mode;              /* 0 PD position, 1 torque, 2 velocity, 3 computed torque, 4 operational space, 5 actuator */
+    uint32_t osc_task_link;            /* control mode 4: the link (index in the articulation) that carries the task frame; must be 0 in other modes */
     float terrain_step_height, terrain_step_width, terrain_platform_width, terrain_grid_width, terrain_grid_height_max;
     uint32_t instance_count;
     float instance_spacing;
@@ -152,6 +152,14 @@ typedef enum nuka_state_field_t {
     NUKA_FIELD_ACTUATOR_NOLOAD_SPEED = 14,    /* E x L f32, writable; actuator mode's torque-speed envelope, <= 0 disables it */
     NUKA_FIELD_JOINT_FEEDFORWARD = 22,        /* E x L f32, writable */
     NUKA_FIELD_ACCELERATION_TARGET = 56,      /* E x L f32, writable; computed-torque control's feed-forward acceleration */
+    /* operational-space control (control_mode 4, nuka.h:596-598, 748-751, 789-790): one task per env on link osc_task_link.
+       The task link's DRIVE_STIFFNESS / DRIVE_DAMPING are the task gains; joints off the chain from that link to the root
+       hold DRIVE_TARGET through their own gains, joints on it through the nullspace gains.  Kept across resets. */
+    NUKA_FIELD_TASK_TARGET = 15,              /* E x 3 f32, writable: world position the task frame reaches for */
+    NUKA_FIELD_TASK_ROTATION_TARGET = 31,     /* E x 4 f32 (w, x, y, z), writable: world orientation; all zero = position-only task */
+    NUKA_FIELD_TASK_LOCAL_POSE = 32,          /* E x 7 f32 (x, y, z, qw, qx, qy, qz), writable: the task frame on the task link */
+    NUKA_FIELD_TASK_NULLSPACE_STIFFNESS = 57, /* E f32, writable */
+    NUKA_FIELD_TASK_NULLSPACE_DAMPING = 58,   /* E f32, writable */
     NUKA_FIELD_BODY_LINEAR_VELOCITY = 25,     /* E x B x 3 f32 */
     NUKA_FIELD_BODY_ANGULAR_VELOCITY = 26,    /* E x B x 3 f32 */
     NUKA_FIELD_JOINT_LIMIT_IMPULSE = 27,      /* E x L x 2 f32, read-only: the multipliers (lower, upper) the latest velocity solve left on

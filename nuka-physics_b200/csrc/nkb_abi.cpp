@@ -120,12 +120,12 @@ nuka_result_t ValidateDesc(const nuka_world_desc_t* d) {
     if (d->determinism > 1u) { SetError("determinism must be 0 or 1"); return NUKA_RESULT_INVALID_ARG; }
     if (d->fixed_dt < 0.f || d->fixed_dt != d->fixed_dt) { SetError("fixed_dt must be positive"); return NUKA_RESULT_INVALID_ARG; }
     if (d->control_mode > 5u) { SetError("control_mode must be 0..5"); return NUKA_RESULT_INVALID_ARG; }
-    if (d->control_mode == 4u) { SetError("control mode 4 (operational-space control) is not provided"); return NUKA_RESULT_NOT_SUPPORTED; }
+    if (d->control_mode != 4u && d->osc_task_link != 0u) { SetError("osc_task_link is read in control mode 4 only"); return NUKA_RESULT_NOT_SUPPORTED; }
     const bool unsupported = d->terrain_step_height != 0.f || d->terrain_step_width != 0.f || d->terrain_platform_width != 0.f ||
         d->terrain_grid_width != 0.f || d->terrain_grid_height_max != 0.f || d->instance_count > 1u || d->contact_family != 0u ||
         d->heightfield_terrain_type != 0u || (d->heightfield_image_path != nullptr && d->heightfield_image_path[0] != '\0') ||
         d->curric_levels != 0u || d->curric_types != 0u || d->cloth_integrator != 0u || d->ogc_contact_capacity != 0u ||
-        d->solver_substeps > 1u || d->contact_detection_substeps > 1u || d->osc_task_link != 0u;
+        d->solver_substeps > 1u || d->contact_detection_substeps > 1u;
     if (unsupported) { SetError("the world desc selects a feature outside the articulated step path"); return NUKA_RESULT_NOT_SUPPORTED; }
     if (d->solver_vel_iters > 65535u) { SetError("solver_vel_iters exceeds 65535"); return NUKA_RESULT_INVALID_ARG; }
     if (d->solver_pos_iters > 65535u) { SetError("solver_pos_iters exceeds 65535"); return NUKA_RESULT_INVALID_ARG; }
@@ -143,6 +143,7 @@ nuka_result_t CreateWorld(nuka_device_handle device, const nuka_world_desc_t* de
         nkb::HostTemplate tpl = nkb::HostTemplate::Parse(blob, bytes);
         if (desc->fixed_dt > 0.f) tpl.cfg.dt = desc->fixed_dt;
         tpl.cfg.control_mode = desc->control_mode;
+        tpl.cfg.task_link = desc->osc_task_link;
         if (desc->gravity_x != 0.f || desc->gravity_y != 0.f || desc->gravity_z != 0.f) {
             tpl.cfg.gravity[0] = desc->gravity_x; tpl.cfg.gravity[1] = desc->gravity_y; tpl.cfg.gravity[2] = desc->gravity_z;
         }

@@ -188,7 +188,7 @@ NKB_DEV void stage_drives(Env& e) {
     const float target = e.s->drive_target[at], kp = e.s->kp[at], kd = e.s->kd[at], vt = e.s->vel_target[at];
     const float limit = e.s->force_limit[at], ff = e.s->feedforward[at];
     const uint32_t mode = t.cfg.control_mode;
-    const bool inverse_dynamics = mode == 3u;          // computed torque: the command comes from stage_computed_torque
+    const bool inverse_dynamics = mode == 3u || mode == 4u;          // computed torque, operational space: the command comes from stage_computed_torque
     const bool position_control = mode == 0u || inverse_dynamics, velocity_control = mode == 2u;
     if ((position_control && (!isfinite(target) || !isfinite(kp) || kp < 0.f || !isfinite(kd) || kd < 0.f)) ||
         ((position_control || velocity_control) && !isfinite(vt)) || (velocity_control && (!isfinite(kp) || kp < 0.f)) ||
@@ -494,10 +494,255 @@ NKB_DEV void stage_dynamics(Env& e, bool integrate_velocity) {
 // allocation of the step kernel's common path.
 struct TorqueIn {
     float* sm; const SmemLayout* lay; const TemplateView* t; const StateView* s;
-    uint32_t env, lane, jtype, link_dof;
+    uint32_t env, lane, jtype, link_dof, mode;
     float q, qd, qdd, lower, upper;
 };
 struct TorqueOut { float tau, command; uint32_t status; uint32_t applied; };
+
+// Pseudoinverse of the symmetric n x n task metric (n = 3 or 6, row stride 6) by cyclic Jacobi rotations; directions whose
+// eigenvalue is within 8 eps of the largest are dropped (ops/articulation.cu:1234-1288).  One lane.
+static __device__ __noinline__ void task_metric_pseudoinverse(float* a, uint32_t n, float* inverse) {
+    float vec[36];
+    for (int i = 0; i < 36; ++i) vec[i] = 0.f;
+    for (uint32_t i = 0u; i < n; ++i) vec[i * 6u + i] = 1.0f;
+    for (uint32_t sweep = 0u; sweep < 24u; ++sweep) {
+        bool changed = false;
+        for (uint32_t p = 0u; p < n; ++p) for (uint32_t q = p + 1u; q < n; ++q) {
+            const float app = a[p * 6u + p], aqq = a[q * 6u + q], apq = a[p * 6u + q];
+            if (fabsf(apq) <= FLT_EPSILON * (fabsf(app) + fabsf(aqq))) continue;
+            changed = true;
+            const double theta = ((double)aqq - app) / (2.0 * apq);
+            const float tangent = (float)(copysign(1.0, theta) / (fabs(theta) + sqrt(1.0 + theta * theta)));
+            const float cosine = rsqrtf(1.0f + tangent * tangent), sine = tangent * cosine;
+            for (uint32_t k = 0u; k < n; ++k) {
+                if (k != p && k != q) {
+                    const float kp = a[k * 6u + p], kq = a[k * 6u + q];
+                    const float np_ = cosine * kp - sine * kq, nq = sine * kp + cosine * kq;
+                    a[k * 6u + p] = np_; a[p * 6u + k] = np_; a[k * 6u + q] = nq; a[q * 6u + k] = nq;
+                }
+                const float vp = vec[k * 6u + p], vq = vec[k * 6u + q];
+                vec[k * 6u + p] = cosine * vp - sine * vq;
+                vec[k * 6u + q] = sine * vp + cosine * vq;
+            }
+            a[p * 6u + p] = app - tangent * apq;
+            a[q * 6u + q] = aqq + tangent * apq;
+            a[p * 6u + q] = 0.f; a[q * 6u + p] = 0.f;
+        }
+        if (!changed) break;
+    }
+    float largest = 0.f;
+    for (uint32_t i = 0u; i < n; ++i) largest = fmaxf(largest, a[i * 6u + i]);
+    const float tolerance = largest * (8.0f * FLT_EPSILON);
+    for (uint32_t r = 0u; r < n; ++r) for (uint32_t c = 0u; c < n; ++c) {
+        double v = 0.0;
+        for (uint32_t k = 0u; k < n; ++k) {
+            const float eigenvalue = a[k * 6u + k];
+            if (eigenvalue > tolerance) v += (double)vec[r * 6u + k] * vec[c * 6u + k] / eigenvalue;
+        }
+        inverse[r * 6u + c] = (float)v;
+    }
+}
+
+// The task frame's velocity and acceleration in the world from the task link's twist and force-free acceleration (link
+// frame, angular first) plus J q'', the pose error, and from them kp x_err - kd v - a (ops/articulation.cu:1490-1513).
+static __device__ __noinline__ void task_right_hand_side(TorqueIn e, const float* acc0, const float* J, const float* qdd, float* trhs, uint32_t rows,
+                                                         V3 task_pos, Q4 task_q, Q4 link_q, V3 offset, Q4 desired) {
+    const TemplateView& t = *e.t;
+    const uint32_t n = t.ndof, L = t.L, tl = t.cfg.task_link;
+    const float* vel = e.sm + e.lay->vel + 6u * tl;
+    const V3 omega = ld3(vel), linear = ld3(vel + 3);
+    const V3 alpha = mk3(acc0[0], acc0[1], acc0[2]), linear_accel = mk3(acc0[3], acc0[4], acc0[5]);
+    const V3 g = mk3(t.cfg.gravity[0], t.cfg.gravity[1], t.cfg.gravity[2]);
+    const V3 task_velocity = qrot(link_q, linear + cross(omega, offset));
+    const V3 task_angular = qrot(link_q, omega);
+    V3 task_accel = qrot(link_q, (linear_accel + cross(omega, linear)) + (cross(alpha, offset) + cross(omega, cross(omega, offset)))) + g;
+    V3 task_angular_accel = qrot(link_q, alpha);
+    float jq[6];
+    for (uint32_t r = 0u; r < 6u; ++r) {
+        float sum = 0.f;
+        for (uint32_t i = 0u; i < n; ++i) sum += J[r * n + i] * qdd[i];
+        jq[r] = sum;
+    }
+    task_accel = task_accel + mk3(jq[0], jq[1], jq[2]);
+    task_angular_accel = task_angular_accel + mk3(jq[3], jq[4], jq[5]);
+    const V3 position_error = ld3(e.s->task_target + (size_t)e.env * 3u) - task_pos;
+    V3 orientation_error = mk3(0.f, 0.f, 0.f);
+    if (rows == 6u) {
+        const Q4 current = qnorm_le(task_q, 1.0e-12f), wanted = qnorm_le(desired, 1.0e-12f);
+        const Q4 err = qmul(wanted, mkq(current.w, -current.x, -current.y, -current.z));
+        const float sign = err.w < 0.f ? -1.0f : 1.0f;
+        const float length = sqrtf(err.x * err.x + err.y * err.y + err.z * err.z);
+        const float scale = length > 1.0e-7f ? sign * 2.0f * atan2f(length, fabsf(err.w)) / length : sign * 2.0f;
+        orientation_error = mk3(err.x * scale, err.y * scale, err.z * scale);
+    }
+    const float kp = e.s->kp[(size_t)e.env * L + tl], kd = e.s->kd[(size_t)e.env * L + tl];
+    trhs[0] = kp * position_error.x - kd * task_velocity.x - task_accel.x;
+    trhs[1] = kp * position_error.y - kd * task_velocity.y - task_accel.y;
+    trhs[2] = kp * position_error.z - kd * task_velocity.z - task_accel.z;
+    trhs[3] = kp * orientation_error.x - kd * task_angular.x - task_angular_accel.x;
+    trhs[4] = kp * orientation_error.y - kd * task_angular.y - task_angular_accel.y;
+    trhs[5] = kp * orientation_error.z - kd * task_angular.z - task_angular_accel.z;
+}
+
+// Operational-space control (control mode 4), the Osc branch of ApplyDynamicsDriveKernel (ops/articulation.cu:1419-1550),
+// entered with H = (S M^-1 S^T)^-1 in `H`, the actuated joints' table in `dofs` and their force-free accelerations,
+// passive terms and inputs in the solver vectors.  J (6 x n, linear rows first) is the Jacobian of the task frame in the
+// world, B = J M^-1 S^T (`resp`), the task force F = (B H B^T)^+ (kp x_err - kd v - a_free - B (bias + damping + posture))
+// acts through H B^T (`tmap`).  Joints on the chain from the task link to the root hold their posture through the
+// nullspace gains, the others through their own drive gains.  Lanes share the work: lane = link for the Jacobian columns,
+// lane = task row for the mass solves, lane = actuated joint for the products; the 6 x 6 pseudoinverse runs on lane 0.
+// The task link's acceleration is the force-free pass's velocity-product acceleration (q'' = 0, `acc0`, read before the
+// actuated-inertia matrix overwrites the link scratch) plus J q''.
+struct OscIn { uint32_t active, rank, joints; float acc0[6]; };
+template <int NR>
+static __device__ __noinline__ float osc_command(TorqueIn e, OscIn o, uint32_t* status) {
+    const TemplateView& t = *e.t;
+    const uint32_t l = e.lane, L = t.L, n = t.ndof, ld = e.lay->ld, active = o.active, tl = t.cfg.task_link;
+    const bool scalar = l < L && joint_dofs(e.jtype) == 1u;
+    const bool column = l < active;
+    float* vecs = e.sm + e.lay->vecs;
+    constexpr uint32_t vs = 32u * NR;
+    const float* free_acc = vecs + vs * kVecFree;
+    const float* passive = vecs + vs * kVecU;
+    float* prhs = vecs + vs * kVecPseudo;                    // posture accelerations of the chain joints
+    const uint32_t* dofs = reinterpret_cast<const uint32_t*>(vecs + vs * kVecTmp);
+    float* command = vecs + vs * kVecTmp2;
+    float* own = vecs + vs * kVecAcc;                        // off-chain joints: their own PD effort (the LDL^T diagonal is dead)
+    const float* F = e.sm + e.lay->factor;
+    float* H = e.sm + e.lay->heads;
+    float* qdd = H + active * active;                        // all n force-free accelerations (saved by the caller)
+    float* J = qdd + n;                                      // 6 x n
+    float* resp = J + 6u * n;                                // 6 x active
+    float* tmap = resp + 6u * active;                        // 6 x active
+    float* metric = tmap + 6u * active;                      // 6 x 6
+    float* inverse = metric + 36u;                           // 6 x 6
+    float* bias = inverse + 36u;                             // active
+    float* posture = bias + active;                          // active
+    float* chain = posture + active;                         // n flags
+    float* trhs = chain + n;                                 // 6
+    float* force = trhs + 6u;                                // 6
+    const size_t at = (size_t)e.env * L + l;
+    const float* pose_t = e.sm + e.lay->pose + 7u * tl;
+    const float* frame = e.s->task_frame + (size_t)e.env * 7u;
+    const Q4 frame_q = qnorm_le(ldq(frame + 3), 1.0e-12f);
+    const V3 offset = ld3(frame);
+    const Q4 link_q = ldq(pose_t + 3);
+    const V3 task_pos = ld3(pose_t) + qrot(link_q, offset);
+    const Q4 task_q = qnorm_le(qmul(link_q, frame_q), 1.0e-12f);
+    // bias = -d qd - H qdd_free, lane = actuated joint
+    if (column) {
+        double b = passive[l];
+        for (uint32_t c = 0u; c < active; ++c) b -= (double)H[l * active + c] * free_acc[c];
+        bias[l] = (float)b;
+    }
+    for (uint32_t i = l; i < 6u * n; i += 32u) J[i] = 0.f;
+    for (uint32_t i = l; i < n; i += 32u) chain[i] = 0.f;
+    __syncwarp();
+    // Jacobian columns, lane = link on the chain from the task link to the root
+    const bool on_chain = l < L && ((__ldg(t.anc_mask + tl) >> l) & 1u) != 0u;
+    if (on_chain) {
+        const float* pose_l = e.sm + e.lay->pose + 7u * l;
+        const V3 lever = task_pos - ld3(pose_l);
+        const uint32_t dof = e.link_dof;
+        if (e.jtype == kFloating) {
+            const Q4 base_q = ldq(e.s->base_pose + (size_t)e.env * 7u + 3);
+#pragma unroll
+            for (uint32_t c = 0u; c < 3u; ++c) {
+                const V3 axis = qrot(base_q, mk3(c == 0u ? 1.f : 0.f, c == 1u ? 1.f : 0.f, c == 2u ? 1.f : 0.f));
+                const V3 lin = cross(axis, lever);
+                J[dof + c] = lin.x; J[n + dof + c] = lin.y; J[2u * n + dof + c] = lin.z;
+                J[3u * n + dof + c] = axis.x; J[4u * n + dof + c] = axis.y; J[5u * n + dof + c] = axis.z;
+                J[dof + 3u + c] = axis.x; J[n + dof + 3u + c] = axis.y; J[2u * n + dof + 3u + c] = axis.z;
+            }
+        } else if (joint_dofs(e.jtype) == 1u) {
+            const V3 axis = qrot(ldq(pose_l + 3), ld3(t.axis + 3u * l));
+            const bool revolute = e.jtype == kRevolute;
+            const V3 lin = revolute ? cross(axis, lever) : axis, ang = revolute ? axis : mk3(0.f, 0.f, 0.f);
+            J[dof] = lin.x; J[n + dof] = lin.y; J[2u * n + dof] = lin.z;
+            J[3u * n + dof] = ang.x; J[4u * n + dof] = ang.y; J[5u * n + dof] = ang.z;
+            chain[dof] = 1.f;
+        }
+    }
+    __syncwarp();
+    const Q4 desired = ldq(e.s->task_rotation + (size_t)e.env * 4u);
+    const uint32_t rows = desired.w * desired.w + desired.x * desired.x + desired.y * desired.y + desired.z * desired.z > 1.0e-12f ? 6u : 3u;
+    // B: M x = J_r^T through the L D L^T factor, lane = task row
+    if (l < rows) {
+        float x[32 * NR];
+        for (uint32_t i = 0u; i < n; ++i) x[i] = J[l * n + i];
+        for (uint32_t j = 0u; j < n; ++j)
+            for (uint32_t i = j + 1u; i < n; ++i) x[i] -= F[i * ld + j] * x[j];
+        for (uint32_t i = 0u; i < n; ++i) x[i] /= F[i * ld + i];
+        for (uint32_t end = n; end > 0u; --end) {
+            const uint32_t i = end - 1u;
+            float sum = x[i];
+            for (uint32_t j = i + 1u; j < n; ++j) sum -= F[j * ld + i] * x[j];
+            x[i] = sum;
+        }
+        for (uint32_t c = 0u; c < active; ++c) resp[l * active + c] = x[dofs[c]];
+    }
+    __syncwarp();
+    if (column)
+        for (uint32_t r = 0u; r < rows; ++r) {
+            double v = 0.0;
+            for (uint32_t a = 0u; a < active; ++a) v += (double)H[l * active + a] * resp[r * active + a];
+            tmap[r * active + l] = (float)v;
+        }
+    for (uint32_t i = l; i < 72u; i += 32u) metric[i] = 0.f;      // metric and inverse
+    __syncwarp();
+    for (uint32_t i = l; i < rows * rows; i += 32u) {
+        const uint32_t r = i / rows, c = i % rows;
+        double v = 0.0;
+        for (uint32_t a = 0u; a < active; ++a) v += (double)resp[r * active + a] * tmap[c * active + a];
+        metric[r * 6u + c] = (float)v;
+    }
+    __syncwarp();
+    if (l == 0u) task_metric_pseudoinverse(metric, rows, inverse);
+    // the task frame's velocity and force-free acceleration in the world, the task-space right-hand side: lane 0
+    if (l == 0u) task_right_hand_side(e, o.acc0, J, qdd, trhs, rows, task_pos, task_q, link_q, offset, desired);
+    // posture: nullspace gains on the chain's joints (as accelerations through H), own gains elsewhere
+    if (scalar) {
+        const float pd_error = e.s->drive_target[at] - e.q, rate_error = e.s->vel_target[at] - e.qd;
+        const bool mine_on_chain = chain[e.link_dof] != 0.f;
+        prhs[o.rank] = mine_on_chain ? e.s->null_kp[e.env] * pd_error + e.s->null_kd[e.env] * rate_error : 0.f;
+        own[o.rank] = mine_on_chain ? 0.f : e.s->kp[at] * pd_error + e.s->kd[at] * rate_error;
+    }
+    __syncwarp();
+    if (column) {
+        double v = 0.0;
+        for (uint32_t c = 0u; c < active; ++c) v += (double)H[l * active + c] * prhs[c];
+        const bool off_chain = chain[dofs[l]] == 0.f;
+        if (off_chain) v += own[l];
+        posture[l] = (float)v;
+    }
+    __syncwarp();
+    if (l < rows) {
+        float rhs = trhs[l];
+        for (uint32_t a = 0u; a < active; ++a) rhs -= resp[l * active + a] * (bias[a] - passive[a] + posture[a]);
+        trhs[l] = rhs;
+    }
+    __syncwarp();
+    if (l < rows) {
+        float sum = 0.f;
+        for (uint32_t c = 0u; c < rows; ++c) sum += inverse[l * 6u + c] * trhs[c];
+        force[l] = sum;
+    }
+    __syncwarp();
+    float value = 0.f;
+    if (column) {
+        double v = bias[l] + posture[l];
+        for (uint32_t r = 0u; r < rows; ++r) v += (double)tmap[r * active + l] * force[r];
+        value = (float)v;
+    }
+    const bool finite = __all_sync(NKB_FULL, !column || isfinite(value));
+    if (column) command[l] = finite ? value : 0.f;
+    __syncwarp();
+    if (!finite) *status = kStatusControlFailure;
+    const float mine = scalar ? command[o.rank] : 0.f;
+    __syncwarp();
+    return mine;
+}
+
 template <int NR>
 __device__ __noinline__ TorqueOut computed_torque(TorqueIn e) {
     const TemplateView& t = *e.t;
@@ -507,6 +752,20 @@ __device__ __noinline__ TorqueOut computed_torque(TorqueIn e) {
     const bool scalar = l < L && joint_dofs(e.jtype) == 1u;
     // a drive the affine stage rejected (bounds left at zero) switches the controller off for the env
     if (__any_sync(NKB_FULL, scalar && e.lower == 0.f && e.upper == 0.f)) return out;
+    const bool osc = e.mode == 4u;
+    if (osc) {          // ops/articulation.cu:1341-1360: every task input finite, gains non-negative
+        const uint32_t tl = t.cfg.task_link;
+        const float* in3 = e.s->task_target + (size_t)e.env * 3u;
+        const float* in4 = e.s->task_rotation + (size_t)e.env * 4u;
+        const float* in7 = e.s->task_frame + (size_t)e.env * 7u;
+        const float gains[4] = {e.s->kp[(size_t)e.env * L + tl], e.s->kd[(size_t)e.env * L + tl], e.s->null_kp[e.env], e.s->null_kd[e.env]};
+        bool ok = true;
+        for (int k = 0; k < 3; ++k) ok &= isfinite(in3[k]);
+        for (int k = 0; k < 4; ++k) ok &= isfinite(in4[k]);
+        for (int k = 0; k < 7; ++k) ok &= isfinite(in7[k]);
+        for (int k = 0; k < 4; ++k) ok &= isfinite(gains[k]) && gains[k] >= 0.f;
+        if (!ok) { out.status = kStatusControlFailure; return out; }
+    }
     const uint32_t joints = __ballot_sync(NKB_FULL, scalar);
     const uint32_t active = (uint32_t)__popc(joints);
     if (active == 0u) return out;
@@ -524,6 +783,18 @@ __device__ __noinline__ TorqueOut computed_torque(TorqueIn e) {
     float* H = e.sm + e.lay->heads;
     const float* F = e.sm + e.lay->factor;
     out.applied = 1u;
+    OscIn osc_in;
+    osc_in.active = active; osc_in.rank = rank; osc_in.joints = joints;
+    if (osc) {
+        // before the actuated-inertia matrix overwrites the link scratch and the solver vectors: the task link's force-free
+        // acceleration and all n force-free coordinate accelerations
+        const float* a0 = e.sm + e.lay->acc + 6u * t.cfg.task_link;
+#pragma unroll
+        for (int k = 0; k < 6; ++k) osc_in.acc0[k] = a0[k];
+        float* keep = H + active * active;
+        for (uint32_t i = l; i < n; i += 32u) keep[i] = vecs[vs * kVecAcc + i];
+    }
+    __syncwarp();
     if (scalar) {
         out.tau = e.s->feedforward[at];
         dofs[rank] = e.link_dof;
@@ -588,6 +859,12 @@ __device__ __noinline__ TorqueOut computed_torque(TorqueIn e) {
         for (uint32_t r = 0u; r < active; ++r) H[r * active + l] = x[r];
     }
     __syncwarp();
+    if (osc) {
+        uint32_t failed = 0u;
+        out.command = osc_command<NR>(e, osc_in, &failed);
+        out.status = failed;
+        return out;
+    }
     // command = bias + H rhs, bias = -d qd - H qdd_free; lane r owns row r
     float value = 0.f;
     if (column) {
@@ -610,6 +887,7 @@ template <int NR>
 NKB_DEV void stage_computed_torque(Env& e) {
     TorqueIn in;
     in.sm = e.sm; in.lay = e.lay; in.t = e.t; in.s = e.s; in.env = e.env; in.lane = e.lane; in.jtype = e.jtype; in.link_dof = e.link_dof;
+    in.mode = e.t->cfg.control_mode;
     in.q = e.q; in.qd = e.qd; in.qdd = e.qdd; in.lower = e.drive_lower; in.upper = e.drive_upper;
     const TorqueOut out = computed_torque<NR>(in);
     e.status |= out.status;

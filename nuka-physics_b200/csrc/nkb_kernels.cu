@@ -21,25 +21,29 @@ __global__ void reset_kernel(ResetParams r) {
 }
 
 extern const StepVariant kStepNarrow, kStepNarrowSlim, kStepNarrowRigid, kStepWide, kStepWideRigid;
+extern const StepVariant kStepNarrowControl, kStepNarrowRigidControl, kStepWideControl, kStepWideRigidControl;
 
-bool step_kernel_has_slim(uint32_t ndof, uint32_t n_free) { return ndof <= 32u && n_free == 0u; }
+bool step_kernel_has_slim(uint32_t ndof, uint32_t n_free, bool control) { return ndof <= 32u && n_free == 0u && !control; }
 
 // up to 32 or up to 64 coordinates per articulation; with or without free rigid bodies; the slim (128-register) build
 // exists for the first kind only
-static const StepVariant& step_variant(uint32_t ndof, uint32_t n_free, bool slim) {
+static const StepVariant& step_variant(uint32_t ndof, uint32_t n_free, bool slim, bool control) {
+    // control modes 3 and 4 run the builds that hold the controllers
+    if (control) return ndof > 32u ? (n_free != 0u ? kStepWideRigidControl : kStepWideControl) : (n_free != 0u ? kStepNarrowRigidControl : kStepNarrowControl);
     if (ndof > 32u) return n_free != 0u ? kStepWideRigid : kStepWide;
     if (n_free != 0u) return kStepNarrowRigid;
     return slim ? kStepNarrowSlim : kStepNarrow;
 }
 
-int step_kernel_registers(uint32_t ndof, uint32_t n_free, bool slim) { return step_variant(ndof, n_free, slim).registers(); }
+int step_kernel_registers(uint32_t ndof, uint32_t n_free, bool slim, bool control) { return step_variant(ndof, n_free, slim, control).registers(); }
 
-int step_kernel_resident_blocks(uint32_t ndof, uint32_t n_free, bool slim, uint32_t warps_per_block, size_t shared_bytes) {
-    return step_variant(ndof, n_free, slim).resident_blocks(warps_per_block, shared_bytes);
+int step_kernel_resident_blocks(uint32_t ndof, uint32_t n_free, bool slim, bool control, uint32_t warps_per_block, size_t shared_bytes) {
+    return step_variant(ndof, n_free, slim, control).resident_blocks(warps_per_block, shared_bytes);
 }
 
 cudaError_t launch_step(const StepParams& p, uint32_t warps_per_block, bool slim, cudaStream_t stream) {
-    return step_variant(p.t.ndof, p.t.n_free, slim).launch(p, warps_per_block, stream);
+    const bool control = p.t.cfg.control_mode == 3u || p.t.cfg.control_mode == 4u;
+    return step_variant(p.t.ndof, p.t.n_free, slim && !control, control).launch(p, warps_per_block, stream);
 }
 
 // One observation record per env, composed from the state arrays in one pass (the reference's gym layer builds the same

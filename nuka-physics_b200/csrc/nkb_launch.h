@@ -14,7 +14,7 @@ struct ResetField {
     uint32_t per_env_src; // 1: src is E x words
     uint32_t fill;
 };
-constexpr uint32_t kMaxResetFields = 28u;
+constexpr uint32_t kMaxResetFields = 36u;
 struct ResetParams {
     uint32_t env_count;
     const uint32_t* env_ids;   // device list of envs to reset, or null for all
@@ -27,11 +27,11 @@ struct ResetParams {
 // shared memory and block slots considered); 0 when the shape cannot launch.  The device must be current.
 // The step kernel has one variant per (coordinates per lane, free rigid bodies present) pair, chosen from `ndof`
 // (up to 32 / up to 64 coordinates) and `n_free` (free dynamic bodies per env).
-int step_kernel_resident_blocks(uint32_t ndof, uint32_t n_free, bool slim, uint32_t warps_per_block, size_t shared_bytes);
+int step_kernel_resident_blocks(uint32_t ndof, uint32_t n_free, bool slim, bool control, uint32_t warps_per_block, size_t shared_bytes);
 // Whether a slim (128-register) build of the world's kernel variant exists.
-bool step_kernel_has_slim(uint32_t ndof, uint32_t n_free);
+bool step_kernel_has_slim(uint32_t ndof, uint32_t n_free, bool control);
 // Registers per thread of the step kernel variant that serves the world.
-int step_kernel_registers(uint32_t ndof, uint32_t n_free, bool slim);
+int step_kernel_registers(uint32_t ndof, uint32_t n_free, bool slim, bool control);
 // Host-side handle of one compiled step-kernel variant.
 struct StepParams;
 struct StepVariant {

@@ -162,7 +162,7 @@ NKB_DEV void stage_store_bodies(Env& e, bool velocities) {
 #ifndef NKB_MAXNREG_SLIM
 #define NKB_MAXNREG_SLIM 128
 #endif
-template <int NR, bool kRigid>
+template <int NR, bool kRigid, bool kControl>
 NKB_DEV void advance_env(const StepParams& p, float* sm, uint32_t env, uint32_t lane) {
     const TemplateView& t = p.t;
     const bool has_artic = t.L != 0u, has_bodies = t.B != 0u;
@@ -183,13 +183,14 @@ NKB_DEV void advance_env(const StepParams& p, float* sm, uint32_t env, uint32_t 
         tick(e, 0);
         if (has_artic) {
             stage_fk(e); tick(e, 1); stage_drives(e);
-            // computed torque (pipeline.cpp:406-426) takes two passes: a force-free one on the current kinematics, the
+            // computed torque and operational-space control (pipeline.cpp:406-426) take two passes: a force-free one on the current kinematics, the
             // controller on its mass response and accelerations, then the step's own pass
-            const bool two_passes = t.cfg.control_mode == 3u && p.mode != kModeDynamicsOnly;
+            // the controllers are compiled into the kControl builds of the kernel only (they would cost every other world registers)
+            const bool two_passes = kControl && (t.cfg.control_mode == 3u || t.cfg.control_mode == 4u) && p.mode != kModeDynamicsOnly;
 #pragma unroll 1
             for (int pass = two_passes ? 0 : 1; pass < 2; ++pass) {
                 stage_dynamics<NR>(e, pass == 1 && p.mode != kModeDynamicsOnly);
-                if (pass == 0) stage_computed_torque<NR>(e);
+                if constexpr (kControl) { if (pass == 0) stage_computed_torque<NR>(e); }
             }
             tick(e, 2);
         }
@@ -344,7 +345,7 @@ NKB_DEV void team_helper(float* sm, const SmemLayout& shared_layout, const Templ
 
 // Block layout: blockDim.x / 32 warps, `team` consecutive warps per env (one unless the world runs in team mode); an
 // env's shared-memory slice is shared by its team.
-template <int NR, bool kRigid, bool kSlim>
+template <int NR, bool kRigid, bool kSlim, bool kControl>
 __global__ void __maxnreg__(kRigid ? NKB_MAXNREG_RIGID : (kSlim ? NKB_MAXNREG_SLIM : NKB_MAXNREG)) step_kernel(const __grid_constant__ StepParams p) {
     extern __shared__ __align__(16) float smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -366,14 +367,14 @@ __global__ void __maxnreg__(kRigid ? NKB_MAXNREG_RIGID : (kSlim ? NKB_MAXNREG_SL
     if constexpr (kRigid) {
         if (member != 0u) { team_helper<kRigid>(sm, p.sm, p.t, p.s, env, member, lane, 32u * NR); return; }
     }
-    advance_env<NR, kRigid>(p, sm, env, lane);
+    advance_env<NR, kRigid, kControl>(p, sm, env, lane);
     if constexpr (kRigid) { if ((p.sm.team_drill & 1u) == 0u) team_dismiss(sm, p.sm, lane); }
 }
 
 // Raises the kernel's dynamic shared-memory limit to `bytes` if it is not there yet.  The limit is per function and
 // per device and only ever grows, so worlds of different sizes stepped from different threads cannot undo each other's
 // setting between the attribute call and the launch.
-template <int NR, bool kRigid, bool kSlim>
+template <int NR, bool kRigid, bool kSlim, bool kControl>
 static cudaError_t variant_reserve_shared(size_t bytes) {
     static std::mutex lock;
     static size_t reserved[64] = {0};
@@ -384,48 +385,48 @@ static cudaError_t variant_reserve_shared(size_t bytes) {
     if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
     std::lock_guard<std::mutex> hold(lock);
     if (bytes <= reserved[device]) return cudaSuccess;
-    err = cudaFuncSetAttribute(step_kernel<NR, kRigid, kSlim>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    err = cudaFuncSetAttribute(step_kernel<NR, kRigid, kSlim, kControl>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (err == cudaSuccess) reserved[device] = bytes;
     return err;
 }
 
-template <int NR, bool kRigid, bool kSlim>
+template <int NR, bool kRigid, bool kSlim, bool kControl>
 static int variant_resident_blocks(uint32_t warps_per_block, size_t shared_bytes) {
-    if (variant_reserve_shared<NR, kRigid, kSlim>(shared_bytes) != cudaSuccess) {
+    if (variant_reserve_shared<NR, kRigid, kSlim, kControl>(shared_bytes) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     int blocks = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, step_kernel<NR, kRigid, kSlim>, (int)(warps_per_block * 32u), shared_bytes) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, step_kernel<NR, kRigid, kSlim, kControl>, (int)(warps_per_block * 32u), shared_bytes) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     return blocks;
 }
 
-template <int NR, bool kRigid, bool kSlim>
+template <int NR, bool kRigid, bool kSlim, bool kControl>
 static int variant_registers() {
     cudaFuncAttributes attr{};
-    if (cudaFuncGetAttributes(&attr, step_kernel<NR, kRigid, kSlim>) != cudaSuccess) { cudaGetLastError(); return 0; }
+    if (cudaFuncGetAttributes(&attr, step_kernel<NR, kRigid, kSlim, kControl>) != cudaSuccess) { cudaGetLastError(); return 0; }
     return attr.numRegs;
 }
 
-template <int NR, bool kRigid, bool kSlim>
+template <int NR, bool kRigid, bool kSlim, bool kControl>
 static cudaError_t variant_launch(const StepParams& p, uint32_t warps_per_block, cudaStream_t stream) {
     const uint32_t team = kRigid ? p.sm.team : 1u;
     const uint32_t envs_per_block = warps_per_block / team;
     if (envs_per_block == 0u || envs_per_block * team != warps_per_block || envs_per_block > 15u) return cudaErrorInvalidConfiguration;
     const size_t bytes = (size_t)envs_per_block * p.sm.words * sizeof(float);
-    const cudaError_t err = variant_reserve_shared<NR, kRigid, kSlim>(bytes);
+    const cudaError_t err = variant_reserve_shared<NR, kRigid, kSlim, kControl>(bytes);
     if (err != cudaSuccess) return err;
     const uint32_t envs = p.sel_ids != nullptr ? p.sel_count : p.s.env_count;
     if (envs == 0u) return cudaSuccess;
     const uint32_t blocks = (envs + envs_per_block - 1u) / envs_per_block;
-    step_kernel<NR, kRigid, kSlim><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
+    step_kernel<NR, kRigid, kSlim, kControl><<<blocks, warps_per_block * 32u, bytes, stream>>>(p);
     return cudaGetLastError();
 }
 
-#define NKB_STEP_VARIANT(name, NR, RIGID, SLIM) \
-    extern const StepVariant name = {variant_resident_blocks<NR, RIGID, SLIM>, variant_registers<NR, RIGID, SLIM>, variant_launch<NR, RIGID, SLIM>};
+#define NKB_STEP_VARIANT(name, NR, RIGID, SLIM, CONTROL) \
+    extern const StepVariant name = {variant_resident_blocks<NR, RIGID, SLIM, CONTROL>, variant_registers<NR, RIGID, SLIM, CONTROL>, variant_launch<NR, RIGID, SLIM, CONTROL>};
 
 }  // namespace nkb

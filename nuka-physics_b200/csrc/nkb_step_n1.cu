@@ -2,5 +2,5 @@
 #include "nkb_step.cuh"
 
 namespace nkb {
-NKB_STEP_VARIANT(kStepNarrow, 1, false, false)
+NKB_STEP_VARIANT(kStepNarrow, 1, false, false, false)
 }  // namespace nkb

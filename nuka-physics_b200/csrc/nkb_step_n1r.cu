@@ -2,5 +2,5 @@
 #include "nkb_step.cuh"
 
 namespace nkb {
-NKB_STEP_VARIANT(kStepNarrowRigid, 1, true, false)
+NKB_STEP_VARIANT(kStepNarrowRigid, 1, true, false, false)
 }  // namespace nkb

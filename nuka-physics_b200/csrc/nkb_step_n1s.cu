@@ -2,5 +2,5 @@
 #include "nkb_step.cuh"
 
 namespace nkb {
-NKB_STEP_VARIANT(kStepNarrowSlim, 1, false, true)
+NKB_STEP_VARIANT(kStepNarrowSlim, 1, false, true, false)
 }  // namespace nkb

@@ -2,5 +2,5 @@
 #include "nkb_step.cuh"
 
 namespace nkb {
-NKB_STEP_VARIANT(kStepWide, 2, false, false)
+NKB_STEP_VARIANT(kStepWide, 2, false, false, false)
 }  // namespace nkb

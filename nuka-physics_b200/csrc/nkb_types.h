@@ -50,7 +50,8 @@ struct Config {
     float gravity[3];
     float pos_beta, pos_slop, contact_margin, baumgarte_max_velocity, overlap_recovery_velocity, velocity_tolerance;
     uint32_t vel_iters, pos_iters, max_contacts, max_pairs;
-    uint32_t control_mode;      // 0 PD position, 1 torque, 2 velocity (reference phi/articulation_contract.hpp:16-23)
+    uint32_t control_mode;      // 0 PD position, 1 torque, 2 velocity, 3 computed torque, 4 operational space, 5 actuator (reference phi/articulation_contract.hpp:16-23)
+    uint32_t task_link;         // mode 4: the link that carries the task frame (nuka_world_desc_t.osc_task_link)
 };
 
 // Device pointers to the template tables (read-only during a step).
@@ -101,6 +102,7 @@ struct StateView {
     float *body_linvel, *body_angvel;                           // E x B x 3
     float *carry_artic;                                         // E x ndof  (solved - free velocity of the last step)
     float *carry_rigid;                                         // E x B x 6
+    float *task_target, *task_rotation, *task_frame, *null_kp, *null_kd;   // E x 3, E x 4 (wxyz, zero = position only), E x 7 (xyz + wxyz on the task link), E, E: mode 4 inputs
     float *limit_lambda;                                        // E x L x 2  (joint-limit multipliers of the last velocity solve: lower, upper)
     CacheEntry *cache;                                          // E x S x 4
     uint32_t *status;                                           // E

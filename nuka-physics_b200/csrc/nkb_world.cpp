@@ -98,6 +98,7 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
     t.cfg.baumgarte_max_velocity = cf[7]; t.cfg.overlap_recovery_velocity = cf[8]; t.cfg.velocity_tolerance = cf[9];
     t.cfg.vel_iters = cu[0]; t.cfg.pos_iters = cu[1]; t.cfg.max_contacts = cu[2]; t.cfg.max_pairs = cu[3];
     t.cfg.control_mode = 0u;       // the world descriptor selects another mode
+    t.cfg.task_link = 0u;
     // sweep counts bound the length of one kernel launch, which cannot be cancelled once it runs
     if (t.cfg.vel_iters > 65535u || t.cfg.pos_iters > 65535u) throw Error(kInvalidArg, "template iteration counts must not exceed 65535");
     t.L = cu[4]; t.B = cu[5];
@@ -303,6 +304,12 @@ void World::BuildLayout() {
     }
     tv.head_cap = (tv.point_cap + t.joint_rows + 3u) & ~3u;
     if (tv.head_cap == 0u) tv.head_cap = 4u;
+    if (t.cfg.control_mode == 4u) {
+        // the operational-space controller keeps its matrices in the head records' region between the two dynamics passes
+        if (t.cfg.task_link >= L) throw Error(kInvalidArg, "osc_task_link is not a link of the articulation");
+        const uint32_t need = n * n + 8u * n + 14u * n + 96u;
+        if (kHeadStride * tv.head_cap < need) tv.head_cap = ((need + kHeadStride - 1u) / kHeadStride + 3u) & ~3u;
+    }
     uint32_t at = 0;
     auto take = [&](uint32_t words) { const uint32_t o = at; at += (words + 3u) & ~3u; return o; };     // 16-byte aligned regions
     // float4-readable matrix rows: a multiple of 4 words that is 4 mod 8 (conflict-free for one lane per row)
@@ -368,11 +375,12 @@ void World::BuildLayout() {
     const uint32_t team = s.team;                  // a block holds whole teams: w counts warps, w / team envs
     size_t resident[2][kWarpsPerBlockMax + 1] = {{0}, {0}};
     size_t best[2] = {0, 0};
-    const bool has_slim = step_kernel_has_slim(n, t.n_free);
+    const bool control = t.cfg.control_mode == 3u || t.cfg.control_mode == 4u;       // these modes run the kernel builds that hold the controllers
+    const bool has_slim = step_kernel_has_slim(n, t.n_free, control);
     for (int slim = 0; slim < (has_slim ? 2 : 1); ++slim)
         for (uint32_t w = team; w <= kWarpsPerBlockMax; w += team) {
             if ((w / team) * bytes > 227u * 1024u) break;
-            resident[slim][w] = static_cast<size_t>(step_kernel_resident_blocks(n, t.n_free, slim != 0, w, (w / team) * bytes)) * w;      // asks the runtime
+            resident[slim][w] = static_cast<size_t>(step_kernel_resident_blocks(n, t.n_free, slim != 0, control, w, (w / team) * bytes)) * w;      // asks the runtime
             best[slim] = std::max(best[slim], resident[slim][w]);
         }
     // The slim build pays about 200 bytes of spills for a fourth warp per scheduler partition: worth it where shared
@@ -394,7 +402,7 @@ void World::BuildLayout() {
     }
     if (std::getenv("NUKA_B200_DEBUG_LAYOUT") != nullptr) {
         std::fprintf(stderr, "[nuka_b200] %zu B of shared memory per env, %d registers per thread%s; resident warps per SM by block size:", bytes,
-                     step_kernel_registers(n, t.n_free, slim_), slim_ ? " (slim build)" : "");
+                     step_kernel_registers(n, t.n_free, slim_, control), slim_ ? " (slim build)" : "");
         for (uint32_t w = 1; w <= kWarpsPerBlockMax; ++w) std::fprintf(stderr, " %u:%zu", w, fits[w]);
         std::fprintf(stderr, " -> %u warps per block, %u per env\n", warps_per_block_, team);
         std::fprintf(stderr, "[nuka_b200] word offsets: overlay %u mass %u vecs %u bodies %u contacts %u heads %u pool %u blocks %u end %u\n",
@@ -437,6 +445,8 @@ World::World(int device, cudaStream_t stream, const HostTemplate& tpl, uint32_t 
         s.base_pose = Alloc<float>(E * 7); s.link_pose = Alloc<float>(E * L * 7); s.link_vel = Alloc<float>(E * L * 6);
         s.drive_target = Alloc<float>(E * L); s.vel_target = Alloc<float>(E * L); s.noload_speed = Alloc<float>(E * L); s.acc_target = Alloc<float>(E * L); s.kp = Alloc<float>(E * L); s.kd = Alloc<float>(E * L);
         s.force_limit = Alloc<float>(E * L); s.feedforward = Alloc<float>(E * L);
+        s.task_target = Alloc<float>(E * 3); s.task_rotation = Alloc<float>(E * 4); s.task_frame = Alloc<float>(E * 7);
+        s.null_kp = Alloc<float>(E); s.null_kd = Alloc<float>(E);
         s.body_pose = Alloc<float>(E * B * 7); s.body_linvel = Alloc<float>(E * B * 3); s.body_angvel = Alloc<float>(E * B * 3);
         s.carry_artic = Alloc<float>(E * n); s.carry_rigid = Alloc<float>(E * B * 6); s.limit_lambda = Alloc<float>(E * L * 2);
         s.cache = Alloc<CacheEntry>(E * S * 4);
@@ -494,6 +504,10 @@ void World::Seed() {
     add_seed(s.drive_target, q0, L); add_seed(s.kp, kp0, L); add_seed(s.kd, kd0, L); add_seed(s.force_limit, fl0, L);
     add_seed(s.vel_target, nullptr, L); add_seed(s.feedforward, nullptr, L); add_seed(s.noload_speed, nullptr, L);
     add_seed(s.acc_target, nullptr, L);
+    // operational-space inputs: no target, no orientation task, the task frame at the link's origin, no posture gains
+    const float* frame0 = Upload(std::vector<float>{0.f, 0.f, 0.f, 1.f, 0.f, 0.f, 0.f});
+    add_seed(s.task_target, nullptr, L ? 3u : 0u); add_seed(s.task_rotation, nullptr, L ? 4u : 0u); add_seed(s.task_frame, frame0, L ? 7u : 0u);
+    add_seed(s.null_kp, nullptr, L ? 1u : 0u); add_seed(s.null_kd, nullptr, L ? 1u : 0u);
     Check(launch_reset(seed, env_count_, stream_), "seed launch");
     ++launches_;
     Refresh();
@@ -710,6 +724,11 @@ bool World::Field(uint32_t id, FieldInfo* out) {
         case 14: return set(s.noload_speed, L, 0, true);
         case 22: return set(s.feedforward, L, 0, true);
         case 56: return set(s.acc_target, L, 0, true);
+        case 15: return set(s.task_target, L ? 3 : 0, 0, true);
+        case 31: return set(s.task_rotation, L ? 4 : 0, 0, true);
+        case 32: return set(s.task_frame, L ? 7 : 0, 0, true);
+        case 57: return set(s.null_kp, L ? 1 : 0, 0, true);
+        case 58: return set(s.null_kd, L ? 1 : 0, 0, true);
         case 25: return set(s.body_linvel, B * 3, 0, true);
         case 26: return set(s.body_angvel, B * 3, 0, true);
         case 27: return set(s.limit_lambda, L * 2, 0, false);

@@ -41,11 +41,16 @@ class Field(enum.IntEnum):
     TORQUE_INPUT = 12
     VELOCITY_TARGET = 13
     ACTUATOR_NOLOAD_SPEED = 14
+    TASK_TARGET = 15
     JOINT_FEEDFORWARD = 22
     ACCELERATION_TARGET = 56
+    TASK_NULLSPACE_STIFFNESS = 57
+    TASK_NULLSPACE_DAMPING = 58
     BODY_LINEAR_VELOCITY = 25
     BODY_ANGULAR_VELOCITY = 26
     JOINT_LIMIT_IMPULSE = 27
+    TASK_ROTATION_TARGET = 31
+    TASK_LOCAL_POSE = 32
     ACTUATOR_EFFORT = 29
     ENV_STATUS = 39
     SOLVER_RESIDUAL = 109

@@ -5,7 +5,8 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "libnuka_b200.so")
-SOURCES = ["nkb_step_n1.cu", "nkb_step_n1s.cu", "nkb_step_n1r.cu", "nkb_step_n2.cu", "nkb_step_n2r.cu", "nkb_kernels.cu", "nkb_static_reset.cu", "nkb_world.cpp", "nkb_scene.cpp", "nkb_abi.cpp"]
+SOURCES = ["nkb_step_n1.cu", "nkb_step_n1s.cu", "nkb_step_n1r.cu", "nkb_step_n2.cu", "nkb_step_n2r.cu",
+           "nkb_step_n1c.cu", "nkb_step_n1rc.cu", "nkb_step_n2c.cu", "nkb_step_n2rc.cu", "nkb_kernels.cu", "nkb_static_reset.cu", "nkb_world.cpp", "nkb_scene.cpp", "nkb_abi.cpp"]
 # nvcc defaults for floating point, as the reference builds its physics ops: IEEE division and square root, denormals
 # kept, fused multiply-add on.  (Approximate division / square root and flush-to-zero for the whole library measured 4 %
 # faster on the 4096-env quadruped step and changed no parity figure; the few places that use rsqrtf / __fdividef on

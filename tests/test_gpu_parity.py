@@ -580,3 +580,48 @@ def test_cylinder_manifolds_match_the_oracle(device, oracle):
         assert np.abs(w.download(field).reshape(E, S, 4, 3)[points] - o.get(name, 12 * S).reshape(E, S, 4, 3)[points]).max() < 1e-5
     assert np.abs(w.download(F.CONTACT_DEPTH).reshape(E, S, 4)[points] - o.get("contact_depth", 4 * S).reshape(E, S, 4)[points]).max() < 1e-5
     w.destroy()
+
+
+def test_operational_space_control_inputs(device, oracle):
+    """Control mode 4 on the arm against the oracle with position and orientation tasks, and its input checks: a task link
+    outside the articulation is refused at creation, a task link in another mode too, a non-finite target raises the
+    control-failure bit of that env only and leaves its command at zero."""
+    import sys
+    sys.path.insert(0, GOLDEN)
+    import ref_cases
+    E, L = 32, 8
+    tb = T.arm7(0)
+    st = ref_cases.arm_osc_state(E, 0)
+    with pytest.raises(nuka.NukaError) as err:
+        nuka.World.create_from_template(device, tb.blob(), E, control_mode=4, osc_task_link=8)
+    assert err.value.code == 1
+    with pytest.raises(nuka.NukaError) as err:
+        nuka.World.create_from_template(device, tb.blob(), E, control_mode=0, osc_task_link=7)
+    assert err.value.code == 7
+    w = nuka.World.create_from_template(device, tb.blob(), E, control_mode=4, osc_task_link=7)
+    o = oracle.World(tb.blob(), E)
+    o.set_control_mode(4); o.set_task_link(7)
+    target = st["task_target"].copy()
+    target[5, 1] = np.nan
+    fields = {"q": (F.JOINT_POSITION, "q"), "qdot": (F.JOINT_VELOCITY, "qdot"), "drive_target": (F.DRIVE_TARGET, "drive_target"),
+              "kp": (F.DRIVE_STIFFNESS, "drive_stiffness"), "kd": (F.DRIVE_DAMPING, "drive_damping"),
+              "task_rotation": (F.TASK_ROTATION_TARGET, "task_rotation_target"), "task_frame": (F.TASK_LOCAL_POSE, "task_local_pose"),
+              "null_kp": (F.TASK_NULLSPACE_STIFFNESS, "task_nullspace_stiffness"), "null_kd": (F.TASK_NULLSPACE_DAMPING, "task_nullspace_damping")}
+    for key, (field, name) in fields.items():
+        w.upload(field, st[key]); o.set(name, st[key].reshape(E, -1))
+    w.upload(F.TASK_TARGET, target); o.set("task_target", target)
+    w.forward_kinematics(); o.refresh()
+    w.step_n(1); o.step(1)
+    status = w.download(F.ENV_STATUS)[:, 0]
+    assert status[5] == 1 << 10 and not np.delete(status, 5).any()
+    assert np.array_equal(o.get("env_status", 1)[:, 0], status)
+    good = np.arange(E) != 5
+    assert rel(w.download(F.JOINT_VELOCITY)[good], o.get("qdot", L)[good]) < 1e-4
+    w.step_n(19); o.step(19)
+    # the six-row tasks amplify last-bit differences (see refparity.SENSITIVE); the position-only ones stay at 1e-5
+    assert rel(w.download(F.JOINT_POSITION)[good], o.get("q", L)[good]) < 1e-3
+    three_rows = good & (np.arange(E) % 2 == 1)
+    assert rel(w.download(F.JOINT_POSITION)[three_rows], o.get("q", L)[three_rows]) < 1e-5
+    w.reset()
+    assert np.array_equal(w.download(F.TASK_LOCAL_POSE), st["task_frame"])      # task inputs survive a reset, like the drive inputs
+    w.destroy()

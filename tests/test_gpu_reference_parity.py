@@ -24,13 +24,8 @@ def make_world(device, case):
     if ref is None:
         pytest.skip(f"no reference vectors for {case}")
     tb, E, L, n, S = RP.template(case, ref)
-    try:
-        w = nuka.World.create_from_template(device, tb.blob(), E, control_mode=RP.CONTROL_MODE.get(case, 0),
-                                            **({"osc_task_link": RP.TASK_LINK[case]} if case in RP.TASK_LINK else {}))
-    except (nuka.NukaError, TypeError):
-        if RP.CONTROL_MODE.get(case) == 4:
-            pytest.skip("operational-space control is not built into this library")
-        raise
+    w = nuka.World.create_from_template(device, tb.blob(), E, control_mode=RP.CONTROL_MODE.get(case, 0),
+                                        **({"osc_task_link": RP.TASK_LINK[case]} if case in RP.TASK_LINK else {}))
     st = RP.start_state(case, E)
     for k in ("q", "qdot", "base_pose", "body_pose"):
         if k in st:
