@@ -59,6 +59,10 @@ CASES = {
     **{f"random{k}": (lambda k=k: ref_cases.random_robot(k), lambda E, k=k: ref_cases.random_robot_state(k, E), 1.0 / 250.0, 6, 60, 20)
        for k in (0, 1, 3, 7)},
 }
+# Runs large enough for the reference to take its tree broadphase (B^2 E > 2^20, ops/broadphase.cu:581): kept as per-env
+# digests of the candidate pairs and contact counts (tests/refparity.py:pair_digests) plus the poses of the first 128 envs
+# (name: scene case, envs, dt, iterations, steps, sampling stride, start state)
+LARGE = {"pile12_tree": ("pile12", 8192, 1.0 / 240.0, 8, 30, 10, lambda E: {"body_pose": T.box_pile_state(E, 0, count=12)["body_pose"]})}
 SCENE_OF = {"quadruped_moving": "quadruped", "arm7_ct": "arm7", "quadruped_ct": "quadruped", "quadruped_torque": "quadruped",
             "quadruped_velocity": "quadruped", "quadruped_actuator": "quadruped", "arm7_osc": "arm7", "quadruped_osc": "quadruped"}
 CONTROL_MODE = {"arm7_ct": 3, "quadruped_ct": 3, "quadruped_torque": 1, "quadruped_velocity": 2, "quadruped_actuator": 5,
@@ -93,6 +97,12 @@ def prepare():
         if name in TASK_LINK:
             mode += f" --task-link {TASK_LINK[name]}"
         lines.append(f"../ref_driver --scene {name}.nks --envs {ENVS} --dt {dt!r} --vel-iters {iters}{mode} --state {name}_state.nkt "
+                     f"--steps {steps} --every {every} --dump \"$OUT/ref_{name}.nkt\"")
+    for name, (scene, envs, dt, iters, steps, every, state) in LARGE.items():
+        st = {k: np.ascontiguousarray(v, np.float32).reshape(envs, -1) for k, v in state(envs).items()}
+        with open(os.path.join(RUN, f"{name}_state.nkt"), "wb") as f:
+            f.write(nkt.pack(st))
+        lines.append(f"../ref_driver --scene {scene}.nks --envs {envs} --dt {dt!r} --vel-iters {iters} --state {name}_state.nkt "
                      f"--steps {steps} --every {every} --dump \"$OUT/ref_{name}.nkt\"")
     # the number to beat: the reference's own step on the bench workload, eager and graph mode, 100 warm-up + 1000 timed steps
     with open(os.path.join(RUN, "quadruped_state4096.nkt"), "wb") as f:
@@ -142,6 +152,22 @@ def collect(src):
         if L:
             out["traj_root_twist"] = arrays["traj_link_velocity"].reshape(samples, E, L, 6)[:, :, 0].copy()
         np.savez_compressed(os.path.join(HERE, f"ref_gpu_{name}.npz"), **out)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import refparity
+    for name in LARGE:
+        path = os.path.join(src, f"ref_{name}.nkt")
+        if not os.path.exists(path):
+            continue
+        with open(path, "rb") as f:
+            arrays = nkt.unpack(f.read())
+        E, B, S = int(arrays["run"][0]), int(arrays["run"][3]), int(arrays["run"][4])
+        K = len(arrays["traj_steps"])
+        digests = [refparity.pair_digests(arrays["traj_pair_count"].reshape(K, E)[i], arrays["traj_candidate_pairs"].reshape(K, E, S, 2)[i],
+                                          arrays["traj_contact_count"].reshape(K, E, S)[i]) for i in range(K)]
+        np.savez_compressed(os.path.join(HERE, f"ref_gpu_{name}.npz"), run=arrays["run"], run_dt=arrays["run_dt"], traj_steps=arrays["traj_steps"],
+                            traj_pair_count=arrays["traj_pair_count"].reshape(K, E), traj_status=arrays["traj_status"].reshape(K, E),
+                            pair_digest=np.stack([d[0] for d in digests]), contact_digest=np.stack([d[1] for d in digests]),
+                            traj_body_pose_head=arrays["traj_body_pose"].reshape(K, E, B * 7)[:, :128].copy())
     if not os.path.exists(os.path.join(src, "ref_timing.jsonl")):
         print("collected into", HERE, "(no timing file in", src + ")")
         return

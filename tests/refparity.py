@@ -179,6 +179,30 @@ def assert_velocity_parity(got, want, first, tag, case=None, keep=None):
         assert d.max() < 1e-3, (tag, float(d.max()))
 
 
+def slot_digest(values, live):
+    """One 64-bit word per env over the live candidate slots, in slot order: sum of (value + 1) * 1099511628211^(slot + 1)
+    modulo 2^64.  `values` is E x S (one integer per slot), `live` E x S booleans.  Lets a run of thousands of envs be
+    compared with the reference through a few bytes per env."""
+    values = np.asarray(values).astype(np.uint64)
+    E, S = values.shape
+    power = np.ones(S, np.uint64)
+    with np.errstate(over="ignore"):
+        for k in range(S):
+            power[k] = (power[k - 1] if k else np.uint64(1)) * np.uint64(1099511628211)
+        terms = (values + np.uint64(1)) * power[None, :]
+        return np.where(live, terms, np.uint64(0)).sum(axis=1, dtype=np.uint64)
+
+
+def pair_digests(pair_count, pairs, contact_count):
+    """(candidate-pair digest, contact-count digest) per env of one sample: pairs as a * 65536 + b."""
+    pair_count = np.asarray(pair_count).reshape(-1)
+    E = len(pair_count)
+    pairs = np.asarray(pairs).reshape(E, -1, 2).astype(np.uint64)
+    S = pairs.shape[1]
+    live = np.arange(S)[None, :] < pair_count[:, None]
+    return slot_digest(pairs[:, :, 0] * np.uint64(65536) + pairs[:, :, 1], live), slot_digest(np.asarray(contact_count).reshape(E, S), live)
+
+
 def start_state(case, E):
     """The per-env start state of a case, keyed by the names both worlds use (q, qdot, base_pose, body_pose)."""
     return {k: v for k, v in CASES[case][1](E).items() if k in ("q", "qdot", "base_pose", "body_pose", "link_velocity") or k in DRIVE_INPUTS}

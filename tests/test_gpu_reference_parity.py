@@ -108,3 +108,31 @@ def test_steps_match_the_reference(device, case):
             else:
                 assert same[keep].mean() >= 0.9, (case, s, float(same[keep].mean()))
     w.destroy()
+
+
+def test_tree_broadphase_matches_the_reference_at_8192_envs(device):
+    """8192 envs of the 12-box pile: the reference's broadphase takes its LBVH route there (B^2 E > 2^20), and so does this
+    library by the same rule.  Candidate pairs and contact counts, compared through per-env digests: bit-equal in all 8192
+    envs on the first step, afterwards in every env that has not left the reference's trajectory (at least 90 %)."""
+    from nuka import nks, templates as T
+    ref = RP.load("pile12_tree")
+    if ref is None:
+        pytest.skip("no reference vectors for pile12_tree")
+    E, B, S, iters = (int(ref["run"][k]) for k in (0, 3, 4, 5))
+    tb = nks.cook(RP.os.path.join(RP.GOLDEN, "scene_pile12.nks"), dt=float(ref["run_dt"][0]), vel_iters=iters, kp=0.0, kd=0.0,
+                  scene_filters=True, ground_height=None, max_contacts=S, max_points=RP.MAX_POINTS["pile12"])
+    w = nuka.World.create_from_template(device, tb.blob(), E)
+    w.upload(F.RIGID_BODY_TRANSFORM, T.box_pile_state(E, 0, count=12)["body_pose"].reshape(E, -1))
+    w.forward_kinematics()
+    done = 0
+    for i, s in enumerate(int(v) for v in ref["traj_steps"]):
+        w.step_n(s - done)
+        done = s
+        count = w.download(F.PAIR_COUNT)[:, 0]
+        pairs, contacts = RP.pair_digests(count, w.download(F.CANDIDATE_PAIRS), w.download(F.CONTACT_COUNT))
+        same = (pairs == ref["pair_digest"][i]) & (contacts == ref["contact_digest"][i]) & (count == ref["traj_pair_count"][i])
+        assert same.all() if i == 0 else same.mean() >= 0.9, (s, float(same.mean()))
+        d = RP.err_envs(w.download(F.RIGID_BODY_TRANSFORM).reshape(E, 7 * B)[:128], ref["traj_body_pose_head"][i], floor=1.0)
+        assert np.median(d) < 1e-5 and np.percentile(d, 90) < 1e-4, (s, float(np.median(d)), float(np.percentile(d, 90)))
+    assert not w.download(F.ENV_STATUS).any()
+    w.destroy()

@@ -114,3 +114,32 @@ def test_steps_match_the_reference(oracle, case):
                 assert same[keep].all(), (case, s, int((~same[keep]).sum()))
             else:
                 assert same[keep].mean() >= 0.9, (case, s, float(same[keep].mean()))
+
+
+def test_tree_broadphase_matches_the_reference_at_8192_envs(oracle):
+    """The reference stepped 8192 envs of the 12-box pile, where its broadphase takes the LBVH route (B^2 E > 2^20,
+    ops/broadphase.cu:581); its candidate pairs and contact counts are kept as per-env digests.  The oracle, with the tree
+    route forced, reproduces them on the first 256 envs (envs are independent): bit-equal on the first step, and afterwards
+    in every env whose trajectory has not left the reference's (at least 90 %: the pile is chaotic)."""
+    ref = RP.load("pile12_tree")
+    if ref is None:
+        pytest.skip("no reference vectors for pile12_tree")
+    E = 256
+    S, iters = int(ref["run"][4]), int(ref["run"][5])
+    B = int(ref["run"][3])
+    tb = RP.nks.cook(RP.os.path.join(RP.GOLDEN, "scene_pile12.nks"), dt=float(ref["run_dt"][0]), vel_iters=iters, kp=0.0, kd=0.0,
+                     scene_filters=True, ground_height=None, max_contacts=S, max_points=RP.MAX_POINTS["pile12"])
+    w = oracle.World(tb.blob(), E)
+    w.set_broadphase(2)
+    w.set("body_pose", RP.T.box_pile_state(8192, 0, count=12)["body_pose"].reshape(8192, -1)[:E])
+    w.refresh()
+    done = 0
+    for i, s in enumerate(int(v) for v in ref["traj_steps"]):
+        w.step(s - done)
+        done = s
+        pairs, contacts = RP.pair_digests(w.get("pair_count", 1)[:, 0], w.get("candidate_pairs", 2 * S), w.get("contact_count", S))
+        same = (pairs == ref["pair_digest"][i][:E]) & (contacts == ref["contact_digest"][i][:E]) & \
+               (w.get("pair_count", 1)[:, 0] == ref["traj_pair_count"][i][:E])
+        assert same.all() if i == 0 else same.mean() >= 0.9, (s, float(same.mean()))
+        d = RP.err_envs(w.get("body_pose", 7 * B)[:128], ref["traj_body_pose_head"][i], floor=1.0)
+        assert np.median(d) < 1e-5 and np.percentile(d, 90) < 1e-4, (s, float(np.median(d)), float(np.percentile(d, 90)))
