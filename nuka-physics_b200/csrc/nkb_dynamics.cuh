@@ -192,7 +192,7 @@ NKB_DEV void stage_drives(Env& e) {
     const bool position_control = mode == 0u || inverse_dynamics, velocity_control = mode == 2u;
     if ((position_control && (!isfinite(target) || !isfinite(kp) || kp < 0.f || !isfinite(kd) || kd < 0.f)) ||
         ((position_control || velocity_control) && !isfinite(vt)) || (velocity_control && (!isfinite(kp) || kp < 0.f)) ||
-        (inverse_dynamics && !isfinite(e.s->acc_target[at]))) {
+        (mode == 3u && !isfinite(e.s->acc_target[at]))) {
         e.status |= kStatusControlFailure; return;
     }
     const float noload = mode == 5u ? e.s->noload_speed[at] : 0.f;

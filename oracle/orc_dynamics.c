@@ -61,7 +61,7 @@ void orc_apply_drives(const orc_model *m, orc_env *e) {
                                   !isfinite(e->kd[l]) || e->kd[l] < 0.0f)) ||
             ((position_control || velocity_control) && !isfinite(e->vel_target[l])) ||
             (velocity_control && (!isfinite(e->kp[l]) || e->kp[l] < 0.0f)) ||
-            (inverse_dynamics && !isfinite(e->acc_target[l])) ||
+            (mode == 3u && !isfinite(e->acc_target[l])) ||
             (mode == 5u && !isfinite(e->noload_speed[l]))) {
             e->status |= ORC_STATUS_CONTROL_FAILURE;
             continue;
