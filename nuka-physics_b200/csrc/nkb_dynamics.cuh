@@ -499,48 +499,57 @@ struct TorqueIn {
 };
 struct TorqueOut { float tau, command; uint32_t status; uint32_t applied; };
 
-// Pseudoinverse of the symmetric n x n task metric (n = 3 or 6, row stride 6) by cyclic Jacobi rotations; directions whose
-// eigenvalue is within 8 eps of the largest are dropped (ops/articulation.cu:1234-1288).  One lane.
-static __device__ __noinline__ void task_metric_pseudoinverse(float* a, uint32_t n, float* inverse) {
-    float vec[36];
-    for (int i = 0; i < 36; ++i) vec[i] = 0.f;
-    for (uint32_t i = 0u; i < n; ++i) vec[i * 6u + i] = 1.0f;
+// Pseudoinverse of the symmetric n x n task metric (n = 3 or 6, row stride 6, in shared memory) by cyclic Jacobi rotations
+// in the reference's pair order and with its rotation formulas (ops/articulation.cu:1234-1288); directions whose
+// eigenvalue is within 8 eps of the largest are dropped.  The whole warp takes part: every lane follows the pivots, lane
+// k < n carries row k of the matrix and of the eigenvector table through each rotation, lane 0 closes the 2 x 2 block,
+// and the n x n entries of the result are spread over the lanes.  `vectors` is 36 words of scratch beside the matrix.
+static __device__ __noinline__ void task_metric_pseudoinverse(float* a, float* vectors, uint32_t n, float* inverse, uint32_t lane) {
+    for (uint32_t i = lane; i < 36u; i += 32u) vectors[i] = (i / 6u == i % 6u && i / 6u < n) ? 1.0f : 0.f;
+    __syncwarp();
     for (uint32_t sweep = 0u; sweep < 24u; ++sweep) {
         bool changed = false;
         for (uint32_t p = 0u; p < n; ++p) for (uint32_t q = p + 1u; q < n; ++q) {
             const float app = a[p * 6u + p], aqq = a[q * 6u + q], apq = a[p * 6u + q];
-            if (fabsf(apq) <= FLT_EPSILON * (fabsf(app) + fabsf(aqq))) continue;
+            if (fabsf(apq) <= FLT_EPSILON * (fabsf(app) + fabsf(aqq))) continue;       // the same words in every lane: a uniform branch
             changed = true;
             const double theta = ((double)aqq - app) / (2.0 * apq);
             const float tangent = (float)(copysign(1.0, theta) / (fabs(theta) + sqrt(1.0 + theta * theta)));
             const float cosine = rsqrtf(1.0f + tangent * tangent), sine = tangent * cosine;
-            for (uint32_t k = 0u; k < n; ++k) {
+            __syncwarp();
+            if (lane < n) {
+                const uint32_t k = lane;
                 if (k != p && k != q) {
                     const float kp = a[k * 6u + p], kq = a[k * 6u + q];
-                    const float np_ = cosine * kp - sine * kq, nq = sine * kp + cosine * kq;
-                    a[k * 6u + p] = np_; a[p * 6u + k] = np_; a[k * 6u + q] = nq; a[q * 6u + k] = nq;
+                    const float turned_p = cosine * kp - sine * kq, turned_q = sine * kp + cosine * kq;
+                    a[k * 6u + p] = turned_p; a[p * 6u + k] = turned_p; a[k * 6u + q] = turned_q; a[q * 6u + k] = turned_q;
                 }
-                const float vp = vec[k * 6u + p], vq = vec[k * 6u + q];
-                vec[k * 6u + p] = cosine * vp - sine * vq;
-                vec[k * 6u + q] = sine * vp + cosine * vq;
+                const float vp = vectors[k * 6u + p], vq = vectors[k * 6u + q];
+                vectors[k * 6u + p] = cosine * vp - sine * vq;
+                vectors[k * 6u + q] = sine * vp + cosine * vq;
             }
-            a[p * 6u + p] = app - tangent * apq;
-            a[q * 6u + q] = aqq + tangent * apq;
-            a[p * 6u + q] = 0.f; a[q * 6u + p] = 0.f;
+            if (lane == 0u) {
+                a[p * 6u + p] = app - tangent * apq;
+                a[q * 6u + q] = aqq + tangent * apq;
+                a[p * 6u + q] = 0.f; a[q * 6u + p] = 0.f;
+            }
+            __syncwarp();
         }
         if (!changed) break;
     }
     float largest = 0.f;
     for (uint32_t i = 0u; i < n; ++i) largest = fmaxf(largest, a[i * 6u + i]);
     const float tolerance = largest * (8.0f * FLT_EPSILON);
-    for (uint32_t r = 0u; r < n; ++r) for (uint32_t c = 0u; c < n; ++c) {
+    for (uint32_t i = lane; i < n * n; i += 32u) {
+        const uint32_t r = i / n, c = i % n;
         double v = 0.0;
         for (uint32_t k = 0u; k < n; ++k) {
             const float eigenvalue = a[k * 6u + k];
-            if (eigenvalue > tolerance) v += (double)vec[r * 6u + k] * vec[c * 6u + k] / eigenvalue;
+            if (eigenvalue > tolerance) v += (double)vectors[r * 6u + k] * vectors[c * 6u + k] / eigenvalue;
         }
         inverse[r * 6u + c] = (float)v;
     }
+    __syncwarp();
 }
 
 // The task frame's velocity and acceleration in the world from the task link's twist and force-free acceleration (link
@@ -621,6 +630,7 @@ static __device__ __noinline__ float osc_command(TorqueIn e, OscIn o, uint32_t* 
     float* chain = posture + active;                         // n flags
     float* trhs = chain + n;                                 // 6
     float* force = trhs + 6u;                                // 6
+    float* eigenvectors = force + 6u;                        // 6 x 6 scratch of the pseudoinverse
     const size_t at = (size_t)e.env * L + l;
     const float* pose_t = e.sm + e.lay->pose + 7u * tl;
     const float* frame = e.s->task_frame + (size_t)e.env * 7u;
@@ -697,7 +707,7 @@ static __device__ __noinline__ float osc_command(TorqueIn e, OscIn o, uint32_t* 
         metric[r * 6u + c] = (float)v;
     }
     __syncwarp();
-    if (l == 0u) task_metric_pseudoinverse(metric, rows, inverse);
+    task_metric_pseudoinverse(metric, eigenvectors, rows, inverse, l);
     // the task frame's velocity and force-free acceleration in the world, the task-space right-hand side: lane 0
     if (l == 0u) task_right_hand_side(e, o.acc0, J, qdd, trhs, rows, task_pos, task_q, link_q, offset, desired);
     // posture: nullspace gains on the chain's joints (as accelerations through H), own gains elsewhere

@@ -307,7 +307,7 @@ void World::BuildLayout() {
     if (t.cfg.control_mode == 4u) {
         // the operational-space controller keeps its matrices in the head records' region between the two dynamics passes
         if (t.cfg.task_link >= L) throw Error(kInvalidArg, "osc_task_link is not a link of the articulation");
-        const uint32_t need = n * n + 8u * n + 14u * n + 96u;
+        const uint32_t need = n * n + 8u * n + 14u * n + 140u;
         if (kHeadStride * tv.head_cap < need) tv.head_cap = ((need + kHeadStride - 1u) / kHeadStride + 3u) & ~3u;
     }
     uint32_t at = 0;
