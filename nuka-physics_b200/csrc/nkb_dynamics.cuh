@@ -599,7 +599,7 @@ static __device__ __noinline__ void task_right_hand_side(TorqueIn e, const float
 // world, B = J M^-1 S^T (`resp`), the task force F = (B H B^T)^+ (kp x_err - kd v - a_free - B (bias + damping + posture))
 // acts through H B^T (`tmap`).  Joints on the chain from the task link to the root hold their posture through the
 // nullspace gains, the others through their own drive gains.  Lanes share the work: lane = link for the Jacobian columns,
-// lane = task row for the mass solves, lane = actuated joint for the products; the 6 x 6 pseudoinverse runs on lane 0.
+// lane = task row for the mass solves, lane = actuated joint for the products, lane = matrix row inside the pseudoinverse's rotations.
 // The task link's acceleration is the force-free pass's velocity-product acceleration (q'' = 0, `acc0`, read before the
 // actuated-inertia matrix overwrites the link scratch) plus J q''.
 struct OscIn { uint32_t active, rank, joints; float acc0[6]; };
