@@ -195,6 +195,11 @@ typedef struct nuka_buffer_view_t {
     uint8_t dtype;                     /* 0 f32, 1 u32, 2 u64, 3 u8 */
 } nuka_buffer_view_t;
 nuka_result_t nuka_world_get_buffer_view(nuka_world_handle world, nuka_state_field_t field, nuka_buffer_view_t* out);
+/* nuka.h:1222-1234.  The name of link `link_index` (links of all envs in a row: index modulo links per env): the joint whose
+ * child the link's body is, else the body's own name, as the scene file gives them.  A null `out` asks for the length
+ * (*out_len, without the terminator); a buffer too small for name + NUL is INVALID_ARG with *out_len still set.
+ * NOT_SUPPORTED for worlds whose template carries no names (the procedural templates). */
+nuka_result_t nuka_world_get_dof_name(nuka_world_handle world, uint32_t link_index, char* out, size_t cap, size_t* out_len);
 /* nuka.h:1180-1187: host <-> field byte transfer; out-of-range is INVALID_ARG, unknown field NOT_SUPPORTED. */
 nuka_result_t nuka_world_upload_field(nuka_world_handle world, nuka_state_field_t field, const void* bytes, size_t nbytes, size_t byte_offset);
 nuka_result_t nuka_world_download_field(nuka_world_handle world, nuka_state_field_t field, void* bytes, size_t nbytes, size_t byte_offset);

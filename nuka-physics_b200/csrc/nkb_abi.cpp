@@ -632,6 +632,22 @@ nuka_result_t nuka_b200_world_set_contact_readout(nuka_world_handle world, uint3
     return Guard([&]() { w->SetContactReadout(enabled != 0u); return NUKA_RESULT_OK; });
 }
 
+// src/c_abi/world.cpp:1170-1215: link_index runs over every env's links; a null `out` is a size query
+nuka_result_t nuka_world_get_dof_name(nuka_world_handle world, uint32_t link_index, char* out, size_t cap, size_t* out_len) {
+    if (out_len != nullptr) *out_len = 0u;
+    NKB_WORLD(w)
+    const std::vector<std::string>& names = w->tpl().link_names;
+    if (names.empty()) { SetError("the world's template carries no link names"); return NUKA_RESULT_NOT_SUPPORTED; }
+    const uint64_t total = static_cast<uint64_t>(names.size()) * w->env_count();
+    if (link_index >= total) { SetError("link_index is out of range"); return NUKA_RESULT_INVALID_ARG; }
+    const std::string& name = names[link_index % names.size()];
+    if (out_len != nullptr) *out_len = name.size();
+    if (out == nullptr) return NUKA_RESULT_OK;
+    if (name.size() + 1u > cap) { SetError("the buffer cannot hold the name and its terminator"); return NUKA_RESULT_INVALID_ARG; }
+    std::memcpy(out, name.c_str(), name.size() + 1u);
+    return NUKA_RESULT_OK;
+}
+
 nuka_result_t nuka_b200_world_launch_count(nuka_world_handle world, uint64_t* out) {
     NKB_WORLD(w)
     if (out == nullptr) { SetError("out pointer is null"); return NUKA_RESULT_INVALID_ARG; }

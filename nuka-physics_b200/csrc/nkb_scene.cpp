@@ -240,6 +240,7 @@ struct LinkRow {
     bool limited = false;
     double lower = 0, upper = 0;
     float inertia[36] = {0};
+    std::string name;          // the joint whose child the body is, else the body's own (src/c_abi/world.cpp:1186-1199)
 };
 struct BodyRow {
     uint32_t kind = kSphere, contype = 0, conaffinity = 0, group = 0, link = kNoLink, geom = 0;
@@ -429,6 +430,8 @@ class Cooker {
         static const Json none;
         LinkRow l;
         l.parent = parent_link;
+        l.name = joint != nullptr ? joint->String("name", "") : std::string();
+        if (l.name.empty()) l.name = node.String("name", "");
         if (parent_link == kNoLink) {
             l.jtype = rb.Truthy("is_static") ? kFixed : kFloating;
             const double bp[7] = {pose.pos.x, pose.pos.y, pose.pos.z, pose.quat.w, pose.quat.x, pose.quat.y, pose.quat.z};
@@ -634,6 +637,16 @@ class Cooker {
         }
         out.U64("excluded", std::vector<uint64_t>(excluded.begin(), excluded.end()));
         if (o_.max_points != 0u) out.U32("max_points", {o_.max_points});
+        bool named = false;
+        for (const LinkRow& l : tb_.links) named |= !l.name.empty();
+        if (named) {        // NUL-terminated names in link order, padded to whole words
+            std::string raw;
+            for (const LinkRow& l : tb_.links) { raw += l.name; raw.push_back('\0'); }
+            while (raw.size() % 4u != 0u) raw.push_back('\0');
+            std::vector<uint32_t> words(raw.size() / 4u);
+            std::memcpy(words.data(), raw.data(), raw.size());
+            out.U32("link_names", words);
+        }
         return out.Finish();
     }
 

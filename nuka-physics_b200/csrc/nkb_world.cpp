@@ -140,6 +140,21 @@ HostTemplate HostTemplate::Parse(const void* blob_in, size_t bytes) {
             t.max_points = BlobVec<uint32_t>(blob, bytes, "max_points", 1)[0];
             if (t.max_points > 1024u) throw Error(kInvalidArg, "max_points above 1024");
         }
+        BlobEntry names;
+        if (BlobFind(blob, bytes, "link_names", &names)) {
+            // NUL-terminated names in link order inside a word array; exactly L of them, the rest padding
+            if (names.dtype != 1u) throw Error(kParseError, "link_names must be a u32 record");
+            const char* text = reinterpret_cast<const char*>(names.data);
+            const size_t length = static_cast<size_t>(names.n) * 4u;
+            size_t at = 0;
+            for (uint32_t l = 0; l < L; ++l) {
+                const void* end = at < length ? std::memchr(text + at, 0, length - at) : nullptr;
+                if (end == nullptr) throw Error(kParseError, "link_names holds fewer names than links");
+                const size_t stop = static_cast<size_t>(static_cast<const char*>(end) - text);
+                t.link_names.emplace_back(text + at, stop - at);
+                at = stop + 1u;
+            }
+        }
     }
     t.q0 = BlobVec<float>(blob, bytes, "q0", L);
     t.base_pose0 = BlobVec<float>(blob, bytes, "base_pose0", 7);

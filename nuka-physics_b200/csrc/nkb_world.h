@@ -32,6 +32,7 @@ struct HostTemplate {
     std::vector<uint32_t> adm_pairs;
     std::vector<uint32_t> adm_mask;      // B x ceil(B / 32) words, bit b of row a for admissible a < b
     uint32_t max_points = 0;            // template's contact-point capacity, 0 = default
+    std::vector<std::string> link_names;   // optional: one name per link (the joint whose child the link is, else the body's)
     std::vector<uint32_t> body_geom_kind;          // per collidable row (several rows may mirror one link)
     std::vector<float> body_geom_pos, body_geom_quat;
     std::vector<uint32_t> free_slot;

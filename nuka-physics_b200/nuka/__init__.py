@@ -270,6 +270,22 @@ class World:
     def run_stage(self, stage):
         _check(_abi.lib().nuka_b200_world_run_stage(self._h, stage))
 
+    def dof_names(self):
+        """Names of one env's links in link order (reference python/nuka: World.dof_names): the joint whose child the link
+        is, else the body's name; the root's is usually empty or the trunk's."""
+        names = []
+        for link in range(self.info.links_per_env):
+            need = ctypes.c_size_t()
+            _check(_abi.lib().nuka_world_get_dof_name(self._h, link, None, 0, ctypes.byref(need)))
+            buf = ctypes.create_string_buffer(need.value + 1)
+            _check(_abi.lib().nuka_world_get_dof_name(self._h, link, buf, need.value + 1, ctypes.byref(need)))
+            names.append(buf.value.decode())
+        return names
+
+    def dof_index(self, name):
+        """Link index of the joint or body called `name`."""
+        return self.dof_names().index(name)
+
     def launch_count(self):
         out = ctypes.c_uint64()
         _check(_abi.lib().nuka_b200_world_launch_count(self._h, ctypes.byref(out)))

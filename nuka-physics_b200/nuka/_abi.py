@@ -66,6 +66,7 @@ EXPORTS = [
     "nuka_b200_world_pack_observations", "nuka_b200_observation_desc_defaults", "nuka_b200_world_reset_envs_masked",
     "nuka_b200_world_set_contact_readout", "nuka_b200_world_set_broadphase", "nuka_b200_template_check", "nuka_b200_cook_options_defaults", "nuka_b200_scene_cook", "nuka_world_checkpoint_capture", "nuka_world_checkpoint_restore", "nuka_checkpoint_destroy",
     "nuka_checkpoint_write", "nuka_world_checkpoint_read", "nuka_checkpoint_byte_size", "nuka_checkpoint_equal", "nuka_world_state_hash",
+    "nuka_world_get_dof_name",
 ]
 
 _LIB = None
@@ -114,6 +115,7 @@ def lib():
     L.nuka_world_get_stream.argtypes = [vp, ctypes.POINTER(vp)]
     L.nuka_world_record_event.argtypes = [vp, vp]
     L.nuka_world_get_buffer_view.argtypes = [vp, ctypes.c_int, ctypes.POINTER(BufferView)]
+    L.nuka_world_get_dof_name.argtypes = [vp, ctypes.c_uint32, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]
     L.nuka_world_upload_field.argtypes = [vp, ctypes.c_int, vp, sz, sz]
     L.nuka_world_download_field.argtypes = [vp, ctypes.c_int, vp, sz, sz]
     L.nuka_b200_world_info.argtypes = [vp, ctypes.POINTER(WorldInfo)]

@@ -138,6 +138,8 @@ def cook(scene, dt=1.0 / 200.0, vel_iters=4, kp=60.0, kd=2.0, ground_height=0.0,
                            shape=_shape_of(first) if first else None,
                            shape_pos=_pose(first, "local")[0] if first else (0, 0, 0), shape_quat=_pose(first, "local")[1] if first else (1, 0, 0, 0),
                            mu=float(first.get("friction_mu", 1.0)) if first else 1.0, local_pos=local_pos, local_quat=local_quat, **robot_bits)
+        # the name a caller asks for: the joint whose child this body is, else the body's (src/c_abi/world.cpp:1186-1199)
+        tb.links[link]["name"] = str((node.get("joint") or {}).get("name", "") or node.get("name", ""))
         if single and float(joint.get("stiffness", 0.0)) != 0.0:
             raise ValueError("joint springs are not carried over")
         if first:

@@ -160,6 +160,11 @@ class TemplateBuilder:
         out["excluded"] = np.array(sorted(excluded), dtype=np.uint64)
         if self.max_points:
             out["max_points"] = np.array([self.max_points], dtype=u32)
+        names = [l.get("name", "") for l in self.links]
+        if any(names):
+            # NUL-terminated UTF-8 names in link order, padded to whole words: what nuka_world_get_dof_name serves
+            raw = b"".join(n.encode() + b"\0" for n in names)
+            out["link_names"] = np.frombuffer(raw + b"\0" * (-len(raw) % 4), dtype=u32).copy()
         return out
 
     def blob(self):

@@ -333,3 +333,26 @@ def test_slim_and_regular_kernel_builds_give_the_same_state(device):
         w.destroy()
     for a, b in zip(*out):
         assert np.array_equal(a, b)
+
+
+def test_dof_names_of_a_scene_world(device):
+    """nuka_world_get_dof_name on a world created from a scene file: joint names in link order, the size query, a buffer
+    that is too small, an index past the last env's links; NOT_SUPPORTED for a procedural template without names."""
+    import ctypes
+    import os
+    from nuka import _abi, templates as T
+    scene = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "scene_quadruped.nks")
+    w = nuka.World.create_from_scene(device, scene, 4)
+    assert w.dof_names() == ["link0"] + [f"joint{i}" for i in range(1, 13)]
+    assert w.dof_index("joint7") == 7
+    need = ctypes.c_size_t()
+    assert _abi.lib().nuka_world_get_dof_name(w._h, 13 * 3 + 2, None, 0, ctypes.byref(need)) == 0 and need.value == 6      # env 3's joint2
+    small = ctypes.create_string_buffer(4)
+    assert _abi.lib().nuka_world_get_dof_name(w._h, 2, small, 4, ctypes.byref(need)) == 1 and need.value == 6
+    assert _abi.lib().nuka_world_get_dof_name(w._h, 13 * 4, None, 0, ctypes.byref(need)) == 1
+    w.destroy()
+    w = nuka.World.create_from_template(device, T.quadruped(0).blob(), 4)
+    with pytest.raises(nuka.NukaError) as err:
+        w.dof_names()
+    assert err.value.code == 7
+    w.destroy()

@@ -72,3 +72,15 @@ def test_contact_point_capacity_travels_in_the_template(tmp_path):
     fixture = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "go2.nkt")
     with open(fixture, "rb") as f:
         assert nkt.unpack(f.read())["max_points"].tolist() == [32]
+
+
+def test_link_names_travel_in_the_template():
+    """The cooked template names every link after the joint whose child it is (the root after its body), NUL-terminated in
+    one word record; templates built without names carry no such record."""
+    import os
+    from nuka import templates as T
+    scene = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "scene_quadruped.nks")
+    a = nks.cook(scene).arrays()
+    names = a["link_names"].tobytes().split(b"\0")[:13]
+    assert [n.decode() for n in names] == ["link0"] + [f"joint{i}" for i in range(1, 13)]
+    assert "link_names" not in T.quadruped(0).arrays()

@@ -74,8 +74,8 @@ def test_scene_round_trip_gives_back_the_template(name):
                     max_contacts=tb.cfg["max_contacts"], max_points=tb.max_points or None).arrays()
     want = tb.arrays()
     for key in want:
-        if key in ("cfg_f", "cfg_u", "body_id") or (key == "base_pose0" and (want["jtype"].size == 0 or want["jtype"][0] != T.FLOATING)):
-            continue                                  # a fixed root's placement lives in its local pose; base_pose is unused
+        if key in ("cfg_f", "cfg_u", "body_id", "link_names") or (key == "base_pose0" and (want["jtype"].size == 0 or want["jtype"][0] != T.FLOATING)):
+            continue                                  # a fixed root's placement lives in its local pose; base_pose is unused; the writer names links by index
         got, expected = np.asarray(back[key], np.float64), np.asarray(want[key], np.float64)
         if key == "armature":                         # a root has no joint to carry one
             got, expected = got[1:], expected[1:]
