@@ -282,9 +282,30 @@ class World:
             names.append(buf.value.decode())
         return names
 
-    def dof_index(self, name):
-        """Link index of the joint or body called `name`."""
-        return self.dof_names().index(name)
+    def dof_index(self, pattern):
+        """Link columns whose name matches the regular expression `pattern` (int32 array, possibly empty), as the reference's
+        World.dof_index (python/src/nuka_ext.cpp:3014-3048): a leading 'entity/' is dropped, unnamed links never match.
+        Index the per-link buffers with it: ``targets[:, world.dof_index("thigh")]``."""
+        import re
+        expr = re.compile(pattern.rsplit("/", 1)[-1])
+        return np.array([k for k, name in enumerate(self.dof_names()) if name and expr.search(name)], dtype=np.int32)
+
+    @property
+    def base_link_count(self):
+        """Links per env; the per-link buffers are this wide, slot 0 is the root (nuka_ext.cpp:2772)."""
+        return self.info.links_per_env
+
+    @property
+    def action_dim(self):
+        """Actuated joint columns a policy controls: base_link_count - 1 (nuka_ext.cpp:2777-2783)."""
+        return self.info.links_per_env - 1
+
+    def set_drive_targets(self, values):
+        """Writes all env_count x base_link_count drive targets from a flat host array (nuka_ext.cpp:3120-3140)."""
+        values = np.ascontiguousarray(values, dtype=np.float32).reshape(-1)
+        if values.size != self.env_count * self.info.links_per_env:
+            raise ValueError(f"set_drive_targets: array length {values.size} != DRIVE_TARGET count {self.env_count * self.info.links_per_env}")
+        self.upload(Field.DRIVE_TARGET, values.reshape(self.env_count, -1))
 
     def launch_count(self):
         out = ctypes.c_uint64()

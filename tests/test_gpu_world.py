@@ -344,7 +344,10 @@ def test_dof_names_of_a_scene_world(device):
     scene = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "scene_quadruped.nks")
     w = nuka.World.create_from_scene(device, scene, 4)
     assert w.dof_names() == ["link0"] + [f"joint{i}" for i in range(1, 13)]
-    assert w.dof_index("joint7") == 7
+    assert list(w.dof_index("joint7")) == [7] and list(w.dof_index("robot/joint1")) == [1, 10, 11, 12] and w.dof_index("nothing").size == 0
+    assert w.base_link_count == 13 and w.action_dim == 12
+    w.set_drive_targets(np.arange(4 * 13, dtype=np.float32))
+    assert np.array_equal(w.download(F.DRIVE_TARGET).reshape(-1), np.arange(4 * 13, dtype=np.float32))
     need = ctypes.c_size_t()
     assert _abi.lib().nuka_world_get_dof_name(w._h, 13 * 3 + 2, None, 0, ctypes.byref(need)) == 0 and need.value == 6      # env 3's joint2
     small = ctypes.create_string_buffer(4)
